@@ -1,0 +1,95 @@
+"""ctypes binding of libqlm_b200.so -- one prototype per declaration in include/qlm_b200.h."""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+# binary layout of qlmb_span == the reference's QSpanD (qlm.cuh:30-38)
+SPAN_DTYPE = np.dtype([("pof", "<u8"), ("gof", "<u8"), ("qi0", "<u8"), ("n", "<u8"),
+                       ("gi0", "<i4"), ("ngrp", "<i4"), ("sref", "<f4"), ("_pad", "<i4")])
+
+F32, BF16 = 0, 1
+KN, NK = 0, 1
+
+
+class QlmbError(RuntimeError):
+    pass
+
+
+class MoeLayer(C.Structure):
+    _fields_ = [("N", C.c_int), ("D", C.c_int), ("F", C.c_int), ("E", C.c_int), ("K", C.c_int),
+                ("dtype", C.c_int),
+                ("w1_codes", C.c_void_p), ("w3_codes", C.c_void_p), ("w2_codes", C.c_void_p),
+                ("w1_scales", C.c_void_p), ("w3_scales", C.c_void_p), ("w2_scales", C.c_void_p),
+                ("wr", C.c_void_p), ("bias", C.c_void_p), ("bias_stride", C.c_int), ("aux", C.c_float)]
+
+
+vp, ci, cf, u64, sz = C.c_void_p, C.c_int, C.c_float, C.c_uint64, C.c_size_t
+
+# name -> (restype, argtypes); the symbol test walks this table against the header
+PROTOTYPES = {
+    "qlmb_last_error": (C.c_char_p, []),
+    "qlmb_version": (ci, []),
+    "qlmb_check_device": (ci, [vp]),
+    "qlmb_encode": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
+    "qlmb_render": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
+    "qlmb_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, cf, cf, cf, cf, cf, vp, cf, cf,
+                       ci, u64, ci, vp, ci, ci, ci, vp]),
+    "qlmb_servo": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, cf, cf, ci, vp]),
+    "qlmb_gnorm": (ci, [vp, sz, vp, vp, ci, ci, vp, vp]),
+    "qlmb_adamw": (ci, [vp, vp, vp, vp, sz, cf, cf, cf, cf, cf, cf, vp, vp]),
+    "qlmb_linear_fwd": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp, ci, vp]),
+    "qlmb_linear_dgrad": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, cf, ci, vp]),
+    "qlmb_linear_wgrad": (ci, [vp, vp, vp, ci, ci, ci, ci, cf, ci, vp]),
+    "qlmb_gemv_decode": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
+    "qlmb_router_topk": (ci, [vp, vp, vp, ci, vp, vp, ci, vp, vp, vp, ci, ci, ci, ci, vp]),
+    "qlmb_perm_build": (ci, [vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]),
+    "qlmb_moe_arena_bytes": (sz, [ci, ci, ci, ci, ci]),
+    "qlmb_moe_arena_member": (vp, [vp, ci, ci, ci, ci, ci, C.c_char_p]),
+    "qlmb_moe_forward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
+    "qlmb_moe_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, vp, vp, vp, cf, vp]),
+}
+
+_lib = None
+
+
+def lib_path():
+    return os.path.join(HERE, "libqlm_b200.so")
+
+
+def lib():
+    """The loaded library.  Raises if it was not built: there is no fallback path."""
+    global _lib
+    if _lib is None:
+        path = lib_path()
+        if not os.path.exists(path):
+            raise QlmbError("%s is missing: build it with `python -m cudalm_c_b200.build` "
+                            "(there is no CPU fallback)" % path)
+        L = C.CDLL(path)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise QlmbError("libqlm_b200 status %d: %s" % (rc, lib().qlmb_last_error().decode()))
+
+
+def ptr(t):
+    """Device (or host) address of a torch tensor / numpy array / None."""
+    if t is None:
+        return None
+    if isinstance(t, np.ndarray):
+        return t.ctypes.data
+    return t.data_ptr()
+
+
+def stream_ptr(stream=None):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream

@@ -1,0 +1,74 @@
+// Shared declarations for libqlm_b200: status handling, span lookup, nibble
+// access and the rounding hash.  Device code here is integer-only, so it is
+// safe to include from translation units built with or without --fmad=false.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include "../../include/qlm_b200.h"
+
+namespace qlmb {
+
+// ---- host-side status ------------------------------------------------------
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);          // records + returns QLMB_E_CUDA
+int *device_error_word(void);                            // per-device int, lazily allocated
+#define QLMB_CUDA(call)                                                        \
+    do {                                                                       \
+        cudaError_t e__ = (call);                                              \
+        if (e__ != cudaSuccess) return qlmb::cuda_fail(e__, #call);            \
+    } while (0)
+#define QLMB_REQUIRE(cond, ...)                                                \
+    do {                                                                       \
+        if (!(cond)) { qlmb::set_error(__VA_ARGS__); return QLMB_E_ARG; }      \
+    } while (0)
+#define QLMB_LAUNCH_CHECK(what)                                                \
+    do {                                                                       \
+        cudaError_t e__ = cudaGetLastError();                                  \
+        if (e__ != cudaSuccess) return qlmb::cuda_fail(e__, what);             \
+    } while (0)
+
+static inline cudaStream_t as_stream(void *s) { return (cudaStream_t)s; }
+int sm_count(void);                                      // SMs of the current device
+
+// ---- device helpers --------------------------------------------------------
+// splitmix64 finaliser, low 32 bits (reference qlm.cuh:78-82).
+__host__ __device__ __forceinline__ uint32_t hash_u32(uint64_t x)
+{
+    x += 0x9E3779B97F4A7C15ULL;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBULL;
+    return (uint32_t)(x ^ (x >> 31));
+}
+#define QLMB_HASH_I 0x2545F4914F6CDD1DULL   // element-index multiplier (qlm.cuh:85)
+#define QLMB_HASH_T 0x9E3779B97F4A7C15ULL   // step multiplier
+
+__host__ __device__ __forceinline__ int clampi(int v, int lo, int hi)
+{
+    return v < lo ? lo : (v > hi ? hi : v);
+}
+
+// digit i of a digit array (qlm.cuh:96-101)
+__device__ __forceinline__ int digit_at(const int8_t *d, uint64_t i, int packed)
+{
+    if (!packed) return d[i];
+    unsigned b = (uint8_t)d[i >> 1];
+    int v = (i & 1) ? (int)(b >> 4) : (int)(b & 15u);
+    return v > 7 ? v - 16 : v;
+}
+
+// span that owns group gi (qlm.cuh:113-117): returns index, fills start/len
+__device__ __forceinline__ int locate_group(const qlmb_span *sp, int nspan, int gi, int group,
+                                            uint64_t &j0, int &n)
+{
+    int si = 0;
+    for (int i = 0; i < nspan; i++)
+        if (gi >= sp[i].gi0 && gi < sp[i].gi0 + sp[i].ngrp) { si = i; break; }
+    j0 = (uint64_t)(gi - sp[si].gi0) * (uint64_t)group;
+    uint64_t left = sp[si].n - j0;
+    n = (int)(left < (uint64_t)group ? left : (uint64_t)group);
+    return si;
+}
+
+}  // namespace qlmb

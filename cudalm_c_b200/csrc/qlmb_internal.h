@@ -1,0 +1,49 @@
+// Internal (non-ABI) interfaces shared between the translation units of
+// libqlm_b200.  All pointers are device pointers unless noted.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace qlmb {
+
+typedef __nv_bfloat16 bf16;
+
+// ---- routing (qlmb_route.cu) ----
+int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N, int E, int K,
+                const float *bias, int bs, cudaStream_t st);
+size_t perm_scratch_ints(int N, int E, int K, int merged);
+int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
+               int *off, int *counts, int *bad_flag, int *tile_expert, int *ntiles, int tile_rows,
+               int *chunk_scratch, cudaStream_t st);
+
+// ---- row kernels (qlmb_dispatch.cu) ----
+int router_logits(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E,
+                  cudaStream_t st);
+// Xp[j,:] = src[perm[j] % N,:] as bf16 (zero rows where perm[j] < 0), rows = *nrows_dev
+int gather_rows(bf16 *Xp, const void *src, int dtype, const int *perm, const int *nrows_dev,
+                int max_rows, int N, int D, cudaStream_t st);
+// out[n,:] = f_in[n,:] + sum_k gate[k*N+n] * yp[inv[k*N+n],:]   (k ascending)
+int combine_rows(void *out, const void *f_in, int dtype, const bf16 *yp, const int *inv,
+                 const float *gate, int N, int D, int K, cudaStream_t st);
+// per permuted row j: d_gate[slot] = dout[n].yp[j]; dyp[j] = gate[slot]*dout[n]; zero filler rows
+int dgate_rows(bf16 *dyp, float *d_gate, const void *dout, int dtype, const bf16 *yp,
+               const int *perm, const float *gate, const int *nrows_dev, int max_rows, int N, int D,
+               cudaStream_t st);
+// router backward pieces (reference cudalm.cu:4372-4391)
+int router_bwd(float *drt, const float *rprobs, const int *assign, const float *d_gate,
+               const int *counts, int N, int E, int K, float aux, cudaStream_t st);
+// dfnorm[n,:] = sum_k dXp[inv[k*N+n],:] + drt[n,:] * Wr^T
+int unpermute_rows(void *dfnorm, int dtype, const bf16 *dXp, const int *inv, const float *drt,
+                   const float *Wr, int N, int D, int E, int K, cudaStream_t st);
+// dWr[D,E] = beta*dWr + fnorm^T drt ; scratch holds ceil(N/256)*D*E floats
+int router_wgrad(float *dWr, const void *fnorm, int dtype, const float *drt, float *scratch, int N,
+                 int D, int E, float beta, cudaStream_t st);
+// fp32 <-> bf16 row conversion helpers
+int convert_f32_to_bf16(bf16 *dst, const float *src, size_t n, cudaStream_t st);
+
+// ---- tensor-core GEMMs (qlmb_gemm.cu) ----
+struct GemmProblem;   // see qlmb_gemm.cuh
+
+}  // namespace qlmb

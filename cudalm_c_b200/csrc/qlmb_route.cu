@@ -1,0 +1,213 @@
+// Top-k router and the stable expert-grouping permutation.
+//
+// Built with --fmad=false: the softmax uses the reference CPU build's
+// polynomial exp and its sequential summation order so probabilities, gates
+// and expert choices match that build bit for bit on the same logits.
+#include "qlmb_common.cuh"
+#include "qlmb_internal.h"
+
+namespace qlmb {
+
+// exp as the reference CPU build computes it (cpu_kern.h:28-34): clamp,
+// two-part ln2 reduction, degree-6 polynomial, exponent by bit shift.
+__device__ __forceinline__ float exp_poly(float x)
+{
+    x = x < -87.0f ? -87.0f : (x > 88.0f ? 88.0f : x);
+    float k = rintf(x * 1.44269504089f);
+    float r = x - k * 0.693145751953125f;
+    r -= k * 1.428606765330187e-06f;
+    float p = 1.0f / 720;
+    p = 1.0f / 120 + r * p;
+    p = 1.0f / 24 + r * p;
+    p = 1.0f / 6 + r * p;
+    p = 0.5f + r * p;
+    p = 1.0f + r * p;
+    p = 1.0f + r * p;
+    return p * __uint_as_float((uint32_t)((int)k + 127) << 23);
+}
+
+// One thread per token (reference cudalm.cu:2515-2534).  The probabilities
+// live in rprobs (global, L1-resident) so any E up to 256 needs no local array.
+__global__ void __launch_bounds__(128) k_router_topk(const float *rt, float *rprobs, int *assign,
+                                                     float *gate, int N, int E, int K,
+                                                     const float *bias, int bs)
+{
+    int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    const float *lg = rt + (size_t)n * E;
+    float *pr = rprobs + (size_t)n * E;
+    float top = -1e30f;
+    for (int e = 0; e < E; e++) { float v = lg[e]; if (v > top) top = v; }
+    float sum = 0.0f;
+    for (int e = 0; e < E; e++) { float p = exp_poly(lg[e] - top); pr[e] = p; sum += p; }
+    float inv = 1.0f / sum;
+    for (int e = 0; e < E; e++) pr[e] *= inv;
+    int took[8];
+    for (int k = 0; k < K; k++) {
+        int pick = -1; float best = -1e30f;
+        for (int e = 0; e < E; e++) {
+            bool used = false;
+            for (int j = 0; j < k; j++) used |= (took[j] == e);
+            if (used) continue;
+            float sc = pr[e] + (bias ? bias[k * bs + e] : 0.0f);
+            if (sc > best) { best = sc; pick = e; }
+        }
+        if (pick < 0) pick = k;                     // NaN scores: stay in range
+        took[k] = pick;
+        assign[(size_t)k * N + n] = pick;
+        gate[(size_t)k * N + n] = pr[pick];
+    }
+}
+
+// ------------------------------------------------------------- permutation
+// Stable counting sort in three launches (chunks of 1024 entries):
+//   hist    : per-chunk expert histogram
+//   scan    : expert offsets (each segment rounded up to `pad`), per-chunk
+//             bases, filler entries (-1), the row-tile table for the grouped
+//             GEMMs and the unpadded counts
+//   scatter : in-chunk stable rank (warp match + per-warp prefix) -> perm, inv
+#define PERM_CHUNK 1024
+
+__global__ void __launch_bounds__(PERM_CHUNK) k_perm_hist(const int *asn, int len, int E, int NC,
+                                                          int *ch, int *bad)
+{
+    extern __shared__ int h[];
+    int c = blockIdx.x, k = blockIdx.y, i = c * PERM_CHUNK + threadIdx.x;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) h[e] = 0;
+    __syncthreads();
+    if (i < len) {
+        int e = asn[(size_t)k * len + i];
+        if ((unsigned)e >= (unsigned)E) atomicExch(bad, e | 0x40000000);
+        else atomicAdd(&h[e], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) ch[((size_t)k * E + e) * NC + c] = h[e];
+}
+
+__global__ void __launch_bounds__(256) k_perm_scan(int *ch, int E, int NC, int pad, int plen,
+                                                   int *off, int *counts, int *perm,
+                                                   int *tile_expert, int *ntiles, int tile_rows,
+                                                   const int *bad, int *errword)
+{
+    extern __shared__ int sm[];           // [E] totals then [E+1] padded offsets
+    int *tot = sm, *po = sm + E;
+    int k = blockIdx.x;
+    int *cp = ch + (size_t)k * E * NC;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int s = 0;
+        for (int c = 0; c < NC; c++) s += cp[(size_t)e * NC + c];
+        tot[e] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int e = 0; e < E; e++) {
+            po[e] = s;
+            s += (tot[e] + pad - 1) / pad * pad;
+        }
+        po[E] = s;
+        if (*bad && errword) { errword[0] = 100; errword[1] = *bad & ~0x40000000; }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) off[(size_t)k * (E + 1) + e] = po[e];
+    if (counts) for (int e = threadIdx.x; e < E; e += blockDim.x) counts[(size_t)k * E + e] = tot[e];
+    // chunk bases
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int s = po[e];
+        for (int c = 0; c < NC; c++) { int t = cp[(size_t)e * NC + c]; cp[(size_t)e * NC + c] = s; s += t; }
+    }
+    // filler rows
+    if (pad > 1)
+        for (int e = 0; e < E; e++)
+            for (int p = po[e] + tot[e] + threadIdx.x; p < po[e + 1]; p += blockDim.x)
+                perm[(size_t)k * plen + p] = -1;
+    // row tiles of the grouped GEMMs (only meaningful when pad is a multiple of tile_rows)
+    if (tile_expert && k == 0) {
+        for (int e = 0; e < E; e++)
+            for (int t = po[e] / tile_rows + threadIdx.x; t < po[e + 1] / tile_rows; t += blockDim.x)
+                tile_expert[t] = e;
+        if (threadIdx.x == 0) *ntiles = po[E] / tile_rows;
+    }
+}
+
+__global__ void __launch_bounds__(PERM_CHUNK) k_perm_scatter(const int *asn, int len, int E, int NC,
+                                                             const int *base, int *perm, int plen,
+                                                             int *inv)
+{
+    extern __shared__ int wc[];           // [32 warps][E] counts of the chunk
+    int c = blockIdx.x, k = blockIdx.y, i = c * PERM_CHUNK + threadIdx.x;
+    int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
+    for (int j = threadIdx.x; j < 32 * E; j += blockDim.x) wc[j] = 0;
+    __syncthreads();
+    int e = -1;
+    if (i < len) { e = asn[(size_t)k * len + i]; if ((unsigned)e >= (unsigned)E) e = -1; }
+    unsigned peers = __match_any_sync(0xffffffffu, e);
+    int rank = __popc(peers & ((1u << ln) - 1u));
+    if (e >= 0 && rank == 0) wc[w * E + e] = __popc(peers);
+    __syncthreads();
+    if (e < 0) return;
+    int pos = base[((size_t)k * E + e) * NC + c] + rank;
+    for (int j = 0; j < w; j++) pos += wc[j * E + e];
+    perm[(size_t)k * plen + pos] = i;
+    if (inv) inv[(size_t)k * len + i] = pos;
+}
+
+int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
+               int *off, int *counts, int *bad_flag, int *tile_expert, int *ntiles, int tile_rows,
+               int *chunk_scratch, cudaStream_t st)
+{
+    int sorts = merged ? 1 : K, len = merged ? K * N : N;
+    int NC = (len + PERM_CHUNK - 1) / PERM_CHUNK;
+    int plen = len + E * (pad - 1);
+    QLMB_CUDA(cudaMemsetAsync(bad_flag, 0, sizeof(int), st));
+    k_perm_hist<<<dim3(NC, sorts), PERM_CHUNK, E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, bad_flag);
+    k_perm_scan<<<sorts, 256, (2 * E + 1) * sizeof(int), st>>>(chunk_scratch, E, NC, pad, plen, off, counts, perm,
+                                                             tile_expert, ntiles, tile_rows, bad_flag,
+                                                             device_error_word());
+    k_perm_scatter<<<dim3(NC, sorts), PERM_CHUNK, 32 * E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, perm,
+                                                                            plen, inv);
+    QLMB_LAUNCH_CHECK("perm_build");
+    return QLMB_OK;
+}
+
+size_t perm_scratch_ints(int N, int E, int K, int merged)
+{
+    int sorts = merged ? 1 : K, len = merged ? K * N : N;
+    int NC = (len + PERM_CHUNK - 1) / PERM_CHUNK;
+    return (size_t)sorts * E * NC;
+}
+
+int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N, int E, int K,
+                const float *bias, int bs, cudaStream_t st)
+{
+    k_router_topk<<<(N + 127) / 128, 128, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
+    QLMB_LAUNCH_CHECK("k_router_topk");
+    return QLMB_OK;
+}
+
+// lazily grown per-device scratch for the public perm entry point
+static int *g_perm_scratch[64];
+static size_t g_perm_cap[64];
+
+}  // namespace qlmb
+
+using namespace qlmb;
+
+extern "C" int qlmb_perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm,
+                               int *inv, int *off, int *counts, int *bad_flag, void *stream)
+{
+    QLMB_REQUIRE(assign && perm && off && bad_flag, "qlmb_perm_build: NULL argument");
+    QLMB_REQUIRE(N > 0 && E > 0 && E <= 256 && K > 0 && K <= 8 && pad >= 1, "qlmb_perm_build: N=%d E=%d K=%d pad=%d", N, E, K, pad);
+    int dev = 0;
+    QLMB_CUDA(cudaGetDevice(&dev));
+    QLMB_REQUIRE(dev >= 0 && dev < 64, "qlmb_perm_build: device index %d", dev);
+    size_t need = perm_scratch_ints(N, E, K, merged);
+    if (g_perm_cap[dev] < need) {
+        if (g_perm_scratch[dev]) QLMB_CUDA(cudaFree(g_perm_scratch[dev]));
+        g_perm_scratch[dev] = nullptr; g_perm_cap[dev] = 0;
+        QLMB_CUDA(cudaMalloc(&g_perm_scratch[dev], need * sizeof(int)));
+        g_perm_cap[dev] = need;
+    }
+    return perm_build(assign, N, E, K, merged, pad, perm, inv, off, counts, bad_flag, nullptr, nullptr, 128,
+                      g_perm_scratch[dev], as_stream(stream));
+}

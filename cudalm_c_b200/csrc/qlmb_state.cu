@@ -1,0 +1,531 @@
+// QLM integer state kernels: encode, render, integer AdamW step, scale servo,
+// global-norm clip and the bf16-moment AdamW for unquantised spans.
+//
+// THIS TRANSLATION UNIT IS BUILT WITH --fmad=false.  The integer state is only
+// reproducible against the reference's CPU build when no a*b+c is fused
+// (the reference documents the same for its own no-FMA flavour, build.py:253);
+// division and sqrt are the IEEE-rounded defaults (-prec-div/-prec-sqrt).
+//
+// Thread mapping of the hot kernel (step_fast): a TEAM of 8 lanes owns one
+// 128-element group, each lane 16 consecutive elements, so every global access
+// is a 128-bit (G, r, m8, v8) or 64-bit (packed digits) vector and a warp
+// covers 4 groups = 2 KiB of gradient per load instruction.  Group maxima are
+// 3-step shuffles inside the team; nibble pairs never leave a lane.
+#include "qlmb_common.cuh"
+
+namespace qlmb {
+
+// ---------------------------------------------------------------- rounding
+// floor(v) + [24-bit draw < frac(v)]  (reference qlm.cuh:83-87); key = the
+// pre-multiplied element term plus the per-launch step term.
+__device__ __forceinline__ int sround_key(float v, uint64_t key)
+{
+    float fl = floorf(v);
+    uint32_t h = hash_u32(key);
+    float u = (float)(h >> 8) * (1.0f / 16777216.0f);
+    return (int)fl + (u < (v - fl) ? 1 : 0);
+}
+
+struct StepArgs {
+    float *P; const float *G; int8_t *d; int8_t *r; const float *s; int8_t *m8; float *m8s;
+    uint8_t *v8; float *v8s; const qlmb_span *sp; int nspan; int group; int dmax;
+    float lr, b1, b2, wd, gscale; const float *gsp; float inv_bc1, inv_sqrt_bc2;
+    int lrmode; uint64_t t; int adam; unsigned long long *stat; int packed; int gi_base, ng;
+};
+
+// Per-element update shared by both paths (reference qlm.cuh:206-242).
+// Returns the new digit; writes mn / rv (the un-quantised new moments).
+struct ElemOut { int dd; int rr; float mn; float rv; int idl; int c; };
+__device__ __forceinline__ ElemOut elem_update(float g, int m8v, int v8v, int dd, int rold,
+                                               float gs, float ms_old, float vs_old, float b1,
+                                               float b2, float omb1, float omb2, float inv_bc1,
+                                               float inv_sqrt_bc2, float L, float dec, int dmax,
+                                               int adam, uint64_t key_t)
+{
+    ElemOut o;
+    float gr = g * gs;
+    float mv = (float)m8v * ms_old;
+    float u;
+    o.rv = 0.0f;
+    if (adam) {
+        float sv = (float)v8v * vs_old;
+        float vv = sv * sv;
+        o.mn = b1 * mv + omb1 * gr;
+        vv = b2 * vv + omb2 * gr * gr;
+        o.rv = sqrtf(vv);
+        float veps = fmaxf(vs_old, 1e-8f);
+        u = (o.mn * inv_bc1) / (o.rv * inv_sqrt_bc2 + veps);
+        u = fmaxf(-8.0f, fminf(8.0f, u));
+    } else {
+        float cc = b1 * mv + omb1 * gr;
+        u = (float)((cc > 0.0f) - (cc < 0.0f));
+        o.mn = b2 * mv + omb2 * gr;
+    }
+    o.idl = sround_key(-(L * u + dec * (float)dd), key_t);
+    int rr = rold + o.idl;
+    int c = 0;
+    if (rr > 64) c = ((rr - 65) >> 7) + 1;
+    else if (rr < -64) c = -((((-rr) - 65) >> 7) + 1);
+    o.c = c;
+    o.rr = rr - 128 * c;
+    o.dd = clampi(dd + c, -dmax, dmax);
+    return o;
+}
+
+// ------------------------------------------------- generic team-per-group step
+// T lanes (team) walk one group two elements (= one packed byte) at a time.
+// Pass 1 updates digits/residuals and finds the group maxima; pass 2 recomputes
+// the new moments from the still-unmodified m8/v8/G and re-quantises them, so
+// no per-lane arrays are needed for any group size up to 256.
+template <int T>
+__device__ void step_group_team(const StepArgs &a, int gi, int tl, unsigned tmask)
+{
+    uint64_t j0; int n;
+    int si = locate_group(a.sp, a.nspan, gi, a.group, j0, n);
+    const qlmb_span &S = a.sp[si];
+    uint64_t q0 = S.qi0 + j0, p0 = S.pof + j0, g0 = S.gof + j0;
+    float gs = a.gsp ? *a.gsp : a.gscale;
+    float sg = a.s[gi];
+    float L = a.lr * 128.0f / (a.lrmode ? sg : S.sref);
+    float dec = a.lr * a.wd * 128.0f;
+    float ms_old = a.m8s[gi], vs_old = a.v8s ? a.v8s[gi] : 0.0f;
+    float omb1 = 1.0f - a.b1, omb2 = 1.0f - a.b2;
+    uint64_t kt = a.t * QLMB_HASH_T;
+    float am = 0.0f, vm = 0.0f;
+    unsigned long long st0 = 0, st1 = 0, st2 = 0, st3 = 0;
+    for (int p = tl; 2 * p < n; p += T) {
+        int dig[2] = {0, 0};
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            int j = 2 * p + h;
+            if (j >= n) break;
+            uint64_t qi = q0 + j;
+            int dd = digit_at(a.d, qi, a.packed);
+            ElemOut o = elem_update(a.G[g0 + j], a.m8[qi], a.adam ? a.v8[qi] : 0, dd, a.r[qi], gs,
+                                    ms_old, vs_old, a.b1, a.b2, omb1, omb2, a.inv_bc1,
+                                    a.inv_sqrt_bc2, L, dec, a.dmax, a.adam, qi * QLMB_HASH_I + kt);
+            dig[h] = o.dd;
+            a.r[qi] = (int8_t)o.rr;
+            if (a.P) a.P[p0 + j] = sg * (float)o.dd;
+            if (!a.packed) a.d[qi] = (int8_t)o.dd;
+            am = fmaxf(am, fabsf(o.mn));
+            vm = fmaxf(vm, o.rv);
+            if (a.stat) {
+                unsigned long long ai = (unsigned long long)(o.idl < 0 ? -o.idl : o.idl);
+                st3 = ai > st3 ? ai : st3;
+                st0 += (unsigned long long)(o.c < 0 ? -o.c : o.c);
+                st1 += (o.dd == a.dmax) | (o.dd == -a.dmax);
+                st2 += (o.dd == 0);
+            }
+        }
+        if (a.packed) a.d[(q0 >> 1) + p] = (int8_t)(((dig[1] & 15) << 4) | (dig[0] & 15));
+    }
+#pragma unroll
+    for (int o = T / 2; o > 0; o >>= 1) {
+        am = fmaxf(am, __shfl_xor_sync(tmask, am, o));
+        vm = fmaxf(vm, __shfl_xor_sync(tmask, vm, o));
+    }
+    float ms = am > 0.0f ? am / 127.0f : 1e-12f;
+    float vs = vm > 0.0f ? vm / 255.0f : 1e-12f;
+    // pass 2: every lane re-derives the moments of the elements it owns
+    for (int p = tl; 2 * p < n; p += T) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            int j = 2 * p + h;
+            if (j >= n) break;
+            uint64_t qi = q0 + j;
+            float gr = a.G[g0 + j] * gs;
+            float mv = (float)a.m8[qi] * ms_old, mn, rv = 0.0f;
+            if (a.adam) {
+                float sv = (float)a.v8[qi] * vs_old, vv = sv * sv;
+                mn = a.b1 * mv + omb1 * gr;
+                vv = a.b2 * vv + omb2 * gr * gr;
+                rv = sqrtf(vv);
+            } else {
+                mn = a.b2 * mv + omb2 * gr;
+            }
+            a.m8[qi] = (int8_t)clampi(sround_key(mn / ms, qi * QLMB_HASH_I + (a.t + 0x5EEDULL) * QLMB_HASH_T), -127, 127);
+            if (a.adam) {
+                int vq = clampi(sround_key(rv / vs, qi * QLMB_HASH_I + (a.t + 0xBEEFULL) * QLMB_HASH_T), 0, 255);
+                if (vq == 0 && rv > 0.0f) vq = 1;
+                a.v8[qi] = (uint8_t)vq;
+            }
+        }
+    }
+    // the scales are read by pass 2 of no other team, so they can be stored last
+    __syncwarp(tmask);
+    if (tl == 0) { a.m8s[gi] = ms; if (a.adam) a.v8s[gi] = vs; }
+    if (a.stat) {
+        atomicAdd(&a.stat[0], st0); atomicAdd(&a.stat[1], st1); atomicAdd(&a.stat[2], st2);
+        atomicMax(&a.stat[3], st3);
+    }
+}
+
+__global__ void __launch_bounds__(256) k_step_generic(StepArgs a)
+{
+    int w = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (w >= a.ng) return;
+    step_group_team<32>(a, a.gi_base + w, threadIdx.x & 31, 0xffffffffu);
+}
+
+// ------------------------------------------------------- fast step, group 128
+// Requirements checked per group at run time (else the team falls back to the
+// generic walk): 128 full elements, digit offset a multiple of 16, P and G
+// offsets multiples of 4; base pointers are 16-byte aligned (checked on host).
+template <bool WRITE_P>
+__global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
+{
+    const int lane = threadIdx.x & 31, tl = lane & 7, team = lane >> 3;
+    const unsigned tmask = 0xffu << (team * 8);
+    long long w = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * 4 + team;
+    if (w >= a.ng) return;
+    int gi = a.gi_base + (int)w;
+    uint64_t j0; int n;
+    int si = locate_group(a.sp, a.nspan, gi, 128, j0, n);
+    const qlmb_span &S = a.sp[si];
+    uint64_t q0 = S.qi0 + j0, p0 = S.pof + j0, g0 = S.gof + j0;
+    if (n != 128 || (q0 & 15) || (g0 & 3) || (WRITE_P && (p0 & 3))) {
+        step_group_team<8>(a, gi, tl, tmask);
+        return;
+    }
+    const uint64_t qe = q0 + (uint64_t)tl * 16;          // first element of this lane
+    // ---- loads: 4x16B gradient, 16B each of r/m8/v8, 8B of digits
+    const float4 *gp = reinterpret_cast<const float4 *>(a.G + g0 + tl * 16);
+    float4 gv[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) gv[i] = __ldcs(gp + i);
+    int4 rv4 = *reinterpret_cast<const int4 *>(a.r + qe);
+    int4 mv4 = *reinterpret_cast<const int4 *>(a.m8 + qe);
+    int4 vv4 = *reinterpret_cast<const int4 *>(a.v8 + qe);
+    uint2 dv2 = *reinterpret_cast<const uint2 *>(a.d + (qe >> 1));
+    float gs = a.gsp ? *a.gsp : a.gscale;
+    float sg = a.s[gi];
+    float L = a.lr * 128.0f / (a.lrmode ? sg : S.sref);
+    float dec = a.lr * a.wd * 128.0f;
+    float ms_old = a.m8s[gi], vs_old = a.v8s[gi];
+    float omb1 = 1.0f - a.b1, omb2 = 1.0f - a.b2;
+    const uint64_t kt = a.t * QLMB_HASH_T;
+    uint64_t key = qe * QLMB_HASH_I;                     // advanced by one multiplier per element
+
+    const float *gf = reinterpret_cast<const float *>(gv);
+    const uint32_t *rw = reinterpret_cast<const uint32_t *>(&rv4);
+    const uint32_t *mw = reinterpret_cast<const uint32_t *>(&mv4);
+    const uint32_t *vw = reinterpret_cast<const uint32_t *>(&vv4);
+    const uint32_t dw[2] = {dv2.x, dv2.y};
+    float mn[16], rv[16], am = 0.0f, vm = 0.0f;
+    uint32_t rout[4] = {0, 0, 0, 0}, dout[2] = {0, 0};
+    float pv[16];
+#pragma unroll
+    for (int e = 0; e < 16; e++) {
+        int rold = (int)(int8_t)((rw[e >> 2] >> ((e & 3) * 8)) & 0xff);
+        int m8v = (int)(int8_t)((mw[e >> 2] >> ((e & 3) * 8)) & 0xff);
+        int v8v = (int)((vw[e >> 2] >> ((e & 3) * 8)) & 0xff);
+        int nib = (int)((dw[e >> 3] >> ((e & 7) * 4)) & 15u);
+        int dd = nib > 7 ? nib - 16 : nib;
+        ElemOut o = elem_update(gf[e], m8v, v8v, dd, rold, gs, ms_old, vs_old, a.b1, a.b2, omb1,
+                                omb2, a.inv_bc1, a.inv_sqrt_bc2, L, dec, a.dmax, 1, key + kt);
+        key += QLMB_HASH_I;
+        mn[e] = o.mn; rv[e] = o.rv;
+        am = fmaxf(am, fabsf(o.mn));
+        vm = fmaxf(vm, o.rv);
+        rout[e >> 2] |= ((uint32_t)(o.rr & 0xff)) << ((e & 3) * 8);
+        dout[e >> 3] |= ((uint32_t)(o.dd & 15)) << ((e & 7) * 4);
+        if (WRITE_P) pv[e] = sg * (float)o.dd;
+    }
+    *reinterpret_cast<int4 *>(a.r + qe) = make_int4(rout[0], rout[1], rout[2], rout[3]);
+    *reinterpret_cast<uint2 *>(a.d + (qe >> 1)) = make_uint2(dout[0], dout[1]);
+    if (WRITE_P) {
+        float4 *pp = reinterpret_cast<float4 *>(a.P + p0 + tl * 16);
+#pragma unroll
+        for (int i = 0; i < 4; i++) pp[i] = make_float4(pv[4 * i], pv[4 * i + 1], pv[4 * i + 2], pv[4 * i + 3]);
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+        am = fmaxf(am, __shfl_xor_sync(tmask, am, o));
+        vm = fmaxf(vm, __shfl_xor_sync(tmask, vm, o));
+    }
+    float ms = am > 0.0f ? am / 127.0f : 1e-12f;
+    float vs = vm > 0.0f ? vm / 255.0f : 1e-12f;
+    if (tl == 0) { a.m8s[gi] = ms; a.v8s[gi] = vs; }
+    uint32_t mo[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
+    const uint64_t ktm = (a.t + 0x5EEDULL) * QLMB_HASH_T, ktv = (a.t + 0xBEEFULL) * QLMB_HASH_T;
+    key = qe * QLMB_HASH_I;
+#pragma unroll
+    for (int e = 0; e < 16; e++) {
+        int mq = clampi(sround_key(mn[e] / ms, key + ktm), -127, 127);
+        int vq = clampi(sround_key(rv[e] / vs, key + ktv), 0, 255);
+        if (vq == 0 && rv[e] > 0.0f) vq = 1;
+        key += QLMB_HASH_I;
+        mo[e >> 2] |= ((uint32_t)(mq & 0xff)) << ((e & 3) * 8);
+        vo[e >> 2] |= ((uint32_t)vq) << ((e & 3) * 8);
+    }
+    *reinterpret_cast<int4 *>(a.m8 + qe) = make_int4(mo[0], mo[1], mo[2], mo[3]);
+    *reinterpret_cast<int4 *>(a.v8 + qe) = make_int4(vo[0], vo[1], vo[2], vo[3]);
+}
+
+// ------------------------------------------------------------------ encode
+// One warp per group, lanes walk byte pairs (reference qlm.cuh:136-167).
+__global__ void __launch_bounds__(256) k_encode(const float *P, int8_t *d, int8_t *r, float *s,
+                                                const qlmb_span *sp, int nspan, int ngrp, int group,
+                                                int dmax, int packed)
+{
+    int gi = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (gi >= ngrp) return;
+    uint64_t j0; int n;
+    int si = locate_group(sp, nspan, gi, group, j0, n);
+    const float *p = P + sp[si].pof + j0;
+    uint64_t q0 = sp[si].qi0 + j0;
+    float amax = 0.0f;
+    for (int j = lane; j < n; j += 32) amax = fmaxf(amax, fabsf(p[j]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float sc = amax / (float)dmax;
+    if (!(sc > 0.0f)) sc = 1e-8f;
+    if (lane == 0) s[gi] = sc;
+    for (int b = lane; 2 * b < n; b += 32) {
+        int dig[2] = {0, 0};
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            int j = 2 * b + h;
+            if (j >= n) break;
+            float t = p[j] / sc;
+            int dd = clampi((int)rintf(t), -dmax, dmax);
+            int rr = clampi((int)rintf((t - (float)dd) * 128.0f), -64, 64);
+            dig[h] = dd;
+            r[q0 + j] = (int8_t)rr;
+            if (!packed) d[q0 + j] = (int8_t)dd;
+        }
+        if (packed) d[(q0 >> 1) + b] = (int8_t)(((dig[1] & 15) << 4) | (dig[0] & 15));
+    }
+}
+
+// ------------------------------------------------------------------ render
+__global__ void __launch_bounds__(256) k_render(float *P, const int8_t *d, const float *s,
+                                                const qlmb_span *sp, int nspan, int group,
+                                                int packed, int gi_base, int ng)
+{
+    int w = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= ng) return;
+    int gi = gi_base + w, n; uint64_t j0;
+    int si = locate_group(sp, nspan, gi, group, j0, n);
+    float sc = s[gi];
+    float *p = P + sp[si].pof + j0;
+    uint64_t q0 = sp[si].qi0 + j0;
+    for (int j = lane; j < n; j += 32) p[j] = sc * (float)digit_at(d, q0 + j, packed);
+}
+
+// ------------------------------------------------------------------- servo
+// One warp per group (reference qlm.cuh:404-441).
+__global__ void __launch_bounds__(256) k_servo(int8_t *d, int8_t *r, float *s, const qlmb_span *sp,
+                                               int nspan, int ngrp, int group, int dmax, float f_hi,
+                                               float f_lo, int packed)
+{
+    int gi = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (gi >= ngrp) return;
+    uint64_t j0; int n;
+    int si = locate_group(sp, nspan, gi, group, j0, n);
+    uint64_t q0 = sp[si].qi0 + j0;
+    int railed = 0;
+    for (int j = lane; j < n; j += 32) {
+        int dd = digit_at(d, q0 + j, packed);
+        railed += (dd == dmax) | (dd == -dmax);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) railed += __shfl_xor_sync(0xffffffffu, railed, o);
+    float f = (float)railed / (float)n, old = s[gi], nw;
+    if (f > f_hi) nw = old * 1.09051f;
+    else if (f < f_lo) nw = old / 1.09051f;
+    else return;
+    float conv = old / nw;
+    __syncwarp();
+    if (lane == 0) s[gi] = nw;
+    for (int b = lane; 2 * b < n; b += 32) {
+        int dig[2] = {0, 0};
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            int j = 2 * b + h;
+            if (j >= n) break;
+            uint64_t qi = q0 + j;
+            float t = ((float)digit_at(d, qi, packed) + (float)r[qi] * (1.0f / 128.0f)) * conv;
+            int dd = clampi((int)rintf(t), -dmax, dmax);
+            int rr = clampi((int)rintf((t - (float)dd) * 128.0f), -64, 64);
+            dig[h] = dd;
+            r[qi] = (int8_t)rr;
+            if (!packed) d[qi] = (int8_t)dd;
+        }
+        if (packed) d[(q0 >> 1) + b] = (int8_t)(((dig[1] & 15) << 4) | (dig[0] & 15));
+    }
+}
+
+// -------------------------------------------------------------- grad norm
+// Stage 1: chunk c of 64 covers [n*c/64, n*(c+1)/64) (reference CPU build,
+// cpu_kern.h:533-540); each chunk is split over SUB blocks whose double sums
+// are combined in a fixed order by stage 2, so the result does not depend on
+// scheduling.  Double accumulation makes the float rounding of each chunk sum
+// agree with the CPU's double loop.
+#define GN_SUB 16
+__global__ void __launch_bounds__(256) k_sq_partial(const float *G, size_t n, double *sub)
+{
+    __shared__ double sh[8];
+    int c = blockIdx.y, b = blockIdx.x;
+    size_t i0 = n * (size_t)c / 64, i1 = n * (size_t)(c + 1) / 64;
+    size_t len = i1 - i0, per = (len + GN_SUB - 1) / GN_SUB;
+    size_t lo = i0 + per * (size_t)b, hi = lo + per < i1 ? lo + per : i1;
+    double acc = 0.0;
+    for (size_t i = lo + threadIdx.x; i < hi; i += 256) { double g = (double)G[i]; acc += g * g; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int i = 0; i < 8; i++) t += sh[i];
+        sub[(size_t)c * GN_SUB + b] = t;
+    }
+}
+// Stage 2 (reference cudalm.cu:2807-2812): part[64*(1+nside)] -> gs[0..1].
+__global__ void k_gnorm_final(const double *sub, int nside, int clip_side, float *gs)
+{
+    double ss = 0.0, sd = 0.0;
+    for (int i = 0; i < 64 * (1 + nside); i++) {
+        double t = 0.0;
+        for (int b = 0; b < GN_SUB; b++) t += sub[(size_t)i * GN_SUB + b];
+        float part = (float)t;
+        if (i < 64) ss += part; else sd += part;
+    }
+    float gn = (float)sqrt(clip_side ? ss + sd : ss);
+    if (!isfinite(sd)) gn = __int_as_float(0x7fc00000);
+    gs[0] = gn > 1.0f ? 1.0f / gn : 1.0f;
+    gs[1] = gn;
+}
+
+// ------------------------------------------------------ float-span AdamW
+__device__ __forceinline__ float bf_to_f(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+__device__ __forceinline__ uint16_t f_to_bf(float f)
+{
+    uint32_t x = __float_as_uint(f);
+    return (uint16_t)((x + 0x7fffu + ((x >> 16) & 1u)) >> 16);
+}
+// reference cudalm.cu:2855-2870 in the CPU build's operation order
+// (cpu_kern.h:552-561): (m/bc1) / (sqrt(v/bc2) + 1e-8)
+__global__ void __launch_bounds__(256) k_adamw_bf16(float *P, const float *G, uint16_t *M,
+                                                    uint16_t *V, size_t n, float lr, float b1,
+                                                    float b2, float wd, float bc1, float bc2,
+                                                    const float *gs)
+{
+    size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float g = gs ? G[i] * gs[0] : G[i];
+    float m = b1 * bf_to_f(M[i]) + (1.0f - b1) * g;
+    float v = b2 * bf_to_f(V[i]) + (1.0f - b2) * g * g;
+    M[i] = f_to_bf(m);
+    V[i] = f_to_bf(v);
+    float p = P[i];
+    P[i] = p - lr * ((m / bc1) / (sqrtf(v / bc2) + 1e-8f) + wd * p);
+}
+
+// per-device scratch for the partial sums, grown on demand
+static double *g_gn_scratch[64];
+static size_t g_gn_cap[64];
+
+}  // namespace qlmb
+
+using namespace qlmb;
+
+extern "C" int qlmb_encode(const float *P, int8_t *d, int8_t *r, float *s, const qlmb_span *sp,
+                           int nspan, int ngrp, int group, int dmax, int packed, void *stream)
+{
+    QLMB_REQUIRE(P && d && r && s && sp && nspan > 0, "qlmb_encode: NULL argument");
+    QLMB_REQUIRE(group >= 32 && group <= 256 && (!packed || (group % 2) == 0), "qlmb_encode: group %d", group);
+    QLMB_REQUIRE(dmax >= 1 && dmax <= 127 && (!packed || dmax <= 7), "qlmb_encode: dmax %d", dmax);
+    if (ngrp <= 0) return QLMB_OK;
+    k_encode<<<(ngrp + 7) / 8, 256, 0, as_stream(stream)>>>(P, d, r, s, sp, nspan, ngrp, group, dmax, packed);
+    QLMB_LAUNCH_CHECK("k_encode");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_render(float *P, const int8_t *d, const float *s, const qlmb_span *sp, int nspan,
+                           int group, int packed, int gi_base, int ng, void *stream)
+{
+    QLMB_REQUIRE(P && d && s && sp && nspan > 0, "qlmb_render: NULL argument");
+    QLMB_REQUIRE(group >= 32 && group <= 256, "qlmb_render: group %d", group);
+    if (ng <= 0) return QLMB_OK;
+    k_render<<<(ng + 7) / 8, 256, 0, as_stream(stream)>>>(P, d, s, sp, nspan, group, packed, gi_base, ng);
+    QLMB_LAUNCH_CHECK("k_render");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const float *s, int8_t *m8,
+                         float *m8s, uint8_t *v8, float *v8s, const qlmb_span *sp, int nspan,
+                         int group, int dmax, float lr, float b1, float b2, float wd, float gscale,
+                         const float *gsp, float inv_bc1, float inv_sqrt_bc2, int lrmode, uint64_t t,
+                         int adam, int64_t *stat, int packed, int gi_base, int ng, void *stream)
+{
+    QLMB_REQUIRE(G && d && r && s && m8 && m8s && sp && nspan > 0, "qlmb_step: NULL argument");
+    QLMB_REQUIRE(!adam || (v8 && v8s), "qlmb_step: adam needs v8 and v8s");
+    QLMB_REQUIRE(group >= 32 && group <= 256 && (!packed || (group % 2) == 0), "qlmb_step: group %d", group);
+    QLMB_REQUIRE(dmax >= 1 && dmax <= 127 && (!packed || dmax <= 7), "qlmb_step: dmax %d", dmax);
+    if (ng <= 0) return QLMB_OK;
+    StepArgs a = {P, G, d, r, s, m8, m8s, v8, v8s, sp, nspan, group, dmax, lr, b1, b2, wd, gscale, gsp,
+                  inv_bc1, inv_sqrt_bc2, lrmode, t, adam, (unsigned long long *)stat, packed, gi_base, ng};
+    auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    bool fast = group == 128 && packed && adam && !stat && al16(G) && al16(d) && al16(r) && al16(m8) &&
+                al16(v8) && (!P || al16(P));
+    cudaStream_t st = as_stream(stream);
+    if (fast) {
+        unsigned nb = (unsigned)((ng + 31) / 32);
+        if (P) k_step_fast<true><<<nb, 256, 0, st>>>(a);
+        else k_step_fast<false><<<nb, 256, 0, st>>>(a);
+    } else {
+        k_step_generic<<<(ng + 7) / 8, 256, 0, st>>>(a);
+    }
+    QLMB_LAUNCH_CHECK("k_step");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_servo(int8_t *d, int8_t *r, float *s, const qlmb_span *sp, int nspan, int ngrp,
+                          int group, int dmax, float f_hi, float f_lo, int packed, void *stream)
+{
+    QLMB_REQUIRE(d && r && s && sp && nspan > 0, "qlmb_servo: NULL argument");
+    QLMB_REQUIRE(group >= 32 && group <= 256 && (!packed || (group % 2) == 0), "qlmb_servo: group %d", group);
+    if (ngrp <= 0) return QLMB_OK;
+    k_servo<<<(ngrp + 7) / 8, 256, 0, as_stream(stream)>>>(d, r, s, sp, nspan, ngrp, group, dmax, f_hi, f_lo, packed);
+    QLMB_LAUNCH_CHECK("k_servo");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_gnorm(const float *G, size_t n, const float *const *side, const size_t *side_n,
+                          int nside, int clip_side, float *gs, void *stream)
+{
+    QLMB_REQUIRE(G && gs && nside >= 0 && nside <= 62, "qlmb_gnorm: bad argument");
+    QLMB_REQUIRE(nside == 0 || (side && side_n), "qlmb_gnorm: side arrays missing");
+    int dev = 0;
+    QLMB_CUDA(cudaGetDevice(&dev));
+    QLMB_REQUIRE(dev >= 0 && dev < 64, "qlmb_gnorm: device index %d", dev);
+    size_t need = (size_t)64 * (1 + nside) * GN_SUB;
+    if (g_gn_cap[dev] < need) {
+        if (g_gn_scratch[dev]) QLMB_CUDA(cudaFree(g_gn_scratch[dev]));
+        g_gn_scratch[dev] = nullptr; g_gn_cap[dev] = 0;
+        QLMB_CUDA(cudaMalloc(&g_gn_scratch[dev], need * sizeof(double)));
+        g_gn_cap[dev] = need;
+    }
+    double *sub = g_gn_scratch[dev];
+    cudaStream_t st = as_stream(stream);
+    k_sq_partial<<<dim3(GN_SUB, 64), 256, 0, st>>>(G, n, sub);
+    for (int i = 0; i < nside; i++)
+        k_sq_partial<<<dim3(GN_SUB, 64), 256, 0, st>>>(side[i], side_n[i], sub + (size_t)64 * GN_SUB * (1 + i));
+    k_gnorm_final<<<1, 1, 0, st>>>(sub, nside, clip_side, gs);
+    QLMB_LAUNCH_CHECK("k_gnorm");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_adamw(float *P, const float *G, uint16_t *M, uint16_t *V, size_t n, float lr,
+                          float b1, float b2, float wd, float bc1, float bc2, const float *gs,
+                          void *stream)
+{
+    QLMB_REQUIRE(P && G && M && V, "qlmb_adamw: NULL argument");
+    if (n == 0) return QLMB_OK;
+    k_adamw_bf16<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(P, G, M, V, n, lr, b1, b2, wd, bc1, bc2, gs);
+    QLMB_LAUNCH_CHECK("k_adamw");
+    return QLMB_OK;
+}

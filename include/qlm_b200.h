@@ -1,0 +1,190 @@
+/* qlm_b200.h -- C ABI of libqlm_b200.so: the QLM hot path of Dsg2/cudalm-c
+ * (4-bit pack/quantise, integer AdamW, dequant-fused linears, top-k routed
+ * expert FFN, decode GEMV) as hand-written sm_100a kernels.
+ *
+ * The reference has no FFI layer: its operators are `static` functions of one
+ * translation unit that take raw device pointers, run on the default stream
+ * and exit() on error.  Each entry point below replaces one of those
+ * operators (cited as file:line of the reference project) with the same
+ * argument meaning, plus an explicit stream, and returns a status instead of
+ * exiting.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer into caller-owned memory unless the
+ *     parameter comment says "host";
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream);
+ *     calls are asynchronous with respect to the host;
+ *   - return value: 0 = QLMB_OK, otherwise a QLMB_E_* code; the message of the
+ *     last failure on the calling thread is qlmb_last_error();
+ *   - there is no CPU fallback: without a CUDA device every compute entry
+ *     point returns QLMB_E_CUDA.
+ *   - matrices are row-major; 4-bit codes are two's-complement nibbles, element
+ *     i in byte i>>1, even i in the low nibble (qlm.cuh:96-101); one fp32 scale
+ *     per 128 consecutive elements of the flat row-major span (qlm.cuh:28-29).
+ */
+#ifndef QLM_B200_H
+#define QLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    QLMB_OK = 0,
+    QLMB_E_ARG = 1,      /* bad argument (shape, alignment, NULL)            */
+    QLMB_E_CUDA = 2,     /* CUDA runtime / driver error                      */
+    QLMB_E_UNSUPPORTED = 3,
+    QLMB_E_DEVICE = 4    /* a kernel reported a bounded wait that ran out    */
+};
+
+/* element type of activation / gradient tensors */
+enum { QLMB_F32 = 0, QLMB_BF16 = 1 };
+/* storage orientation of a quantised weight relative to Y = X * W:
+ * KN: codes are W[K,N] (the reference's own layout, applied with g_ab);
+ * NK: codes are W[N,K] (applied with g_abt, BASELINE config 1).            */
+enum { QLMB_KN = 0, QLMB_NK = 1 };
+
+/* One quantised span; binary-compatible with the reference's QSpanD
+ * (qlm.cuh:30-38). */
+typedef struct {
+    uint64_t pof;    /* offset of the span in P                         */
+    uint64_t gof;    /* offset of the span in G                         */
+    uint64_t qi0;    /* offset of the span in d / r / m8 / v8           */
+    uint64_t n;      /* elements                                        */
+    int32_t gi0;     /* first group index                               */
+    int32_t ngrp;    /* groups in the span (the last may be short)      */
+    float sref;      /* frozen reference scale (relative-LR mode)       */
+} qlmb_span;
+
+const char *qlmb_last_error(void);
+int qlmb_version(void);
+/* Reads and clears the per-device error word kernels set when a bounded
+ * wait expires (QLMB_E_DEVICE); synchronises `stream`. */
+int qlmb_check_device(void *stream);
+
+/* ------------------------------------------------------------------ QLM state */
+
+/* k_qlm_encode (qlm.cuh:136-167): P -> digits d, residuals r, scales s for
+ * all `ngrp` groups of the span table. */
+int qlmb_encode(const float *P, int8_t *d, int8_t *r, float *s, const qlmb_span *sp, int nspan,
+                int ngrp, int group, int dmax, int packed, void *stream);
+
+/* k_qlm_render (qlm.cuh:170-178): P = s*d for groups [gi_base, gi_base+ng). */
+int qlmb_render(float *P, const int8_t *d, const float *s, const qlmb_span *sp, int nspan,
+                int group, int packed, int gi_base, int ng, void *stream);
+
+/* qlm_step_launch (qlm.cuh:377-397): one integer-AdamW step over groups
+ * [gi_base, gi_base+ng).  P may be NULL (no fp32 view is written); gsp, when
+ * not NULL, is a device float that replaces gscale (the clip multiplier);
+ * stat may be NULL.  Element indices in the rounding hash are global, so a
+ * step split over several calls / GPUs gives the same bytes as one call. */
+int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const float *s, int8_t *m8,
+              float *m8s, uint8_t *v8, float *v8s, const qlmb_span *sp, int nspan, int group,
+              int dmax, float lr, float b1, float b2, float wd, float gscale, const float *gsp,
+              float inv_bc1, float inv_sqrt_bc2, int lrmode, uint64_t t, int adam, int64_t *stat,
+              int packed, int gi_base, int ng, void *stream);
+
+/* k_qlm_servo (qlm.cuh:404-441). */
+int qlmb_servo(int8_t *d, int8_t *r, float *s, const qlmb_span *sp, int nspan, int ngrp, int group,
+               int dmax, float f_hi, float f_lo, int packed, void *stream);
+
+/* k_sqsum + k_gnorm (cudalm.cu:2794-2812, 6442-6444): gs[0] = clip multiplier,
+ * gs[1] = global gradient norm.  side/side_n are HOST arrays of nside device
+ * pointers / lengths.  Partial sums follow the reference CPU build
+ * (cpu_kern.h:533-540): 64 contiguous chunks, double accumulation.  Uses a
+ * lazily grown per-device scratch buffer (cudaMalloc on first use). */
+int qlmb_gnorm(const float *G, size_t n, const float *const *side, const size_t *side_n, int nside,
+               int clip_side, float *gs, void *stream);
+
+/* k_adamw (cudalm.cu:2855-2870) for the unquantised spans: bf16 moments,
+ * gs (device, may be NULL) = clip multiplier applied on load. */
+int qlmb_adamw(float *P, const float *G, uint16_t *M, uint16_t *V, size_t n, float lr, float b1,
+               float b2, float wd, float bc1, float bc2, const float *gs, void *stream);
+
+/* ------------------------------------------------------- dequant-fused linears */
+
+/* g_ab / g_abt / g_ab_res (cudalm.cu:3133-3172) on 4-bit codes instead of the
+ * rendered fp32 view: Y[M,N] = X[M,K] * deq(W) (+ R).  X, Y, R have element
+ * type `dtype` (QLMB_F32 or QLMB_BF16); the contraction runs on tcgen05 with
+ * bf16 operands and fp32 accumulation.  K and N must be multiples of 128. */
+int qlmb_linear_fwd(void *Y, const void *X, const int8_t *codes, const float *scales, int layout,
+                    int M, int K, int N, const void *R, int dtype, void *stream);
+
+/* g_abt_b / g_ab (cudalm.cu:3174-3186): dX[M,K] = dY[M,N] * deq(W)^T for the
+ * same (codes, layout) as the forward; beta in {0,1} adds into dX. */
+int qlmb_linear_dgrad(void *dX, const void *dY, const int8_t *codes, const float *scales,
+                      int layout, int M, int K, int N, float beta, int dtype, void *stream);
+
+/* g_atb (cudalm.cu:3190-3202): dW (fp32, the shape of W for `layout`)
+ * = beta*dW + X^T dY resp. dY^T X; beta in {0,1} (the reference is always 1). */
+int qlmb_linear_wgrad(float *dW, const void *dY, const void *X, int layout, int M, int K, int N,
+                      float beta, int dtype, void *stream);
+
+/* Decode path (cudalm.cu:7178-7198, g_ab with M = live slots <= 64):
+ * Y[B,N] = X[B,K] * deq(W), weight-streaming kernel. */
+int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, const float *scales, int layout,
+                     int B, int K, int N, int dtype, void *stream);
+
+/* ------------------------------------------------------- router + permutation */
+
+/* g_ab(f_norm, Wr) + k_router_topk (cudalm.cu:4158, 2515-2534).  If rt_in is
+ * not NULL the logits are read from it (then X, Wr may be NULL); otherwise
+ * they are computed as X[N,D] * Wr[D,E] in fp32 and, if rt_out is not NULL,
+ * stored there.  exp() is the reference CPU build's polynomial
+ * (cpu_kern.h:28-34) so probabilities match the oracle bit for bit. */
+int qlmb_router_topk(const float *rt_in, float *rt_out, const void *X, int x_dtype, const float *Wr,
+                     const float *bias, int bias_stride, float *rprobs, int *assign, float *gate,
+                     int N, int D, int E, int K, void *stream);
+
+/* moe_perm_all / moe_gperm (cudalm.cu:3537-3602): stable grouping of token
+ * slots by expert.  merged=0: K sorts of N entries, off[K*(E+1)], perm[k*N+pos];
+ * merged=1: one sort of the K*N entries n' = k*N+n, off[E+1].
+ * pad >= 1 rounds every expert's segment up to a multiple of `pad` rows; the
+ * filler entries of perm are -1 (the reference's capacity-padded form,
+ * cudalm.cu:3597-3599) and off holds the padded offsets.  inv (may be NULL)
+ * receives the position of every entry.  perm must hold
+ * len + E*(pad-1) ints per sort.  bad_flag (device int) is set to
+ * 0x40000000|e when an expert index e is out of range (cudalm.cu:3507).
+ * counts (may be NULL) receives the unpadded per-expert counts. */
+int qlmb_perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
+                    int *off, int *counts, int *bad_flag, void *stream);
+
+/* ------------------------------------------------------------- MoE expert FFN */
+
+typedef struct {
+    int N, D, F, E, K;        /* tokens, d_model, d_ff, experts, top-k            */
+    int dtype;                /* element type of f_in / f_norm / out / dout / dfnorm */
+    const int8_t *w1_codes, *w3_codes, *w2_codes; /* [E][D][F], [E][D][F], [E][F][D]  */
+    const float *w1_scales, *w3_scales, *w2_scales;
+    const float *wr;          /* router weights [D][E], fp32                      */
+    const float *bias;        /* selection-only bias [K][bias_stride] or NULL     */
+    int bias_stride;
+    float aux;                /* load-balance coefficient (cudalm.cu:3334)        */
+} qlmb_moe_layer;
+
+/* Bytes of the per-layer activation arena the two calls below share (the MoE
+ * members of the reference's GA, cudalm.cu:3308-3333, with the stash on). */
+size_t qlmb_moe_arena_bytes(int N, int D, int F, int E, int K);
+/* Device pointer of a named arena member ("rt","rprobs","assign","gate",
+ * "perm","inv","off","counts","Xp","gp","up","ap","yp","d_gate","drt","dyp",
+ * "dgp","dup","dXp","ntiles","bad") or NULL. rows_out receives its row capacity. */
+void *qlmb_moe_arena_member(void *arena, int N, int D, int F, int E, int K, const char *name);
+
+/* moe_forward (cudalm.cu:4151-4229): out = f_in + sum_k gate_k * FFN_e(f_norm). */
+int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in,
+                     const void *f_norm, void *stream);
+
+/* moe_backward (cudalm.cu:4233-4393): consumes dout, produces dfnorm and adds
+ * the weight gradients into dW1/dW3/dW2/dWr (fp32; beta=1 as the reference,
+ * beta=0 overwrites, valid when G was just zeroed). */
+int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const void *dout,
+                      const void *f_norm, float *dW1, float *dW3, float *dW2, float *dWr,
+                      float beta, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QLM_B200_H */

@@ -1,0 +1,316 @@
+"""ctypes loaders for the two CPU checkers.  TEST INFRASTRUCTURE ONLY.
+
+`restatement()` loads oracle/_build/libqlm_oracle.so (the C restatement in
+qlm_oracle.c).  `reference(exact=True)` loads oracle/_ref/libcudalm_ref_*.so
+(the unmodified reference compiled by the Makefile) or returns None when it was
+never built.  Both are used only by tests/, by __graft_entry__.smoke() and by
+bench.py's CPU-baseline legs; the shipped package never imports this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+SPAN_DTYPE = np.dtype(
+    [("pof", "<u8"), ("gof", "<u8"), ("qi0", "<u8"), ("n", "<u8"),
+     ("gi0", "<i4"), ("ngrp", "<i4"), ("sref", "<f4"), ("_pad", "<i4")])
+assert SPAN_DTYPE.itemsize == 48
+
+
+def make_spans(sizes, group=128, pofs=None):
+    """Span table for consecutive matrices of the given element counts
+    (the reference's qlm_add_span, qlm.cuh:448-455)."""
+    sp = np.zeros(len(sizes), SPAN_DTYPE)
+    nq = 0
+    ngrp = 0
+    pof = 0
+    for i, n in enumerate(sizes):
+        sp[i]["pof"] = pofs[i] if pofs is not None else pof
+        sp[i]["gof"] = sp[i]["pof"]
+        sp[i]["qi0"] = nq
+        sp[i]["n"] = n
+        sp[i]["gi0"] = ngrp
+        sp[i]["ngrp"] = (n + group - 1) // group
+        sp[i]["sref"] = 1.0
+        nq += n
+        ngrp += int(sp[i]["ngrp"])
+        pof += n
+    return sp, nq, ngrp
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def build(target="oracle"):
+    subprocess.check_call(["make", "-s", "-C", HERE, target])
+
+
+class Restatement:
+    def __init__(self, path):
+        L = self.lib = C.CDLL(path)
+        L.qo_hash.restype = C.c_uint32
+        L.qo_hash.argtypes = [C.c_uint64]
+        L.qo_sround.restype = C.c_int
+        L.qo_sround.argtypes = [C.c_float, C.c_uint64, C.c_uint64]
+        L.qo_fexp.restype = C.c_float
+        L.qo_fexp.argtypes = [C.c_float]
+        L.qo_perm_build.restype = C.c_int
+        self.threads = os.cpu_count()
+
+    def hash(self, x):
+        return self.lib.qo_hash(x)
+
+    def sround(self, v, i, t):
+        return self.lib.qo_sround(v, i, t)
+
+    def fexp(self, x):
+        return self.lib.qo_fexp(x)
+
+    def encode(self, P, d, r, s, sp, group=128, dmax=7, packed=1):
+        self.lib.qo_encode(_p(P), _p(d), _p(r), _p(s), _p(sp), C.c_int(len(sp)), C.c_int(len(s)),
+                           C.c_int(group), C.c_int(dmax), C.c_int(packed))
+
+    def render(self, P, d, s, sp, group=128, packed=1, gi_base=0, ng=None):
+        ng = len(s) if ng is None else ng
+        self.lib.qo_render(_p(P), _p(d), _p(s), _p(sp), C.c_int(len(sp)), C.c_int(group),
+                           C.c_int(packed), C.c_int(gi_base), C.c_int(ng))
+
+    def step(self, P, G, d, r, s, m8, m8s, v8, v8s, sp, *, group=128, dmax=7, lr, b1, b2, wd,
+             gscale=1.0, inv_bc1, inv_sqrt_bc2, lrmode=0, t, adam=1, stat=None, packed=1,
+             gi_base=0, ng=None):
+        ng = len(s) if ng is None else ng
+        f = C.c_float
+        self.lib.qo_step(_p(P), _p(G), _p(d), _p(r), _p(s), _p(m8), _p(m8s), _p(v8), _p(v8s), _p(sp),
+                         C.c_int(len(sp)), C.c_int(group), C.c_int(dmax), f(lr), f(b1), f(b2), f(wd),
+                         f(gscale), f(inv_bc1), f(inv_sqrt_bc2), C.c_int(lrmode), C.c_uint64(t),
+                         C.c_int(adam), _p(stat), C.c_int(packed), C.c_int(gi_base), C.c_int(ng))
+
+    def servo(self, d, r, s, sp, group=128, dmax=7, f_hi=0.0, f_lo=0.0, packed=1):
+        self.lib.qo_servo(_p(d), _p(r), _p(s), _p(sp), C.c_int(len(sp)), C.c_int(len(s)),
+                          C.c_int(group), C.c_int(dmax), C.c_float(f_hi), C.c_float(f_lo),
+                          C.c_int(packed))
+
+    def gnorm(self, G, sides=(), clip_side=0):
+        gs = np.zeros(2, np.float32)
+        ns = len(sides)
+        ptrs = (C.c_void_p * max(ns, 1))(*[x.ctypes.data for x in sides])
+        lens = (C.c_size_t * max(ns, 1))(*[x.size for x in sides])
+        self.lib.qo_gnorm(_p(G), C.c_size_t(G.size), ptrs, lens, C.c_int(ns), C.c_int(clip_side), _p(gs))
+        return gs
+
+    def adamw(self, P, G, M, V, lr, b1, b2, wd, bc1, bc2, gs=None):
+        f = C.c_float
+        self.lib.qo_adamw(_p(P), _p(G), _p(M), _p(V), C.c_size_t(P.size), f(lr), f(b1), f(b2), f(wd),
+                          f(bc1), f(bc2), _p(gs))
+
+    def router_topk(self, rt, K, bias=None, bs=0):
+        N, E = rt.shape
+        rprobs = np.zeros((N, E), np.float32)
+        assign = np.zeros((K, N), np.int32)
+        gate = np.zeros((K, N), np.float32)
+        self.lib.qo_router_topk(_p(rt), _p(rprobs), _p(assign), _p(gate), C.c_int(N), C.c_int(E),
+                                C.c_int(K), _p(bias), C.c_int(bs))
+        return rprobs, assign, gate
+
+    def perm_build(self, assign, E, merged):
+        K, N = assign.shape
+        perm = np.zeros(K * N, np.int32)
+        inv = np.zeros(K * N, np.int32)
+        off = np.zeros((1 if merged else K) * (E + 1), np.int32)
+        bad = self.lib.qo_perm_build(_p(assign), C.c_int(N), C.c_int(E), C.c_int(K), C.c_int(merged),
+                                     _p(perm), _p(inv), _p(off))
+        return perm, inv, off, bad
+
+    def linear_fwd(self, X, d, s, layout, N, group=128):
+        M, K = X.shape
+        Y = np.zeros((M, N), np.float32)
+        self.lib.qo_linear_fwd(_p(Y), _p(X), _p(d), _p(s), C.c_int(layout), C.c_int(M), C.c_int(K),
+                               C.c_int(N), C.c_int(group))
+        return Y
+
+    def linear_dgrad(self, dY, d, s, layout, K, group=128):
+        M, N = dY.shape
+        dX = np.zeros((M, K), np.float32)
+        self.lib.qo_linear_dgrad(_p(dX), _p(dY), _p(d), _p(s), C.c_int(layout), C.c_int(M), C.c_int(K),
+                                 C.c_int(N), C.c_int(group))
+        return dX
+
+    def linear_wgrad(self, dW, dY, X, layout):
+        M, K = X.shape
+        N = dY.shape[1]
+        self.lib.qo_linear_wgrad(_p(dW), _p(dY), _p(X), C.c_int(layout), C.c_int(M), C.c_int(K), C.c_int(N))
+        return dW
+
+    def moe_fwd(self, f_in, fnorm, Wr, q1, q3, q2, F, K, group=128):
+        """q1/q3/q2 = (codes, scales) of W1,W3 [E,D,F] and W2 [E,F,D]."""
+        N, D = fnorm.shape
+        E = Wr.shape[1]
+        o = dict(out=np.zeros((N, D), np.float32), rt=np.zeros((N, E), np.float32),
+                 rprobs=np.zeros((N, E), np.float32), assign=np.zeros((K, N), np.int32),
+                 gate=np.zeros((K, N), np.float32), g=np.zeros((K * N, F), np.float32),
+                 u=np.zeros((K * N, F), np.float32), y=np.zeros((K * N, D), np.float32))
+        self.lib.qo_moe_fwd(_p(o["out"]), _p(f_in), _p(fnorm), _p(Wr), _p(q1[0]), _p(q1[1]), _p(q3[0]),
+                            _p(q3[1]), _p(q2[0]), _p(q2[1]), C.c_int(N), C.c_int(D), C.c_int(F),
+                            C.c_int(E), C.c_int(K), _p(o["rt"]), _p(o["rprobs"]), _p(o["assign"]),
+                            _p(o["gate"]), _p(o["g"]), _p(o["u"]), _p(o["y"]), C.c_int(group))
+        return o
+
+    def moe_bwd(self, dout, fnorm, Wr, q1, q3, q2, F, K, fw, aux=0.03, group=128):
+        N, D = fnorm.shape
+        E = Wr.shape[1]
+        o = dict(dfnorm=np.zeros((N, D), np.float32), dW1=np.zeros((E, D, F), np.float32),
+                 dW3=np.zeros((E, D, F), np.float32), dW2=np.zeros((E, F, D), np.float32),
+                 dWr=np.zeros((D, E), np.float32), d_gate=np.zeros((K, N), np.float32))
+        self.lib.qo_moe_bwd(_p(o["dfnorm"]), _p(o["dW1"]), _p(o["dW3"]), _p(o["dW2"]), _p(o["dWr"]),
+                            _p(o["d_gate"]), _p(dout), _p(fnorm), _p(Wr), _p(q1[0]), _p(q1[1]),
+                            _p(q3[0]), _p(q3[1]), _p(q2[0]), _p(q2[1]), C.c_int(N), C.c_int(D),
+                            C.c_int(F), C.c_int(E), C.c_int(K), _p(fw["rprobs"]), _p(fw["assign"]),
+                            _p(fw["gate"]), _p(fw["g"]), _p(fw["u"]), _p(fw["y"]), C.c_float(aux),
+                            C.c_int(group))
+        return o
+
+
+class Reference:
+    """The unmodified reference's CPU build behind ref_harness.cpp."""
+
+    def __init__(self, path):
+        L = self.lib = C.CDLL(path)
+        L.ref_hash.restype = C.c_uint32
+        L.ref_hash.argtypes = [C.c_uint64]
+        L.ref_sround.restype = C.c_int
+        L.ref_sround.argtypes = [C.c_float, C.c_uint64, C.c_uint64]
+        L.ref_threads.restype = C.c_int
+        L.ref_moe_new.restype = C.c_void_p
+        L.ref_moe_buf.restype = C.c_void_p
+        L.ref_moe_buf.argtypes = [C.c_void_p, C.c_char_p]
+        L.ref_moe_off.restype = C.c_longlong
+        L.ref_moe_off.argtypes = [C.c_void_p, C.c_char_p]
+        L.ref_moe_forward.argtypes = [C.c_void_p]
+        L.ref_moe_backward.argtypes = [C.c_void_p]
+        self.threads = L.ref_threads()
+
+    def hash(self, x):
+        return self.lib.ref_hash(x)
+
+    def sround(self, v, i, t):
+        return self.lib.ref_sround(v, i, t)
+
+    def encode(self, P, d, r, s, sp, group=128, dmax=7, packed=1):
+        self.lib.ref_encode(_p(P), _p(d), _p(r), _p(s), _p(sp), C.c_int(len(sp)), C.c_int(len(s)),
+                            C.c_int(group), C.c_int(dmax), C.c_int(packed))
+
+    def render(self, P, d, s, sp, group=128, packed=1, gi_base=0, ng=None):
+        ng = len(s) if ng is None else ng
+        self.lib.ref_render(_p(P), _p(d), _p(s), _p(sp), C.c_int(len(sp)), C.c_int(group),
+                            C.c_int(packed), C.c_int(gi_base), C.c_int(ng))
+
+    def step(self, P, G, d, r, s, m8, m8s, v8, v8s, sp, *, group=128, dmax=7, lr, b1, b2, wd,
+             gscale=1.0, inv_bc1, inv_sqrt_bc2, lrmode=0, t, adam=1, stat=None, packed=1,
+             gi_base=0, ng=None):
+        ng = len(s) if ng is None else ng
+        f = C.c_float
+        self.lib.ref_step(_p(P), _p(G), _p(d), _p(r), _p(s), _p(m8), _p(m8s), _p(v8), _p(v8s), _p(sp),
+                          C.c_int(len(sp)), C.c_int(group), C.c_int(dmax), f(lr), f(b1), f(b2), f(wd),
+                          f(gscale), None, f(inv_bc1), f(inv_sqrt_bc2), C.c_int(lrmode), C.c_uint64(t),
+                          C.c_int(adam), _p(stat), C.c_int(packed), C.c_int(gi_base), C.c_int(ng))
+
+    def servo(self, d, r, s, sp, group=128, dmax=7, f_hi=0.0, f_lo=0.0, packed=1):
+        self.lib.ref_servo(_p(d), _p(r), _p(s), _p(sp), C.c_int(len(sp)), C.c_int(len(s)),
+                           C.c_int(group), C.c_int(dmax), C.c_float(f_hi), C.c_float(f_lo),
+                           C.c_int(packed))
+
+    def gnorm(self, G, sides=(), clip_side=0):
+        gs = np.zeros(2, np.float32)
+        ns = len(sides)
+        ptrs = (C.c_void_p * max(ns, 1))(*[x.ctypes.data for x in sides])
+        lens = (C.c_size_t * max(ns, 1))(*[x.size for x in sides])
+        self.lib.ref_gnorm(_p(G), C.c_size_t(G.size), ptrs, lens, C.c_int(ns), C.c_int(clip_side), _p(gs))
+        return gs
+
+    def adamw(self, P, G, M, V, lr, b1, b2, wd, bc1, bc2, gs=None):
+        f = C.c_float
+        self.lib.ref_adamw(_p(P), _p(G), _p(M), _p(V), C.c_size_t(P.size), f(lr), f(b1), f(b2), f(wd),
+                           f(bc1), f(bc2), _p(gs))
+
+    def router_topk(self, rt, K, bias=None, bs=0):
+        N, E = rt.shape
+        rprobs = np.zeros((N, E), np.float32)
+        assign = np.zeros((K, N), np.int32)
+        gate = np.zeros((K, N), np.float32)
+        self.lib.ref_router_topk(_p(rt), _p(rprobs), _p(assign), _p(gate), C.c_int(N), C.c_int(E),
+                                 C.c_int(K), _p(bias), C.c_int(bs))
+        return rprobs, assign, gate
+
+    def g_ab(self, A, B):
+        M, K = A.shape
+        N = B.shape[1]
+        Cc = np.zeros((M, N), np.float32)
+        self.lib.ref_g_ab(_p(A), _p(B), _p(Cc), C.c_int(M), C.c_int(K), C.c_int(N))
+        return Cc
+
+    def g_abt(self, A, B):
+        M, K = A.shape
+        N = B.shape[0]
+        Cc = np.zeros((M, N), np.float32)
+        self.lib.ref_g_abt(_p(A), _p(B), _p(Cc), C.c_int(M), C.c_int(K), C.c_int(N))
+        return Cc
+
+    def g_atb(self, A, B, Cc):
+        """Cc[K,N] += A[M,K]^T @ B[M,N]"""
+        M, K = A.shape
+        N = B.shape[1]
+        self.lib.ref_g_atb(_p(A), _p(B), _p(Cc), C.c_int(M), C.c_int(K), C.c_int(N))
+        return Cc
+
+    # one MoE layer
+    def moe_new(self, N, D, F, E, K, aux=0.03):
+        h = self.lib.ref_moe_new(C.c_int(N), C.c_int(D), C.c_int(F), C.c_int(E), C.c_int(K), C.c_float(aux))
+        return RefMoeLayer(self, h, N, D, F, E, K)
+
+
+class RefMoeLayer:
+    def __init__(self, ref, h, N, D, F, E, K):
+        self.ref, self.h = ref, h
+        self.N, self.D, self.F, self.E, self.K = N, D, F, E, K
+        self.np = ref.lib.ref_moe_off(h, b"np")
+
+    def buf(self, name, shape, dtype=np.float32):
+        ptr = self.ref.lib.ref_moe_buf(self.h, name.encode())
+        assert ptr, name
+        n = int(np.prod(shape))
+        ct = {np.float32: C.c_float, np.int32: C.c_int32}[dtype]
+        arr = np.ctypeslib.as_array(C.cast(ptr, C.POINTER(ct)), shape=(n,))
+        return arr.reshape(shape)
+
+    def off(self, name):
+        return int(self.ref.lib.ref_moe_off(self.h, name.encode()))
+
+    def forward(self):
+        self.ref.lib.ref_moe_forward(self.h)
+
+    def backward(self):
+        self.ref.lib.ref_moe_backward(self.h)
+
+
+_cache = {}
+
+
+def restatement():
+    if "o" not in _cache:
+        path = os.path.join(HERE, "_build", "libqlm_oracle.so")
+        if not os.path.exists(path):
+            build("oracle")
+        _cache["o"] = Restatement(path)
+    return _cache["o"]
+
+
+def reference(exact=True):
+    key = "exact" if exact else "fast"
+    if key not in _cache:
+        path = os.path.join(HERE, "_ref", "libcudalm_ref_%s.so" % key)
+        _cache[key] = Reference(path) if os.path.exists(path) else None
+    return _cache[key]

@@ -1,0 +1,226 @@
+"""Generate tests/golden/*.npz by running the UNMODIFIED reference.
+
+Needs oracle/_ref/libcudalm_ref_exact.so (make -C oracle ref), i.e. a checkout
+of the reference; the produced vectors are committed so the tests run without
+it.  Every array an op reads is stored next to what the reference wrote, so a
+fixture is self-contained and does not depend on any RNG staying stable.
+
+    python tests/golden/make_golden.py
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from oracle import loader  # noqa: E402
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+f32 = np.float32
+
+
+def bias_corr(b1, b2, t):
+    """inv_bc1, inv_sqrt_bc2 as the reference derives them (cudalm.cu:6454, 6085)."""
+    bc1 = f32(1) - f32(np.power(f32(b1), f32(t)))
+    bc2 = f32(1) - f32(np.power(f32(b2), f32(t)))
+    return float(f32(1) / bc1), float(f32(1) / np.sqrt(bc2))
+
+
+def set_sref(sp, s):
+    for i in range(len(sp)):
+        g0 = int(sp[i]["gi0"])
+        sp[i]["sref"] = f32(s[g0:g0 + int(sp[i]["ngrp"])].astype(np.float64).mean())
+
+
+def golden_hash(ref):
+    xs = np.array([0, 1, 2, 0x0123456789ABCDEF, 0xFFFFFFFFFFFFFFFF, 12345678901234567], np.uint64)
+    hs = np.array([ref.hash(int(x)) for x in xs], np.uint32)
+    vals = np.array([0.5, -0.5, 2.25, -47.75, 0.001, -0.999, 7.5, 126.99], f32)
+    idx = np.arange(16, dtype=np.uint64) * np.uint64(1000003) + np.uint64(5)
+    ts = np.array([1, 2, 3, 1000, 1 + 0x5EED, 1 + 0xBEEF], np.uint64)
+    sr = np.zeros((len(vals), len(idx), len(ts)), np.int32)
+    for a, v in enumerate(vals):
+        for b, i in enumerate(idx):
+            for c, t in enumerate(ts):
+                sr[a, b, c] = ref.sround(float(v), int(i), int(t))
+    np.savez_compressed(os.path.join(OUT, "hash.npz"), xs=xs, hs=hs, vals=vals, idx=idx, ts=ts, sr=sr)
+
+
+def golden_one_group(ref):
+    """The single 128-element group of the reference survey's known-answer table."""
+    j = np.arange(128)
+    P = ((j - 64).astype(f32) * f32(0.001)).astype(f32)
+    G = (f32(1e-3) * ((j % 7) - 3).astype(f32)).astype(f32)
+    sp, nq, ng = loader.make_spans([128])
+    d = np.zeros(64, np.int8); r = np.zeros(128, np.int8); s = np.zeros(1, f32)
+    ref.encode(P, d, r, s, sp)
+    out = dict(P=P, G=G, d0=d.copy(), r0=r.copy(), s0=s.copy())
+    sp[0]["sref"] = s[0]
+    m8 = np.zeros(128, np.int8); v8 = np.zeros(128, np.uint8)
+    m8s = np.zeros(1, f32); v8s = np.zeros(1, f32); Pv = np.zeros(128, f32)
+    for t in (1, 2):
+        i1, i2 = bias_corr(0.9, 0.95, t)
+        ref.step(Pv, G, d, r, s, m8, m8s, v8, v8s, sp, lr=3e-4, b1=0.9, b2=0.95, wd=0.1,
+                 inv_bc1=i1, inv_sqrt_bc2=i2, t=t)
+        for k, v in dict(d=d, r=r, m8=m8, v8=v8, m8s=m8s, v8s=v8s, P=Pv).items():
+            out["%s_t%d" % (k, t)] = v.copy()
+    # the values the table quotes
+    assert s.view(np.uint32)[0] == 0x3C15CBED
+    assert out["m8s_t1"].view(np.uint32)[0] == 0x361E8661
+    assert out["v8s_t2"].view(np.uint32)[0] == 0x367686BE
+    np.savez_compressed(os.path.join(OUT, "one_group.npz"), **out)
+
+
+def golden_state(ref, name, sizes, group, dmax, packed, steps, seed, lrmode=0, adam=1):
+    """Ragged multi-span state: encode, `steps` optimiser steps with a servo
+    tick after step 3 (thresholds widened so it fires) and a final render."""
+    rng = np.random.default_rng(seed)
+    sp, nq, ng = loader.make_spans(sizes, group)
+    P = (rng.standard_normal(nq) * 0.02).astype(f32)
+    P[:7] = 0.0
+    d = np.zeros((nq + 1) // 2 if packed else nq, np.int8)
+    r = np.zeros(nq, np.int8); s = np.zeros(ng, f32)
+    ref.encode(P, d, r, s, sp, group, dmax, packed)
+    set_sref(sp, s)
+    out = dict(P=P, sizes=np.array(sizes), cfg=np.array([group, dmax, packed, steps, lrmode, adam]),
+               sref=sp["sref"].copy(), d0=d.copy(), r0=r.copy(), s0=s.copy())
+    m8 = np.zeros(nq, np.int8); v8 = np.zeros(nq, np.uint8)
+    m8s = np.zeros(ng, f32); v8s = np.zeros(ng, f32); Pv = np.zeros(nq, f32)
+    Gs = []
+    gsc = []
+    for t in range(1, steps + 1):
+        G = (rng.standard_normal(nq) * 1e-3).astype(f32)
+        if t == 2:
+            G[::5] *= 300.0          # multi-carry steps and the +-8 clamp
+        Gs.append(G)
+        gscale = 0.37 if t % 2 == 0 else 1.0
+        gsc.append(gscale)
+        i1, i2 = bias_corr(0.9, 0.95, t)
+        stat = np.zeros(4, np.int64)
+        ref.step(Pv, G, d, r, s, m8, m8s, v8, v8s, sp, group=group, dmax=dmax, lr=3e-4, b1=0.9,
+                 b2=0.95, wd=0.1, gscale=gscale, inv_bc1=i1, inv_sqrt_bc2=i2, lrmode=lrmode, t=t,
+                 adam=adam, stat=stat, packed=packed)
+        if t == 3:
+            ref.servo(d, r, s, sp, group, dmax, 0.9 / group, 0.2 / group, packed)
+        for k, v in dict(d=d, r=r, s=s, m8=m8, v8=v8, m8s=m8s, v8s=v8s, stat=stat).items():
+            out["%s_t%d" % (k, t)] = v.copy()
+    ref.render(Pv, d, s, sp, group, packed)
+    out["P_final"] = Pv.copy()
+    out["G"] = np.stack(Gs); out["gscale"] = np.array(gsc, f32)
+    np.savez_compressed(os.path.join(OUT, name + ".npz"), **out)
+
+
+def golden_gnorm(ref):
+    rng = np.random.default_rng(11)
+    G = (rng.standard_normal(60007) * 7e-3).astype(f32)
+    side = (rng.standard_normal(1234) * 0.1).astype(f32)
+    small = (rng.standard_normal(1000) * 1e-3).astype(f32)
+    np.savez_compressed(os.path.join(OUT, "gnorm.npz"), G=G, side=side, small=small,
+                        gs_plain=ref.gnorm(G), gs_side=ref.gnorm(G, [side], 1),
+                        gs_noclip=ref.gnorm(G, [side], 0), gs_small=ref.gnorm(small))
+
+
+def golden_router(ref):
+    rng = np.random.default_rng(21)
+    out = {}
+    for tag, (N, E, K) in dict(a=(300, 32, 2), b=(257, 7, 3), c=(64, 4, 1), d=(100, 256, 8)).items():
+        rt = (rng.standard_normal((N, E)) * 2.0).astype(f32)
+        rt[3] = rt[3, 0]                   # exact ties: first index must win
+        bias = (rng.standard_normal((K, E)) * 0.01).astype(f32)
+        for bt, (b, bs) in dict(nb=(None, 0), wb=(bias, E)).items():
+            rp, asg, gt = ref.router_topk(rt, K, b, bs)
+            out["%s_%s_rprobs" % (tag, bt)] = rp
+            out["%s_%s_assign" % (tag, bt)] = asg
+            out["%s_%s_gate" % (tag, bt)] = gt
+        out[tag + "_rt"] = rt
+        out[tag + "_bias"] = bias
+    np.savez_compressed(os.path.join(OUT, "router.npz"), **out)
+
+
+def golden_linear(ref):
+    """g_ab / g_abt / g_atb on a rendered 4-bit weight (the selftest's odd shapes
+    rounded up to whole groups)."""
+    rng = np.random.default_rng(31)
+    M, K, N = 67, 128, 256
+    X = rng.standard_normal((M, K)).astype(f32)
+    dY = rng.standard_normal((M, N)).astype(f32)
+    W = (rng.standard_normal(K * N) * 0.02).astype(f32)
+    sp, nq, ng = loader.make_spans([K * N])
+    d = np.zeros(nq // 2, np.int8); r = np.zeros(nq, np.int8); s = np.zeros(ng, f32)
+    ref.encode(W, d, r, s, sp)
+    Wr = np.zeros(nq, f32); ref.render(Wr, d, s, sp)
+    out = dict(X=X, dY=dY, d=d, s=s)
+    Wkn = Wr.reshape(K, N)                 # layout KN: Y = X @ W
+    out["Y_kn"] = ref.g_ab(X, Wkn); out["dX_kn"] = ref.g_abt(dY, Wkn)
+    out["dW_kn"] = ref.g_atb(X, dY, np.zeros((K, N), f32))
+    Wnk = Wr.reshape(N, K)                 # layout NK: Y = X @ W^T
+    out["Y_nk"] = ref.g_abt(X, Wnk); out["dX_nk"] = ref.g_ab(dY, Wnk)
+    out["dW_nk"] = ref.g_atb(dY, X, np.zeros((N, K), f32))
+    np.savez_compressed(os.path.join(OUT, "linear.npz"), **out)
+
+
+def golden_moe(ref):
+    """One MoE layer forward+backward through the reference's moe_forward /
+    moe_backward (top-2, selection bias off, aux 0.03, stash on)."""
+    rng = np.random.default_rng(41)
+    N, D, F, E, K = 160, 128, 256, 4, 2
+
+    def quant(n):
+        sp, nq, ng = loader.make_spans([n])
+        W = (rng.standard_normal(n) * 0.02).astype(f32)
+        d = np.zeros(n // 2, np.int8); r = np.zeros(n, np.int8); s = np.zeros(ng, f32)
+        ref.encode(W, d, r, s, sp)
+        Wv = np.zeros(n, f32); ref.render(Wv, d, s, sp)
+        return d, s, Wv
+
+    d1, s1, P1 = quant(E * D * F); d3, s3, P3 = quant(E * D * F); d2, s2, P2 = quant(E * F * D)
+    Wr = (rng.standard_normal((D, E)) * 0.02).astype(f32)
+    # activations are bf16-representable so a bf16 path sees identical inputs
+    def bf(x):
+        u = x.astype(f32).view(np.uint32)
+        return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(f32)
+    fn = bf(rng.standard_normal((N, D))); fi = bf(rng.standard_normal((N, D)))
+    dout = bf(rng.standard_normal((N, D)))
+    L = ref.moe_new(N, D, F, E, K, 0.03)
+    P = L.buf("P", (L.np,))
+    for nm, v in (("wr", Wr.ravel()), ("w1", P1), ("w3", P3), ("w2", P2)):
+        P[L.off(nm):L.off(nm) + v.size] = v
+    L.buf("f_norm", (N, D))[:] = fn; L.buf("f_in", (N, D))[:] = fi; L.buf("dout", (N, D))[:] = dout
+    L.forward(); L.backward()
+    G = L.buf("G", (L.np,))
+    np.savez_compressed(
+        os.path.join(OUT, "moe.npz"), shape=np.array([N, D, F, E, K]), aux=f32(0.03),
+        d1=d1, s1=s1, d3=d3, s3=s3, d2=d2, s2=s2, Wr=Wr, fn=fn, fi=fi, dout=dout,
+        out=L.buf("out", (N, D)).copy(), rt=L.buf("rt", (N, E)).copy(),
+        rprobs=L.buf("rprobs", (N, E)).copy(), assign=L.buf("assign", (K, N), np.int32).copy(),
+        gate=L.buf("gate", (K, N)).copy(), perm=L.buf("perm", (K, N), np.int32).copy(),
+        hoff=L.buf("hoff", (K, E + 1), np.int32).copy(), d_gate=L.buf("d_gate", (K, N)).copy(),
+        dfnorm=L.buf("dfnorm", (N, D)).copy(),
+        dW1=G[L.off("w1"):L.off("w1") + E * D * F].astype(np.float16),
+        dW3=G[L.off("w3"):L.off("w3") + E * D * F].astype(np.float16),
+        dW2=G[L.off("w2"):L.off("w2") + E * D * F].astype(np.float16),
+        dWr=G[L.off("wr"):L.off("wr") + D * E].copy())
+
+
+def main():
+    ref = loader.reference(exact=True)
+    if ref is None:
+        sys.exit("oracle/_ref/libcudalm_ref_exact.so missing: run `make -C oracle ref` first")
+    golden_hash(ref)
+    golden_one_group(ref)
+    golden_state(ref, "state_g128", [128 * 40, 1000, 77, 128 * 3 + 2], 128, 7, 1, 6, seed=1)
+    golden_state(ref, "state_g64_abs", [640, 130, 64], 64, 3, 1, 4, seed=2, lrmode=1)
+    golden_state(ref, "state_g96_int8", [960, 100], 96, 127, 0, 4, seed=3)
+    golden_state(ref, "state_g256_lion", [2560, 300], 256, 1, 1, 4, seed=4, adam=0)
+    golden_gnorm(ref)
+    golden_router(ref)
+    golden_linear(ref)
+    golden_moe(ref)
+    for f in sorted(os.listdir(OUT)):
+        if f.endswith(".npz"):
+            print("%-24s %8d B" % (f, os.path.getsize(os.path.join(OUT, f))))
+
+
+if __name__ == "__main__":
+    main()
