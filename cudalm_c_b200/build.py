@@ -25,6 +25,7 @@ UNITS = {
     "qlmb_route.cu": ["--fmad=false"],
     "qlmb_dispatch.cu": [],
     "qlmb_gemm.cu": [],
+    "qlmb_linear.cu": [],
     "qlmb_gemv.cu": [],
     "qlmb_moe.cu": [],
     "qlmb_stubs.cu": [],

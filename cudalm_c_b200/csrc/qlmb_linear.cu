@@ -1,0 +1,147 @@
+// Quantised linear entry points (the reference's g_ab / g_abt / g_abt_b / g_atb
+// call sites, cudalm.cu:3133-3202) on top of the tcgen05 GEMM engine.
+#include "qlmb_common.cuh"
+#include "qlmb_gemm.cuh"
+
+namespace qlmb {
+
+// per-device scratch for the bf16 copies of fp32 operands, grown on demand
+static void *g_ws[64];
+static size_t g_ws_cap[64];
+int workspace(size_t bytes, void **out)
+{
+    int dev = 0;
+    QLMB_CUDA(cudaGetDevice(&dev));
+    QLMB_REQUIRE(dev >= 0 && dev < 64, "workspace: device index %d", dev);
+    if (g_ws_cap[dev] < bytes) {
+        if (g_ws[dev]) { QLMB_CUDA(cudaDeviceSynchronize()); QLMB_CUDA(cudaFree(g_ws[dev])); }
+        g_ws[dev] = nullptr; g_ws_cap[dev] = 0;
+        size_t cap = (bytes + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
+        QLMB_CUDA(cudaMalloc(&g_ws[dev], cap));
+        g_ws_cap[dev] = cap;
+    }
+    *out = g_ws[dev];
+    return QLMB_OK;
+}
+
+// bf16 view of an activation matrix: the matrix itself, or a converted copy in `slot`
+static int as_bf16(const void *x, int dtype, size_t n, bf16 *slot, const bf16 **out, cudaStream_t st)
+{
+    if (dtype == QLMB_BF16) { *out = (const bf16 *)x; return QLMB_OK; }
+    int rc = convert_f32_to_bf16(slot, (const float *)x, n, st);
+    *out = slot;
+    return rc;
+}
+
+static int check_linear(const char *who, int layout, int M, int K, int N, int dtype)
+{
+    QLMB_REQUIRE(layout == QLMB_KN || layout == QLMB_NK, "%s: layout %d", who, layout);
+    QLMB_REQUIRE(dtype == QLMB_F32 || dtype == QLMB_BF16, "%s: dtype %d", who, dtype);
+    QLMB_REQUIRE(M >= 0 && K > 0 && N > 0, "%s: M=%d K=%d N=%d", who, M, K, N);
+    if ((K % 128) || (N % 128)) {
+        set_error("%s: K=%d and N=%d must be multiples of the 128-element scale group", who, K, N);
+        return QLMB_E_UNSUPPORTED;
+    }
+    return QLMB_OK;
+}
+
+}  // namespace qlmb
+
+using namespace qlmb;
+
+extern "C" int qlmb_linear_fwd(void *Y, const void *X, const int8_t *codes, const float *scales, int layout,
+                               int M, int K, int N, const void *R, int dtype, void *stream)
+{
+    QLMB_REQUIRE(Y && X && codes && scales, "qlmb_linear_fwd: NULL argument");
+    int rc = check_linear("qlmb_linear_fwd", layout, M, K, N, dtype);
+    if (rc) return rc;
+    if (M == 0) return QLMB_OK;
+    cudaStream_t st = as_stream(stream);
+    void *ws = nullptr;
+    if (dtype == QLMB_F32) { rc = workspace((size_t)M * K * 2, &ws); if (rc) return rc; }
+    const bf16 *xb;
+    rc = as_bf16(X, dtype, (size_t)M * K, (bf16 *)ws, &xb, st);
+    if (rc) return rc;
+    GemmLaunch g = {};
+    g.bmode = layout == QLMB_KN ? B_DEQ_MN : B_DEQ_K;
+    g.epi = EPI_STORE; g.sched = SCHED_DENSE; g.bn = (N % 256 == 0) ? 256 : 128;
+    g.a[0] = xb; g.a_rows = M; g.a_cols = K;
+    g.w[0] = codes; g.scales[0] = scales;
+    g.w_rows = layout == QLMB_KN ? K : N; g.w_cols = layout == QLMB_KN ? N : K;
+    g.nseg = 1; g.ksteps = K / 64; g.M = M; g.N = N; g.E = 1;
+    g.out = Y; g.out_dtype = dtype; g.ldo = N; g.resid = R; g.beta = 0.0f;
+    return gemm_launch(g, st);
+}
+
+extern "C" int qlmb_linear_dgrad(void *dX, const void *dY, const int8_t *codes, const float *scales, int layout,
+                                 int M, int K, int N, float beta, int dtype, void *stream)
+{
+    QLMB_REQUIRE(dX && dY && codes && scales, "qlmb_linear_dgrad: NULL argument");
+    QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_linear_dgrad: beta %g", beta);
+    int rc = check_linear("qlmb_linear_dgrad", layout, M, K, N, dtype);
+    if (rc) return rc;
+    if (M == 0) return QLMB_OK;
+    cudaStream_t st = as_stream(stream);
+    void *ws = nullptr;
+    if (dtype == QLMB_F32) { rc = workspace((size_t)M * N * 2, &ws); if (rc) return rc; }
+    const bf16 *gb;
+    rc = as_bf16(dY, dtype, (size_t)M * N, (bf16 *)ws, &gb, st);
+    if (rc) return rc;
+    GemmLaunch g = {};
+    // the contraction now runs over N: codes W[K][N] are K-major for it, W[N][K] MN-major
+    g.bmode = layout == QLMB_KN ? B_DEQ_K : B_DEQ_MN;
+    g.epi = EPI_STORE; g.sched = SCHED_DENSE; g.bn = (K % 256 == 0) ? 256 : 128;
+    g.a[0] = gb; g.a_rows = M; g.a_cols = N;
+    g.w[0] = codes; g.scales[0] = scales;
+    g.w_rows = layout == QLMB_KN ? K : N; g.w_cols = layout == QLMB_KN ? N : K;
+    g.nseg = 1; g.ksteps = N / 64; g.M = M; g.N = K; g.E = 1;
+    g.out = dX; g.out_dtype = dtype; g.ldo = K; g.resid = nullptr; g.beta = beta;
+    return gemm_launch(g, st);
+}
+
+extern "C" int qlmb_linear_wgrad(float *dW, const void *dY, const void *X, int layout, int M, int K, int N,
+                                 float beta, int dtype, void *stream)
+{
+    QLMB_REQUIRE(dW && dY && X, "qlmb_linear_wgrad: NULL argument");
+    QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_linear_wgrad: beta %g", beta);
+    int rc = check_linear("qlmb_linear_wgrad", layout, M, K, N, dtype);
+    if (rc) return rc;
+    cudaStream_t st = as_stream(stream);
+    if (M == 0) {
+        if (beta == 0.0f) QLMB_CUDA(cudaMemsetAsync(dW, 0, (size_t)K * N * sizeof(float), st));
+        return QLMB_OK;
+    }
+    void *ws = nullptr;
+    if (dtype == QLMB_F32) { rc = workspace(((size_t)M * K + (size_t)M * N) * 2 + 256, &ws); if (rc) return rc; }
+    const bf16 *xb, *gb;
+    bf16 *slot2 = ws ? (bf16 *)((uint8_t *)ws + (((size_t)M * K * 2 + 255) & ~(size_t)255)) : nullptr;
+    rc = as_bf16(X, dtype, (size_t)M * K, (bf16 *)ws, &xb, st);
+    if (rc) return rc;
+    rc = as_bf16(dY, dtype, (size_t)M * N, slot2, &gb, st);
+    if (rc) return rc;
+    GemmLaunch g = {};
+    g.bmode = AB_TMA_MN; g.epi = EPI_ACCUM; g.sched = SCHED_DENSE;
+    // dW[K,N] = X^T dY (KN)   or   dW[N,K] = dY^T X (NK)
+    const int Md = layout == QLMB_KN ? K : N, Nd = layout == QLMB_KN ? N : K;
+    g.bn = (Nd % 256 == 0) ? 256 : 128;
+    g.a[0] = layout == QLMB_KN ? xb : gb; g.a_rows = M; g.a_cols = Md;
+    g.w[0] = layout == QLMB_KN ? gb : xb; g.w_cols = Nd; g.w_rows = 0;
+    g.nseg = 1; g.ksteps = (M + 63) / 64; g.M = Md; g.N = Nd; g.E = 1;
+    g.out = dW; g.out_dtype = QLMB_F32; g.ldo = Nd; g.beta = beta;
+    return gemm_launch(g, st);
+}
+
+// Engine check (not part of the reference's operator surface): C[M,N] (fp32) =
+// A[M,K] * B[N,K]^T with both bf16 operands delivered by TMA, i.e. the same
+// pipeline as the quantised kernels minus the dequant warps.
+extern "C" int qlmb_selftest_gemm_bf16(float *C, const void *A, const void *B, int M, int K, int N, void *stream)
+{
+    QLMB_REQUIRE(C && A && B && M > 0 && K > 0 && N > 0 && K % 64 == 0 && N % 256 == 0, "qlmb_selftest_gemm_bf16: bad shape");
+    GemmLaunch g = {};
+    g.bmode = B_TMA_K; g.epi = EPI_STORE; g.sched = SCHED_DENSE; g.bn = 256;
+    g.a[0] = A; g.a_rows = M; g.a_cols = K;
+    g.w[0] = B; g.w_rows = N; g.w_cols = K;
+    g.nseg = 1; g.ksteps = K / 64; g.M = M; g.N = N; g.E = 1;
+    g.out = C; g.out_dtype = QLMB_F32; g.ldo = N;
+    return gemm_launch(g, as_stream(stream));
+}

@@ -1,0 +1,202 @@
+// MoE expert FFN layer: host-side control flow of the reference's moe_forward /
+// moe_backward (cudalm.cu:4151-4393) over the kernels of this library.  Nothing
+// here synchronises with the host: expert row counts, the row-tile table and
+// the padded offsets stay on the device (the reference reads the offsets back
+// once per layer, cudalm.cu:3554-3559).
+//
+// Row layout: the K*N routed slots n' = k*N+n are grouped by expert in stable
+// order ("merged" grouping, cudalm.cu:3532-3535) and every expert's segment is
+// padded with zero rows to a multiple of 128, so each 128-row GEMM tile belongs
+// to one expert and filler rows contribute exact zeros to the weight gradients.
+#include <string.h>
+#include "qlmb_common.cuh"
+#include "qlmb_gemm.cuh"
+
+namespace qlmb {
+
+struct Arena {
+    size_t rows_cap;     // padded row capacity
+    float *rt, *rprobs, *gate, *d_gate, *drt, *wr_scratch;
+    int *assign, *perm, *inv, *off, *counts, *tile_expert, *ntiles, *bad, *chunk;
+    bf16 *Xp, *gp, *up, *ap, *yp, *dyp, *dgp, *dup, *dXp;
+    size_t bytes;
+};
+
+static size_t take(size_t &cur, size_t bytes)
+{
+    size_t at = cur;
+    cur += (bytes + 255) & ~(size_t)255;
+    return at;
+}
+
+// Carves the arena; with base == nullptr only the size is computed.
+static Arena carve(void *base, int N, int D, int F, int E, int K)
+{
+    Arena a;
+    memset(&a, 0, sizeof a);
+    size_t KN = (size_t)K * N;
+    a.rows_cap = (KN + (size_t)E * 127 + 127) / 128 * 128;
+    size_t R = a.rows_cap, cur = 0;
+    uint8_t *b = (uint8_t *)base;
+#define MEMBER(field, type, count) a.field = (type *)(b + take(cur, (size_t)(count) * sizeof(type)))
+    MEMBER(rt, float, (size_t)N * E);
+    MEMBER(rprobs, float, (size_t)N * E);
+    MEMBER(gate, float, KN);
+    MEMBER(d_gate, float, KN);
+    MEMBER(drt, float, (size_t)N * E);
+    MEMBER(wr_scratch, float, (size_t)((N + 255) / 256) * D * E);
+    MEMBER(assign, int, KN);
+    MEMBER(perm, int, R);
+    MEMBER(inv, int, KN);
+    MEMBER(off, int, E + 1);
+    MEMBER(counts, int, E);
+    MEMBER(tile_expert, int, R / 128);
+    MEMBER(ntiles, int, 1);
+    MEMBER(bad, int, 1);
+    MEMBER(chunk, int, perm_scratch_ints(N, E, K, 1));
+    MEMBER(Xp, bf16, R * D);
+    MEMBER(gp, bf16, R * F);
+    MEMBER(up, bf16, R * F);
+    MEMBER(ap, bf16, R * F);
+    MEMBER(yp, bf16, R * D);
+    MEMBER(dyp, bf16, R * D);
+    MEMBER(dgp, bf16, R * F);
+    MEMBER(dup, bf16, R * F);
+    MEMBER(dXp, bf16, R * D);
+#undef MEMBER
+    a.bytes = cur;
+    return a;
+}
+
+static int check_layer(const char *who, const qlmb_moe_layer *L)
+{
+    QLMB_REQUIRE(L, "%s: NULL layer", who);
+    QLMB_REQUIRE(L->N > 0 && L->E > 0 && L->E <= 256 && L->K > 0 && L->K <= 8 && L->K <= L->E, "%s: N=%d E=%d K=%d", who, L->N, L->E, L->K);
+    QLMB_REQUIRE(L->dtype == QLMB_F32 || L->dtype == QLMB_BF16, "%s: dtype %d", who, L->dtype);
+    QLMB_REQUIRE(L->w1_codes && L->w3_codes && L->w2_codes && L->w1_scales && L->w3_scales && L->w2_scales && L->wr, "%s: NULL weight pointer", who);
+    if ((L->D % 128) || (L->F % 128)) {
+        set_error("%s: D=%d and F=%d must be multiples of 128", who, L->D, L->F);
+        return QLMB_E_UNSUPPORTED;
+    }
+    return QLMB_OK;
+}
+
+}  // namespace qlmb
+
+using namespace qlmb;
+
+extern "C" size_t qlmb_moe_arena_bytes(int N, int D, int F, int E, int K)
+{
+    if (N <= 0 || D <= 0 || F <= 0 || E <= 0 || K <= 0) return 0;
+    return carve(nullptr, N, D, F, E, K).bytes;
+}
+
+extern "C" void *qlmb_moe_arena_member(void *arena, int N, int D, int F, int E, int K, const char *name)
+{
+    if (!arena || !name || N <= 0 || D <= 0 || F <= 0 || E <= 0 || K <= 0) return nullptr;
+    Arena a = carve(arena, N, D, F, E, K);
+#define NAMED(f) if (!strcmp(name, #f)) return (void *)a.f
+    NAMED(rt); NAMED(rprobs); NAMED(gate); NAMED(d_gate); NAMED(drt); NAMED(assign); NAMED(perm); NAMED(inv);
+    NAMED(off); NAMED(counts); NAMED(tile_expert); NAMED(ntiles); NAMED(bad); NAMED(Xp); NAMED(gp); NAMED(up);
+    NAMED(ap); NAMED(yp); NAMED(dyp); NAMED(dgp); NAMED(dup); NAMED(dXp);
+#undef NAMED
+    return nullptr;
+}
+
+extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in,
+                                const void *f_norm, void *stream)
+{
+    int rc = check_layer("qlmb_moe_forward", L);
+    if (rc) return rc;
+    QLMB_REQUIRE(arena && out && f_in && f_norm, "qlmb_moe_forward: NULL argument");
+    QLMB_REQUIRE(((uintptr_t)arena & 255) == 0, "qlmb_moe_forward: arena must be 256-byte aligned");
+    const int N = L->N, D = L->D, F = L->F, E = L->E, K = L->K;
+    Arena a = carve(arena, N, D, F, E, K);
+    cudaStream_t st = as_stream(stream);
+    const int R = (int)a.rows_cap;
+
+    // router: logits, softmax top-k (cudalm.cu:4158, 4174)
+    if ((rc = router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc;
+    if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc;
+    // expert grouping, padded to 128-row tiles (cudalm.cu:4189)
+    if ((rc = perm_build(a.assign, N, E, K, 1, 128, a.perm, a.inv, a.off, a.counts, a.bad, a.tile_expert, a.ntiles, 128, a.chunk, st))) return rc;
+    if ((rc = gather_rows(a.Xp, f_norm, L->dtype, a.perm, a.off + E, R, N, D, st))) return rc;
+
+    // gate/up projections with SwiGLU in the epilogue (cudalm.cu:4211-4215)
+    GemmLaunch g = {};
+    g.bmode = B_DEQ_MN; g.epi = EPI_SWIGLU; g.sched = SCHED_ROWS; g.bn = 256;
+    g.a[0] = a.Xp; g.a_rows = R; g.a_cols = D;
+    g.w[0] = L->w1_codes; g.w[1] = L->w3_codes; g.scales[0] = L->w1_scales; g.scales[1] = L->w3_scales;
+    g.w_rows = D; g.w_cols = F; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
+    g.tile_expert = a.tile_expert; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 128;
+    g.gp = a.gp; g.up = a.up; g.ap = a.ap; g.ldo = F;
+    if ((rc = gemm_launch(g, st))) return rc;
+
+    // down projection (cudalm.cu:4224-4225)
+    GemmLaunch h = {};
+    h.bmode = B_DEQ_MN; h.epi = EPI_STORE; h.sched = SCHED_ROWS; h.bn = (D % 256 == 0) ? 256 : 128;
+    h.a[0] = a.ap; h.a_rows = R; h.a_cols = F;
+    h.w[0] = L->w2_codes; h.scales[0] = L->w2_scales;
+    h.w_rows = F; h.w_cols = D; h.nseg = 1; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
+    h.tile_expert = a.tile_expert; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 128;
+    h.out = a.yp; h.out_dtype = QLMB_BF16; h.ldo = D;
+    if ((rc = gemm_launch(h, st))) return rc;
+
+    // residual + gated sum over the K passes (cudalm.cu:4177, 4227)
+    return combine_rows(out, f_in, L->dtype, a.yp, a.inv, a.gate, N, D, K, st);
+}
+
+extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const void *dout,
+                                 const void *f_norm, float *dW1, float *dW3, float *dW2, float *dWr,
+                                 float beta, void *stream)
+{
+    int rc = check_layer("qlmb_moe_backward", L);
+    if (rc) return rc;
+    QLMB_REQUIRE(arena && dfnorm && dout && f_norm && dW1 && dW3 && dW2 && dWr, "qlmb_moe_backward: NULL argument");
+    QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_moe_backward: beta %g", beta);
+    const int N = L->N, D = L->D, F = L->F, E = L->E, K = L->K;
+    Arena a = carve(arena, N, D, F, E, K);
+    cudaStream_t st = as_stream(stream);
+    const int R = (int)a.rows_cap;
+
+    // d_gate and the gated dy (cudalm.cu:4317-4319)
+    if ((rc = dgate_rows(a.dyp, a.d_gate, dout, L->dtype, a.yp, a.perm, a.gate, a.off + E, R, N, D, st))) return rc;
+
+    // d(act) = dy W2^T with the SwiGLU backward in the epilogue (cudalm.cu:4336, 4339-4341)
+    GemmLaunch g = {};
+    g.bmode = B_DEQ_K; g.epi = EPI_SWIGLU_BWD; g.sched = SCHED_ROWS; g.bn = (F % 256 == 0) ? 256 : 128;
+    g.a[0] = a.dyp; g.a_rows = R; g.a_cols = D;
+    g.w[0] = L->w2_codes; g.scales[0] = L->w2_scales;
+    g.w_rows = F; g.w_cols = D; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
+    g.tile_expert = a.tile_expert; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 128;
+    g.gp = a.gp; g.up = a.up; g.dgp = a.dgp; g.dup = a.dup; g.ldo = F;
+    if ((rc = gemm_launch(g, st))) return rc;
+
+    // dXp = dg W1^T + du W3^T in one accumulator (cudalm.cu:4365-4366)
+    GemmLaunch h = {};
+    h.bmode = B_DEQ_K; h.epi = EPI_STORE; h.sched = SCHED_ROWS; h.bn = (D % 256 == 0) ? 256 : 128;
+    h.a[0] = a.dgp; h.a[1] = a.dup; h.a_rows = R; h.a_cols = F;
+    h.w[0] = L->w1_codes; h.w[1] = L->w3_codes; h.scales[0] = L->w1_scales; h.scales[1] = L->w3_scales;
+    h.w_rows = D; h.w_cols = F; h.nseg = 2; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
+    h.tile_expert = a.tile_expert; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 128;
+    h.out = a.dXp; h.out_dtype = QLMB_BF16; h.ldo = D;
+    if ((rc = gemm_launch(h, st))) return rc;
+
+    // weight gradients, contraction over each expert's rows (cudalm.cu:4335, 4363-4364)
+    struct { const bf16 *A; int Ma; const bf16 *B; int Nb; float *out; } wg[3] = {
+        {a.Xp, D, a.dgp, F, dW1}, {a.Xp, D, a.dup, F, dW3}, {a.ap, F, a.dyp, D, dW2}};
+    for (int i = 0; i < 3; i++) {
+        GemmLaunch w = {};
+        w.bmode = AB_TMA_MN; w.epi = EPI_ACCUM; w.sched = SCHED_GROUPK; w.bn = (wg[i].Nb % 256 == 0) ? 256 : 128;
+        w.a[0] = wg[i].A; w.a_rows = R; w.a_cols = wg[i].Ma;
+        w.w[0] = wg[i].B; w.w_cols = wg[i].Nb;
+        w.nseg = 1; w.M = wg[i].Ma; w.N = wg[i].Nb; w.E = E; w.off = a.off;
+        w.out = wg[i].out; w.out_dtype = QLMB_F32; w.ldo = wg[i].Nb; w.beta = beta;
+        if ((rc = gemm_launch(w, st))) return rc;
+    }
+
+    // router backward (cudalm.cu:4372-4391)
+    if ((rc = router_bwd(a.drt, a.rprobs, a.assign, a.d_gate, a.counts, N, E, K, L->aux, st))) return rc;
+    if ((rc = unpermute_rows(dfnorm, L->dtype, a.dXp, a.inv, a.drt, L->wr, N, D, E, K, st))) return rc;
+    return router_wgrad(dWr, f_norm, L->dtype, a.drt, a.wr_scratch, N, D, E, beta, st);
+}

@@ -43,3 +43,44 @@ def moe_perm_all(assign, E, merged=False, pad=1):
     check(lib().qlmb_perm_build(ptr(assign), N, E, K, 1 if merged else 0, pad, ptr(perm), ptr(inv), ptr(off),
                                 ptr(counts), ptr(bad), stream_ptr()))
     return perm, inv, off, counts, bad
+
+
+class MoeLayerState:
+    """One MoE layer's 4-bit expert weights, router and activation arena: the
+    slice of the reference's GA / P that moe_forward and moe_backward touch."""
+
+    def __init__(self, N, D, F, E, K, q1, q3, q2, wr, dtype=torch.bfloat16, aux=0.03, bias=None, bias_stride=0):
+        self.N, self.D, self.F, self.E, self.K = N, D, F, E, K
+        self.q1, self.q3, self.q2, self.wr, self.bias = q1, q3, q2, wr, bias   # (codes, scales) pairs
+        self.dtype = dtype
+        dev = wr.device
+        nbytes = lib().qlmb_moe_arena_bytes(N, D, F, E, K)
+        self.arena = torch.zeros(nbytes + 256, dtype=torch.uint8, device=dev)
+        self.arena_ptr = (self.arena.data_ptr() + 255) // 256 * 256
+        self.c = MoeLayer(N, D, F, E, K, BF16 if dtype == torch.bfloat16 else F32,
+                          ptr(q1[0]), ptr(q3[0]), ptr(q2[0]), ptr(q1[1]), ptr(q3[1]), ptr(q2[1]),
+                          ptr(wr), ptr(bias), bias_stride, aux)
+        self.rows_cap = (K * N + E * 127 + 127) // 128 * 128
+
+    def member(self, name, shape, dtype):
+        """A named arena member viewed as a tensor (no copy)."""
+        p = lib().qlmb_moe_arena_member(self.arena_ptr, self.N, self.D, self.F, self.E, self.K, name.encode())
+        if not p:
+            raise KeyError(name)
+        off = p - self.arena.data_ptr()
+        n = 1
+        for s in shape:
+            n *= s
+        esz = torch.empty(0, dtype=dtype).element_size()
+        return self.arena[off:off + n * esz].view(dtype).view(*shape)
+
+    def forward(self, f_in, f_norm, out=None):
+        out = out if out is not None else torch.empty_like(f_in)
+        check(lib().qlmb_moe_forward(self.c, self.arena_ptr, ptr(out), ptr(f_in), ptr(f_norm), stream_ptr()))
+        return out
+
+    def backward(self, dout, f_norm, dW1, dW3, dW2, dWr, beta=1.0, dfnorm=None):
+        dfnorm = dfnorm if dfnorm is not None else torch.empty_like(dout)
+        check(lib().qlmb_moe_backward(self.c, self.arena_ptr, ptr(dfnorm), ptr(dout), ptr(f_norm), ptr(dW1),
+                                      ptr(dW3), ptr(dW2), ptr(dWr), beta, stream_ptr()))
+        return dfnorm

@@ -209,7 +209,7 @@ def main():
         sys.exit("oracle/_ref/libcudalm_ref_exact.so missing: run `make -C oracle ref` first")
     golden_hash(ref)
     golden_one_group(ref)
-    golden_state(ref, "state_g128", [128 * 40, 1000, 77, 128 * 3 + 2], 128, 7, 1, 6, seed=1)
+    golden_state(ref, "state_g128", [128 * 40, 1000, 78, 128 * 3 + 2], 128, 7, 1, 6, seed=1)
     golden_state(ref, "state_g64_abs", [640, 130, 64], 64, 3, 1, 4, seed=2, lrmode=1)
     golden_state(ref, "state_g96_int8", [960, 100], 96, 127, 0, 4, seed=3)
     golden_state(ref, "state_g256_lion", [2560, 300], 256, 1, 1, 4, seed=4, adam=0)
