@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Headline benchmark: one MoE expert-FFN layer with 4-bit weights, forward +
+backward (BASELINE config 2: 32 experts, top-2 softmax routing, d_model 768,
+d_ff 1536, 8192 tokens of bf16 activations per GPU).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one qlmb_moe_forward + qlmb_moe_backward over one batch of synthetic
+tokens.  `value` times K steps with inputs resident in HBM (CUDA events, max over
+ranks); `e2e` runs the same calls from pinned HOST buffers with the H2D / D2H
+copies inside the timed region.  FLOPs are counted on routed rows only
+(347.9 GFLOP per step and GPU), never on the zero filler rows.
+--impl reference times the unmodified reference's CPU build (moe_forward +
+moe_backward on the same shapes) on this machine's host cores.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(N=8192, D=768, F=1536, E=32, K=2)
+METRIC = "moe_grouped_dequant_gemm_tflops"
+UNIT = "TFLOP/s"
+
+
+def flops_per_step(c, rows=None):
+    rows = c["K"] * c["N"] if rows is None else rows
+    fwd = 2.0 * rows * c["D"] * (2 * c["F"]) + 2.0 * rows * c["F"] * c["D"]
+    return 3.0 * fwd
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm=d["hbm_gbs"], tf_burst=d["bf16_tflops"], tf_sustained=d["bf16_tflops_sustained"], src="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, src="fallback")
+
+
+class ClockSampler(threading.Thread):
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self.stop_flag = index, [], False
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def summary(self):
+        if not self.rows:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unsampled"])
+        mhz = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return dict(sm_mhz=mhz[len(mhz) // 2] if mhz else None,
+                    sm_max_mhz=int(self.rows[0][1]) if self.rows[0][1].isdigit() else None,
+                    reasons=reasons, samples=len(self.rows))
+
+
+def make_layer(dev, seed):
+    """Synthetic layer of the config-2 shape: expert weights ~ N(0,0.02) quantised
+    by the library's own encode kernel (bit-identical to the reference's, see the
+    parity tests), router ~ N(0,0.02), activations ~ N(0,1) in bf16."""
+    import torch
+    from cudalm_c_b200 import moe, qlm
+    c = CFG
+    gen = torch.Generator(device=dev); gen.manual_seed(seed)
+    qs = []
+    for rows, cols in ((c["E"] * c["D"], c["F"]), (c["E"] * c["D"], c["F"]), (c["E"] * c["F"], c["D"])):
+        n = rows * cols
+        Q = qlm.Qlm([(0, n)], n, dev)
+        P = torch.randn(n, device=dev, generator=gen) * 0.02
+        Q.init_from(P, render=False)
+        qs.append((Q.d, Q.s))
+        del P
+    wr = torch.randn(c["D"], c["E"], device=dev, generator=gen) * 0.02
+    L = moe.MoeLayerState(c["N"], c["D"], c["F"], c["E"], c["K"], qs[0], qs[1], qs[2], wr, dtype=torch.bfloat16)
+    acts = [torch.randn(c["N"], c["D"], device=dev, generator=gen).bfloat16() for _ in range(3)]
+    grads = [torch.zeros(c["E"], c["D"], c["F"], device=dev), torch.zeros(c["E"], c["D"], c["F"], device=dev),
+             torch.zeros(c["E"], c["F"], c["D"], device=dev), torch.zeros(c["D"], c["E"], device=dev)]
+    return L, acts, grads
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import cudalm_c_b200 as q
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = q.lib()
+    pk = peaks()
+    c = CFG
+    fn_dev = None
+    if world > 1:
+        from cudalm_c_b200 import dist_moe
+        runner = dist_moe.ExpertParallelLayer(c, dev, rank, world, seed=1234)
+        step = runner.step
+        launches_per_step = runner.launches_per_step
+        parallelism = "ep%d" % world
+    else:
+        L, (fn, fi, dout), grads = make_layer(dev, 1234)
+        out = torch.empty_like(fi); dfn = torch.empty_like(fi)
+
+        def step():
+            L.forward(fi, fn, out=out)
+            L.backward(dout, fn, grads[0], grads[1], grads[2], grads[3], beta=0.0, dfnorm=dfn)
+        launches_per_step = 19
+        parallelism = "single"
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    q.check(lib.qlmb_check_device(None))
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    sampler.stop_flag = True
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    value = world * flops_per_step(c) / (ms * 1e-3) / 1e12
+
+    # per-kernel durations (events inside the library) over a few extra steps
+    roof, kern = None, {}
+    if world == 1:
+        q.check(lib.qlmb_prof_enable(1))
+        reps = 5
+        for _ in range(reps):
+            step()
+        names = C.create_string_buffer(64 * 512); msb = (C.c_float * 512)()
+        n = lib.qlmb_prof_read(names, msb, 512)
+        lib.qlmb_prof_enable(0)
+        for i in range(max(n, 0)):
+            nm = names.raw[64 * i:64 * i + 64].split(b"\0")[0].decode()
+            kern.setdefault(nm, []).append(msb[i])
+        kern = {k: sum(v) / len(v) for k, v in kern.items()}
+        rows = c["K"] * c["N"]
+        fl = {"gemm_gate_up_swiglu": 2.0 * rows * c["D"] * 2 * c["F"], "gemm_down": 2.0 * rows * c["F"] * c["D"],
+              "gemm_dact_swiglu_bwd": 2.0 * rows * c["D"] * c["F"], "gemm_dx": 2.0 * rows * 2 * c["F"] * c["D"],
+              "gemm_wgrad_w1": 2.0 * rows * c["D"] * c["F"], "gemm_wgrad_w3": 2.0 * rows * c["D"] * c["F"],
+              "gemm_wgrad_w2": 2.0 * rows * c["D"] * c["F"]}
+        top = max((k for k in kern if k in fl), key=lambda k: kern[k])
+        ach = fl[top] / (kern[top] * 1e-3) / 1e12
+        long_run = ms * args.steps > 1000.0
+        peak = pk["tf_sustained"] if long_run else pk["tf_burst"]
+        roof = dict(bound="tensor", kernel=top, achieved=round(ach, 1), peak=peak, unit="TFLOP/s", frac=round(ach / peak, 4),
+                    traffic=None, peak_kind=("sustained" if long_run else "burst") + " bf16, of " + pk["src"],
+                    kernel_ms={k: round(v, 4) for k, v in sorted(kern.items(), key=lambda kv: -kv[1])},
+                    gemm_phase_tflops=round(sum(fl.values()) / (sum(kern[k] for k in fl) * 1e-3) / 1e12, 1))
+
+    # end to end from pinned host buffers through the same C-ABI calls
+    e2e = None
+    if world == 1:
+        hin = [torch.empty(c["N"], c["D"], dtype=torch.bfloat16).pin_memory() for _ in range(3)]
+        for h, d in zip(hin, (fn, fi, dout)):
+            h.copy_(d)
+        hout = [torch.empty(c["N"], c["D"], dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+
+        def step_e2e():
+            fn.copy_(hin[0], non_blocking=True); fi.copy_(hin[1], non_blocking=True); dout.copy_(hin[2], non_blocking=True)
+            step()
+            hout[0].copy_(out, non_blocking=True); hout[1].copy_(dfn, non_blocking=True)
+        for _ in range(3):
+            step_e2e()
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        e0.record()
+        for _ in range(args.steps):
+            step_e2e()
+        e1.record()
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - w0) * 1e3 / args.steps
+        ms_e = max(e0.elapsed_time(e1) / args.steps, wall)
+        bi = 3 * c["N"] * c["D"] * 2
+        bo = 2 * c["N"] * c["D"] * 2
+        e2e = dict(value=round(flops_per_step(c) / (ms_e * 1e-3) / 1e12, 2), unit=UNIT, h2d_bytes_per_step=bi,
+                   d2h_bytes_per_step=bo, ms_per_step=round(ms_e, 4))
+    q.check(lib.qlmb_check_device(None))
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(steps=2)
+    if rank == 0:
+        line = dict(metric=METRIC, value=round(value, 2), unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                    ms_per_step=round(ms, 4), higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                    data="synthetic",
+                    config=dict(workload="MoE expert FFN layer fwd+bwd, 4-bit weights (BASELINE config 2)", tokens_per_gpu=c["N"],
+                                d_model=c["D"], d_ff=c["F"], experts=c["E"], top_k=c["K"], parallelism=parallelism,
+                                flops_per_step_per_gpu=flops_per_step(c), weight_grad="beta=0 (overwrite; one writer per expert)",
+                                l2="per-step working set ~1.3 GB (arena 447 MB + 453 MB of weight gradients) exceeds the 126 MB L2"),
+                    roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=launches_per_step * args.steps,
+                    clocks=sampler.summary())
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(steps=2, fast=True):
+    """The reference's own moe_forward + moe_backward (CPU build, all host threads)
+    on the config-2 shapes; weights are the rendered view of encoded N(0,0.02)."""
+    import numpy as np
+    from oracle import loader
+    ref = loader.reference(exact=not fast)
+    kind = "reference"
+    if ref is None:
+        return dict(value=None, unit=UNIT, cores=0, kind="reference", sample="oracle/_ref not built on this machine")
+    c = CFG
+    rng = np.random.default_rng(1234)
+    L = ref.moe_new(c["N"], c["D"], c["F"], c["E"], c["K"], 0.03)
+    P = L.buf("P", (L.np,))
+    nW = c["E"] * c["D"] * c["F"]
+    o = loader.restatement()
+    for nm in ("w1", "w3", "w2"):
+        W = (rng.standard_normal(nW, dtype=np.float32) * np.float32(0.02))
+        sp, nq, ng = loader.make_spans([nW])
+        d = np.zeros(nW // 2, np.int8); r = np.zeros(nW, np.int8); s = np.zeros(ng, np.float32)
+        ref.encode(W, d, r, s, sp)
+        ref.render(W, d, s, sp)
+        P[L.off(nm):L.off(nm) + nW] = W
+    P[L.off("wr"):L.off("wr") + c["D"] * c["E"]] = rng.standard_normal(c["D"] * c["E"], dtype=np.float32) * np.float32(0.02)
+    for nm in ("f_norm", "f_in", "dout"):
+        L.buf(nm, (c["N"], c["D"]))[:] = rng.standard_normal((c["N"], c["D"]), dtype=np.float32)
+    L.forward(); L.backward()                       # warm-up (page faults, thread pool)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        L.forward(); L.backward()
+    dt = (time.perf_counter() - t0) / steps
+    return dict(value=round(flops_per_step(c) / dt / 1e12, 4), unit=UNIT, cores=ref.threads, kind=kind,
+                sample="%d full steps (8192 tokens) after 1 warm-up, %.2f s/step, reference CPU build, stock flags" % (steps, dt),
+                ms_per_step=round(dt * 1e3, 1))
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 5))
+    cpu = cpu_baseline(steps=steps)
+    if cpu["value"] is None:
+        print(json.dumps(dict(impl="reference", unavailable=cpu["sample"])))
+        return
+    c = CFG
+    line = dict(impl="reference", metric=METRIC, value=cpu["value"], unit=UNIT, n_gpus=world, steps=steps, warmup=1,
+                ms_per_step=cpu["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32",
+                data="synthetic",
+                config=dict(workload="MoE expert FFN layer fwd+bwd, 4-bit weights (BASELINE config 2)", tokens_per_gpu=c["N"],
+                            d_model=c["D"], d_ff=c["F"], experts=c["E"], top_k=c["K"], parallelism="cpu",
+                            flops_per_step_per_gpu=flops_per_step(c)),
+                cpu_baseline=cpu, e2e=dict(value=cpu["value"], unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the 8192 of config 2); smaller values are for profiler captures")
+    args = ap.parse_args()
+    if args.tokens > 0:
+        CFG["N"] = args.tokens
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -33,6 +33,8 @@ PROTOTYPES = {
     "qlmb_last_error": (C.c_char_p, []),
     "qlmb_version": (ci, []),
     "qlmb_check_device": (ci, [vp]),
+    "qlmb_prof_enable": (ci, [ci]),
+    "qlmb_prof_read": (ci, [vp, vp, ci]),
     "qlmb_encode": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_render": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, cf, cf, cf, cf, cf, vp, cf, cf,

@@ -31,6 +31,12 @@ int *device_error_word(void);                            // per-device int, lazi
 
 static inline cudaStream_t as_stream(void *s) { return (cudaStream_t)s; }
 int sm_count(void);                                      // SMs of the current device
+// Times the enclosed launches with CUDA events when qlmb_prof_enable(1) was called.
+struct ProfScope {
+    int slot; cudaStream_t stream;
+    ProfScope(const char *name, cudaStream_t st);
+    ~ProfScope();
+};
 
 // ---- device helpers --------------------------------------------------------
 // splitmix64 finaliser, low 32 bits (reference qlm.cuh:78-82).

@@ -598,6 +598,7 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
     int rc = load_encode();
     if (rc) return rc;
     QLMB_REQUIRE(g.bn == 128 || g.bn == 256, "gemm: bn %d", g.bn);
+    QLMB_REQUIRE(g.sched != SCHED_GROUPK || g.M % BM == 0, "gemm: grouped weight gradient needs M=%d to be a multiple of %d", g.M, BM);
     QLMB_REQUIRE(g.N % g.bn == 0 || g.epi == EPI_SWIGLU, "gemm: N=%d is not a multiple of the %d-column tile", g.N, g.bn);
     GemmParams p;
     memset(&p, 0, sizeof p);
@@ -646,6 +647,7 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
     if (total <= 0) return QLMB_OK;
     int grid = sm_count();
     if (total < grid) grid = (int)total;
+    ProfScope prof(g.name ? g.name : "gemm", st);
 
 #define INST(BM_, EP_, SC_, BN_) if (g.bmode == BM_ && g.epi == EP_ && g.sched == SC_ && g.bn == BN_) return launch_inst<BM_, EP_, SC_, BN_>(p, grid, st)
     // dense linears

@@ -44,6 +44,7 @@ struct GemmLaunch {
     void *out; int out_dtype; long long ldo;
     const void *resid; float beta;
     bf16 *gp, *up, *ap, *dgp, *dup;
+    const char *name;              // label for the optional per-kernel timing
 };
 
 int gemm_launch(const GemmLaunch &g, cudaStream_t st);

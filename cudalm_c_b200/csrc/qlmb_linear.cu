@@ -52,10 +52,10 @@ using namespace qlmb;
 extern "C" int qlmb_linear_fwd(void *Y, const void *X, const int8_t *codes, const float *scales, int layout,
                                int M, int K, int N, const void *R, int dtype, void *stream)
 {
-    QLMB_REQUIRE(Y && X && codes && scales, "qlmb_linear_fwd: NULL argument");
     int rc = check_linear("qlmb_linear_fwd", layout, M, K, N, dtype);
     if (rc) return rc;
     if (M == 0) return QLMB_OK;
+    QLMB_REQUIRE(Y && X && codes && scales, "qlmb_linear_fwd: NULL argument");
     cudaStream_t st = as_stream(stream);
     void *ws = nullptr;
     if (dtype == QLMB_F32) { rc = workspace((size_t)M * K * 2, &ws); if (rc) return rc; }
@@ -76,11 +76,11 @@ extern "C" int qlmb_linear_fwd(void *Y, const void *X, const int8_t *codes, cons
 extern "C" int qlmb_linear_dgrad(void *dX, const void *dY, const int8_t *codes, const float *scales, int layout,
                                  int M, int K, int N, float beta, int dtype, void *stream)
 {
-    QLMB_REQUIRE(dX && dY && codes && scales, "qlmb_linear_dgrad: NULL argument");
     QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_linear_dgrad: beta %g", beta);
     int rc = check_linear("qlmb_linear_dgrad", layout, M, K, N, dtype);
     if (rc) return rc;
     if (M == 0) return QLMB_OK;
+    QLMB_REQUIRE(dX && dY && codes && scales, "qlmb_linear_dgrad: NULL argument");
     cudaStream_t st = as_stream(stream);
     void *ws = nullptr;
     if (dtype == QLMB_F32) { rc = workspace((size_t)M * N * 2, &ws); if (rc) return rc; }
@@ -102,7 +102,7 @@ extern "C" int qlmb_linear_dgrad(void *dX, const void *dY, const int8_t *codes, 
 extern "C" int qlmb_linear_wgrad(float *dW, const void *dY, const void *X, int layout, int M, int K, int N,
                                  float beta, int dtype, void *stream)
 {
-    QLMB_REQUIRE(dW && dY && X, "qlmb_linear_wgrad: NULL argument");
+    QLMB_REQUIRE(dW && (M == 0 || (dY && X)), "qlmb_linear_wgrad: NULL argument");
     QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_linear_wgrad: beta %g", beta);
     int rc = check_linear("qlmb_linear_wgrad", layout, M, K, N, dtype);
     if (rc) return rc;

@@ -116,11 +116,14 @@ extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out,
     const int R = (int)a.rows_cap;
 
     // router: logits, softmax top-k (cudalm.cu:4158, 4174)
-    if ((rc = router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc;
-    if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc;
+    { ProfScope ps("router_logits", st); if ((rc = router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc; }
+    { ProfScope ps("router_topk", st);
+    if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc; }
     // expert grouping, padded to 128-row tiles (cudalm.cu:4189)
-    if ((rc = perm_build(a.assign, N, E, K, 1, 128, a.perm, a.inv, a.off, a.counts, a.bad, a.tile_expert, a.ntiles, 128, a.chunk, st))) return rc;
-    if ((rc = gather_rows(a.Xp, f_norm, L->dtype, a.perm, a.off + E, R, N, D, st))) return rc;
+    { ProfScope ps("perm_build", st);
+    if ((rc = perm_build(a.assign, N, E, K, 1, 128, a.perm, a.inv, a.off, a.counts, a.bad, a.tile_expert, a.ntiles, 128, a.chunk, st))) return rc; }
+    { ProfScope ps("gather_rows", st);
+    if ((rc = gather_rows(a.Xp, f_norm, L->dtype, a.perm, a.off + E, R, N, D, st))) return rc; }
 
     // gate/up projections with SwiGLU in the epilogue (cudalm.cu:4211-4215)
     GemmLaunch g = {};
@@ -129,7 +132,7 @@ extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out,
     g.w[0] = L->w1_codes; g.w[1] = L->w3_codes; g.scales[0] = L->w1_scales; g.scales[1] = L->w3_scales;
     g.w_rows = D; g.w_cols = F; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
     g.tile_expert = a.tile_expert; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 128;
-    g.gp = a.gp; g.up = a.up; g.ap = a.ap; g.ldo = F;
+    g.gp = a.gp; g.up = a.up; g.ap = a.ap; g.ldo = F; g.name = "gemm_gate_up_swiglu";
     if ((rc = gemm_launch(g, st))) return rc;
 
     // down projection (cudalm.cu:4224-4225)
@@ -139,10 +142,11 @@ extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out,
     h.w[0] = L->w2_codes; h.scales[0] = L->w2_scales;
     h.w_rows = F; h.w_cols = D; h.nseg = 1; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
     h.tile_expert = a.tile_expert; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 128;
-    h.out = a.yp; h.out_dtype = QLMB_BF16; h.ldo = D;
+    h.out = a.yp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_down";
     if ((rc = gemm_launch(h, st))) return rc;
 
     // residual + gated sum over the K passes (cudalm.cu:4177, 4227)
+    ProfScope ps("combine_rows", st);
     return combine_rows(out, f_in, L->dtype, a.yp, a.inv, a.gate, N, D, K, st);
 }
 
@@ -160,7 +164,8 @@ extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfn
     const int R = (int)a.rows_cap;
 
     // d_gate and the gated dy (cudalm.cu:4317-4319)
-    if ((rc = dgate_rows(a.dyp, a.d_gate, dout, L->dtype, a.yp, a.perm, a.gate, a.off + E, R, N, D, st))) return rc;
+    { ProfScope ps("dgate_rows", st);
+    if ((rc = dgate_rows(a.dyp, a.d_gate, dout, L->dtype, a.yp, a.perm, a.gate, a.off + E, R, N, D, st))) return rc; }
 
     // d(act) = dy W2^T with the SwiGLU backward in the epilogue (cudalm.cu:4336, 4339-4341)
     GemmLaunch g = {};
@@ -169,7 +174,7 @@ extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfn
     g.w[0] = L->w2_codes; g.scales[0] = L->w2_scales;
     g.w_rows = F; g.w_cols = D; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
     g.tile_expert = a.tile_expert; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 128;
-    g.gp = a.gp; g.up = a.up; g.dgp = a.dgp; g.dup = a.dup; g.ldo = F;
+    g.gp = a.gp; g.up = a.up; g.dgp = a.dgp; g.dup = a.dup; g.ldo = F; g.name = "gemm_dact_swiglu_bwd";
     if ((rc = gemm_launch(g, st))) return rc;
 
     // dXp = dg W1^T + du W3^T in one accumulator (cudalm.cu:4365-4366)
@@ -179,24 +184,25 @@ extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfn
     h.w[0] = L->w1_codes; h.w[1] = L->w3_codes; h.scales[0] = L->w1_scales; h.scales[1] = L->w3_scales;
     h.w_rows = D; h.w_cols = F; h.nseg = 2; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
     h.tile_expert = a.tile_expert; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 128;
-    h.out = a.dXp; h.out_dtype = QLMB_BF16; h.ldo = D;
+    h.out = a.dXp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_dx";
     if ((rc = gemm_launch(h, st))) return rc;
 
     // weight gradients, contraction over each expert's rows (cudalm.cu:4335, 4363-4364)
-    struct { const bf16 *A; int Ma; const bf16 *B; int Nb; float *out; } wg[3] = {
-        {a.Xp, D, a.dgp, F, dW1}, {a.Xp, D, a.dup, F, dW3}, {a.ap, F, a.dyp, D, dW2}};
+    struct { const bf16 *A; int Ma; const bf16 *B; int Nb; float *out; const char *name; } wg[3] = {
+        {a.Xp, D, a.dgp, F, dW1, "gemm_wgrad_w1"}, {a.Xp, D, a.dup, F, dW3, "gemm_wgrad_w3"}, {a.ap, F, a.dyp, D, dW2, "gemm_wgrad_w2"}};
     for (int i = 0; i < 3; i++) {
         GemmLaunch w = {};
         w.bmode = AB_TMA_MN; w.epi = EPI_ACCUM; w.sched = SCHED_GROUPK; w.bn = (wg[i].Nb % 256 == 0) ? 256 : 128;
         w.a[0] = wg[i].A; w.a_rows = R; w.a_cols = wg[i].Ma;
         w.w[0] = wg[i].B; w.w_cols = wg[i].Nb;
         w.nseg = 1; w.M = wg[i].Ma; w.N = wg[i].Nb; w.E = E; w.off = a.off;
-        w.out = wg[i].out; w.out_dtype = QLMB_F32; w.ldo = wg[i].Nb; w.beta = beta;
+        w.out = wg[i].out; w.out_dtype = QLMB_F32; w.ldo = wg[i].Nb; w.beta = beta; w.name = wg[i].name;
         if ((rc = gemm_launch(w, st))) return rc;
     }
 
     // router backward (cudalm.cu:4372-4391)
-    if ((rc = router_bwd(a.drt, a.rprobs, a.assign, a.d_gate, a.counts, N, E, K, L->aux, st))) return rc;
-    if ((rc = unpermute_rows(dfnorm, L->dtype, a.dXp, a.inv, a.drt, L->wr, N, D, E, K, st))) return rc;
+    { ProfScope ps("router_bwd", st); if ((rc = router_bwd(a.drt, a.rprobs, a.assign, a.d_gate, a.counts, N, E, K, L->aux, st))) return rc; }
+    { ProfScope ps("unpermute_rows", st); if ((rc = unpermute_rows(dfnorm, L->dtype, a.dXp, a.inv, a.drt, L->wr, N, D, E, K, st))) return rc; }
+    ProfScope ps("router_wgrad", st);
     return router_wgrad(dWr, f_norm, L->dtype, a.drt, a.wr_scratch, N, D, E, beta, st);
 }

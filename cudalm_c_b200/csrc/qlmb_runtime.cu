@@ -49,7 +49,54 @@ int sm_count(void)
     return g_sms[dev];
 }
 
+
+// ---- optional per-kernel timing (CUDA events on the launching stream) ----
+static bool g_prof_on = false;
+static int g_prof_n = 0;
+static const int PROF_MAX = 512;
+static const char *g_prof_name[PROF_MAX];
+static cudaEvent_t g_prof_ev[PROF_MAX][2];
+static bool g_prof_have[PROF_MAX];
+
+ProfScope::ProfScope(const char *name, cudaStream_t st) : slot(-1), stream(st)
+{
+    if (!g_prof_on || g_prof_n >= PROF_MAX) return;
+    slot = g_prof_n++;
+    if (!g_prof_have[slot]) {
+        if (cudaEventCreate(&g_prof_ev[slot][0]) != cudaSuccess || cudaEventCreate(&g_prof_ev[slot][1]) != cudaSuccess) { slot = -1; g_prof_n--; return; }
+        g_prof_have[slot] = true;
+    }
+    g_prof_name[slot] = name;
+    cudaEventRecord(g_prof_ev[slot][0], st);
+}
+ProfScope::~ProfScope()
+{
+    if (slot >= 0) cudaEventRecord(g_prof_ev[slot][1], stream);
+}
+
 }  // namespace qlmb
+
+extern "C" int qlmb_prof_enable(int on)
+{
+    qlmb::g_prof_on = on != 0;
+    qlmb::g_prof_n = 0;
+    return QLMB_OK;
+}
+// Synchronises the device and returns the recorded scopes since the last call:
+// names (64 bytes each) and milliseconds; the return value is the count.
+extern "C" int qlmb_prof_read(char *names, float *ms, int max)
+{
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    int n = qlmb::g_prof_n < max ? qlmb::g_prof_n : max;
+    for (int i = 0; i < n; i++) {
+        float t = 0.0f;
+        cudaEventElapsedTime(&t, qlmb::g_prof_ev[i][0], qlmb::g_prof_ev[i][1]);
+        ms[i] = t;
+        snprintf(names + 64 * i, 64, "%s", qlmb::g_prof_name[i]);
+    }
+    qlmb::g_prof_n = 0;
+    return n;
+}
 
 extern "C" const char *qlmb_last_error(void) { return qlmb::g_err; }
 extern "C" int qlmb_version(void) { return 1; }

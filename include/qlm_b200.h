@@ -65,6 +65,14 @@ int qlmb_version(void);
  * wait expires (QLMB_E_DEVICE); synchronises `stream`. */
 int qlmb_check_device(void *stream);
 
+/* Per-operator timing, the counterpart of the reference's CUDALM_PROF=3 event
+ * timers (cudalm.cu:806-825): while enabled, every kernel launch of the MoE
+ * and linear entry points is bracketed by CUDA events on its stream.
+ * qlmb_prof_read synchronises the device, fills up to `max` names (64 bytes
+ * each) and milliseconds, clears the record and returns the count. */
+int qlmb_prof_enable(int on);
+int qlmb_prof_read(char *names, float *ms, int max);
+
 /* ------------------------------------------------------------------ QLM state */
 
 /* k_qlm_encode (qlm.cuh:136-167): P -> digits d, residuals r, scales s for
@@ -132,8 +140,7 @@ int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, const float *s
 
 /* g_ab(f_norm, Wr) + k_router_topk (cudalm.cu:4158, 2515-2534).  If rt_in is
  * not NULL the logits are read from it (then X, Wr may be NULL); otherwise
- * they are computed as X[N,D] * Wr[D,E] in fp32 and, if rt_out is not NULL,
- * stored there.  exp() is the reference CPU build's polynomial
+ * they are computed as X[N,D] * Wr[D,E] in fp32 into rt_out (required then).  exp() is the reference CPU build's polynomial
  * (cpu_kern.h:28-34) so probabilities match the oracle bit for bit. */
 int qlmb_router_topk(const float *rt_in, float *rt_out, const void *X, int x_dtype, const float *Wr,
                      const float *bias, int bias_stride, float *rprobs, int *assign, float *gate,

@@ -1,0 +1,140 @@
+"""Dequant-fused linears (tcgen05) through the C ABI.
+Tolerance (stated by the task): <= 1e-2 relative for bf16 tensor-core operands
+against fp32 results, measured both as ||a-b||_F/||b||_F and max|a-b|/max|b|."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+f32 = np.float32
+
+
+def dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return max(float((a - b).norm() / b.norm()), float((a - b).abs().max() / b.abs().max()))
+
+
+def test_engine_plain_bf16(cuda):
+    """TMA + tcgen05 + TMEM pipeline without the dequant warps vs fp32 matmul."""
+    import cudalm_c_b200 as q
+    from cudalm_c_b200._lib import ptr, stream_ptr
+    L = q.lib()
+    L.qlmb_selftest_gemm_bf16.argtypes = [C.c_void_p] * 3 + [C.c_int] * 3 + [C.c_void_p]
+    torch.manual_seed(1)
+    for M, K, N in ((128, 64, 256), (1000, 512, 512), (4096, 1024, 1024)):
+        A = torch.randn(M, K, device=cuda).bfloat16(); B = torch.randn(N, K, device=cuda).bfloat16()
+        Cc = torch.zeros(M, N, device=cuda)
+        q.check(L.qlmb_selftest_gemm_bf16(ptr(Cc), ptr(A), ptr(B), M, K, N, stream_ptr()))
+        assert rel(Cc, A.float() @ B.float().T) < 1e-5
+    q.check(L.qlmb_check_device(None))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_matches_reference_vectors(cuda, dtype):
+    """g_ab / g_abt / g_atb of the reference on its rendered weights (fixture)."""
+    from cudalm_c_b200 import linear
+    from cudalm_c_b200._lib import KN, NK
+    g = golden("linear")
+    X, dY = dev(g["X"], cuda).to(dtype), dev(g["dY"], cuda).to(dtype)
+    d, s = dev(g["d"], cuda), dev(g["s"], cuda)
+    M, K = X.shape
+    N = dY.shape[1]
+    for lay, tag in ((KN, "kn"), (NK, "nk")):
+        assert rel(linear.linear_fwd(X, d, s, lay, N), dev(g["Y_" + tag], cuda)) < TOL
+        assert rel(linear.linear_dgrad(dY, d, s, lay, K), dev(g["dX_" + tag], cuda)) < TOL
+        shape = (K, N) if lay == KN else (N, K)
+        dW = torch.zeros(shape, device=cuda)
+        linear.linear_wgrad(dW, dY, X, lay, beta=1.0)
+        assert rel(dW, dev(g["dW_" + tag], cuda)) < TOL
+
+
+def quantise(cuda, rows, cols, seed):
+    from cudalm_c_b200 import qlm
+    n = rows * cols
+    Q = qlm.Qlm([(0, n)], n, cuda)
+    gen = torch.Generator(device=cuda); gen.manual_seed(seed)
+    P = torch.randn(n, device=cuda, generator=gen) * 0.02
+    Q.init_from(P)                       # P now holds the rendered view s*d
+    return Q, P.view(rows, cols)
+
+
+@pytest.mark.parametrize("layout_name", ["KN", "NK"])
+def test_config1_shape(cuda, oracle, layout_name):
+    """BASELINE config 1: X[8192,512], W[2048,512] (NK) resp. [512,2048] (KN),
+    fwd + dgrad + wgrad with fp32 I/O; full result vs fp32 matmul on the rendered
+    view, 32 rows vs the oracle, plus linearity and run-to-run determinism."""
+    from cudalm_c_b200 import linear
+    from cudalm_c_b200._lib import KN, NK
+    lay = KN if layout_name == "KN" else NK
+    M, K, N = 8192, 512, 2048
+    Q, W = quantise(cuda, K, N, 3) if lay == KN else quantise(cuda, N, K, 3)
+    Wm = W if lay == KN else W.T
+    gen = torch.Generator(device=cuda); gen.manual_seed(4)
+    X = torch.randn(M, K, device=cuda, generator=gen); dY = torch.randn(M, N, device=cuda, generator=gen)
+    Y = linear.linear_fwd(X, Q.d, Q.s, lay, N)
+    assert rel(Y, X @ Wm) < TOL
+    dX = linear.linear_dgrad(dY, Q.d, Q.s, lay, K)
+    assert rel(dX, dY @ Wm.T) < TOL
+    dW = torch.zeros_like(W)
+    linear.linear_wgrad(dW, dY, X, lay, beta=0.0)
+    assert rel(dW, X.T @ dY if lay == KN else dY.T @ X) < TOL
+    # oracle on a slice of rows
+    dn, sn = Q.d.cpu().numpy(), Q.s.cpu().numpy()
+    Yo = oracle.linear_fwd(X[:32].cpu().numpy(), dn, sn, lay, N)
+    assert rel(Y[:32], dev(Yo, cuda)) < TOL
+    dXo = oracle.linear_dgrad(dY[:32].cpu().numpy(), dn, sn, lay, K)
+    assert rel(dX[:32], dev(dXo, cuda)) < TOL
+    # size-independent properties: determinism, and linearity in the bf16-exact factor 2
+    assert torch.equal(Y, linear.linear_fwd(X, Q.d, Q.s, lay, N))
+    assert torch.equal(linear.linear_fwd(2 * X, Q.d, Q.s, lay, N), 2 * Y)
+    # residual epilogue and accumulate modes
+    R = torch.randn(M, N, device=cuda, generator=gen)
+    assert rel(linear.linear_fwd(X, Q.d, Q.s, lay, N, R=R) - R, Y) < 1e-5
+    acc = dX.clone()
+    linear.linear_dgrad(dY, Q.d, Q.s, lay, K, beta=1.0, out=acc)
+    assert rel(acc, 2 * dX) < 1e-6
+    dW2 = dW.clone()
+    linear.linear_wgrad(dW2, dY, X, lay, beta=1.0)
+    assert rel(dW2, 2 * dW) < 1e-6
+
+
+@pytest.mark.parametrize("M", [1, 127, 129, 300])
+def test_ragged_row_counts(cuda, M):
+    from cudalm_c_b200 import linear
+    from cudalm_c_b200._lib import KN, NK
+    K, N = 256, 384
+    for lay in (KN, NK):
+        Q, W = quantise(cuda, K, N, 7) if lay == KN else quantise(cuda, N, K, 7)
+        Wm = W if lay == KN else W.T
+        X = torch.randn(M, K, device=cuda).bfloat16(); dY = torch.randn(M, N, device=cuda).bfloat16()
+        guard = torch.full((M + 1, N), 7.0, device=cuda, dtype=torch.bfloat16)
+        linear.linear_fwd(X, Q.d, Q.s, lay, N, out=guard[:M])
+        assert rel(guard[:M], X.float() @ Wm) < TOL
+        assert (guard[M] == 7.0).all()            # rows past M are never written
+        assert rel(linear.linear_dgrad(dY, Q.d, Q.s, lay, K), dY.float() @ Wm.T) < TOL
+        dW = torch.zeros_like(W)
+        linear.linear_wgrad(dW, dY, X, lay, beta=0.0)
+        assert rel(dW, X.float().T @ dY.float() if lay == KN else dY.float().T @ X.float()) < TOL
+
+
+def test_empty_and_unsupported(cuda):
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import linear
+    from cudalm_c_b200._lib import KN
+    Q, W = quantise(cuda, 128, 128, 9)
+    assert linear.linear_fwd(torch.zeros(0, 128, device=cuda), Q.d, Q.s, KN, 128).shape == (0, 128)
+    dW = torch.ones(128, 128, device=cuda)
+    linear.linear_wgrad(dW, torch.zeros(0, 128, device=cuda), torch.zeros(0, 128, device=cuda), KN, beta=0.0)
+    assert (dW == 0).all()
+    with pytest.raises(q.QlmbError):               # K not a multiple of the scale group
+        linear.linear_fwd(torch.zeros(4, 96, device=cuda), Q.d, Q.s, KN, 128)
+    q.check(q.lib().qlmb_check_device(None))

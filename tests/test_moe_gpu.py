@@ -1,0 +1,167 @@
+"""MoE expert FFN layer (router -> permute -> grouped dequant-GEMMs -> combine,
+and its backward) through the C ABI.  Integer outputs (assign, perm, offsets)
+are compared exactly, floating-point ones within 1e-2 (forward) and 2e-2
+(gradients, which additionally carry the bf16 rounding of the stashed
+pre-activations) relative to the fp32 reference."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden
+from oracle import loader
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+TOL_F, TOL_B = 1e-2, 2e-2
+
+
+def dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return max(float((a - b).norm() / b.norm()), float((a - b).abs().max() / b.abs().max()))
+
+
+def layer_from_fixture(cuda, g, dtype):
+    from cudalm_c_b200 import moe
+    N, D, F, E, K = [int(x) for x in g["shape"]]
+    q = [(dev(g["d%d" % i], cuda), dev(g["s%d" % i], cuda)) for i in (1, 3, 2)]
+    return moe.MoeLayerState(N, D, F, E, K, q[0], q[1], q[2], dev(g["Wr"], cuda), dtype=dtype, aux=float(g["aux"])), (N, D, F, E, K)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_layer_matches_reference_vectors(cuda, dtype):
+    """moe_forward + moe_backward of the reference (fixture, top-2, aux 0.03)."""
+    g = golden("moe")
+    L, (N, D, F, E, K) = layer_from_fixture(cuda, g, dtype)
+    fn, fi, dout = [dev(g[k], cuda).to(dtype) for k in ("fn", "fi", "dout")]
+    out = L.forward(fi, fn)
+    asg = L.member("assign", (K, N), torch.int32).cpu().numpy()
+    assert (asg == g["assign"]).all()
+    assert rel(L.member("rt", (N, E), torch.float32), dev(g["rt"], cuda)) < 1e-5
+    assert rel(L.member("gate", (K, N), torch.float32), dev(g["gate"], cuda)) < 1e-5
+    assert rel(out, dev(g["out"], cuda)) < TOL_F
+    # per-expert counts and (after removing the padding) the reference's grouping
+    counts = L.member("counts", (E,), torch.int32).cpu().numpy()
+    off = L.member("off", (E + 1,), torch.int32).cpu().numpy()
+    perm = L.member("perm", (L.rows_cap,), torch.int32).cpu().numpy()
+    assert (counts == np.diff(g["hoff"], axis=1).sum(0)).all()
+    o = loader.restatement()
+    p2, _, o2, _ = o.perm_build(g["assign"], E, merged=1)
+    for e in range(E):
+        assert (perm[off[e]:off[e] + counts[e]] == p2[o2[e]:o2[e + 1]]).all()
+        assert (perm[off[e] + counts[e]:off[e + 1]] == -1).all()
+    dW1 = torch.zeros(E, D, F, device=cuda); dW3 = torch.zeros(E, D, F, device=cuda)
+    dW2 = torch.zeros(E, F, D, device=cuda); dWr = torch.zeros(D, E, device=cuda)
+    dfn = L.backward(dout, fn, dW1, dW3, dW2, dWr, beta=1.0)
+    assert rel(L.member("d_gate", (K, N), torch.float32), dev(g["d_gate"], cuda)) < TOL_B
+    assert rel(dfn, dev(g["dfnorm"], cuda)) < TOL_B
+    assert rel(dWr, dev(g["dWr"], cuda).view(D, E)) < TOL_B
+    for name, t in (("dW1", dW1), ("dW3", dW3), ("dW2", dW2)):
+        assert rel(t.view(-1), dev(g[name].astype(f32), cuda)) < TOL_B, name
+    # beta = 1 accumulates (the reference's g_atb), beta = 0 overwrites
+    keep = dW1.clone()
+    L.backward(dout, fn, dW1, dW3, dW2, dWr, beta=1.0)
+    assert rel(dW1, 2 * keep) < 1e-6
+    L.backward(dout, fn, dW1, dW3, dW2, dWr, beta=0.0)
+    assert rel(dW1, keep) < 1e-6
+    import cudalm_c_b200 as q
+    q.check(q.lib().qlmb_check_device(None))
+
+
+def build_layer(cuda, N, D, F, E, K, seed, dtype=torch.bfloat16):
+    from cudalm_c_b200 import moe, qlm
+    gen = torch.Generator(device=cuda); gen.manual_seed(seed)
+    qs, views = [], []
+    for rows, cols in ((E * D, F), (E * D, F), (E * F, D)):
+        n = rows * cols
+        Q = qlm.Qlm([(0, n)], n, cuda)
+        P = torch.randn(n, device=cuda, generator=gen) * 0.02
+        Q.init_from(P)
+        qs.append((Q.d, Q.s)); views.append(P)
+    wr = torch.randn(D, E, device=cuda, generator=gen) * 0.02
+    L = moe.MoeLayerState(N, D, F, E, K, qs[0], qs[1], qs[2], wr, dtype=dtype)
+    acts = [torch.randn(N, D, device=cuda, generator=gen).to(dtype) for _ in range(3)]
+    return L, qs, wr, acts
+
+
+def test_midsize_vs_oracle(cuda, oracle):
+    """Config-2 weights (32 experts, 768 x 1536) on 384 tokens against the CPU oracle."""
+    N, D, F, E, K = 384, 768, 1536, 32, 2
+    L, qs, wr, (fn, fi, dout) = build_layer(cuda, N, D, F, E, K, 11)
+    out = L.forward(fi, fn)
+    h = lambda t: t.float().cpu().numpy()
+    qh = [(a.cpu().numpy(), b.cpu().numpy()) for a, b in qs]
+    fw = oracle.moe_fwd(h(fi), h(fn), h(wr), qh[0], qh[1], qh[2], F, K)
+    asg = L.member("assign", (K, N), torch.int32).cpu().numpy()
+    assert (asg != fw["assign"]).mean() < 0.01       # only a near-tie of logits may differ
+    if (asg == fw["assign"]).all():
+        assert rel(out, dev(fw["out"], cuda)) < TOL_F
+        dW1 = torch.zeros(E, D, F, device=cuda); dW3 = torch.zeros(E, D, F, device=cuda)
+        dW2 = torch.zeros(E, F, D, device=cuda); dWr = torch.zeros(D, E, device=cuda)
+        dfn = L.backward(dout, fn, dW1, dW3, dW2, dWr, beta=0.0)
+        bw = oracle.moe_bwd(h(dout), h(fn), h(wr), qh[0], qh[1], qh[2], F, K, fw, aux=0.03)
+        assert rel(dfn, dev(bw["dfnorm"], cuda)) < TOL_B
+        assert rel(dWr, dev(bw["dWr"], cuda)) < TOL_B
+        assert rel(dW1, dev(bw["dW1"], cuda)) < TOL_B and rel(dW3, dev(bw["dW3"], cuda)) < TOL_B
+        assert rel(dW2, dev(bw["dW2"], cuda)) < TOL_B
+
+
+def test_config2_full_size_properties(cuda):
+    """BASELINE config 2 (8192 tokens, 32 experts, top-2, 768/1536): checks that do
+    not need an fp32 recomputation of 348 GFLOP -- conservation of rows through the
+    permutation, exact zeros in filler rows, run-to-run determinism, linearity of
+    the backward in dout, and an fp32 torch recomputation of four experts."""
+    N, D, F, E, K = 8192, 768, 1536, 32, 2
+    L, qs, wr, (fn, fi, dout) = build_layer(cuda, N, D, F, E, K, 21)
+    out = L.forward(fi, fn)
+    R = L.rows_cap
+    counts = L.member("counts", (E,), torch.int32)
+    off = L.member("off", (E + 1,), torch.int32)
+    perm = L.member("perm", (R,), torch.int32)
+    inv = L.member("inv", (K * N,), torch.int32).long()
+    assert int(counts.sum()) == K * N
+    assert torch.equal(perm[inv], torch.arange(K * N, device=cuda, dtype=torch.int32))
+    rows = int(off[E])
+    filler = perm[:rows] < 0
+    for name, width in (("Xp", D), ("ap", F), ("yp", D)):
+        assert (L.member(name, (R, width), torch.bfloat16)[:rows][filler] == 0).all(), name
+    out2 = L.forward(fi, fn)
+    assert torch.equal(out, out2)
+    # four experts recomputed in fp32 from the rendered weights
+    from cudalm_c_b200 import qlm
+    asg = L.member("assign", (K, N), torch.int32).long(); gate = L.member("gate", (K, N), torch.float32)
+    yp = L.member("yp", (R, D), torch.bfloat16)
+    for e in (0, 7, 19, 31):
+        def view(q, rows_, cols_, which):
+            n = rows_ * cols_
+            sp = loader.make_spans([n])[0]
+            P = torch.empty(n, device=cuda)
+            qlm.qlm_render(P, q[0][e * n // 2:(e + 1) * n // 2], q[1][e * n // 128:(e + 1) * n // 128],
+                           qlm.spans_to_device(sp, cuda), 1)
+            return P.view(rows_, cols_)
+        W1, W3, W2 = view(qs[0], D, F, 1), view(qs[1], D, F, 3), view(qs[2], F, D, 2)
+        slots = perm[int(off[e]):int(off[e]) + int(counts[e])].long()
+        x = fn.float()[slots % N]
+        y = (torch.nn.functional.silu(x @ W1) * (x @ W3)) @ W2
+        assert rel(yp[int(off[e]):int(off[e]) + int(counts[e])], y) < TOL_F
+    dW = [torch.zeros(E, D, F, device=cuda), torch.zeros(E, D, F, device=cuda), torch.zeros(E, F, D, device=cuda)]
+    dWr = torch.zeros(D, E, device=cuda)
+    dfn = L.backward(dout, fn, dW[0], dW[1], dW[2], dWr, beta=0.0)
+    keep = [t.clone() for t in dW] + [dWr.clone(), dfn.clone()]
+    dfn_b = L.backward(dout, fn, dW[0], dW[1], dW[2], dWr, beta=0.0)
+    for a, b in zip(keep, dW + [dWr, dfn_b]):
+        assert torch.equal(a, b)                     # deterministic
+    assert all(torch.isfinite(t).all() for t in keep)
+    import cudalm_c_b200 as q
+    q.check(q.lib().qlmb_check_device(None))
+
+
+def test_unsupported_shapes_are_rejected(cuda):
+    import cudalm_c_b200 as q
+    with pytest.raises(q.QlmbError):
+        L, *_ = build_layer(cuda, 64, 128, 256, 4, 2, 1)
+        L.c.D = 96
+        L.forward(torch.zeros(64, 96, device=cuda), torch.zeros(64, 96, device=cuda))
