@@ -529,3 +529,52 @@ extern "C" int qlmb_adamw(float *P, const float *G, uint16_t *M, uint16_t *V, si
     QLMB_LAUNCH_CHECK("k_adamw");
     return QLMB_OK;
 }
+
+// ------------------------------------------------- grad-norm clip without allocation
+// Some hosts cannot let a library allocate device memory: a training job that
+// has handed every spare byte to its own pool, or a serving loop that must not
+// meet the device-wide synchronisation cudaMalloc/cudaFree imply in the middle
+// of a step.  For them the partial sums of the norm live in this fixed array,
+// which exists once per GPU from the moment the library is loaded until the
+// process ends: 64 chunks x 16 sub-blocks x (1 gradient + up to 7 side buffers)
+// doubles = 64 KiB.
+#define QLMB_NOALLOC_MAX_SIDES 7
+static __device__ __align__(256) double g_gnorm_static_partials[64 * GN_SUB * (1 + QLMB_NOALLOC_MAX_SIDES)];
+// The array's name is only a handle on the host; the kernels need its device
+// address, looked up once per device (with that device current) and kept here.
+static double *g_gnorm_static_addr[64];
+
+// Same result as qlmb_gnorm, with no cudaMalloc/cudaFree and no other allocating
+// call on any path.  The first call on each device resolves the address of the
+// static array; make that call before starting any stream capture.  All calls on
+// a device share the one array: two calls whose kernels may overlap on the GPU
+// (different streams, no ordering between them) race on it.  Nothing in it has to
+// be cleared beforehand: every slot the final kernel reads is written earlier in
+// the same call, so what an earlier call left behind is never seen.
+extern "C" int qlmb_gnorm_noalloc(const float *G, size_t n, const float *const *side, const size_t *side_n,
+                                  int nside, int clip_side, float *gs, void *stream)
+{
+    QLMB_REQUIRE(G && gs && nside >= 0, "qlmb_gnorm_noalloc: bad argument");
+    QLMB_REQUIRE(nside == 0 || (side && side_n), "qlmb_gnorm_noalloc: side arrays missing");
+    if (nside > QLMB_NOALLOC_MAX_SIDES) {
+        set_error("qlmb_gnorm_noalloc: %d side buffers exceed the fixed scratch (at most %d; use qlmb_gnorm for more)",
+                  nside, QLMB_NOALLOC_MAX_SIDES);
+        return QLMB_E_ARG;
+    }
+    int dev = 0;
+    QLMB_CUDA(cudaGetDevice(&dev));
+    QLMB_REQUIRE(dev >= 0 && dev < 64, "qlmb_gnorm_noalloc: device index %d", dev);
+    if (!g_gnorm_static_addr[dev]) {
+        double *p = nullptr;
+        QLMB_CUDA(cudaGetSymbolAddress((void **)&p, g_gnorm_static_partials));
+        g_gnorm_static_addr[dev] = p;
+    }
+    double *sub = g_gnorm_static_addr[dev];
+    cudaStream_t st = as_stream(stream);
+    k_sq_partial<<<dim3(GN_SUB, 64), 256, 0, st>>>(G, n, sub);
+    for (int i = 0; i < nside; i++)
+        k_sq_partial<<<dim3(GN_SUB, 64), 256, 0, st>>>(side[i], side_n[i], sub + (size_t)64 * GN_SUB * (1 + i));
+    k_gnorm_final<<<1, 1, 0, st>>>(sub, nside, clip_side, gs);
+    QLMB_LAUNCH_CHECK("qlmb_gnorm_noalloc");
+    return QLMB_OK;
+}

@@ -107,6 +107,17 @@ int qlmb_servo(int8_t *d, int8_t *r, float *s, const qlmb_span *sp, int nspan, i
 int qlmb_gnorm(const float *G, size_t n, const float *const *side, const size_t *side_n, int nside,
                int clip_side, float *gs, void *stream);
 
+/* No counterpart in the reference.  qlmb_gnorm for hosts that cannot let a
+ * library allocate device memory (all of it already belongs to their own pool,
+ * or a cudaMalloc's device-wide synchronisation is not acceptable inside a
+ * step): identical arguments and result, but the partial sums sit in a fixed
+ * 64 KiB array inside the library, so no allocation happens on any path.
+ * Limit: nside <= 7, more is rejected with QLMB_E_ARG.  The first call on a
+ * device looks up the array's address -- make it before any stream capture.
+ * Calls on one device share the array; calls that can overlap on the GPU race. */
+int qlmb_gnorm_noalloc(const float *G, size_t n, const float *const *side, const size_t *side_n,
+                       int nside, int clip_side, float *gs, void *stream);
+
 /* k_adamw (cudalm.cu:2855-2870) for the unquantised spans: bf16 moments,
  * gs (device, may be NULL) = clip multiplier applied on load. */
 int qlmb_adamw(float *P, const float *G, uint16_t *M, uint16_t *V, size_t n, float lr, float b1,
