@@ -28,7 +28,6 @@ UNITS = {
     "qlmb_linear.cu": [],
     "qlmb_gemv.cu": [],
     "qlmb_moe.cu": [],
-    "qlmb_stubs.cu": [],
 }
 COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
           "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

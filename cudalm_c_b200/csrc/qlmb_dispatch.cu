@@ -49,9 +49,48 @@ __device__ __forceinline__ void st_act8(void *p, int dtype, size_t i, const floa
 }
 
 // ------------------------------------------------------------ router logits
-// rt[n,e] = sum_j X[n,j] * Wr[j,e]  (reference cudalm.cu:4158, g_ab with N = E).
-// A block owns 32 tokens; each warp 4 of them; lane = expert.  The token tile
-// is staged in shared memory 256 features at a time.
+// rt[n,e] = sum_j X[n,j] * Wr[j,e]  (reference cudalm.cu:4158, g_ab with N = E), fp32.
+// A warp owns 8 tokens, lane = expert; Wr rows (128 B) and the token rows (broadcast
+// vector loads) come through L1, which holds all of Wr.
+template <int XBF16>
+__global__ void __launch_bounds__(512) k_router_logits_warp(float *rt, const void *X, const float *Wr, int N, int D, int E)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * 16 + warp) * 8;
+    if (n0 >= N) return;
+    const int e = lane < E ? lane : E - 1;
+    float acc[8];
+#pragma unroll
+    for (int t = 0; t < 8; t++) acc[t] = 0.0f;
+#pragma unroll 2
+    for (int j = 0; j < D; j += 4) {
+        float w[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) w[jj] = __ldg(Wr + (size_t)(j + jj) * E + e);
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            const int n = n0 + t < N ? n0 + t : N - 1;
+            float x0, x1, x2, x3;
+            if (XBF16) {
+                uint2 q = __ldg(reinterpret_cast<const uint2 *>((const bf16 *)X + (size_t)n * D + j));
+                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
+                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
+                x0 = a.x; x1 = a.y; x2 = b.x; x3 = b.y;
+            } else {
+                float4 q = __ldg(reinterpret_cast<const float4 *>((const float *)X + (size_t)n * D + j));
+                x0 = q.x; x1 = q.y; x2 = q.z; x3 = q.w;
+            }
+            acc[t] += x0 * w[0]; acc[t] += x1 * w[1]; acc[t] += x2 * w[2]; acc[t] += x3 * w[3];
+        }
+    }
+    if (lane < E) {
+#pragma unroll
+        for (int t = 0; t < 8; t++) if (n0 + t < N) rt[(size_t)(n0 + t) * E + lane] = acc[t];
+    }
+}
+
+// General shape (E > 32 or Wr too large for shared memory): a block owns 32 tokens,
+// the token tile is staged 256 features at a time.
 #define RL_TOK 32
 #define RL_DCH 256
 __global__ void __launch_bounds__(256) k_router_logits(float *rt, const void *X, int x_dtype,
@@ -91,7 +130,13 @@ __global__ void __launch_bounds__(256) k_router_logits(float *rt, const void *X,
 
 int router_logits(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E, cudaStream_t st)
 {
-    k_router_logits<<<(N + RL_TOK - 1) / RL_TOK, 256, 0, st>>>(rt, X, x_dtype, Wr, N, D, E);
+    if (E <= 32 && (D % 4) == 0) {
+        int blocks = (N + 127) / 128;               // 16 warps x 8 tokens per block
+        if (x_dtype == QLMB_BF16) k_router_logits_warp<1><<<blocks, 512, 0, st>>>(rt, X, Wr, N, D, E);
+        else k_router_logits_warp<0><<<blocks, 512, 0, st>>>(rt, X, Wr, N, D, E);
+    } else {
+        k_router_logits<<<(N + RL_TOK - 1) / RL_TOK, 256, 0, st>>>(rt, X, x_dtype, Wr, N, D, E);
+    }
     QLMB_LAUNCH_CHECK("k_router_logits");
     return QLMB_OK;
 }
@@ -215,6 +260,24 @@ int dgate_rows(bf16 *dyp, float *d_gate, const void *dout, int dtype, const bf16
 // drt[n,:] = softmax Jacobian of (aux weights + gate gradients)
 // (reference k_router_bwd_topk, cudalm.cu:2621-2629, with the aux weights
 // w[e] = aux*E*(cnt[e]/(K*N))/N of cudalm.cu:4382 built on the device).
+// One warp per token, lane = expert (E <= 32); the thread-per-token form below
+// covers larger E.
+__global__ void __launch_bounds__(256) k_router_bwd_warp(float *drt, const float *rprobs, const int *assign,
+                                                         const float *d_gate, const int *counts, int N, int E,
+                                                         int K, float aux)
+{
+    int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float invN = 1.0f / N, invKN = 1.0f / ((float)K * N);
+    float pr = lane < E ? rprobs[(size_t)n * E + lane] : 0.0f;
+    float d = lane < E ? aux * E * ((float)counts[lane] * invKN) * invN : 0.0f;
+    for (int k = 0; k < K; k++)
+        if (assign[(size_t)k * N + n] == lane) d += d_gate[(size_t)k * N + n];
+    float dot = pr * d;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane < E) drt[(size_t)n * E + lane] = pr * (d - dot);
+}
 __global__ void __launch_bounds__(128) k_router_bwd(float *drt, const float *rprobs, const int *assign,
                                                     const float *d_gate, const int *counts, int N, int E,
                                                     int K, float aux)
@@ -233,15 +296,53 @@ __global__ void __launch_bounds__(128) k_router_bwd(float *drt, const float *rpr
 int router_bwd(float *drt, const float *rprobs, const int *assign, const float *d_gate, const int *counts,
                int N, int E, int K, float aux, cudaStream_t st)
 {
-    k_router_bwd<<<(N + 127) / 128, 128, 0, st>>>(drt, rprobs, assign, d_gate, counts, N, E, K, aux);
+    if (E <= 32) k_router_bwd_warp<<<(N + 7) / 8, 256, 0, st>>>(drt, rprobs, assign, d_gate, counts, N, E, K, aux);
+    else k_router_bwd<<<(N + 127) / 128, 128, 0, st>>>(drt, rprobs, assign, d_gate, counts, N, E, K, aux);
     QLMB_LAUNCH_CHECK("k_router_bwd");
     return QLMB_OK;
 }
 
 // --------------------------------------------------------------- unpermute
 // dfnorm[n,j] = sum_k dXp[inv[k,n], j] + sum_e drt[n,e] * Wr[j,e]
-// (reference k_scatter_add + g_abt_b(drt, Wr), cudalm.cu:4368-4390).  A block
-// owns 8 tokens; a thread owns feature columns j = tid, tid+256, ...
+// (reference k_scatter_add + g_abt_b(drt, Wr), cudalm.cu:4368-4390).
+// WrT is Wr transposed ([E][D], written by k_transpose_wr into scratch), so a
+// lane's 8 consecutive features are two 16-byte loads that hit L1; a warp owns a
+// token, a lane 8 consecutive features per pass.
+__global__ void __launch_bounds__(256) k_transpose_wr(float *WrT, const float *Wr, int D, int E)
+{
+    int i = blockIdx.x * 256 + threadIdx.x;
+    if (i < D * E) { int j = i / E, e = i % E; WrT[(size_t)e * D + j] = Wr[i]; }
+}
+__global__ void __launch_bounds__(256) k_unpermute_rows_warp(void *dfnorm, int dtype, const bf16 *dXp, const int *inv,
+                                                             const float *drt, const float *WrT, int N, int D, int E, int K)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    float dr = lane < E ? drt[(size_t)n * E + lane] : 0.0f;
+    int slot = lane < K ? inv[(size_t)lane * N + n] : 0;
+    for (int j = lane * 8; j < D; j += 256) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int k = 0; k < K; k++) {
+            int row = __shfl_sync(0xffffffffu, slot, k);
+            float y[8];
+            ld_act8(dXp, QLMB_BF16, (size_t)row * D + j, y);
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[i] += y[i];
+        }
+#pragma unroll 4
+        for (int e = 0; e < E; e++) {
+            float dv = __shfl_sync(0xffffffffu, dr, e);
+            float4 w0 = __ldg(reinterpret_cast<const float4 *>(WrT + (size_t)e * D + j));
+            float4 w1 = __ldg(reinterpret_cast<const float4 *>(WrT + (size_t)e * D + j + 4));
+            acc[0] += dv * w0.x; acc[1] += dv * w0.y; acc[2] += dv * w0.z; acc[3] += dv * w0.w;
+            acc[4] += dv * w1.x; acc[5] += dv * w1.y; acc[6] += dv * w1.z; acc[7] += dv * w1.w;
+        }
+        st_act8(dfnorm, dtype, (size_t)n * D + j, acc);
+    }
+}
+
+// General shape: a block owns 8 tokens; a thread owns feature columns j = tid, tid+256, ...
 #define UP_TOK 8
 __global__ void __launch_bounds__(256) k_unpermute_rows(void *dfnorm, int dtype, const bf16 *dXp,
                                                         const int *inv, const float *drt, const float *Wr,
@@ -282,54 +383,56 @@ __global__ void __launch_bounds__(256) k_unpermute_rows(void *dfnorm, int dtype,
 }
 
 int unpermute_rows(void *dfnorm, int dtype, const bf16 *dXp, const int *inv, const float *drt, const float *Wr,
-                   int N, int D, int E, int K, cudaStream_t st)
+                   float *wrt_scratch, int N, int D, int E, int K, cudaStream_t st)
 {
-    size_t smem = (size_t)UP_TOK * E * sizeof(float) + (size_t)UP_TOK * K * sizeof(int);
-    k_unpermute_rows<<<(N + UP_TOK - 1) / UP_TOK, 256, smem, st>>>(dfnorm, dtype, dXp, inv, drt, Wr, N, D, E, K);
+    if (E <= 32 && (D % 8) == 0 && wrt_scratch) {
+        k_transpose_wr<<<(D * E + 255) / 256, 256, 0, st>>>(wrt_scratch, Wr, D, E);
+        k_unpermute_rows_warp<<<(N + 7) / 8, 256, 0, st>>>(dfnorm, dtype, dXp, inv, drt, wrt_scratch, N, D, E, K);
+    } else {
+        size_t smem = (size_t)UP_TOK * E * sizeof(float) + (size_t)UP_TOK * K * sizeof(int);
+        k_unpermute_rows<<<(N + UP_TOK - 1) / UP_TOK, 256, smem, st>>>(dfnorm, dtype, dXp, inv, drt, Wr, N, D, E, K);
+    }
     QLMB_LAUNCH_CHECK("k_unpermute_rows");
     return QLMB_OK;
 }
 
 // ------------------------------------------------------------ router wgrad
 // dWr[j,e] = beta*dWr[j,e] + sum_n fnorm[n,j]*drt[n,e]  (reference g_atb,
-// cudalm.cu:4391).  Stage 1: per 256-token chunk partial sums; stage 2: fixed
-// order reduction over chunks, so the result is run-to-run identical.
-#define RW_TOK 256
+// cudalm.cu:4391).  Stage 1: block (c, jb) sums token chunk c for the 256
+// features of block jb in registers (warp = 32 features, lane = expert); stage 2
+// adds the chunks in a fixed order, so the result is run-to-run identical.
+#define RW_CHUNKS 192
 __global__ void __launch_bounds__(256) k_router_wgrad_part(float *part, const void *fnorm, int dtype,
-                                                           const float *drt, int N, int D, int E)
+                                                           const float *drt, int N, int D, int E, int e0)
 {
-    __shared__ float xs[32][33];          // [token][j]
-    extern __shared__ float ds[];         // [32 tokens][E]
-    int c = blockIdx.x, j0 = blockIdx.y * 32;
-    int tj = threadIdx.x >> 5, lane = threadIdx.x & 31;   // thread owns j = j0 + tj*4 .. +3 for expert columns lane, lane+32, ...
-    int n_lo = c * RW_TOK, n_hi = n_lo + RW_TOK < N ? n_lo + RW_TOK : N;
-    for (int e0 = 0; e0 < E; e0 += 32) {
-        int e = e0 + lane;
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int nb = n_lo; nb < n_hi; nb += 32) {
-            __syncthreads();
-            for (int i = threadIdx.x; i < 32 * 32; i += 256) {
-                int t = i >> 5, j = i & 31, n = nb + t;
-                xs[t][j] = (n < n_hi && j0 + j < D) ? ld_act(fnorm, dtype, (size_t)n * D + j0 + j) : 0.0f;
-            }
-            for (int i = threadIdx.x; i < 32 * 32; i += 256) {
-                int t = i >> 5, ee = e0 + (i & 31), n = nb + t;
-                ds[t * 32 + (i & 31)] = (n < n_hi && ee < E) ? drt[(size_t)n * E + ee] : 0.0f;
-            }
-            __syncthreads();
-#pragma unroll 8
-            for (int t = 0; t < 32; t++) {
-                float dv = ds[t * 32 + lane];
+    const int c = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j0 = blockIdx.y * 256 + warp * 32;
+    const int per = (N + RW_CHUNKS - 1) / RW_CHUNKS;
+    const int n_lo = c * per, n_hi = n_lo + per < N ? n_lo + per : N;
+    const int e = e0 + lane;
+    float acc[32];
 #pragma unroll
-                for (int q = 0; q < 4; q++) acc[q] += xs[t][tj * 4 + q] * dv;
+    for (int i = 0; i < 32; i++) acc[i] = 0.0f;
+    if (j0 < D) {
+#pragma unroll 2
+        for (int n = n_lo; n < n_hi; n++) {
+            float dv = e < E ? drt[(size_t)n * E + e] : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                float x[8];
+                if (j0 + i + 8 <= D) ld_act8(fnorm, dtype, (size_t)n * D + j0 + i, x);
+                else {
+#pragma unroll
+                    for (int k = 0; k < 8; k++) x[k] = j0 + i + k < D ? ld_act(fnorm, dtype, (size_t)n * D + j0 + i + k) : 0.0f;
+                }
+#pragma unroll
+                for (int k = 0; k < 8; k++) acc[i + k] += x[k] * dv;
             }
         }
         if (e < E) {
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                int j = j0 + tj * 4 + q;
-                if (j < D) part[((size_t)c * D + j) * E + e] = acc[q];
-            }
+            for (int i = 0; i < 32; i++)
+                if (j0 + i < D) part[((size_t)c * D + j0 + i) * E + e] = acc[i];
         }
     }
 }
@@ -345,9 +448,9 @@ __global__ void __launch_bounds__(256) k_router_wgrad_sum(float *dWr, const floa
 int router_wgrad(float *dWr, const void *fnorm, int dtype, const float *drt, float *scratch, int N, int D, int E,
                  float beta, cudaStream_t st)
 {
-    int nchunk = (N + RW_TOK - 1) / RW_TOK;
-    k_router_wgrad_part<<<dim3(nchunk, (D + 31) / 32), 256, 32 * 32 * sizeof(float), st>>>(scratch, fnorm, dtype, drt, N, D, E);
-    k_router_wgrad_sum<<<(D * E + 255) / 256, 256, 0, st>>>(dWr, scratch, nchunk, D * E, beta);
+    for (int e0 = 0; e0 < E; e0 += 32)
+        k_router_wgrad_part<<<dim3(RW_CHUNKS, (D + 255) / 256), 256, 0, st>>>(scratch, fnorm, dtype, drt, N, D, E, e0);
+    k_router_wgrad_sum<<<(D * E + 255) / 256, 256, 0, st>>>(dWr, scratch, RW_CHUNKS, D * E, beta);
     QLMB_LAUNCH_CHECK("router_wgrad");
     return QLMB_OK;
 }

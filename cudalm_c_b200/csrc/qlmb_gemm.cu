@@ -1,12 +1,16 @@
 // tcgen05 GEMM engine for sm_100a: persistent, warp-specialised CTAs.
 //
+// A CTA tile is 256 rows x 128 columns: two M=128 MMAs per 16-deep step share
+// one B slice, so every expanded weight element feeds 512 flops.
+//
 //   warp 0      TMA producer   activations (bf16, 128-byte swizzle) and packed
 //                              4-bit code tiles into shared-memory rings
 //   warp 1      MMA issuer     tcgen05.mma, fp32 accumulators in TMEM (two
-//                              accumulator buffers so the epilogue of tile i
-//                              overlaps the main loop of tile i+1)
-//   warps 2-5   epilogue       tcgen05.ld -> registers -> fused epilogue -> HBM
-//   warps 6-13  dequant        codes (shared) -> registers -> bf16 x scale ->
+//                              accumulator buffers of 2 x 128 columns, so the
+//                              epilogue of tile i overlaps the main loop of i+1)
+//   warps 2-9   epilogue       tcgen05.ld -> registers -> fused epilogue ->
+//                              swizzled staging -> whole-row stores to HBM
+//   warps 10-17 dequant        codes (shared) -> registers -> bf16 x scale ->
 //                              UMMA-canonical swizzled B tile (shared)
 //
 // The weights never exist in HBM as bf16 or fp32: each 64-deep slice of the B
@@ -22,10 +26,15 @@
 
 namespace qlmb {
 
-constexpr int BM = 128;           // rows per tile (UMMA M)
+constexpr int BM = 128;           // rows per MMA (UMMA M); a CTA tile has MH such halves
+constexpr int MH = 2;
+constexpr int BN = 128;           // accumulator columns per tile
 constexpr int BK = 64;            // contraction elements per pipeline stage (one 128-byte swizzle row)
 constexpr int DQ_WARPS = 8;
-constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int EPI_WARPS = 8;
+constexpr int A_STAGE_BYTES = MH * BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int C_STAGE_BYTES = BN * BK / 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 struct GemmParams {
@@ -36,7 +45,7 @@ struct GemmParams {
     int M, N, E;
     int tiles_m, tiles_n;
     int w_rows, w_cols;
-    const int *tile_expert, *ntiles_dev, *off;
+    const int *tile_info, *ntiles_dev, *off;
     void *out; int out_dtype; long long ldo;
     const void *resid; float beta;
     bf16 *gp, *up, *ap, *dgp, *dup;
@@ -107,6 +116,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t v[32])
                    "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                  : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t v[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle (Blackwell descriptor version 1).
@@ -153,56 +169,106 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 s2)
     return o;
 }
 
+// ------------------------------------------------------------------ epilogue staging
+// Lane r of a warp owns tile row r and holds VECS 16-byte vectors of it (a row
+// piece of 32, 64 or 128 bytes).  The piece goes through a swizzled 4 KiB buffer so
+// that each global access instruction covers whole row pieces: 4 rows x 128 B,
+// 8 rows x 64 B or 16 rows x 32 B.  Both the lane-per-row and the transposed access pattern are
+// free of shared-memory bank conflicts.
+template <int VECS>
+__device__ __forceinline__ int stage_slot(int r, int c)
+{
+    return VECS == 8 ? (c ^ (r & 7)) : VECS == 4 ? (c ^ ((r >> 1) & 3)) : (c ^ ((r >> 2) & 1));
+}
+
+template <int VECS>
+__device__ __forceinline__ void warp_store_rows(uint8_t *stage, const uint4 *v, int lane, uint8_t *g0, long long pitch, int valid_rows)
+{
+    constexpr int RB = VECS * 16;
+#pragma unroll
+    for (int c = 0; c < VECS; c++) *reinterpret_cast<uint4 *>(stage + lane * RB + stage_slot<VECS>(lane, c) * 16) = v[c];
+    __syncwarp();
+    constexpr int RPI = 32 / VECS;
+#pragma unroll
+    for (int j = 0; j < VECS; j++) {
+        const int r = j * RPI + lane / VECS, c = lane % VECS;
+        uint4 x = *reinterpret_cast<const uint4 *>(stage + r * RB + stage_slot<VECS>(r, c) * 16);
+        if (r < valid_rows) *reinterpret_cast<uint4 *>(g0 + (long long)r * pitch + c * 16) = x;
+    }
+    __syncwarp();
+}
+
+template <int VECS>
+__device__ __forceinline__ void warp_load_rows(uint8_t *stage, uint4 *v, int lane, const uint8_t *g0, long long pitch, int valid_rows)
+{
+    constexpr int RB = VECS * 16;
+    constexpr int RPI = 32 / VECS;
+#pragma unroll
+    for (int j = 0; j < VECS; j++) {
+        const int r = j * RPI + lane / VECS, c = lane % VECS;
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (r < valid_rows) x = *reinterpret_cast<const uint4 *>(g0 + (long long)r * pitch + c * 16);
+        *reinterpret_cast<uint4 *>(stage + r * RB + stage_slot<VECS>(r, c) * 16) = x;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < VECS; c++) v[c] = *reinterpret_cast<const uint4 *>(stage + lane * RB + stage_slot<VECS>(lane, c) * 16);
+    __syncwarp();
+}
+
 struct Ring {
     int idx; uint32_t phase;
     __device__ __forceinline__ void next(int n) { if (++idx == n) { idx = 0; phase ^= 1u; } }
 };
 
-struct TileInfo { int m0, n_t, e, ksteps; long long row0; };
+// m0: first row of the tile; halves: how many 128-row halves carry rows (1 or 2)
+struct TileInfo { int m0, n_t, e, ksteps, row0, halves; };
 
 template <int SCHED>
 __device__ __forceinline__ TileInfo decode_tile(const GemmParams &p, int tile, int ntr)
 {
     TileInfo t;
     if (SCHED == SCHED_DENSE) {
-        t.m0 = (tile % p.tiles_m) * BM; t.n_t = tile / p.tiles_m; t.e = 0; t.ksteps = p.ksteps; t.row0 = 0;
+        t.m0 = (tile % p.tiles_m) * (MH * BM); t.n_t = tile / p.tiles_m; t.e = 0; t.ksteps = p.ksteps; t.row0 = 0;
+        t.halves = (t.m0 + BM < p.M) ? 2 : 1;
     } else if (SCHED == SCHED_ROWS) {
         int rt = tile % ntr;
-        t.m0 = rt * BM; t.n_t = tile / ntr; t.e = p.tile_expert[rt]; t.ksteps = p.ksteps; t.row0 = 0;
+        int info = p.tile_info[rt];
+        t.m0 = (info & 0xFFFFF) * BM; t.e = (info >> 20) & 0x1FF; t.halves = ((info >> 30) & 1) + 1;
+        t.n_t = tile / ntr; t.ksteps = p.ksteps; t.row0 = 0;
     } else {
         int per = p.tiles_m * p.tiles_n;
         t.e = tile / per;
         int r = tile % per;
-        t.m0 = (r % p.tiles_m) * BM; t.n_t = r / p.tiles_m;
+        t.m0 = (r % p.tiles_m) * (MH * BM); t.n_t = r / p.tiles_m;
         t.row0 = p.off[t.e];
         t.ksteps = (p.off[t.e + 1] - p.off[t.e]) / BK;
+        t.halves = (t.m0 + BM < p.M) ? 2 : 1;
     }
     return t;
 }
 
-__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + __expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
 
 // ------------------------------------------------------------------ the kernel
-template <int BMODE, int EPI, int SCHED, int BN>
-__global__ void __launch_bounds__((BMODE == B_DEQ_MN || BMODE == B_DEQ_K) ? 448 : 192, 1)
+template <int BMODE, int EPI, int SCHED>
+__global__ void __launch_bounds__((BMODE == B_DEQ_MN || BMODE == B_DEQ_K) ? 576 : 320, 1)
 k_gemm(const __grid_constant__ GemmParams p)
 {
     constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
-    constexpr bool DUAL = (EPI == EPI_SWIGLU);           // B tile = [W1 cols | W3 cols]
-    constexpr int B_STAGE_BYTES = BN * BK * 2;
-    constexpr int C_STAGE_BYTES = BN * BK / 2;
-    constexpr int NSA = 4, NSB = DEQ ? 3 : 4, NSC = 4;
+    constexpr bool DUAL = (EPI == EPI_SWIGLU);           // B tile = [64 W1 columns | 64 W3 columns]
+    constexpr int NSA = DEQ ? 3 : 4, NSB = DEQ ? 3 : 4, NSC = 4;
     constexpr uint32_t IDESC = make_idesc(BM, BN, BMODE == AB_TMA_MN ? 1 : 0, (BMODE == B_DEQ_MN || BMODE == AB_TMA_MN) ? 1 : 0);
-    constexpr uint32_t TMEM_COLS = 2 * BN;
-    static_assert(!DUAL || BN == 256, "swiglu tiles are 128 g + 128 u columns");
+    constexpr uint32_t ACC_COLS = MH * BN;               // one accumulator buffer
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sA = smem;
     uint8_t *sB = sA + NSA * A_STAGE_BYTES;
     uint8_t *sC = sB + NSB * B_STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sC + (DEQ ? NSC * C_STAGE_BYTES : 0));
-    // barrier layout
+    uint8_t *sE = sC + (DEQ ? NSC * C_STAGE_BYTES : 0);       // 8 epilogue warps x 4 KiB staging
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sE + EPI_WARPS * 4096);
     uint64_t *full_a = bars, *empty_a = full_a + NSA, *full_b = empty_a + NSA, *empty_b = full_b + NSB;
     uint64_t *full_c = empty_b + NSB, *empty_c = full_c + NSC, *tmem_full = empty_c + NSC, *tmem_empty = tmem_full + 2;
     uint64_t *spare = tmem_empty + 2;
@@ -215,7 +281,7 @@ k_gemm(const __grid_constant__ GemmParams p)
         for (int i = 0; i < NSA; i++) { mbar_init(smem_u32(&full_a[i]), 1); mbar_init(smem_u32(&empty_a[i]), 1); }
         for (int i = 0; i < NSB; i++) { mbar_init(smem_u32(&full_b[i]), DEQ ? DQ_WARPS : 1); mbar_init(smem_u32(&empty_b[i]), 1); }
         for (int i = 0; i < NSC; i++) { mbar_init(smem_u32(&full_c[i]), 1); mbar_init(smem_u32(&empty_c[i]), DQ_WARPS); }
-        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&tmem_full[i]), 1); mbar_init(smem_u32(&tmem_empty[i]), 4); }
+        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&tmem_full[i]), 1); mbar_init(smem_u32(&tmem_empty[i]), EPI_WARPS); }
         mbar_init(smem_u32(spare), 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -245,21 +311,19 @@ k_gemm(const __grid_constant__ GemmParams p)
                         uint32_t dstA = smem_u32(sA + ra.idx * A_STAGE_BYTES);
                         if (BMODE == AB_TMA_MN) {
                             uint32_t dstB = smem_u32(sB + ra.idx * B_STAGE_BYTES);
-                            int row = (int)t.row0 + ks * BK;
-                            mbar_expect_tx(bar, A_STAGE_BYTES + B_STAGE_BYTES);
-                            tma_load_2d(dstA, &p.a_map[0], bar, t.m0, row);
-                            tma_load_2d(dstA + 8192, &p.a_map[0], bar, t.m0 + 64, row);
+                            int row = t.row0 + ks * BK;
+                            mbar_expect_tx(bar, t.halves * (BM * BK * 2) + B_STAGE_BYTES);
+                            for (int i = 0; i < 2 * t.halves; i++)
+                                tma_load_2d(dstA + i * 8192, &p.a_map[0], bar, t.m0 + 64 * i, row);
 #pragma unroll
                             for (int j = 0; j < BN / 64; j++)
                                 tma_load_2d(dstB + j * 8192, &p.w_map[0], bar, t.n_t * BN + 64 * j, row);
-                        } else if (BMODE == B_TMA_K) {
-                            uint32_t dstB = smem_u32(sB + ra.idx * B_STAGE_BYTES);
-                            mbar_expect_tx(bar, A_STAGE_BYTES + B_STAGE_BYTES);
-                            tma_load_2d(dstA, &p.a_map[seg], bar, ks * BK, t.m0);
-                            tma_load_2d(dstB, &p.w_map[seg], bar, ks * BK, t.n_t * BN);
                         } else {
-                            mbar_expect_tx(bar, A_STAGE_BYTES);
-                            tma_load_2d(dstA, &p.a_map[seg], bar, ks * BK, t.m0);
+                            mbar_expect_tx(bar, t.halves * (BM * BK * 2) + (BMODE == B_TMA_K ? B_STAGE_BYTES : 0));
+                            for (int h = 0; h < t.halves; h++)
+                                tma_load_2d(dstA + h * (BM * BK * 2), &p.a_map[seg], bar, ks * BK, t.m0 + h * BM);
+                            if (BMODE == B_TMA_K)
+                                tma_load_2d(smem_u32(sB + ra.idx * B_STAGE_BYTES), &p.w_map[seg], bar, ks * BK, t.n_t * BN);
                         }
                     }
                     __syncwarp();
@@ -274,8 +338,8 @@ k_gemm(const __grid_constant__ GemmParams p)
                             if (BMODE == B_DEQ_MN) {
                                 int row = t.e * p.w_rows + ks * BK;
                                 if (DUAL) {
-                                    tma_load_2d(dstC, &p.w_map[0], bar, t.n_t * 64, row);
-                                    tma_load_2d(dstC + C_STAGE_BYTES / 2, &p.w_map[1], bar, t.n_t * 64, row);
+                                    tma_load_2d(dstC, &p.w_map[0], bar, t.n_t * (BN / 4), row);
+                                    tma_load_2d(dstC + C_STAGE_BYTES / 2, &p.w_map[1], bar, t.n_t * (BN / 4), row);
                                 } else {
                                     tma_load_2d(dstC, &p.w_map[seg], bar, t.n_t * (BN / 2), row);
                                 }
@@ -300,8 +364,8 @@ k_gemm(const __grid_constant__ GemmParams p)
             ok = mbar_wait(smem_u32(&tmem_empty[acc]), (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag, p.errword, 3);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-            uint32_t first = 1;
+            const uint32_t tmem_d = tmem_base + (uint32_t)acc * ACC_COLS;
+            uint32_t accumulate = 0;
             for (int seg = 0; ok && seg < p.nseg; seg++) {
                 for (int ks = 0; ks < t.ksteps; ks++) {
                     ok = mbar_wait(smem_u32(&full_a[ra.idx]), ra.phase, abort_flag, p.errword, 4);
@@ -317,17 +381,20 @@ k_gemm(const __grid_constant__ GemmParams p)
                         const uint32_t b0 = smem_u32(sB + sb * B_STAGE_BYTES);
 #pragma unroll
                         for (int k16 = 0; k16 < BK / 16; k16++) {
-                            uint64_t ad = (BMODE == AB_TMA_MN) ? make_desc(a0 + k16 * 2048, 8192, 1024)
-                                                               : make_desc(a0 + k16 * 32, 16, 1024);
                             uint64_t bd = (BMODE == B_DEQ_MN || BMODE == AB_TMA_MN) ? make_desc(b0 + k16 * 2048, 8192, 1024)
                                                                                     : make_desc(b0 + k16 * 32, 16, 1024);
-                            tc_mma_bf16(tmem_d, ad, bd, IDESC, first ? 0u : 1u);
-                            first = 0;
+                            for (int h = 0; h < t.halves; h++) {
+                                uint64_t ad = (BMODE == AB_TMA_MN) ? make_desc(a0 + h * 16384 + k16 * 2048, 8192, 1024)
+                                                                   : make_desc(a0 + h * 16384 + k16 * 32, 16, 1024);
+                                tc_mma_bf16(tmem_d + (uint32_t)h * BN, ad, bd, IDESC, accumulate);
+                            }
+                            accumulate = 1;
                         }
                         tc_commit(smem_u32(&empty_a[ra.idx]));
                         if (DEQ) tc_commit(smem_u32(&empty_b[rb.idx]));
                     }
                     __syncwarp();
+                    accumulate = 1;
                     ra.next(NSA);
                     if (DEQ) rb.next(NSB);
                 }
@@ -342,10 +409,14 @@ k_gemm(const __grid_constant__ GemmParams p)
             __syncwarp();
             for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(smem_u32(spare), 0); i++) {}
         }
-    } else if (warp < 6) {
+    } else if (warp < 2 + EPI_WARPS) {
         // =============================== epilogue ===============================
-        const int q = warp & 3;                          // TMEM lane quarter this warp may read
-        const int row_in_tile = q * 32 + lane;
+        // Warp (q, h): q = TMEM lane quarter it may read (= warp id mod 4), h = which
+        // 128-row half of the tile.  A lane holds one tile row; element-wise work runs in
+        // registers, then the row pieces go through a swizzled 4 KiB staging buffer so that
+        // every global store instruction writes whole row pieces.
+        const int q = warp & 3, h = (warp - 2) >> 2;
+        uint8_t *stage = sE + (warp - 2) * 4096;
         bool ok = true;
         int it = 0;
         for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x, it++) {
@@ -354,112 +425,109 @@ k_gemm(const __grid_constant__ GemmParams p)
             ok = mbar_wait(smem_u32(&tmem_full[acc]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 6);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-            const long long row = (long long)t.m0 + row_in_tile;
-            const bool have_acc = (SCHED != SCHED_GROUPK) || t.ksteps > 0;
-            const bool row_ok = (SCHED != SCHED_DENSE) || row < p.M;
-            if (EPI == EPI_STORE || EPI == EPI_ACCUM) {
-                const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.tiles_m * BM + row) : row;
+            if (h < t.halves) {
+                const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * ACC_COLS + (uint32_t)h * BN;
+                const long long row0 = (long long)t.m0 + h * BM + q * 32;            // first row of this warp
+                const bool have_acc = (SCHED != SCHED_GROUPK) || t.ksteps > 0;
+                int valid = 32;
+                if (SCHED != SCHED_ROWS) { long long left = (long long)p.M - row0; valid = left < 0 ? 0 : (left < 32 ? (int)left : 32); }
+                if (EPI == EPI_STORE || EPI == EPI_ACCUM) {
+                    const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; c++) {
-                    uint32_t v[32];
-                    tmem_ld32(tbase + c * 32, v);
-                    tmem_ld_wait();
-                    if (!row_ok) continue;
-                    const long long o = rbase * p.ldo + (long long)t.n_t * BN + c * 32;
-                    float f[32];
+                    for (int c = 0; c < BN / 32; c++) {
+                        uint32_t v[32];
+                        tmem_ld32(tbase + c * 32, v);
+                        tmem_ld_wait();
+                        const long long o = rbase * p.ldo + (long long)t.n_t * BN + c * 32;
+                        float f[32];
 #pragma unroll
-                    for (int i = 0; i < 32; i++) f[i] = have_acc ? __uint_as_float(v[i]) : 0.0f;
-                    if (p.out_dtype == QLMB_F32) {
-                        float4 *op = reinterpret_cast<float4 *>((float *)p.out + o);
-                        const float4 *rp = p.resid ? reinterpret_cast<const float4 *>((const float *)p.resid + o) : nullptr;
+                        for (int i = 0; i < 32; i++) f[i] = have_acc ? __uint_as_float(v[i]) : 0.0f;
+                        if (p.out_dtype == QLMB_F32) {
+                            if (p.resid) {
+                                uint4 r[8];
+                                warp_load_rows<8>(stage, r, lane, reinterpret_cast<const uint8_t *>((const float *)p.resid + o), p.ldo * 4, valid);
+                                const float *rf = reinterpret_cast<const float *>(r);
 #pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            float4 x = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
-                            if (rp) { float4 r = rp[i]; x.x += r.x; x.y += r.y; x.z += r.z; x.w += r.w; }
-                            if (p.beta != 0.0f) { float4 r = op[i]; x.x += p.beta * r.x; x.y += p.beta * r.y; x.z += p.beta * r.z; x.w += p.beta * r.w; }
-                            op[i] = x;
-                        }
-                    } else {
-                        uint4 *op = reinterpret_cast<uint4 *>((bf16 *)p.out + o);
-                        const uint4 *rp = p.resid ? reinterpret_cast<const uint4 *>((const bf16 *)p.resid + o) : nullptr;
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            float x[8];
-#pragma unroll
-                            for (int k = 0; k < 8; k++) x[k] = f[8 * i + k];
-                            if (rp) {
-                                uint4 r = rp[i];
-                                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&r);
-#pragma unroll
-                                for (int k = 0; k < 4; k++) { float2 g = __bfloat1622float2(h[k]); x[2 * k] += g.x; x[2 * k + 1] += g.y; }
+                                for (int i = 0; i < 32; i++) f[i] += rf[i];
                             }
                             if (p.beta != 0.0f) {
-                                uint4 r = op[i];
-                                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&r);
+                                uint4 r[8];
+                                warp_load_rows<8>(stage, r, lane, reinterpret_cast<const uint8_t *>((const float *)p.out + o), p.ldo * 4, valid);
+                                const float *rf = reinterpret_cast<const float *>(r);
 #pragma unroll
-                                for (int k = 0; k < 4; k++) { float2 g = __bfloat1622float2(h[k]); x[2 * k] += p.beta * g.x; x[2 * k + 1] += p.beta * g.y; }
+                                for (int i = 0; i < 32; i++) f[i] += p.beta * rf[i];
                             }
-                            uint4 w;
-                            __nv_bfloat162 *hw = reinterpret_cast<__nv_bfloat162 *>(&w);
+                            warp_store_rows<8>(stage, reinterpret_cast<const uint4 *>(f), lane, reinterpret_cast<uint8_t *>((float *)p.out + o), p.ldo * 4, valid);
+                        } else {
+                            if (p.resid) {
+                                uint4 r[4];
+                                warp_load_rows<4>(stage, r, lane, reinterpret_cast<const uint8_t *>((const bf16 *)p.resid + o), p.ldo * 2, valid);
+                                const __nv_bfloat162 *hh = reinterpret_cast<const __nv_bfloat162 *>(r);
 #pragma unroll
-                            for (int k = 0; k < 4; k++) hw[k] = __floats2bfloat162_rn(x[2 * k], x[2 * k + 1]);
-                            op[i] = w;
+                                for (int i = 0; i < 16; i++) { float2 g = __bfloat1622float2(hh[i]); f[2 * i] += g.x; f[2 * i + 1] += g.y; }
+                            }
+                            if (p.beta != 0.0f) {
+                                uint4 r[4];
+                                warp_load_rows<4>(stage, r, lane, reinterpret_cast<const uint8_t *>((const bf16 *)p.out + o), p.ldo * 2, valid);
+                                const __nv_bfloat162 *hh = reinterpret_cast<const __nv_bfloat162 *>(r);
+#pragma unroll
+                                for (int i = 0; i < 16; i++) { float2 g = __bfloat1622float2(hh[i]); f[2 * i] += p.beta * g.x; f[2 * i + 1] += p.beta * g.y; }
+                            }
+                            uint4 w[4];
+                            __nv_bfloat162 *hw = reinterpret_cast<__nv_bfloat162 *>(w);
+#pragma unroll
+                            for (int i = 0; i < 16; i++) hw[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                            warp_store_rows<4>(stage, w, lane, reinterpret_cast<uint8_t *>((bf16 *)p.out + o), p.ldo * 2, valid);
                         }
                     }
-                }
-            } else if (EPI == EPI_SWIGLU) {
-                // accumulator columns [0,128) = gate pre-activation, [128,256) = up projection
+                } else if (EPI == EPI_SWIGLU) {
+                    // accumulator columns [0,64) = gate pre-activation, [64,128) = up projection
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
-                    uint32_t g[32], u[32];
-                    tmem_ld32(tbase + c * 32, g);
-                    tmem_ld32(tbase + 128 + c * 32, u);
-                    tmem_ld_wait();
-                    const long long o = row * p.ldo + (long long)t.n_t * 128 + c * 32;
-                    uint4 *pa = reinterpret_cast<uint4 *>(p.ap + o), *pg = reinterpret_cast<uint4 *>(p.gp + o),
-                          *pu = reinterpret_cast<uint4 *>(p.up + o);
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t g[16], u[16];
+                        tmem_ld16(tbase + c * 16, g);
+                        tmem_ld16(tbase + 64 + c * 16, u);
+                        tmem_ld_wait();
+                        const long long o = row0 * p.ldo + (long long)t.n_t * 64 + c * 16;
+                        uint4 wa[2], wg[2], wu[2];
+                        __nv_bfloat162 *ha = reinterpret_cast<__nv_bfloat162 *>(wa), *hg = reinterpret_cast<__nv_bfloat162 *>(wg),
+                                       *hu = reinterpret_cast<__nv_bfloat162 *>(wu);
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        uint4 wa, wg, wu;
-                        __nv_bfloat162 *ha = reinterpret_cast<__nv_bfloat162 *>(&wa), *hg = reinterpret_cast<__nv_bfloat162 *>(&wg),
-                                       *hu = reinterpret_cast<__nv_bfloat162 *>(&wu);
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            float g0 = __uint_as_float(g[8 * i + 2 * k]), g1 = __uint_as_float(g[8 * i + 2 * k + 1]);
-                            float u0 = __uint_as_float(u[8 * i + 2 * k]), u1 = __uint_as_float(u[8 * i + 2 * k + 1]);
-                            ha[k] = __floats2bfloat162_rn(silu_f(g0) * u0, silu_f(g1) * u1);
+                        for (int k = 0; k < 8; k++) {
+                            float g0 = __uint_as_float(g[2 * k]), g1 = __uint_as_float(g[2 * k + 1]);
+                            float u0 = __uint_as_float(u[2 * k]), u1 = __uint_as_float(u[2 * k + 1]);
+                            ha[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
                             hg[k] = __floats2bfloat162_rn(g0, g1);
                             hu[k] = __floats2bfloat162_rn(u0, u1);
                         }
-                        pa[i] = wa; pg[i] = wg; pu[i] = wu;
+                        warp_store_rows<2>(stage, wa, lane, reinterpret_cast<uint8_t *>(p.ap + o), p.ldo * 2, valid);
+                        warp_store_rows<2>(stage, wg, lane, reinterpret_cast<uint8_t *>(p.gp + o), p.ldo * 2, valid);
+                        warp_store_rows<2>(stage, wu, lane, reinterpret_cast<uint8_t *>(p.up + o), p.ldo * 2, valid);
                     }
-                }
-            } else {   // EPI_SWIGLU_BWD: accumulator = d(act); dg = da*u*silu'(g), du = da*silu(g)
+                } else {   // EPI_SWIGLU_BWD: accumulator = d(act); dg = da*u*silu'(g), du = da*silu(g)
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; c++) {
-                    uint32_t v[32];
-                    tmem_ld32(tbase + c * 32, v);
-                    tmem_ld_wait();
-                    const long long o = row * p.ldo + (long long)t.n_t * BN + c * 32;
-                    const uint4 *pg = reinterpret_cast<const uint4 *>(p.gp + o), *pu = reinterpret_cast<const uint4 *>(p.up + o);
-                    uint4 *pdg = reinterpret_cast<uint4 *>(p.dgp + o), *pdu = reinterpret_cast<uint4 *>(p.dup + o);
+                    for (int c = 0; c < BN / 16; c++) {
+                        uint32_t v[16];
+                        tmem_ld16(tbase + c * 16, v);
+                        const long long o = row0 * p.ldo + (long long)t.n_t * BN + c * 16;
+                        uint4 rg[2], ru[2], wdg[2], wdu[2];
+                        warp_load_rows<2>(stage, rg, lane, reinterpret_cast<const uint8_t *>(p.gp + o), p.ldo * 2, valid);
+                        warp_load_rows<2>(stage, ru, lane, reinterpret_cast<const uint8_t *>(p.up + o), p.ldo * 2, valid);
+                        tmem_ld_wait();
+                        const __nv_bfloat162 *hg = reinterpret_cast<const __nv_bfloat162 *>(rg), *hu = reinterpret_cast<const __nv_bfloat162 *>(ru);
+                        __nv_bfloat162 *hdg = reinterpret_cast<__nv_bfloat162 *>(wdg), *hdu = reinterpret_cast<__nv_bfloat162 *>(wdu);
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        uint4 rg = pg[i], ru = pu[i], wdg, wdu;
-                        const __nv_bfloat162 *hg = reinterpret_cast<const __nv_bfloat162 *>(&rg), *hu = reinterpret_cast<const __nv_bfloat162 *>(&ru);
-                        __nv_bfloat162 *hdg = reinterpret_cast<__nv_bfloat162 *>(&wdg), *hdu = reinterpret_cast<__nv_bfloat162 *>(&wdu);
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
+                        for (int k = 0; k < 8; k++) {
                             float2 gg = __bfloat1622float2(hg[k]), uu = __bfloat1622float2(hu[k]);
-                            float d0 = __uint_as_float(v[8 * i + 2 * k]), d1 = __uint_as_float(v[8 * i + 2 * k + 1]);
-                            float s0 = 1.0f / (1.0f + __expf(-gg.x)), s1 = 1.0f / (1.0f + __expf(-gg.y));
+                            float d0 = __uint_as_float(v[2 * k]), d1 = __uint_as_float(v[2 * k + 1]);
+                            float s0 = sigmoid_f(gg.x), s1 = sigmoid_f(gg.y);
                             float dg0 = d0 * uu.x * (s0 + gg.x * s0 * (1.0f - s0)), dg1 = d1 * uu.y * (s1 + gg.y * s1 * (1.0f - s1));
                             float du0 = d0 * gg.x * s0, du1 = d1 * gg.y * s1;
                             hdg[k] = __floats2bfloat162_rn(dg0, dg1);
                             hdu[k] = __floats2bfloat162_rn(du0, du1);
                         }
-                        pdg[i] = wdg; pdu[i] = wdu;
+                        warp_store_rows<2>(stage, wdg, lane, reinterpret_cast<uint8_t *>(p.dgp + o), p.ldo * 2, valid);
+                        warp_store_rows<2>(stage, wdu, lane, reinterpret_cast<uint8_t *>(p.dup + o), p.ldo * 2, valid);
                     }
                 }
             }
@@ -469,48 +537,63 @@ k_gemm(const __grid_constant__ GemmParams p)
         }
     } else if (DEQ) {
         // =============================== dequant warps ===============================
-        const int dw = warp - 6;
+        const int dw = warp - (2 + EPI_WARPS);
         constexpr int ITERS = (C_STAGE_BYTES / 4) / (DQ_WARPS * 32);
         Ring rc = {0, 0}, rb = {0, 0};
         bool ok = true;
-        // destination offsets inside a B stage are the same for every stage
+        // per-lane constants: where each of its code words lands in a B stage, and which
+        // (row, column) of the stored code matrix it comes from (for the scale lookup)
         uint32_t dst_off[ITERS];
-        int srow[ITERS], scol[ITERS], shalf[ITERS];
+        int srow[ITERS], scol[ITERS];
+        bool second[ITERS];
 #pragma unroll
         for (int i = 0; i < ITERS; i++) {
             int wi = (i * DQ_WARPS + dw) * 32 + lane;
             if (BMODE == B_DEQ_MN) {
-                int k, c, nb, half = 0;
-                if (DUAL) { half = wi / 1024; int r = wi % 1024; k = r / 16; c = r % 16; nb = half * 2 + c / 8; }
-                else { constexpr int WPR = BN / 8; k = wi / WPR; c = wi % WPR; nb = c / 8; }
+                int k, c, nb;
+                if (DUAL) { int half = wi / (BN * 4); int r = wi % (BN * 4); k = r / (BN / 16); c = r % (BN / 16); nb = half * (BN / 128) + c / 8; second[i] = half != 0; }
+                else { constexpr int WPR = BN / 8; k = wi / WPR; c = wi % WPR; nb = c / 8; second[i] = false; }
                 dst_off[i] = (uint32_t)(nb * 8192 + (k >> 3) * 1024 + (k & 7) * 128 + (((c & 7) ^ (k & 7)) << 4));
-                srow[i] = k; scol[i] = c * 8; shalf[i] = half;
+                srow[i] = k; scol[i] = c * 8;
             } else {
                 int n = wi / 8, c = wi % 8;
                 dst_off[i] = (uint32_t)((n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4));
-                srow[i] = n; scol[i] = c * 8; shalf[i] = 0;
+                srow[i] = n; scol[i] = c * 8; second[i] = false;
             }
         }
-        const int groups_per_row = p.w_cols / 128;
+        const int gpr = p.w_cols / 128;                  // scale groups per stored row
+        const float *sc0 = p.scales[0], *sc1 = p.scales[1];
         for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
             TileInfo t = decode_tile<SCHED>(p, tile, ntr);
             for (int seg = 0; ok && seg < p.nseg; seg++) {
-                for (int ks = 0; ks < t.ksteps; ks++) {
-                    // scales first: they do not depend on the code tile being resident
-                    float sc[ITERS];
+                const float *sseg = seg ? sc1 : sc0;
+                // index of the scale of word i at step ks = sbase[i] + ks * sstep
+                int sbase[ITERS], sstep;
 #pragma unroll
-                    for (int i = 0; i < ITERS; i++) {
-                        long long gi;
-                        const float *sp;
-                        if (BMODE == B_DEQ_MN) {
-                            sp = DUAL ? p.scales[shalf[i]] : p.scales[seg];
-                            int ncol = DUAL ? (t.n_t * 128 + scol[i]) : (t.n_t * BN + scol[i]);
-                            gi = ((long long)t.e * p.w_rows + ks * BK + srow[i]) * groups_per_row + ncol / 128;
-                        } else {
-                            sp = p.scales[seg];
-                            gi = ((long long)t.e * p.w_rows + t.n_t * BN + srow[i]) * groups_per_row + (ks * BK) / 128;
+                for (int i = 0; i < ITERS; i++) {
+                    if (BMODE == B_DEQ_MN) {
+                        int ncol = DUAL ? (t.n_t * (BN / 2) + scol[i]) : (t.n_t * BN + scol[i]);
+                        sbase[i] = (t.e * p.w_rows + srow[i]) * gpr + ncol / 128;
+                    } else {
+                        sbase[i] = (t.e * p.w_rows + t.n_t * BN + srow[i]) * gpr;
+                    }
+                }
+                sstep = (BMODE == B_DEQ_MN) ? BK * gpr : 0;
+                float cur[ITERS], nxt[ITERS];
+#pragma unroll
+                for (int i = 0; i < ITERS; i++) {
+                    const float *sp = (DUAL && second[i]) ? sc1 : sseg;
+                    cur[i] = __ldg(sp + sbase[i]);
+                }
+                for (int ks = 0; ks < t.ksteps; ks++) {
+                    // scales of the next step are requested before this step's tile is awaited
+                    if (ks + 1 < t.ksteps) {
+#pragma unroll
+                        for (int i = 0; i < ITERS; i++) {
+                            const float *sp = (DUAL && second[i]) ? sc1 : sseg;
+                            int idx = (BMODE == B_DEQ_MN) ? sbase[i] + (ks + 1) * sstep : sbase[i] + ((ks + 1) * BK) / 128;
+                            nxt[i] = __ldg(sp + idx);
                         }
-                        sc[i] = __ldg(sp + gi);
                     }
                     ok = mbar_wait(smem_u32(&full_c[rc.idx]), rc.phase, abort_flag, p.errword, 7);
                     if (!ok) break;
@@ -523,12 +606,14 @@ k_gemm(const __grid_constant__ GemmParams p)
                     uint8_t *bdst = sB + rb.idx * B_STAGE_BYTES;
 #pragma unroll
                     for (int i = 0; i < ITERS; i++)
-                        *reinterpret_cast<uint4 *>(bdst + dst_off[i]) = dequant8(w[i], __float2bfloat162_rn(sc[i]));
+                        *reinterpret_cast<uint4 *>(bdst + dst_off[i]) = dequant8(w[i], __float2bfloat162_rn(cur[i]));
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) { mbar_arrive(smem_u32(&full_b[rb.idx])); mbar_arrive(smem_u32(&empty_c[rc.idx])); }
                     rc.next(NSC);
                     rb.next(NSB);
+#pragma unroll
+                    for (int i = 0; i < ITERS; i++) cur[i] = nxt[i];
                 }
             }
         }
@@ -576,19 +661,19 @@ static int make_map(CUtensorMap *m, const void *base, CUtensorMapDataType dt, in
     return QLMB_OK;
 }
 
-template <int BMODE, int EPI, int SCHED, int BN>
+template <int BMODE, int EPI, int SCHED>
 static int launch_inst(const GemmParams &p, int grid, cudaStream_t st)
 {
     constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
-    constexpr int NSA = 4, NSB = DEQ ? 3 : 4, NSC = 4;
-    constexpr size_t smem = 1024 + NSA * A_STAGE_BYTES + NSB * (BN * BK * 2) + (DEQ ? NSC * (BN * BK / 2) : 0) + 256;
+    constexpr int NSA = DEQ ? 3 : 4, NSB = DEQ ? 3 : 4, NSC = 4;
+    constexpr size_t smem = 1024 + NSA * A_STAGE_BYTES + NSB * B_STAGE_BYTES + (DEQ ? NSC * C_STAGE_BYTES : 0) + EPI_WARPS * 4096 + 512;
     static bool configured = false;
-    auto kfn = k_gemm<BMODE, EPI, SCHED, BN>;
+    auto kfn = k_gemm<BMODE, EPI, SCHED>;
     if (!configured) {
         QLMB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    kfn<<<grid, DEQ ? 448 : 192, smem, st>>>(p);
+    kfn<<<grid, DEQ ? 576 : 320, smem, st>>>(p);
     QLMB_LAUNCH_CHECK("k_gemm");
     return QLMB_OK;
 }
@@ -597,18 +682,16 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
 {
     int rc = load_encode();
     if (rc) return rc;
-    QLMB_REQUIRE(g.bn == 128 || g.bn == 256, "gemm: bn %d", g.bn);
+    const bool dual = g.epi == EPI_SWIGLU;
+    QLMB_REQUIRE(g.N % (dual ? BN / 2 : BN) == 0, "gemm: N=%d is not a multiple of the %d-column tile", g.N, dual ? BN / 2 : BN);
     QLMB_REQUIRE(g.sched != SCHED_GROUPK || g.M % BM == 0, "gemm: grouped weight gradient needs M=%d to be a multiple of %d", g.M, BM);
-    QLMB_REQUIRE(g.N % g.bn == 0 || g.epi == EPI_SWIGLU, "gemm: N=%d is not a multiple of the %d-column tile", g.N, g.bn);
     GemmParams p;
     memset(&p, 0, sizeof p);
-    const bool deq = g.bmode == B_DEQ_MN || g.bmode == B_DEQ_K;
-    const bool dual = g.epi == EPI_SWIGLU;
     p.nseg = g.nseg; p.ksteps = g.ksteps; p.M = g.M; p.N = g.N; p.E = g.E;
-    p.tiles_m = (g.sched == SCHED_GROUPK) ? g.M / BM : (g.M + BM - 1) / BM;
-    p.tiles_n = dual ? g.N / 128 : g.N / g.bn;
+    p.tiles_m = (g.M + MH * BM - 1) / (MH * BM);
+    p.tiles_n = dual ? g.N / (BN / 2) : g.N / BN;
     p.w_rows = g.w_rows; p.w_cols = g.w_cols;
-    p.tile_expert = g.tile_expert; p.ntiles_dev = g.ntiles_dev; p.off = g.off;
+    p.tile_info = g.tile_info; p.ntiles_dev = g.ntiles_dev; p.off = g.off;
     p.out = g.out; p.out_dtype = g.out_dtype; p.ldo = g.ldo; p.resid = g.resid; p.beta = g.beta;
     p.gp = g.gp; p.up = g.up; p.ap = g.ap; p.dgp = g.dgp; p.dup = g.dup;
     p.errword = device_error_word();
@@ -630,13 +713,13 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
             if (rc) return rc;
         }
         if (g.bmode == B_TMA_K) {
-            rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, g.w_cols, wrows_total, (unsigned long long)g.w_cols * 2, 64, g.bn, CU_TENSOR_MAP_SWIZZLE_128B);
+            rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, g.w_cols, wrows_total, (unsigned long long)g.w_cols * 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B);
         } else if (g.bmode == B_DEQ_MN) {
             QLMB_REQUIRE(g.w_cols % 128 == 0, "gemm: code matrix width %d is not a multiple of the 128-element group", g.w_cols);
-            rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w_cols / 2, wrows_total, g.w_cols / 2, dual ? 64 : g.bn / 2, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+            rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w_cols / 2, wrows_total, g.w_cols / 2, dual ? BN / 4 : BN / 2, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
         } else {
             QLMB_REQUIRE(g.w_cols % 128 == 0, "gemm: code matrix width %d is not a multiple of the 128-element group", g.w_cols);
-            rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w_cols / 2, wrows_total, g.w_cols / 2, 32, g.bn, CU_TENSOR_MAP_SWIZZLE_NONE);
+            rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w_cols / 2, wrows_total, g.w_cols / 2, 32, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
         }
         if (rc) return rc;
     }
@@ -649,21 +732,20 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
     if (total < grid) grid = (int)total;
     ProfScope prof(g.name ? g.name : "gemm", st);
 
-#define INST(BM_, EP_, SC_, BN_) if (g.bmode == BM_ && g.epi == EP_ && g.sched == SC_ && g.bn == BN_) return launch_inst<BM_, EP_, SC_, BN_>(p, grid, st)
+#define INST(BM_, EP_, SC_) if (g.bmode == BM_ && g.epi == EP_ && g.sched == SC_) return launch_inst<BM_, EP_, SC_>(p, grid, st)
     // dense linears
-    INST(B_DEQ_MN, EPI_STORE, SCHED_DENSE, 256); INST(B_DEQ_MN, EPI_STORE, SCHED_DENSE, 128);
-    INST(B_DEQ_K, EPI_STORE, SCHED_DENSE, 256);  INST(B_DEQ_K, EPI_STORE, SCHED_DENSE, 128);
-    INST(AB_TMA_MN, EPI_ACCUM, SCHED_DENSE, 256); INST(AB_TMA_MN, EPI_ACCUM, SCHED_DENSE, 128);
-    INST(B_TMA_K, EPI_STORE, SCHED_DENSE, 256);
+    INST(B_DEQ_MN, EPI_STORE, SCHED_DENSE);
+    INST(B_DEQ_K, EPI_STORE, SCHED_DENSE);
+    INST(AB_TMA_MN, EPI_ACCUM, SCHED_DENSE);
+    INST(B_TMA_K, EPI_STORE, SCHED_DENSE);
     // expert FFN
-    INST(B_DEQ_MN, EPI_SWIGLU, SCHED_ROWS, 256);
-    INST(B_DEQ_MN, EPI_STORE, SCHED_ROWS, 256); INST(B_DEQ_MN, EPI_STORE, SCHED_ROWS, 128);
-    INST(B_DEQ_K, EPI_SWIGLU_BWD, SCHED_ROWS, 256); INST(B_DEQ_K, EPI_SWIGLU_BWD, SCHED_ROWS, 128);
-    INST(B_DEQ_K, EPI_STORE, SCHED_ROWS, 256); INST(B_DEQ_K, EPI_STORE, SCHED_ROWS, 128);
-    INST(AB_TMA_MN, EPI_ACCUM, SCHED_GROUPK, 256); INST(AB_TMA_MN, EPI_ACCUM, SCHED_GROUPK, 128);
+    INST(B_DEQ_MN, EPI_SWIGLU, SCHED_ROWS);
+    INST(B_DEQ_MN, EPI_STORE, SCHED_ROWS);
+    INST(B_DEQ_K, EPI_SWIGLU_BWD, SCHED_ROWS);
+    INST(B_DEQ_K, EPI_STORE, SCHED_ROWS);
+    INST(AB_TMA_MN, EPI_ACCUM, SCHED_GROUPK);
 #undef INST
-    (void)deq;
-    set_error("gemm: no kernel instance for bmode %d epi %d sched %d bn %d", g.bmode, g.epi, g.sched, g.bn);
+    set_error("gemm: no kernel instance for bmode %d epi %d sched %d", g.bmode, g.epi, g.sched);
     return QLMB_E_UNSUPPORTED;
 }
 

@@ -18,13 +18,13 @@ enum Epi {
     EPI_ACCUM = 3        // out(fp32) = beta*out + acc
 };
 enum Sched {
-    SCHED_DENSE = 0,   // tiles over [ceil(M/128)] x [N/BN]
-    SCHED_ROWS = 1,    // row tiles from a device table (expert per 128-row tile) x [N/BN]
-    SCHED_GROUPK = 2   // per expert: [Ma/128] x [Nb/BN] tiles, contraction over the expert's rows
+    SCHED_DENSE = 0,   // tiles over [ceil(M/256)] x [N/128]
+    SCHED_ROWS = 1,    // row tiles from a device table (one expert per tile) x [N/128]
+    SCHED_GROUPK = 2   // per expert: [ceil(Ma/256)] x [Nb/128] tiles, contraction over the expert's rows
 };
 
 struct GemmLaunch {
-    int bmode, epi, sched, bn;     // bn: 128 or 256 accumulator columns per tile
+    int bmode, epi, sched;
     // A operand(s): bf16 [a_rows][a_cols] row-major; one per contraction segment
     const void *a[2];
     long long a_rows;
@@ -36,7 +36,7 @@ struct GemmLaunch {
     int nseg;                      // contraction segments (2: dXp = dg W1^T + du W3^T)
     int ksteps;                    // 64-wide contraction steps per segment (DENSE / ROWS)
     int M, N, E;                   // valid rows (DENSE), output columns, experts
-    const int *tile_expert;        // ROWS: expert of every 128-row tile
+    const int *tile_info;          // ROWS: per 256-row tile: first row/128 | expert << 20 | (halves-1) << 30
     const int *ntiles_dev;         // ROWS: number of row tiles (device int)
     const int *off;                // GROUPK: padded row offsets [E+1]
     int max_row_tiles;             // ROWS: upper bound of *ntiles_dev (grid sizing)

@@ -15,7 +15,7 @@ int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N,
                 const float *bias, int bs, cudaStream_t st);
 size_t perm_scratch_ints(int N, int E, int K, int merged);
 int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
-               int *off, int *counts, int *bad_flag, int *tile_expert, int *ntiles, int tile_rows,
+               int *off, int *counts, int *bad_flag, int *tile_info, int *ntiles,
                int *chunk_scratch, cudaStream_t st);
 
 // ---- row kernels (qlmb_dispatch.cu) ----
@@ -36,8 +36,9 @@ int router_bwd(float *drt, const float *rprobs, const int *assign, const float *
                const int *counts, int N, int E, int K, float aux, cudaStream_t st);
 // dfnorm[n,:] = sum_k dXp[inv[k*N+n],:] + drt[n,:] * Wr^T
 int unpermute_rows(void *dfnorm, int dtype, const bf16 *dXp, const int *inv, const float *drt,
-                   const float *Wr, int N, int D, int E, int K, cudaStream_t st);
-// dWr[D,E] = beta*dWr + fnorm^T drt ; scratch holds ceil(N/256)*D*E floats
+                   const float *Wr, float *wrt_scratch /* D*E floats */, int N, int D, int E, int K,
+                   cudaStream_t st);
+// dWr[D,E] = beta*dWr + fnorm^T drt ; scratch holds 192*D*E floats
 int router_wgrad(float *dWr, const void *fnorm, int dtype, const float *drt, float *scratch, int N,
                  int D, int E, float beta, cudaStream_t st);
 // fp32 <-> bf16 row conversion helpers

@@ -16,8 +16,8 @@ namespace qlmb {
 
 struct Arena {
     size_t rows_cap;     // padded row capacity
-    float *rt, *rprobs, *gate, *d_gate, *drt, *wr_scratch;
-    int *assign, *perm, *inv, *off, *counts, *tile_expert, *ntiles, *bad, *chunk;
+    float *rt, *rprobs, *gate, *d_gate, *drt, *wr_scratch, *wrt;
+    int *assign, *perm, *inv, *off, *counts, *tile_info, *ntiles, *bad, *chunk;
     bf16 *Xp, *gp, *up, *ap, *yp, *dyp, *dgp, *dup, *dXp;
     size_t bytes;
 };
@@ -44,13 +44,14 @@ static Arena carve(void *base, int N, int D, int F, int E, int K)
     MEMBER(gate, float, KN);
     MEMBER(d_gate, float, KN);
     MEMBER(drt, float, (size_t)N * E);
-    MEMBER(wr_scratch, float, (size_t)((N + 255) / 256) * D * E);
+    MEMBER(wr_scratch, float, (size_t)192 * D * E);
+    MEMBER(wrt, float, (size_t)D * E);
     MEMBER(assign, int, KN);
     MEMBER(perm, int, R);
     MEMBER(inv, int, KN);
     MEMBER(off, int, E + 1);
     MEMBER(counts, int, E);
-    MEMBER(tile_expert, int, R / 128);
+    MEMBER(tile_info, int, R / 256 + E + 1);
     MEMBER(ntiles, int, 1);
     MEMBER(bad, int, 1);
     MEMBER(chunk, int, perm_scratch_ints(N, E, K, 1));
@@ -97,7 +98,7 @@ extern "C" void *qlmb_moe_arena_member(void *arena, int N, int D, int F, int E, 
     Arena a = carve(arena, N, D, F, E, K);
 #define NAMED(f) if (!strcmp(name, #f)) return (void *)a.f
     NAMED(rt); NAMED(rprobs); NAMED(gate); NAMED(d_gate); NAMED(drt); NAMED(assign); NAMED(perm); NAMED(inv);
-    NAMED(off); NAMED(counts); NAMED(tile_expert); NAMED(ntiles); NAMED(bad); NAMED(Xp); NAMED(gp); NAMED(up);
+    NAMED(off); NAMED(counts); NAMED(tile_info); NAMED(ntiles); NAMED(bad); NAMED(Xp); NAMED(gp); NAMED(up);
     NAMED(ap); NAMED(yp); NAMED(dyp); NAMED(dgp); NAMED(dup); NAMED(dXp);
 #undef NAMED
     return nullptr;
@@ -121,27 +122,27 @@ extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out,
     if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc; }
     // expert grouping, padded to 128-row tiles (cudalm.cu:4189)
     { ProfScope ps("perm_build", st);
-    if ((rc = perm_build(a.assign, N, E, K, 1, 128, a.perm, a.inv, a.off, a.counts, a.bad, a.tile_expert, a.ntiles, 128, a.chunk, st))) return rc; }
+    if ((rc = perm_build(a.assign, N, E, K, 1, 128, a.perm, a.inv, a.off, a.counts, a.bad, a.tile_info, a.ntiles, a.chunk, st))) return rc; }
     { ProfScope ps("gather_rows", st);
     if ((rc = gather_rows(a.Xp, f_norm, L->dtype, a.perm, a.off + E, R, N, D, st))) return rc; }
 
     // gate/up projections with SwiGLU in the epilogue (cudalm.cu:4211-4215)
     GemmLaunch g = {};
-    g.bmode = B_DEQ_MN; g.epi = EPI_SWIGLU; g.sched = SCHED_ROWS; g.bn = 256;
+    g.bmode = B_DEQ_MN; g.epi = EPI_SWIGLU; g.sched = SCHED_ROWS;
     g.a[0] = a.Xp; g.a_rows = R; g.a_cols = D;
     g.w[0] = L->w1_codes; g.w[1] = L->w3_codes; g.scales[0] = L->w1_scales; g.scales[1] = L->w3_scales;
     g.w_rows = D; g.w_cols = F; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
-    g.tile_expert = a.tile_expert; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 128;
+    g.tile_info = a.tile_info; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 256 + E / 2 + 1;
     g.gp = a.gp; g.up = a.up; g.ap = a.ap; g.ldo = F; g.name = "gemm_gate_up_swiglu";
     if ((rc = gemm_launch(g, st))) return rc;
 
     // down projection (cudalm.cu:4224-4225)
     GemmLaunch h = {};
-    h.bmode = B_DEQ_MN; h.epi = EPI_STORE; h.sched = SCHED_ROWS; h.bn = (D % 256 == 0) ? 256 : 128;
+    h.bmode = B_DEQ_MN; h.epi = EPI_STORE; h.sched = SCHED_ROWS;
     h.a[0] = a.ap; h.a_rows = R; h.a_cols = F;
     h.w[0] = L->w2_codes; h.scales[0] = L->w2_scales;
     h.w_rows = F; h.w_cols = D; h.nseg = 1; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
-    h.tile_expert = a.tile_expert; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 128;
+    h.tile_info = a.tile_info; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 256 + E / 2 + 1;
     h.out = a.yp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_down";
     if ((rc = gemm_launch(h, st))) return rc;
 
@@ -169,21 +170,21 @@ extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfn
 
     // d(act) = dy W2^T with the SwiGLU backward in the epilogue (cudalm.cu:4336, 4339-4341)
     GemmLaunch g = {};
-    g.bmode = B_DEQ_K; g.epi = EPI_SWIGLU_BWD; g.sched = SCHED_ROWS; g.bn = (F % 256 == 0) ? 256 : 128;
+    g.bmode = B_DEQ_K; g.epi = EPI_SWIGLU_BWD; g.sched = SCHED_ROWS;
     g.a[0] = a.dyp; g.a_rows = R; g.a_cols = D;
     g.w[0] = L->w2_codes; g.scales[0] = L->w2_scales;
     g.w_rows = F; g.w_cols = D; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
-    g.tile_expert = a.tile_expert; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 128;
+    g.tile_info = a.tile_info; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 256 + E / 2 + 1;
     g.gp = a.gp; g.up = a.up; g.dgp = a.dgp; g.dup = a.dup; g.ldo = F; g.name = "gemm_dact_swiglu_bwd";
     if ((rc = gemm_launch(g, st))) return rc;
 
     // dXp = dg W1^T + du W3^T in one accumulator (cudalm.cu:4365-4366)
     GemmLaunch h = {};
-    h.bmode = B_DEQ_K; h.epi = EPI_STORE; h.sched = SCHED_ROWS; h.bn = (D % 256 == 0) ? 256 : 128;
+    h.bmode = B_DEQ_K; h.epi = EPI_STORE; h.sched = SCHED_ROWS;
     h.a[0] = a.dgp; h.a[1] = a.dup; h.a_rows = R; h.a_cols = F;
     h.w[0] = L->w1_codes; h.w[1] = L->w3_codes; h.scales[0] = L->w1_scales; h.scales[1] = L->w3_scales;
     h.w_rows = D; h.w_cols = F; h.nseg = 2; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
-    h.tile_expert = a.tile_expert; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 128;
+    h.tile_info = a.tile_info; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 256 + E / 2 + 1;
     h.out = a.dXp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_dx";
     if ((rc = gemm_launch(h, st))) return rc;
 
@@ -192,7 +193,7 @@ extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfn
         {a.Xp, D, a.dgp, F, dW1, "gemm_wgrad_w1"}, {a.Xp, D, a.dup, F, dW3, "gemm_wgrad_w3"}, {a.ap, F, a.dyp, D, dW2, "gemm_wgrad_w2"}};
     for (int i = 0; i < 3; i++) {
         GemmLaunch w = {};
-        w.bmode = AB_TMA_MN; w.epi = EPI_ACCUM; w.sched = SCHED_GROUPK; w.bn = (wg[i].Nb % 256 == 0) ? 256 : 128;
+        w.bmode = AB_TMA_MN; w.epi = EPI_ACCUM; w.sched = SCHED_GROUPK;
         w.a[0] = wg[i].A; w.a_rows = R; w.a_cols = wg[i].Ma;
         w.w[0] = wg[i].B; w.w_cols = wg[i].Nb;
         w.nseg = 1; w.M = wg[i].Ma; w.N = wg[i].Nb; w.E = E; w.off = a.off;
@@ -202,7 +203,7 @@ extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfn
 
     // router backward (cudalm.cu:4372-4391)
     { ProfScope ps("router_bwd", st); if ((rc = router_bwd(a.drt, a.rprobs, a.assign, a.d_gate, a.counts, N, E, K, L->aux, st))) return rc; }
-    { ProfScope ps("unpermute_rows", st); if ((rc = unpermute_rows(dfnorm, L->dtype, a.dXp, a.inv, a.drt, L->wr, N, D, E, K, st))) return rc; }
+    { ProfScope ps("unpermute_rows", st); if ((rc = unpermute_rows(dfnorm, L->dtype, a.dXp, a.inv, a.drt, L->wr, a.wrt, N, D, E, K, st))) return rc; }
     ProfScope ps("router_wgrad", st);
     return router_wgrad(dWr, f_norm, L->dtype, a.drt, a.wr_scratch, N, D, E, beta, st);
 }

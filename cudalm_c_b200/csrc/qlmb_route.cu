@@ -59,6 +59,48 @@ __global__ void __launch_bounds__(128) k_router_topk(const float *rt, float *rpr
     }
 }
 
+// Same arithmetic with one warp per token and lane = expert (E <= 32): the
+// maximum is order-free, the softmax sum is still taken in expert order (every
+// lane adds the 32 shuffled terms sequentially) and the K selection rounds are
+// warp arg-max reductions with the lowest index winning ties, so the outputs are
+// bit-identical to the thread-per-token form above.
+__global__ void __launch_bounds__(256) k_router_topk_warp(const float *rt, float *rprobs, int *assign,
+                                                          float *gate, int N, int E, int K,
+                                                          const float *bias, int bs)
+{
+    int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    const bool live = lane < E;
+    float lg = live ? rt[(size_t)n * E + lane] : 0.0f;
+    float top = (live && lg > -1e30f) ? lg : -1e30f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    float p = live ? exp_poly(lg - top) : 0.0f;
+    float sum = 0.0f;
+    for (int e = 0; e < E; e++) sum += __shfl_sync(0xffffffffu, p, e);
+    float inv = 1.0f / sum;
+    float pr = p * inv;
+    if (live) rprobs[(size_t)n * E + lane] = pr;
+    bool taken = false;
+    for (int k = 0; k < K; k++) {
+        float sc = pr + (bias && live ? bias[k * bs + lane] : 0.0f);
+        bool ok = live && !taken && (sc > -1e30f);
+        int idx = lane;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float osc = __shfl_xor_sync(0xffffffffu, sc, o);
+            int oidx = __shfl_xor_sync(0xffffffffu, idx, o);
+            bool ook = __shfl_xor_sync(0xffffffffu, (int)ok, o) != 0;
+            bool take = ook && (!ok || osc > sc || (osc == sc && oidx < idx));
+            if (take) { sc = osc; idx = oidx; ok = true; }
+        }
+        int pick = ok ? idx : k;                    // NaN scores: stay in range
+        float g = __shfl_sync(0xffffffffu, pr, pick);
+        if (lane == 0) { assign[(size_t)k * N + n] = pick; gate[(size_t)k * N + n] = g; }
+        taken = taken || (lane == pick);
+    }
+}
+
 // ------------------------------------------------------------- permutation
 // Stable counting sort in three launches (chunks of 1024 entries):
 //   hist    : per-chunk expert histogram
@@ -86,7 +128,7 @@ __global__ void __launch_bounds__(PERM_CHUNK) k_perm_hist(const int *asn, int le
 
 __global__ void __launch_bounds__(256) k_perm_scan(int *ch, int E, int NC, int pad, int plen,
                                                    int *off, int *counts, int *perm,
-                                                   int *tile_expert, int *ntiles, int tile_rows,
+                                                   int *tile_info, int *ntiles,
                                                    const int *bad, int *errword)
 {
     extern __shared__ int sm[];           // [E] totals then [E+1] padded offsets
@@ -121,12 +163,16 @@ __global__ void __launch_bounds__(256) k_perm_scan(int *ch, int E, int NC, int p
         for (int e = 0; e < E; e++)
             for (int p = po[e] + tot[e] + threadIdx.x; p < po[e + 1]; p += blockDim.x)
                 perm[(size_t)k * plen + p] = -1;
-    // row tiles of the grouped GEMMs (only meaningful when pad is a multiple of tile_rows)
-    if (tile_expert && k == 0) {
-        for (int e = 0; e < E; e++)
-            for (int t = po[e] / tile_rows + threadIdx.x; t < po[e + 1] / tile_rows; t += blockDim.x)
-                tile_expert[t] = e;
-        if (threadIdx.x == 0) *ntiles = po[E] / tile_rows;
+    // row tiles of the grouped GEMMs (pad must be 128): up to 256 rows of one expert each,
+    // packed as first row / 128 | expert << 20 | (halves - 1) << 30
+    if (tile_info && k == 0 && threadIdx.x == 0) {
+        int nt = 0;
+        for (int e = 0; e < E; e++) {
+            int n128 = (po[e + 1] - po[e]) / 128;
+            for (int i = 0; i < n128; i += 2)
+                tile_info[nt++] = (po[e] / 128 + i) | (e << 20) | ((i + 1 < n128 ? 1 : 0) << 30);
+        }
+        *ntiles = nt;
     }
 }
 
@@ -153,7 +199,7 @@ __global__ void __launch_bounds__(PERM_CHUNK) k_perm_scatter(const int *asn, int
 }
 
 int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
-               int *off, int *counts, int *bad_flag, int *tile_expert, int *ntiles, int tile_rows,
+               int *off, int *counts, int *bad_flag, int *tile_info, int *ntiles,
                int *chunk_scratch, cudaStream_t st)
 {
     int sorts = merged ? 1 : K, len = merged ? K * N : N;
@@ -162,7 +208,7 @@ int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int 
     QLMB_CUDA(cudaMemsetAsync(bad_flag, 0, sizeof(int), st));
     k_perm_hist<<<dim3(NC, sorts), PERM_CHUNK, E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, bad_flag);
     k_perm_scan<<<sorts, 256, (2 * E + 1) * sizeof(int), st>>>(chunk_scratch, E, NC, pad, plen, off, counts, perm,
-                                                             tile_expert, ntiles, tile_rows, bad_flag,
+                                                             tile_info, ntiles, bad_flag,
                                                              device_error_word());
     k_perm_scatter<<<dim3(NC, sorts), PERM_CHUNK, 32 * E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, perm,
                                                                             plen, inv);
@@ -180,7 +226,8 @@ size_t perm_scratch_ints(int N, int E, int K, int merged)
 int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N, int E, int K,
                 const float *bias, int bs, cudaStream_t st)
 {
-    k_router_topk<<<(N + 127) / 128, 128, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
+    if (E <= 32) k_router_topk_warp<<<(N + 7) / 8, 256, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
+    else k_router_topk<<<(N + 127) / 128, 128, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
     QLMB_LAUNCH_CHECK("k_router_topk");
     return QLMB_OK;
 }
@@ -208,6 +255,6 @@ extern "C" int qlmb_perm_build(const int *assign, int N, int E, int K, int merge
         QLMB_CUDA(cudaMalloc(&g_perm_scratch[dev], need * sizeof(int)));
         g_perm_cap[dev] = need;
     }
-    return perm_build(assign, N, E, K, merged, pad, perm, inv, off, counts, bad_flag, nullptr, nullptr, 128,
+    return perm_build(assign, N, E, K, merged, pad, perm, inv, off, counts, bad_flag, nullptr, nullptr,
                       g_perm_scratch[dev], as_stream(stream));
 }

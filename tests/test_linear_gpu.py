@@ -138,3 +138,35 @@ def test_empty_and_unsupported(cuda):
     with pytest.raises(q.QlmbError):               # K not a multiple of the scale group
         linear.linear_fwd(torch.zeros(4, 96, device=cuda), Q.d, Q.s, KN, 128)
     q.check(q.lib().qlmb_check_device(None))
+
+
+@pytest.mark.parametrize("B", [1, 8, 64])
+def test_gemv_decode(cuda, oracle, B):
+    """Decode path (M = live slots <= 64): fp32 accumulation of exact dequantised
+    weights, so the result agrees with the fp32 reference to round-off (1e-5)."""
+    from cudalm_c_b200 import linear
+    from cudalm_c_b200._lib import KN, NK
+    for K, N in ((768, 1536), (1536, 768), (768, 16384)):
+        for lay in (KN, NK):
+            Q, W = quantise(cuda, K, N, 5) if lay == KN else quantise(cuda, N, K, 5)
+            Wm = W if lay == KN else W.T
+            for dt in (torch.float32, torch.bfloat16):
+                X = torch.randn(B, K, device=cuda).to(dt)
+                Y = linear.gemv_decode(X, Q.d, Q.s, lay, N)
+                ref = X.float() @ Wm
+                assert rel(Y, ref) < (1e-5 if dt == torch.float32 else 8e-3), (K, N, lay, dt)
+                assert torch.equal(Y, linear.gemv_decode(X, Q.d, Q.s, lay, N))      # deterministic
+    # oracle on one case
+    Q, W = quantise(cuda, 256, 384, 6)
+    X = torch.randn(B, 256, device=cuda)
+    Yo = oracle.linear_fwd(X.cpu().numpy(), Q.d.cpu().numpy(), Q.s.cpu().numpy(), 0, 384)
+    assert rel(linear.gemv_decode(X, Q.d, Q.s, KN, 384), dev(Yo, cuda)) < 1e-5
+
+
+def test_gemv_rejects_more_than_64_slots(cuda):
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import linear
+    from cudalm_c_b200._lib import KN
+    Q, W = quantise(cuda, 128, 128, 9)
+    with pytest.raises(q.QlmbError):
+        linear.gemv_decode(torch.zeros(65, 128, device=cuda), Q.d, Q.s, KN, 128)
