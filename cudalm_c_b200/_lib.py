@@ -53,6 +53,12 @@ PROTOTYPES = {
     "qlmb_moe_arena_member": (vp, [vp, ci, ci, ci, ci, ci, C.c_char_p]),
     "qlmb_moe_forward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
     "qlmb_moe_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, vp, vp, vp, cf, vp]),
+    "qlmb_moe_route": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp]),
+    "qlmb_moe_experts_forward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, ci, vp]),
+    "qlmb_moe_combine": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
+    "qlmb_moe_dgate": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
+    "qlmb_moe_experts_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, ci, vp, vp, vp, cf, vp]),
+    "qlmb_moe_route_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, cf, vp]),
 }
 
 _lib = None

@@ -144,9 +144,9 @@ int router_logits(float *rt, const void *X, int x_dtype, const float *Wr, int N,
 // ------------------------------------------------------------------ gather
 // One warp per permuted row, 16-byte chunks (reference k_gather_bf, cudalm.cu:3892).
 __global__ void __launch_bounds__(256) k_gather_rows(bf16 *Xp, const void *src, int dtype,
-                                                     const int *perm, const int *nrows_dev, int N, int D)
+                                                     const int *perm, const int *nrows_dev, int nrows_host, int N, int D)
 {
-    int rows = *nrows_dev;
+    int rows = nrows_dev ? *nrows_dev : nrows_host;
     int lane = threadIdx.x & 31;
     for (int j = blockIdx.x * 8 + (threadIdx.x >> 5); j < rows; j += gridDim.x * 8) {
         int np = perm[j];
@@ -175,7 +175,7 @@ int gather_rows(bf16 *Xp, const void *src, int dtype, const int *perm, const int
     int blocks = (max_rows + 7) / 8;
     int cap = sm_count() * 8;
     if (blocks > cap) blocks = cap;
-    k_gather_rows<<<blocks, 256, 0, st>>>(Xp, src, dtype, perm, nrows_dev, N, D);
+    k_gather_rows<<<blocks, 256, 0, st>>>(Xp, src, dtype, perm, nrows_dev, max_rows, N, D);
     QLMB_LAUNCH_CHECK("k_gather_rows");
     return QLMB_OK;
 }
@@ -218,9 +218,9 @@ int combine_rows(void *out, const void *f_in, int dtype, const bf16 *yp, const i
 // nothing to the weight gradients (reference k_moe_dgate4, cudalm.cu:2569-2584).
 __global__ void __launch_bounds__(256) k_dgate_rows(bf16 *dyp, float *d_gate, const void *dout, int dtype,
                                                     const bf16 *yp, const int *perm, const float *gate,
-                                                    const int *nrows_dev, int N, int D)
+                                                    const int *nrows_dev, int nrows_host, int N, int D)
 {
-    int rows = *nrows_dev;
+    int rows = nrows_dev ? *nrows_dev : nrows_host;
     int lane = threadIdx.x & 31;
     for (int j = blockIdx.x * 8 + (threadIdx.x >> 5); j < rows; j += gridDim.x * 8) {
         int np = perm[j];
@@ -251,7 +251,7 @@ int dgate_rows(bf16 *dyp, float *d_gate, const void *dout, int dtype, const bf16
     int blocks = (max_rows + 7) / 8;
     int cap = sm_count() * 8;
     if (blocks > cap) blocks = cap;
-    k_dgate_rows<<<blocks, 256, 0, st>>>(dyp, d_gate, dout, dtype, yp, perm, gate, nrows_dev, N, D);
+    k_dgate_rows<<<blocks, 256, 0, st>>>(dyp, d_gate, dout, dtype, yp, perm, gate, nrows_dev, max_rows, N, D);
     QLMB_LAUNCH_CHECK("k_dgate_rows");
     return QLMB_OK;
 }

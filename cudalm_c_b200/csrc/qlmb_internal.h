@@ -21,7 +21,8 @@ int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int 
 // ---- row kernels (qlmb_dispatch.cu) ----
 int router_logits(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E,
                   cudaStream_t st);
-// Xp[j,:] = src[perm[j] % N,:] as bf16 (zero rows where perm[j] < 0), rows = *nrows_dev
+// Xp[j,:] = src[perm[j] % N,:] as bf16 (zero rows where perm[j] < 0); rows = *nrows_dev, or
+// max_rows when nrows_dev is NULL
 int gather_rows(bf16 *Xp, const void *src, int dtype, const int *perm, const int *nrows_dev,
                 int max_rows, int N, int D, cudaStream_t st);
 // out[n,:] = f_in[n,:] + sum_k gate[k*N+n] * yp[inv[k*N+n],:]   (k ascending)

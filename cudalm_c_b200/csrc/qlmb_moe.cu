@@ -69,15 +69,75 @@ static Arena carve(void *base, int N, int D, int F, int E, int K)
     return a;
 }
 
-static int check_layer(const char *who, const qlmb_moe_layer *L)
+static int check_layer(const char *who, const qlmb_moe_layer *L, bool need_experts = true, bool need_router = true)
 {
     QLMB_REQUIRE(L, "%s: NULL layer", who);
     QLMB_REQUIRE(L->N > 0 && L->E > 0 && L->E <= 256 && L->K > 0 && L->K <= 8 && L->K <= L->E, "%s: N=%d E=%d K=%d", who, L->N, L->E, L->K);
     QLMB_REQUIRE(L->dtype == QLMB_F32 || L->dtype == QLMB_BF16, "%s: dtype %d", who, L->dtype);
-    QLMB_REQUIRE(L->w1_codes && L->w3_codes && L->w2_codes && L->w1_scales && L->w3_scales && L->w2_scales && L->wr, "%s: NULL weight pointer", who);
+    QLMB_REQUIRE(!need_experts || (L->w1_codes && L->w3_codes && L->w2_codes && L->w1_scales && L->w3_scales && L->w2_scales), "%s: NULL expert weight pointer", who);
+    QLMB_REQUIRE(!need_router || L->wr, "%s: NULL router weight pointer", who);
     if ((L->D % 128) || (L->F % 128)) {
         set_error("%s: D=%d and F=%d must be multiples of 128", who, L->D, L->F);
         return QLMB_E_UNSUPPORTED;
+    }
+    return QLMB_OK;
+}
+
+// gate/up (+SwiGLU) and down projections over the expert-grouped rows of `a` (cudalm.cu:4211-4225)
+static int experts_forward_gemms(const qlmb_moe_layer *L, const Arena &a, cudaStream_t st)
+{
+    const int D = L->D, F = L->F, E = L->E, R = (int)a.rows_cap;
+    int rc;
+    GemmLaunch g = {};
+    g.bmode = B_DEQ_MN; g.epi = EPI_SWIGLU; g.sched = SCHED_ROWS;
+    g.a[0] = a.Xp; g.a_rows = R; g.a_cols = D;
+    g.w[0] = L->w1_codes; g.w[1] = L->w3_codes; g.scales[0] = L->w1_scales; g.scales[1] = L->w3_scales;
+    g.w_rows = D; g.w_cols = F; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
+    g.tile_info = a.tile_info; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 256 + E / 2 + 1;
+    g.gp = a.gp; g.up = a.up; g.ap = a.ap; g.ldo = F; g.name = "gemm_gate_up_swiglu";
+    if ((rc = gemm_launch(g, st))) return rc;
+    GemmLaunch h = {};
+    h.bmode = B_DEQ_MN; h.epi = EPI_STORE; h.sched = SCHED_ROWS;
+    h.a[0] = a.ap; h.a_rows = R; h.a_cols = F;
+    h.w[0] = L->w2_codes; h.scales[0] = L->w2_scales;
+    h.w_rows = F; h.w_cols = D; h.nseg = 1; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
+    h.tile_info = a.tile_info; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 256 + E / 2 + 1;
+    h.out = a.yp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_down";
+    return gemm_launch(h, st);
+}
+
+// d(act) with the SwiGLU backward, dXp, and the three weight gradients (cudalm.cu:4335-4366)
+static int experts_backward_gemms(const qlmb_moe_layer *L, const Arena &a, float *dW1, float *dW3, float *dW2,
+                                  float beta, cudaStream_t st)
+{
+    const int D = L->D, F = L->F, E = L->E, R = (int)a.rows_cap;
+    int rc;
+    GemmLaunch g = {};
+    g.bmode = B_DEQ_K; g.epi = EPI_SWIGLU_BWD; g.sched = SCHED_ROWS;
+    g.a[0] = a.dyp; g.a_rows = R; g.a_cols = D;
+    g.w[0] = L->w2_codes; g.scales[0] = L->w2_scales;
+    g.w_rows = F; g.w_cols = D; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
+    g.tile_info = a.tile_info; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 256 + E / 2 + 1;
+    g.gp = a.gp; g.up = a.up; g.dgp = a.dgp; g.dup = a.dup; g.ldo = F; g.name = "gemm_dact_swiglu_bwd";
+    if ((rc = gemm_launch(g, st))) return rc;
+    GemmLaunch h = {};
+    h.bmode = B_DEQ_K; h.epi = EPI_STORE; h.sched = SCHED_ROWS;
+    h.a[0] = a.dgp; h.a[1] = a.dup; h.a_rows = R; h.a_cols = F;
+    h.w[0] = L->w1_codes; h.w[1] = L->w3_codes; h.scales[0] = L->w1_scales; h.scales[1] = L->w3_scales;
+    h.w_rows = D; h.w_cols = F; h.nseg = 2; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
+    h.tile_info = a.tile_info; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 256 + E / 2 + 1;
+    h.out = a.dXp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_dx";
+    if ((rc = gemm_launch(h, st))) return rc;
+    struct { const bf16 *A; int Ma; const bf16 *B; int Nb; float *out; const char *name; } wg[3] = {
+        {a.Xp, D, a.dgp, F, dW1, "gemm_wgrad_w1"}, {a.Xp, D, a.dup, F, dW3, "gemm_wgrad_w3"}, {a.ap, F, a.dyp, D, dW2, "gemm_wgrad_w2"}};
+    for (int i = 0; i < 3; i++) {
+        GemmLaunch w = {};
+        w.bmode = AB_TMA_MN; w.epi = EPI_ACCUM; w.sched = SCHED_GROUPK;
+        w.a[0] = wg[i].A; w.a_rows = R; w.a_cols = wg[i].Ma;
+        w.w[0] = wg[i].B; w.w_cols = wg[i].Nb;
+        w.nseg = 1; w.M = wg[i].Ma; w.N = wg[i].Nb; w.E = E; w.off = a.off;
+        w.out = wg[i].out; w.out_dtype = QLMB_F32; w.ldo = wg[i].Nb; w.beta = beta; w.name = wg[i].name;
+        if ((rc = gemm_launch(w, st))) return rc;
     }
     return QLMB_OK;
 }
@@ -126,25 +186,8 @@ extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out,
     { ProfScope ps("gather_rows", st);
     if ((rc = gather_rows(a.Xp, f_norm, L->dtype, a.perm, a.off + E, R, N, D, st))) return rc; }
 
-    // gate/up projections with SwiGLU in the epilogue (cudalm.cu:4211-4215)
-    GemmLaunch g = {};
-    g.bmode = B_DEQ_MN; g.epi = EPI_SWIGLU; g.sched = SCHED_ROWS;
-    g.a[0] = a.Xp; g.a_rows = R; g.a_cols = D;
-    g.w[0] = L->w1_codes; g.w[1] = L->w3_codes; g.scales[0] = L->w1_scales; g.scales[1] = L->w3_scales;
-    g.w_rows = D; g.w_cols = F; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
-    g.tile_info = a.tile_info; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 256 + E / 2 + 1;
-    g.gp = a.gp; g.up = a.up; g.ap = a.ap; g.ldo = F; g.name = "gemm_gate_up_swiglu";
-    if ((rc = gemm_launch(g, st))) return rc;
-
-    // down projection (cudalm.cu:4224-4225)
-    GemmLaunch h = {};
-    h.bmode = B_DEQ_MN; h.epi = EPI_STORE; h.sched = SCHED_ROWS;
-    h.a[0] = a.ap; h.a_rows = R; h.a_cols = F;
-    h.w[0] = L->w2_codes; h.scales[0] = L->w2_scales;
-    h.w_rows = F; h.w_cols = D; h.nseg = 1; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
-    h.tile_info = a.tile_info; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 256 + E / 2 + 1;
-    h.out = a.yp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_down";
-    if ((rc = gemm_launch(h, st))) return rc;
+    // gate/up projections with SwiGLU in the epilogue, down projection (cudalm.cu:4211-4225)
+    if ((rc = experts_forward_gemms(L, a, st))) return rc;
 
     // residual + gated sum over the K passes (cudalm.cu:4177, 4227)
     ProfScope ps("combine_rows", st);
@@ -168,42 +211,128 @@ extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfn
     { ProfScope ps("dgate_rows", st);
     if ((rc = dgate_rows(a.dyp, a.d_gate, dout, L->dtype, a.yp, a.perm, a.gate, a.off + E, R, N, D, st))) return rc; }
 
-    // d(act) = dy W2^T with the SwiGLU backward in the epilogue (cudalm.cu:4336, 4339-4341)
-    GemmLaunch g = {};
-    g.bmode = B_DEQ_K; g.epi = EPI_SWIGLU_BWD; g.sched = SCHED_ROWS;
-    g.a[0] = a.dyp; g.a_rows = R; g.a_cols = D;
-    g.w[0] = L->w2_codes; g.scales[0] = L->w2_scales;
-    g.w_rows = F; g.w_cols = D; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
-    g.tile_info = a.tile_info; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 256 + E / 2 + 1;
-    g.gp = a.gp; g.up = a.up; g.dgp = a.dgp; g.dup = a.dup; g.ldo = F; g.name = "gemm_dact_swiglu_bwd";
-    if ((rc = gemm_launch(g, st))) return rc;
-
-    // dXp = dg W1^T + du W3^T in one accumulator (cudalm.cu:4365-4366)
-    GemmLaunch h = {};
-    h.bmode = B_DEQ_K; h.epi = EPI_STORE; h.sched = SCHED_ROWS;
-    h.a[0] = a.dgp; h.a[1] = a.dup; h.a_rows = R; h.a_cols = F;
-    h.w[0] = L->w1_codes; h.w[1] = L->w3_codes; h.scales[0] = L->w1_scales; h.scales[1] = L->w3_scales;
-    h.w_rows = D; h.w_cols = F; h.nseg = 2; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
-    h.tile_info = a.tile_info; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 256 + E / 2 + 1;
-    h.out = a.dXp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_dx";
-    if ((rc = gemm_launch(h, st))) return rc;
-
-    // weight gradients, contraction over each expert's rows (cudalm.cu:4335, 4363-4364)
-    struct { const bf16 *A; int Ma; const bf16 *B; int Nb; float *out; const char *name; } wg[3] = {
-        {a.Xp, D, a.dgp, F, dW1, "gemm_wgrad_w1"}, {a.Xp, D, a.dup, F, dW3, "gemm_wgrad_w3"}, {a.ap, F, a.dyp, D, dW2, "gemm_wgrad_w2"}};
-    for (int i = 0; i < 3; i++) {
-        GemmLaunch w = {};
-        w.bmode = AB_TMA_MN; w.epi = EPI_ACCUM; w.sched = SCHED_GROUPK;
-        w.a[0] = wg[i].A; w.a_rows = R; w.a_cols = wg[i].Ma;
-        w.w[0] = wg[i].B; w.w_cols = wg[i].Nb;
-        w.nseg = 1; w.M = wg[i].Ma; w.N = wg[i].Nb; w.E = E; w.off = a.off;
-        w.out = wg[i].out; w.out_dtype = QLMB_F32; w.ldo = wg[i].Nb; w.beta = beta; w.name = wg[i].name;
-        if ((rc = gemm_launch(w, st))) return rc;
-    }
+    // d(act), dXp and the weight gradients (cudalm.cu:4335-4366)
+    if ((rc = experts_backward_gemms(L, a, dW1, dW3, dW2, beta, st))) return rc;
 
     // router backward (cudalm.cu:4372-4391)
     { ProfScope ps("router_bwd", st); if ((rc = router_bwd(a.drt, a.rprobs, a.assign, a.d_gate, a.counts, N, E, K, L->aux, st))) return rc; }
     { ProfScope ps("unpermute_rows", st); if ((rc = unpermute_rows(dfnorm, L->dtype, a.dXp, a.inv, a.drt, L->wr, a.wrt, N, D, E, K, st))) return rc; }
     ProfScope ps("router_wgrad", st);
     return router_wgrad(dWr, f_norm, L->dtype, a.drt, a.wr_scratch, N, D, E, beta, st);
+}
+
+// ===================================================================== expert parallelism
+// The same layer cut at the two places where rows cross GPUs.  The home rank of a token
+// routes it and packs its K copies into expert order (compact, no filler rows) for the
+// dispatch all-to-all; the rank that owns an expert runs the FFN on whatever rows arrive,
+// tagged with their local expert index; the home rank combines what comes back.  The
+// exchanges themselves (NCCL all-to-all) are done by the caller between these calls.
+
+extern "C" int qlmb_moe_route(const qlmb_moe_layer *L, void *arena, void *Xs, const void *f_norm, void *stream)
+{
+    int rc = check_layer("qlmb_moe_route", L, false, true);
+    if (rc) return rc;
+    QLMB_REQUIRE(arena && Xs && f_norm, "qlmb_moe_route: NULL argument");
+    const int N = L->N, D = L->D, F = L->F, E = L->E, K = L->K;
+    Arena a = carve(arena, N, D, F, E, K);
+    cudaStream_t st = as_stream(stream);
+    { ProfScope ps("router_logits", st); if ((rc = router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc; }
+    { ProfScope ps("router_topk", st); if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc; }
+    { ProfScope ps("perm_build", st);
+      if ((rc = perm_build(a.assign, N, E, K, 1, 1, a.perm, a.inv, a.off, a.counts, a.bad, nullptr, nullptr, a.chunk, st))) return rc; }
+    ProfScope ps("gather_rows", st);
+    return gather_rows((bf16 *)Xs, f_norm, L->dtype, a.perm, nullptr, K * N, N, D, st);
+}
+
+extern "C" int qlmb_moe_combine(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in, const void *Ys,
+                                void *stream)
+{
+    int rc = check_layer("qlmb_moe_combine", L, false, false);
+    if (rc) return rc;
+    QLMB_REQUIRE(arena && out && f_in && Ys, "qlmb_moe_combine: NULL argument");
+    Arena a = carve(arena, L->N, L->D, L->F, L->E, L->K);
+    ProfScope ps("combine_rows", as_stream(stream));
+    return combine_rows(out, f_in, L->dtype, (const bf16 *)Ys, a.inv, a.gate, L->N, L->D, L->K, as_stream(stream));
+}
+
+extern "C" int qlmb_moe_dgate(const qlmb_moe_layer *L, void *arena, void *dYs, const void *dout, const void *Ys,
+                              void *stream)
+{
+    int rc = check_layer("qlmb_moe_dgate", L, false, false);
+    if (rc) return rc;
+    QLMB_REQUIRE(arena && dYs && dout && Ys, "qlmb_moe_dgate: NULL argument");
+    Arena a = carve(arena, L->N, L->D, L->F, L->E, L->K);
+    ProfScope ps("dgate_rows", as_stream(stream));
+    return dgate_rows((bf16 *)dYs, a.d_gate, dout, L->dtype, (const bf16 *)Ys, a.perm, a.gate, nullptr, L->K * L->N,
+                      L->N, L->D, as_stream(stream));
+}
+
+extern "C" int qlmb_moe_route_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const void *dXs,
+                                       const void *f_norm, float *dWr, float beta, void *stream)
+{
+    int rc = check_layer("qlmb_moe_route_backward", L, false, true);
+    if (rc) return rc;
+    QLMB_REQUIRE(arena && dfnorm && dXs && f_norm && dWr, "qlmb_moe_route_backward: NULL argument");
+    QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_moe_route_backward: beta %g", beta);
+    const int N = L->N, D = L->D, E = L->E, K = L->K;
+    Arena a = carve(arena, N, D, L->F, E, K);
+    cudaStream_t st = as_stream(stream);
+    { ProfScope ps("router_bwd", st); if ((rc = router_bwd(a.drt, a.rprobs, a.assign, a.d_gate, a.counts, N, E, K, L->aux, st))) return rc; }
+    { ProfScope ps("unpermute_rows", st); if ((rc = unpermute_rows(dfnorm, L->dtype, (const bf16 *)dXs, a.inv, a.drt, L->wr, a.wrt, N, D, E, K, st))) return rc; }
+    ProfScope ps("router_wgrad", st);
+    return router_wgrad(dWr, f_norm, L->dtype, a.drt, a.wr_scratch, N, D, E, beta, st);
+}
+
+// Expert side.  L describes the experts held by this rank (E = local experts, K is ignored,
+// N = row capacity of `earena`, which was sized with qlmb_moe_arena_bytes(N, D, F, E, 1)).
+// X[R][D] (bf16) are the received rows in arrival order, expert_of_row[R] their local expert
+// index; Y[R][D] receives the FFN output of every row, in the same order.
+extern "C" int qlmb_moe_experts_forward(const qlmb_moe_layer *L, void *earena, void *Y, const void *X,
+                                        const int *expert_of_row, int R, void *stream)
+{
+    int rc = check_layer("qlmb_moe_experts_forward", L, true, false);
+    if (rc) return rc;
+    QLMB_REQUIRE(earena && R >= 0 && R <= L->N, "qlmb_moe_experts_forward: %d rows exceed the arena capacity %d", R, L->N);
+    if (R == 0) return QLMB_OK;
+    QLMB_REQUIRE(Y && X && expert_of_row, "qlmb_moe_experts_forward: NULL argument");
+    const int D = L->D, E = L->E;
+    Arena a = carve(earena, L->N, D, L->F, E, 1);
+    cudaStream_t st = as_stream(stream);
+    { ProfScope ps("perm_build", st);
+      if ((rc = perm_build(expert_of_row, R, E, 1, 1, 128, a.perm, a.inv, a.off, a.counts, a.bad, a.tile_info, a.ntiles, a.chunk, st))) return rc; }
+    { ProfScope ps("gather_rows", st);
+      if ((rc = gather_rows(a.Xp, X, QLMB_BF16, a.perm, a.off + E, (int)a.rows_cap, R, D, st))) return rc; }
+    if ((rc = experts_forward_gemms(L, a, st))) return rc;
+    ProfScope ps("gather_rows", st);
+    return gather_rows((bf16 *)Y, a.yp, QLMB_BF16, a.inv, nullptr, R, (int)a.rows_cap, D, st);
+}
+
+// dY[R][D] (bf16): gradients of the rows' outputs, in arrival order (gate already applied by
+// the home rank).  dX[R][D] receives the gradients of the rows' inputs; the weight gradients
+// of the local experts are added into (beta = 1) or written to (beta = 0) dW1/dW3/dW2.
+extern "C" int qlmb_moe_experts_backward(const qlmb_moe_layer *L, void *earena, void *dX, const void *dY, int R,
+                                         float *dW1, float *dW3, float *dW2, float beta, void *stream)
+{
+    int rc = check_layer("qlmb_moe_experts_backward", L, true, false);
+    if (rc) return rc;
+    QLMB_REQUIRE(earena && dW1 && dW3 && dW2 && R >= 0 && R <= L->N, "qlmb_moe_experts_backward: bad argument");
+    QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_moe_experts_backward: beta %g", beta);
+    QLMB_REQUIRE(R == 0 || (dX && dY), "qlmb_moe_experts_backward: NULL argument");
+    const int D = L->D, E = L->E;
+    Arena a = carve(earena, L->N, D, L->F, E, 1);
+    cudaStream_t st = as_stream(stream);
+    if (R == 0) {
+        // no rows arrived: the permutation of the forward holds zero rows per expert
+        if (beta == 0.0f) {
+            QLMB_CUDA(cudaMemsetAsync(dW1, 0, (size_t)E * D * L->F * sizeof(float), st));
+            QLMB_CUDA(cudaMemsetAsync(dW3, 0, (size_t)E * D * L->F * sizeof(float), st));
+            QLMB_CUDA(cudaMemsetAsync(dW2, 0, (size_t)E * D * L->F * sizeof(float), st));
+        }
+        return QLMB_OK;
+    }
+    { ProfScope ps("gather_rows", st);
+      if ((rc = gather_rows(a.dyp, dY, QLMB_BF16, a.perm, a.off + E, (int)a.rows_cap, R, D, st))) return rc; }
+    if ((rc = experts_backward_gemms(L, a, dW1, dW3, dW2, beta, st))) return rc;
+    ProfScope ps("gather_rows", st);
+    return gather_rows((bf16 *)dX, a.dXp, QLMB_BF16, a.inv, nullptr, R, (int)a.rows_cap, D, st);
 }

@@ -202,6 +202,29 @@ int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const 
                       const void *f_norm, float *dW1, float *dW3, float *dW2, float *dWr,
                       float beta, void *stream);
 
+/* ----------------------------------------------------- expert parallelism (new)
+ * The reference runs on one GPU.  These six calls are moe_forward / moe_backward
+ * (cudalm.cu:4151-4393) cut where rows cross GPUs when the experts are sharded:
+ * the home rank of a token routes and packs (route), the expert's rank computes
+ * (experts_forward / experts_backward) and the home rank finishes (combine,
+ * dgate, route_backward).  The caller moves the packed rows between ranks
+ * (all-to-all) between the calls.  Packed rows are bf16 [K*N][D], grouped by
+ * global expert index in stable order, no filler rows; the number of rows per
+ * expert is arena member "counts".  qlmb_moe_route needs only L->wr (+bias);
+ * the experts_* calls need only the expert weights, with L->E = experts held by
+ * the rank, L->N = row capacity of `earena` = qlmb_moe_arena_bytes(N,D,F,E,1). */
+int qlmb_moe_route(const qlmb_moe_layer *L, void *arena, void *Xs, const void *f_norm, void *stream);
+int qlmb_moe_experts_forward(const qlmb_moe_layer *L, void *earena, void *Y, const void *X,
+                             const int *expert_of_row, int R, void *stream);
+int qlmb_moe_combine(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in, const void *Ys,
+                     void *stream);
+int qlmb_moe_dgate(const qlmb_moe_layer *L, void *arena, void *dYs, const void *dout, const void *Ys,
+                   void *stream);
+int qlmb_moe_experts_backward(const qlmb_moe_layer *L, void *earena, void *dX, const void *dY, int R,
+                              float *dW1, float *dW3, float *dW2, float beta, void *stream);
+int qlmb_moe_route_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const void *dXs,
+                            const void *f_norm, float *dWr, float beta, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
