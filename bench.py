@@ -45,34 +45,47 @@ def peaks():
 
 
 class ClockSampler(threading.Thread):
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons while the timed region runs (NVML reads, ~1 ms apart;
+    nvidia-smi as the fallback when the NVML binding is missing)."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index):
         super().__init__(daemon=True)
-        self.index, self.rows, self.stop_flag = index, [], False
+        self.index, self.mhz, self.max_mhz, self.mask, self.stop_flag, self.active = index, [], None, 0, False, False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
 
     def run(self):
-        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         while not self.stop_flag:
+            if not self.active:
+                time.sleep(0.0005)
+                continue
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([x.strip() for x in out.split(",")])
+                if self.nv is not None:
+                    self.mhz.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                    self.mask |= int(self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                else:
+                    out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=clocks.sm,clocks.max.sm",
+                                          "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                    a, b = [int(x) for x in out.strip().split(",")]
+                    self.mhz.append(a); self.max_mhz = b
             except Exception:
                 pass
-            time.sleep(0.1)
+            time.sleep(0.001)
 
     def summary(self):
-        if not self.rows:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unsampled"])
-        mhz = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
-        return dict(sm_mhz=mhz[len(mhz) // 2] if mhz else None,
-                    sm_max_mhz=int(self.rows[0][1]) if self.rows[0][1].isdigit() else None,
-                    reasons=reasons, samples=len(self.rows))
+        if not self.mhz:
+            return dict(sm_mhz=None, sm_max_mhz=self.max_mhz, reasons=["unsampled"])
+        m = sorted(self.mhz)
+        return dict(sm_mhz=m[len(m) // 2], sm_max_mhz=self.max_mhz, samples=len(m),
+                    reasons=[n for bit, n in self.REASONS.items() if self.mask & bit])
 
 
 def make_layer(dev, seed):
@@ -118,8 +131,9 @@ def run_ours(args):
         from cudalm_c_b200 import dist_moe
         runner = dist_moe.ExpertParallelLayer(c, dev, rank, world, seed=1234)
         step = runner.step
+        fn, fi, dout, out, dfn = runner.fn, runner.fi, runner.dout, runner.out, runner.dfn
         launches_per_step = runner.launches_per_step
-        parallelism = "ep%d" % world
+        parallelism = "ep%d (experts sharded, token all-to-all over NCCL)" % world
     else:
         L, (fn, fi, dout), grads = make_layer(dev, 1234)
         out = torch.empty_like(fi); dfn = torch.empty_like(fi)
@@ -144,13 +158,15 @@ def run_ours(args):
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.active = True
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
-    ms = e0.elapsed_time(e1) / args.steps
+    sampler.active = False
     sampler.stop_flag = True
+    ms = e0.elapsed_time(e1) / args.steps
     t = torch.tensor([ms], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -159,7 +175,7 @@ def run_ours(args):
 
     # per-kernel durations (events inside the library) over a few extra steps
     roof, kern = None, {}
-    if world == 1:
+    if True:
         q.check(lib.qlmb_prof_enable(1))
         reps = 5
         for _ in range(reps):
@@ -187,7 +203,7 @@ def run_ours(args):
 
     # end to end from pinned host buffers through the same C-ABI calls
     e2e = None
-    if world == 1:
+    if True:
         hin = [torch.empty(c["N"], c["D"], dtype=torch.bfloat16).pin_memory() for _ in range(3)]
         for h, d in zip(hin, (fn, fi, dout)):
             h.copy_(d)
@@ -199,18 +215,22 @@ def run_ours(args):
             hout[0].copy_(out, non_blocking=True); hout[1].copy_(dfn, non_blocking=True)
         for _ in range(3):
             step_e2e()
-        torch.cuda.synchronize()
+        barrier()
         w0 = time.perf_counter()
         e0.record()
         for _ in range(args.steps):
             step_e2e()
         e1.record()
-        torch.cuda.synchronize()
+        barrier()
         wall = (time.perf_counter() - w0) * 1e3 / args.steps
         ms_e = max(e0.elapsed_time(e1) / args.steps, wall)
+        if world > 1:
+            te = torch.tensor([ms_e], device=dev)
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            ms_e = float(te.item())
         bi = 3 * c["N"] * c["D"] * 2
         bo = 2 * c["N"] * c["D"] * 2
-        e2e = dict(value=round(flops_per_step(c) / (ms_e * 1e-3) / 1e12, 2), unit=UNIT, h2d_bytes_per_step=bi,
+        e2e = dict(value=round(world * flops_per_step(c) / (ms_e * 1e-3) / 1e12, 2), unit=UNIT, h2d_bytes_per_step=bi,
                    d2h_bytes_per_step=bo, ms_per_step=round(ms_e, 4))
     q.check(lib.qlmb_check_device(None))
 
@@ -289,6 +309,70 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_adamw(args):
+    """Secondary line (BASELINE config 3): integer AdamW over a flat 120 Mi-parameter 4-bit
+    span, one step per launch; metric = algorithmic bytes (11.15625 B/param, no fp32 view) / time."""
+    import numpy as np
+    import torch
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import qlm
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    n = args.params
+    pk = peaks()
+    Q = qlm.Qlm([(0, n)], n, dev)
+    gen = torch.Generator(device=dev); gen.manual_seed(3)
+    P = torch.randn(n, device=dev, generator=gen) * 0.02
+    Q.init_from(P, render=False)
+    del P
+    G = torch.randn(n, device=dev, generator=gen) * 1e-3
+    t = 0
+    for _ in range(max(args.warmup, 3)):
+        t += 1; Q.step(None, G, 3e-4, 0.9, 0.95, 0.1, t)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev.index); sampler.start(); sampler.active = True
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        t += 1; Q.step(None, G, 3e-4, 0.9, 0.95, 0.1, t)
+    e1.record(); torch.cuda.synchronize()
+    sampler.active = False; sampler.stop_flag = True
+    ms = e0.elapsed_time(e1) / args.steps
+    bpp = 11.15625
+    gbs = n * bpp / (ms * 1e-3) / 1e9
+    cpu = None
+    if not args.no_cpu:
+        from oracle import loader
+        ref = loader.reference(exact=False)
+        if ref is not None:
+            m = 128 * 131072
+            rng = np.random.default_rng(3)
+            sp, nq, ng = loader.make_spans([m])
+            W = rng.standard_normal(m, dtype=np.float32) * np.float32(0.02)
+            d = np.zeros(m // 2, np.int8); r = np.zeros(m, np.int8); sc = np.zeros(ng, np.float32)
+            ref.encode(W, d, r, sc, sp)
+            sp["sref"] = np.float32(sc.mean())
+            m8 = np.zeros(m, np.int8); v8 = np.zeros(m, np.uint8); m8s = np.zeros(ng, np.float32); v8s = np.zeros(ng, np.float32)
+            Gh = rng.standard_normal(m, dtype=np.float32) * np.float32(1e-3)
+            kw = dict(lr=3e-4, b1=0.9, b2=0.95, wd=0.1, inv_bc1=10.0, inv_sqrt_bc2=4.47)
+            ref.step(W, Gh, d, r, sc, m8, m8s, v8, v8s, sp, t=1, **kw)
+            w0 = time.perf_counter()
+            for i in range(5):
+                ref.step(W, Gh, d, r, sc, m8, m8s, v8, v8s, sp, t=2 + i, **kw)
+            dt = (time.perf_counter() - w0) / 5
+            cpu = dict(value=round(m * 15.15625 / dt / 1e9, 2), unit="GB/s", cores=ref.threads, kind="reference",
+                       sample="5 steps over a 16.8 M-parameter span (the CPU path also writes the fp32 view: 15.16 B/param), %.1f ms/step" % (dt * 1e3))
+    print(json.dumps(dict(metric="integer_adamw_gbs", value=round(gbs, 1), unit="GB/s", n_gpus=1, steps=args.steps,
+                          warmup=max(args.warmup, 3), ms_per_step=round(ms, 4), higher_is_better=True, scaling="weak",
+                          vs_baseline=None, dtype="int8/f32", data="synthetic",
+                          config=dict(workload="integer AdamW step, flat 4-bit span (BASELINE config 3)", params=n,
+                                      bytes_per_param=bpp, l2="1.4 GB of state per step exceeds the 126 MB L2"),
+                          roofline=dict(bound="hbm", kernel="k_step_fast", achieved=round(gbs, 1), peak=pk["hbm"], unit="GB/s",
+                                        frac=round(gbs / pk["hbm"], 4), traffic=None, peak_kind="copy bandwidth, of " + pk["src"]),
+                          cpu_baseline=cpu, gparams_per_s=round(n / (ms * 1e-3) / 1e9, 2), gpu_launches=args.steps,
+                          clocks=sampler.summary())))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -296,11 +380,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="moe", choices=["moe", "adamw"], help="moe = the headline line; adamw = secondary line for config 3")
+    ap.add_argument("--params", type=int, default=125829120, help="span size of --workload adamw")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the 8192 of config 2); smaller values are for profiler captures")
     args = ap.parse_args()
     if args.tokens > 0:
         CFG["N"] = args.tokens
-    if args.impl == "reference":
+    if args.workload == "adamw":
+        run_adamw(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -20,6 +20,8 @@
 // and every role leaves its loop, so a broken pipeline ends the kernel instead
 // of hanging the GPU.
 #include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
 #include <cuda_bf16.h>
 #include "qlmb_common.cuh"
 #include "qlmb_gemm.cuh"
@@ -250,6 +252,114 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams &p, int tile, i
 
 __device__ __forceinline__ float sigmoid_f(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
 
+// ------------------------------------------------------------------ fused epilogues
+// One warp, 32 tile rows (lane = row) x 128 accumulator columns starting at TMEM
+// address tbase; rbase = index of the warp's first row in the output, col0 = first
+// output column.  EPI_SWIGLU reads 64 gate columns at tbase and 64 up columns at
+// tbase + u_off and writes 64 activation columns.
+template <int EPI>
+__device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stage, int lane, uint32_t tbase,
+                                              long long rbase, long long col0, int valid, bool have_acc, uint32_t u_off)
+{
+    if (EPI == EPI_STORE || EPI == EPI_ACCUM) {
+#pragma unroll 1
+        for (int c = 0; c < 4; c++) {
+            uint32_t v[32];
+            tmem_ld32(tbase + c * 32, v);
+            tmem_ld_wait();
+            const long long o = rbase * p.ldo + col0 + c * 32;
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) f[i] = have_acc ? __uint_as_float(v[i]) : 0.0f;
+            if (p.out_dtype == QLMB_F32) {
+                if (p.resid) {
+                    uint4 r[8];
+                    warp_load_rows<8>(stage, r, lane, reinterpret_cast<const uint8_t *>((const float *)p.resid + o), p.ldo * 4, valid);
+                    const float *rf = reinterpret_cast<const float *>(r);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) f[i] += rf[i];
+                }
+                if (p.beta != 0.0f) {
+                    uint4 r[8];
+                    warp_load_rows<8>(stage, r, lane, reinterpret_cast<const uint8_t *>((const float *)p.out + o), p.ldo * 4, valid);
+                    const float *rf = reinterpret_cast<const float *>(r);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) f[i] += p.beta * rf[i];
+                }
+                warp_store_rows<8>(stage, reinterpret_cast<const uint4 *>(f), lane, reinterpret_cast<uint8_t *>((float *)p.out + o), p.ldo * 4, valid);
+            } else {
+                if (p.resid) {
+                    uint4 r[4];
+                    warp_load_rows<4>(stage, r, lane, reinterpret_cast<const uint8_t *>((const bf16 *)p.resid + o), p.ldo * 2, valid);
+                    const __nv_bfloat162 *hh = reinterpret_cast<const __nv_bfloat162 *>(r);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) { float2 g = __bfloat1622float2(hh[i]); f[2 * i] += g.x; f[2 * i + 1] += g.y; }
+                }
+                if (p.beta != 0.0f) {
+                    uint4 r[4];
+                    warp_load_rows<4>(stage, r, lane, reinterpret_cast<const uint8_t *>((const bf16 *)p.out + o), p.ldo * 2, valid);
+                    const __nv_bfloat162 *hh = reinterpret_cast<const __nv_bfloat162 *>(r);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) { float2 g = __bfloat1622float2(hh[i]); f[2 * i] += p.beta * g.x; f[2 * i + 1] += p.beta * g.y; }
+                }
+                uint4 w[4];
+                __nv_bfloat162 *hw = reinterpret_cast<__nv_bfloat162 *>(w);
+#pragma unroll
+                for (int i = 0; i < 16; i++) hw[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                warp_store_rows<4>(stage, w, lane, reinterpret_cast<uint8_t *>((bf16 *)p.out + o), p.ldo * 2, valid);
+            }
+        }
+    } else if (EPI == EPI_SWIGLU) {
+#pragma unroll 1
+        for (int c = 0; c < 4; c++) {
+            uint32_t g[16], u[16];
+            tmem_ld16(tbase + c * 16, g);
+            tmem_ld16(tbase + u_off + c * 16, u);
+            tmem_ld_wait();
+            const long long o = rbase * p.ldo + col0 + c * 16;
+            uint4 wa[2], wg[2], wu[2];
+            __nv_bfloat162 *ha = reinterpret_cast<__nv_bfloat162 *>(wa), *hg = reinterpret_cast<__nv_bfloat162 *>(wg),
+                           *hu = reinterpret_cast<__nv_bfloat162 *>(wu);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                float g0 = __uint_as_float(g[2 * k]), g1 = __uint_as_float(g[2 * k + 1]);
+                float u0 = __uint_as_float(u[2 * k]), u1 = __uint_as_float(u[2 * k + 1]);
+                ha[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
+                hg[k] = __floats2bfloat162_rn(g0, g1);
+                hu[k] = __floats2bfloat162_rn(u0, u1);
+            }
+            warp_store_rows<2>(stage, wa, lane, reinterpret_cast<uint8_t *>(p.ap + o), p.ldo * 2, valid);
+            warp_store_rows<2>(stage, wg, lane, reinterpret_cast<uint8_t *>(p.gp + o), p.ldo * 2, valid);
+            warp_store_rows<2>(stage, wu, lane, reinterpret_cast<uint8_t *>(p.up + o), p.ldo * 2, valid);
+        }
+    } else {   // EPI_SWIGLU_BWD: accumulator = d(act); dg = da*u*silu'(g), du = da*silu(g)
+#pragma unroll 1
+        for (int c = 0; c < 8; c++) {
+            uint32_t v[16];
+            tmem_ld16(tbase + c * 16, v);
+            const long long o = rbase * p.ldo + col0 + c * 16;
+            uint4 rg[2], ru[2], wdg[2], wdu[2];
+            warp_load_rows<2>(stage, rg, lane, reinterpret_cast<const uint8_t *>(p.gp + o), p.ldo * 2, valid);
+            warp_load_rows<2>(stage, ru, lane, reinterpret_cast<const uint8_t *>(p.up + o), p.ldo * 2, valid);
+            tmem_ld_wait();
+            const __nv_bfloat162 *hg = reinterpret_cast<const __nv_bfloat162 *>(rg), *hu = reinterpret_cast<const __nv_bfloat162 *>(ru);
+            __nv_bfloat162 *hdg = reinterpret_cast<__nv_bfloat162 *>(wdg), *hdu = reinterpret_cast<__nv_bfloat162 *>(wdu);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                float2 gg = __bfloat1622float2(hg[k]), uu = __bfloat1622float2(hu[k]);
+                float d0 = __uint_as_float(v[2 * k]), d1 = __uint_as_float(v[2 * k + 1]);
+                float s0 = sigmoid_f(gg.x), s1 = sigmoid_f(gg.y);
+                float dg0 = d0 * uu.x * (s0 + gg.x * s0 * (1.0f - s0)), dg1 = d1 * uu.y * (s1 + gg.y * s1 * (1.0f - s1));
+                float du0 = d0 * gg.x * s0, du1 = d1 * gg.y * s1;
+                hdg[k] = __floats2bfloat162_rn(dg0, dg1);
+                hdu[k] = __floats2bfloat162_rn(du0, du1);
+            }
+            warp_store_rows<2>(stage, wdg, lane, reinterpret_cast<uint8_t *>(p.dgp + o), p.ldo * 2, valid);
+            warp_store_rows<2>(stage, wdu, lane, reinterpret_cast<uint8_t *>(p.dup + o), p.ldo * 2, valid);
+        }
+    }
+}
+
 // ------------------------------------------------------------------ the kernel
 template <int BMODE, int EPI, int SCHED>
 __global__ void __launch_bounds__((BMODE == B_DEQ_MN || BMODE == B_DEQ_K) ? 576 : 320, 1)
@@ -431,105 +541,8 @@ k_gemm(const __grid_constant__ GemmParams p)
                 const bool have_acc = (SCHED != SCHED_GROUPK) || t.ksteps > 0;
                 int valid = 32;
                 if (SCHED != SCHED_ROWS) { long long left = (long long)p.M - row0; valid = left < 0 ? 0 : (left < 32 ? (int)left : 32); }
-                if (EPI == EPI_STORE || EPI == EPI_ACCUM) {
-                    const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
-#pragma unroll 1
-                    for (int c = 0; c < BN / 32; c++) {
-                        uint32_t v[32];
-                        tmem_ld32(tbase + c * 32, v);
-                        tmem_ld_wait();
-                        const long long o = rbase * p.ldo + (long long)t.n_t * BN + c * 32;
-                        float f[32];
-#pragma unroll
-                        for (int i = 0; i < 32; i++) f[i] = have_acc ? __uint_as_float(v[i]) : 0.0f;
-                        if (p.out_dtype == QLMB_F32) {
-                            if (p.resid) {
-                                uint4 r[8];
-                                warp_load_rows<8>(stage, r, lane, reinterpret_cast<const uint8_t *>((const float *)p.resid + o), p.ldo * 4, valid);
-                                const float *rf = reinterpret_cast<const float *>(r);
-#pragma unroll
-                                for (int i = 0; i < 32; i++) f[i] += rf[i];
-                            }
-                            if (p.beta != 0.0f) {
-                                uint4 r[8];
-                                warp_load_rows<8>(stage, r, lane, reinterpret_cast<const uint8_t *>((const float *)p.out + o), p.ldo * 4, valid);
-                                const float *rf = reinterpret_cast<const float *>(r);
-#pragma unroll
-                                for (int i = 0; i < 32; i++) f[i] += p.beta * rf[i];
-                            }
-                            warp_store_rows<8>(stage, reinterpret_cast<const uint4 *>(f), lane, reinterpret_cast<uint8_t *>((float *)p.out + o), p.ldo * 4, valid);
-                        } else {
-                            if (p.resid) {
-                                uint4 r[4];
-                                warp_load_rows<4>(stage, r, lane, reinterpret_cast<const uint8_t *>((const bf16 *)p.resid + o), p.ldo * 2, valid);
-                                const __nv_bfloat162 *hh = reinterpret_cast<const __nv_bfloat162 *>(r);
-#pragma unroll
-                                for (int i = 0; i < 16; i++) { float2 g = __bfloat1622float2(hh[i]); f[2 * i] += g.x; f[2 * i + 1] += g.y; }
-                            }
-                            if (p.beta != 0.0f) {
-                                uint4 r[4];
-                                warp_load_rows<4>(stage, r, lane, reinterpret_cast<const uint8_t *>((const bf16 *)p.out + o), p.ldo * 2, valid);
-                                const __nv_bfloat162 *hh = reinterpret_cast<const __nv_bfloat162 *>(r);
-#pragma unroll
-                                for (int i = 0; i < 16; i++) { float2 g = __bfloat1622float2(hh[i]); f[2 * i] += p.beta * g.x; f[2 * i + 1] += p.beta * g.y; }
-                            }
-                            uint4 w[4];
-                            __nv_bfloat162 *hw = reinterpret_cast<__nv_bfloat162 *>(w);
-#pragma unroll
-                            for (int i = 0; i < 16; i++) hw[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-                            warp_store_rows<4>(stage, w, lane, reinterpret_cast<uint8_t *>((bf16 *)p.out + o), p.ldo * 2, valid);
-                        }
-                    }
-                } else if (EPI == EPI_SWIGLU) {
-                    // accumulator columns [0,64) = gate pre-activation, [64,128) = up projection
-#pragma unroll 1
-                    for (int c = 0; c < 4; c++) {
-                        uint32_t g[16], u[16];
-                        tmem_ld16(tbase + c * 16, g);
-                        tmem_ld16(tbase + 64 + c * 16, u);
-                        tmem_ld_wait();
-                        const long long o = row0 * p.ldo + (long long)t.n_t * 64 + c * 16;
-                        uint4 wa[2], wg[2], wu[2];
-                        __nv_bfloat162 *ha = reinterpret_cast<__nv_bfloat162 *>(wa), *hg = reinterpret_cast<__nv_bfloat162 *>(wg),
-                                       *hu = reinterpret_cast<__nv_bfloat162 *>(wu);
-#pragma unroll
-                        for (int k = 0; k < 8; k++) {
-                            float g0 = __uint_as_float(g[2 * k]), g1 = __uint_as_float(g[2 * k + 1]);
-                            float u0 = __uint_as_float(u[2 * k]), u1 = __uint_as_float(u[2 * k + 1]);
-                            ha[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
-                            hg[k] = __floats2bfloat162_rn(g0, g1);
-                            hu[k] = __floats2bfloat162_rn(u0, u1);
-                        }
-                        warp_store_rows<2>(stage, wa, lane, reinterpret_cast<uint8_t *>(p.ap + o), p.ldo * 2, valid);
-                        warp_store_rows<2>(stage, wg, lane, reinterpret_cast<uint8_t *>(p.gp + o), p.ldo * 2, valid);
-                        warp_store_rows<2>(stage, wu, lane, reinterpret_cast<uint8_t *>(p.up + o), p.ldo * 2, valid);
-                    }
-                } else {   // EPI_SWIGLU_BWD: accumulator = d(act); dg = da*u*silu'(g), du = da*silu(g)
-#pragma unroll 1
-                    for (int c = 0; c < BN / 16; c++) {
-                        uint32_t v[16];
-                        tmem_ld16(tbase + c * 16, v);
-                        const long long o = row0 * p.ldo + (long long)t.n_t * BN + c * 16;
-                        uint4 rg[2], ru[2], wdg[2], wdu[2];
-                        warp_load_rows<2>(stage, rg, lane, reinterpret_cast<const uint8_t *>(p.gp + o), p.ldo * 2, valid);
-                        warp_load_rows<2>(stage, ru, lane, reinterpret_cast<const uint8_t *>(p.up + o), p.ldo * 2, valid);
-                        tmem_ld_wait();
-                        const __nv_bfloat162 *hg = reinterpret_cast<const __nv_bfloat162 *>(rg), *hu = reinterpret_cast<const __nv_bfloat162 *>(ru);
-                        __nv_bfloat162 *hdg = reinterpret_cast<__nv_bfloat162 *>(wdg), *hdu = reinterpret_cast<__nv_bfloat162 *>(wdu);
-#pragma unroll
-                        for (int k = 0; k < 8; k++) {
-                            float2 gg = __bfloat1622float2(hg[k]), uu = __bfloat1622float2(hu[k]);
-                            float d0 = __uint_as_float(v[2 * k]), d1 = __uint_as_float(v[2 * k + 1]);
-                            float s0 = sigmoid_f(gg.x), s1 = sigmoid_f(gg.y);
-                            float dg0 = d0 * uu.x * (s0 + gg.x * s0 * (1.0f - s0)), dg1 = d1 * uu.y * (s1 + gg.y * s1 * (1.0f - s1));
-                            float du0 = d0 * gg.x * s0, du1 = d1 * gg.y * s1;
-                            hdg[k] = __floats2bfloat162_rn(dg0, dg1);
-                            hdu[k] = __floats2bfloat162_rn(du0, du1);
-                        }
-                        warp_store_rows<2>(stage, wdg, lane, reinterpret_cast<uint8_t *>(p.dgp + o), p.ldo * 2, valid);
-                        warp_store_rows<2>(stage, wdu, lane, reinterpret_cast<uint8_t *>(p.dup + o), p.ldo * 2, valid);
-                    }
-                }
+                const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
+                epilogue_rows<EPI>(p, stage, lane, tbase, rbase, (long long)t.n_t * (EPI == EPI_SWIGLU ? BN / 2 : BN), valid, have_acc, BN / 2);
             }
             tc_fence_before();
             __syncwarp();
@@ -625,6 +638,12 @@ k_gemm(const __grid_constant__ GemmParams p)
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
+}  // namespace qlmb
+
+#include "qlmb_gemm_pair.cuh"
+
+namespace qlmb {
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -678,6 +697,45 @@ static int launch_inst(const GemmParams &p, int grid, cudaStream_t st)
     return QLMB_OK;
 }
 
+template <int BMODE, int EPI, int SCHED>
+static int launch_pair(const GemmParams &p, long long total, cudaStream_t st)
+{
+    constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
+    constexpr int NSA = DEQ ? 5 : 6;
+    constexpr size_t smem = 1024 + (size_t)NSA * (P_A_STAGE + P_B_STAGE) + (DEQ ? 4 * P_C_STAGE : 0) + EPI_WARPS * 4096 + 512;
+    // persistent kernel: every cluster must be resident at once, so the grid is the number of
+    // clusters the device can hold at the same time (asked once per kernel instance)
+    static int max_clusters = 0;
+    auto kfn = k_gemm_pair<BMODE, EPI, SCHED>;
+    if (!max_clusters) {
+        QLMB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(sm_count() & ~1)); cfg.blockDim = dim3(DEQ ? 576 : 320); cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        int n = 0;
+        QLMB_CUDA(cudaOccupancyMaxActiveClusters(&n, kfn, &cfg));
+        QLMB_REQUIRE(n > 0, "gemm: the device cannot hold a two-SM cluster of this kernel");
+        max_clusters = n;
+    }
+    long long clusters = total < max_clusters ? total : max_clusters;
+    kfn<<<(unsigned)(2 * clusters), DEQ ? 576 : 320, smem, st>>>(p);
+    QLMB_LAUNCH_CHECK("k_gemm_pair");
+    return QLMB_OK;
+}
+
+// The two-SM form needs whole 256-column tiles (128 activation columns with the SwiGLU
+// epilogue); QLMB_GEMM_PAIR=0 forces the one-SM form.
+static bool use_pair(const GemmLaunch &g)
+{
+    static int enabled = -1;
+    if (enabled < 0) { const char *e = getenv("QLMB_GEMM_PAIR"); enabled = (e && atoi(e) == 0) ? 0 : 1; }
+    if (!enabled) return false;
+    return g.epi == EPI_SWIGLU ? (g.N % 128 == 0) : (g.N % 256 == 0);
+}
+
 int gemm_launch(const GemmLaunch &g, cudaStream_t st)
 {
     int rc = load_encode();
@@ -685,11 +743,12 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
     const bool dual = g.epi == EPI_SWIGLU;
     QLMB_REQUIRE(g.N % (dual ? BN / 2 : BN) == 0, "gemm: N=%d is not a multiple of the %d-column tile", g.N, dual ? BN / 2 : BN);
     QLMB_REQUIRE(g.sched != SCHED_GROUPK || g.M % BM == 0, "gemm: grouped weight gradient needs M=%d to be a multiple of %d", g.M, BM);
+    const bool pair = use_pair(g);
     GemmParams p;
     memset(&p, 0, sizeof p);
     p.nseg = g.nseg; p.ksteps = g.ksteps; p.M = g.M; p.N = g.N; p.E = g.E;
     p.tiles_m = (g.M + MH * BM - 1) / (MH * BM);
-    p.tiles_n = dual ? g.N / (BN / 2) : g.N / BN;
+    p.tiles_n = pair ? (dual ? g.N / 128 : g.N / 256) : (dual ? g.N / (BN / 2) : g.N / BN);
     p.w_rows = g.w_rows; p.w_cols = g.w_cols;
     p.tile_info = g.tile_info; p.ntiles_dev = g.ntiles_dev; p.off = g.off;
     p.out = g.out; p.out_dtype = g.out_dtype; p.ldo = g.ldo; p.resid = g.resid; p.beta = g.beta;
@@ -716,7 +775,7 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
             rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, g.w_cols, wrows_total, (unsigned long long)g.w_cols * 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B);
         } else if (g.bmode == B_DEQ_MN) {
             QLMB_REQUIRE(g.w_cols % 128 == 0, "gemm: code matrix width %d is not a multiple of the 128-element group", g.w_cols);
-            rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w_cols / 2, wrows_total, g.w_cols / 2, dual ? BN / 4 : BN / 2, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+            rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w_cols / 2, wrows_total, g.w_cols / 2, (dual && !pair) ? BN / 4 : BN / 2, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
         } else {
             QLMB_REQUIRE(g.w_cols % 128 == 0, "gemm: code matrix width %d is not a multiple of the 128-element group", g.w_cols);
             rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w_cols / 2, wrows_total, g.w_cols / 2, 32, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -731,6 +790,18 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
     int grid = sm_count();
     if (total < grid) grid = (int)total;
     ProfScope prof(g.name ? g.name : "gemm", st);
+
+#define PAIR(BM_, EP_, SC_) if (pair && g.bmode == BM_ && g.epi == EP_ && g.sched == SC_) return launch_pair<BM_, EP_, SC_>(p, total, st)
+    PAIR(B_DEQ_MN, EPI_STORE, SCHED_DENSE);
+    PAIR(B_DEQ_K, EPI_STORE, SCHED_DENSE);
+    PAIR(AB_TMA_MN, EPI_ACCUM, SCHED_DENSE);
+    PAIR(B_TMA_K, EPI_STORE, SCHED_DENSE);
+    PAIR(B_DEQ_MN, EPI_SWIGLU, SCHED_ROWS);
+    PAIR(B_DEQ_MN, EPI_STORE, SCHED_ROWS);
+    PAIR(B_DEQ_K, EPI_SWIGLU_BWD, SCHED_ROWS);
+    PAIR(B_DEQ_K, EPI_STORE, SCHED_ROWS);
+    PAIR(AB_TMA_MN, EPI_ACCUM, SCHED_GROUPK);
+#undef PAIR
 
 #define INST(BM_, EP_, SC_) if (g.bmode == BM_ && g.epi == EP_ && g.sched == SC_) return launch_inst<BM_, EP_, SC_>(p, grid, st)
     // dense linears

@@ -1,0 +1,410 @@
+// Two-SM form of the GEMM engine (included by qlmb_gemm.cu).
+//
+// A cluster of two CTAs on neighbouring SMs computes a 256 x 256 tile with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and its own
+// 128 columns of B (expanding only that half of the weights), the leader CTA
+// issues one M=256 instruction per 16-deep step that reads both halves, and each
+// CTA's TMEM holds its 128 rows x 256 columns of the result.  Per SM and step the
+// tensor core therefore reads half as much shared memory and the dequant warps
+// expand half as many weights as in the one-SM form.
+//
+// Hand-shakes across the pair (all waits bounded, as everywhere in this file):
+//   peer_full[s]   leader   the peer's relay warp arrives when the peer's A and B
+//                           stage are complete (remote mbarrier arrive)
+//   empty_a/b[s]   both     released by tcgen05.commit from the leader, once to its
+//                           own barrier and once to the peer's (mapped address)
+//   tmem_full[a]   both     committed the same way after a tile's last step
+//   tmem_empty[a]  leader   8 local + 8 remote epilogue warps
+// No bulk copy in this file is a cluster-wide (multi-destination) copy.
+#pragma once
+
+namespace qlmb {
+
+constexpr int P_BN = 256;                 // accumulator columns of the pair tile
+constexpr int P_A_STAGE = BM * BK * 2;    // per CTA: 128 rows
+constexpr int P_B_STAGE = 128 * BK * 2;   // per CTA: 128 columns of B
+constexpr int P_C_STAGE = 128 * BK / 2;   // per CTA: codes of those columns
+
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+// (default semantics: a cluster-scope release here costs a full memory fence per call, which
+// throttled the relay to one stage per microsecond)
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr)
+{ asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory"); }
+__device__ __forceinline__ uint32_t mbar_try_cluster(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *errword, int site)
+{
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try_cluster(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    if (!*abort_flag) {
+        *abort_flag = 1;
+        if (errword && atomicCAS(errword, 0, 201) == 0) { errword[1] = site; errword[2] = (int)blockIdx.x; errword[3] = (int)parity; }
+    }
+    return false;
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols)
+{ asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory"); }
+__device__ __forceinline__ void tmem_relinquish2()
+{ asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols)
+{ asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory"); }
+// completion of all MMAs issued so far -> one arrival on the barrier at this cluster address
+__device__ __forceinline__ void tc_commit2(uint32_t cluster_bar)
+{ asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory"); }
+__device__ __forceinline__ void tc_mma2_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate),
+                   "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+
+// Pair tile: 256 rows starting at m0 (CTA r owns rows m0 + 128 r ...), 256 output columns
+// starting at n_t * 256 (CTA r expands columns + 128 r); with the SwiGLU epilogue the pair
+// tile is 128 gate + 128 up columns of the same 128 activation columns.
+template <int SCHED>
+__device__ __forceinline__ TileInfo decode_pair_tile(const GemmParams &p, int tile, int ntr)
+{
+    TileInfo t;
+    if (SCHED == SCHED_DENSE) {
+        t.m0 = (tile % p.tiles_m) * 256; t.n_t = tile / p.tiles_m; t.e = 0; t.ksteps = p.ksteps; t.row0 = 0;
+        t.halves = (t.m0 + BM < p.M) ? 2 : 1;
+    } else if (SCHED == SCHED_ROWS) {
+        int rt = tile % ntr;
+        int info = p.tile_info[rt];
+        t.m0 = (info & 0xFFFFF) * BM; t.e = (info >> 20) & 0x1FF; t.halves = ((info >> 30) & 1) + 1;
+        t.n_t = tile / ntr; t.ksteps = p.ksteps; t.row0 = 0;
+    } else {
+        int per = p.tiles_m * p.tiles_n;
+        t.e = tile / per;
+        int r = tile % per;
+        t.m0 = (r % p.tiles_m) * 256; t.n_t = r / p.tiles_m;
+        t.row0 = p.off[t.e];
+        t.ksteps = (p.off[t.e + 1] - p.off[t.e]) / BK;
+        t.halves = (t.m0 + BM < p.M) ? 2 : 1;
+    }
+    return t;
+}
+
+template <int BMODE, int EPI, int SCHED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((BMODE == B_DEQ_MN || BMODE == B_DEQ_K) ? 576 : 320, 1)
+k_gemm_pair(const __grid_constant__ GemmParams p)
+{
+    constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
+    constexpr bool DUAL = (EPI == EPI_SWIGLU);           // CTA 0 expands W1 (gate), CTA 1 expands W3 (up)
+    constexpr int NSA = DEQ ? 5 : 6, NSB = NSA, NSC = 4, NSP = 8;   // NSP > NSA: a slot is consumed before it is signalled again
+    constexpr uint32_t IDESC = make_idesc(256, P_BN, BMODE == AB_TMA_MN ? 1 : 0, (BMODE == B_DEQ_MN || BMODE == AB_TMA_MN) ? 1 : 0);
+    constexpr uint32_t TMEM_COLS = 2 * P_BN;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sA = smem;
+    uint8_t *sB = sA + NSA * P_A_STAGE;
+    uint8_t *sC = sB + NSB * P_B_STAGE;
+    uint8_t *sE = sC + (DEQ ? NSC * P_C_STAGE : 0);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sE + EPI_WARPS * 4096);
+    uint64_t *full_a = bars, *empty_a = full_a + NSA, *full_b = empty_a + NSA, *empty_b = full_b + NSB;
+    uint64_t *full_c = empty_b + NSB, *empty_c = full_c + NSC, *peer_full = empty_c + NSC;
+    uint64_t *tmem_full = peer_full + NSP, *tmem_empty = tmem_full + 2, *spare = tmem_empty + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(spare + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NSA; i++) { mbar_init(smem_u32(&full_a[i]), 1); mbar_init(smem_u32(&empty_a[i]), 1); }
+        for (int i = 0; i < NSB; i++) { mbar_init(smem_u32(&full_b[i]), DEQ ? DQ_WARPS : 1); mbar_init(smem_u32(&empty_b[i]), 1); }
+        for (int i = 0; i < NSC; i++) { mbar_init(smem_u32(&full_c[i]), 1); mbar_init(smem_u32(&empty_c[i]), DQ_WARPS); }
+        for (int i = 0; i < NSP; i++) mbar_init(smem_u32(&peer_full[i]), 1);
+        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&tmem_full[i]), 1); mbar_init(smem_u32(&tmem_empty[i]), 2 * EPI_WARPS); }
+        mbar_init(smem_u32(spare), 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc2(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish2(); }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int npairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
+    const int ntr = (SCHED == SCHED_ROWS) ? *p.ntiles_dev : 0;
+    const int total = (SCHED == SCHED_DENSE) ? p.tiles_m * p.tiles_n
+                    : (SCHED == SCHED_ROWS) ? ntr * p.tiles_n : p.E * p.tiles_m * p.tiles_n;
+    const int my_m = (int)rank * BM;                     // this CTA's row offset inside the pair tile
+    const int my_n = (int)rank * 128;                    // and its column offset
+
+    if (warp == 0) {
+        // =============================== TMA producer (both CTAs) ===============================
+        Ring ra = {0, 0}, rc = {0, 0};
+        bool ok = true;
+        for (int tile = pair; ok && tile < total; tile += npairs) {
+            TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
+            for (int seg = 0; ok && seg < p.nseg; seg++) {
+                for (int ks = 0; ks < t.ksteps; ks++) {
+                    ok = mbar_wait(smem_u32(&empty_a[ra.idx]), ra.phase ^ 1u, abort_flag, p.errword, 11);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        uint32_t bar = smem_u32(&full_a[ra.idx]);
+                        uint32_t dstA = smem_u32(sA + ra.idx * P_A_STAGE);
+                        uint32_t dstB = smem_u32(sB + ra.idx * P_B_STAGE);
+                        if (BMODE == AB_TMA_MN) {
+                            int row = t.row0 + ks * BK;
+                            mbar_expect_tx(bar, P_A_STAGE + P_B_STAGE);
+                            tma_load_2d(dstA, &p.a_map[0], bar, t.m0 + my_m, row);
+                            tma_load_2d(dstA + 8192, &p.a_map[0], bar, t.m0 + my_m + 64, row);
+                            tma_load_2d(dstB, &p.w_map[0], bar, t.n_t * P_BN + my_n, row);
+                            tma_load_2d(dstB + 8192, &p.w_map[0], bar, t.n_t * P_BN + my_n + 64, row);
+                        } else {
+                            mbar_expect_tx(bar, P_A_STAGE + (BMODE == B_TMA_K ? P_B_STAGE : 0));
+                            tma_load_2d(dstA, &p.a_map[seg], bar, ks * BK, t.m0 + my_m);
+                            if (BMODE == B_TMA_K) tma_load_2d(dstB, &p.w_map[seg], bar, ks * BK, t.n_t * P_BN + my_n);
+                        }
+                    }
+                    __syncwarp();
+                    ra.next(NSA);
+                    if (DEQ) {
+                        ok = mbar_wait(smem_u32(&empty_c[rc.idx]), rc.phase ^ 1u, abort_flag, p.errword, 12);
+                        if (!ok) break;
+                        if (lane == 0) {
+                            uint32_t bar = smem_u32(&full_c[rc.idx]);
+                            uint32_t dstC = smem_u32(sC + rc.idx * P_C_STAGE);
+                            mbar_expect_tx(bar, P_C_STAGE);
+                            if (BMODE == B_DEQ_MN) {
+                                int row = t.e * p.w_rows + ks * BK;
+                                if (DUAL) tma_load_2d(dstC, &p.w_map[rank], bar, t.n_t * 64, row);
+                                else tma_load_2d(dstC, &p.w_map[seg], bar, (t.n_t * P_BN + my_n) / 2, row);
+                            } else {
+                                tma_load_2d(dstC, &p.w_map[seg], bar, ks * (BK / 2), t.e * p.w_rows + t.n_t * P_BN + my_n);
+                            }
+                        }
+                        __syncwarp();
+                        rc.next(NSC);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        Ring ra = {0, 0}, rb = {0, 0}, rp = {0, 0};
+        bool ok = true;
+        if (leader) {
+            // =============================== MMA issuer (leader CTA) ===============================
+            int it = 0;
+            for (int tile = pair; ok && tile < total; tile += npairs, it++) {
+                TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
+                const int acc = it & 1;
+                ok = mbar_wait_cluster(smem_u32(&tmem_empty[acc]), (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag, p.errword, 13);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)acc * P_BN;
+                uint32_t accumulate = 0;
+                for (int seg = 0; ok && seg < p.nseg; seg++) {
+                    for (int ks = 0; ks < t.ksteps; ks++) {
+                        ok = mbar_wait(smem_u32(&full_a[ra.idx]), ra.phase, abort_flag, p.errword, 14);
+                        if (!ok) break;
+                        const int sb = DEQ ? rb.idx : ra.idx;
+                        if (DEQ) {
+                            ok = mbar_wait(smem_u32(&full_b[rb.idx]), rb.phase, abort_flag, p.errword, 15);
+                            if (!ok) break;
+                        }
+                        ok = mbar_wait_cluster(smem_u32(&peer_full[rp.idx]), rp.phase, abort_flag, p.errword, 16);
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (lane == 0) {
+                            const uint32_t a0 = smem_u32(sA + ra.idx * P_A_STAGE);
+                            const uint32_t b0 = smem_u32(sB + sb * P_B_STAGE);
+#pragma unroll
+                            for (int k16 = 0; k16 < BK / 16; k16++) {
+                                uint64_t ad = (BMODE == AB_TMA_MN) ? make_desc(a0 + k16 * 2048, 8192, 1024) : make_desc(a0 + k16 * 32, 16, 1024);
+                                uint64_t bd = (BMODE == B_DEQ_MN || BMODE == AB_TMA_MN) ? make_desc(b0 + k16 * 2048, 8192, 1024)
+                                                                                        : make_desc(b0 + k16 * 32, 16, 1024);
+                                tc_mma2_bf16(tmem_d, ad, bd, IDESC, accumulate);
+                                accumulate = 1;
+                            }
+                            const uint32_t ea = smem_u32(&empty_a[ra.idx]);
+                            tc_commit2(ea);
+                            tc_commit2(map_to_cta(ea, 1));
+                            if (DEQ) {
+                                const uint32_t eb = smem_u32(&empty_b[rb.idx]);
+                                tc_commit2(eb);
+                                tc_commit2(map_to_cta(eb, 1));
+                            }
+                        }
+                        __syncwarp();
+                        accumulate = 1;
+                        ra.next(NSA);
+                        if (DEQ) rb.next(NSB);
+                        rp.next(NSP);
+                    }
+                }
+                if (ok) {
+                    if (lane == 0) {
+                        const uint32_t tf = smem_u32(&tmem_full[acc]);
+                        tc_commit2(tf);
+                        tc_commit2(map_to_cta(tf, 1));
+                    }
+                    __syncwarp();
+                }
+            }
+            if (*abort_flag) {
+                if (lane == 0) tc_commit2(smem_u32(spare));
+                __syncwarp();
+                for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(smem_u32(spare), 0); i++) {}
+            }
+        } else {
+            // =============================== relay (peer CTA) ===============================
+            // tells the leader when this CTA's halves of a stage are complete
+            for (int tile = pair; ok && tile < total; tile += npairs) {
+                TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
+                for (int seg = 0; ok && seg < p.nseg; seg++) {
+                    for (int ks = 0; ks < t.ksteps; ks++) {
+                        ok = mbar_wait(smem_u32(&full_a[ra.idx]), ra.phase, abort_flag, p.errword, 17);
+                        if (!ok) break;
+                        if (DEQ) {
+                            ok = mbar_wait(smem_u32(&full_b[rb.idx]), rb.phase, abort_flag, p.errword, 18);
+                            if (!ok) break;
+                        }
+                        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&peer_full[rp.idx]), 0));
+                        __syncwarp();
+                        ra.next(NSA);
+                        if (DEQ) rb.next(NSB);
+                        rp.next(NSP);
+                    }
+                }
+            }
+        }
+    } else if (warp < 2 + EPI_WARPS) {
+        // =============================== epilogue (both CTAs) ===============================
+        // warp (q, h): q = TMEM lane quarter (= warp id mod 4), h = which 128 of the 256 columns
+        const int q = warp & 3, h = (warp - 2) >> 2;
+        uint8_t *stage = sE + (warp - 2) * 4096;
+        bool ok = true;
+        int it = 0;
+        for (int tile = pair; ok && tile < total; tile += npairs, it++) {
+            TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
+            const int acc = it & 1;
+            ok = mbar_wait_cluster(smem_u32(&tmem_full[acc]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 19);
+            if (!ok) break;
+            tc_fence_after();
+            const long long row0 = (long long)t.m0 + my_m + q * 32;
+            int valid = 32;
+            if (SCHED == SCHED_ROWS) valid = ((int)rank < t.halves) ? 32 : 0;
+            else { long long left = (long long)p.M - row0; valid = left < 0 ? 0 : (left < 32 ? (int)left : 32); }
+            if (valid > 0) {
+                const bool have_acc = (SCHED != SCHED_GROUPK) || t.ksteps > 0;
+                const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
+                const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * P_BN;
+                if (EPI == EPI_SWIGLU)
+                    epilogue_rows<EPI>(p, stage, lane, tbase + (uint32_t)h * 64, rbase, (long long)t.n_t * 128 + h * 64, valid, have_acc, 128);
+                else
+                    epilogue_rows<EPI>(p, stage, lane, tbase + (uint32_t)h * 128, rbase, (long long)t.n_t * P_BN + h * 128, valid, have_acc, 0);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t te = smem_u32(&tmem_empty[acc]);
+                if (leader) mbar_arrive(te); else mbar_arrive_remote(map_to_cta(te, 0));
+            }
+        }
+    } else if (DEQ) {
+        // =============================== dequant warps (both CTAs) ===============================
+        const int dw = warp - (2 + EPI_WARPS);
+        constexpr int ITERS = (P_C_STAGE / 4) / (DQ_WARPS * 32);     // 4 code words per lane and stage
+        Ring rc = {0, 0}, rb = {0, 0};
+        bool ok = true;
+        uint32_t dst_off[ITERS];
+        int srow[ITERS], scol[ITERS];
+#pragma unroll
+        for (int i = 0; i < ITERS; i++) {
+            int wi = (i * DQ_WARPS + dw) * 32 + lane;
+            if (BMODE == B_DEQ_MN) {
+                int k = wi / 16, c = wi % 16;            // 64 rows (k) x 16 words (128 columns)
+                dst_off[i] = (uint32_t)((c / 8) * 8192 + (k >> 3) * 1024 + (k & 7) * 128 + (((c & 7) ^ (k & 7)) << 4));
+                srow[i] = k; scol[i] = c * 8;
+            } else {
+                int n = wi / 8, c = wi % 8;              // 128 rows (n) x 8 words (64 k)
+                dst_off[i] = (uint32_t)((n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4));
+                srow[i] = n; scol[i] = c * 8;
+            }
+        }
+        const int gpr = p.w_cols / 128;
+        for (int tile = pair; ok && tile < total; tile += npairs) {
+            TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
+            for (int seg = 0; ok && seg < p.nseg; seg++) {
+                const float *sp = DUAL ? p.scales[rank] : p.scales[seg];
+                int sbase[ITERS];
+#pragma unroll
+                for (int i = 0; i < ITERS; i++) {
+                    if (BMODE == B_DEQ_MN) {
+                        int ncol = (DUAL ? t.n_t * 128 : t.n_t * P_BN + my_n) + scol[i];
+                        sbase[i] = (t.e * p.w_rows + srow[i]) * gpr + ncol / 128;
+                    } else {
+                        sbase[i] = (t.e * p.w_rows + t.n_t * P_BN + my_n + srow[i]) * gpr;
+                    }
+                }
+                const int sstep = (BMODE == B_DEQ_MN) ? BK * gpr : 0;
+                float cur[ITERS], nxt[ITERS];
+#pragma unroll
+                for (int i = 0; i < ITERS; i++) cur[i] = __ldg(sp + sbase[i]);
+                for (int ks = 0; ks < t.ksteps; ks++) {
+                    if (ks + 1 < t.ksteps) {
+#pragma unroll
+                        for (int i = 0; i < ITERS; i++) {
+                            int idx = (BMODE == B_DEQ_MN) ? sbase[i] + (ks + 1) * sstep : sbase[i] + ((ks + 1) * BK) / 128;
+                            nxt[i] = __ldg(sp + idx);
+                        }
+                    }
+                    ok = mbar_wait(smem_u32(&full_c[rc.idx]), rc.phase, abort_flag, p.errword, 20);
+                    if (!ok) break;
+                    const uint32_t *cw = reinterpret_cast<const uint32_t *>(sC + rc.idx * P_C_STAGE);
+                    uint32_t w[ITERS];
+#pragma unroll
+                    for (int i = 0; i < ITERS; i++) w[i] = cw[(i * DQ_WARPS + dw) * 32 + lane];
+                    ok = mbar_wait(smem_u32(&empty_b[rb.idx]), rb.phase ^ 1u, abort_flag, p.errword, 21);
+                    if (!ok) break;
+                    uint8_t *bdst = sB + rb.idx * P_B_STAGE;
+#pragma unroll
+                    for (int i = 0; i < ITERS; i++)
+                        *reinterpret_cast<uint4 *>(bdst + dst_off[i]) = dequant8(w[i], __float2bfloat162_rn(cur[i]));
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(smem_u32(&full_b[rb.idx])); mbar_arrive(smem_u32(&empty_c[rc.idx])); }
+                    rc.next(NSC);
+                    rb.next(NSB);
+#pragma unroll
+                    for (int i = 0; i < ITERS; i++) cur[i] = nxt[i];
+                }
+            }
+        }
+    }
+
+    // =============================== teardown ===============================
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                      // the peer's shared memory stays alive until the leader's MMAs are done
+    if (warp == 1) { tc_fence_after(); tmem_dealloc2(tmem_base, TMEM_COLS); }
+}
+
+}  // namespace qlmb

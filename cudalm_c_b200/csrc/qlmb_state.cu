@@ -11,6 +11,8 @@
 // is a 128-bit (G, r, m8, v8) or 64-bit (packed digits) vector and a warp
 // covers 4 groups = 2 KiB of gradient per load instruction.  Group maxima are
 // 3-step shuffles inside the team; nibble pairs never leave a lane.
+#include <stdlib.h>
+#include <string.h>
 #include "qlmb_common.cuh"
 
 namespace qlmb {
@@ -169,15 +171,43 @@ __global__ void __launch_bounds__(256) k_step_generic(StepArgs a)
 }
 
 // ------------------------------------------------------- fast step, group 128
+// A TEAM of 128/EPL lanes owns one group, each lane EPL consecutive elements
+// (EPL = 4, 8 or 16), so a warp covers EPL/4 groups and every access is a
+// vector of EPL*4 (gradient), EPL (r, m8, v8) or EPL/2 (digits) bytes.  Fewer
+// elements per lane mean a smaller fully unrolled body (instruction cache)
+// at the price of two more shuffle steps per reduction.
 // Requirements checked per group at run time (else the team falls back to the
 // generic walk): 128 full elements, digit offset a multiple of 16, P and G
 // offsets multiples of 4; base pointers are 16-byte aligned (checked on host).
-template <bool WRITE_P>
+template <int BYTES> struct VecOf;
+template <> struct VecOf<2> { typedef unsigned short T; };
+template <> struct VecOf<4> { typedef uint32_t T; };
+template <> struct VecOf<8> { typedef uint2 T; };
+template <> struct VecOf<16> { typedef uint4 T; };
+template <int BYTES>
+__device__ __forceinline__ void ld_vec(uint32_t *dst, const void *src)
+{
+    typename VecOf<BYTES>::T v = *reinterpret_cast<const typename VecOf<BYTES>::T *>(src);
+    if (BYTES == 2) dst[0] = *reinterpret_cast<unsigned short *>(&v);
+    else memcpy(dst, &v, BYTES);
+}
+template <int BYTES>
+__device__ __forceinline__ void st_vec(void *dst, const uint32_t *src)
+{
+    typename VecOf<BYTES>::T v;
+    if (BYTES == 2) { unsigned short h = (unsigned short)src[0]; memcpy(&v, &h, 2); }
+    else memcpy(&v, src, BYTES);
+    *reinterpret_cast<typename VecOf<BYTES>::T *>(dst) = v;
+}
+
+template <bool WRITE_P, int EPL>
 __global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
 {
-    const int lane = threadIdx.x & 31, tl = lane & 7, team = lane >> 3;
-    const unsigned tmask = 0xffu << (team * 8);
-    long long w = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * 4 + team;
+    constexpr int TEAM = 128 / EPL;                      // lanes per group
+    constexpr int GPW = 32 / TEAM;                       // groups per warp
+    const int lane = threadIdx.x & 31, tl = lane % TEAM, team = lane / TEAM;
+    const unsigned tmask = (TEAM == 32) ? 0xffffffffu : (((1u << TEAM) - 1u) << (team * TEAM));
+    long long w = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * GPW + team;
     if (w >= a.ng) return;
     int gi = a.gi_base + (int)w;
     uint64_t j0; int n;
@@ -185,19 +215,19 @@ __global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
     const qlmb_span &S = a.sp[si];
     uint64_t q0 = S.qi0 + j0, p0 = S.pof + j0, g0 = S.gof + j0;
     if (n != 128 || (q0 & 15) || (g0 & 3) || (WRITE_P && (p0 & 3))) {
-        step_group_team<8>(a, gi, tl, tmask);
+        step_group_team<TEAM>(a, gi, tl, tmask);
         return;
     }
-    const uint64_t qe = q0 + (uint64_t)tl * 16;          // first element of this lane
-    // ---- loads: 4x16B gradient, 16B each of r/m8/v8, 8B of digits
-    const float4 *gp = reinterpret_cast<const float4 *>(a.G + g0 + tl * 16);
-    float4 gv[4];
+    const uint64_t qe = q0 + (uint64_t)tl * EPL;         // first element of this lane
+    const float4 *gp = reinterpret_cast<const float4 *>(a.G + g0 + tl * EPL);
+    float4 gv[EPL / 4];
 #pragma unroll
-    for (int i = 0; i < 4; i++) gv[i] = __ldcs(gp + i);
-    int4 rv4 = *reinterpret_cast<const int4 *>(a.r + qe);
-    int4 mv4 = *reinterpret_cast<const int4 *>(a.m8 + qe);
-    int4 vv4 = *reinterpret_cast<const int4 *>(a.v8 + qe);
-    uint2 dv2 = *reinterpret_cast<const uint2 *>(a.d + (qe >> 1));
+    for (int i = 0; i < EPL / 4; i++) gv[i] = __ldcs(gp + i);
+    uint32_t rw[(EPL + 3) / 4], mw[(EPL + 3) / 4], vw[(EPL + 3) / 4], dw[(EPL + 7) / 8];
+    ld_vec<EPL>(rw, a.r + qe);
+    ld_vec<EPL>(mw, a.m8 + qe);
+    ld_vec<EPL>(vw, a.v8 + qe);
+    ld_vec<EPL / 2>(dw, a.d + (qe >> 1));
     float gs = a.gsp ? *a.gsp : a.gscale;
     float sg = a.s[gi];
     float L = a.lr * 128.0f / (a.lrmode ? sg : S.sref);
@@ -208,15 +238,15 @@ __global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
     uint64_t key = qe * QLMB_HASH_I;                     // advanced by one multiplier per element
 
     const float *gf = reinterpret_cast<const float *>(gv);
-    const uint32_t *rw = reinterpret_cast<const uint32_t *>(&rv4);
-    const uint32_t *mw = reinterpret_cast<const uint32_t *>(&mv4);
-    const uint32_t *vw = reinterpret_cast<const uint32_t *>(&vv4);
-    const uint32_t dw[2] = {dv2.x, dv2.y};
-    float mn[16], rv[16], am = 0.0f, vm = 0.0f;
-    uint32_t rout[4] = {0, 0, 0, 0}, dout[2] = {0, 0};
-    float pv[16];
+    float mn[EPL], rv[EPL], am = 0.0f, vm = 0.0f;
+    uint32_t rout[(EPL + 3) / 4], dout[(EPL + 7) / 8];
 #pragma unroll
-    for (int e = 0; e < 16; e++) {
+    for (int i = 0; i < (EPL + 3) / 4; i++) rout[i] = 0;
+#pragma unroll
+    for (int i = 0; i < (EPL + 7) / 8; i++) dout[i] = 0;
+    float pv[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; e++) {
         int rold = (int)(int8_t)((rw[e >> 2] >> ((e & 3) * 8)) & 0xff);
         int m8v = (int)(int8_t)((mw[e >> 2] >> ((e & 3) * 8)) & 0xff);
         int v8v = (int)((vw[e >> 2] >> ((e & 3) * 8)) & 0xff);
@@ -232,26 +262,28 @@ __global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
         dout[e >> 3] |= ((uint32_t)(o.dd & 15)) << ((e & 7) * 4);
         if (WRITE_P) pv[e] = sg * (float)o.dd;
     }
-    *reinterpret_cast<int4 *>(a.r + qe) = make_int4(rout[0], rout[1], rout[2], rout[3]);
-    *reinterpret_cast<uint2 *>(a.d + (qe >> 1)) = make_uint2(dout[0], dout[1]);
+    st_vec<EPL>(a.r + qe, rout);
+    st_vec<EPL / 2>(a.d + (qe >> 1), dout);
     if (WRITE_P) {
-        float4 *pp = reinterpret_cast<float4 *>(a.P + p0 + tl * 16);
+        float4 *pp = reinterpret_cast<float4 *>(a.P + p0 + tl * EPL);
 #pragma unroll
-        for (int i = 0; i < 4; i++) pp[i] = make_float4(pv[4 * i], pv[4 * i + 1], pv[4 * i + 2], pv[4 * i + 3]);
+        for (int i = 0; i < EPL / 4; i++) pp[i] = make_float4(pv[4 * i], pv[4 * i + 1], pv[4 * i + 2], pv[4 * i + 3]);
     }
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
+    for (int o = TEAM / 2; o > 0; o >>= 1) {
         am = fmaxf(am, __shfl_xor_sync(tmask, am, o));
         vm = fmaxf(vm, __shfl_xor_sync(tmask, vm, o));
     }
     float ms = am > 0.0f ? am / 127.0f : 1e-12f;
     float vs = vm > 0.0f ? vm / 255.0f : 1e-12f;
     if (tl == 0) { a.m8s[gi] = ms; a.v8s[gi] = vs; }
-    uint32_t mo[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
+    uint32_t mo[(EPL + 3) / 4], vo[(EPL + 3) / 4];
+#pragma unroll
+    for (int i = 0; i < (EPL + 3) / 4; i++) { mo[i] = 0; vo[i] = 0; }
     const uint64_t ktm = (a.t + 0x5EEDULL) * QLMB_HASH_T, ktv = (a.t + 0xBEEFULL) * QLMB_HASH_T;
     key = qe * QLMB_HASH_I;
 #pragma unroll
-    for (int e = 0; e < 16; e++) {
+    for (int e = 0; e < EPL; e++) {
         int mq = clampi(sround_key(mn[e] / ms, key + ktm), -127, 127);
         int vq = clampi(sround_key(rv[e] / vs, key + ktv), 0, 255);
         if (vq == 0 && rv[e] > 0.0f) vq = 1;
@@ -259,8 +291,8 @@ __global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
         mo[e >> 2] |= ((uint32_t)(mq & 0xff)) << ((e & 3) * 8);
         vo[e >> 2] |= ((uint32_t)vq) << ((e & 3) * 8);
     }
-    *reinterpret_cast<int4 *>(a.m8 + qe) = make_int4(mo[0], mo[1], mo[2], mo[3]);
-    *reinterpret_cast<int4 *>(a.v8 + qe) = make_int4(vo[0], vo[1], vo[2], vo[3]);
+    st_vec<EPL>(a.m8 + qe, mo);
+    st_vec<EPL>(a.v8 + qe, vo);
 }
 
 // ------------------------------------------------------------------ encode
@@ -473,9 +505,14 @@ extern "C" int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const f
                 al16(v8) && (!P || al16(P));
     cudaStream_t st = as_stream(stream);
     if (fast) {
-        unsigned nb = (unsigned)((ng + 31) / 32);
-        if (P) k_step_fast<true><<<nb, 256, 0, st>>>(a);
-        else k_step_fast<false><<<nb, 256, 0, st>>>(a);
+        // elements per lane: 4 by default (smallest unrolled body); QLMB_STEP_EPL=8|16 selects the wider forms
+        static int epl = 0;
+        if (!epl) { const char *e = getenv("QLMB_STEP_EPL"); epl = e ? atoi(e) : 4; if (epl != 8 && epl != 16) epl = 4; }
+        unsigned gpb = 8u * (unsigned)(epl / 4);          // groups per block
+        unsigned nb = (unsigned)((ng + gpb - 1) / gpb);
+        if (epl == 4) { if (P) k_step_fast<true, 4><<<nb, 256, 0, st>>>(a); else k_step_fast<false, 4><<<nb, 256, 0, st>>>(a); }
+        else if (epl == 8) { if (P) k_step_fast<true, 8><<<nb, 256, 0, st>>>(a); else k_step_fast<false, 8><<<nb, 256, 0, st>>>(a); }
+        else { if (P) k_step_fast<true, 16><<<nb, 256, 0, st>>>(a); else k_step_fast<false, 16><<<nb, 256, 0, st>>>(a); }
     } else {
         k_step_generic<<<(ng + 7) / 8, 256, 0, st>>>(a);
     }
