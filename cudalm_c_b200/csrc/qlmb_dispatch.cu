@@ -50,42 +50,88 @@ __device__ __forceinline__ void st_act8(void *p, int dtype, size_t i, const floa
 
 // ------------------------------------------------------------ router logits
 // rt[n,e] = sum_j X[n,j] * Wr[j,e]  (reference cudalm.cu:4158, g_ab with N = E), fp32.
-// A warp owns 8 tokens, lane = expert; Wr rows (128 B) and the token rows (broadcast
-// vector loads) come through L1, which holds all of Wr.
+// Register-tiled: a block of 128 threads owns 64 tokens, a thread 4 tokens (16 apart) x 4 experts; the
+// token tile and Wr are staged through shared memory 32 features at a time (next chunk
+// prefetched into registers while the current one is multiplied).  Each output is summed
+// over the features in ascending order.
+#define RLT_TOK 64
+#define RLT_CH 32
+#define RLT_LD 36
 template <int XBF16>
-__global__ void __launch_bounds__(512) k_router_logits_warp(float *rt, const void *X, const float *Wr, int N, int D, int E)
+__global__ void __launch_bounds__(128) k_router_logits_tile(float *rt, const void *X, const float *Wr, int N, int D, int E)
 {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = (blockIdx.x * 16 + warp) * 8;
-    if (n0 >= N) return;
-    const int e = lane < E ? lane : E - 1;
-    float acc[8];
+    __shared__ __align__(16) float xs[2][RLT_TOK][RLT_LD];
+    __shared__ __align__(16) float ws[2][RLT_CH][32];
+    const int tid = threadIdx.x, n0 = blockIdx.x * RLT_TOK;
+    const int tg = tid >> 3, eg = tid & 7;
+    float acc[4][4];
 #pragma unroll
-    for (int t = 0; t < 8; t++) acc[t] = 0.0f;
-#pragma unroll 2
-    for (int j = 0; j < D; j += 4) {
-        float w[4];
+    for (int t = 0; t < 4; t++)
 #pragma unroll
-        for (int jj = 0; jj < 4; jj++) w[jj] = __ldg(Wr + (size_t)(j + jj) * E + e);
+        for (int i = 0; i < 4; i++) acc[t][i] = 0.0f;
+    float xr[2][8], wr[8];
+    auto fetch = [&](int j0) {
 #pragma unroll
-        for (int t = 0; t < 8; t++) {
-            const int n = n0 + t < N ? n0 + t : N - 1;
-            float x0, x1, x2, x3;
-            if (XBF16) {
-                uint2 q = __ldg(reinterpret_cast<const uint2 *>((const bf16 *)X + (size_t)n * D + j));
-                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
-                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
-                x0 = a.x; x1 = a.y; x2 = b.x; x3 = b.y;
-            } else {
-                float4 q = __ldg(reinterpret_cast<const float4 *>((const float *)X + (size_t)n * D + j));
-                x0 = q.x; x1 = q.y; x2 = q.z; x3 = q.w;
+        for (int i = 0; i < 2; i++) {
+            const int p = tid + i * 128, tok = p >> 2, part = p & 3;
+            const int n = n0 + tok, j = j0 + part * 8;
+            if (n < N && j < D) ld_act8(X, XBF16 ? QLMB_BF16 : QLMB_F32, (size_t)n * D + j, xr[i]);
+            else {
+#pragma unroll
+                for (int k = 0; k < 8; k++) xr[i][k] = 0.0f;
             }
-            acc[t] += x0 * w[0]; acc[t] += x1 * w[1]; acc[t] += x2 * w[2]; acc[t] += x3 * w[3];
         }
-    }
-    if (lane < E) {
 #pragma unroll
-        for (int t = 0; t < 8; t++) if (n0 + t < N) rt[(size_t)(n0 + t) * E + lane] = acc[t];
+        for (int i = 0; i < 8; i++) {
+            const int q = tid + i * 128, row = q >> 5, e = q & 31;
+            wr[i] = (e < E && j0 + row < D) ? __ldg(Wr + (size_t)(j0 + row) * E + e) : 0.0f;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int p = tid + i * 128, tok = p >> 2, part = p & 3;
+            *reinterpret_cast<float4 *>(&xs[buf][tok][part * 8]) = make_float4(xr[i][0], xr[i][1], xr[i][2], xr[i][3]);
+            *reinterpret_cast<float4 *>(&xs[buf][tok][part * 8 + 4]) = make_float4(xr[i][4], xr[i][5], xr[i][6], xr[i][7]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int q = tid + i * 128;
+            ws[buf][q >> 5][q & 31] = wr[i];
+        }
+    };
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    const int nch = (D + RLT_CH - 1) / RLT_CH;
+    for (int c = 0; c < nch; c++) {
+        const int buf = c & 1;
+        if (c + 1 < nch) fetch((c + 1) * RLT_CH);
+#pragma unroll
+        for (int kk = 0; kk < RLT_CH; kk += 4) {
+            float4 xv[4];
+#pragma unroll
+            for (int t = 0; t < 4; t++) xv[t] = *reinterpret_cast<const float4 *>(&xs[buf][tg + 16 * t][kk]);
+#pragma unroll
+            for (int k4 = 0; k4 < 4; k4++) {
+                const float4 w = *reinterpret_cast<const float4 *>(&ws[buf][kk + k4][eg * 4]);
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    const float x = k4 == 0 ? xv[t].x : k4 == 1 ? xv[t].y : k4 == 2 ? xv[t].z : xv[t].w;
+                    acc[t][0] += x * w.x; acc[t][1] += x * w.y; acc[t][2] += x * w.z; acc[t][3] += x * w.w;
+                }
+            }
+        }
+        if (c + 1 < nch) stash(buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        const int n = n0 + tg + 16 * t;
+        if (n >= N) continue;
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (eg * 4 + i < E) rt[(size_t)n * E + eg * 4 + i] = acc[t][i];
     }
 }
 
@@ -130,10 +176,10 @@ __global__ void __launch_bounds__(256) k_router_logits(float *rt, const void *X,
 
 int router_logits(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E, cudaStream_t st)
 {
-    if (E <= 32 && (D % 4) == 0) {
-        int blocks = (N + 127) / 128;               // 16 warps x 8 tokens per block
-        if (x_dtype == QLMB_BF16) k_router_logits_warp<1><<<blocks, 512, 0, st>>>(rt, X, Wr, N, D, E);
-        else k_router_logits_warp<0><<<blocks, 512, 0, st>>>(rt, X, Wr, N, D, E);
+    if (E <= 32 && (D % 8) == 0) {
+        int blocks = (N + RLT_TOK - 1) / RLT_TOK;
+        if (x_dtype == QLMB_BF16) k_router_logits_tile<1><<<blocks, 128, 0, st>>>(rt, X, Wr, N, D, E);
+        else k_router_logits_tile<0><<<blocks, 128, 0, st>>>(rt, X, Wr, N, D, E);
     } else {
         k_router_logits<<<(N + RL_TOK - 1) / RL_TOK, 256, 0, st>>>(rt, X, x_dtype, Wr, N, D, E);
     }
@@ -305,40 +351,96 @@ int router_bwd(float *drt, const float *rprobs, const int *assign, const float *
 // --------------------------------------------------------------- unpermute
 // dfnorm[n,j] = sum_k dXp[inv[k,n], j] + sum_e drt[n,e] * Wr[j,e]
 // (reference k_scatter_add + g_abt_b(drt, Wr), cudalm.cu:4368-4390).
-// WrT is Wr transposed ([E][D], written by k_transpose_wr into scratch), so a
-// lane's 8 consecutive features are two 16-byte loads that hit L1; a warp owns a
-// token, a lane 8 consecutive features per pass.
+// WrT is Wr transposed ([E][D], written by k_transpose_wr into scratch), so that a
+// feature slice of it is staged with 16-byte copies.
 __global__ void __launch_bounds__(256) k_transpose_wr(float *WrT, const float *Wr, int D, int E)
 {
     int i = blockIdx.x * 256 + threadIdx.x;
     if (i < D * E) { int j = i / E, e = i % E; WrT[(size_t)e * D + j] = Wr[i]; }
 }
-__global__ void __launch_bounds__(256) k_unpermute_rows_warp(void *dfnorm, int dtype, const bf16 *dXp, const int *inv,
-                                                             const float *drt, const float *WrT, int N, int D, int E, int K)
+// Register-tiled: a block owns 32 tokens x 256 features; warp = 4 tokens, lane = features
+// [4*lane, 4*lane+4) and [128+4*lane, ...) of the block's slice.  The slice of WrT and the
+// tokens' drt rows sit in shared memory; the K permuted rows are fetched first so their
+// latency overlaps the staging.
+#define UPT_TOK 32
+#define UPT_F 256
+__global__ void __launch_bounds__(256, 3) k_unpermute_rows_tile(void *dfnorm, int dtype, const bf16 *dXp, const int *inv,
+                                                                const float *drt, const float *WrT, int N, int D, int E, int K)
 {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * 8 + warp;
-    if (n >= N) return;
-    float dr = lane < E ? drt[(size_t)n * E + lane] : 0.0f;
-    int slot = lane < K ? inv[(size_t)lane * N + n] : 0;
-    for (int j = lane * 8; j < D; j += 256) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int k = 0; k < K; k++) {
-            int row = __shfl_sync(0xffffffffu, slot, k);
-            float y[8];
-            ld_act8(dXp, QLMB_BF16, (size_t)row * D + j, y);
+    __shared__ __align__(16) float ws[32][UPT_F];
+    __shared__ __align__(16) float drs[UPT_TOK][32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * UPT_TOK, j0 = blockIdx.y * UPT_F;
+    const int jA = j0 + lane * 4, jB = jA + 128;
+    float acc[4][8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) acc[i] += y[i];
+    for (int t = 0; t < 4; t++) {
+        const int n = n0 + warp * 4 + t;
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[t][i] = 0.0f;
+        if (n >= N) continue;
+        for (int k = 0; k < K; k++) {
+            const size_t row = (size_t)__ldg(inv + (size_t)k * N + n) * D;
+            if (jA < D) {
+                uint2 q = __ldg(reinterpret_cast<const uint2 *>(dXp + row + jA));
+                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
+                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
+                acc[t][0] += a.x; acc[t][1] += a.y; acc[t][2] += b.x; acc[t][3] += b.y;
+            }
+            if (jB < D) {
+                uint2 q = __ldg(reinterpret_cast<const uint2 *>(dXp + row + jB));
+                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
+                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
+                acc[t][4] += a.x; acc[t][5] += a.y; acc[t][6] += b.x; acc[t][7] += b.y;
+            }
         }
-#pragma unroll 4
-        for (int e = 0; e < E; e++) {
-            float dv = __shfl_sync(0xffffffffu, dr, e);
-            float4 w0 = __ldg(reinterpret_cast<const float4 *>(WrT + (size_t)e * D + j));
-            float4 w1 = __ldg(reinterpret_cast<const float4 *>(WrT + (size_t)e * D + j + 4));
-            acc[0] += dv * w0.x; acc[1] += dv * w0.y; acc[2] += dv * w0.z; acc[3] += dv * w0.w;
-            acc[4] += dv * w1.x; acc[5] += dv * w1.y; acc[6] += dv * w1.z; acc[7] += dv * w1.w;
+    }
+    for (int i = tid; i < 32 * (UPT_F / 4); i += 256) {
+        const int e = i / (UPT_F / 4), c = i % (UPT_F / 4), j = j0 + c * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < E && j < D) v = __ldg(reinterpret_cast<const float4 *>(WrT + (size_t)e * D + j));
+        *reinterpret_cast<float4 *>(&ws[e][c * 4]) = v;
+    }
+    for (int i = tid; i < UPT_TOK * 32; i += 256) {
+        const int n = n0 + (i >> 5), e = i & 31;
+        drs[i >> 5][e] = (n < N && e < E) ? drt[(size_t)n * E + e] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int e4 = 0; e4 < 32; e4 += 4) {
+        float4 dv[4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) dv[t] = *reinterpret_cast<const float4 *>(&drs[warp * 4 + t][e4]);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; k4++) {
+            const float4 wa = *reinterpret_cast<const float4 *>(&ws[e4 + k4][lane * 4]);
+            const float4 wb = *reinterpret_cast<const float4 *>(&ws[e4 + k4][128 + lane * 4]);
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const float d = k4 == 0 ? dv[t].x : k4 == 1 ? dv[t].y : k4 == 2 ? dv[t].z : dv[t].w;
+                acc[t][0] += d * wa.x; acc[t][1] += d * wa.y; acc[t][2] += d * wa.z; acc[t][3] += d * wa.w;
+                acc[t][4] += d * wb.x; acc[t][5] += d * wb.y; acc[t][6] += d * wb.z; acc[t][7] += d * wb.w;
+            }
         }
-        st_act8(dfnorm, dtype, (size_t)n * D + j, acc);
+    }
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        const int n = n0 + warp * 4 + t;
+        if (n >= N) continue;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int j = h ? jB : jA;
+            if (j >= D) continue;
+            const float *v = &acc[t][h * 4];
+            if (dtype == QLMB_BF16) {
+                uint2 q;
+                *reinterpret_cast<__nv_bfloat162 *>(&q.x) = __floats2bfloat162_rn(v[0], v[1]);
+                *reinterpret_cast<__nv_bfloat162 *>(&q.y) = __floats2bfloat162_rn(v[2], v[3]);
+                *reinterpret_cast<uint2 *>((bf16 *)dfnorm + (size_t)n * D + j) = q;
+            } else {
+                *reinterpret_cast<float4 *>((float *)dfnorm + (size_t)n * D + j) = make_float4(v[0], v[1], v[2], v[3]);
+            }
+        }
     }
 }
 
@@ -387,7 +489,7 @@ int unpermute_rows(void *dfnorm, int dtype, const bf16 *dXp, const int *inv, con
 {
     if (E <= 32 && (D % 8) == 0 && wrt_scratch) {
         k_transpose_wr<<<(D * E + 255) / 256, 256, 0, st>>>(wrt_scratch, Wr, D, E);
-        k_unpermute_rows_warp<<<(N + 7) / 8, 256, 0, st>>>(dfnorm, dtype, dXp, inv, drt, wrt_scratch, N, D, E, K);
+        k_unpermute_rows_tile<<<dim3((N + UPT_TOK - 1) / UPT_TOK, (D + UPT_F - 1) / UPT_F), 256, 0, st>>>(dfnorm, dtype, dXp, inv, drt, wrt_scratch, N, D, E, K);
     } else {
         size_t smem = (size_t)UP_TOK * E * sizeof(float) + (size_t)UP_TOK * K * sizeof(int);
         k_unpermute_rows<<<(N + UP_TOK - 1) / UP_TOK, 256, smem, st>>>(dfnorm, dtype, dXp, inv, drt, Wr, N, D, E, K);
@@ -436,6 +538,82 @@ __global__ void __launch_bounds__(256) k_router_wgrad_part(float *part, const vo
         }
     }
 }
+// Register-tiled stage 1 for E <= 32: block (c, jb) owns token chunk c and 128 features; a
+// thread 4 features x 4 experts.  Tokens are staged 32 at a time (fp32 in shared memory,
+// next sub-chunk prefetched into registers during the multiply).
+#define RWT_F 128
+#define RWT_SUB 32
+template <int XBF16>
+__global__ void __launch_bounds__(256) k_router_wgrad_tile(float *part, const void *fnorm, const float *drt,
+                                                           int N, int D, int E, int per)
+{
+    __shared__ __align__(16) float xs[2][RWT_SUB][RWT_F];
+    __shared__ __align__(16) float ds[2][RWT_SUB][32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int c = blockIdx.x, j0 = blockIdx.y * RWT_F;
+    const int n_lo = c * per, n_hi = n_lo + per < N ? n_lo + per : N;
+    const int eg = lane & 7, fg = warp * 4 + (lane >> 3);
+    float acc[4][4];
+#pragma unroll
+    for (int f = 0; f < 4; f++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[f][i] = 0.0f;
+    float xr[2][8], dr[4];
+    auto fetch = [&](int nb) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int p = tid + i * 256, n = nb + (p >> 4), j = j0 + (p & 15) * 8;
+            if (n < n_hi && j < D) ld_act8(fnorm, XBF16 ? QLMB_BF16 : QLMB_F32, (size_t)n * D + j, xr[i]);
+            else {
+#pragma unroll
+                for (int k = 0; k < 8; k++) xr[i][k] = 0.0f;
+            }
+        }
+        const int n = nb + (tid >> 3);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int e = (tid & 7) * 4 + i;
+            dr[i] = (n < n_hi && e < E) ? drt[(size_t)n * E + e] : 0.0f;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int p = tid + i * 256;
+            float *o = &xs[buf][p >> 4][(p & 15) * 8];
+            *reinterpret_cast<float4 *>(o) = make_float4(xr[i][0], xr[i][1], xr[i][2], xr[i][3]);
+            *reinterpret_cast<float4 *>(o + 4) = make_float4(xr[i][4], xr[i][5], xr[i][6], xr[i][7]);
+        }
+        *reinterpret_cast<float4 *>(&ds[buf][tid >> 3][(tid & 7) * 4]) = make_float4(dr[0], dr[1], dr[2], dr[3]);
+    };
+    fetch(n_lo);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int nb = n_lo; nb < n_hi; nb += RWT_SUB, buf ^= 1) {
+        const bool more = nb + RWT_SUB < n_hi;
+        if (more) fetch(nb + RWT_SUB);
+#pragma unroll 8
+        for (int t = 0; t < RWT_SUB; t++) {
+            const float4 x = *reinterpret_cast<const float4 *>(&xs[buf][t][fg * 4]);
+            const float4 d = *reinterpret_cast<const float4 *>(&ds[buf][t][eg * 4]);
+            acc[0][0] += x.x * d.x; acc[0][1] += x.x * d.y; acc[0][2] += x.x * d.z; acc[0][3] += x.x * d.w;
+            acc[1][0] += x.y * d.x; acc[1][1] += x.y * d.y; acc[1][2] += x.y * d.z; acc[1][3] += x.y * d.w;
+            acc[2][0] += x.z * d.x; acc[2][1] += x.z * d.y; acc[2][2] += x.z * d.z; acc[2][3] += x.z * d.w;
+            acc[3][0] += x.w * d.x; acc[3][1] += x.w * d.y; acc[3][2] += x.w * d.z; acc[3][3] += x.w * d.w;
+        }
+        if (more) stash(buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int f = 0; f < 4; f++) {
+        const int j = j0 + fg * 4 + f;
+        if (j >= D) continue;
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (eg * 4 + i < E) part[((size_t)c * D + j) * E + eg * 4 + i] = acc[f][i];
+    }
+}
 __global__ void __launch_bounds__(256) k_router_wgrad_sum(float *dWr, const float *part, int nchunk, int DE, float beta)
 {
     int i = blockIdx.x * 256 + threadIdx.x;
@@ -448,9 +626,21 @@ __global__ void __launch_bounds__(256) k_router_wgrad_sum(float *dWr, const floa
 int router_wgrad(float *dWr, const void *fnorm, int dtype, const float *drt, float *scratch, int N, int D, int E,
                  float beta, cudaStream_t st)
 {
-    for (int e0 = 0; e0 < E; e0 += 32)
-        k_router_wgrad_part<<<dim3(RW_CHUNKS, (D + 255) / 256), 256, 0, st>>>(scratch, fnorm, dtype, drt, N, D, E, e0);
-    k_router_wgrad_sum<<<(D * E + 255) / 256, 256, 0, st>>>(dWr, scratch, RW_CHUNKS, D * E, beta);
+    int nchunk = RW_CHUNKS;
+    if (E <= 32 && (D % 8) == 0) {
+        const int fblocks = (D + RWT_F - 1) / RWT_F;
+        int want = 4 * sm_count() / fblocks;
+        if (want < 1) want = 1;
+        if (want > RW_CHUNKS) want = RW_CHUNKS;
+        int per = ((N + want - 1) / want + RWT_SUB - 1) / RWT_SUB * RWT_SUB;
+        nchunk = (N + per - 1) / per;
+        if (dtype == QLMB_BF16) k_router_wgrad_tile<1><<<dim3(nchunk, fblocks), 256, 0, st>>>(scratch, fnorm, drt, N, D, E, per);
+        else k_router_wgrad_tile<0><<<dim3(nchunk, fblocks), 256, 0, st>>>(scratch, fnorm, drt, N, D, E, per);
+    } else {
+        for (int e0 = 0; e0 < E; e0 += 32)
+            k_router_wgrad_part<<<dim3(RW_CHUNKS, (D + 255) / 256), 256, 0, st>>>(scratch, fnorm, dtype, drt, N, D, E, e0);
+    }
+    k_router_wgrad_sum<<<(D * E + 255) / 256, 256, 0, st>>>(dWr, scratch, nchunk, D * E, beta);
     QLMB_LAUNCH_CHECK("router_wgrad");
     return QLMB_OK;
 }
