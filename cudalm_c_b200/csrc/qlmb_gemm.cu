@@ -52,6 +52,7 @@ struct GemmParams {
     const void *resid; float beta;
     bf16 *gp, *up, *ap, *dgp, *dup;
     int *errword;
+    int dbg;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -75,6 +76,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 {
     for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
         if (mbar_try(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    if (!*abort_flag) {
+        *abort_flag = 1;
+        if (errword && atomicCAS(errword, 0, 200) == 0) { errword[1] = site; errword[2] = (int)blockIdx.x; errword[3] = (int)parity; }
+    }
+    return false;
+}
+// same contract, for waiters that are not on the MMA issue path: a failed probe backs off for a
+// few tens of nanoseconds, so that spinning warps do not take issue slots from the working ones
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *errword, int site)
+{
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try(bar, parity)) return true;
+        __nanosleep(32);
         if ((i & 255u) == 255u && *abort_flag) return false;
     }
     if (!*abort_flag) {
@@ -697,16 +713,15 @@ static int launch_inst(const GemmParams &p, int grid, cudaStream_t st)
     return QLMB_OK;
 }
 
-template <int BMODE, int EPI, int SCHED>
-static int launch_pair(const GemmParams &p, long long total, cudaStream_t st)
+template <int BMODE, int EPI, int SCHED, int DQG>
+static int launch_pair_g(const GemmParams &p, long long total, cudaStream_t st)
 {
     constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
-    constexpr int NSA = DEQ ? 5 : 6;
-    constexpr size_t smem = 1024 + (size_t)NSA * (P_A_STAGE + P_B_STAGE) + (DEQ ? 4 * P_C_STAGE : 0) + EPI_WARPS * 4096 + 512;
+    constexpr size_t smem = 1024 + (size_t)(DEQ ? 5 : 6) * (P_A_STAGE + P_B_STAGE) + (DEQ ? 8 * P_C_STAGE : 0) + EPI_WARPS * 4096 + 512;
     // persistent kernel: every cluster must be resident at once, so the grid is the number of
     // clusters the device can hold at the same time (asked once per kernel instance)
     static int max_clusters = 0;
-    auto kfn = k_gemm_pair<BMODE, EPI, SCHED>;
+    auto kfn = k_gemm_pair<BMODE, EPI, SCHED, DQG>;
     if (!max_clusters) {
         QLMB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         cudaLaunchConfig_t cfg = {};
@@ -724,6 +739,19 @@ static int launch_pair(const GemmParams &p, long long total, cudaStream_t st)
     kfn<<<(unsigned)(2 * clusters), DEQ ? 576 : 320, smem, st>>>(p);
     QLMB_LAUNCH_CHECK("k_gemm_pair");
     return QLMB_OK;
+}
+
+template <int BMODE, int EPI, int SCHED>
+static int launch_pair(const GemmParams &p, long long total, cudaStream_t st)
+{
+    constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
+    if (DEQ) {
+        static int groups = 0;
+        if (!groups) { const char *e = getenv("QLMB_DQ_GROUPS"); groups = e ? atoi(e) : 2; }
+        if (groups == 1) return launch_pair_g<BMODE, EPI, SCHED, DEQ ? 1 : 2>(p, total, st);
+        if (groups == 4) return launch_pair_g<BMODE, EPI, SCHED, DEQ ? 4 : 2>(p, total, st);
+    }
+    return launch_pair_g<BMODE, EPI, SCHED, 2>(p, total, st);     // two dequant stage groups
 }
 
 // The two-SM form needs whole 256-column tiles (128 activation columns with the SwiGLU
@@ -754,6 +782,7 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
     p.out = g.out; p.out_dtype = g.out_dtype; p.ldo = g.ldo; p.resid = g.resid; p.beta = g.beta;
     p.gp = g.gp; p.up = g.up; p.ap = g.ap; p.dgp = g.dgp; p.dup = g.dup;
     p.errword = device_error_word();
+    { static int dbg = -1; if (dbg < 0) { const char *e = getenv("QLMB_DBG"); dbg = e ? atoi(e) : 0; } p.dbg = dbg; }
     p.scales[0] = g.scales[0]; p.scales[1] = g.scales[1];
     const unsigned long long wrows_total = (unsigned long long)g.E * g.w_rows;
     for (int s = 0; s < (dual ? 2 : g.nseg); s++) {

@@ -9,13 +9,15 @@
 // expand half as many weights as in the one-SM form.
 //
 // Hand-shakes across the pair (all waits bounded, as everywhere in this file):
-//   peer_full[s]   leader   the peer's relay warp arrives when the peer's A and B
-//                           stage are complete (remote mbarrier arrive)
-//   empty_a/b[s]   both     released by tcgen05.commit from the leader, once to its
-//                           own barrier and once to the peer's (mapped address)
+//   full[s]        leader   one barrier per stage collects everything the MMA needs: the
+//                           byte counts of both CTAs' bulk tensor loads (the peer's loads
+//                           name the leader's barrier, cta_group::2 form) and one arrival
+//                           per dequant warp of either CTA (the peer's arrive remotely)
+//   empty[s]       both     released by one tcgen05.commit that arrives in both CTAs
 //   tmem_full[a]   both     committed the same way after a tile's last step
 //   tmem_empty[a]  leader   8 local + 8 remote epilogue warps
-// No bulk copy in this file is a cluster-wide (multi-destination) copy.
+//   full_c/empty_c local    ring of packed-code tiles between the loader and the dequant warps
+// No bulk copy in this file has more than one destination CTA.
 #pragma once
 
 namespace qlmb {
@@ -61,6 +63,13 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     }
     return false;
 }
+// bulk tensor load into this CTA's shared memory whose byte count is reported to a barrier
+// of either CTA of the pair (cluster address)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t cluster_bar, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols)
 { asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory"); }
 __device__ __forceinline__ void tmem_relinquish2()
@@ -70,6 +79,12 @@ __device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols)
 // completion of all MMAs issued so far -> one arrival on the barrier at this cluster address
 __device__ __forceinline__ void tc_commit2(uint32_t cluster_bar)
 { asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory"); }
+// one commit that arrives on the barrier at this shared-memory offset in both CTAs of the pair
+__device__ __forceinline__ void tc_commit2_both(uint32_t local_bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(local_bar), "h"((uint16_t)3) : "memory");
+}
 __device__ __forceinline__ void tc_mma2_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -105,26 +120,28 @@ __device__ __forceinline__ TileInfo decode_pair_tile(const GemmParams &p, int ti
     return t;
 }
 
-template <int BMODE, int EPI, int SCHED>
+template <int BMODE, int EPI, int SCHED, int DQG>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((BMODE == B_DEQ_MN || BMODE == B_DEQ_K) ? 576 : 320, 1)
 k_gemm_pair(const __grid_constant__ GemmParams p)
 {
     constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
     constexpr bool DUAL = (EPI == EPI_SWIGLU);           // CTA 0 expands W1 (gate), CTA 1 expands W3 (up)
-    constexpr int NSA = DEQ ? 5 : 6, NSB = NSA, NSC = 4, NSP = 8;   // NSP > NSA: a slot is consumed before it is signalled again
+    constexpr int NS = DEQ ? 5 : 6, NSC = 8;
+    constexpr int GW = DQ_WARPS / DQG;                   // dequant warps per stage group
     constexpr uint32_t IDESC = make_idesc(256, P_BN, BMODE == AB_TMA_MN ? 1 : 0, (BMODE == B_DEQ_MN || BMODE == AB_TMA_MN) ? 1 : 0);
     constexpr uint32_t TMEM_COLS = 2 * P_BN;
+    constexpr uint32_t TX_BYTES = 2u * (P_A_STAGE + (DEQ ? 0 : P_B_STAGE));   // both CTAs' loads of a stage
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sA = smem;
-    uint8_t *sB = sA + NSA * P_A_STAGE;
-    uint8_t *sC = sB + NSB * P_B_STAGE;
+    uint8_t *sB = sA + NS * P_A_STAGE;
+    uint8_t *sC = sB + NS * P_B_STAGE;
     uint8_t *sE = sC + (DEQ ? NSC * P_C_STAGE : 0);
     uint64_t *bars = reinterpret_cast<uint64_t *>(sE + EPI_WARPS * 4096);
-    uint64_t *full_a = bars, *empty_a = full_a + NSA, *full_b = empty_a + NSA, *empty_b = full_b + NSB;
-    uint64_t *full_c = empty_b + NSB, *empty_c = full_c + NSC, *peer_full = empty_c + NSC;
-    uint64_t *tmem_full = peer_full + NSP, *tmem_empty = tmem_full + 2, *spare = tmem_empty + 2;
+    uint64_t *full = bars, *empty = full + NS;
+    uint64_t *full_c = empty + NS, *empty_c = full_c + NSC;
+    uint64_t *tmem_full = empty_c + NSC, *tmem_empty = tmem_full + 2, *spare = tmem_empty + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(spare + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -133,10 +150,8 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
     const bool leader = rank == 0;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NSA; i++) { mbar_init(smem_u32(&full_a[i]), 1); mbar_init(smem_u32(&empty_a[i]), 1); }
-        for (int i = 0; i < NSB; i++) { mbar_init(smem_u32(&full_b[i]), DEQ ? DQ_WARPS : 1); mbar_init(smem_u32(&empty_b[i]), 1); }
-        for (int i = 0; i < NSC; i++) { mbar_init(smem_u32(&full_c[i]), 1); mbar_init(smem_u32(&empty_c[i]), DQ_WARPS); }
-        for (int i = 0; i < NSP; i++) mbar_init(smem_u32(&peer_full[i]), 1);
+        for (int i = 0; i < NS; i++) { mbar_init(smem_u32(&full[i]), 1 + (DEQ ? 2 * GW : 0)); mbar_init(smem_u32(&empty[i]), 1); }
+        for (int i = 0; i < NSC; i++) { mbar_init(smem_u32(&full_c[i]), 1); mbar_init(smem_u32(&empty_c[i]), GW); }
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&tmem_full[i]), 1); mbar_init(smem_u32(&tmem_empty[i]), 2 * EPI_WARPS); }
         mbar_init(smem_u32(spare), 1);
         *abort_flag = 0;
@@ -158,35 +173,34 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
 
     if (warp == 0) {
         // =============================== TMA producer (both CTAs) ===============================
-        Ring ra = {0, 0}, rc = {0, 0};
+        Ring rs = {0, 0}, rc = {0, 0};
         bool ok = true;
         for (int tile = pair; ok && tile < total; tile += npairs) {
             TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
             for (int seg = 0; ok && seg < p.nseg; seg++) {
                 for (int ks = 0; ks < t.ksteps; ks++) {
-                    ok = mbar_wait(smem_u32(&empty_a[ra.idx]), ra.phase ^ 1u, abort_flag, p.errword, 11);
+                    ok = mbar_wait_idle(smem_u32(&empty[rs.idx]), rs.phase ^ 1u, abort_flag, p.errword, 11);
                     if (!ok) break;
                     if (lane == 0) {
-                        uint32_t bar = smem_u32(&full_a[ra.idx]);
-                        uint32_t dstA = smem_u32(sA + ra.idx * P_A_STAGE);
-                        uint32_t dstB = smem_u32(sB + ra.idx * P_B_STAGE);
+                        if (leader) mbar_expect_tx(smem_u32(&full[rs.idx]), TX_BYTES);
+                        const uint32_t bar = map_to_cta(smem_u32(&full[rs.idx]), 0);
+                        const uint32_t dstA = smem_u32(sA + rs.idx * P_A_STAGE);
+                        const uint32_t dstB = smem_u32(sB + rs.idx * P_B_STAGE);
                         if (BMODE == AB_TMA_MN) {
-                            int row = t.row0 + ks * BK;
-                            mbar_expect_tx(bar, P_A_STAGE + P_B_STAGE);
-                            tma_load_2d(dstA, &p.a_map[0], bar, t.m0 + my_m, row);
-                            tma_load_2d(dstA + 8192, &p.a_map[0], bar, t.m0 + my_m + 64, row);
-                            tma_load_2d(dstB, &p.w_map[0], bar, t.n_t * P_BN + my_n, row);
-                            tma_load_2d(dstB + 8192, &p.w_map[0], bar, t.n_t * P_BN + my_n + 64, row);
+                            const int row = t.row0 + ks * BK;
+                            tma_load_2d_pair(dstA, &p.a_map[0], bar, t.m0 + my_m, row);
+                            tma_load_2d_pair(dstA + 8192, &p.a_map[0], bar, t.m0 + my_m + 64, row);
+                            tma_load_2d_pair(dstB, &p.w_map[0], bar, t.n_t * P_BN + my_n, row);
+                            tma_load_2d_pair(dstB + 8192, &p.w_map[0], bar, t.n_t * P_BN + my_n + 64, row);
                         } else {
-                            mbar_expect_tx(bar, P_A_STAGE + (BMODE == B_TMA_K ? P_B_STAGE : 0));
-                            tma_load_2d(dstA, &p.a_map[seg], bar, ks * BK, t.m0 + my_m);
-                            if (BMODE == B_TMA_K) tma_load_2d(dstB, &p.w_map[seg], bar, ks * BK, t.n_t * P_BN + my_n);
+                            tma_load_2d_pair(dstA, &p.a_map[seg], bar, ks * BK, t.m0 + my_m);
+                            if (BMODE == B_TMA_K) tma_load_2d_pair(dstB, &p.w_map[seg], bar, ks * BK, t.n_t * P_BN + my_n);
                         }
                     }
                     __syncwarp();
-                    ra.next(NSA);
+                    rs.next(NS);
                     if (DEQ) {
-                        ok = mbar_wait(smem_u32(&empty_c[rc.idx]), rc.phase ^ 1u, abort_flag, p.errword, 12);
+                        ok = mbar_wait_idle(smem_u32(&empty_c[rc.idx]), rc.phase ^ 1u, abort_flag, p.errword, 12);
                         if (!ok) break;
                         if (lane == 0) {
                             uint32_t bar = smem_u32(&full_c[rc.idx]);
@@ -207,10 +221,10 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
             }
         }
     } else if (warp == 1) {
-        Ring ra = {0, 0}, rb = {0, 0}, rp = {0, 0};
-        bool ok = true;
         if (leader) {
             // =============================== MMA issuer (leader CTA) ===============================
+            Ring rs = {0, 0};
+            bool ok = true;
             int it = 0;
             for (int tile = pair; ok && tile < total; tile += npairs, it++) {
                 TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
@@ -222,19 +236,12 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                 uint32_t accumulate = 0;
                 for (int seg = 0; ok && seg < p.nseg; seg++) {
                     for (int ks = 0; ks < t.ksteps; ks++) {
-                        ok = mbar_wait(smem_u32(&full_a[ra.idx]), ra.phase, abort_flag, p.errword, 14);
-                        if (!ok) break;
-                        const int sb = DEQ ? rb.idx : ra.idx;
-                        if (DEQ) {
-                            ok = mbar_wait(smem_u32(&full_b[rb.idx]), rb.phase, abort_flag, p.errword, 15);
-                            if (!ok) break;
-                        }
-                        ok = mbar_wait_cluster(smem_u32(&peer_full[rp.idx]), rp.phase, abort_flag, p.errword, 16);
+                        ok = mbar_wait_cluster(smem_u32(&full[rs.idx]), rs.phase, abort_flag, p.errword, 14);
                         if (!ok) break;
                         tc_fence_after();
                         if (lane == 0) {
-                            const uint32_t a0 = smem_u32(sA + ra.idx * P_A_STAGE);
-                            const uint32_t b0 = smem_u32(sB + sb * P_B_STAGE);
+                            const uint32_t a0 = smem_u32(sA + rs.idx * P_A_STAGE);
+                            const uint32_t b0 = smem_u32(sB + rs.idx * P_B_STAGE);
 #pragma unroll
                             for (int k16 = 0; k16 < BK / 16; k16++) {
                                 uint64_t ad = (BMODE == AB_TMA_MN) ? make_desc(a0 + k16 * 2048, 8192, 1024) : make_desc(a0 + k16 * 32, 16, 1024);
@@ -243,28 +250,15 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                                 tc_mma2_bf16(tmem_d, ad, bd, IDESC, accumulate);
                                 accumulate = 1;
                             }
-                            const uint32_t ea = smem_u32(&empty_a[ra.idx]);
-                            tc_commit2(ea);
-                            tc_commit2(map_to_cta(ea, 1));
-                            if (DEQ) {
-                                const uint32_t eb = smem_u32(&empty_b[rb.idx]);
-                                tc_commit2(eb);
-                                tc_commit2(map_to_cta(eb, 1));
-                            }
+                            tc_commit2_both(smem_u32(&empty[rs.idx]));
                         }
                         __syncwarp();
                         accumulate = 1;
-                        ra.next(NSA);
-                        if (DEQ) rb.next(NSB);
-                        rp.next(NSP);
+                        rs.next(NS);
                     }
                 }
                 if (ok) {
-                    if (lane == 0) {
-                        const uint32_t tf = smem_u32(&tmem_full[acc]);
-                        tc_commit2(tf);
-                        tc_commit2(map_to_cta(tf, 1));
-                    }
+                    if (lane == 0) tc_commit2_both(smem_u32(&tmem_full[acc]));
                     __syncwarp();
                 }
             }
@@ -272,27 +266,6 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                 if (lane == 0) tc_commit2(smem_u32(spare));
                 __syncwarp();
                 for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(smem_u32(spare), 0); i++) {}
-            }
-        } else {
-            // =============================== relay (peer CTA) ===============================
-            // tells the leader when this CTA's halves of a stage are complete
-            for (int tile = pair; ok && tile < total; tile += npairs) {
-                TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
-                for (int seg = 0; ok && seg < p.nseg; seg++) {
-                    for (int ks = 0; ks < t.ksteps; ks++) {
-                        ok = mbar_wait(smem_u32(&full_a[ra.idx]), ra.phase, abort_flag, p.errword, 17);
-                        if (!ok) break;
-                        if (DEQ) {
-                            ok = mbar_wait(smem_u32(&full_b[rb.idx]), rb.phase, abort_flag, p.errword, 18);
-                            if (!ok) break;
-                        }
-                        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&peer_full[rp.idx]), 0));
-                        __syncwarp();
-                        ra.next(NSA);
-                        if (DEQ) rb.next(NSB);
-                        rp.next(NSP);
-                    }
-                }
             }
         }
     } else if (warp < 2 + EPI_WARPS) {
@@ -305,7 +278,7 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
         for (int tile = pair; ok && tile < total; tile += npairs, it++) {
             TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
             const int acc = it & 1;
-            ok = mbar_wait_cluster(smem_u32(&tmem_full[acc]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 19);
+            ok = mbar_wait_idle(smem_u32(&tmem_full[acc]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 19);
             if (!ok) break;
             tc_fence_after();
             const long long row0 = (long long)t.m0 + my_m + q * 32;
@@ -330,72 +303,87 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
         }
     } else if (DEQ) {
         // =============================== dequant warps (both CTAs) ===============================
+        // The warps form DQG groups; group g expands the stages whose running index is g modulo
+        // DQG, so one stage's chain (code read, expand, store, proxy fence, arrive) may take DQG
+        // MMA stage times before it limits the tensor pipe.
         const int dw = warp - (2 + EPI_WARPS);
-        constexpr int ITERS = (P_C_STAGE / 4) / (DQ_WARPS * 32);     // 4 code words per lane and stage
+        constexpr int ITERS = (P_C_STAGE / 4) / (GW * 32);           // code words per lane and stage
+        const int g = dw / GW, gw = dw % GW;
+        // word i of a lane sits ROWS_I rows below word i-1; the swizzle term repeats every PER words
+        constexpr int ROWS_I = (BMODE == B_DEQ_MN) ? 2 * GW : 4 * GW;
+        constexpr int PER = ROWS_I >= 8 ? 1 : 8 / ROWS_I;
+        const int r0 = (BMODE == B_DEQ_MN) ? gw * 2 + (lane >> 4) : gw * 4 + (lane >> 3);   // row of word 0
+        const int c0 = (BMODE == B_DEQ_MN) ? (lane & 15) : (lane & 7);
+        uint32_t dst0[PER];
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int r = r0 + i * ROWS_I;
+            if (BMODE == B_DEQ_MN) dst0[i] = (uint32_t)((c0 / 8) * 8192 + (r >> 3) * 1024 + (r & 7) * 128 + (((c0 & 7) ^ (r & 7)) << 4));
+            else dst0[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c0 ^ (r & 7)) << 4));
+        }
+        constexpr uint32_t DST_STEP = (uint32_t)(PER * ROWS_I / 8) * 1024u;      // bytes per PER words
+        const int gpr = p.w_cols / 128;
         Ring rc = {0, 0}, rb = {0, 0};
         bool ok = true;
-        uint32_t dst_off[ITERS];
-        int srow[ITERS], scol[ITERS];
-#pragma unroll
-        for (int i = 0; i < ITERS; i++) {
-            int wi = (i * DQ_WARPS + dw) * 32 + lane;
-            if (BMODE == B_DEQ_MN) {
-                int k = wi / 16, c = wi % 16;            // 64 rows (k) x 16 words (128 columns)
-                dst_off[i] = (uint32_t)((c / 8) * 8192 + (k >> 3) * 1024 + (k & 7) * 128 + (((c & 7) ^ (k & 7)) << 4));
-                srow[i] = k; scol[i] = c * 8;
-            } else {
-                int n = wi / 8, c = wi % 8;              // 128 rows (n) x 8 words (64 k)
-                dst_off[i] = (uint32_t)((n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4));
-                srow[i] = n; scol[i] = c * 8;
-            }
-        }
-        const int gpr = p.w_cols / 128;
+        const uint32_t full0 = map_to_cta(smem_u32(&full[0]), 0);    // the leader's stage barriers
+        int kc = 0;                                                  // running stage index of this CTA
         for (int tile = pair; ok && tile < total; tile += npairs) {
             TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
             for (int seg = 0; ok && seg < p.nseg; seg++) {
                 const float *sp = DUAL ? p.scales[rank] : p.scales[seg];
-                int sbase[ITERS];
-#pragma unroll
-                for (int i = 0; i < ITERS; i++) {
-                    if (BMODE == B_DEQ_MN) {
-                        int ncol = (DUAL ? t.n_t * 128 : t.n_t * P_BN + my_n) + scol[i];
-                        sbase[i] = (t.e * p.w_rows + srow[i]) * gpr + ncol / 128;
-                    } else {
-                        sbase[i] = (t.e * p.w_rows + t.n_t * P_BN + my_n + srow[i]) * gpr;
-                    }
-                }
-                const int sstep = (BMODE == B_DEQ_MN) ? BK * gpr : 0;
+                // scale of word i at stage ks: sp[sb + r(i)*gpr + ks*sstep] (MN) / sp[sb + r(i)*gpr + ks*64/128] (K)
+                int sb;
+                if (BMODE == B_DEQ_MN) sb = (t.e * p.w_rows + r0) * gpr + (DUAL ? t.n_t * 128 : t.n_t * P_BN + my_n) / 128;
+                else sb = (t.e * p.w_rows + t.n_t * P_BN + my_n + r0) * gpr;
+                const int rstep = ROWS_I * gpr;
+                int ks = (g - kc % DQG + DQG) % DQG;                 // first stage of this group in the tile
+                for (int i = 0; i < ks && i < t.ksteps; i++) { rc.next(NSC); rb.next(NS); }
                 float cur[ITERS], nxt[ITERS];
+                if (ks < t.ksteps) {
+                    const int so = (BMODE == B_DEQ_MN) ? ks * BK * gpr : (ks * BK) / 128;
 #pragma unroll
-                for (int i = 0; i < ITERS; i++) cur[i] = __ldg(sp + sbase[i]);
-                for (int ks = 0; ks < t.ksteps; ks++) {
-                    if (ks + 1 < t.ksteps) {
+                    for (int i = 0; i < ITERS; i++) cur[i] = __ldg(sp + sb + i * rstep + so);
+                }
+                for (; ks < t.ksteps; ks += DQG) {
+                    if (ks + DQG < t.ksteps) {
+                        const int so = (BMODE == B_DEQ_MN) ? (ks + DQG) * BK * gpr : ((ks + DQG) * BK) / 128;
 #pragma unroll
-                        for (int i = 0; i < ITERS; i++) {
-                            int idx = (BMODE == B_DEQ_MN) ? sbase[i] + (ks + 1) * sstep : sbase[i] + ((ks + 1) * BK) / 128;
-                            nxt[i] = __ldg(sp + idx);
-                        }
+                        for (int i = 0; i < ITERS; i++) nxt[i] = __ldg(sp + sb + i * rstep + so);
                     }
-                    ok = mbar_wait(smem_u32(&full_c[rc.idx]), rc.phase, abort_flag, p.errword, 20);
+                    ok = mbar_wait_idle(smem_u32(&full_c[rc.idx]), rc.phase, abort_flag, p.errword, 20);
                     if (!ok) break;
                     const uint32_t *cw = reinterpret_cast<const uint32_t *>(sC + rc.idx * P_C_STAGE);
                     uint32_t w[ITERS];
+                    if (p.dbg < 3) {
 #pragma unroll
-                    for (int i = 0; i < ITERS; i++) w[i] = cw[(i * DQ_WARPS + dw) * 32 + lane];
-                    ok = mbar_wait(smem_u32(&empty_b[rb.idx]), rb.phase ^ 1u, abort_flag, p.errword, 21);
+                    for (int i = 0; i < ITERS; i++) w[i] = cw[(i * GW + gw) * 32 + lane];
+                    }
+                    ok = mbar_wait_idle(smem_u32(&empty[rb.idx]), rb.phase ^ 1u, abort_flag, p.errword, 21);
                     if (!ok) break;
                     uint8_t *bdst = sB + rb.idx * P_B_STAGE;
+                    if (p.dbg == 0) {
 #pragma unroll
                     for (int i = 0; i < ITERS; i++)
-                        *reinterpret_cast<uint4 *>(bdst + dst_off[i]) = dequant8(w[i], __float2bfloat162_rn(cur[i]));
-                    fence_proxy_async();
+                        *reinterpret_cast<uint4 *>(bdst + dst0[i % PER] + (uint32_t)(i / PER) * DST_STEP) = dequant8(w[i], __float2bfloat162_rn(cur[i]));
+                    } else if (p.dbg == 1) {       // math, one store
+                        uint4 acc4 = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                        for (int i = 0; i < ITERS; i++) { uint4 v = dequant8(w[i], __float2bfloat162_rn(cur[i])); acc4.x ^= v.x; acc4.y ^= v.y; acc4.z ^= v.z; acc4.w ^= v.w; }
+                        *reinterpret_cast<uint4 *>(bdst + dst0[0]) = acc4;
+                    } else if (p.dbg == 2) {       // stores, no math
+#pragma unroll
+                    for (int i = 0; i < ITERS; i++)
+                        *reinterpret_cast<uint4 *>(bdst + dst0[i % PER] + (uint32_t)(i / PER) * DST_STEP) = make_uint4(w[i], w[i], w[i], __float_as_uint(cur[i]));
+                    }
+                    if (p.dbg != 4) fence_proxy_async();
                     __syncwarp();
-                    if (lane == 0) { mbar_arrive(smem_u32(&full_b[rb.idx])); mbar_arrive(smem_u32(&empty_c[rc.idx])); }
-                    rc.next(NSC);
-                    rb.next(NSB);
+                    if (lane == 0) { mbar_arrive_remote(full0 + (uint32_t)rb.idx * 8u); mbar_arrive(smem_u32(&empty_c[rc.idx])); }
+                    const int adv = ks + DQG <= t.ksteps ? DQG : t.ksteps - ks;
+                    for (int i = 0; i < adv; i++) { rc.next(NSC); rb.next(NS); }
 #pragma unroll
                     for (int i = 0; i < ITERS; i++) cur[i] = nxt[i];
                 }
+                kc += t.ksteps;
             }
         }
     }
