@@ -234,6 +234,37 @@ __device__ __forceinline__ void warp_load_rows(uint8_t *stage, uint4 *v, int lan
     __syncwarp();
 }
 
+// 32 rows x 128 bytes in a 4 KiB block: 16-byte vector c of row r sits at a swizzled slot, so
+// both "lane = row" accesses and "8 lanes = one whole row" accesses are free of bank conflicts.
+__device__ __forceinline__ uint4 *blk_vec(uint8_t *blk, int r, int c)
+{
+    return reinterpret_cast<uint4 *>(blk + r * 128 + ((c ^ (r & 7)) << 4));
+}
+// the block to / from global rows of 128 bytes: every access instruction covers 4 whole rows
+__device__ __forceinline__ void blk_store(uint8_t *blk, int lane, uint8_t *g0, long long pitch, int valid_rows)
+{
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int r = j * 4 + (lane >> 3), c = lane & 7;
+        const uint4 x = *blk_vec(blk, r, c);
+        if (r < valid_rows) *reinterpret_cast<uint4 *>(g0 + (long long)r * pitch + c * 16) = x;
+    }
+    __syncwarp();
+}
+__device__ __forceinline__ void blk_load(uint8_t *blk, int lane, const uint8_t *g0, long long pitch, int valid_rows)
+{
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int r = j * 4 + (lane >> 3), c = lane & 7;
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (r < valid_rows) x = __ldg(reinterpret_cast<const uint4 *>(g0 + (long long)r * pitch + c * 16));
+        *blk_vec(blk, r, c) = x;
+    }
+}
+// staging bytes per epilogue warp
+__host__ __device__ constexpr int epi_stage_bytes(int epi) { return epi == EPI_SWIGLU_BWD ? 8192 : 4096; }
+
 struct Ring {
     int idx; uint32_t phase;
     __device__ __forceinline__ void next(int n) { if (++idx == n) { idx = 0; phase ^= 1u; } }
@@ -277,7 +308,26 @@ template <int EPI>
 __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stage, int lane, uint32_t tbase,
                                               long long rbase, long long col0, int valid, bool have_acc, uint32_t u_off)
 {
-    if (EPI == EPI_STORE || EPI == EPI_ACCUM) {
+    if (EPI == EPI_STORE && p.out_dtype == QLMB_BF16 && !p.resid && p.beta == 0.0f) {
+        // plain bf16 store: two blocks of 64 columns, each written with whole 128-byte rows
+#pragma unroll 1
+        for (int half = 0; half < 2; half++) {
+#pragma unroll 1
+            for (int cc = 0; cc < 2; cc++) {
+                uint32_t v[32];
+                tmem_ld32(tbase + half * 64 + cc * 32, v);
+                tmem_ld_wait();
+                uint4 w[4];
+                __nv_bfloat162 *hw = reinterpret_cast<__nv_bfloat162 *>(w);
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    hw[i] = have_acc ? __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])) : __floats2bfloat162_rn(0.0f, 0.0f);
+#pragma unroll
+                for (int k = 0; k < 4; k++) *blk_vec(stage, lane, cc * 4 + k) = w[k];
+            }
+            blk_store(stage, lane, reinterpret_cast<uint8_t *>((bf16 *)p.out + rbase * p.ldo + col0 + half * 64), p.ldo * 2, valid);
+        }
+    } else if (EPI == EPI_STORE || EPI == EPI_ACCUM) {
 #pragma unroll 1
         for (int c = 0; c < 4; c++) {
             uint32_t v[32];
@@ -326,53 +376,90 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
             }
         }
     } else if (EPI == EPI_SWIGLU) {
+        // three passes over the warp's 64 activation columns (activation, gate, up), each staged
+        // as one block and written with whole 128-byte rows; the accumulators are re-read from
+        // TMEM per pass, which costs less than holding them
+        const long long o = rbase * p.ldo + col0;
 #pragma unroll 1
-        for (int c = 0; c < 4; c++) {
-            uint32_t g[16], u[16];
-            tmem_ld16(tbase + c * 16, g);
-            tmem_ld16(tbase + u_off + c * 16, u);
-            tmem_ld_wait();
-            const long long o = rbase * p.ldo + col0 + c * 16;
-            uint4 wa[2], wg[2], wu[2];
-            __nv_bfloat162 *ha = reinterpret_cast<__nv_bfloat162 *>(wa), *hg = reinterpret_cast<__nv_bfloat162 *>(wg),
-                           *hu = reinterpret_cast<__nv_bfloat162 *>(wu);
+        for (int pass = 0; pass < 3; pass++) {
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t g[16], u[16];
+                uint4 w[2];
+                __nv_bfloat162 *hw = reinterpret_cast<__nv_bfloat162 *>(w);
+                if (pass == 0) {
+                    tmem_ld16(tbase + c * 16, g);
+                    tmem_ld16(tbase + u_off + c * 16, u);
+                    tmem_ld_wait();
 #pragma unroll
-            for (int k = 0; k < 8; k++) {
-                float g0 = __uint_as_float(g[2 * k]), g1 = __uint_as_float(g[2 * k + 1]);
-                float u0 = __uint_as_float(u[2 * k]), u1 = __uint_as_float(u[2 * k + 1]);
-                ha[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
-                hg[k] = __floats2bfloat162_rn(g0, g1);
-                hu[k] = __floats2bfloat162_rn(u0, u1);
+                    for (int k = 0; k < 8; k++) {
+                        float g0 = __uint_as_float(g[2 * k]), g1 = __uint_as_float(g[2 * k + 1]);
+                        float u0 = __uint_as_float(u[2 * k]), u1 = __uint_as_float(u[2 * k + 1]);
+                        hw[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
+                    }
+                } else {
+                    tmem_ld16(tbase + (pass == 2 ? u_off : 0u) + c * 16, g);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int k = 0; k < 8; k++) hw[k] = __floats2bfloat162_rn(__uint_as_float(g[2 * k]), __uint_as_float(g[2 * k + 1]));
+                }
+                *blk_vec(stage, lane, 2 * c) = w[0];
+                *blk_vec(stage, lane, 2 * c + 1) = w[1];
             }
-            warp_store_rows<2>(stage, wa, lane, reinterpret_cast<uint8_t *>(p.ap + o), p.ldo * 2, valid);
-            warp_store_rows<2>(stage, wg, lane, reinterpret_cast<uint8_t *>(p.gp + o), p.ldo * 2, valid);
-            warp_store_rows<2>(stage, wu, lane, reinterpret_cast<uint8_t *>(p.up + o), p.ldo * 2, valid);
+            bf16 *dst = pass == 0 ? p.ap : pass == 1 ? p.gp : p.up;
+            blk_store(stage, lane, reinterpret_cast<uint8_t *>(dst + o), p.ldo * 2, valid);
         }
     } else {   // EPI_SWIGLU_BWD: accumulator = d(act); dg = da*u*silu'(g), du = da*silu(g)
+        // Two groups of 64 columns.  The gate and up pieces of a group are staged as two blocks
+        // (whole 128-byte rows), the results overwrite them in place and leave the same way.
+        // Group 0 was staged by epilogue_prefetch before the accumulator was ready.
+        const long long o0 = rbase * p.ldo + col0;
+        const long long pitch = p.ldo * 2;
+        uint8_t *bg = stage, *bu = stage + 4096;
 #pragma unroll 1
-        for (int c = 0; c < 8; c++) {
-            uint32_t v[16];
-            tmem_ld16(tbase + c * 16, v);
-            const long long o = rbase * p.ldo + col0 + c * 16;
-            uint4 rg[2], ru[2], wdg[2], wdu[2];
-            warp_load_rows<2>(stage, rg, lane, reinterpret_cast<const uint8_t *>(p.gp + o), p.ldo * 2, valid);
-            warp_load_rows<2>(stage, ru, lane, reinterpret_cast<const uint8_t *>(p.up + o), p.ldo * 2, valid);
-            tmem_ld_wait();
-            const __nv_bfloat162 *hg = reinterpret_cast<const __nv_bfloat162 *>(rg), *hu = reinterpret_cast<const __nv_bfloat162 *>(ru);
-            __nv_bfloat162 *hdg = reinterpret_cast<__nv_bfloat162 *>(wdg), *hdu = reinterpret_cast<__nv_bfloat162 *>(wdu);
-#pragma unroll
-            for (int k = 0; k < 8; k++) {
-                float2 gg = __bfloat1622float2(hg[k]), uu = __bfloat1622float2(hu[k]);
-                float d0 = __uint_as_float(v[2 * k]), d1 = __uint_as_float(v[2 * k + 1]);
-                float s0 = sigmoid_f(gg.x), s1 = sigmoid_f(gg.y);
-                float dg0 = d0 * uu.x * (s0 + gg.x * s0 * (1.0f - s0)), dg1 = d1 * uu.y * (s1 + gg.y * s1 * (1.0f - s1));
-                float du0 = d0 * gg.x * s0, du1 = d1 * gg.y * s1;
-                hdg[k] = __floats2bfloat162_rn(dg0, dg1);
-                hdu[k] = __floats2bfloat162_rn(du0, du1);
+        for (int grp = 0; grp < 2; grp++) {
+            if (grp == 1) {
+                blk_load(bg, lane, reinterpret_cast<const uint8_t *>(p.gp + o0 + 64), pitch, valid);
+                blk_load(bu, lane, reinterpret_cast<const uint8_t *>(p.up + o0 + 64), pitch, valid);
             }
-            warp_store_rows<2>(stage, wdg, lane, reinterpret_cast<uint8_t *>(p.dgp + o), p.ldo * 2, valid);
-            warp_store_rows<2>(stage, wdu, lane, reinterpret_cast<uint8_t *>(p.dup + o), p.ldo * 2, valid);
+            __syncwarp();
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[16];
+                tmem_ld16(tbase + grp * 64 + c * 16, v);
+                uint4 rg[2], ru[2], wdg[2], wdu[2];
+#pragma unroll
+                for (int k = 0; k < 2; k++) { rg[k] = *blk_vec(bg, lane, 2 * c + k); ru[k] = *blk_vec(bu, lane, 2 * c + k); }
+                tmem_ld_wait();
+                const __nv_bfloat162 *hg = reinterpret_cast<const __nv_bfloat162 *>(rg), *hu = reinterpret_cast<const __nv_bfloat162 *>(ru);
+                __nv_bfloat162 *hdg = reinterpret_cast<__nv_bfloat162 *>(wdg), *hdu = reinterpret_cast<__nv_bfloat162 *>(wdu);
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    float2 gg = __bfloat1622float2(hg[k]), uu = __bfloat1622float2(hu[k]);
+                    float d0 = __uint_as_float(v[2 * k]), d1 = __uint_as_float(v[2 * k + 1]);
+                    float s0 = sigmoid_f(gg.x), s1 = sigmoid_f(gg.y);
+                    float dg0 = d0 * uu.x * (s0 + gg.x * s0 * (1.0f - s0)), dg1 = d1 * uu.y * (s1 + gg.y * s1 * (1.0f - s1));
+                    float du0 = d0 * gg.x * s0, du1 = d1 * gg.y * s1;
+                    hdg[k] = __floats2bfloat162_rn(dg0, dg1);
+                    hdu[k] = __floats2bfloat162_rn(du0, du1);
+                }
+#pragma unroll
+                for (int k = 0; k < 2; k++) { *blk_vec(bg, lane, 2 * c + k) = wdg[k]; *blk_vec(bu, lane, 2 * c + k) = wdu[k]; }
+            }
+            blk_store(bg, lane, reinterpret_cast<uint8_t *>(p.dgp + o0 + grp * 64), pitch, valid);
+            blk_store(bu, lane, reinterpret_cast<uint8_t *>(p.dup + o0 + grp * 64), pitch, valid);
         }
+    }
+}
+
+// Work an epilogue warp can do for its next tile before that tile's accumulator is complete.
+template <int EPI>
+__device__ __forceinline__ void epilogue_prefetch(const GemmParams &p, uint8_t *stage, int lane, long long rbase, long long col0, int valid)
+{
+    if (EPI == EPI_SWIGLU_BWD) {
+        const long long o0 = rbase * p.ldo + col0;
+        blk_load(stage, lane, reinterpret_cast<const uint8_t *>(p.gp + o0), p.ldo * 2, valid);
+        blk_load(stage + 4096, lane, reinterpret_cast<const uint8_t *>(p.up + o0), p.ldo * 2, valid);
     }
 }
 
@@ -394,7 +481,7 @@ k_gemm(const __grid_constant__ GemmParams p)
     uint8_t *sB = sA + NSA * A_STAGE_BYTES;
     uint8_t *sC = sB + NSB * B_STAGE_BYTES;
     uint8_t *sE = sC + (DEQ ? NSC * C_STAGE_BYTES : 0);       // 8 epilogue warps x 4 KiB staging
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sE + EPI_WARPS * 4096);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sE + EPI_WARPS * epi_stage_bytes(EPI));
     uint64_t *full_a = bars, *empty_a = full_a + NSA, *full_b = empty_a + NSA, *empty_b = full_b + NSB;
     uint64_t *full_c = empty_b + NSB, *empty_c = full_c + NSC, *tmem_full = empty_c + NSC, *tmem_empty = tmem_full + 2;
     uint64_t *spare = tmem_empty + 2;
@@ -542,23 +629,25 @@ k_gemm(const __grid_constant__ GemmParams p)
         // registers, then the row pieces go through a swizzled 4 KiB staging buffer so that
         // every global store instruction writes whole row pieces.
         const int q = warp & 3, h = (warp - 2) >> 2;
-        uint8_t *stage = sE + (warp - 2) * 4096;
+        uint8_t *stage = sE + (warp - 2) * epi_stage_bytes(EPI);
         bool ok = true;
         int it = 0;
         for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x, it++) {
             TileInfo t = decode_tile<SCHED>(p, tile, ntr);
             const int acc = it & 1;
+            const long long row0 = (long long)t.m0 + h * BM + q * 32;                // first row of this warp
+            int valid = 32;
+            if (SCHED != SCHED_ROWS) { long long left = (long long)p.M - row0; valid = left < 0 ? 0 : (left < 32 ? (int)left : 32); }
+            const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
+            const long long col0 = (long long)t.n_t * (EPI == EPI_SWIGLU ? BN / 2 : BN);
+            if (h < t.halves) epilogue_prefetch<EPI>(p, stage, lane, rbase, col0, valid);
             ok = mbar_wait(smem_u32(&tmem_full[acc]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 6);
             if (!ok) break;
             tc_fence_after();
             if (h < t.halves) {
                 const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * ACC_COLS + (uint32_t)h * BN;
-                const long long row0 = (long long)t.m0 + h * BM + q * 32;            // first row of this warp
                 const bool have_acc = (SCHED != SCHED_GROUPK) || t.ksteps > 0;
-                int valid = 32;
-                if (SCHED != SCHED_ROWS) { long long left = (long long)p.M - row0; valid = left < 0 ? 0 : (left < 32 ? (int)left : 32); }
-                const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
-                epilogue_rows<EPI>(p, stage, lane, tbase, rbase, (long long)t.n_t * (EPI == EPI_SWIGLU ? BN / 2 : BN), valid, have_acc, BN / 2);
+                epilogue_rows<EPI>(p, stage, lane, tbase, rbase, col0, valid, have_acc, BN / 2);
             }
             tc_fence_before();
             __syncwarp();
@@ -701,7 +790,7 @@ static int launch_inst(const GemmParams &p, int grid, cudaStream_t st)
 {
     constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
     constexpr int NSA = DEQ ? 3 : 4, NSB = DEQ ? 3 : 4, NSC = 4;
-    constexpr size_t smem = 1024 + NSA * A_STAGE_BYTES + NSB * B_STAGE_BYTES + (DEQ ? NSC * C_STAGE_BYTES : 0) + EPI_WARPS * 4096 + 512;
+    constexpr size_t smem = 1024 + NSA * A_STAGE_BYTES + NSB * B_STAGE_BYTES + (DEQ ? NSC * C_STAGE_BYTES : 0) + EPI_WARPS * epi_stage_bytes(EPI) + 512;
     static bool configured = false;
     auto kfn = k_gemm<BMODE, EPI, SCHED>;
     if (!configured) {
@@ -717,7 +806,7 @@ template <int BMODE, int EPI, int SCHED, int DQG>
 static int launch_pair_g(const GemmParams &p, long long total, cudaStream_t st)
 {
     constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
-    constexpr size_t smem = 1024 + (size_t)(DEQ ? 5 : 6) * (P_A_STAGE + P_B_STAGE) + (DEQ ? 8 * P_C_STAGE : 0) + EPI_WARPS * 4096 + 512;
+    constexpr size_t smem = 1024 + (size_t)(DEQ ? (EPI == EPI_SWIGLU_BWD ? 4 : 5) : 6) * (P_A_STAGE + P_B_STAGE) + (DEQ ? 8 * P_C_STAGE : 0) + EPI_WARPS * epi_stage_bytes(EPI) + 512;
     // persistent kernel: every cluster must be resident at once, so the grid is the number of
     // clusters the device can hold at the same time (asked once per kernel instance)
     static int max_clusters = 0;
@@ -744,13 +833,6 @@ static int launch_pair_g(const GemmParams &p, long long total, cudaStream_t st)
 template <int BMODE, int EPI, int SCHED>
 static int launch_pair(const GemmParams &p, long long total, cudaStream_t st)
 {
-    constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
-    if (DEQ) {
-        static int groups = 0;
-        if (!groups) { const char *e = getenv("QLMB_DQ_GROUPS"); groups = e ? atoi(e) : 2; }
-        if (groups == 1) return launch_pair_g<BMODE, EPI, SCHED, DEQ ? 1 : 2>(p, total, st);
-        if (groups == 4) return launch_pair_g<BMODE, EPI, SCHED, DEQ ? 4 : 2>(p, total, st);
-    }
     return launch_pair_g<BMODE, EPI, SCHED, 2>(p, total, st);     // two dequant stage groups
 }
 

@@ -126,7 +126,7 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
 {
     constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
     constexpr bool DUAL = (EPI == EPI_SWIGLU);           // CTA 0 expands W1 (gate), CTA 1 expands W3 (up)
-    constexpr int NS = DEQ ? 5 : 6, NSC = 8;
+    constexpr int NS = DEQ ? (EPI == EPI_SWIGLU_BWD ? 4 : 5) : 6, NSC = 8;
     constexpr int GW = DQ_WARPS / DQG;                   // dequant warps per stage group
     constexpr uint32_t IDESC = make_idesc(256, P_BN, BMODE == AB_TMA_MN ? 1 : 0, (BMODE == B_DEQ_MN || BMODE == AB_TMA_MN) ? 1 : 0);
     constexpr uint32_t TMEM_COLS = 2 * P_BN;
@@ -138,7 +138,7 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
     uint8_t *sB = sA + NS * P_A_STAGE;
     uint8_t *sC = sB + NS * P_B_STAGE;
     uint8_t *sE = sC + (DEQ ? NSC * P_C_STAGE : 0);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sE + EPI_WARPS * 4096);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sE + EPI_WARPS * epi_stage_bytes(EPI));
     uint64_t *full = bars, *empty = full + NS;
     uint64_t *full_c = empty + NS, *empty_c = full_c + NSC;
     uint64_t *tmem_full = empty_c + NSC, *tmem_empty = tmem_full + 2, *spare = tmem_empty + 2;
@@ -272,27 +272,29 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
         // =============================== epilogue (both CTAs) ===============================
         // warp (q, h): q = TMEM lane quarter (= warp id mod 4), h = which 128 of the 256 columns
         const int q = warp & 3, h = (warp - 2) >> 2;
-        uint8_t *stage = sE + (warp - 2) * 4096;
+        uint8_t *stage = sE + (warp - 2) * epi_stage_bytes(EPI);
         bool ok = true;
         int it = 0;
         for (int tile = pair; ok && tile < total; tile += npairs, it++) {
             TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
             const int acc = it & 1;
-            ok = mbar_wait_idle(smem_u32(&tmem_full[acc]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 19);
-            if (!ok) break;
-            tc_fence_after();
             const long long row0 = (long long)t.m0 + my_m + q * 32;
             int valid = 32;
             if (SCHED == SCHED_ROWS) valid = ((int)rank < t.halves) ? 32 : 0;
             else { long long left = (long long)p.M - row0; valid = left < 0 ? 0 : (left < 32 ? (int)left : 32); }
+            const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
+            const long long col0 = (EPI == EPI_SWIGLU) ? (long long)t.n_t * 128 + h * 64 : (long long)t.n_t * P_BN + h * 128;
+            if (valid > 0) epilogue_prefetch<EPI>(p, stage, lane, rbase, col0, valid);
+            ok = mbar_wait_idle(smem_u32(&tmem_full[acc]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 19);
+            if (!ok) break;
+            tc_fence_after();
             if (valid > 0) {
                 const bool have_acc = (SCHED != SCHED_GROUPK) || t.ksteps > 0;
-                const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
                 const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * P_BN;
                 if (EPI == EPI_SWIGLU)
-                    epilogue_rows<EPI>(p, stage, lane, tbase + (uint32_t)h * 64, rbase, (long long)t.n_t * 128 + h * 64, valid, have_acc, 128);
+                    epilogue_rows<EPI>(p, stage, lane, tbase + (uint32_t)h * 64, rbase, col0, valid, have_acc, 128);
                 else
-                    epilogue_rows<EPI>(p, stage, lane, tbase + (uint32_t)h * 128, rbase, (long long)t.n_t * P_BN + h * 128, valid, have_acc, 0);
+                    epilogue_rows<EPI>(p, stage, lane, tbase + (uint32_t)h * 128, rbase, col0, valid, have_acc, 0);
             }
             tc_fence_before();
             __syncwarp();
