@@ -42,6 +42,8 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;
 struct GemmParams {
     alignas(64) CUtensorMap a_map[2];
     alignas(64) CUtensorMap w_map[2];
+    alignas(64) CUtensorMap o_map[3];      // bf16 outputs written by bulk tensor stores (boxes of 32 rows x 64 columns)
+    int o_tma;                             // 1: o_map valid
     const float *scales[2];
     int nseg, ksteps;
     int M, N, E;
@@ -107,6 +109,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+
+// shared -> global bulk tensor store of one box; rows or columns outside the tensor are not written
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
 { asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory"); }
@@ -262,6 +274,19 @@ __device__ __forceinline__ void blk_load(uint8_t *blk, int lane, const uint8_t *
         *blk_vec(blk, r, c) = x;
     }
 }
+// The block layout is the 128-byte swizzle of a bulk tensor copy, so a staged block can leave as
+// one asynchronous store issued by lane 0.  blk_reuse() must precede the next write to the block.
+__device__ __forceinline__ void blk_store_bulk(uint8_t *blk, int lane, const CUtensorMap *map, int x, int y)
+{
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) { tma_store_2d(map, smem_u32(blk), x, y); bulk_commit(); }
+}
+__device__ __forceinline__ void blk_reuse(int lane)
+{
+    if (lane == 0) bulk_wait_read();
+    __syncwarp();
+}
 // staging bytes per epilogue warp
 __host__ __device__ constexpr int epi_stage_bytes(int epi) { return epi == EPI_SWIGLU_BWD ? 8192 : 4096; }
 
@@ -312,6 +337,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
         // plain bf16 store: two blocks of 64 columns, each written with whole 128-byte rows
 #pragma unroll 1
         for (int half = 0; half < 2; half++) {
+            if (p.o_tma) blk_reuse(lane);
 #pragma unroll 1
             for (int cc = 0; cc < 2; cc++) {
                 uint32_t v[32];
@@ -325,7 +351,8 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
 #pragma unroll
                 for (int k = 0; k < 4; k++) *blk_vec(stage, lane, cc * 4 + k) = w[k];
             }
-            blk_store(stage, lane, reinterpret_cast<uint8_t *>((bf16 *)p.out + rbase * p.ldo + col0 + half * 64), p.ldo * 2, valid);
+            if (p.o_tma) blk_store_bulk(stage, lane, &p.o_map[0], (int)(col0 + half * 64), (int)rbase);
+            else blk_store(stage, lane, reinterpret_cast<uint8_t *>((bf16 *)p.out + rbase * p.ldo + col0 + half * 64), p.ldo * 2, valid);
         }
     } else if (EPI == EPI_STORE || EPI == EPI_ACCUM) {
 #pragma unroll 1
@@ -382,24 +409,36 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
         const long long o = rbase * p.ldo + col0;
 #pragma unroll 1
         for (int pass = 0; pass < 3; pass++) {
+            if (p.o_tma) blk_reuse(lane);
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
                 uint32_t g[16], u[16];
                 uint4 w[2];
                 __nv_bfloat162 *hw = reinterpret_cast<__nv_bfloat162 *>(w);
                 if (pass == 0) {
+                    if (p.dbg != 8) {
                     tmem_ld16(tbase + c * 16, g);
                     tmem_ld16(tbase + u_off + c * 16, u);
                     tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 16; k++) { g[k] = 0x3f800000u + k; u[k] = 0x3f000000u + lane; }
+                    }
 #pragma unroll
                     for (int k = 0; k < 8; k++) {
                         float g0 = __uint_as_float(g[2 * k]), g1 = __uint_as_float(g[2 * k + 1]);
                         float u0 = __uint_as_float(u[2 * k]), u1 = __uint_as_float(u[2 * k + 1]);
-                        hw[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
+                        if (p.dbg == 9) hw[k] = __floats2bfloat162_rn(g0 * u0, g1 * u1);
+                        else hw[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
                     }
                 } else {
+                    if (p.dbg != 8) {
                     tmem_ld16(tbase + (pass == 2 ? u_off : 0u) + c * 16, g);
                     tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 16; k++) g[k] = 0x3f800000u + k;
+                    }
 #pragma unroll
                     for (int k = 0; k < 8; k++) hw[k] = __floats2bfloat162_rn(__uint_as_float(g[2 * k]), __uint_as_float(g[2 * k + 1]));
                 }
@@ -407,7 +446,8 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
                 *blk_vec(stage, lane, 2 * c + 1) = w[1];
             }
             bf16 *dst = pass == 0 ? p.ap : pass == 1 ? p.gp : p.up;
-            blk_store(stage, lane, reinterpret_cast<uint8_t *>(dst + o), p.ldo * 2, valid);
+            if (p.o_tma) blk_store_bulk(stage, lane, &p.o_map[pass], (int)col0, (int)rbase);
+            else blk_store(stage, lane, reinterpret_cast<uint8_t *>(dst + o), p.ldo * 2, valid);
         }
     } else {   // EPI_SWIGLU_BWD: accumulator = d(act); dg = da*u*silu'(g), du = da*silu(g)
         // Two groups of 64 columns.  The gate and up pieces of a group are staged as two blocks
@@ -419,6 +459,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
 #pragma unroll 1
         for (int grp = 0; grp < 2; grp++) {
             if (grp == 1) {
+                if (p.o_tma) blk_reuse(lane);
                 blk_load(bg, lane, reinterpret_cast<const uint8_t *>(p.gp + o0 + 64), pitch, valid);
                 blk_load(bu, lane, reinterpret_cast<const uint8_t *>(p.up + o0 + 64), pitch, valid);
             }
@@ -446,8 +487,13 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
 #pragma unroll
                 for (int k = 0; k < 2; k++) { *blk_vec(bg, lane, 2 * c + k) = wdg[k]; *blk_vec(bu, lane, 2 * c + k) = wdu[k]; }
             }
-            blk_store(bg, lane, reinterpret_cast<uint8_t *>(p.dgp + o0 + grp * 64), pitch, valid);
-            blk_store(bu, lane, reinterpret_cast<uint8_t *>(p.dup + o0 + grp * 64), pitch, valid);
+            if (p.o_tma) {
+                blk_store_bulk(bg, lane, &p.o_map[0], (int)(col0 + grp * 64), (int)rbase);
+                blk_store_bulk(bu, lane, &p.o_map[1], (int)(col0 + grp * 64), (int)rbase);
+            } else {
+                blk_store(bg, lane, reinterpret_cast<uint8_t *>(p.dgp + o0 + grp * 64), pitch, valid);
+                blk_store(bu, lane, reinterpret_cast<uint8_t *>(p.dup + o0 + grp * 64), pitch, valid);
+            }
         }
     }
 }
@@ -458,6 +504,7 @@ __device__ __forceinline__ void epilogue_prefetch(const GemmParams &p, uint8_t *
 {
     if (EPI == EPI_SWIGLU_BWD) {
         const long long o0 = rbase * p.ldo + col0;
+        if (p.o_tma) blk_reuse(lane);
         blk_load(stage, lane, reinterpret_cast<const uint8_t *>(p.gp + o0), p.ldo * 2, valid);
         blk_load(stage + 4096, lane, reinterpret_cast<const uint8_t *>(p.up + o0), p.ldo * 2, valid);
     }
@@ -653,6 +700,7 @@ k_gemm(const __grid_constant__ GemmParams p)
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tmem_empty[acc]));
         }
+        if (lane == 0) bulk_wait_all();                  // outstanding bulk stores of this warp
     } else if (DEQ) {
         // =============================== dequant warps ===============================
         const int dw = warp - (2 + EPI_WARPS);
@@ -892,6 +940,23 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
             rc = make_map(&p.w_map[s], g.w[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w_cols / 2, wrows_total, g.w_cols / 2, 32, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
         }
         if (rc) return rc;
+    }
+    // bf16 outputs leave through bulk tensor stores when their layout allows a tensor map
+    {
+        const unsigned long long orows = (g.sched == SCHED_ROWS) ? (unsigned long long)g.a_rows : (unsigned long long)g.M;
+        const void *optr[3] = {nullptr, nullptr, nullptr};
+        int no = 0;
+        if (g.epi == EPI_STORE && g.out_dtype == QLMB_BF16 && !g.resid && g.beta == 0.0f) { optr[0] = g.out; no = 1; }
+        else if (g.epi == EPI_SWIGLU) { optr[0] = g.ap; optr[1] = g.gp; optr[2] = g.up; no = 3; }
+        else if (g.epi == EPI_SWIGLU_BWD) { optr[0] = g.dgp; optr[1] = g.dup; no = 2; }
+        bool can = no > 0 && (g.ldo % 8) == 0 && g.sched != SCHED_GROUPK && orows > 0;
+        for (int i = 0; i < no && can; i++) can = optr[i] && (((uintptr_t)optr[i]) & 15) == 0;
+        for (int i = 0; i < no && can; i++) {
+            rc = make_map(&p.o_map[i], optr[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (unsigned long long)g.ldo, orows,
+                          (unsigned long long)g.ldo * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc) return rc;
+        }
+        p.o_tma = can ? 1 : 0;
     }
     long long total;
     if (g.sched == SCHED_DENSE) total = (long long)p.tiles_m * p.tiles_n;

@@ -303,6 +303,7 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                 if (leader) mbar_arrive(te); else mbar_arrive_remote(map_to_cta(te, 0));
             }
         }
+        if (lane == 0) bulk_wait_all();                  // outstanding bulk stores of this warp
     } else if (DEQ) {
         // =============================== dequant warps (both CTAs) ===============================
         // The warps form DQG groups; group g expands the stages whose running index is g modulo
