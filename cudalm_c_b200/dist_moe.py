@@ -110,9 +110,10 @@ class ExpertParallelLayer:
         n = int(np.prod(shape)) * torch.empty(0, dtype=dtype).element_size()
         return self.harena[off:off + n].view(dtype).view(*shape)
 
-    def forward(self, fi=None, fn=None):
+    def forward(self, fi=None, fn=None, out=None):
         fi = self.fi if fi is None else fi
         fn = self.fn if fn is None else fn
+        out = self.out if out is None else out
         L, st = lib(), stream_ptr()
         check(L.qlmb_moe_route(self.home, self.hptr, ptr(self.Xs), ptr(fn), st))
         counts = self.member("counts", (self.E,), torch.int32)
@@ -126,20 +127,21 @@ class ExpertParallelLayer:
         all_to_all_rows(self.Xr[:self.R], self.Xs, self.recv, self.send, self.group)
         check(L.qlmb_moe_experts_forward(self.loc, self.eptr, ptr(self.Yr), ptr(self.Xr), ptr(self.tags), self.R, st))
         all_to_all_rows(self.Ys, self.Yr[:self.R], self.send, self.recv, self.group)
-        check(L.qlmb_moe_combine(self.home, self.hptr, ptr(self.out), ptr(fi), ptr(self.Ys), st))
-        return self.out
+        check(L.qlmb_moe_combine(self.home, self.hptr, ptr(out), ptr(fi), ptr(self.Ys), st))
+        return out
 
-    def backward(self, dout=None, fn=None, beta=0.0):
+    def backward(self, dout=None, fn=None, beta=0.0, dfn=None):
         dout = self.dout if dout is None else dout
         fn = self.fn if fn is None else fn
+        dfn = self.dfn if dfn is None else dfn
         L, st = lib(), stream_ptr()
         check(L.qlmb_moe_dgate(self.home, self.hptr, ptr(self.dYs), ptr(dout), ptr(self.Ys), st))
         all_to_all_rows(self.dYr[:self.R], self.dYs, self.recv, self.send, self.group)
         check(L.qlmb_moe_experts_backward(self.loc, self.eptr, ptr(self.dXr), ptr(self.dYr), self.R, ptr(self.dW[0]),
                                           ptr(self.dW[1]), ptr(self.dW[2]), beta, st))
         all_to_all_rows(self.dXs, self.dXr[:self.R], self.send, self.recv, self.group)
-        check(L.qlmb_moe_route_backward(self.home, self.hptr, ptr(self.dfn), ptr(self.dXs), ptr(fn), ptr(self.dWr), beta, st))
-        return self.dfn
+        check(L.qlmb_moe_route_backward(self.home, self.hptr, ptr(dfn), ptr(self.dXs), ptr(fn), ptr(self.dWr), beta, st))
+        return dfn
 
     def step(self):
         self.forward()
