@@ -54,7 +54,6 @@ struct GemmParams {
     const void *resid; float beta;
     bf16 *gp, *up, *ap, *dgp, *dup;
     int *errword;
-    int dbg;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -416,29 +415,18 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
                 uint4 w[2];
                 __nv_bfloat162 *hw = reinterpret_cast<__nv_bfloat162 *>(w);
                 if (pass == 0) {
-                    if (p.dbg != 8) {
                     tmem_ld16(tbase + c * 16, g);
                     tmem_ld16(tbase + u_off + c * 16, u);
                     tmem_ld_wait();
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < 16; k++) { g[k] = 0x3f800000u + k; u[k] = 0x3f000000u + lane; }
-                    }
 #pragma unroll
                     for (int k = 0; k < 8; k++) {
                         float g0 = __uint_as_float(g[2 * k]), g1 = __uint_as_float(g[2 * k + 1]);
                         float u0 = __uint_as_float(u[2 * k]), u1 = __uint_as_float(u[2 * k + 1]);
-                        if (p.dbg == 9) hw[k] = __floats2bfloat162_rn(g0 * u0, g1 * u1);
-                        else hw[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
+                        hw[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
                     }
                 } else {
-                    if (p.dbg != 8) {
                     tmem_ld16(tbase + (pass == 2 ? u_off : 0u) + c * 16, g);
                     tmem_ld_wait();
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < 16; k++) g[k] = 0x3f800000u + k;
-                    }
 #pragma unroll
                     for (int k = 0; k < 8; k++) hw[k] = __floats2bfloat162_rn(__uint_as_float(g[2 * k]), __uint_as_float(g[2 * k + 1]));
                 }
@@ -912,7 +900,6 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
     p.out = g.out; p.out_dtype = g.out_dtype; p.ldo = g.ldo; p.resid = g.resid; p.beta = g.beta;
     p.gp = g.gp; p.up = g.up; p.ap = g.ap; p.dgp = g.dgp; p.dup = g.dup;
     p.errword = device_error_word();
-    { static int dbg = -1; if (dbg < 0) { const char *e = getenv("QLMB_DBG"); dbg = e ? atoi(e) : 0; } p.dbg = dbg; }
     p.scales[0] = g.scales[0]; p.scales[1] = g.scales[1];
     const unsigned long long wrows_total = (unsigned long long)g.E * g.w_rows;
     for (int s = 0; s < (dual ? 2 : g.nseg); s++) {

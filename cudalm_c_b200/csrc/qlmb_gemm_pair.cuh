@@ -357,28 +357,15 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                     if (!ok) break;
                     const uint32_t *cw = reinterpret_cast<const uint32_t *>(sC + rc.idx * P_C_STAGE);
                     uint32_t w[ITERS];
-                    if (p.dbg < 3) {
 #pragma unroll
                     for (int i = 0; i < ITERS; i++) w[i] = cw[(i * GW + gw) * 32 + lane];
-                    }
                     ok = mbar_wait_idle(smem_u32(&empty[rb.idx]), rb.phase ^ 1u, abort_flag, p.errword, 21);
                     if (!ok) break;
                     uint8_t *bdst = sB + rb.idx * P_B_STAGE;
-                    if (p.dbg == 0) {
 #pragma unroll
                     for (int i = 0; i < ITERS; i++)
                         *reinterpret_cast<uint4 *>(bdst + dst0[i % PER] + (uint32_t)(i / PER) * DST_STEP) = dequant8(w[i], __float2bfloat162_rn(cur[i]));
-                    } else if (p.dbg == 1) {       // math, one store
-                        uint4 acc4 = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                        for (int i = 0; i < ITERS; i++) { uint4 v = dequant8(w[i], __float2bfloat162_rn(cur[i])); acc4.x ^= v.x; acc4.y ^= v.y; acc4.z ^= v.z; acc4.w ^= v.w; }
-                        *reinterpret_cast<uint4 *>(bdst + dst0[0]) = acc4;
-                    } else if (p.dbg == 2) {       // stores, no math
-#pragma unroll
-                    for (int i = 0; i < ITERS; i++)
-                        *reinterpret_cast<uint4 *>(bdst + dst0[i % PER] + (uint32_t)(i / PER) * DST_STEP) = make_uint4(w[i], w[i], w[i], __float_as_uint(cur[i]));
-                    }
-                    if (p.dbg != 4) fence_proxy_async();
+                    fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) { mbar_arrive_remote(full0 + (uint32_t)rb.idx * 8u); mbar_arrive(smem_u32(&empty_c[rc.idx])); }
                     const int adv = ks + DQG <= t.ksteps ? DQG : t.ksteps - ks;

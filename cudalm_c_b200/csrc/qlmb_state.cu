@@ -505,9 +505,9 @@ extern "C" int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const f
                 al16(v8) && (!P || al16(P));
     cudaStream_t st = as_stream(stream);
     if (fast) {
-        // elements per lane: 4 by default (smallest unrolled body); QLMB_STEP_EPL=8|16 selects the wider forms
+        // elements per lane: 8 by default (measured fastest); QLMB_STEP_EPL=4|16 selects the other forms
         static int epl = 0;
-        if (!epl) { const char *e = getenv("QLMB_STEP_EPL"); epl = e ? atoi(e) : 4; if (epl != 8 && epl != 16) epl = 4; }
+        if (!epl) { const char *e = getenv("QLMB_STEP_EPL"); epl = e ? atoi(e) : 8; if (epl != 4 && epl != 16) epl = 8; }
         unsigned gpb = 8u * (unsigned)(epl / 4);          // groups per block
         unsigned nb = (unsigned)((ng + gpb - 1) / gpb);
         if (epl == 4) { if (P) k_step_fast<true, 4><<<nb, 256, 0, st>>>(a); else k_step_fast<false, 4><<<nb, 256, 0, st>>>(a); }
