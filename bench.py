@@ -129,11 +129,15 @@ def run_ours(args):
     fn_dev = None
     if world > 1:
         from cudalm_c_b200 import dist_moe
-        runner = dist_moe.ExpertParallelLayer(c, dev, rank, world, seed=1234)
+        if args.ep == "nccl":
+            runner = dist_moe.ExpertParallelLayer(c, dev, rank, world, seed=1234)
+            parallelism = "ep%d (experts sharded, token all-to-all over NCCL)" % world
+        else:
+            runner = dist_moe.PeerExpertParallelLayer(c, dev, rank, world, seed=1234)
+            parallelism = "ep%d (experts sharded, foreign rows read by peer loads inside the row kernels)" % world
         step = runner.step
         fn, fi, dout, out, dfn = runner.fn, runner.fi, runner.dout, runner.out, runner.dfn
         launches_per_step = runner.launches_per_step
-        parallelism = "ep%d (experts sharded, token all-to-all over NCCL)" % world
     else:
         L, (fn, fi, dout), grads = make_layer(dev, 1234)
         out = torch.empty_like(fi); dfn = torch.empty_like(fi)
@@ -211,8 +215,10 @@ def run_ours(args):
         for h, d in zip(hin, (fn, fi, dout)):
             h.copy_(d)
         hout = [torch.empty(c["N"], c["D"], dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        peer_sets = world > 1 and hasattr(runner, "fn_set")      # inputs other ranks read live in the window
         sets = [dict(fn=fn, fi=fi, dout=dout, out=out, dfn=dfn),
-                dict(fn=torch.empty_like(fn), fi=torch.empty_like(fi), dout=torch.empty_like(dout),
+                dict(fn=runner.fn_set[1] if peer_sets else torch.empty_like(fn), fi=torch.empty_like(fi),
+                     dout=runner.dout_set[1] if peer_sets else torch.empty_like(dout),
                      out=torch.empty_like(out), dfn=torch.empty_like(dfn))]
         s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
         ev_in = [torch.cuda.Event() for _ in range(2)]
@@ -413,6 +419,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--workload", default="moe", choices=["moe", "adamw"], help="moe = the headline line; adamw = secondary line for config 3")
     ap.add_argument("--params", type=int, default=125829120, help="span size of --workload adamw")
+    ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
+                    help="N>1: peer = foreign rows read by peer loads inside the row kernels; nccl = all-to-all exchanges")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the 8192 of config 2); smaller values are for profiler captures")
     args = ap.parse_args()
     if args.tokens > 0:

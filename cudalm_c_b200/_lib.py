@@ -29,6 +29,10 @@ class MoeLayer(C.Structure):
 vp, ci, cf, u64, sz = C.c_void_p, C.c_int, C.c_float, C.c_uint64, C.c_size_t
 
 # name -> (restype, argtypes); the symbol test walks this table against the header
+class EpPeers(C.Structure):
+    _fields_ = [("rank", C.c_int), ("world", C.c_int), ("base", C.c_void_p * 8)]
+
+
 PROTOTYPES = {
     "qlmb_last_error": (C.c_char_p, []),
     "qlmb_version": (ci, []),
@@ -59,6 +63,19 @@ PROTOTYPES = {
     "qlmb_moe_dgate": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
     "qlmb_moe_experts_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, ci, vp, vp, vp, cf, vp]),
     "qlmb_moe_route_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, cf, vp]),
+    "qlmb_peer_alloc": (ci, [C.c_size_t, C.POINTER(vp)]),
+    "qlmb_peer_free": (ci, [vp]),
+    "qlmb_peer_export": (ci, [vp, vp]),
+    "qlmb_peer_open": (ci, [vp, C.POINTER(vp)]),
+    "qlmb_peer_close": (ci, [vp]),
+    "qlmb_ep_route": (ci, [C.POINTER(MoeLayer), vp, vp, vp]),
+    "qlmb_ep_experts_forward": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp, ci, ci, ci, vp]),
+    "qlmb_ep_combine": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp, vp]),
+    "qlmb_ep_dgate": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp]),
+    "qlmb_ep_experts_backward": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, ci, ci,
+                                      vp, vp, vp, cf, vp]),
+    "qlmb_ep_route_backward": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp, vp,
+                                    cf, vp]),
 }
 
 _lib = None

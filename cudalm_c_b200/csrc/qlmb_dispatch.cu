@@ -645,6 +645,262 @@ int router_wgrad(float *dWr, const void *fnorm, int dtype, const float *drt, flo
     return QLMB_OK;
 }
 
+// ------------------------------------------------- expert parallelism by peer loads
+// Rows that belong to another GPU are read through peer pointers (plain loads over NVLink)
+// inside the row kernels themselves, so no separate exchange step exists.  Global slot
+// g = s * KN + k * Nh + n names copy k of token n of rank s (Nh tokens per rank, KN = K * Nh).
+// A PeerPtrs holds, per rank, the address of the same buffer in that rank's window.
+
+// expert side: Xp[j] = f_norm of rank s, token n, for perm[j] = g (zero rows where perm[j] < 0)
+__global__ void __launch_bounds__(256) k_gather_rows_peer(bf16 *Xp, PeerPtrs src, int dtype, const int *perm,
+                                                          const int *nrows_dev, int Nh, int KN, int D)
+{
+    const int rows = *nrows_dev, lane = threadIdx.x & 31;
+    for (int j = blockIdx.x * 8 + (threadIdx.x >> 5); j < rows; j += gridDim.x * 8) {
+        const int g = perm[j];
+        uint4 *o = reinterpret_cast<uint4 *>(Xp + (size_t)j * D);
+        if (g < 0) {
+            for (int c = lane; c < D / 8; c += 32) o[c] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const int s = g / KN, n = (g % KN) % Nh;
+        const size_t base = (size_t)n * D;
+        if (dtype == QLMB_BF16) {
+            const uint4 *r = reinterpret_cast<const uint4 *>((const bf16 *)src.p[s] + base);
+            for (int c = lane; c < D / 8; c += 32) o[c] = r[c];
+        } else {
+            for (int c = lane; c < D / 8; c += 32) {
+                float v[8];
+                ld_act8(src.p[s], QLMB_F32, base + (size_t)c * 8, v);
+                o[c] = pack_bf16x8(v);
+            }
+        }
+    }
+}
+
+// home side: rowidx[slot] = row of the slot in the arena of the rank that owns its expert
+__global__ void __launch_bounds__(256) k_pull_rowidx(int *rowidx, const int *assign, PeerPtrs inv, int el, int slot0, int KN)
+{
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= KN) return;
+    const int re = assign[i] / el;
+    rowidx[i] = ((const int *)inv.p[re])[(size_t)slot0 + i];
+}
+
+// home side: out[n] = f_in[n] + sum_k gate[k,n] * yp_{owner}[rowidx[k,n]], k ascending
+__global__ void __launch_bounds__(256) k_combine_rows_peer(void *out, const void *f_in, int dtype, PeerPtrs yp,
+                                                           const int *assign, const int *rowidx, const float *gate,
+                                                           int N, int D, int K, int el)
+{
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    for (int c = lane; c < D / 8; c += 32) {
+        float acc[8];
+        ld_act8(f_in, dtype, (size_t)n * D + (size_t)c * 8, acc);
+        for (int k = 0; k < K; k++) {
+            const size_t slot = (size_t)k * N + n;
+            const float g = gate[slot];
+            float y[8];
+            ld_act8(yp.p[assign[slot] / el], QLMB_BF16, (size_t)rowidx[slot] * D + (size_t)c * 8, y);
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[i] += g * y[i];
+        }
+        st_act8(out, dtype, (size_t)n * D + (size_t)c * 8, acc);
+    }
+}
+
+// home side: d_gate[slot] = dout[n] . yp_{owner}[rowidx[slot]]  (one warp per slot)
+__global__ void __launch_bounds__(256) k_dgate_dot_peer(float *d_gate, const void *dout, int dtype, PeerPtrs yp,
+                                                        const int *assign, const int *rowidx, int N, int D, int KN, int el)
+{
+    const int slot = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (slot >= KN) return;
+    const int n = slot % N;
+    const void *y = yp.p[assign[slot] / el];
+    const size_t yb = (size_t)rowidx[slot] * D, db = (size_t)n * D;
+    float dot = 0.0f;
+    for (int c = lane; c < D / 8; c += 32) {
+        float dv[8], yv[8];
+        ld_act8(dout, dtype, db + (size_t)c * 8, dv);
+        ld_act8(y, QLMB_BF16, yb + (size_t)c * 8, yv);
+#pragma unroll
+        for (int i = 0; i < 8; i++) dot += dv[i] * yv[i];
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+    if (lane == 0) d_gate[slot] = dot;
+}
+
+// expert side: dyp[j] = gate_s[slot] * dout_s[n] for perm[j] = s * KN + slot (zero filler rows)
+__global__ void __launch_bounds__(256) k_dyp_rows_peer(bf16 *dyp, PeerPtrs dout, PeerPtrs gate, int dtype, const int *perm,
+                                                       const int *nrows_dev, int Nh, int KN, int D)
+{
+    const int rows = *nrows_dev, lane = threadIdx.x & 31;
+    for (int j = blockIdx.x * 8 + (threadIdx.x >> 5); j < rows; j += gridDim.x * 8) {
+        const int g = perm[j];
+        uint4 *o = reinterpret_cast<uint4 *>(dyp + (size_t)j * D);
+        if (g < 0) {
+            for (int c = lane; c < D / 8; c += 32) o[c] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const int s = g / KN, slot = g % KN, n = slot % Nh;
+        const float gv = ((const float *)gate.p[s])[slot];
+        for (int c = lane; c < D / 8; c += 32) {
+            float dv[8];
+            ld_act8(dout.p[s], dtype, (size_t)n * D + (size_t)c * 8, dv);
+#pragma unroll
+            for (int i = 0; i < 8; i++) dv[i] *= gv;
+            o[c] = pack_bf16x8(dv);
+        }
+    }
+}
+
+// home side: dfnorm[n,j] = sum_k dXp_{owner}[rowidx[k,n], j] + sum_e drt[n,e] * Wr[j,e]
+// (same tiling as k_unpermute_rows_tile; only the row source differs)
+__global__ void __launch_bounds__(256, 3) k_unpermute_rows_tile_peer(void *dfnorm, int dtype, PeerPtrs dXp, const int *assign,
+                                                                     const int *rowidx, int el, const float *drt,
+                                                                     const float *WrT, int N, int D, int E, int K)
+{
+    __shared__ __align__(16) float ws[32][UPT_F];
+    __shared__ __align__(16) float drs[UPT_TOK][32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * UPT_TOK, j0 = blockIdx.y * UPT_F;
+    const int jA = j0 + lane * 4, jB = jA + 128;
+    float acc[4][8];
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        const int n = n0 + warp * 4 + t;
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[t][i] = 0.0f;
+        if (n >= N) continue;
+        for (int k = 0; k < K; k++) {
+            const size_t slot = (size_t)k * N + n;
+            const bf16 *src = (const bf16 *)dXp.p[__ldg(assign + slot) / el] + (size_t)__ldg(rowidx + slot) * D;
+            if (jA < D) {
+                uint2 q = *reinterpret_cast<const uint2 *>(src + jA);
+                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
+                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
+                acc[t][0] += a.x; acc[t][1] += a.y; acc[t][2] += b.x; acc[t][3] += b.y;
+            }
+            if (jB < D) {
+                uint2 q = *reinterpret_cast<const uint2 *>(src + jB);
+                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
+                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
+                acc[t][4] += a.x; acc[t][5] += a.y; acc[t][6] += b.x; acc[t][7] += b.y;
+            }
+        }
+    }
+    for (int i = tid; i < 32 * (UPT_F / 4); i += 256) {
+        const int e = i / (UPT_F / 4), c = i % (UPT_F / 4), j = j0 + c * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < E && j < D) v = __ldg(reinterpret_cast<const float4 *>(WrT + (size_t)e * D + j));
+        *reinterpret_cast<float4 *>(&ws[e][c * 4]) = v;
+    }
+    for (int i = tid; i < UPT_TOK * 32; i += 256) {
+        const int n = n0 + (i >> 5), e = i & 31;
+        drs[i >> 5][e] = (n < N && e < E) ? drt[(size_t)n * E + e] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int e4 = 0; e4 < 32; e4 += 4) {
+        float4 dv[4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) dv[t] = *reinterpret_cast<const float4 *>(&drs[warp * 4 + t][e4]);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; k4++) {
+            const float4 wa = *reinterpret_cast<const float4 *>(&ws[e4 + k4][lane * 4]);
+            const float4 wb = *reinterpret_cast<const float4 *>(&ws[e4 + k4][128 + lane * 4]);
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const float d = k4 == 0 ? dv[t].x : k4 == 1 ? dv[t].y : k4 == 2 ? dv[t].z : dv[t].w;
+                acc[t][0] += d * wa.x; acc[t][1] += d * wa.y; acc[t][2] += d * wa.z; acc[t][3] += d * wa.w;
+                acc[t][4] += d * wb.x; acc[t][5] += d * wb.y; acc[t][6] += d * wb.z; acc[t][7] += d * wb.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        const int n = n0 + warp * 4 + t;
+        if (n >= N) continue;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int j = h ? jB : jA;
+            if (j >= D) continue;
+            const float *v = &acc[t][h * 4];
+            if (dtype == QLMB_BF16) {
+                uint2 q;
+                *reinterpret_cast<__nv_bfloat162 *>(&q.x) = __floats2bfloat162_rn(v[0], v[1]);
+                *reinterpret_cast<__nv_bfloat162 *>(&q.y) = __floats2bfloat162_rn(v[2], v[3]);
+                *reinterpret_cast<uint2 *>((bf16 *)dfnorm + (size_t)n * D + j) = q;
+            } else {
+                *reinterpret_cast<float4 *>((float *)dfnorm + (size_t)n * D + j) = make_float4(v[0], v[1], v[2], v[3]);
+            }
+        }
+    }
+}
+
+// counts[e] = how many of the K*N slots chose expert e (integer atomics: order independent)
+__global__ void __launch_bounds__(256) k_count_assign(int *counts, const int *assign, int KN, int E)
+{
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i < KN) { const int e = assign[i]; if ((unsigned)e < (unsigned)E) atomicAdd(&counts[e], 1); }
+}
+
+int gather_rows_peer(bf16 *Xp, const PeerPtrs &src, int dtype, const int *perm, const int *nrows_dev, int max_rows,
+                     int Nh, int KN, int D, cudaStream_t st)
+{
+    int blocks = (max_rows + 7) / 8, cap = sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    k_gather_rows_peer<<<blocks, 256, 0, st>>>(Xp, src, dtype, perm, nrows_dev, Nh, KN, D);
+    QLMB_LAUNCH_CHECK("k_gather_rows_peer");
+    return QLMB_OK;
+}
+int pull_rowidx(int *rowidx, const int *assign, const PeerPtrs &inv, int el, int slot0, int KN, cudaStream_t st)
+{
+    k_pull_rowidx<<<(KN + 255) / 256, 256, 0, st>>>(rowidx, assign, inv, el, slot0, KN);
+    QLMB_LAUNCH_CHECK("k_pull_rowidx");
+    return QLMB_OK;
+}
+int combine_rows_peer(void *out, const void *f_in, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
+                      const float *gate, int N, int D, int K, int el, cudaStream_t st)
+{
+    k_combine_rows_peer<<<(N + 7) / 8, 256, 0, st>>>(out, f_in, dtype, yp, assign, rowidx, gate, N, D, K, el);
+    QLMB_LAUNCH_CHECK("k_combine_rows_peer");
+    return QLMB_OK;
+}
+int dgate_dot_peer(float *d_gate, const void *dout, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
+                   int N, int D, int K, int el, cudaStream_t st)
+{
+    k_dgate_dot_peer<<<(K * N + 7) / 8, 256, 0, st>>>(d_gate, dout, dtype, yp, assign, rowidx, N, D, K * N, el);
+    QLMB_LAUNCH_CHECK("k_dgate_dot_peer");
+    return QLMB_OK;
+}
+int dyp_rows_peer(bf16 *dyp, const PeerPtrs &dout, const PeerPtrs &gate, int dtype, const int *perm, const int *nrows_dev,
+                  int max_rows, int Nh, int KN, int D, cudaStream_t st)
+{
+    int blocks = (max_rows + 7) / 8, cap = sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    k_dyp_rows_peer<<<blocks, 256, 0, st>>>(dyp, dout, gate, dtype, perm, nrows_dev, Nh, KN, D);
+    QLMB_LAUNCH_CHECK("k_dyp_rows_peer");
+    return QLMB_OK;
+}
+int unpermute_rows_peer(void *dfnorm, int dtype, const PeerPtrs &dXp, const int *assign, const int *rowidx, int el,
+                        const float *drt, const float *Wr, float *wrt_scratch, int N, int D, int E, int K, cudaStream_t st)
+{
+    k_transpose_wr<<<(D * E + 255) / 256, 256, 0, st>>>(wrt_scratch, Wr, D, E);
+    k_unpermute_rows_tile_peer<<<dim3((N + UPT_TOK - 1) / UPT_TOK, (D + UPT_F - 1) / UPT_F), 256, 0, st>>>(
+        dfnorm, dtype, dXp, assign, rowidx, el, drt, wrt_scratch, N, D, E, K);
+    QLMB_LAUNCH_CHECK("k_unpermute_rows_tile_peer");
+    return QLMB_OK;
+}
+int count_assign(int *counts, const int *assign, int KN, int E, cudaStream_t st)
+{
+    QLMB_CUDA(cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), st));
+    k_count_assign<<<(KN + 255) / 256, 256, 0, st>>>(counts, assign, KN, E);
+    QLMB_LAUNCH_CHECK("k_count_assign");
+    return QLMB_OK;
+}
+
 // ----------------------------------------------------------- conversions
 __global__ void __launch_bounds__(256) k_f32_to_bf16(bf16 *dst, const float *src, size_t n8, size_t n)
 {

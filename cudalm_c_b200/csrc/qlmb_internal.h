@@ -16,7 +16,7 @@ int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N,
 size_t perm_scratch_ints(int N, int E, int K, int merged);
 int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
                int *off, int *counts, int *bad_flag, int *tile_info, int *ntiles,
-               int *chunk_scratch, cudaStream_t st);
+               int *chunk_scratch, cudaStream_t st, int e_lo = 0, int skip = 0);
 
 // ---- row kernels (qlmb_dispatch.cu) ----
 int router_logits(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E,
@@ -42,6 +42,21 @@ int unpermute_rows(void *dfnorm, int dtype, const bf16 *dXp, const int *inv, con
 // dWr[D,E] = beta*dWr + fnorm^T drt ; scratch holds 192*D*E floats
 int router_wgrad(float *dWr, const void *fnorm, int dtype, const float *drt, float *scratch, int N,
                  int D, int E, float beta, cudaStream_t st);
+// ---- expert parallelism by peer loads (qlmb_dispatch.cu) ----
+#define QLMB_EP_MAX_WORLD 8
+struct PeerPtrs { const void *p[QLMB_EP_MAX_WORLD]; };   // the same buffer in every rank's window
+int gather_rows_peer(bf16 *Xp, const PeerPtrs &src, int dtype, const int *perm, const int *nrows_dev, int max_rows,
+                     int Nh, int KN, int D, cudaStream_t st);
+int pull_rowidx(int *rowidx, const int *assign, const PeerPtrs &inv, int el, int slot0, int KN, cudaStream_t st);
+int combine_rows_peer(void *out, const void *f_in, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
+                      const float *gate, int N, int D, int K, int el, cudaStream_t st);
+int dgate_dot_peer(float *d_gate, const void *dout, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
+                   int N, int D, int K, int el, cudaStream_t st);
+int dyp_rows_peer(bf16 *dyp, const PeerPtrs &dout, const PeerPtrs &gate, int dtype, const int *perm, const int *nrows_dev,
+                  int max_rows, int Nh, int KN, int D, cudaStream_t st);
+int unpermute_rows_peer(void *dfnorm, int dtype, const PeerPtrs &dXp, const int *assign, const int *rowidx, int el,
+                        const float *drt, const float *Wr, float *wrt_scratch, int N, int D, int E, int K, cudaStream_t st);
+int count_assign(int *counts, const int *assign, int KN, int E, cudaStream_t st);
 // fp32 <-> bf16 row conversion helpers
 int convert_f32_to_bf16(bf16 *dst, const float *src, size_t n, cudaStream_t st);
 

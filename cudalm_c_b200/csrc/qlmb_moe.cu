@@ -336,3 +336,141 @@ extern "C" int qlmb_moe_experts_backward(const qlmb_moe_layer *L, void *earena, 
     ProfScope ps("gather_rows", st);
     return gather_rows((bf16 *)dX, a.dXp, QLMB_BF16, a.inv, nullptr, R, (int)a.rows_cap, D, st);
 }
+
+// ------------------------------------------------ expert parallelism by peer loads
+namespace qlmb {
+static int check_peers(const char *who, const qlmb_ep_peers *P)
+{
+    QLMB_REQUIRE(P && P->world >= 1 && P->world <= QLMB_EP_MAX_WORLD && P->rank >= 0 && P->rank < P->world,
+                 "%s: bad peer table", who);
+    for (int i = 0; i < P->world; i++) QLMB_REQUIRE(P->base[i], "%s: window of rank %d is not mapped", who, i);
+    return QLMB_OK;
+}
+// the buffer at `local` (inside this rank's window) as seen in every rank's window
+static PeerPtrs peer_view(const qlmb_ep_peers *P, const void *local)
+{
+    PeerPtrs v;
+    memset(&v, 0, sizeof v);
+    const ptrdiff_t off = (const char *)local - (const char *)P->base[P->rank];
+    for (int i = 0; i < P->world; i++) v.p[i] = (const char *)P->base[i] + off;
+    return v;
+}
+static int check_ep_shapes(const char *who, const qlmb_moe_layer *home, const qlmb_moe_layer *loc, const qlmb_ep_peers *P)
+{
+    QLMB_REQUIRE(home->E == loc->E * P->world, "%s: %d experts in total but %d ranks x %d local", who, home->E, P->world, loc->E);
+    QLMB_REQUIRE(loc->N == P->world * home->K * home->N, "%s: expert arena holds %d slots, need %d", who, loc->N,
+                 P->world * home->K * home->N);
+    QLMB_REQUIRE(home->D == loc->D && home->F == loc->F, "%s: D/F differ between the two layer views", who);
+    return QLMB_OK;
+}
+}  // namespace qlmb
+
+extern "C" int qlmb_ep_route(const qlmb_moe_layer *L, void *harena, const void *f_norm, void *stream)
+{
+    int rc = check_layer("qlmb_ep_route", L, false, true);
+    if (rc) return rc;
+    QLMB_REQUIRE(harena && f_norm, "qlmb_ep_route: NULL argument");
+    const int N = L->N, D = L->D, E = L->E, K = L->K;
+    Arena a = carve(harena, N, D, L->F, E, K);
+    cudaStream_t st = as_stream(stream);
+    { ProfScope ps("router_logits", st); if ((rc = router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc; }
+    { ProfScope ps("router_topk", st); if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc; }
+    ProfScope ps("count_assign", st);
+    return count_assign(a.counts, a.assign, K * N, E, st);
+}
+
+extern "C" int qlmb_ep_experts_forward(const qlmb_moe_layer *L, void *earena, const qlmb_ep_peers *P,
+                                       const int *assign_all, const void *f_norm, int x_dtype, int tokens_per_rank,
+                                       int K, void *stream)
+{
+    int rc = check_layer("qlmb_ep_experts_forward", L, true, false);
+    if (rc) return rc;
+    if ((rc = check_peers("qlmb_ep_experts_forward", P))) return rc;
+    QLMB_REQUIRE(earena && assign_all && f_norm, "qlmb_ep_experts_forward: NULL argument");
+    QLMB_REQUIRE(x_dtype == QLMB_F32 || x_dtype == QLMB_BF16, "qlmb_ep_experts_forward: dtype %d", x_dtype);
+    QLMB_REQUIRE(tokens_per_rank > 0 && K > 0 && L->N == P->world * K * tokens_per_rank,
+                 "qlmb_ep_experts_forward: arena holds %d slots, need %d", L->N, P->world * K * tokens_per_rank);
+    const int D = L->D, E = L->E, KN = K * tokens_per_rank;
+    Arena a = carve(earena, L->N, D, L->F, E, 1);
+    cudaStream_t st = as_stream(stream);
+    { ProfScope ps("perm_build", st);
+      if ((rc = perm_build(assign_all, L->N, E, 1, 1, 128, a.perm, a.inv, a.off, a.counts, a.bad, a.tile_info, a.ntiles,
+                           a.chunk, st, P->rank * E, 1))) return rc; }
+    { ProfScope ps("gather_rows_peer", st);
+      if ((rc = gather_rows_peer(a.Xp, peer_view(P, f_norm), x_dtype, a.perm, a.off + E, (int)a.rows_cap, tokens_per_rank, KN, D, st))) return rc; }
+    return experts_forward_gemms(L, a, st);
+}
+
+extern "C" int qlmb_ep_combine(const qlmb_moe_layer *H, void *harena, const qlmb_moe_layer *L, void *earena,
+                               const qlmb_ep_peers *P, void *out, const void *f_in, void *stream)
+{
+    int rc = check_layer("qlmb_ep_combine", H, false, false);
+    if (rc) return rc;
+    if ((rc = check_peers("qlmb_ep_combine", P))) return rc;
+    QLMB_REQUIRE(L && harena && earena && out && f_in, "qlmb_ep_combine: NULL argument");
+    if ((rc = check_ep_shapes("qlmb_ep_combine", H, L, P))) return rc;
+    Arena h = carve(harena, H->N, H->D, H->F, H->E, H->K);
+    Arena e = carve(earena, L->N, L->D, L->F, L->E, 1);
+    cudaStream_t st = as_stream(stream);
+    const int KN = H->K * H->N;
+    { ProfScope ps("pull_rowidx", st);
+      if ((rc = pull_rowidx(h.inv, h.assign, peer_view(P, e.inv), L->E, P->rank * KN, KN, st))) return rc; }
+    ProfScope ps("combine_rows_peer", st);
+    return combine_rows_peer(out, f_in, H->dtype, peer_view(P, e.yp), h.assign, h.inv, h.gate, H->N, H->D, H->K, L->E, st);
+}
+
+extern "C" int qlmb_ep_dgate(const qlmb_moe_layer *H, void *harena, const qlmb_moe_layer *L, void *earena,
+                             const qlmb_ep_peers *P, const void *dout, void *stream)
+{
+    int rc = check_layer("qlmb_ep_dgate", H, false, false);
+    if (rc) return rc;
+    if ((rc = check_peers("qlmb_ep_dgate", P))) return rc;
+    QLMB_REQUIRE(L && harena && earena && dout, "qlmb_ep_dgate: NULL argument");
+    if ((rc = check_ep_shapes("qlmb_ep_dgate", H, L, P))) return rc;
+    Arena h = carve(harena, H->N, H->D, H->F, H->E, H->K);
+    Arena e = carve(earena, L->N, L->D, L->F, L->E, 1);
+    ProfScope ps("dgate_dot_peer", as_stream(stream));
+    return dgate_dot_peer(h.d_gate, dout, H->dtype, peer_view(P, e.yp), h.assign, h.inv, H->N, H->D, H->K, L->E, as_stream(stream));
+}
+
+extern "C" int qlmb_ep_experts_backward(const qlmb_moe_layer *L, void *earena, const qlmb_moe_layer *H, void *harena,
+                                        const qlmb_ep_peers *P, const void *dout, int tokens_per_rank, int K,
+                                        float *dW1, float *dW3, float *dW2, float beta, void *stream)
+{
+    int rc = check_layer("qlmb_ep_experts_backward", L, true, false);
+    if (rc) return rc;
+    if ((rc = check_peers("qlmb_ep_experts_backward", P))) return rc;
+    QLMB_REQUIRE(H && earena && harena && dout && dW1 && dW3 && dW2, "qlmb_ep_experts_backward: NULL argument");
+    QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_ep_experts_backward: beta %g", beta);
+    if ((rc = check_ep_shapes("qlmb_ep_experts_backward", H, L, P))) return rc;
+    QLMB_REQUIRE(tokens_per_rank == H->N && K == H->K, "qlmb_ep_experts_backward: tokens_per_rank / K differ from the router view");
+    Arena h = carve(harena, H->N, H->D, H->F, H->E, H->K);
+    Arena e = carve(earena, L->N, L->D, L->F, L->E, 1);
+    cudaStream_t st = as_stream(stream);
+    { ProfScope ps("dyp_rows_peer", st);
+      if ((rc = dyp_rows_peer(e.dyp, peer_view(P, dout), peer_view(P, h.gate), H->dtype, e.perm, e.off + L->E, (int)e.rows_cap,
+                              tokens_per_rank, K * tokens_per_rank, L->D, st))) return rc; }
+    return experts_backward_gemms(L, e, dW1, dW3, dW2, beta, st);
+}
+
+extern "C" int qlmb_ep_route_backward(const qlmb_moe_layer *H, void *harena, const qlmb_moe_layer *L, void *earena,
+                                      const qlmb_ep_peers *P, void *dfnorm, const void *f_norm, float *dWr, float beta,
+                                      void *stream)
+{
+    int rc = check_layer("qlmb_ep_route_backward", H, false, true);
+    if (rc) return rc;
+    if ((rc = check_peers("qlmb_ep_route_backward", P))) return rc;
+    QLMB_REQUIRE(L && harena && earena && dfnorm && f_norm && dWr, "qlmb_ep_route_backward: NULL argument");
+    QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_ep_route_backward: beta %g", beta);
+    QLMB_REQUIRE(H->E <= 32 && (H->D % 8) == 0, "qlmb_ep_route_backward: needs E <= 32 and D a multiple of 8");
+    if ((rc = check_ep_shapes("qlmb_ep_route_backward", H, L, P))) return rc;
+    const int N = H->N, D = H->D, E = H->E, K = H->K;
+    Arena h = carve(harena, N, D, H->F, E, K);
+    Arena e = carve(earena, L->N, L->D, L->F, L->E, 1);
+    cudaStream_t st = as_stream(stream);
+    { ProfScope ps("router_bwd", st); if ((rc = router_bwd(h.drt, h.rprobs, h.assign, h.d_gate, h.counts, N, E, K, H->aux, st))) return rc; }
+    { ProfScope ps("unpermute_rows_peer", st);
+      if ((rc = unpermute_rows_peer(dfnorm, H->dtype, peer_view(P, e.dXp), h.assign, h.inv, L->E, h.drt, H->wr, h.wrt, N, D, E, K, st))) return rc; }
+    ProfScope ps("router_wgrad", st);
+    return router_wgrad(dWr, f_norm, H->dtype, h.drt, h.wr_scratch, N, D, E, beta, st);
+}

@@ -110,16 +110,18 @@ __global__ void __launch_bounds__(256) k_router_topk_warp(const float *rt, float
 //   scatter : in-chunk stable rank (warp match + per-warp prefix) -> perm, inv
 #define PERM_CHUNK 1024
 
+// e_lo / skip: expert ids are taken relative to e_lo; with skip != 0 a slot whose id falls outside
+// [e_lo, e_lo + E) is left out (inv = -1) instead of being reported as an error
 __global__ void __launch_bounds__(PERM_CHUNK) k_perm_hist(const int *asn, int len, int E, int NC,
-                                                          int *ch, int *bad)
+                                                          int *ch, int *bad, int e_lo, int skip)
 {
     extern __shared__ int h[];
     int c = blockIdx.x, k = blockIdx.y, i = c * PERM_CHUNK + threadIdx.x;
     for (int e = threadIdx.x; e < E; e += blockDim.x) h[e] = 0;
     __syncthreads();
     if (i < len) {
-        int e = asn[(size_t)k * len + i];
-        if ((unsigned)e >= (unsigned)E) atomicExch(bad, e | 0x40000000);
+        int e = asn[(size_t)k * len + i] - e_lo;
+        if ((unsigned)e >= (unsigned)E) { if (!skip) atomicExch(bad, (e + e_lo) | 0x40000000); }
         else atomicAdd(&h[e], 1);
     }
     __syncthreads();
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(256) k_perm_scan(int *ch, int E, int NC, int p
 
 __global__ void __launch_bounds__(PERM_CHUNK) k_perm_scatter(const int *asn, int len, int E, int NC,
                                                              const int *base, int *perm, int plen,
-                                                             int *inv)
+                                                             int *inv, int e_lo)
 {
     extern __shared__ int wc[];           // [32 warps][E] counts of the chunk
     int c = blockIdx.x, k = blockIdx.y, i = c * PERM_CHUNK + threadIdx.x;
@@ -186,12 +188,12 @@ __global__ void __launch_bounds__(PERM_CHUNK) k_perm_scatter(const int *asn, int
     for (int j = threadIdx.x; j < 32 * E; j += blockDim.x) wc[j] = 0;
     __syncthreads();
     int e = -1;
-    if (i < len) { e = asn[(size_t)k * len + i]; if ((unsigned)e >= (unsigned)E) e = -1; }
+    if (i < len) { e = asn[(size_t)k * len + i] - e_lo; if ((unsigned)e >= (unsigned)E) e = -1; }
     unsigned peers = __match_any_sync(0xffffffffu, e);
     int rank = __popc(peers & ((1u << ln) - 1u));
     if (e >= 0 && rank == 0) wc[w * E + e] = __popc(peers);
     __syncthreads();
-    if (e < 0) return;
+    if (e < 0) { if (inv && i < len) inv[(size_t)k * len + i] = -1; return; }
     int pos = base[((size_t)k * E + e) * NC + c] + rank;
     for (int j = 0; j < w; j++) pos += wc[j * E + e];
     perm[(size_t)k * plen + pos] = i;
@@ -200,18 +202,18 @@ __global__ void __launch_bounds__(PERM_CHUNK) k_perm_scatter(const int *asn, int
 
 int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
                int *off, int *counts, int *bad_flag, int *tile_info, int *ntiles,
-               int *chunk_scratch, cudaStream_t st)
+               int *chunk_scratch, cudaStream_t st, int e_lo, int skip)
 {
     int sorts = merged ? 1 : K, len = merged ? K * N : N;
     int NC = (len + PERM_CHUNK - 1) / PERM_CHUNK;
     int plen = len + E * (pad - 1);
     QLMB_CUDA(cudaMemsetAsync(bad_flag, 0, sizeof(int), st));
-    k_perm_hist<<<dim3(NC, sorts), PERM_CHUNK, E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, bad_flag);
+    k_perm_hist<<<dim3(NC, sorts), PERM_CHUNK, E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, bad_flag, e_lo, skip);
     k_perm_scan<<<sorts, 256, (2 * E + 1) * sizeof(int), st>>>(chunk_scratch, E, NC, pad, plen, off, counts, perm,
                                                              tile_info, ntiles, bad_flag,
                                                              device_error_word());
     k_perm_scatter<<<dim3(NC, sorts), PERM_CHUNK, 32 * E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, perm,
-                                                                            plen, inv);
+                                                                            plen, inv, e_lo);
     QLMB_LAUNCH_CHECK("perm_build");
     return QLMB_OK;
 }

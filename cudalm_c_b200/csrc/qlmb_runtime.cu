@@ -115,3 +115,38 @@ extern "C" int qlmb_check_device(void *stream)
     }
     return QLMB_OK;
 }
+
+// ---- device memory that other processes of the node can map (CUDA IPC) ----
+extern "C" int qlmb_peer_alloc(size_t bytes, void **ptr)
+{
+    QLMB_REQUIRE(ptr && bytes > 0, "qlmb_peer_alloc: bad argument");
+    QLMB_CUDA(cudaMalloc(ptr, bytes));
+    return QLMB_OK;
+}
+extern "C" int qlmb_peer_free(void *ptr)
+{
+    if (ptr) QLMB_CUDA(cudaFree(ptr));
+    return QLMB_OK;
+}
+extern "C" int qlmb_peer_export(const void *ptr, unsigned char handle[64])
+{
+    QLMB_REQUIRE(ptr && handle, "qlmb_peer_export: NULL argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    QLMB_CUDA(cudaIpcGetMemHandle(&h, const_cast<void *>(ptr)));
+    memcpy(handle, &h, 64);
+    return QLMB_OK;
+}
+extern "C" int qlmb_peer_open(const unsigned char handle[64], void **ptr)
+{
+    QLMB_REQUIRE(ptr && handle, "qlmb_peer_open: NULL argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    QLMB_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return QLMB_OK;
+}
+extern "C" int qlmb_peer_close(void *ptr)
+{
+    if (ptr) QLMB_CUDA(cudaIpcCloseMemHandle(ptr));
+    return QLMB_OK;
+}

@@ -146,3 +146,156 @@ class ExpertParallelLayer:
     def step(self):
         self.forward()
         self.backward()
+
+
+class _DeviceWindow:
+    """A raw device allocation exposed to torch without a copy."""
+
+    def __init__(self, address, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 2}
+
+
+class PeerExpertParallelLayer:
+    """The same layer with no exchange step: foreign rows are read through peer-mapped pointers
+    inside the library's row kernels (include/qlm_b200.h, qlmb_ep_*).  Every rank owns one window
+    of device memory (token inputs, router-side arena, expert-side arena) with the same layout;
+    the ranks of the node map each other's windows once at construction.  Per step the ranks
+    exchange only the routing table (one fixed-size all-gather) and two one-element all-reduces
+    that act as stream-ordered barriers; nothing waits on the host."""
+
+    launches_per_step = 25          # library kernels per forward+backward on a rank
+
+    def __init__(self, cfg, dev, rank, world, seed=1234, aux=0.03, group=None, weights=None):
+        import ctypes as C
+        from . import qlm
+        from ._lib import EpPeers
+        self.N, self.D, self.F, self.E, self.K = cfg["N"], cfg["D"], cfg["F"], cfg["E"], cfg["K"]
+        N, D, F, E, K = self.N, self.D, self.F, self.E, self.K
+        assert E % world == 0 and world <= 8
+        self.rank, self.world, self.group, self.dev = rank, world, group, dev
+        self.el = el = E // world
+        L = lib()
+        gen = torch.Generator(device=dev); gen.manual_seed(seed)
+        self.q = []
+        for wi, (rows, cols) in enumerate(((D, F), (D, F), (F, D))):
+            full = weights[wi] if weights is not None else torch.randn(E * rows * cols, device=dev, generator=gen) * 0.02
+            n = el * rows * cols
+            Q = qlm.Qlm([(0, n)], n, dev)
+            Q.init_from(full[rank * n:(rank + 1) * n].clone(), render=False)
+            self.q.append((Q.d, Q.s))
+            del full
+        self.wr = weights[3] if weights is not None else torch.randn(D, E, device=dev, generator=gen) * 0.02
+        # window layout (identical on every rank)
+        self.slots = world * K * N
+        hb = L.qlmb_moe_arena_bytes(N, D, F, E, K)
+        eb = L.qlmb_moe_arena_bytes(self.slots, D, F, el, 1)
+        al = lambda x: (x + 255) // 256 * 256
+        row_bytes = al(N * D * 2)
+        self.off_fn = [0, row_bytes]
+        self.off_dout = [2 * row_bytes, 3 * row_bytes]
+        self.off_h = 4 * row_bytes
+        self.off_e = self.off_h + al(hb)
+        self.win_bytes = self.off_e + al(eb)
+        p = C.c_void_p()
+        check(L.qlmb_peer_alloc(self.win_bytes, C.byref(p)))
+        self.win_ptr = p.value
+        self.win = torch.as_tensor(_DeviceWindow(self.win_ptr, self.win_bytes), device=dev)
+        self.win.zero_()
+        self.peers = EpPeers()
+        self.peers.rank, self.peers.world = rank, world
+        self._opened = []
+        if world > 1:
+            hbuf = (C.c_ubyte * 64)()
+            check(L.qlmb_peer_export(self.win_ptr, hbuf))
+            mine = torch.tensor(list(hbuf), dtype=torch.uint8, device=dev)
+            allh = torch.empty(world, 64, dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(allh.view(-1), mine, group=group)
+            allh = allh.cpu().numpy()
+            for r in range(world):
+                if r == rank:
+                    self.peers.base[r] = self.win_ptr
+                    continue
+                hb_r = (C.c_ubyte * 64)(*[int(x) for x in allh[r]])
+                q = C.c_void_p()
+                check(L.qlmb_peer_open(hb_r, C.byref(q)))
+                self.peers.base[r] = q.value
+                self._opened.append(q.value)
+        else:
+            self.peers.base[0] = self.win_ptr
+        self.hptr = self.win_ptr + self.off_h
+        self.eptr = self.win_ptr + self.off_e
+        bf = torch.bfloat16
+
+        def view(off, shape, dtype):
+            n = int(np.prod(shape)) * torch.empty(0, dtype=dtype).element_size()
+            return self.win[off:off + n].view(dtype).view(*shape)
+        self.fn_set = [view(o, (N, D), bf) for o in self.off_fn]
+        self.dout_set = [view(o, (N, D), bf) for o in self.off_dout]
+        self.home = MoeLayer(N, D, F, E, K, BF16, None, None, None, None, None, None, ptr(self.wr), None, 0, aux)
+        self.loc = MoeLayer(self.slots, D, F, el, 1, BF16, ptr(self.q[0][0]), ptr(self.q[1][0]), ptr(self.q[2][0]),
+                            ptr(self.q[0][1]), ptr(self.q[1][1]), ptr(self.q[2][1]), None, None, 0, aux)
+        ap = L.qlmb_moe_arena_member(self.hptr, N, D, F, E, K, b"assign")
+        self.assign = view(ap - self.win_ptr, (K * N,), torch.int32)
+        self.assign_all = torch.empty(world, K * N, dtype=torch.int32, device=dev)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.dW = [torch.zeros(el, D, F, device=dev), torch.zeros(el, D, F, device=dev), torch.zeros(el, F, D, device=dev)]
+        self.dWr = torch.zeros(D, E, device=dev)
+        g2 = torch.Generator(device=dev); g2.manual_seed(seed + 1000 + rank)
+        self.fn, self.dout = self.fn_set[0], self.dout_set[0]
+        self.fn.copy_(torch.randn(N, D, device=dev, generator=g2).bfloat16())
+        self.fi = torch.randn(N, D, device=dev, generator=g2).bfloat16()
+        self.dout.copy_(torch.randn(N, D, device=dev, generator=g2).bfloat16())
+        self.out = torch.empty_like(self.fi); self.dfn = torch.empty_like(self.fi)
+        if world > 1:
+            dist.barrier(group=group)           # every window is mapped before the first step reads one
+
+    def _barrier(self):
+        if self.world > 1:
+            dist.all_reduce(self.flag, group=self.group)
+
+    def forward(self, fi=None, fn=None, out=None):
+        """fn must be one of fn_set (it is read by the other ranks)."""
+        fi = self.fi if fi is None else fi
+        fn = self.fn if fn is None else fn
+        out = self.out if out is None else out
+        L, st = lib(), stream_ptr()
+        check(L.qlmb_ep_route(self.home, self.hptr, ptr(fn), st))
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.assign_all.view(-1), self.assign, group=self.group)
+        else:
+            self.assign_all.view(-1).copy_(self.assign)
+        check(L.qlmb_ep_experts_forward(self.loc, self.eptr, self.peers, ptr(self.assign_all), ptr(fn), BF16, self.N, self.K, st))
+        self._barrier()
+        check(L.qlmb_ep_combine(self.home, self.hptr, self.loc, self.eptr, self.peers, ptr(out), ptr(fi), st))
+        return out
+
+    def backward(self, dout=None, fn=None, beta=0.0, dfn=None):
+        """dout must be one of dout_set (it is read by the other ranks)."""
+        dout = self.dout if dout is None else dout
+        fn = self.fn if fn is None else fn
+        dfn = self.dfn if dfn is None else dfn
+        L, st = lib(), stream_ptr()
+        check(L.qlmb_ep_dgate(self.home, self.hptr, self.loc, self.eptr, self.peers, ptr(dout), st))
+        check(L.qlmb_ep_experts_backward(self.loc, self.eptr, self.home, self.hptr, self.peers, ptr(dout), self.N, self.K,
+                                         ptr(self.dW[0]), ptr(self.dW[1]), ptr(self.dW[2]), beta, st))
+        self._barrier()
+        check(L.qlmb_ep_route_backward(self.home, self.hptr, self.loc, self.eptr, self.peers, ptr(dfn), ptr(fn), ptr(self.dWr),
+                                       beta, st))
+        return dfn
+
+    def step(self):
+        self.forward()
+        self.backward()
+
+    def close(self):
+        L = lib()
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)      # nobody reads a window that is about to go away
+        for q in self._opened:
+            L.qlmb_peer_close(q)
+        self._opened = []
+        self.win = None
+        if self.win_ptr:
+            L.qlmb_peer_free(self.win_ptr)
+            self.win_ptr = 0

@@ -225,6 +225,57 @@ int qlmb_moe_experts_backward(const qlmb_moe_layer *L, void *earena, void *dX, c
 int qlmb_moe_route_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const void *dXs,
                             const void *f_norm, float *dWr, float beta, void *stream);
 
+/* ------------------------------- expert parallelism by peer loads (new, no reference counterpart)
+ * Same cut of moe_forward / moe_backward (cudalm.cu:4151-4393), but rows never travel in a
+ * separate exchange: every rank places its inputs and both arenas in one "window" of device
+ * memory that the other ranks of the node map (qlmb_peer_*), all windows have the same layout,
+ * and the row kernels read foreign rows through the mapped pointers (plain loads over NVLink).
+ * The caller provides the stream-ordered synchronisation between the calls with collectives of
+ * its own (no kernel of this library waits for another GPU):
+ *   qlmb_ep_route            every rank
+ *   all-gather of arena member "assign" ([K*N] ints per rank) into assign_all[W][K*N]
+ *   qlmb_ep_experts_forward  every rank, for the experts it holds
+ *   barrier
+ *   qlmb_ep_combine          (forward done)
+ *   qlmb_ep_dgate
+ *   qlmb_ep_experts_backward
+ *   barrier
+ *   qlmb_ep_route_backward
+ * The all-gather of the next step is the barrier that protects the arenas from being
+ * overwritten while a slower rank still reads them.  Global slot g = s*K*N + k*N + n is copy k
+ * of token n of rank s.  `home` describes the router side (N tokens of this rank, E experts in
+ * total, K, wr); `loc` the expert side (E = experts held by this rank, rank r holds experts
+ * [r*E_loc, (r+1)*E_loc), N = W*K*N_home slots, the capacity of `earena` =
+ * qlmb_moe_arena_bytes(loc->N, D, F, loc->E, 1)).  Pointers named f_norm / dout / harena /
+ * earena must lie inside this rank's window; the same offsets are read in the peers' windows. */
+#define QLMB_EP_MAX_WORLD 8
+typedef struct qlmb_ep_peers {
+    int rank, world;
+    void *base[QLMB_EP_MAX_WORLD];   /* window of rank i as mapped into this process; base[rank] = own */
+} qlmb_ep_peers;
+
+/* device memory that other processes of the node can map */
+int qlmb_peer_alloc(size_t bytes, void **ptr);
+int qlmb_peer_free(void *ptr);
+int qlmb_peer_export(const void *ptr, unsigned char handle[64]);
+int qlmb_peer_open(const unsigned char handle[64], void **ptr);
+int qlmb_peer_close(void *ptr);
+
+int qlmb_ep_route(const qlmb_moe_layer *home, void *harena, const void *f_norm, void *stream);
+int qlmb_ep_experts_forward(const qlmb_moe_layer *loc, void *earena, const qlmb_ep_peers *peers,
+                            const int *assign_all, const void *f_norm, int x_dtype, int tokens_per_rank,
+                            int K, void *stream);
+int qlmb_ep_combine(const qlmb_moe_layer *home, void *harena, const qlmb_moe_layer *loc, void *earena,
+                    const qlmb_ep_peers *peers, void *out, const void *f_in, void *stream);
+int qlmb_ep_dgate(const qlmb_moe_layer *home, void *harena, const qlmb_moe_layer *loc, void *earena,
+                  const qlmb_ep_peers *peers, const void *dout, void *stream);
+int qlmb_ep_experts_backward(const qlmb_moe_layer *loc, void *earena, const qlmb_moe_layer *home,
+                             void *harena, const qlmb_ep_peers *peers, const void *dout, int tokens_per_rank,
+                             int K, float *dW1, float *dW3, float *dW2, float beta, void *stream);
+int qlmb_ep_route_backward(const qlmb_moe_layer *home, void *harena, const qlmb_moe_layer *loc, void *earena,
+                           const qlmb_ep_peers *peers, void *dfnorm, const void *f_norm, float *dWr,
+                           float beta, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

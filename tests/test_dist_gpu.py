@@ -1,4 +1,5 @@
-"""Expert-parallel layer (split C-ABI calls + NCCL all-to-all) against the
+"""Expert-parallel layer, in both forms (split C-ABI calls + NCCL all-to-all; peer loads
+inside the row kernels, no exchange step), against the
 single-call layer with the same weights and tokens.  Runs on every visible GPU
 (1, or 2 when the box has them): rows of an expert GEMM are independent, so the
 layer output and the input gradient must be bit-identical to the single-GPU
@@ -24,7 +25,7 @@ def rel(a, b):
     return max(float((a - b).norm() / b.norm()), float((a - b).abs().max() / b.abs().max()))
 
 
-def worker(rank, world, port, ret):
+def worker(rank, world, port, ret, mode):
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
@@ -37,7 +38,10 @@ def worker(rank, world, port, ret):
     gen = torch.Generator(device=dev); gen.manual_seed(7)
     full = [torch.randn(E * D * F, device=dev, generator=gen) * 0.02 for _ in range(3)]
     wr = torch.randn(D, E, device=dev, generator=gen) * 0.02
-    ep = dist_moe.ExpertParallelLayer(c, dev, rank, world, seed=7, weights=full + [wr])
+    if mode == "peer":
+        ep = dist_moe.PeerExpertParallelLayer(c, dev, rank, world, seed=7, weights=full + [wr])
+    else:
+        ep = dist_moe.ExpertParallelLayer(c, dev, rank, world, seed=7, weights=full + [wr])
     # single-call reference with all experts local, on this rank's tokens
     qs = []
     for w in full:
@@ -50,7 +54,8 @@ def worker(rank, world, port, ret):
     for _ in range(2):                       # twice: buffers and arenas are reused
         out = ep.forward(); dfn = ep.backward()
     torch.cuda.synchronize()
-    assert torch.equal(ep.member("assign", (K, N), torch.int32), ref.member("assign", (K, N), torch.int32))
+    mine = ep.assign.view(K, N) if mode == "peer" else ep.member("assign", (K, N), torch.int32)
+    assert torch.equal(mine, ref.member("assign", (K, N), torch.int32))
     assert torch.equal(out, out_ref)
     assert torch.equal(dfn, dfn_ref)
     assert rel(ep.dWr, dWr) < 1e-5
@@ -60,13 +65,16 @@ def worker(rank, world, port, ret):
         dist.all_reduce(tot)                 # weight gradients over all ranks' tokens
         assert rel(ep.dW[i], tot[rank * el:(rank + 1) * el]) < 1e-2, i
     q.check(q.lib().qlmb_check_device(None))
+    if mode == "peer":
+        ep.close()
     ret[rank] = True
     dist.destroy_process_group()
 
 
-def test_expert_parallel_matches_single_call(cuda):
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
+def test_expert_parallel_matches_single_call(cuda, mode):
     world = min(torch.cuda.device_count(), 2)
     with mp.Manager() as m:
         ret = m.dict()
-        mp.spawn(worker, args=(world, free_port(), ret), nprocs=world, join=True)
+        mp.spawn(worker, args=(world, free_port(), ret, mode), nprocs=world, join=True)
         assert all(ret.get(r) for r in range(world))
