@@ -688,9 +688,10 @@ __global__ void __launch_bounds__(256) k_pull_rowidx(int *rowidx, const int *ass
 }
 
 // home side: out[n] = f_in[n] + sum_k gate[k,n] * yp_{owner}[rowidx[k,n]], k ascending
+// (ykeep[slot] keeps a local copy of every fetched row for the backward's gate gradient)
 __global__ void __launch_bounds__(256) k_combine_rows_peer(void *out, const void *f_in, int dtype, PeerPtrs yp,
                                                            const int *assign, const int *rowidx, const float *gate,
-                                                           int N, int D, int K, int el)
+                                                           bf16 *ykeep, int N, int D, int K, int el)
 {
     const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (n >= N) return;
@@ -701,7 +702,11 @@ __global__ void __launch_bounds__(256) k_combine_rows_peer(void *out, const void
             const size_t slot = (size_t)k * N + n;
             const float g = gate[slot];
             float y[8];
-            ld_act8(yp.p[assign[slot] / el], QLMB_BF16, (size_t)rowidx[slot] * D + (size_t)c * 8, y);
+            const uint4 q = *reinterpret_cast<const uint4 *>((const bf16 *)yp.p[assign[slot] / el] + (size_t)rowidx[slot] * D + (size_t)c * 8);
+            *reinterpret_cast<uint4 *>(ykeep + slot * D + (size_t)c * 8) = q;
+            const __nv_bfloat162 *hq = reinterpret_cast<const __nv_bfloat162 *>(&q);
+#pragma unroll
+            for (int i = 0; i < 4; i++) { float2 f = __bfloat1622float2(hq[i]); y[2 * i] = f.x; y[2 * i + 1] = f.y; }
 #pragma unroll
             for (int i = 0; i < 8; i++) acc[i] += g * y[i];
         }
@@ -709,15 +714,15 @@ __global__ void __launch_bounds__(256) k_combine_rows_peer(void *out, const void
     }
 }
 
-// home side: d_gate[slot] = dout[n] . yp_{owner}[rowidx[slot]]  (one warp per slot)
-__global__ void __launch_bounds__(256) k_dgate_dot_peer(float *d_gate, const void *dout, int dtype, PeerPtrs yp,
-                                                        const int *assign, const int *rowidx, int N, int D, int KN, int el)
+// home side: d_gate[slot] = dout[n] . y[slot], y = the row copies kept by the combine (one warp per slot)
+__global__ void __launch_bounds__(256) k_dgate_dot_peer(float *d_gate, const void *dout, int dtype, const bf16 *ykeep,
+                                                        int N, int D, int KN)
 {
     const int slot = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (slot >= KN) return;
     const int n = slot % N;
-    const void *y = yp.p[assign[slot] / el];
-    const size_t yb = (size_t)rowidx[slot] * D, db = (size_t)n * D;
+    const void *y = ykeep;
+    const size_t yb = (size_t)slot * D, db = (size_t)n * D;
     float dot = 0.0f;
     for (int c = lane; c < D / 8; c += 32) {
         float dv[8], yv[8];
@@ -862,16 +867,15 @@ int pull_rowidx(int *rowidx, const int *assign, const PeerPtrs &inv, int el, int
     return QLMB_OK;
 }
 int combine_rows_peer(void *out, const void *f_in, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
-                      const float *gate, int N, int D, int K, int el, cudaStream_t st)
+                      const float *gate, bf16 *ykeep, int N, int D, int K, int el, cudaStream_t st)
 {
-    k_combine_rows_peer<<<(N + 7) / 8, 256, 0, st>>>(out, f_in, dtype, yp, assign, rowidx, gate, N, D, K, el);
+    k_combine_rows_peer<<<(N + 7) / 8, 256, 0, st>>>(out, f_in, dtype, yp, assign, rowidx, gate, ykeep, N, D, K, el);
     QLMB_LAUNCH_CHECK("k_combine_rows_peer");
     return QLMB_OK;
 }
-int dgate_dot_peer(float *d_gate, const void *dout, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
-                   int N, int D, int K, int el, cudaStream_t st)
+int dgate_dot_peer(float *d_gate, const void *dout, int dtype, const bf16 *ykeep, int N, int D, int K, cudaStream_t st)
 {
-    k_dgate_dot_peer<<<(K * N + 7) / 8, 256, 0, st>>>(d_gate, dout, dtype, yp, assign, rowidx, N, D, K * N, el);
+    k_dgate_dot_peer<<<(K * N + 7) / 8, 256, 0, st>>>(d_gate, dout, dtype, ykeep, N, D, K * N);
     QLMB_LAUNCH_CHECK("k_dgate_dot_peer");
     return QLMB_OK;
 }

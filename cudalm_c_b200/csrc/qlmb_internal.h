@@ -49,9 +49,8 @@ int gather_rows_peer(bf16 *Xp, const PeerPtrs &src, int dtype, const int *perm, 
                      int Nh, int KN, int D, cudaStream_t st);
 int pull_rowidx(int *rowidx, const int *assign, const PeerPtrs &inv, int el, int slot0, int KN, cudaStream_t st);
 int combine_rows_peer(void *out, const void *f_in, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
-                      const float *gate, int N, int D, int K, int el, cudaStream_t st);
-int dgate_dot_peer(float *d_gate, const void *dout, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
-                   int N, int D, int K, int el, cudaStream_t st);
+                      const float *gate, bf16 *ykeep, int N, int D, int K, int el, cudaStream_t st);
+int dgate_dot_peer(float *d_gate, const void *dout, int dtype, const bf16 *ykeep, int N, int D, int K, cudaStream_t st);
 int dyp_rows_peer(bf16 *dyp, const PeerPtrs &dout, const PeerPtrs &gate, int dtype, const int *perm, const int *nrows_dev,
                   int max_rows, int Nh, int KN, int D, cudaStream_t st);
 int unpermute_rows_peer(void *dfnorm, int dtype, const PeerPtrs &dXp, const int *assign, const int *rowidx, int el,

@@ -416,7 +416,7 @@ extern "C" int qlmb_ep_combine(const qlmb_moe_layer *H, void *harena, const qlmb
     { ProfScope ps("pull_rowidx", st);
       if ((rc = pull_rowidx(h.inv, h.assign, peer_view(P, e.inv), L->E, P->rank * KN, KN, st))) return rc; }
     ProfScope ps("combine_rows_peer", st);
-    return combine_rows_peer(out, f_in, H->dtype, peer_view(P, e.yp), h.assign, h.inv, h.gate, H->N, H->D, H->K, L->E, st);
+    return combine_rows_peer(out, f_in, H->dtype, peer_view(P, e.yp), h.assign, h.inv, h.gate, h.yp, H->N, H->D, H->K, L->E, st);
 }
 
 extern "C" int qlmb_ep_dgate(const qlmb_moe_layer *H, void *harena, const qlmb_moe_layer *L, void *earena,
@@ -430,7 +430,7 @@ extern "C" int qlmb_ep_dgate(const qlmb_moe_layer *H, void *harena, const qlmb_m
     Arena h = carve(harena, H->N, H->D, H->F, H->E, H->K);
     Arena e = carve(earena, L->N, L->D, L->F, L->E, 1);
     ProfScope ps("dgate_dot_peer", as_stream(stream));
-    return dgate_dot_peer(h.d_gate, dout, H->dtype, peer_view(P, e.yp), h.assign, h.inv, H->N, H->D, H->K, L->E, as_stream(stream));
+    return dgate_dot_peer(h.d_gate, dout, H->dtype, h.yp, H->N, H->D, H->K, as_stream(stream));
 }
 
 extern "C" int qlmb_ep_experts_backward(const qlmb_moe_layer *L, void *earena, const qlmb_moe_layer *H, void *harena,
