@@ -50,84 +50,99 @@ __device__ __forceinline__ void st_act8(void *p, int dtype, size_t i, const floa
 
 // ------------------------------------------------------------ router logits
 // rt[n,e] = sum_j X[n,j] * Wr[j,e]  (reference cudalm.cu:4158, g_ab with N = E), fp32.
-// Register-tiled: a block of 128 threads owns 64 tokens, a thread 4 tokens (16 apart) x 4 experts; the
-// token tile and Wr are staged through shared memory 32 features at a time (next chunk
-// prefetched into registers while the current one is multiplied).  Each output is summed
-// over the features in ascending order.
+// Register-tiled: a block of 256 threads owns 64 tokens, a thread 2 tokens (32 apart) x 4 experts.
+// The token tile and Wr move through a ring of shared-memory stages, 32 features per stage,
+// filled by cp.async three (bf16) or two (fp32) stages ahead of the multiply.  Each output is
+// summed over the features in ascending order.
 #define RLT_TOK 64
 #define RLT_CH 32
-#define RLT_LD 36
-template <int XBF16>
-__global__ void __launch_bounds__(128) k_router_logits_tile(float *rt, const void *X, const float *Wr, int N, int D, int E)
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, bool live)
 {
-    __shared__ __align__(16) float xs[2][RLT_TOK][RLT_LD];
-    __shared__ __align__(16) float ws[2][RLT_CH][32];
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = live ? 16 : 0;                         // 0 source bytes: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N_> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
+
+template <int XBF16>
+__global__ void __launch_bounds__(256) k_router_logits_tile(float *rt, const void *X, const float *Wr, int N, int D, int E)
+{
+    constexpr int NST = XBF16 ? 4 : 3;                   // stages
+    constexpr int XROW = XBF16 ? 80 : 144;               // bytes per token row of a stage (64 / 128 + pad)
+    __shared__ __align__(16) uint8_t xs[NST][RLT_TOK * XROW];
+    __shared__ __align__(16) float ws[NST][RLT_CH][32];
     const int tid = threadIdx.x, n0 = blockIdx.x * RLT_TOK;
     const int tg = tid >> 3, eg = tid & 7;
-    float acc[4][4];
+    float acc[2][4];
 #pragma unroll
-    for (int t = 0; t < 4; t++)
+    for (int t = 0; t < 2; t++)
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[t][i] = 0.0f;
-    float xr[2][8], wr[8];
-    auto fetch = [&](int j0) {
+    const int nch = (D + RLT_CH - 1) / RLT_CH;
+    auto fill = [&](int c) {
+        if (c < nch) {
+            const int st = c % NST, j0 = c * RLT_CH;
+            // token tile: 16-byte pieces (8 bf16 or 4 fp32 features)
+            constexpr int PPR = XBF16 ? 4 : 8;           // pieces per token row
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const int p = tid + i * 128, tok = p >> 2, part = p & 3;
-            const int n = n0 + tok, j = j0 + part * 8;
-            if (n < N && j < D) ld_act8(X, XBF16 ? QLMB_BF16 : QLMB_F32, (size_t)n * D + j, xr[i]);
-            else {
+            for (int i = 0; i < RLT_TOK * PPR / 256; i++) {
+                const int p = tid + i * 256, tok = p / PPR, part = p % PPR;
+                const int n = n0 + tok, j = j0 + part * (XBF16 ? 8 : 4);
+                const bool live = n < N && j < D;
+                const uint8_t *src = (const uint8_t *)X + (live ? ((size_t)n * D + j) * (XBF16 ? 2 : 4) : 0);
+                cp_async16(&xs[st][tok * XROW + part * 16], src, live);
+            }
+            if (E == 32) {
+                const int row = tid >> 3, c4 = tid & 7;
+                const bool live = j0 + row < D;
+                cp_async16(&ws[st][row][c4 * 4], Wr + (live ? (size_t)(j0 + row) * 32 + c4 * 4 : 0), live);
+            } else {
 #pragma unroll
-                for (int k = 0; k < 8; k++) xr[i][k] = 0.0f;
+                for (int i = 0; i < 4; i++) {
+                    const int q = tid + i * 256, row = q >> 5, e = q & 31;
+                    ws[st][row][e] = (e < E && j0 + row < D) ? __ldg(Wr + (size_t)(j0 + row) * E + e) : 0.0f;
+                }
             }
         }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int q = tid + i * 128, row = q >> 5, e = q & 31;
-            wr[i] = (e < E && j0 + row < D) ? __ldg(Wr + (size_t)(j0 + row) * E + e) : 0.0f;
-        }
+        cp_async_commit();
     };
-    auto stash = [&](int buf) {
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const int p = tid + i * 128, tok = p >> 2, part = p & 3;
-            *reinterpret_cast<float4 *>(&xs[buf][tok][part * 8]) = make_float4(xr[i][0], xr[i][1], xr[i][2], xr[i][3]);
-            *reinterpret_cast<float4 *>(&xs[buf][tok][part * 8 + 4]) = make_float4(xr[i][4], xr[i][5], xr[i][6], xr[i][7]);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int q = tid + i * 128;
-            ws[buf][q >> 5][q & 31] = wr[i];
-        }
-    };
-    fetch(0);
-    stash(0);
-    __syncthreads();
-    const int nch = (D + RLT_CH - 1) / RLT_CH;
+    for (int c = 0; c < NST - 1; c++) fill(c);
     for (int c = 0; c < nch; c++) {
-        const int buf = c & 1;
-        if (c + 1 < nch) fetch((c + 1) * RLT_CH);
+        cp_async_wait<NST - 2>();
+        __syncthreads();
+        fill(c + NST - 1);
+        const int st = c % NST;
 #pragma unroll
         for (int kk = 0; kk < RLT_CH; kk += 4) {
-            float4 xv[4];
+            float xv[2][4];
 #pragma unroll
-            for (int t = 0; t < 4; t++) xv[t] = *reinterpret_cast<const float4 *>(&xs[buf][tg + 16 * t][kk]);
+            for (int t = 0; t < 2; t++) {
+                const uint8_t *row = &xs[st][(tg + 32 * t) * XROW];
+                if (XBF16) {
+                    const uint2 q = *reinterpret_cast<const uint2 *>(row + kk * 2);
+                    xv[t][0] = __uint_as_float(q.x << 16); xv[t][1] = __uint_as_float(q.x & 0xffff0000u);
+                    xv[t][2] = __uint_as_float(q.y << 16); xv[t][3] = __uint_as_float(q.y & 0xffff0000u);
+                } else {
+                    const float4 q = *reinterpret_cast<const float4 *>(row + kk * 4);
+                    xv[t][0] = q.x; xv[t][1] = q.y; xv[t][2] = q.z; xv[t][3] = q.w;
+                }
+            }
 #pragma unroll
             for (int k4 = 0; k4 < 4; k4++) {
-                const float4 w = *reinterpret_cast<const float4 *>(&ws[buf][kk + k4][eg * 4]);
+                const float4 w = *reinterpret_cast<const float4 *>(&ws[st][kk + k4][eg * 4]);
 #pragma unroll
-                for (int t = 0; t < 4; t++) {
-                    const float x = k4 == 0 ? xv[t].x : k4 == 1 ? xv[t].y : k4 == 2 ? xv[t].z : xv[t].w;
+                for (int t = 0; t < 2; t++) {
+                    const float x = xv[t][k4];
                     acc[t][0] += x * w.x; acc[t][1] += x * w.y; acc[t][2] += x * w.z; acc[t][3] += x * w.w;
                 }
             }
         }
-        if (c + 1 < nch) stash(buf ^ 1);
-        __syncthreads();
     }
 #pragma unroll
-    for (int t = 0; t < 4; t++) {
-        const int n = n0 + tg + 16 * t;
+    for (int t = 0; t < 2; t++) {
+        const int n = n0 + tg + 32 * t;
         if (n >= N) continue;
 #pragma unroll
         for (int i = 0; i < 4; i++)
@@ -176,10 +191,10 @@ __global__ void __launch_bounds__(256) k_router_logits(float *rt, const void *X,
 
 int router_logits(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E, cudaStream_t st)
 {
-    if (E <= 32 && (D % 8) == 0) {
+    if (E <= 32 && (D % 8) == 0 && (((uintptr_t)X | (uintptr_t)Wr) & 15) == 0) {
         int blocks = (N + RLT_TOK - 1) / RLT_TOK;
-        if (x_dtype == QLMB_BF16) k_router_logits_tile<1><<<blocks, 128, 0, st>>>(rt, X, Wr, N, D, E);
-        else k_router_logits_tile<0><<<blocks, 128, 0, st>>>(rt, X, Wr, N, D, E);
+        if (x_dtype == QLMB_BF16) k_router_logits_tile<1><<<blocks, 256, 0, st>>>(rt, X, Wr, N, D, E);
+        else k_router_logits_tile<0><<<blocks, 256, 0, st>>>(rt, X, Wr, N, D, E);
     } else {
         k_router_logits<<<(N + RL_TOK - 1) / RL_TOK, 256, 0, st>>>(rt, X, x_dtype, Wr, N, D, E);
     }
@@ -358,90 +373,124 @@ __global__ void __launch_bounds__(256) k_transpose_wr(float *WrT, const float *W
     int i = blockIdx.x * 256 + threadIdx.x;
     if (i < D * E) { int j = i / E, e = i % E; WrT[(size_t)e * D + j] = Wr[i]; }
 }
-// Register-tiled: a block owns 32 tokens x 256 features; warp = 4 tokens, lane = features
-// [4*lane, 4*lane+4) and [128+4*lane, ...) of the block's slice.  The slice of WrT and the
-// tokens' drt rows sit in shared memory; the K permuted rows are fetched first so their
-// latency overlaps the staging.
+// Register-tiled: a block owns 256 features and walks over tiles of 32 tokens; warp = 4 tokens,
+// lane = features [4*lane, 4*lane+4) and [128+4*lane, ...) of the block's slice.  The slice of WrT
+// is staged in shared memory once per block, the tokens' drt rows and row indices per tile.
+// With PEER the permuted rows live in the arena of the rank that owns the slot's expert
+// (rows = that arena's row index per slot, read through the peer pointers).
 #define UPT_TOK 32
 #define UPT_F 256
-__global__ void __launch_bounds__(256, 3) k_unpermute_rows_tile(void *dfnorm, int dtype, const bf16 *dXp, const int *inv,
-                                                                const float *drt, const float *WrT, int N, int D, int E, int K)
+template <bool PEER>
+__global__ void __launch_bounds__(256, 3) k_unpermute_rows_tile(void *dfnorm, int dtype, const bf16 *dXp, PeerPtrs dXpP,
+                                                                const int *rows, const int *assign, int el, const float *drt,
+                                                                const float *WrT, int N, int D, int E, int K)
 {
     __shared__ __align__(16) float ws[32][UPT_F];
     __shared__ __align__(16) float drs[UPT_TOK][32];
+    __shared__ int srow[UPT_TOK][8], sown[UPT_TOK][8];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * UPT_TOK, j0 = blockIdx.y * UPT_F;
+    const int j0 = blockIdx.y * UPT_F;
     const int jA = j0 + lane * 4, jB = jA + 128;
-    float acc[4][8];
-#pragma unroll
-    for (int t = 0; t < 4; t++) {
-        const int n = n0 + warp * 4 + t;
-#pragma unroll
-        for (int i = 0; i < 8; i++) acc[t][i] = 0.0f;
-        if (n >= N) continue;
-        for (int k = 0; k < K; k++) {
-            const size_t row = (size_t)__ldg(inv + (size_t)k * N + n) * D;
-            if (jA < D) {
-                uint2 q = __ldg(reinterpret_cast<const uint2 *>(dXp + row + jA));
-                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
-                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
-                acc[t][0] += a.x; acc[t][1] += a.y; acc[t][2] += b.x; acc[t][3] += b.y;
-            }
-            if (jB < D) {
-                uint2 q = __ldg(reinterpret_cast<const uint2 *>(dXp + row + jB));
-                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
-                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
-                acc[t][4] += a.x; acc[t][5] += a.y; acc[t][6] += b.x; acc[t][7] += b.y;
-            }
-        }
-    }
     for (int i = tid; i < 32 * (UPT_F / 4); i += 256) {
         const int e = i / (UPT_F / 4), c = i % (UPT_F / 4), j = j0 + c * 4;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (e < E && j < D) v = __ldg(reinterpret_cast<const float4 *>(WrT + (size_t)e * D + j));
         *reinterpret_cast<float4 *>(&ws[e][c * 4]) = v;
     }
-    for (int i = tid; i < UPT_TOK * 32; i += 256) {
-        const int n = n0 + (i >> 5), e = i & 31;
-        drs[i >> 5][e] = (n < N && e < E) ? drt[(size_t)n * E + e] : 0.0f;
-    }
-    __syncthreads();
-#pragma unroll 2
-    for (int e4 = 0; e4 < 32; e4 += 4) {
-        float4 dv[4];
+    const int ntiles = (N + UPT_TOK - 1) / UPT_TOK;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int n0 = tile * UPT_TOK;
+        __syncthreads();                                 // the previous tile's reads of drs / srow are done
+        for (int i = tid; i < UPT_TOK * K; i += 256) {
+            const int t = i / K, k = i % K, n = n0 + t;
+            int row = -1, own = 0;
+            if (n < N) {
+                const size_t slot = (size_t)k * N + n;
+                row = __ldg(rows + slot);
+                if (PEER) own = __ldg(assign + slot) / el;
+            }
+            srow[t][k] = row; sown[t][k] = own;
+        }
+        for (int i = tid; i < UPT_TOK * 32; i += 256) {
+            const int n = n0 + (i >> 5), e = i & 31;
+            drs[i >> 5][e] = (n < N && e < E) ? drt[(size_t)n * E + e] : 0.0f;
+        }
+        __syncthreads();
+        // the K permuted rows of the warp's 4 tokens: all loads of one k are in flight together
+        float acc[4][8];
 #pragma unroll
-        for (int t = 0; t < 4; t++) dv[t] = *reinterpret_cast<const float4 *>(&drs[warp * 4 + t][e4]);
+        for (int t = 0; t < 4; t++)
 #pragma unroll
-        for (int k4 = 0; k4 < 4; k4++) {
-            const float4 wa = *reinterpret_cast<const float4 *>(&ws[e4 + k4][lane * 4]);
-            const float4 wb = *reinterpret_cast<const float4 *>(&ws[e4 + k4][128 + lane * 4]);
+            for (int i = 0; i < 8; i++) acc[t][i] = 0.0f;
+        for (int k = 0; k < K; k++) {
+            uint2 qa[4], qb[4];
 #pragma unroll
             for (int t = 0; t < 4; t++) {
-                const float d = k4 == 0 ? dv[t].x : k4 == 1 ? dv[t].y : k4 == 2 ? dv[t].z : dv[t].w;
-                acc[t][0] += d * wa.x; acc[t][1] += d * wa.y; acc[t][2] += d * wa.z; acc[t][3] += d * wa.w;
-                acc[t][4] += d * wb.x; acc[t][5] += d * wb.y; acc[t][6] += d * wb.z; acc[t][7] += d * wb.w;
+                const int row = srow[warp * 4 + t][k];
+                qa[t] = qb[t] = make_uint2(0u, 0u);
+                if (row >= 0) {
+                    const bf16 *src = (PEER ? (const bf16 *)dXpP.p[sown[warp * 4 + t][k]] : dXp) + (size_t)row * D;
+                    if (jA < D) qa[t] = *reinterpret_cast<const uint2 *>(src + jA);
+                    if (jB < D) qb[t] = *reinterpret_cast<const uint2 *>(src + jB);
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&qa[t].x));
+                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&qa[t].y));
+                acc[t][0] += a.x; acc[t][1] += a.y; acc[t][2] += b.x; acc[t][3] += b.y;
+                a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&qb[t].x));
+                b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&qb[t].y));
+                acc[t][4] += a.x; acc[t][5] += a.y; acc[t][6] += b.x; acc[t][7] += b.y;
+            }
+        }
+#pragma unroll 2
+        for (int e4 = 0; e4 < 32; e4 += 4) {
+            float4 dv[4];
+#pragma unroll
+            for (int t = 0; t < 4; t++) dv[t] = *reinterpret_cast<const float4 *>(&drs[warp * 4 + t][e4]);
+#pragma unroll
+            for (int k4 = 0; k4 < 4; k4++) {
+                const float4 wa = *reinterpret_cast<const float4 *>(&ws[e4 + k4][lane * 4]);
+                const float4 wb = *reinterpret_cast<const float4 *>(&ws[e4 + k4][128 + lane * 4]);
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    const float d = k4 == 0 ? dv[t].x : k4 == 1 ? dv[t].y : k4 == 2 ? dv[t].z : dv[t].w;
+                    acc[t][0] += d * wa.x; acc[t][1] += d * wa.y; acc[t][2] += d * wa.z; acc[t][3] += d * wa.w;
+                    acc[t][4] += d * wb.x; acc[t][5] += d * wb.y; acc[t][6] += d * wb.z; acc[t][7] += d * wb.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            const int n = n0 + warp * 4 + t;
+            if (n >= N) continue;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int j = h ? jB : jA;
+                if (j >= D) continue;
+                const float *v = &acc[t][h * 4];
+                if (dtype == QLMB_BF16) {
+                    uint2 q;
+                    *reinterpret_cast<__nv_bfloat162 *>(&q.x) = __floats2bfloat162_rn(v[0], v[1]);
+                    *reinterpret_cast<__nv_bfloat162 *>(&q.y) = __floats2bfloat162_rn(v[2], v[3]);
+                    *reinterpret_cast<uint2 *>((bf16 *)dfnorm + (size_t)n * D + j) = q;
+                } else {
+                    *reinterpret_cast<float4 *>((float *)dfnorm + (size_t)n * D + j) = make_float4(v[0], v[1], v[2], v[3]);
+                }
             }
         }
     }
-#pragma unroll
-    for (int t = 0; t < 4; t++) {
-        const int n = n0 + warp * 4 + t;
-        if (n >= N) continue;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int j = h ? jB : jA;
-            if (j >= D) continue;
-            const float *v = &acc[t][h * 4];
-            if (dtype == QLMB_BF16) {
-                uint2 q;
-                *reinterpret_cast<__nv_bfloat162 *>(&q.x) = __floats2bfloat162_rn(v[0], v[1]);
-                *reinterpret_cast<__nv_bfloat162 *>(&q.y) = __floats2bfloat162_rn(v[2], v[3]);
-                *reinterpret_cast<uint2 *>((bf16 *)dfnorm + (size_t)n * D + j) = q;
-            } else {
-                *reinterpret_cast<float4 *>((float *)dfnorm + (size_t)n * D + j) = make_float4(v[0], v[1], v[2], v[3]);
-            }
-        }
-    }
+}
+static dim3 unpermute_grid(int N, int D)
+{
+    const int ny = (D + UPT_F - 1) / UPT_F, ntiles = (N + UPT_TOK - 1) / UPT_TOK;
+    int gx = 3 * sm_count() / ny;
+    if (gx < 1) gx = 1;
+    if (gx > ntiles) gx = ntiles;
+    const int per = (ntiles + gx - 1) / gx;              // whole tiles per block, evenly
+    gx = (ntiles + per - 1) / per;
+    return dim3(gx, ny);
 }
 
 // General shape: a block owns 8 tokens; a thread owns feature columns j = tid, tid+256, ...
@@ -489,7 +538,8 @@ int unpermute_rows(void *dfnorm, int dtype, const bf16 *dXp, const int *inv, con
 {
     if (E <= 32 && (D % 8) == 0 && wrt_scratch) {
         k_transpose_wr<<<(D * E + 255) / 256, 256, 0, st>>>(wrt_scratch, Wr, D, E);
-        k_unpermute_rows_tile<<<dim3((N + UPT_TOK - 1) / UPT_TOK, (D + UPT_F - 1) / UPT_F), 256, 0, st>>>(dfnorm, dtype, dXp, inv, drt, wrt_scratch, N, D, E, K);
+        PeerPtrs none = {};
+        k_unpermute_rows_tile<false><<<unpermute_grid(N, D), 256, 0, st>>>(dfnorm, dtype, dXp, none, inv, nullptr, 1, drt, wrt_scratch, N, D, E, K);
     } else {
         size_t smem = (size_t)UP_TOK * E * sizeof(float) + (size_t)UP_TOK * K * sizeof(int);
         k_unpermute_rows<<<(N + UP_TOK - 1) / UP_TOK, 256, smem, st>>>(dfnorm, dtype, dXp, inv, drt, Wr, N, D, E, K);
@@ -614,13 +664,18 @@ __global__ void __launch_bounds__(256) k_router_wgrad_tile(float *part, const vo
             if (eg * 4 + i < E) part[((size_t)c * D + j) * E + eg * 4 + i] = acc[f][i];
     }
 }
+// four lanes per output: each adds one quarter of the chunks in ascending order, then the quarters
+// are combined as (q0 + q1) + (q2 + q3) -- a fixed order, so the result is run-to-run identical
 __global__ void __launch_bounds__(256) k_router_wgrad_sum(float *dWr, const float *part, int nchunk, int DE, float beta)
 {
-    int i = blockIdx.x * 256 + threadIdx.x;
-    if (i >= DE) return;
+    const int gid = blockIdx.x * 256 + threadIdx.x, i = gid >> 2, q = gid & 3;
+    const int per = (nchunk + 3) / 4, c0 = q * per, c1 = c0 + per < nchunk ? c0 + per : nchunk;
     float s = 0.0f;
-    for (int c = 0; c < nchunk; c++) s += part[(size_t)c * DE + i];
-    dWr[i] = (beta != 0.0f ? beta * dWr[i] : 0.0f) + s;
+    if (i < DE)
+        for (int c = c0; c < c1; c++) s += part[(size_t)c * DE + i];
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if (i < DE && q == 0) dWr[i] = (beta != 0.0f ? beta * dWr[i] : 0.0f) + s;
 }
 
 int router_wgrad(float *dWr, const void *fnorm, int dtype, const float *drt, float *scratch, int N, int D, int E,
@@ -640,7 +695,7 @@ int router_wgrad(float *dWr, const void *fnorm, int dtype, const float *drt, flo
         for (int e0 = 0; e0 < E; e0 += 32)
             k_router_wgrad_part<<<dim3(RW_CHUNKS, (D + 255) / 256), 256, 0, st>>>(scratch, fnorm, dtype, drt, N, D, E, e0);
     }
-    k_router_wgrad_sum<<<(D * E + 255) / 256, 256, 0, st>>>(dWr, scratch, nchunk, D * E, beta);
+    k_router_wgrad_sum<<<(4 * D * E + 255) / 256, 256, 0, st>>>(dWr, scratch, nchunk, D * E, beta);
     QLMB_LAUNCH_CHECK("router_wgrad");
     return QLMB_OK;
 }
@@ -760,90 +815,6 @@ __global__ void __launch_bounds__(256) k_dyp_rows_peer(bf16 *dyp, PeerPtrs dout,
     }
 }
 
-// home side: dfnorm[n,j] = sum_k dXp_{owner}[rowidx[k,n], j] + sum_e drt[n,e] * Wr[j,e]
-// (same tiling as k_unpermute_rows_tile; only the row source differs)
-__global__ void __launch_bounds__(256, 3) k_unpermute_rows_tile_peer(void *dfnorm, int dtype, PeerPtrs dXp, const int *assign,
-                                                                     const int *rowidx, int el, const float *drt,
-                                                                     const float *WrT, int N, int D, int E, int K)
-{
-    __shared__ __align__(16) float ws[32][UPT_F];
-    __shared__ __align__(16) float drs[UPT_TOK][32];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * UPT_TOK, j0 = blockIdx.y * UPT_F;
-    const int jA = j0 + lane * 4, jB = jA + 128;
-    float acc[4][8];
-#pragma unroll
-    for (int t = 0; t < 4; t++) {
-        const int n = n0 + warp * 4 + t;
-#pragma unroll
-        for (int i = 0; i < 8; i++) acc[t][i] = 0.0f;
-        if (n >= N) continue;
-        for (int k = 0; k < K; k++) {
-            const size_t slot = (size_t)k * N + n;
-            const bf16 *src = (const bf16 *)dXp.p[__ldg(assign + slot) / el] + (size_t)__ldg(rowidx + slot) * D;
-            if (jA < D) {
-                uint2 q = *reinterpret_cast<const uint2 *>(src + jA);
-                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
-                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
-                acc[t][0] += a.x; acc[t][1] += a.y; acc[t][2] += b.x; acc[t][3] += b.y;
-            }
-            if (jB < D) {
-                uint2 q = *reinterpret_cast<const uint2 *>(src + jB);
-                float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
-                float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
-                acc[t][4] += a.x; acc[t][5] += a.y; acc[t][6] += b.x; acc[t][7] += b.y;
-            }
-        }
-    }
-    for (int i = tid; i < 32 * (UPT_F / 4); i += 256) {
-        const int e = i / (UPT_F / 4), c = i % (UPT_F / 4), j = j0 + c * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (e < E && j < D) v = __ldg(reinterpret_cast<const float4 *>(WrT + (size_t)e * D + j));
-        *reinterpret_cast<float4 *>(&ws[e][c * 4]) = v;
-    }
-    for (int i = tid; i < UPT_TOK * 32; i += 256) {
-        const int n = n0 + (i >> 5), e = i & 31;
-        drs[i >> 5][e] = (n < N && e < E) ? drt[(size_t)n * E + e] : 0.0f;
-    }
-    __syncthreads();
-#pragma unroll 2
-    for (int e4 = 0; e4 < 32; e4 += 4) {
-        float4 dv[4];
-#pragma unroll
-        for (int t = 0; t < 4; t++) dv[t] = *reinterpret_cast<const float4 *>(&drs[warp * 4 + t][e4]);
-#pragma unroll
-        for (int k4 = 0; k4 < 4; k4++) {
-            const float4 wa = *reinterpret_cast<const float4 *>(&ws[e4 + k4][lane * 4]);
-            const float4 wb = *reinterpret_cast<const float4 *>(&ws[e4 + k4][128 + lane * 4]);
-#pragma unroll
-            for (int t = 0; t < 4; t++) {
-                const float d = k4 == 0 ? dv[t].x : k4 == 1 ? dv[t].y : k4 == 2 ? dv[t].z : dv[t].w;
-                acc[t][0] += d * wa.x; acc[t][1] += d * wa.y; acc[t][2] += d * wa.z; acc[t][3] += d * wa.w;
-                acc[t][4] += d * wb.x; acc[t][5] += d * wb.y; acc[t][6] += d * wb.z; acc[t][7] += d * wb.w;
-            }
-        }
-    }
-#pragma unroll
-    for (int t = 0; t < 4; t++) {
-        const int n = n0 + warp * 4 + t;
-        if (n >= N) continue;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int j = h ? jB : jA;
-            if (j >= D) continue;
-            const float *v = &acc[t][h * 4];
-            if (dtype == QLMB_BF16) {
-                uint2 q;
-                *reinterpret_cast<__nv_bfloat162 *>(&q.x) = __floats2bfloat162_rn(v[0], v[1]);
-                *reinterpret_cast<__nv_bfloat162 *>(&q.y) = __floats2bfloat162_rn(v[2], v[3]);
-                *reinterpret_cast<uint2 *>((bf16 *)dfnorm + (size_t)n * D + j) = q;
-            } else {
-                *reinterpret_cast<float4 *>((float *)dfnorm + (size_t)n * D + j) = make_float4(v[0], v[1], v[2], v[3]);
-            }
-        }
-    }
-}
-
 // counts[e] = how many of the K*N slots chose expert e (integer atomics: order independent)
 __global__ void __launch_bounds__(256) k_count_assign(int *counts, const int *assign, int KN, int E)
 {
@@ -892,8 +863,7 @@ int unpermute_rows_peer(void *dfnorm, int dtype, const PeerPtrs &dXp, const int 
                         const float *drt, const float *Wr, float *wrt_scratch, int N, int D, int E, int K, cudaStream_t st)
 {
     k_transpose_wr<<<(D * E + 255) / 256, 256, 0, st>>>(wrt_scratch, Wr, D, E);
-    k_unpermute_rows_tile_peer<<<dim3((N + UPT_TOK - 1) / UPT_TOK, (D + UPT_F - 1) / UPT_F), 256, 0, st>>>(
-        dfnorm, dtype, dXp, assign, rowidx, el, drt, wrt_scratch, N, D, E, K);
+    k_unpermute_rows_tile<true><<<unpermute_grid(N, D), 256, 0, st>>>(dfnorm, dtype, nullptr, dXp, rowidx, assign, el, drt, wrt_scratch, N, D, E, K);
     QLMB_LAUNCH_CHECK("k_unpermute_rows_tile_peer");
     return QLMB_OK;
 }
