@@ -145,7 +145,7 @@ def run_ours(args):
         def step():
             L.forward(fi, fn, out=out)
             L.backward(dout, fn, grads[0], grads[1], grads[2], grads[3], beta=0.0, dfnorm=dfn)
-        launches_per_step = 19
+        launches_per_step = 20
         parallelism = "single"
 
     def barrier():

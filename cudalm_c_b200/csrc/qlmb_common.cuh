@@ -31,6 +31,10 @@ int *device_error_word(void);                            // per-device int, lazi
 
 static inline cudaStream_t as_stream(void *s) { return (cudaStream_t)s; }
 int sm_count(void);                                      // SMs of the current device
+// second stream of the device for overlappable work (qlmb_runtime.cu); returns `st` itself when unavailable
+cudaStream_t side_fork(cudaStream_t st);
+void side_wait_main(cudaStream_t side, cudaStream_t st);
+void side_join(cudaStream_t side, cudaStream_t st);
 // Times the enclosed launches with CUDA events when qlmb_prof_enable(1) was called.
 struct ProfScope {
     int slot; cudaStream_t stream;

@@ -106,12 +106,28 @@ static int experts_forward_gemms(const qlmb_moe_layer *L, const Arena &a, cudaSt
     return gemm_launch(h, st);
 }
 
-// d(act) with the SwiGLU backward, dXp, and the three weight gradients (cudalm.cu:4335-4366)
+// d(act) with the SwiGLU backward, dXp, and the three weight gradients (cudalm.cu:4335-4366).
+// The weight gradients run on the device's side stream: dW2 needs only what exists before this
+// call, dW1/dW3 need d(act)'s outputs; their tiles fill the SMs that the last, partial wave of
+// d(act) and dXp leaves idle.  Everything is joined back into `st` before returning.
 static int experts_backward_gemms(const qlmb_moe_layer *L, const Arena &a, float *dW1, float *dW3, float *dW2,
                                   float beta, cudaStream_t st)
 {
     const int D = L->D, F = L->F, E = L->E, R = (int)a.rows_cap;
     int rc;
+    struct { const bf16 *A; int Ma; const bf16 *B; int Nb; float *out; const char *name; } wg[3] = {
+        {a.ap, F, a.dyp, D, dW2, "gemm_wgrad_w2"}, {a.Xp, D, a.dgp, F, dW1, "gemm_wgrad_w1"}, {a.Xp, D, a.dup, F, dW3, "gemm_wgrad_w3"}};
+    auto wgrad = [&](int i, cudaStream_t s) {
+        GemmLaunch w = {};
+        w.bmode = AB_TMA_MN; w.epi = EPI_ACCUM; w.sched = SCHED_GROUPK;
+        w.a[0] = wg[i].A; w.a_rows = R; w.a_cols = wg[i].Ma;
+        w.w[0] = wg[i].B; w.w_cols = wg[i].Nb;
+        w.nseg = 1; w.M = wg[i].Ma; w.N = wg[i].Nb; w.E = E; w.off = a.off;
+        w.out = wg[i].out; w.out_dtype = QLMB_F32; w.ldo = wg[i].Nb; w.beta = beta; w.name = wg[i].name;
+        return gemm_launch(w, s);
+    };
+    cudaStream_t side = side_fork(st);
+    if ((rc = wgrad(0, side))) { side_join(side, st); return rc; }
     GemmLaunch g = {};
     g.bmode = B_DEQ_K; g.epi = EPI_SWIGLU_BWD; g.sched = SCHED_ROWS;
     g.a[0] = a.dyp; g.a_rows = R; g.a_cols = D;
@@ -119,7 +135,8 @@ static int experts_backward_gemms(const qlmb_moe_layer *L, const Arena &a, float
     g.w_rows = F; g.w_cols = D; g.nseg = 1; g.ksteps = D / 64; g.M = R; g.N = F; g.E = E;
     g.tile_info = a.tile_info; g.ntiles_dev = a.ntiles; g.max_row_tiles = R / 256 + E / 2 + 1;
     g.gp = a.gp; g.up = a.up; g.dgp = a.dgp; g.dup = a.dup; g.ldo = F; g.name = "gemm_dact_swiglu_bwd";
-    if ((rc = gemm_launch(g, st))) return rc;
+    if ((rc = gemm_launch(g, st))) { side_join(side, st); return rc; }
+    side_wait_main(side, st);
     GemmLaunch h = {};
     h.bmode = B_DEQ_K; h.epi = EPI_STORE; h.sched = SCHED_ROWS;
     h.a[0] = a.dgp; h.a[1] = a.dup; h.a_rows = R; h.a_cols = F;
@@ -127,19 +144,11 @@ static int experts_backward_gemms(const qlmb_moe_layer *L, const Arena &a, float
     h.w_rows = D; h.w_cols = F; h.nseg = 2; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
     h.tile_info = a.tile_info; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 256 + E / 2 + 1;
     h.out = a.dXp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_dx";
-    if ((rc = gemm_launch(h, st))) return rc;
-    struct { const bf16 *A; int Ma; const bf16 *B; int Nb; float *out; const char *name; } wg[3] = {
-        {a.Xp, D, a.dgp, F, dW1, "gemm_wgrad_w1"}, {a.Xp, D, a.dup, F, dW3, "gemm_wgrad_w3"}, {a.ap, F, a.dyp, D, dW2, "gemm_wgrad_w2"}};
-    for (int i = 0; i < 3; i++) {
-        GemmLaunch w = {};
-        w.bmode = AB_TMA_MN; w.epi = EPI_ACCUM; w.sched = SCHED_GROUPK;
-        w.a[0] = wg[i].A; w.a_rows = R; w.a_cols = wg[i].Ma;
-        w.w[0] = wg[i].B; w.w_cols = wg[i].Nb;
-        w.nseg = 1; w.M = wg[i].Ma; w.N = wg[i].Nb; w.E = E; w.off = a.off;
-        w.out = wg[i].out; w.out_dtype = QLMB_F32; w.ldo = wg[i].Nb; w.beta = beta; w.name = wg[i].name;
-        if ((rc = gemm_launch(w, st))) return rc;
-    }
-    return QLMB_OK;
+    rc = gemm_launch(h, st);
+    if (!rc) rc = wgrad(1, side);
+    if (!rc) rc = wgrad(2, side);
+    side_join(side, st);
+    return rc;
 }
 
 }  // namespace qlmb

@@ -2,6 +2,7 @@
 // word that kernels with bounded waits report into, and device queries.
 #include "qlmb_common.cuh"
 #include <string.h>
+#include <stdlib.h>
 
 namespace qlmb {
 
@@ -49,6 +50,45 @@ int sm_count(void)
     return g_sms[dev];
 }
 
+
+// ---- a second stream per device for work that may overlap the caller's stream ----
+// side_fork() makes the side stream wait for everything queued on `st` so far, side_join()
+// makes `st` wait for everything queued on the side stream; side_wait_main() is a second
+// fork point in between.  QLMB_SIDE_STREAM=0 runs everything on the caller's stream.
+static cudaStream_t g_side[64];
+static cudaEvent_t g_side_ev[64][3];
+static int g_side_on = -1;
+
+cudaStream_t side_fork(cudaStream_t st)
+{
+    if (g_side_on < 0) { const char *e = getenv("QLMB_SIDE_STREAM"); g_side_on = (e && atoi(e) == 0) ? 0 : 1; }
+    int dev = 0;
+    if (!g_side_on || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return st;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return st;
+    if (!g_side[dev]) {
+        if (cudaStreamCreateWithFlags(&g_side[dev], cudaStreamNonBlocking) != cudaSuccess) { g_side[dev] = nullptr; return st; }
+        for (int i = 0; i < 3; i++)
+            if (cudaEventCreateWithFlags(&g_side_ev[dev][i], cudaEventDisableTiming) != cudaSuccess) return st;
+    }
+    if (cudaEventRecord(g_side_ev[dev][0], st) != cudaSuccess) return st;
+    if (cudaStreamWaitEvent(g_side[dev], g_side_ev[dev][0], 0) != cudaSuccess) return st;
+    return g_side[dev];
+}
+void side_wait_main(cudaStream_t side, cudaStream_t st)
+{
+    int dev = 0;
+    if (side == st || cudaGetDevice(&dev) != cudaSuccess) return;
+    cudaEventRecord(g_side_ev[dev][1], st);
+    cudaStreamWaitEvent(side, g_side_ev[dev][1], 0);
+}
+void side_join(cudaStream_t side, cudaStream_t st)
+{
+    int dev = 0;
+    if (side == st || cudaGetDevice(&dev) != cudaSuccess) return;
+    cudaEventRecord(g_side_ev[dev][2], side);
+    cudaStreamWaitEvent(st, g_side_ev[dev][2], 0);
+}
 
 // ---- optional per-kernel timing (CUDA events on the launching stream) ----
 static bool g_prof_on = false;

@@ -163,7 +163,7 @@ class PeerExpertParallelLayer:
     exchange only the routing table (one fixed-size all-gather) and two one-element all-reduces
     that act as stream-ordered barriers; nothing waits on the host."""
 
-    launches_per_step = 25          # library kernels per forward+backward on a rank
+    launches_per_step = 23          # library kernels per forward+backward on a rank
 
     def __init__(self, cfg, dev, rank, world, seed=1234, aux=0.03, group=None, weights=None):
         import ctypes as C
