@@ -180,6 +180,7 @@ def run_ours(args):
     # per-kernel durations (events inside the library) over a few extra steps
     roof, kern = None, {}
     if True:
+        q.check(lib.qlmb_side_stream_enable(0))      # overlapped kernels would be timed with their waiting
         q.check(lib.qlmb_prof_enable(1))
         reps = 5
         for _ in range(reps):
@@ -187,6 +188,7 @@ def run_ours(args):
         names = C.create_string_buffer(64 * 512); msb = (C.c_float * 512)()
         n = lib.qlmb_prof_read(names, msb, 512)
         lib.qlmb_prof_enable(0)
+        q.check(lib.qlmb_side_stream_enable(1))
         for i in range(max(n, 0)):
             nm = names.raw[64 * i:64 * i + 64].split(b"\0")[0].decode()
             kern.setdefault(nm, []).append(msb[i])

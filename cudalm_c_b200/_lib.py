@@ -38,6 +38,7 @@ PROTOTYPES = {
     "qlmb_version": (ci, []),
     "qlmb_check_device": (ci, [vp]),
     "qlmb_prof_enable": (ci, [ci]),
+    "qlmb_side_stream_enable": (ci, [ci]),
     "qlmb_prof_read": (ci, [vp, vp, ci]),
     "qlmb_encode": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_render": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),

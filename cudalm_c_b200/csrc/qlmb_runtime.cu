@@ -82,6 +82,13 @@ void side_wait_main(cudaStream_t side, cudaStream_t st)
     cudaEventRecord(g_side_ev[dev][1], st);
     cudaStreamWaitEvent(side, g_side_ev[dev][1], 0);
 }
+}  // namespace qlmb
+extern "C" int qlmb_side_stream_enable(int on)
+{
+    qlmb::g_side_on = on ? 1 : 0;
+    return QLMB_OK;
+}
+namespace qlmb {
 void side_join(cudaStream_t side, cudaStream_t st)
 {
     int dev = 0;

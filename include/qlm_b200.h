@@ -65,6 +65,13 @@ int qlmb_version(void);
  * wait expires (QLMB_E_DEVICE); synchronises `stream`. */
 int qlmb_check_device(void *stream);
 
+/* Work that does not depend on each other inside one call (the three expert weight-gradient GEMMs
+ * of the MoE backward against d(act) and dX) runs on a second, library-owned stream per device and
+ * is joined back into the caller's stream before the call returns.  on = 0 keeps everything on the
+ * caller's stream (also: environment QLMB_SIDE_STREAM=0, and always while the stream is being
+ * captured).  No reference counterpart (the reference uses the default stream only). */
+int qlmb_side_stream_enable(int on);
+
 /* Per-operator timing, the counterpart of the reference's CUDALM_PROF=3 event
  * timers (cudalm.cu:806-825): while enabled, every kernel launch of the MoE
  * and linear entry points is bracketed by CUDA events on its stream.
