@@ -43,7 +43,8 @@ struct GemmParams {
     alignas(64) CUtensorMap a_map[2];
     alignas(64) CUtensorMap w_map[2];
     alignas(64) CUtensorMap o_map[3];      // bf16 outputs written by bulk tensor stores (boxes of 32 rows x 64 columns)
-    int o_tma;                             // 1: o_map valid
+    alignas(64) CUtensorMap i_map[2];      // SwiGLU backward: stashed gate / up, boxes of 32 rows x 32 columns
+    int o_tma;                             // 1: o_map (and i_map) valid
     const float *scales[2];
     int nseg, ksteps;
     int M, N, E;
@@ -323,15 +324,20 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams &p, int tile, i
 
 __device__ __forceinline__ float sigmoid_f(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
 
+struct EpiCtx;
+__device__ __forceinline__ bool swiglu_bwd_bulk(const GemmParams &p, uint8_t *stage, EpiCtx &ec, int lane, uint32_t tbase,
+                                                long long rbase, long long col0);
+
 // ------------------------------------------------------------------ fused epilogues
 // One warp, 32 tile rows (lane = row) x 128 accumulator columns starting at TMEM
 // address tbase; rbase = index of the warp's first row in the output, col0 = first
 // output column.  EPI_SWIGLU reads 64 gate columns at tbase and 64 up columns at
 // tbase + u_off and writes 64 activation columns.
 template <int EPI>
-__device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stage, int lane, uint32_t tbase,
+__device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stage, EpiCtx &ec, int lane, uint32_t tbase,
                                               long long rbase, long long col0, int valid, bool have_acc, uint32_t u_off)
 {
+    if (EPI == EPI_SWIGLU_BWD && p.o_tma) { swiglu_bwd_bulk(p, stage, ec, lane, tbase, rbase, col0); return; }
     if (EPI == EPI_STORE && p.out_dtype == QLMB_BF16 && !p.resid && p.beta == 0.0f) {
         // plain bf16 store: two blocks of 64 columns, each written with whole 128-byte rows
 #pragma unroll 1
@@ -486,11 +492,83 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
     }
 }
 
+// Per-warp state of the SwiGLU-backward epilogue's input ring: two mbarriers (one per 4 KiB buffer)
+// and the parity to wait for next on each.
+struct EpiCtx { uint64_t *bar; uint32_t ph; };
+
+// SwiGLU backward over bulk tensor copies: the warp's 128 columns are four groups of 32; a group's
+// gate and up pieces (32 rows x 64 bytes each) arrive by TMA in one of two buffers, the results
+// overwrite them in place and leave by TMA.  The load of group j+1 is issued before group j is
+// computed, the load of the next tile's group 0 before its accumulator is ready.
+__device__ __forceinline__ void swiglu_bwd_issue(const GemmParams &p, uint8_t *buf, uint64_t *bar, int lane, int x, int y)
+{
+    if (lane == 0) bulk_wait_read();                     // stores that still read this buffer
+    __syncwarp();
+    if (lane == 0) {
+        mbar_expect_tx(smem_u32(bar), 4096);
+        tma_load_2d(smem_u32(buf), &p.i_map[0], smem_u32(bar), x, y);
+        tma_load_2d(smem_u32(buf + 2048), &p.i_map[1], smem_u32(bar), x, y);
+    }
+}
+__device__ __forceinline__ bool swiglu_bwd_bulk(const GemmParams &p, uint8_t *stage, EpiCtx &ec, int lane, uint32_t tbase,
+                                                long long rbase, long long col0)
+{
+#pragma unroll 1
+    for (int j = 0; j < 4; j++) {
+        const int b = j & 1;
+        uint8_t *bg = stage + b * 4096, *bu = bg + 2048;
+        if (j < 3) swiglu_bwd_issue(p, stage + (b ^ 1) * 4096, ec.bar + (b ^ 1), lane, (int)(col0 + (j + 1) * 32), (int)rbase);
+        bool ok = false;
+        for (uint32_t i = 0; i < WAIT_LIMIT && !ok; i++) ok = mbar_try(smem_u32(ec.bar + b), (ec.ph >> b) & 1u);
+        if (!ok) { if (p.errword && atomicCAS(p.errword, 0, 202) == 0) { p.errword[1] = 30 + j; p.errword[2] = (int)blockIdx.x; } return false; }
+        ec.ph ^= 1u << b;
+#pragma unroll 1
+        for (int c = 0; c < 2; c++) {
+            uint32_t v[16];
+            tmem_ld16(tbase + j * 32 + c * 16, v);
+            uint4 rg[2], ru[2], wdg[2], wdu[2];
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                rg[k] = *reinterpret_cast<const uint4 *>(bg + lane * 64 + stage_slot<4>(lane, 2 * c + k) * 16);
+                ru[k] = *reinterpret_cast<const uint4 *>(bu + lane * 64 + stage_slot<4>(lane, 2 * c + k) * 16);
+            }
+            tmem_ld_wait();
+            const __nv_bfloat162 *hg = reinterpret_cast<const __nv_bfloat162 *>(rg), *hu = reinterpret_cast<const __nv_bfloat162 *>(ru);
+            __nv_bfloat162 *hdg = reinterpret_cast<__nv_bfloat162 *>(wdg), *hdu = reinterpret_cast<__nv_bfloat162 *>(wdu);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                float2 gg = __bfloat1622float2(hg[k]), uu = __bfloat1622float2(hu[k]);
+                float d0 = __uint_as_float(v[2 * k]), d1 = __uint_as_float(v[2 * k + 1]);
+                float s0 = sigmoid_f(gg.x), s1 = sigmoid_f(gg.y);
+                float dg0 = d0 * uu.x * (s0 + gg.x * s0 * (1.0f - s0)), dg1 = d1 * uu.y * (s1 + gg.y * s1 * (1.0f - s1));
+                float du0 = d0 * gg.x * s0, du1 = d1 * gg.y * s1;
+                hdg[k] = __floats2bfloat162_rn(dg0, dg1);
+                hdu[k] = __floats2bfloat162_rn(du0, du1);
+            }
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                *reinterpret_cast<uint4 *>(bg + lane * 64 + stage_slot<4>(lane, 2 * c + k) * 16) = wdg[k];
+                *reinterpret_cast<uint4 *>(bu + lane * 64 + stage_slot<4>(lane, 2 * c + k) * 16) = wdu[k];
+            }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(&p.o_map[0], smem_u32(bg), (int)(col0 + j * 32), (int)rbase);
+            tma_store_2d(&p.o_map[1], smem_u32(bu), (int)(col0 + j * 32), (int)rbase);
+            bulk_commit();
+        }
+    }
+    return true;
+}
+
 // Work an epilogue warp can do for its next tile before that tile's accumulator is complete.
 template <int EPI>
-__device__ __forceinline__ void epilogue_prefetch(const GemmParams &p, uint8_t *stage, int lane, long long rbase, long long col0, int valid)
+__device__ __forceinline__ void epilogue_prefetch(const GemmParams &p, uint8_t *stage, EpiCtx &ec, int lane, long long rbase, long long col0, int valid)
 {
-    if (EPI == EPI_SWIGLU_BWD) {
+    if (EPI == EPI_SWIGLU_BWD && p.o_tma) {
+        swiglu_bwd_issue(p, stage, ec.bar, lane, (int)col0, (int)rbase);
+    } else if (EPI == EPI_SWIGLU_BWD) {
         const long long o0 = rbase * p.ldo + col0;
         if (p.o_tma) blk_reuse(lane);
         blk_load(stage, lane, reinterpret_cast<const uint8_t *>(p.gp + o0), p.ldo * 2, valid);
@@ -531,6 +609,7 @@ k_gemm(const __grid_constant__ GemmParams p)
         for (int i = 0; i < NSC; i++) { mbar_init(smem_u32(&full_c[i]), 1); mbar_init(smem_u32(&empty_c[i]), DQ_WARPS); }
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&tmem_full[i]), 1); mbar_init(smem_u32(&tmem_empty[i]), EPI_WARPS); }
         mbar_init(smem_u32(spare), 1);
+        for (int i = 0; i < 2 * EPI_WARPS; i++) mbar_init(smem_u32(bars + 48 + i), 1);   // epilogue input rings
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -665,6 +744,7 @@ k_gemm(const __grid_constant__ GemmParams p)
         // every global store instruction writes whole row pieces.
         const int q = warp & 3, h = (warp - 2) >> 2;
         uint8_t *stage = sE + (warp - 2) * epi_stage_bytes(EPI);
+        EpiCtx ec = {bars + 48 + 2 * (warp - 2), 0u};
         bool ok = true;
         int it = 0;
         for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x, it++) {
@@ -675,14 +755,14 @@ k_gemm(const __grid_constant__ GemmParams p)
             if (SCHED != SCHED_ROWS) { long long left = (long long)p.M - row0; valid = left < 0 ? 0 : (left < 32 ? (int)left : 32); }
             const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
             const long long col0 = (long long)t.n_t * (EPI == EPI_SWIGLU ? BN / 2 : BN);
-            if (h < t.halves) epilogue_prefetch<EPI>(p, stage, lane, rbase, col0, valid);
+            if (h < t.halves) epilogue_prefetch<EPI>(p, stage, ec, lane, rbase, col0, valid);
             ok = mbar_wait(smem_u32(&tmem_full[acc]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 6);
             if (!ok) break;
             tc_fence_after();
             if (h < t.halves) {
                 const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * ACC_COLS + (uint32_t)h * BN;
                 const bool have_acc = (SCHED != SCHED_GROUPK) || t.ksteps > 0;
-                epilogue_rows<EPI>(p, stage, lane, tbase, rbase, col0, valid, have_acc, BN / 2);
+                epilogue_rows<EPI>(p, stage, ec, lane, tbase, rbase, col0, valid, have_acc, BN / 2);
             }
             tc_fence_before();
             __syncwarp();
@@ -938,9 +1018,16 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
         else if (g.epi == EPI_SWIGLU_BWD) { optr[0] = g.dgp; optr[1] = g.dup; no = 2; }
         bool can = no > 0 && (g.ldo % 8) == 0 && g.sched != SCHED_GROUPK && orows > 0;
         for (int i = 0; i < no && can; i++) can = optr[i] && (((uintptr_t)optr[i]) & 15) == 0;
+        const bool bwd = g.epi == EPI_SWIGLU_BWD;           // 32-column boxes, 64-byte swizzle
+        if (bwd) can = can && g.gp && g.up && ((((uintptr_t)g.gp) | ((uintptr_t)g.up)) & 15) == 0;
         for (int i = 0; i < no && can; i++) {
             rc = make_map(&p.o_map[i], optr[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (unsigned long long)g.ldo, orows,
-                          (unsigned long long)g.ldo * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+                          (unsigned long long)g.ldo * 2, bwd ? 32 : 64, 32, bwd ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc) return rc;
+        }
+        for (int i = 0; i < 2 && can && bwd; i++) {
+            rc = make_map(&p.i_map[i], i ? (const void *)g.up : (const void *)g.gp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                          (unsigned long long)g.ldo, orows, (unsigned long long)g.ldo * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
             if (rc) return rc;
         }
         p.o_tma = can ? 1 : 0;

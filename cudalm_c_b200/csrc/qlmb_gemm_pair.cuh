@@ -154,6 +154,7 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
         for (int i = 0; i < NSC; i++) { mbar_init(smem_u32(&full_c[i]), 1); mbar_init(smem_u32(&empty_c[i]), GW); }
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&tmem_full[i]), 1); mbar_init(smem_u32(&tmem_empty[i]), 2 * EPI_WARPS); }
         mbar_init(smem_u32(spare), 1);
+        for (int i = 0; i < 2 * EPI_WARPS; i++) mbar_init(smem_u32(bars + 48 + i), 1);   // epilogue input rings
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -273,6 +274,7 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
         // warp (q, h): q = TMEM lane quarter (= warp id mod 4), h = which 128 of the 256 columns
         const int q = warp & 3, h = (warp - 2) >> 2;
         uint8_t *stage = sE + (warp - 2) * epi_stage_bytes(EPI);
+        EpiCtx ec = {bars + 48 + 2 * (warp - 2), 0u};
         bool ok = true;
         int it = 0;
         for (int tile = pair; ok && tile < total; tile += npairs, it++) {
@@ -284,7 +286,7 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
             else { long long left = (long long)p.M - row0; valid = left < 0 ? 0 : (left < 32 ? (int)left : 32); }
             const long long rbase = (SCHED == SCHED_GROUPK) ? ((long long)t.e * p.M + row0) : row0;
             const long long col0 = (EPI == EPI_SWIGLU) ? (long long)t.n_t * 128 + h * 64 : (long long)t.n_t * P_BN + h * 128;
-            if (valid > 0) epilogue_prefetch<EPI>(p, stage, lane, rbase, col0, valid);
+            if (valid > 0) epilogue_prefetch<EPI>(p, stage, ec, lane, rbase, col0, valid);
             ok = mbar_wait_idle(smem_u32(&tmem_full[acc]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 19);
             if (!ok) break;
             tc_fence_after();
@@ -292,9 +294,9 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                 const bool have_acc = (SCHED != SCHED_GROUPK) || t.ksteps > 0;
                 const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * P_BN;
                 if (EPI == EPI_SWIGLU)
-                    epilogue_rows<EPI>(p, stage, lane, tbase + (uint32_t)h * 64, rbase, col0, valid, have_acc, 128);
+                    epilogue_rows<EPI>(p, stage, ec, lane, tbase + (uint32_t)h * 64, rbase, col0, valid, have_acc, 128);
                 else
-                    epilogue_rows<EPI>(p, stage, lane, tbase + (uint32_t)h * 128, rbase, col0, valid, have_acc, 0);
+                    epilogue_rows<EPI>(p, stage, ec, lane, tbase + (uint32_t)h * 128, rbase, col0, valid, have_acc, 0);
             }
             tc_fence_before();
             __syncwarp();
