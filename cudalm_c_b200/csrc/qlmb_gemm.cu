@@ -922,7 +922,7 @@ template <int BMODE, int EPI, int SCHED, int DQG>
 static int launch_pair_g(const GemmParams &p, long long total, cudaStream_t st)
 {
     constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
-    constexpr size_t smem = 1024 + (size_t)(DEQ ? (EPI == EPI_SWIGLU_BWD ? 4 : 5) : 6) * (P_A_STAGE + P_B_STAGE) + (DEQ ? 8 * P_C_STAGE : 0) + EPI_WARPS * epi_stage_bytes(EPI) + 512;
+    constexpr size_t smem = 1024 + (size_t)(DEQ ? (EPI == EPI_SWIGLU_BWD ? 4 : 5) : 6) * (P_A_STAGE + P_B_STAGE) + (DEQ ? P_NSC * P_C_STAGE + P_S_RING : 0) + EPI_WARPS * epi_stage_bytes(EPI) + 512;
     // persistent kernel: every cluster must be resident at once, so the grid is the number of
     // clusters the device can hold at the same time (asked once per kernel instance)
     static int max_clusters = 0;

@@ -26,6 +26,9 @@ constexpr int P_BN = 256;                 // accumulator columns of the pair til
 constexpr int P_A_STAGE = BM * BK * 2;    // per CTA: 128 rows
 constexpr int P_B_STAGE = 128 * BK * 2;   // per CTA: 128 columns of B
 constexpr int P_C_STAGE = 128 * BK / 2;   // per CTA: codes of those columns
+constexpr int P_S_STAGE = 128 * 4;        // per CTA: the stage's group scales (up to 128 floats)
+constexpr int P_S_RING = 4096;            // the scale slots together, padded so that what follows stays 1 KiB aligned
+constexpr int P_NSC = 7;                  // depth of the code / scale ring
 
 __device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ void cluster_sync()
@@ -69,6 +72,17 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
 {
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+}
+// 4-byte asynchronous copy global -> shared, and an mbarrier arrival that fires when all
+// earlier asynchronous copies of the calling thread have landed (the barrier's expected count
+// must include one such arrival per calling thread)
+__device__ __forceinline__ void cp_async4(void *dst, const void *src)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar)
+{
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols)
 { asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory"); }
@@ -126,8 +140,11 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
 {
     constexpr bool DEQ = (BMODE == B_DEQ_MN || BMODE == B_DEQ_K);
     constexpr bool DUAL = (EPI == EPI_SWIGLU);           // CTA 0 expands W1 (gate), CTA 1 expands W3 (up)
-    constexpr int NS = DEQ ? (EPI == EPI_SWIGLU_BWD ? 4 : 5) : 6, NSC = 8;
+    constexpr int NS = DEQ ? (EPI == EPI_SWIGLU_BWD ? 4 : 5) : 6, NSC = P_NSC;
     constexpr int GW = DQ_WARPS / DQG;                   // dequant warps per stage group
+    // group scales: codes [K][N] need 64 new scales per stage, fetched by the producer warp into the
+    // stage's slot; codes [N][K] reuse a row's scale for two stages, each lane keeps its own in registers
+    constexpr bool S_SMEM = (BMODE == B_DEQ_MN);
     constexpr uint32_t IDESC = make_idesc(256, P_BN, BMODE == AB_TMA_MN ? 1 : 0, (BMODE == B_DEQ_MN || BMODE == AB_TMA_MN) ? 1 : 0);
     constexpr uint32_t TMEM_COLS = 2 * P_BN;
     constexpr uint32_t TX_BYTES = 2u * (P_A_STAGE + (DEQ ? 0 : P_B_STAGE));   // both CTAs' loads of a stage
@@ -137,7 +154,10 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
     uint8_t *sA = smem;
     uint8_t *sB = sA + NS * P_A_STAGE;
     uint8_t *sC = sB + NS * P_B_STAGE;
-    uint8_t *sE = sC + (DEQ ? NSC * P_C_STAGE : 0);
+    float *sS = reinterpret_cast<float *>(sC + (DEQ ? NSC * P_C_STAGE : 0));      // [NSC][128] group scales
+    uint8_t *sE = sC + (DEQ ? NSC * P_C_STAGE + P_S_RING : 0);
+    static_assert((P_C_STAGE % 1024) == 0 && (P_S_RING % 1024) == 0 && P_NSC * P_S_STAGE <= P_S_RING,
+                  "the epilogue staging blocks are bulk-tensor boxes with a 128-byte swizzle: 1 KiB alignment");
     uint64_t *bars = reinterpret_cast<uint64_t *>(sE + EPI_WARPS * epi_stage_bytes(EPI));
     uint64_t *full = bars, *empty = full + NS;
     uint64_t *full_c = empty + NS, *empty_c = full_c + NSC;
@@ -151,7 +171,7 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; i++) { mbar_init(smem_u32(&full[i]), 1 + (DEQ ? 2 * GW : 0)); mbar_init(smem_u32(&empty[i]), 1); }
-        for (int i = 0; i < NSC; i++) { mbar_init(smem_u32(&full_c[i]), 1); mbar_init(smem_u32(&empty_c[i]), GW); }
+        for (int i = 0; i < NSC; i++) { mbar_init(smem_u32(&full_c[i]), S_SMEM ? 33 : 1); mbar_init(smem_u32(&empty_c[i]), GW); }
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&tmem_full[i]), 1); mbar_init(smem_u32(&tmem_empty[i]), 2 * EPI_WARPS); }
         mbar_init(smem_u32(spare), 1);
         for (int i = 0; i < 2 * EPI_WARPS; i++) mbar_init(smem_u32(bars + 48 + i), 1);   // epilogue input rings
@@ -176,6 +196,10 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
         // =============================== TMA producer (both CTAs) ===============================
         Ring rs = {0, 0}, rc = {0, 0};
         bool ok = true;
+        // group scales of a stage (codes [K][N]): every lane copies its rows' scales into the stage's slot with
+        // 4-byte asynchronous copies and lets full_c[s] count their completion, so full_c[s]
+        // completes when the code bytes (expect_tx arrival of lane 0) and all 32 lanes' scales landed
+        const int gpr = p.w_cols / 128;
         for (int tile = pair; ok && tile < total; tile += npairs) {
             TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
             for (int seg = 0; ok && seg < p.nseg; seg++) {
@@ -214,6 +238,14 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                             } else {
                                 tma_load_2d(dstC, &p.w_map[seg], bar, ks * (BK / 2), t.e * p.w_rows + t.n_t * P_BN + my_n);
                             }
+                        }
+                        if (S_SMEM) {
+                            const float *sp = DUAL ? p.scales[rank] : p.scales[seg];
+                            float *sdst = sS + rc.idx * 128;
+                            const size_t b0 = (size_t)(t.e * p.w_rows + ks * BK) * gpr + (DUAL ? t.n_t * 128 : t.n_t * P_BN + my_n) / 128;
+#pragma unroll
+                            for (int i = 0; i < 2; i++) cp_async4(sdst + lane + 32 * i, sp + b0 + (size_t)(lane + 32 * i) * gpr);
+                            cp_async_arrive(smem_u32(&full_c[rc.idx]));
                         }
                         __syncwarp();
                         rc.next(NSC);
@@ -327,33 +359,28 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
             else dst0[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c0 ^ (r & 7)) << 4));
         }
         constexpr uint32_t DST_STEP = (uint32_t)(PER * ROWS_I / 8) * 1024u;      // bytes per PER words
-        const int gpr = p.w_cols / 128;
         Ring rc = {0, 0}, rb = {0, 0};
         bool ok = true;
         const uint32_t full0 = map_to_cta(smem_u32(&full[0]), 0);    // the leader's stage barriers
+        const int gpr = p.w_cols / 128;
         int kc = 0;                                                  // running stage index of this CTA
         for (int tile = pair; ok && tile < total; tile += npairs) {
             TileInfo t = decode_pair_tile<SCHED>(p, tile, ntr);
             for (int seg = 0; ok && seg < p.nseg; seg++) {
-                const float *sp = DUAL ? p.scales[rank] : p.scales[seg];
-                // scale of word i at stage ks: sp[sb + r(i)*gpr + ks*sstep] (MN) / sp[sb + r(i)*gpr + ks*64/128] (K)
-                int sb;
-                if (BMODE == B_DEQ_MN) sb = (t.e * p.w_rows + r0) * gpr + (DUAL ? t.n_t * 128 : t.n_t * P_BN + my_n) / 128;
-                else sb = (t.e * p.w_rows + t.n_t * P_BN + my_n + r0) * gpr;
-                const int rstep = ROWS_I * gpr;
                 int ks = (g - kc % DQG + DQG) % DQG;                 // first stage of this group in the tile
                 for (int i = 0; i < ks && i < t.ksteps; i++) { rc.next(NSC); rb.next(NS); }
+                // codes [N][K]: scale of word i at stage ks is sp[sb + i * rstep + ks * 64 / 128]
+                const float *sp = p.scales[seg];
+                const int sb = (t.e * p.w_rows + t.n_t * P_BN + my_n + r0) * gpr, rstep = ROWS_I * gpr;
                 float cur[ITERS], nxt[ITERS];
-                if (ks < t.ksteps) {
-                    const int so = (BMODE == B_DEQ_MN) ? ks * BK * gpr : (ks * BK) / 128;
+                if (!S_SMEM && ks < t.ksteps) {
 #pragma unroll
-                    for (int i = 0; i < ITERS; i++) cur[i] = __ldg(sp + sb + i * rstep + so);
+                    for (int i = 0; i < ITERS; i++) cur[i] = __ldg(sp + sb + i * rstep + (ks * BK) / 128);
                 }
                 for (; ks < t.ksteps; ks += DQG) {
-                    if (ks + DQG < t.ksteps) {
-                        const int so = (BMODE == B_DEQ_MN) ? (ks + DQG) * BK * gpr : ((ks + DQG) * BK) / 128;
+                    if (!S_SMEM && ks + DQG < t.ksteps) {
 #pragma unroll
-                        for (int i = 0; i < ITERS; i++) nxt[i] = __ldg(sp + sb + i * rstep + so);
+                        for (int i = 0; i < ITERS; i++) nxt[i] = __ldg(sp + sb + i * rstep + ((ks + DQG) * BK) / 128);
                     }
                     ok = mbar_wait_idle(smem_u32(&full_c[rc.idx]), rc.phase, abort_flag, p.errword, 20);
                     if (!ok) break;
@@ -361,6 +388,11 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                     uint32_t w[ITERS];
 #pragma unroll
                     for (int i = 0; i < ITERS; i++) w[i] = cw[(i * GW + gw) * 32 + lane];
+                    if (S_SMEM) {
+                        const float *sc = sS + rc.idx * 128 + r0;    // scale of word i: sc[i * ROWS_I]
+#pragma unroll
+                        for (int i = 0; i < ITERS; i++) cur[i] = sc[i * ROWS_I];
+                    }
                     ok = mbar_wait_idle(smem_u32(&empty[rb.idx]), rb.phase ^ 1u, abort_flag, p.errword, 21);
                     if (!ok) break;
                     uint8_t *bdst = sB + rb.idx * P_B_STAGE;
@@ -372,8 +404,10 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                     if (lane == 0) { mbar_arrive_remote(full0 + (uint32_t)rb.idx * 8u); mbar_arrive(smem_u32(&empty_c[rc.idx])); }
                     const int adv = ks + DQG <= t.ksteps ? DQG : t.ksteps - ks;
                     for (int i = 0; i < adv; i++) { rc.next(NSC); rb.next(NS); }
+                    if (!S_SMEM) {
 #pragma unroll
-                    for (int i = 0; i < ITERS; i++) cur[i] = nxt[i];
+                        for (int i = 0; i < ITERS; i++) cur[i] = nxt[i];
+                    }
                 }
                 kc += t.ksteps;
             }
