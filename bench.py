@@ -412,6 +412,126 @@ def run_adamw(args):
                           clocks=sampler.summary())))
 
 
+def _time(fn, steps, warmup):
+    import torch
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record(); torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_linear(args):
+    """Secondary lines (BASELINE config 1): one dequant-fused linear, forward + input gradient +
+    weight gradient, X[8192,512], W[2048,512] stored [out,in] with groups along the input axis,
+    once with fp32 and once with bf16 activations.  51.54 GFLOP per step."""
+    import torch
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import linear, qlm
+    from cudalm_c_b200._lib import NK
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    M, K, N = 8192, 512, 2048
+    gen = torch.Generator(device=dev); gen.manual_seed(1)
+    W = torch.randn(N * K, device=dev, generator=gen) * 0.02
+    Q = qlm.Qlm([(0, N * K)], N * K, dev); Q.init_from(W, render=False)
+    flops = 3 * 2.0 * M * K * N
+    for dt, name, io_bytes in ((torch.float32, "f32", 4), (torch.bfloat16, "bf16", 2)):
+        X = torch.randn(M, K, device=dev, generator=gen).to(dt); dY = torch.randn(M, N, device=dev, generator=gen).to(dt)
+        Y = torch.empty(M, N, device=dev, dtype=dt); dX = torch.empty(M, K, device=dev, dtype=dt)
+        dW = torch.zeros(N, K, device=dev)
+
+        def step():
+            linear.linear_fwd(X, Q.d, Q.s, NK, N, out=Y)
+            linear.linear_dgrad(dY, Q.d, Q.s, NK, K, out=dX)
+            linear.linear_wgrad(dW, dY, X, NK, beta=0.0)
+        ms = _time(step, args.steps, args.warmup)
+        q.check(q.lib().qlmb_check_device(None))
+        tf = flops / (ms * 1e-3) / 1e12
+        # bytes per step: fwd X + Y + codes, dgrad dY + dX + codes, wgrad dY + X + dW(fp32)
+        byts = (M * K + M * N) * io_bytes * 3 + 2 * N * K * 0.53125 + N * K * 4
+        print(json.dumps(dict(metric="dequant_linear_tflops", value=round(tf, 1), unit="TFLOP/s", n_gpus=1, steps=args.steps,
+                              warmup=max(args.warmup, 3), ms_per_step=round(ms, 4), higher_is_better=True, scaling="weak",
+                              vs_baseline=None, dtype=name, data="synthetic",
+                              config=dict(workload="dequant-fused linear fwd+dgrad+wgrad (BASELINE config 1)", M=M, K=K, N=N,
+                                          io=name, l2="working set %.0f MB, re-read every step (fits the 126 MB L2 only with bf16 I/O)" % (byts / 1e6)),
+                              roofline=dict(bound="tensor", kernel="k_gemm_pair", achieved=round(tf, 1), peak=pk["tf_burst"], unit="TFLOP/s",
+                                            frac=round(tf / pk["tf_burst"], 4), traffic=None, peak_kind="burst bf16, of " + pk["src"],
+                                            byte_bound_ms=round(byts / (pk["hbm"] * 1e9) * 1e3, 4),
+                                            flop_bound_ms=round(flops / (pk["tf_burst"] * 1e12) * 1e3, 4)),
+                              cpu_baseline=None, gpu_launches=3 * args.steps)))
+
+
+def run_gemv(args):
+    """Secondary lines (decode path, BASELINE config 5's building block): Y[B,N] = X[B,K] deq(W) for
+    B live slots; metric = weight bytes streamed (0.53125 B per weight) / time."""
+    import torch
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import linear, qlm
+    from cudalm_c_b200._lib import KN, NK
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    gen = torch.Generator(device=dev); gen.manual_seed(5)
+    for K, N, lay, tag in ((768, 1536, KN, "KN 768x1536 (expert up-projection)"), (4096, 16384, KN, "KN 4096x16384"),
+                           (4096, 16384, NK, "NK 16384x4096")):
+        W = torch.randn(K * N, device=dev, generator=gen) * 0.02
+        Q = qlm.Qlm([(0, K * N)], K * N, dev); Q.init_from(W, render=False)
+        for B in (1, 8, 64):
+            X = torch.randn(B, K, device=dev, generator=gen).bfloat16()
+            Y = torch.empty(B, N, device=dev, dtype=torch.bfloat16)
+            ms = _time(lambda: linear.gemv_decode(X, Q.d, Q.s, lay, N, out=Y), args.steps, args.warmup)
+            gbs = K * N * 0.53125 / (ms * 1e-3) / 1e9
+            print(json.dumps(dict(metric="decode_gemv_weight_gbs", value=round(gbs, 1), unit="GB/s", n_gpus=1, steps=args.steps,
+                                  warmup=max(args.warmup, 3), ms_per_step=round(ms, 5), higher_is_better=True, scaling="weak",
+                                  vs_baseline=None, dtype="bf16", data="synthetic",
+                                  config=dict(workload="decode GEMV, 4-bit weights " + tag, slots=B,
+                                              l2="weights %.1f MB per call (the small matrix stays in L2)" % (K * N * 0.53125 / 1e6)),
+                                  roofline=dict(bound="hbm", kernel="k_gemv", achieved=round(gbs, 1), peak=pk["hbm"], unit="GB/s",
+                                                frac=round(gbs / pk["hbm"], 4), traffic=None, peak_kind="copy bandwidth, of " + pk["src"]),
+                                  cpu_baseline=None, gpu_launches=2 * args.steps)))
+        del Q, W
+    q.check(q.lib().qlmb_check_device(None))
+
+
+def run_state(args):
+    """Secondary lines: the other passes over the optimizer state at config 3's size --
+    encode (4 B read + 1.53 B written per parameter), render (0.53 read + 4 written) and the
+    global-norm reduction (4 B read)."""
+    import torch
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import qlm
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    n = args.params
+    Q = qlm.Qlm([(0, n)], n, dev)
+    gen = torch.Generator(device=dev); gen.manual_seed(3)
+    P = torch.randn(n, device=dev, generator=gen) * 0.02
+    G = torch.randn(n, device=dev, generator=gen) * 1e-3
+    out = torch.zeros(2, device=dev)
+    Q.init_from(P, render=False)
+    for name, fn, bpp in (("encode", lambda: qlm.qlm_encode(P, Q.d, Q.r, Q.s, Q.spanD, Q.nspan, Q.group, Q.dmax, Q.packed), 4 + 1.53125),
+                          ("render", lambda: Q.render(P), 0.53125 + 4),
+                          ("gnorm", lambda: qlm.gnorm(G, out=out), 4.0)):
+        ms = _time(fn, args.steps, args.warmup)
+        gbs = n * bpp / (ms * 1e-3) / 1e9
+        print(json.dumps(dict(metric="qlm_%s_gbs" % name, value=round(gbs, 1), unit="GB/s", n_gpus=1, steps=args.steps,
+                              warmup=max(args.warmup, 3), ms_per_step=round(ms, 4), higher_is_better=True, scaling="weak",
+                              vs_baseline=None, dtype="f32/int8", data="synthetic",
+                              config=dict(workload="QLM %s pass over a flat span (BASELINE config 3 size)" % name, params=n,
+                                          bytes_per_param=bpp, l2="inputs exceed the 126 MB L2"),
+                              roofline=dict(bound="hbm", kernel="k_" + name, achieved=round(gbs, 1), peak=pk["hbm"], unit="GB/s",
+                                            frac=round(gbs / pk["hbm"], 4), traffic=None, peak_kind="copy bandwidth, of " + pk["src"]),
+                              cpu_baseline=None, gpu_launches=args.steps)))
+    q.check(q.lib().qlmb_check_device(None))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -419,7 +539,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="moe", choices=["moe", "adamw"], help="moe = the headline line; adamw = secondary line for config 3")
+    ap.add_argument("--workload", default="moe", choices=["moe", "adamw", "linear", "gemv", "state"],
+                    help="moe = the headline line; the others print secondary lines: adamw (config 3), linear (config 1), "
+                         "gemv (decode building block), state (encode / render / gnorm passes)")
     ap.add_argument("--params", type=int, default=125829120, help="span size of --workload adamw")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="N>1: peer = foreign rows read by peer loads inside the row kernels; nccl = all-to-all exchanges")
@@ -429,6 +551,12 @@ def main():
         CFG["N"] = args.tokens
     if args.workload == "adamw":
         run_adamw(args)
+    elif args.workload == "linear":
+        run_linear(args)
+    elif args.workload == "gemv":
+        run_gemv(args)
+    elif args.workload == "state":
+        run_state(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

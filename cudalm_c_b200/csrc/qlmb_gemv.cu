@@ -10,7 +10,6 @@ namespace qlmb {
 
 int workspace(size_t bytes, void **out);       // qlmb_linear.cu
 
-#define GV_BT 8                                 // activation rows processed per pass
 
 __device__ __forceinline__ float ld_x(const void *X, int dtype, size_t i)
 {
@@ -30,104 +29,158 @@ __device__ __forceinline__ void unpack8(uint32_t w, float d[8])
     }
 }
 
-// ---- codes W[K][N] (groups along N).  Block: 256 output columns x a K slice; warp w takes
-// rows k0+w, k0+w+8, ...; lane = 8 consecutive columns.  part[ks][b][n] receives the slice sums.
-__global__ void __launch_bounds__(256) k_gemv_kn(float *part, const void *X, int dtype, const uint8_t *codes,
+// ---- codes W[K][N] (groups along N).  Block: 256 output columns x a K slice; warp w takes rows
+// k0+w, k0+w+8, ..., eight of them in flight per step; lane = 8 consecutive columns (one code word).
+// BT activation rows are multiplied per pass (BT = 1, 2, 4 or 8: no arithmetic on absent rows);
+// part[ks][b][n] receives the slice sums.
+template <int BT>
+__global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, const void *X, int dtype, const uint8_t *codes,
                                                  const float *scales, int B, int K, int N, int kslice)
 {
-    extern __shared__ float xs[];               // [GV_BT][kslice]
-    __shared__ float red[GV_BT][256];
+    extern __shared__ float xs[];               // [BT][kslice]
+    constexpr bool PAR = BT <= 2;               // every warp parks its sums, one pass adds them in warp order
+    __shared__ float red[PAR ? 8 * BT : BT][256];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * 256 + lane * 8;
     const int k0 = blockIdx.y * kslice, k1 = k0 + kslice < K ? k0 + kslice : K;
     const int gpr = N / 128;
     const bool live = n0 < N;
-    for (int b0 = 0; b0 < B; b0 += GV_BT) {
+    const uint8_t *cp = codes + (size_t)n0 / 2;
+    const float *sp = scales + n0 / 128;
+    for (int b0 = 0; b0 < B; b0 += BT) {
         __syncthreads();
-        for (int i = threadIdx.x; i < GV_BT * kslice; i += 256) {
-            int b = b0 + i / kslice, k = k0 + i % kslice;
+        for (int i = threadIdx.x; i < BT * kslice; i += 256) {
+            const int b = b0 + i / kslice, k = k0 + i % kslice;
             xs[i] = (b < B && k < k1) ? ld_x(X, dtype, (size_t)b * K + k) : 0.0f;
         }
-        for (int i = threadIdx.x; i < GV_BT * 256; i += 256) red[i / 256][i % 256] = 0.0f;
+        if (!PAR) for (int i = threadIdx.x; i < BT * 256; i += 256) red[i / 256][i % 256] = 0.0f;
         __syncthreads();
-        float acc[GV_BT][8];
+        float acc[BT][8];
 #pragma unroll
-        for (int b = 0; b < GV_BT; b++)
+        for (int b = 0; b < BT; b++)
 #pragma unroll
             for (int j = 0; j < 8; j++) acc[b][j] = 0.0f;
         if (live) {
-#pragma unroll 4
-            for (int k = k0 + warp; k < k1; k += 8) {
-                uint32_t w = __ldcs(reinterpret_cast<const uint32_t *>(codes + ((size_t)k * N + n0) / 2));
-                float s = __ldg(scales + (size_t)k * gpr + n0 / 128);
-                float d[8];
-                unpack8(w, d);
+            for (int k = k0 + warp; k < k1; k += 64) {
+                uint32_t w[8];
+                float sc[8];
 #pragma unroll
-                for (int b = 0; b < GV_BT; b++) {
-                    float xv = xs[b * kslice + (k - k0)] * s;
+                for (int u = 0; u < 8; u++) {
+                    const int kk = k + 8 * u;
+                    w[u] = 0u; sc[u] = 0.0f;
+                    if (kk < k1) {
+                        w[u] = __ldcs(reinterpret_cast<const uint32_t *>(cp + (size_t)kk * N / 2));
+                        sc[u] = __ldg(sp + (size_t)kk * gpr);
+                    }
+                }
 #pragma unroll
-                    for (int j = 0; j < 8; j++) acc[b][j] += xv * d[j];
+                for (int u = 0; u < 8; u++) {
+                    const int kk = k + 8 * u;
+                    if (kk >= k1) break;
+                    float d[8];
+                    unpack8(w[u], d);
+#pragma unroll
+                    for (int b = 0; b < BT; b++) {
+                        const float xv = xs[b * kslice + (kk - k0)] * sc[u];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) acc[b][j] += xv * d[j];
+                    }
                 }
             }
         }
         // fixed-order combination of the 8 warps
-        for (int w8 = 0; w8 < 8; w8++) {
-            if (warp == w8 && live) {
+        if (PAR) {
 #pragma unroll
-                for (int b = 0; b < GV_BT; b++)
+            for (int b = 0; b < BT; b++)
 #pragma unroll
-                    for (int j = 0; j < 8; j++) red[b][lane * 8 + j] += acc[b][j];
-            }
+                for (int j = 0; j < 8; j++) red[warp * BT + b][lane * 8 + j] = acc[b][j];
             __syncthreads();
-        }
-        for (int i = threadIdx.x; i < GV_BT * 256; i += 256) {
-            int b = b0 + i / 256, n = blockIdx.x * 256 + i % 256;
-            if (b < B && n < N) part[((size_t)blockIdx.y * B + b) * N + n] = red[i / 256][i % 256];
+            for (int i = threadIdx.x; i < BT * 256; i += 256) {
+                const int bb = i / 256, c = i % 256, b = b0 + bb, n = blockIdx.x * 256 + c;
+                float v = 0.0f;
+#pragma unroll
+                for (int w8 = 0; w8 < 8; w8++) v += red[w8 * BT + bb][c];
+                if (b < B && n < N) part[((size_t)blockIdx.y * B + b) * N + n] = v;
+            }
+        } else {
+            for (int w8 = 0; w8 < 8; w8++) {
+                if (warp == w8 && live) {
+#pragma unroll
+                    for (int b = 0; b < BT; b++)
+#pragma unroll
+                        for (int j = 0; j < 8; j++) red[b][lane * 8 + j] += acc[b][j];
+                }
+                __syncthreads();
+            }
+            for (int i = threadIdx.x; i < BT * 256; i += 256) {
+                const int b = b0 + i / 256, n = blockIdx.x * 256 + i % 256;
+                if (b < B && n < N) part[((size_t)blockIdx.y * B + b) * N + n] = red[i / 256][i % 256];
+            }
         }
     }
 }
 
-// ---- codes W[N][K] (groups along K).  One warp per output column n; lanes stride over the
-// row's code words; the scale multiplies the 8-element partial dot product of each word.
-__global__ void __launch_bounds__(256) k_gemv_nk(float *part, const void *X, int dtype, const uint8_t *codes,
-                                                 const float *scales, int B, int K, int N)
+// ---- codes W[N][K] (groups along K).  A warp owns 4 consecutive output columns (rows of W) and a
+// K slice; lanes stride over the code words of the slice, 4 words (one per column) per step share the
+// activation values; the scale multiplies the 8-element partial dot product of each word.
+template <int BT>
+__global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_nk(float *part, const void *X, int dtype, const uint8_t *codes,
+                                                 const float *scales, int B, int K, int N, int kslice)
 {
-    extern __shared__ float xs[];               // [GV_BT][K]
+    extern __shared__ float xs[];               // [BT][kslice]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * 8 + warp;
-    const int gpr = K / 128;
-    for (int b0 = 0; b0 < B; b0 += GV_BT) {
+    const int n0 = (blockIdx.x * 8 + warp) * 4;
+    const int k0 = blockIdx.y * kslice, k1 = k0 + kslice < K ? k0 + kslice : K;
+    const int gpr = K / 128, nw = (k1 - k0) / 8;             // code words of the slice
+    for (int b0 = 0; b0 < B; b0 += BT) {
         __syncthreads();
-        for (int i = threadIdx.x; i < GV_BT * K; i += 256) {
-            int b = b0 + i / K;
-            xs[i] = b < B ? ld_x(X, dtype, (size_t)b * K + i % K) : 0.0f;
+        for (int i = threadIdx.x; i < BT * kslice; i += 256) {
+            const int b = b0 + i / kslice, k = k0 + i % kslice;
+            xs[i] = (b < B && k < k1) ? ld_x(X, dtype, (size_t)b * K + k) : 0.0f;
         }
         __syncthreads();
-        if (n >= N) continue;
-        float acc[GV_BT];
+        if (n0 >= N) continue;
+        float acc[4][BT];
 #pragma unroll
-        for (int b = 0; b < GV_BT; b++) acc[b] = 0.0f;
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+            for (int b = 0; b < BT; b++) acc[c][b] = 0.0f;
 #pragma unroll 2
-        for (int k = lane * 8; k < K; k += 256) {
-            uint32_t w = __ldcs(reinterpret_cast<const uint32_t *>(codes + ((size_t)n * K + k) / 2));
-            float s = __ldg(scales + (size_t)n * gpr + k / 128);
-            float d[8];
-            unpack8(w, d);
+        for (int kw = lane; kw < nw; kw += 32) {
+            uint32_t w[4];
+            float sc[4];
 #pragma unroll
-            for (int b = 0; b < GV_BT; b++) {
-                const float4 x0 = *reinterpret_cast<const float4 *>(&xs[b * K + k]);
-                const float4 x1 = *reinterpret_cast<const float4 *>(&xs[b * K + k + 4]);
-                float t = x0.x * d[0] + x0.y * d[1] + x0.z * d[2] + x0.w * d[3] + x1.x * d[4] + x1.y * d[5] + x1.z * d[6] + x1.w * d[7];
-                acc[b] += s * t;
+            for (int c = 0; c < 4; c++) {
+                w[c] = 0u; sc[c] = 0.0f;
+                if (n0 + c < N) {
+                    w[c] = __ldcs(reinterpret_cast<const uint32_t *>(codes + ((size_t)(n0 + c) * K + k0) / 2) + kw);
+                    sc[c] = __ldg(scales + (size_t)(n0 + c) * gpr + (k0 + kw * 8) / 128);
+                }
+            }
+            float d[4][8];
+#pragma unroll
+            for (int c = 0; c < 4; c++) unpack8(w[c], d[c]);
+#pragma unroll
+            for (int b = 0; b < BT; b++) {
+                const float4 x0 = *reinterpret_cast<const float4 *>(&xs[b * kslice + kw * 8]);
+                const float4 x1 = *reinterpret_cast<const float4 *>(&xs[b * kslice + kw * 8 + 4]);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const float t = x0.x * d[c][0] + x0.y * d[c][1] + x0.z * d[c][2] + x0.w * d[c][3] +
+                                    x1.x * d[c][4] + x1.y * d[c][5] + x1.z * d[c][6] + x1.w * d[c][7];
+                    acc[c][b] += sc[c] * t;
+                }
             }
         }
 #pragma unroll
-        for (int b = 0; b < GV_BT; b++) {
-            float v = acc[b];
+        for (int c = 0; c < 4; c++)
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && b0 + b < B) part[(size_t)(b0 + b) * N + n] = v;
-        }
+            for (int b = 0; b < BT; b++) {
+                float v = acc[c][b];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && b0 + b < B && n0 + c < N) part[((size_t)blockIdx.y * B + b0 + b) * N + n0 + c] = v;
+            }
     }
 }
 
@@ -159,34 +212,36 @@ extern "C" int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, con
     if (B == 0) return QLMB_OK;
     QLMB_REQUIRE(Y && X && codes && scales, "qlmb_gemv_decode: NULL argument");
     cudaStream_t st = as_stream(stream);
-    int nslice = 1, kslice = K;
-    if (layout == QLMB_KN) {
-        // enough K slices to give every SM a few blocks, at least 64 rows each
-        int nchunks = (N + 255) / 256;
-        int want = (4 * sm_count() + nchunks - 1) / nchunks;
-        nslice = want < 1 ? 1 : want;
-        if (nslice > K / 64) nslice = K / 64;
-        if (nslice < 1) nslice = 1;
-        kslice = ((K + nslice - 1) / nslice + 7) / 8 * 8;
-        nslice = (K + kslice - 1) / kslice;
-    }
+    // more than 4 live slots with bf16 activations: the tensor-core engine streams the weights
+    // faster than fp32 FMAs can consume them (fp32 activations keep the exact fp32 path)
+    if (B > 4 && dtype == QLMB_BF16 && (K % 64) == 0)
+        return qlmb_linear_fwd(Y, X, codes, scales, layout, B, K, N, nullptr, dtype, stream);
+    const int bt = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
+    // K slices: enough blocks to fill the device several times over, at least 64 rows each,
+    // a multiple of 8 rows, and small enough for the activation tile in shared memory
+    const int nblk = layout == QLMB_KN ? (N + 255) / 256 : (N + 31) / 32;
+    int nslice = (6 * sm_count() + nblk - 1) / nblk;
+    if (nslice > K / 64) nslice = K / 64;
+    if (nslice < 1) nslice = 1;
+    int kslice = ((K + nslice - 1) / nslice + 127) / 128 * 128;
+    while ((size_t)bt * kslice * sizeof(float) > 32 * 1024) kslice = (kslice / 2 + 127) / 128 * 128;
+    nslice = (K + kslice - 1) / kslice;
     void *ws = nullptr;
     int rc = workspace((size_t)nslice * B * N * sizeof(float), &ws);
     if (rc) return rc;
     float *part = (float *)ws;
-    if (layout == QLMB_KN) {
-        size_t smem = (size_t)GV_BT * kslice * sizeof(float);
-        QLMB_REQUIRE(smem <= 40 * 1024, "qlmb_gemv_decode: K slice of %d rows does not fit shared memory", kslice);
-        k_gemv_kn<<<dim3((N + 255) / 256, nslice), 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice);
-    } else {
-        size_t smem = (size_t)GV_BT * K * sizeof(float);
-        static bool cfg = false;
-        if (smem > 48 * 1024) {
-            QLMB_REQUIRE(smem <= 200 * 1024, "qlmb_gemv_decode: K=%d too large for the shared-memory activation tile", K);
-            if (!cfg) { QLMB_CUDA(cudaFuncSetAttribute(k_gemv_nk, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); cfg = true; }
-        }
-        k_gemv_nk<<<(N + 7) / 8, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N);
-    }
+    const size_t smem = (size_t)bt * kslice * sizeof(float);
+    const dim3 grid(nblk, nslice);
+#define GV_LAUNCH(KERN) \
+    do { \
+        if (bt == 1) KERN<1><<<grid, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice); \
+        else if (bt == 2) KERN<2><<<grid, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice); \
+        else if (bt == 4) KERN<4><<<grid, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice); \
+        else KERN<8><<<grid, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice); \
+    } while (0)
+    if (layout == QLMB_KN) GV_LAUNCH(k_gemv_kn);
+    else GV_LAUNCH(k_gemv_nk);
+#undef GV_LAUNCH
     k_gemv_finish<<<(unsigned)(((size_t)B * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)B * N);
     QLMB_LAUNCH_CHECK("qlmb_gemv_decode");
     return QLMB_OK;
