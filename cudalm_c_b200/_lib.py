@@ -29,6 +29,14 @@ class MoeLayer(C.Structure):
 vp, ci, cf, u64, sz = C.c_void_p, C.c_int, C.c_float, C.c_uint64, C.c_size_t
 
 # name -> (restype, argtypes); the symbol test walks this table against the header
+class StateFile(C.Structure):
+    _fields_ = [("dmax", C.c_int), ("group", C.c_int), ("adam", C.c_int), ("nspan", C.c_int), ("packed", C.c_int),
+                ("iter", C.c_int), ("nq", C.c_ulonglong), ("ngrp", C.c_ulonglong), ("nfloat", C.c_ulonglong),
+                ("Mc", C.c_void_p), ("Vc", C.c_void_p), ("d", C.c_void_p), ("r", C.c_void_p), ("m8", C.c_void_p),
+                ("v8", C.c_void_p), ("s", C.c_void_p), ("m8s", C.c_void_p), ("v8s", C.c_void_p), ("sref", C.c_void_p),
+                ("have_sref", C.c_int), ("prev_gn", C.c_float), ("have_prev_gn", C.c_int)]
+
+
 class EpPeers(C.Structure):
     _fields_ = [("rank", C.c_int), ("world", C.c_int), ("base", C.c_void_p * 8)]
 
@@ -64,6 +72,9 @@ PROTOTYPES = {
     "qlmb_moe_dgate": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
     "qlmb_moe_experts_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, ci, vp, vp, vp, cf, vp]),
     "qlmb_moe_route_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, cf, vp]),
+    "qlmb_statefile_write": (ci, [C.c_char_p, C.POINTER(StateFile)]),
+    "qlmb_statefile_read_header": (ci, [C.c_char_p, C.POINTER(StateFile)]),
+    "qlmb_statefile_read": (ci, [C.c_char_p, C.POINTER(StateFile)]),
     "qlmb_peer_alloc": (ci, [C.c_size_t, C.POINTER(vp)]),
     "qlmb_peer_free": (ci, [vp]),
     "qlmb_peer_export": (ci, [vp, vp]),

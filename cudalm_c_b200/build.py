@@ -28,6 +28,7 @@ UNITS = {
     "qlmb_linear.cu": [],
     "qlmb_gemv.cu": [],
     "qlmb_moe.cu": [],
+    "qlmb_statefile.cu": [],
 }
 COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
           "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

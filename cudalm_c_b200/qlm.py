@@ -156,6 +156,53 @@ class Qlm:
         if self.servo_every > 0 and t % self.servo_every == 0:
             self.servo()
 
+    # ---- QLMH state file (qlm_save / qlm_load, qlm.cuh:703-788) ----
+    def _statefile(self, arrays):
+        from ._lib import StateFile
+        v = StateFile()
+        v.dmax, v.group, v.adam, v.nspan, v.packed = self.dmax, self.group, self.adam, self.nspan, self.packed
+        v.nq, v.ngrp, v.nfloat = self.nq, self.ngrp, self.nfloat
+        for k, a in arrays.items():
+            setattr(v, k, a.ctypes.data if a is not None and a.size else None)
+        return v
+
+    def save(self, path, iteration, prev_gn=1.0):
+        """Write the integer state as the reference's .opt.q file (device -> host -> file, atomic replace)."""
+        h = lambda t, n: np.ascontiguousarray(t[:n].cpu().numpy())
+        arr = dict(Mc=h(self.Mc, self.nfloat).view(np.uint16), Vc=h(self.Vc, self.nfloat).view(np.uint16),
+                   d=h(self.d, qd_bytes(self.nq, self.packed)), r=h(self.r, self.nq), m8=h(self.m8, self.nq),
+                   v8=h(self.v8, self.nq) if self.adam else None, s=h(self.s, self.ngrp), m8s=h(self.m8s, self.ngrp),
+                   v8s=h(self.v8s, self.ngrp) if self.adam else None,
+                   sref=np.ascontiguousarray(self.spanH["sref"].astype(np.float32)))
+        v = self._statefile(arr)
+        v.iter, v.prev_gn = int(iteration), float(prev_gn)
+        check(lib().qlmb_statefile_write(str(path).encode(), v))
+
+    def load(self, path):
+        """Read a .opt.q file written by this library or by the reference into this state.
+        Returns (iteration, prev_gn or None).  A file of another shape raises QlmbError; without the
+        SREF trailer the spans keep their current reference scales, as in the reference."""
+        z = lambda n, dt: np.zeros(max(int(n), 1), dt)
+        arr = dict(Mc=z(self.nfloat, np.uint16), Vc=z(self.nfloat, np.uint16), d=z(qd_bytes(self.nq, self.packed), np.int8),
+                   r=z(self.nq, np.int8), m8=z(self.nq, np.int8), v8=z(self.nq, np.uint8) if self.adam else None,
+                   s=z(self.ngrp, np.float32), m8s=z(self.ngrp, np.float32),
+                   v8s=z(self.ngrp, np.float32) if self.adam else None, sref=z(self.nspan, np.float32))
+        v = self._statefile(arr)
+        for k in ("Mc", "Vc", "d", "r", "m8", "s", "m8s", "sref"):
+            setattr(v, k, arr[k].ctypes.data)
+        check(lib().qlmb_statefile_read(str(path).encode(), v))
+        nf = int(v.nfloat)
+        up = lambda t, a, n: t[:n].copy_(torch.from_numpy(a[:n].copy()).to(t.device)) if n else None
+        up(self.Mc, arr["Mc"].view(np.int16), nf); up(self.Vc, arr["Vc"].view(np.int16), nf)
+        up(self.d, arr["d"], qd_bytes(self.nq, self.packed)); up(self.r, arr["r"], self.nq); up(self.m8, arr["m8"], self.nq)
+        up(self.s, arr["s"], self.ngrp); up(self.m8s, arr["m8s"], self.ngrp)
+        if self.adam:
+            up(self.v8, arr["v8"], self.nq); up(self.v8s, arr["v8s"], self.ngrp)
+        if v.have_sref:
+            self.spanH["sref"] = arr["sref"][:self.nspan]
+            self.spanD = spans_to_device(self.spanH, self.device)
+        return int(v.iter), (float(v.prev_gn) if v.have_prev_gn else None)
+
     def persist_bytes(self):
         """qlm_persist_bytes (qlm.cuh:678-683)."""
         return (qd_bytes(self.nq, self.packed) + self.nq + self.nq * (2 if self.adam else 1)

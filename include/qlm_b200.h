@@ -232,6 +232,32 @@ int qlmb_moe_experts_backward(const qlmb_moe_layer *L, void *earena, void *dX, c
 int qlmb_moe_route_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const void *dXs,
                             const void *f_norm, float *dWr, float beta, void *stream);
 
+/* ------------------------------------------------------------ QLMH state file
+ * The reference's checkpoint of the integer optimizer state (qlm_save / qlm_load,
+ * qlm.cuh:703-788), same bytes, on caller-owned HOST arrays: copy the device state to the
+ * host, call qlmb_statefile_write; or size the arrays from qlmb_statefile_read_header, call
+ * qlmb_statefile_read and upload.  d holds (nq+1)/2 bytes when packed, else nq; v8 / v8s
+ * exist only with adam != 0; Mc / Vc are the bf16 moments of the float spans (cudalm.cu:
+ * 2855-2870); sref[i] is span i's frozen reference scale (the file's SREF trailer); prev_gn
+ * is the previous step's gradient norm (PGN1 trailer).  Reading refuses a file whose
+ * dmax/group/adam/packed/nq/ngrp differ from the caller's fields or that holds more
+ * float-span moments than the caller (QLMB_E_UNSUPPORTED), like the reference. */
+typedef struct qlmb_statefile {
+    int dmax, group, adam, nspan, packed, iter;
+    unsigned long long nq, ngrp, nfloat;
+    unsigned short *Mc, *Vc;
+    int8_t *d, *r, *m8;
+    uint8_t *v8;
+    float *s, *m8s, *v8s;
+    float *sref;
+    int have_sref;
+    float prev_gn;
+    int have_prev_gn;
+} qlmb_statefile;
+int qlmb_statefile_write(const char *path, const qlmb_statefile *v);
+int qlmb_statefile_read_header(const char *path, qlmb_statefile *v);
+int qlmb_statefile_read(const char *path, qlmb_statefile *v);
+
 /* ------------------------------- expert parallelism by peer loads (new, no reference counterpart)
  * Same cut of moe_forward / moe_backward (cudalm.cu:4151-4393), but rows never travel in a
  * separate exchange: every rank places its inputs and both arenas in one "window" of device

@@ -266,6 +266,24 @@ class Reference:
         self.lib.ref_g_atb(_p(A), _p(B), _p(Cc), C.c_int(M), C.c_int(K), C.c_int(N))
         return Cc
 
+    # QLMH state file (qlm_save / qlm_load) on host arrays
+    def _state_args(self, st, sp):
+        ull = C.c_ulonglong
+        return [C.c_int(st["dmax"]), C.c_int(st["group"]), C.c_int(st["adam"]), C.c_int(st["packed"]), _p(sp),
+                C.c_int(len(sp)), ull(st["r"].size), ull(st["s"].size), ull(st["Mc"].size), _p(st["d"]), _p(st["r"]),
+                _p(st["m8"]), _p(st.get("v8")), _p(st["s"]), _p(st["m8s"]), _p(st.get("v8s")), _p(st["Mc"]), _p(st["Vc"])]
+
+    def qlm_save(self, path, st, sp, iter_, prev_gn):
+        """st: dict of numpy arrays d, r, m8, v8, s, m8s, v8s, Mc, Vc (uint16) + ints dmax, group, adam, packed."""
+        self.lib.ref_qlm_save.restype = C.c_int
+        return self.lib.ref_qlm_save(path.encode(), C.c_int(iter_), C.c_float(prev_gn), *self._state_args(st, sp))
+
+    def qlm_load(self, path, st, sp):
+        it = C.c_int(-1); pg = C.c_float(0.0)
+        self.lib.ref_qlm_load.restype = C.c_int
+        ok = self.lib.ref_qlm_load(path.encode(), C.byref(it), C.byref(pg), *self._state_args(st, sp))
+        return ok, it.value, pg.value
+
     # one MoE layer
     def moe_new(self, N, D, F, E, K, aux=0.03):
         h = self.lib.ref_moe_new(C.c_int(N), C.c_int(D), C.c_int(F), C.c_int(E), C.c_int(K), C.c_float(aux))

@@ -156,4 +156,40 @@ void ref_moe_backward(void *hv)
     moe_backward(h->P, h->G, &h->o, h->a, 0, h->N);
 }
 
+/* ---- QLMH optimizer-state file (qlm.cuh:703-788), on caller-owned host arrays ---- */
+static void fill_qlm(Qlm *q, int dmax, int group, int adam, int packed, QSpanD *spans, int nspan,
+                     unsigned long long nq, unsigned long long ngrp, unsigned long long nfloat,
+                     signed char *d, signed char *r, signed char *m8, unsigned char *v8, float *s,
+                     float *m8s, float *v8s, unsigned short *Mc, unsigned short *Vc)
+{
+    memset(q, 0, sizeof *q);
+    q->dmax = dmax; q->group = group; q->adam = adam; q->packed = packed;
+    q->nspan = nspan; q->spanH = spans; q->spanD = spans;
+    q->nq = nq; q->ngrp = ngrp; q->nfloat = nfloat;
+    q->d = d; q->r = r; q->m8 = m8; q->v8 = v8; q->s = s; q->m8s = m8s; q->v8s = v8s;
+    q->Mc = (bf16 *)Mc; q->Vc = (bf16 *)Vc;
+}
+int ref_qlm_save(const char *path, int iter, float prev_gn, int dmax, int group, int adam, int packed,
+                 QSpanD *spans, int nspan, unsigned long long nq, unsigned long long ngrp,
+                 unsigned long long nfloat, signed char *d, signed char *r, signed char *m8,
+                 unsigned char *v8, float *s, float *m8s, float *v8s, unsigned short *Mc, unsigned short *Vc)
+{
+    Qlm q;
+    fill_qlm(&q, dmax, group, adam, packed, spans, nspan, nq, ngrp, nfloat, d, r, m8, v8, s, m8s, v8s, Mc, Vc);
+    g_prev_gn = prev_gn;
+    return qlm_save(&q, path, iter);
+}
+int ref_qlm_load(const char *path, int *iter, float *prev_gn, int dmax, int group, int adam, int packed,
+                 QSpanD *spans, int nspan, unsigned long long nq, unsigned long long ngrp,
+                 unsigned long long nfloat, signed char *d, signed char *r, signed char *m8,
+                 unsigned char *v8, float *s, float *m8s, float *v8s, unsigned short *Mc, unsigned short *Vc)
+{
+    Qlm q;
+    fill_qlm(&q, dmax, group, adam, packed, spans, nspan, nq, ngrp, nfloat, d, r, m8, v8, s, m8s, v8s, Mc, Vc);
+    g_prev_gn = 0.0f;
+    int ok = qlm_load(&q, path, iter);
+    if (prev_gn) *prev_gn = g_prev_gn;
+    return ok;
+}
+
 } /* extern "C" */

@@ -203,6 +203,31 @@ def golden_moe(ref):
         dWr=G[L.off("wr"):L.off("wr") + D * E].copy())
 
 
+def golden_statefile(ref):
+    """A QLMH optimizer-state file written by the reference's own qlm_save (two ragged spans,
+    3 optimizer steps, 40 float-span moments), plus the arrays that went into it."""
+    rng = np.random.default_rng(11)
+    group, dmax, packed = 128, 7, 1
+    sp, nq, ng = loader.make_spans([128 * 5, 300], group)
+    P = (rng.standard_normal(nq) * 0.02).astype(f32)
+    d = np.zeros((nq + 1) // 2, np.int8); r = np.zeros(nq, np.int8); s = np.zeros(ng, f32)
+    ref.encode(P, d, r, s, sp, group, dmax, packed)
+    set_sref(sp, s)
+    m8 = np.zeros(nq, np.int8); v8 = np.zeros(nq, np.uint8); m8s = np.zeros(ng, f32); v8s = np.zeros(ng, f32)
+    Pv = np.zeros(nq, f32)
+    for t in range(1, 4):
+        G = (rng.standard_normal(nq) * 1e-3).astype(f32)
+        i1, i2 = bias_corr(0.9, 0.95, t)
+        ref.step(Pv, G, d, r, s, m8, m8s, v8, v8s, sp, group=group, dmax=dmax, lr=3e-4, b1=0.9, b2=0.95, wd=0.1,
+                 inv_bc1=i1, inv_sqrt_bc2=i2, t=t, packed=packed)
+    Mc = rng.integers(0, 65536, 40).astype(np.uint16); Vc = rng.integers(0, 32768, 40).astype(np.uint16)
+    st = dict(dmax=dmax, group=group, adam=1, packed=packed, d=d, r=r, m8=m8, v8=v8, s=s, m8s=m8s, v8s=v8s, Mc=Mc, Vc=Vc)
+    path = os.path.join(OUT, "qlmh_small.opt.q")
+    assert ref.qlm_save(path, st, sp, 1234, 2.5) == 1
+    np.savez_compressed(os.path.join(OUT, "qlmh_small.npz"), d=d, r=r, m8=m8, v8=v8, s=s, m8s=m8s, v8s=v8s, Mc=Mc, Vc=Vc,
+                        sref=sp["sref"].copy(), cfg=np.array([dmax, group, 1, len(sp), packed, 1234]), prev_gn=np.float32(2.5))
+
+
 def main():
     ref = loader.reference(exact=True)
     if ref is None:
@@ -217,6 +242,7 @@ def main():
     golden_router(ref)
     golden_linear(ref)
     golden_moe(ref)
+    golden_statefile(ref)
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print("%-24s %8d B" % (f, os.path.getsize(os.path.join(OUT, f))))
