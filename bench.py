@@ -518,12 +518,24 @@ def run_gemv(args):
         for B in (1, 8, 64):
             X = torch.randn(B, K, device=dev, generator=gen).bfloat16()
             Y = torch.empty(B, N, device=dev, dtype=torch.bfloat16)
-            ms = _time(lambda: linear.gemv_decode(X, Q.d, Q.s, lay, N, out=Y), args.steps, args.warmup)
+            call = lambda: linear.gemv_decode(X, Q.d, Q.s, lay, N, out=Y)
+            ms_call = _time(call, args.steps, args.warmup)      # one host call per GEMV (host overhead included)
+            # device time: 20 calls captured in a CUDA graph, replayed
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(20):
+                        call()
+            torch.cuda.current_stream().wait_stream(side)
+            ms = _time(graph.replay, max(args.steps // 4, 3), 3) / 20
             gbs = K * N * 0.53125 / (ms * 1e-3) / 1e9
             print(json.dumps(dict(metric="decode_gemv_weight_gbs", value=round(gbs, 1), unit="GB/s", n_gpus=1, steps=args.steps,
                                   warmup=max(args.warmup, 3), ms_per_step=round(ms, 5), higher_is_better=True, scaling="weak",
                                   vs_baseline=None, dtype="bf16", data="synthetic",
                                   config=dict(workload="decode GEMV, 4-bit weights " + tag, slots=B,
+                                              timing="20 calls in a replayed CUDA graph; one host call per GEMV takes %.1f us" % (ms_call * 1e3),
                                               l2="weights %.1f MB per call (the small matrix stays in L2)" % (K * N * 0.53125 / 1e6)),
                                   roofline=dict(bound="hbm", kernel="k_gemv", achieved=round(gbs, 1), peak=pk["hbm"], unit="GB/s",
                                                 frac=round(gbs / pk["hbm"], 4), traffic=None, peak_kind="copy bandwidth, of " + pk["src"]),

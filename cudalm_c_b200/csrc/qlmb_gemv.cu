@@ -217,10 +217,11 @@ extern "C" int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, con
     if (B > 4 && dtype == QLMB_BF16 && (K % 64) == 0)
         return qlmb_linear_fwd(Y, X, codes, scales, layout, B, K, N, nullptr, dtype, stream);
     const int bt = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
-    // K slices: enough blocks to fill the device several times over, at least 64 rows each,
+    // K slices: enough blocks to fill the device once, at least 64 rows each,
     // a multiple of 8 rows, and small enough for the activation tile in shared memory
     const int nblk = layout == QLMB_KN ? (N + 255) / 256 : (N + 31) / 32;
-    int nslice = (6 * sm_count() + nblk - 1) / nblk;
+    // one full wave: 4 (bt <= 2) or 2 resident blocks per SM
+    int nslice = ((bt <= 2 ? 4 : 2) * sm_count()) / nblk;
     if (nslice > K / 64) nslice = K / 64;
     if (nslice < 1) nslice = 1;
     int kslice = ((K + nslice - 1) / nslice + 127) / 128 * 128;

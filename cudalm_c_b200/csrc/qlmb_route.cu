@@ -133,13 +133,19 @@ __global__ void __launch_bounds__(256) k_perm_scan(int *ch, int E, int NC, int p
                                                    int *tile_info, int *ntiles,
                                                    const int *bad, int *errword)
 {
-    extern __shared__ int sm[];           // [E] totals then [E+1] padded offsets
-    int *tot = sm, *po = sm + E;
-    int k = blockIdx.x;
+    extern __shared__ int sm[];           // [E] totals, [E+1] padded offsets, then (when it fits) the E*NC chunk counts
+    int *tot = sm, *po = sm + E, *cs = sm + 2 * E + 1;
+    const int k = blockIdx.x;
     int *cp = ch + (size_t)k * E * NC;
+    const bool staged = (size_t)E * NC <= 8192;          // chunk counts through shared memory: no dependent global accesses
+    if (staged) {
+        for (int i = threadIdx.x; i < E * NC; i += blockDim.x) cs[i] = cp[i];
+        __syncthreads();
+    }
+    const int *src = staged ? cs : cp;
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int s = 0;
-        for (int c = 0; c < NC; c++) s += cp[(size_t)e * NC + c];
+        for (int c = 0; c < NC; c++) s += src[(size_t)e * NC + c];
         tot[e] = s;
     }
     __syncthreads();
@@ -158,23 +164,40 @@ __global__ void __launch_bounds__(256) k_perm_scan(int *ch, int E, int NC, int p
     // chunk bases
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int s = po[e];
-        for (int c = 0; c < NC; c++) { int t = cp[(size_t)e * NC + c]; cp[(size_t)e * NC + c] = s; s += t; }
+        if (staged) {
+            for (int c = 0; c < NC; c++) { int t = cs[e * NC + c]; cs[e * NC + c] = s; s += t; }
+        } else {
+            for (int c = 0; c < NC; c++) { int t = cp[(size_t)e * NC + c]; cp[(size_t)e * NC + c] = s; s += t; }
+        }
     }
-    // filler rows
+    if (staged) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < E * NC; i += blockDim.x) cp[i] = cs[i];
+    }
+    // filler rows: the padded tail of every expert segment, all experts at once
     if (pad > 1)
-        for (int e = 0; e < E; e++)
-            for (int p = po[e] + tot[e] + threadIdx.x; p < po[e + 1]; p += blockDim.x)
-                perm[(size_t)k * plen + p] = -1;
+        for (int i = threadIdx.x; i < E * (pad - 1); i += blockDim.x) {
+            const int e = i / (pad - 1), p = po[e] + tot[e] + i % (pad - 1);
+            if (p < po[e + 1]) perm[(size_t)k * plen + p] = -1;
+        }
     // row tiles of the grouped GEMMs (pad must be 128): up to 256 rows of one expert each,
-    // packed as first row / 128 | expert << 20 | (halves - 1) << 30
-    if (tile_info && k == 0 && threadIdx.x == 0) {
-        int nt = 0;
-        for (int e = 0; e < E; e++) {
-            int n128 = (po[e + 1] - po[e]) / 128;
+    // packed as first row / 128 | expert << 20 | (halves - 1) << 30; expert e's tiles start
+    // at the number of tiles of the experts before it
+    if (tile_info && k == 0) {
+        __shared__ int tbase[257];
+        if (threadIdx.x == 0) {
+            int nt = 0;
+            for (int e = 0; e < E; e++) { tbase[e] = nt; nt += ((po[e + 1] - po[e]) / 128 + 1) / 2; }
+            tbase[E] = nt;
+            *ntiles = nt;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            const int n128 = (po[e + 1] - po[e]) / 128;
+            int nt = tbase[e];
             for (int i = 0; i < n128; i += 2)
                 tile_info[nt++] = (po[e] / 128 + i) | (e << 20) | ((i + 1 < n128 ? 1 : 0) << 30);
         }
-        *ntiles = nt;
     }
 }
 
@@ -209,7 +232,7 @@ int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int 
     int plen = len + E * (pad - 1);
     QLMB_CUDA(cudaMemsetAsync(bad_flag, 0, sizeof(int), st));
     k_perm_hist<<<dim3(NC, sorts), PERM_CHUNK, E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, bad_flag, e_lo, skip);
-    k_perm_scan<<<sorts, 256, (2 * E + 1) * sizeof(int), st>>>(chunk_scratch, E, NC, pad, plen, off, counts, perm,
+    k_perm_scan<<<sorts, 256, (2 * E + 1 + ((size_t)E * NC <= 8192 ? (size_t)E * NC : 0)) * sizeof(int), st>>>(chunk_scratch, E, NC, pad, plen, off, counts, perm,
                                                              tile_info, ntiles, bad_flag,
                                                              device_error_word());
     k_perm_scatter<<<dim3(NC, sorts), PERM_CHUNK, 32 * E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, perm,
