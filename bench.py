@@ -202,8 +202,13 @@ def run_ours(args):
         ach = fl[top] / (kern[top] * 1e-3) / 1e12
         long_run = ms * args.steps > 1000.0
         peak = pk["tf_sustained"] if long_run else pk["tf_burst"]
+        # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of one ncu capture of this very
+        # workload (profiles/k_gemm_pair_dram_traffic.md); only valid for the default configuration on one GPU
+        ncu_dram = {"gemm_gate_up_swiglu": 183.2e6, "gemm_down": 82.6e6, "gemm_dact_swiglu_bwd": 237.5e6, "gemm_dx": 168.5e6,
+                    "gemm_wgrad_w1": 175.1e6, "gemm_wgrad_w3": 174.6e6, "gemm_wgrad_w2": 174.5e6}
+        traffic = ncu_dram.get(top) if (world == 1 and c == dict(N=8192, D=768, F=1536, E=32, K=2)) else None
         roof = dict(bound="tensor", kernel=top, achieved=round(ach, 1), peak=peak, unit="TFLOP/s", frac=round(ach / peak, 4),
-                    traffic=None, peak_kind=("sustained" if long_run else "burst") + " bf16, of " + pk["src"],
+                    traffic=traffic, peak_kind=("sustained" if long_run else "burst") + " bf16, of " + pk["src"],
                     kernel_ms={k: round(v, 4) for k, v in sorted(kern.items(), key=lambda kv: -kv[1])},
                     gemm_phase_tflops=round(sum(fl.values()) / (sum(kern[k] for k in fl) * 1e-3) / 1e12, 1))
 

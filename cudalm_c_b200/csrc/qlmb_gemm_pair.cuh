@@ -118,10 +118,12 @@ __device__ __forceinline__ TileInfo decode_pair_tile(const GemmParams &p, int ti
         t.m0 = (tile % p.tiles_m) * 256; t.n_t = tile / p.tiles_m; t.e = 0; t.ksteps = p.ksteps; t.row0 = 0;
         t.halves = (t.m0 + BM < p.M) ? 2 : 1;
     } else if (SCHED == SCHED_ROWS) {
-        int rt = tile % ntr;
+        // column tiles fastest: the pairs that run side by side share a row tile of A (which can be
+        // far larger than L2 in total: 113 MB for dX) and differ in the weight slice (40 MB in total)
+        int rt = tile / p.tiles_n;
         int info = p.tile_info[rt];
         t.m0 = (info & 0xFFFFF) * BM; t.e = (info >> 20) & 0x1FF; t.halves = ((info >> 30) & 1) + 1;
-        t.n_t = tile / ntr; t.ksteps = p.ksteps; t.row0 = 0;
+        t.n_t = tile % p.tiles_n; t.ksteps = p.ksteps; t.row0 = 0;
     } else {
         int per = p.tiles_m * p.tiles_n;
         t.e = tile / per;
