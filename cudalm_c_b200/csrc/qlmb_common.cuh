@@ -32,7 +32,7 @@ int *device_error_word(void);                            // per-device int, lazi
 static inline cudaStream_t as_stream(void *s) { return (cudaStream_t)s; }
 int sm_count(void);                                      // SMs of the current device
 // second stream of the device for overlappable work (qlmb_runtime.cu); returns `st` itself when unavailable
-cudaStream_t side_fork(cudaStream_t st);
+cudaStream_t side_fork(cudaStream_t st, int which = 0);   // two side streams per device: which = 0 or 1
 void side_wait_main(cudaStream_t side, cudaStream_t st);
 void side_join(cudaStream_t side, cudaStream_t st);
 // Times the enclosed launches with CUDA events when qlmb_prof_enable(1) was called.

@@ -116,6 +116,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sr
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
+// shared -> global bulk tensor reduction (element-wise add into the tensor) of one box
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, uint32_t src, int x, int y)
+{
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -358,6 +364,30 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
             }
             if (p.o_tma) blk_store_bulk(stage, lane, &p.o_map[0], (int)(col0 + half * 64), (int)rbase);
             else blk_store(stage, lane, reinterpret_cast<uint8_t *>((bf16 *)p.out + rbase * p.ldo + col0 + half * 64), p.ldo * 2, valid);
+        }
+    } else if ((EPI == EPI_STORE || EPI == EPI_ACCUM) && p.out_dtype == QLMB_F32 && p.o_tma) {
+        // fp32 output through bulk tensor copies: 32 rows x 32 columns (128-byte rows) per block;
+        // beta = 1 adds into the tensor with a bulk reduction, so the old values are never read here
+        if (!(p.beta != 0.0f && !have_acc)) {
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[32];
+                tmem_ld32(tbase + c * 32, v);
+                tmem_ld_wait();
+                blk_reuse(lane);
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    uint4 q = have_acc ? make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]) : make_uint4(0, 0, 0, 0);
+                    *blk_vec(stage, lane, k) = q;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (p.beta != 0.0f) tma_reduce_add_2d(&p.o_map[0], smem_u32(stage), (int)(col0 + c * 32), (int)rbase);
+                    else tma_store_2d(&p.o_map[0], smem_u32(stage), (int)(col0 + c * 32), (int)rbase);
+                    bulk_commit();
+                }
+            }
         }
     } else if (EPI == EPI_STORE || EPI == EPI_ACCUM) {
 #pragma unroll 1
@@ -1010,19 +1040,27 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
     }
     // bf16 outputs leave through bulk tensor stores when their layout allows a tensor map
     {
-        const unsigned long long orows = (g.sched == SCHED_ROWS) ? (unsigned long long)g.a_rows : (unsigned long long)g.M;
+        const unsigned long long orows = (g.sched == SCHED_ROWS) ? (unsigned long long)g.a_rows
+                                       : (g.sched == SCHED_GROUPK) ? (unsigned long long)g.E * g.M : (unsigned long long)g.M;
         const void *optr[3] = {nullptr, nullptr, nullptr};
         int no = 0;
-        if (g.epi == EPI_STORE && g.out_dtype == QLMB_BF16 && !g.resid && g.beta == 0.0f) { optr[0] = g.out; no = 1; }
+        const bool f32out = (g.epi == EPI_STORE || g.epi == EPI_ACCUM) && g.out_dtype == QLMB_F32 && !g.resid &&
+                            (g.beta == 0.0f || g.beta == 1.0f);
+        if (f32out) { optr[0] = g.out; no = 1; }
+        else if (g.epi == EPI_STORE && g.out_dtype == QLMB_BF16 && !g.resid && g.beta == 0.0f) { optr[0] = g.out; no = 1; }
         else if (g.epi == EPI_SWIGLU) { optr[0] = g.ap; optr[1] = g.gp; optr[2] = g.up; no = 3; }
         else if (g.epi == EPI_SWIGLU_BWD) { optr[0] = g.dgp; optr[1] = g.dup; no = 2; }
-        bool can = no > 0 && (g.ldo % 8) == 0 && g.sched != SCHED_GROUPK && orows > 0;
+        bool can = no > 0 && (g.ldo % 8) == 0 && (g.sched != SCHED_GROUPK || f32out) && orows > 0;
         for (int i = 0; i < no && can; i++) can = optr[i] && (((uintptr_t)optr[i]) & 15) == 0;
         const bool bwd = g.epi == EPI_SWIGLU_BWD;           // 32-column boxes, 64-byte swizzle
         if (bwd) can = can && g.gp && g.up && ((((uintptr_t)g.gp) | ((uintptr_t)g.up)) & 15) == 0;
         for (int i = 0; i < no && can; i++) {
-            rc = make_map(&p.o_map[i], optr[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (unsigned long long)g.ldo, orows,
-                          (unsigned long long)g.ldo * 2, bwd ? 32 : 64, 32, bwd ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+            if (f32out)
+                rc = make_map(&p.o_map[i], optr[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (unsigned long long)g.ldo, orows,
+                              (unsigned long long)g.ldo * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+            else
+                rc = make_map(&p.o_map[i], optr[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (unsigned long long)g.ldo, orows,
+                              (unsigned long long)g.ldo * 2, bwd ? 32 : 64, 32, bwd ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc) return rc;
         }
         for (int i = 0; i < 2 && can && bwd; i++) {

@@ -220,14 +220,19 @@ extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfn
     { ProfScope ps("dgate_rows", st);
     if ((rc = dgate_rows(a.dyp, a.d_gate, dout, L->dtype, a.yp, a.perm, a.gate, a.off + E, R, N, D, st))) return rc; }
 
-    // d(act), dXp and the weight gradients (cudalm.cu:4335-4366)
-    if ((rc = experts_backward_gemms(L, a, dW1, dW3, dW2, beta, st))) return rc;
+    // router backward (cudalm.cu:4372-4391): needs only d_gate, so it and the router weight gradient
+    // run on the second side stream next to the expert GEMMs
+    cudaStream_t side = side_fork(st, 1);
+    { ProfScope ps("router_bwd", side); rc = router_bwd(a.drt, a.rprobs, a.assign, a.d_gate, a.counts, N, E, K, L->aux, side); }
+    if (!rc) { ProfScope ps("router_wgrad", side); rc = router_wgrad(dWr, f_norm, L->dtype, a.drt, a.wr_scratch, N, D, E, beta, side); }
 
-    // router backward (cudalm.cu:4372-4391)
-    { ProfScope ps("router_bwd", st); if ((rc = router_bwd(a.drt, a.rprobs, a.assign, a.d_gate, a.counts, N, E, K, L->aux, st))) return rc; }
-    { ProfScope ps("unpermute_rows", st); if ((rc = unpermute_rows(dfnorm, L->dtype, a.dXp, a.inv, a.drt, L->wr, a.wrt, N, D, E, K, st))) return rc; }
-    ProfScope ps("router_wgrad", st);
-    return router_wgrad(dWr, f_norm, L->dtype, a.drt, a.wr_scratch, N, D, E, beta, st);
+    // d(act), dXp and the weight gradients (cudalm.cu:4335-4366)
+    if (!rc) rc = experts_backward_gemms(L, a, dW1, dW3, dW2, beta, st);
+    side_join(side, st);
+    if (rc) return rc;
+
+    ProfScope ps("unpermute_rows", st);
+    return unpermute_rows(dfnorm, L->dtype, a.dXp, a.inv, a.drt, L->wr, a.wrt, N, D, E, K, st);
 }
 
 // ===================================================================== expert parallelism
@@ -287,9 +292,11 @@ extern "C" int qlmb_moe_route_backward(const qlmb_moe_layer *L, void *arena, voi
     Arena a = carve(arena, N, D, L->F, E, K);
     cudaStream_t st = as_stream(stream);
     { ProfScope ps("router_bwd", st); if ((rc = router_bwd(a.drt, a.rprobs, a.assign, a.d_gate, a.counts, N, E, K, L->aux, st))) return rc; }
-    { ProfScope ps("unpermute_rows", st); if ((rc = unpermute_rows(dfnorm, L->dtype, (const bf16 *)dXs, a.inv, a.drt, L->wr, a.wrt, N, D, E, K, st))) return rc; }
-    ProfScope ps("router_wgrad", st);
-    return router_wgrad(dWr, f_norm, L->dtype, a.drt, a.wr_scratch, N, D, E, beta, st);
+    cudaStream_t side = side_fork(st, 1);
+    { ProfScope ps("router_wgrad", side); rc = router_wgrad(dWr, f_norm, L->dtype, a.drt, a.wr_scratch, N, D, E, beta, side); }
+    if (!rc) { ProfScope ps("unpermute_rows", st); rc = unpermute_rows(dfnorm, L->dtype, (const bf16 *)dXs, a.inv, a.drt, L->wr, a.wrt, N, D, E, K, st); }
+    side_join(side, st);
+    return rc;
 }
 
 // Expert side.  L describes the experts held by this rank (E = local experts, K is ignored,
@@ -478,8 +485,10 @@ extern "C" int qlmb_ep_route_backward(const qlmb_moe_layer *H, void *harena, con
     Arena e = carve(earena, L->N, L->D, L->F, L->E, 1);
     cudaStream_t st = as_stream(stream);
     { ProfScope ps("router_bwd", st); if ((rc = router_bwd(h.drt, h.rprobs, h.assign, h.d_gate, h.counts, N, E, K, H->aux, st))) return rc; }
-    { ProfScope ps("unpermute_rows_peer", st);
-      if ((rc = unpermute_rows_peer(dfnorm, H->dtype, peer_view(P, e.dXp), h.assign, h.inv, L->E, h.drt, H->wr, h.wrt, N, D, E, K, st))) return rc; }
-    ProfScope ps("router_wgrad", st);
-    return router_wgrad(dWr, f_norm, H->dtype, h.drt, h.wr_scratch, N, D, E, beta, st);
+    cudaStream_t side = side_fork(st, 1);
+    { ProfScope ps("router_wgrad", side); rc = router_wgrad(dWr, f_norm, H->dtype, h.drt, h.wr_scratch, N, D, E, beta, side); }
+    if (!rc) { ProfScope ps("unpermute_rows_peer", st);
+               rc = unpermute_rows_peer(dfnorm, H->dtype, peer_view(P, e.dXp), h.assign, h.inv, L->E, h.drt, H->wr, h.wrt, N, D, E, K, st); }
+    side_join(side, st);
+    return rc;
 }

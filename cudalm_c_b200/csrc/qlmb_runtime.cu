@@ -51,36 +51,43 @@ int sm_count(void)
 }
 
 
-// ---- a second stream per device for work that may overlap the caller's stream ----
+// ---- two library-owned streams per device for work that may overlap the caller's stream ----
 // side_fork() makes the side stream wait for everything queued on `st` so far, side_join()
 // makes `st` wait for everything queued on the side stream; side_wait_main() is a second
 // fork point in between.  QLMB_SIDE_STREAM=0 runs everything on the caller's stream.
-static cudaStream_t g_side[64];
-static cudaEvent_t g_side_ev[64][3];
+static cudaStream_t g_side[64][2];
+static cudaEvent_t g_side_ev[64][2][3];
 static int g_side_on = -1;
 
-cudaStream_t side_fork(cudaStream_t st)
+cudaStream_t side_fork(cudaStream_t st, int which)
 {
     if (g_side_on < 0) { const char *e = getenv("QLMB_SIDE_STREAM"); g_side_on = (e && atoi(e) == 0) ? 0 : 1; }
     int dev = 0;
-    if (!g_side_on || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return st;
+    if (!g_side_on || which < 0 || which > 1 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return st;
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return st;
-    if (!g_side[dev]) {
-        if (cudaStreamCreateWithFlags(&g_side[dev], cudaStreamNonBlocking) != cudaSuccess) { g_side[dev] = nullptr; return st; }
+    if (!g_side[dev][which]) {
+        if (cudaStreamCreateWithFlags(&g_side[dev][which], cudaStreamNonBlocking) != cudaSuccess) { g_side[dev][which] = nullptr; return st; }
         for (int i = 0; i < 3; i++)
-            if (cudaEventCreateWithFlags(&g_side_ev[dev][i], cudaEventDisableTiming) != cudaSuccess) return st;
+            if (cudaEventCreateWithFlags(&g_side_ev[dev][which][i], cudaEventDisableTiming) != cudaSuccess) return st;
     }
-    if (cudaEventRecord(g_side_ev[dev][0], st) != cudaSuccess) return st;
-    if (cudaStreamWaitEvent(g_side[dev], g_side_ev[dev][0], 0) != cudaSuccess) return st;
-    return g_side[dev];
+    if (cudaEventRecord(g_side_ev[dev][which][0], st) != cudaSuccess) return st;
+    if (cudaStreamWaitEvent(g_side[dev][which], g_side_ev[dev][which][0], 0) != cudaSuccess) return st;
+    return g_side[dev][which];
+}
+static int side_index(cudaStream_t side)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    for (int w = 0; w < 2; w++) if (g_side[dev][w] && g_side[dev][w] == side) return dev * 2 + w;
+    return -1;
 }
 void side_wait_main(cudaStream_t side, cudaStream_t st)
 {
-    int dev = 0;
-    if (side == st || cudaGetDevice(&dev) != cudaSuccess) return;
-    cudaEventRecord(g_side_ev[dev][1], st);
-    cudaStreamWaitEvent(side, g_side_ev[dev][1], 0);
+    const int ix = side == st ? -1 : side_index(side);
+    if (ix < 0) return;
+    cudaEventRecord(g_side_ev[ix / 2][ix % 2][1], st);
+    cudaStreamWaitEvent(side, g_side_ev[ix / 2][ix % 2][1], 0);
 }
 }  // namespace qlmb
 extern "C" int qlmb_side_stream_enable(int on)
@@ -91,10 +98,10 @@ extern "C" int qlmb_side_stream_enable(int on)
 namespace qlmb {
 void side_join(cudaStream_t side, cudaStream_t st)
 {
-    int dev = 0;
-    if (side == st || cudaGetDevice(&dev) != cudaSuccess) return;
-    cudaEventRecord(g_side_ev[dev][2], side);
-    cudaStreamWaitEvent(st, g_side_ev[dev][2], 0);
+    const int ix = side == st ? -1 : side_index(side);
+    if (ix < 0) return;
+    cudaEventRecord(g_side_ev[ix / 2][ix % 2][2], side);
+    cudaStreamWaitEvent(st, g_side_ev[ix / 2][ix % 2][2], 0);
 }
 
 // ---- optional per-kernel timing (CUDA events on the launching stream) ----

@@ -66,8 +66,9 @@ int qlmb_version(void);
 int qlmb_check_device(void *stream);
 
 /* Work that does not depend on each other inside one call (the three expert weight-gradient GEMMs
- * of the MoE backward against d(act) and dX) runs on a second, library-owned stream per device and
- * is joined back into the caller's stream before the call returns.  on = 0 keeps everything on the
+ * of the MoE backward against d(act) and dX, the router's backward chain against all of them) runs on
+ * library-owned side streams (two per device) and is joined back into the caller's stream before the
+ * call returns.  on = 0 keeps everything on the
  * caller's stream (also: environment QLMB_SIDE_STREAM=0, and always while the stream is being
  * captured).  No reference counterpart (the reference uses the default stream only). */
 int qlmb_side_stream_enable(int on);
