@@ -205,6 +205,37 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 s2)
     return o;
 }
 
+// The same expansion without the final reordering: the eight results stay in the order
+// (0,4,1,5,2,6,3,7), i.e. position c of each group of eight holds element PERM8[c].  Used where the
+// eight elements run along the OUTPUT columns (codes [K][N]): the epilogue reads accumulator column
+// 8m + c as output column 8m + PERM8[c], which costs nothing, and four PRMTs per word are saved.
+// The nibble extraction folds the sign flip and the exponent into one LOP3 per pair:
+// bit = mask ? (cst ? ~w : w) : cst, with mask 0x000F000F and cst 0x43084308 (0x4300 | the flipped bit 3).
+__device__ __forceinline__ uint32_t nib_pair(uint32_t w)
+{
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x43084308, 0x6A;" : "=r"(r) : "r"(w));
+    return r;
+}
+__device__ __forceinline__ uint4 dequant8_perm(uint32_t w, __nv_bfloat162 s2)
+{
+    uint32_t q[4] = {nib_pair(w), nib_pair(w >> 4), nib_pair(w >> 8), nib_pair(w >> 12)};
+    const uint32_t k136 = 0x43084308u;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162 *>(&q[i]);
+        x = __hmul2(__hsub2(x, *reinterpret_cast<const __nv_bfloat162 *>(&k136)), s2);
+        q[i] = *reinterpret_cast<uint32_t *>(&x);
+    }
+    return make_uint4(q[0], q[1], q[2], q[3]);
+}
+// accumulator column that holds output column i of a tile expanded with dequant8_perm
+template <bool NPERM>
+__device__ __forceinline__ constexpr int acc_col(int i)
+{
+    return NPERM ? ((i & ~7) | (((i & 7) >> 2) | ((i & 3) << 1))) : i;
+}
+
 // ------------------------------------------------------------------ epilogue staging
 // Lane r of a warp owns tile row r and holds VECS 16-byte vectors of it (a row
 // piece of 32, 64 or 128 bytes).  The piece goes through a swizzled 4 KiB buffer so
@@ -339,10 +370,11 @@ __device__ __forceinline__ bool swiglu_bwd_bulk(const GemmParams &p, uint8_t *st
 // address tbase; rbase = index of the warp's first row in the output, col0 = first
 // output column.  EPI_SWIGLU reads 64 gate columns at tbase and 64 up columns at
 // tbase + u_off and writes 64 activation columns.
-template <int EPI>
+template <int EPI, bool NPERM = false>
 __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stage, EpiCtx &ec, int lane, uint32_t tbase,
                                               long long rbase, long long col0, int valid, bool have_acc, uint32_t u_off)
 {
+    static_assert(!(EPI == EPI_SWIGLU_BWD && NPERM), "the SwiGLU-backward epilogue reads accumulator columns in place");
     if (EPI == EPI_SWIGLU_BWD && p.o_tma) { swiglu_bwd_bulk(p, stage, ec, lane, tbase, rbase, col0); return; }
     if (EPI == EPI_STORE && p.out_dtype == QLMB_BF16 && !p.resid && p.beta == 0.0f) {
         // plain bf16 store: two blocks of 64 columns, each written with whole 128-byte rows
@@ -358,7 +390,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
                 __nv_bfloat162 *hw = reinterpret_cast<__nv_bfloat162 *>(w);
 #pragma unroll
                 for (int i = 0; i < 16; i++)
-                    hw[i] = have_acc ? __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])) : __floats2bfloat162_rn(0.0f, 0.0f);
+                    hw[i] = have_acc ? __floats2bfloat162_rn(__uint_as_float(v[acc_col<NPERM>(2 * i)]), __uint_as_float(v[acc_col<NPERM>(2 * i + 1)])) : __floats2bfloat162_rn(0.0f, 0.0f);
 #pragma unroll
                 for (int k = 0; k < 4; k++) *blk_vec(stage, lane, cc * 4 + k) = w[k];
             }
@@ -377,7 +409,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
                 blk_reuse(lane);
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
-                    uint4 q = have_acc ? make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]) : make_uint4(0, 0, 0, 0);
+                    uint4 q = have_acc ? make_uint4(v[acc_col<NPERM>(4 * k)], v[acc_col<NPERM>(4 * k + 1)], v[acc_col<NPERM>(4 * k + 2)], v[acc_col<NPERM>(4 * k + 3)]) : make_uint4(0, 0, 0, 0);
                     *blk_vec(stage, lane, k) = q;
                 }
                 fence_proxy_async();
@@ -398,7 +430,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
             const long long o = rbase * p.ldo + col0 + c * 32;
             float f[32];
 #pragma unroll
-            for (int i = 0; i < 32; i++) f[i] = have_acc ? __uint_as_float(v[i]) : 0.0f;
+            for (int i = 0; i < 32; i++) f[i] = have_acc ? __uint_as_float(v[acc_col<NPERM>(i)]) : 0.0f;
             if (p.out_dtype == QLMB_F32) {
                 if (p.resid) {
                     uint4 r[8];
@@ -456,15 +488,15 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
                     tmem_ld_wait();
 #pragma unroll
                     for (int k = 0; k < 8; k++) {
-                        float g0 = __uint_as_float(g[2 * k]), g1 = __uint_as_float(g[2 * k + 1]);
-                        float u0 = __uint_as_float(u[2 * k]), u1 = __uint_as_float(u[2 * k + 1]);
+                        float g0 = __uint_as_float(g[acc_col<NPERM>(2 * k)]), g1 = __uint_as_float(g[acc_col<NPERM>(2 * k + 1)]);
+                        float u0 = __uint_as_float(u[acc_col<NPERM>(2 * k)]), u1 = __uint_as_float(u[acc_col<NPERM>(2 * k + 1)]);
                         hw[k] = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
                     }
                 } else {
                     tmem_ld16(tbase + (pass == 2 ? u_off : 0u) + c * 16, g);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int k = 0; k < 8; k++) hw[k] = __floats2bfloat162_rn(__uint_as_float(g[2 * k]), __uint_as_float(g[2 * k + 1]));
+                    for (int k = 0; k < 8; k++) hw[k] = __floats2bfloat162_rn(__uint_as_float(g[acc_col<NPERM>(2 * k)]), __uint_as_float(g[acc_col<NPERM>(2 * k + 1)]));
                 }
                 *blk_vec(stage, lane, 2 * c) = w[0];
                 *blk_vec(stage, lane, 2 * c + 1) = w[1];

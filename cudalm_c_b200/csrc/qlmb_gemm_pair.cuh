@@ -328,9 +328,9 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                 const bool have_acc = (SCHED != SCHED_GROUPK) || t.ksteps > 0;
                 const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * P_BN;
                 if (EPI == EPI_SWIGLU)
-                    epilogue_rows<EPI>(p, stage, ec, lane, tbase + (uint32_t)h * 64, rbase, col0, valid, have_acc, 128);
+                    epilogue_rows<EPI, BMODE == B_DEQ_MN>(p, stage, ec, lane, tbase + (uint32_t)h * 64, rbase, col0, valid, have_acc, 128);
                 else
-                    epilogue_rows<EPI>(p, stage, ec, lane, tbase + (uint32_t)h * 128, rbase, col0, valid, have_acc, 0);
+                    epilogue_rows<EPI, BMODE == B_DEQ_MN>(p, stage, ec, lane, tbase + (uint32_t)h * 128, rbase, col0, valid, have_acc, 0);
             }
             tc_fence_before();
             __syncwarp();
@@ -400,7 +400,7 @@ k_gemm_pair(const __grid_constant__ GemmParams p)
                     uint8_t *bdst = sB + rb.idx * P_B_STAGE;
 #pragma unroll
                     for (int i = 0; i < ITERS; i++)
-                        *reinterpret_cast<uint4 *>(bdst + dst0[i % PER] + (uint32_t)(i / PER) * DST_STEP) = dequant8(w[i], __float2bfloat162_rn(cur[i]));
+                        *reinterpret_cast<uint4 *>(bdst + dst0[i % PER] + (uint32_t)(i / PER) * DST_STEP) = (BMODE == B_DEQ_MN) ? dequant8_perm(w[i], __float2bfloat162_rn(cur[i])) : dequant8(w[i], __float2bfloat162_rn(cur[i]));
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) { mbar_arrive_remote(full0 + (uint32_t)rb.idx * 8u); mbar_arrive(smem_u32(&empty_c[rc.idx])); }

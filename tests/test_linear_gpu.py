@@ -146,7 +146,7 @@ def test_gemv_decode(cuda, oracle, B):
     weights, so the result agrees with the fp32 reference to round-off (1e-5)."""
     from cudalm_c_b200 import linear
     from cudalm_c_b200._lib import KN, NK
-    for K, N in ((768, 1536), (1536, 768), (768, 16384)):
+    for K, N in ((768, 1536), (1536, 768), (768, 16384), (2048, 4096)):
         for lay in (KN, NK):
             Q, W = quantise(cuda, K, N, 5) if lay == KN else quantise(cuda, N, K, 5)
             Wm = W if lay == KN else W.T

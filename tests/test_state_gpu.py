@@ -135,6 +135,43 @@ def test_step_sharded_equals_whole(cuda):
             assert (ha[k] == hb[k]).all(), (k, t)
 
 
+def test_config3_full_size_properties(cuda):
+    """BASELINE config 3's size (125 829 120 parameters, 983 040 groups), where the CPU oracle is too
+    slow: properties that do not depend on the size.  (1) encode -> render -> encode reproduces the
+    digits and scales exactly and leaves no residual (every rendered value is digit x scale);
+    (2) two optimizer steps taken as four group ranges give the same bytes as taken whole;
+    (3) the weights written by the step kernel equal a render of the state it left."""
+    n = 125829120
+    gen = torch.Generator(device=cuda); gen.manual_seed(3)
+    a = DevState(cuda, [n], 128, 7, 1); b = DevState(cuda, [n], 128, 7, 1)
+    P0 = torch.randn(n, device=cuda, generator=gen) * 0.02
+    a.encode(P0)
+    R = torch.empty_like(P0)
+    a.q.qlm_render(R, a.d, a.s, a.spd, 1)
+    b.encode(R)
+    assert torch.equal(a.d, b.d)
+    # the re-derived scale is |max digit| x scale / 7, which is the scale again only up to one rounding
+    assert float(((a.s - b.s).abs() / a.s).max()) < 2e-7
+    assert int(b.r.abs().max()) <= 1
+    del R
+    for st in (a, b):
+        st.sp[0]["sref"] = f32(float(a.s.double().mean())); st.push_spans()
+    b.d.copy_(a.d); b.r.copy_(a.r); b.s.copy_(a.s)
+    P = torch.zeros(n, device=cuda)
+    ng = a.ng
+    cuts = [0, ng // 4 + 3, ng // 2, ng - 5, ng]
+    for t in (1, 2):
+        G = torch.randn(n, device=cuda, generator=gen) * 1e-3
+        a.step(P, G, t)
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            b.step(None, G, t, gi_base=lo, ng=hi - lo)
+        for k in ("d", "r", "m8", "v8", "m8s", "v8s"):
+            assert torch.equal(getattr(a, k), getattr(b, k)), (k, t)
+    R = torch.empty(n, device=cuda)
+    a.q.qlm_render(R, a.d, a.s, a.spd, 1)
+    assert torch.equal(R, P)
+
+
 def test_empty_and_bad_arguments(cuda):
     import cudalm_c_b200 as q
     st = DevState(cuda, [256], 128, 7, 1)
