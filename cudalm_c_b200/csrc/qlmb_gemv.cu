@@ -61,31 +61,43 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
 #pragma unroll
             for (int j = 0; j < 8; j++) acc[b][j] = 0.0f;
         if (live) {
-            for (int k = k0 + warp; k < k1; k += 64) {
-                uint32_t w[8];
-                float sc[8];
+            // four rows per batch (k, k+8, k+16, k+24); the next batch is loaded before the current one is used
+            uint32_t w[2][4];
+            float sc[2][4];
+            auto fetch = [&](int buf, int k) {
 #pragma unroll
-                for (int u = 0; u < 8; u++) {
+                for (int u = 0; u < 4; u++) {
                     const int kk = k + 8 * u;
-                    w[u] = 0u; sc[u] = 0.0f;
+                    w[buf][u] = 0u; sc[buf][u] = 0.0f;
                     if (kk < k1) {
-                        w[u] = __ldcs(reinterpret_cast<const uint32_t *>(cp + (size_t)kk * N / 2));
-                        sc[u] = __ldg(sp + (size_t)kk * gpr);
+                        w[buf][u] = __ldcs(reinterpret_cast<const uint32_t *>(cp + (size_t)kk * N / 2));
+                        sc[buf][u] = __ldg(sp + (size_t)kk * gpr);
                     }
                 }
+            };
+            auto use = [&](int buf, int k) {
 #pragma unroll
-                for (int u = 0; u < 8; u++) {
+                for (int u = 0; u < 4; u++) {
                     const int kk = k + 8 * u;
-                    if (kk >= k1) break;
-                    float d[8];
-                    unpack8(w[u], d);
+                    if (kk < k1) {
+                        float d[8];
+                        unpack8(w[buf][u], d);
 #pragma unroll
-                    for (int b = 0; b < BT; b++) {
-                        const float xv = xs[b * kslice + (kk - k0)] * sc[u];
+                        for (int b = 0; b < BT; b++) {
+                            const float xv = xs[b * kslice + (kk - k0)] * sc[buf][u];
 #pragma unroll
-                        for (int j = 0; j < 8; j++) acc[b][j] += xv * d[j];
+                            for (int j = 0; j < 8; j++) acc[b][j] += xv * d[j];
+                        }
                     }
                 }
+            };
+            int k = k0 + warp;
+            fetch(0, k);
+            for (; k < k1; k += 64) {
+                fetch(1, k + 32);
+                use(0, k);
+                fetch(0, k + 64);
+                use(1, k + 32);
             }
         }
         // fixed-order combination of the 8 warps
@@ -184,118 +196,6 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_nk(float *part, c
     }
 }
 
-// ---- one live slot, wide matrices: 16-byte code loads (32 weights per lane and load), so that a
-// warp has 2 KiB of codes in flight.  codes W[K][N]: block = 1024 columns x a K slice, warp w takes
-// rows k0+w, k0+w+8, ..., four per step.
-__global__ void __launch_bounds__(256, 3) k_gemv_kn_wide(float *part, const void *X, int dtype, const uint8_t *codes,
-                                                         const float *scales, int K, int N, int kslice)
-{
-    extern __shared__ float sm[];               // xs[kslice], then red[8][1024]
-    float *xs = sm, *red = sm + kslice;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * 1024 + lane * 32;
-    const int k0 = blockIdx.y * kslice, k1 = k0 + kslice < K ? k0 + kslice : K;
-    const int gpr = N / 128;
-    for (int i = threadIdx.x; i < kslice; i += 256) xs[i] = k0 + i < k1 ? ld_x(X, dtype, (size_t)k0 + i) : 0.0f;
-    __syncthreads();
-    float acc[32];
-#pragma unroll
-    for (int j = 0; j < 32; j++) acc[j] = 0.0f;
-    const uint8_t *cp = codes + (size_t)n0 / 2;
-    const float *sp = scales + n0 / 128;
-    for (int k = k0 + warp; k < k1; k += 32) {
-        uint4 w[4];
-        float sc[4];
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int kk = k + 8 * u;
-            w[u] = make_uint4(0, 0, 0, 0); sc[u] = 0.0f;
-            if (kk < k1) {
-                w[u] = __ldcs(reinterpret_cast<const uint4 *>(cp + (size_t)kk * N / 2));
-                sc[u] = __ldg(sp + (size_t)kk * gpr);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int kk = k + 8 * u;
-            if (kk >= k1) break;
-            const float xv = xs[kk - k0] * sc[u];
-            const uint32_t ww[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                float d[8];
-                unpack8(ww[q], d);
-#pragma unroll
-                for (int j = 0; j < 8; j++) acc[q * 8 + j] += xv * d[j];
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < 32; j++) red[warp * 1024 + lane * 32 + j] = acc[j];
-    __syncthreads();
-    for (int c = threadIdx.x; c < 1024; c += 256) {
-        float v = 0.0f;
-#pragma unroll
-        for (int w8 = 0; w8 < 8; w8++) v += red[w8 * 1024 + c];
-        const int n = blockIdx.x * 1024 + c;
-        if (n < N) part[(size_t)blockIdx.y * N + n] = v;
-    }
-}
-
-// codes W[N][K], one live slot: a warp owns 4 consecutive output columns; a lane takes 32 consecutive k
-// (one 16-byte load) of each per step.
-__global__ void __launch_bounds__(256, 3) k_gemv_nk_wide(float *part, const void *X, int dtype, const uint8_t *codes,
-                                                         const float *scales, int K, int N, int kslice)
-{
-    extern __shared__ float xs[];               // [kslice]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = (blockIdx.x * 8 + warp) * 4;
-    const int k0 = blockIdx.y * kslice, k1 = k0 + kslice < K ? k0 + kslice : K;
-    const int gpr = K / 128, nq = (k1 - k0) / 32;            // 16-byte code pieces of the slice
-    for (int i = threadIdx.x; i < kslice; i += 256) xs[i] = k0 + i < k1 ? ld_x(X, dtype, (size_t)k0 + i) : 0.0f;
-    __syncthreads();
-    if (n0 >= N) return;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int kq = lane; kq < nq; kq += 32) {
-        uint4 w[4];
-        float sc[4];
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            w[c] = make_uint4(0, 0, 0, 0); sc[c] = 0.0f;
-            if (n0 + c < N) {
-                w[c] = __ldcs(reinterpret_cast<const uint4 *>(codes + ((size_t)(n0 + c) * K + k0) / 2) + kq);
-                sc[c] = __ldg(scales + (size_t)(n0 + c) * gpr + (k0 + kq * 32) / 128);
-            }
-        }
-        float x[32];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const float4 v = *reinterpret_cast<const float4 *>(&xs[kq * 32 + j * 4]);
-            x[4 * j] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
-        }
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const uint32_t ww[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
-            float t = 0.0f;
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                float d[8];
-                unpack8(ww[q], d);
-#pragma unroll
-                for (int j = 0; j < 8; j++) t += x[q * 8 + j] * d[j];
-            }
-            acc[c] += sc[c] * t;
-        }
-    }
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        float v = acc[c];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && n0 + c < N) part[(size_t)blockIdx.y * N + n0 + c] = v;
-    }
-}
-
 // Y[b,n] = sum over K slices (ascending) of part[ks][b][n]
 __global__ void __launch_bounds__(256) k_gemv_finish(void *Y, int dtype, const float *part, int nslice, size_t BN_)
 {
@@ -329,32 +229,6 @@ extern "C" int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, con
     if (B > 4 && dtype == QLMB_BF16 && (K % 64) == 0)
         return qlmb_linear_fwd(Y, X, codes, scales, layout, B, K, N, nullptr, dtype, stream);
     const int bt = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
-    // one slot, wide matrix: the 16-byte-load kernels
-    if (B == 1 && ((uintptr_t)codes & 15) == 0 && ((layout == QLMB_KN && (N % 1024) == 0 && K >= 512) || (layout == QLMB_NK && (K % 1024) == 0 && N >= 2048))) {
-        const int nblk1 = layout == QLMB_KN ? N / 1024 : (N + 31) / 32;
-        int ns = (3 * sm_count()) / nblk1;
-        if (ns > K / 128) ns = K / 128;
-        if (ns < 1) ns = 1;
-        const int unit = layout == QLMB_KN ? 32 : 1024;              // slice granularity
-        int ksl = ((K + ns - 1) / ns + unit - 1) / unit * unit;
-        if (ksl > 8192) ksl = 8192;
-        ns = (K + ksl - 1) / ksl;
-        void *ws1 = nullptr;
-        int rc1 = workspace((size_t)ns * N * sizeof(float), &ws1);
-        if (rc1) return rc1;
-        float *part1 = (float *)ws1;
-        if (layout == QLMB_KN) {
-            const size_t sm1 = (size_t)(ksl + 8 * 1024) * sizeof(float);
-            static bool cfg1 = false;
-            if (!cfg1) { QLMB_CUDA(cudaFuncSetAttribute(k_gemv_kn_wide, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024)); cfg1 = true; }
-            k_gemv_kn_wide<<<dim3(nblk1, ns), 256, sm1, st>>>(part1, X, dtype, (const uint8_t *)codes, scales, K, N, ksl);
-        } else {
-            k_gemv_nk_wide<<<dim3(nblk1, ns), 256, (size_t)ksl * sizeof(float), st>>>(part1, X, dtype, (const uint8_t *)codes, scales, K, N, ksl);
-        }
-        k_gemv_finish<<<(unsigned)(((size_t)N + 255) / 256), 256, 0, st>>>(Y, dtype, part1, ns, (size_t)N);
-        QLMB_LAUNCH_CHECK("qlmb_gemv_decode");
-        return QLMB_OK;
-    }
     // K slices: enough blocks to fill the device once, at least 64 rows each,
     // a multiple of 8 rows, and small enough for the activation tile in shared memory
     const int nblk = layout == QLMB_KN ? (N + 255) / 256 : (N + 31) / 32;
