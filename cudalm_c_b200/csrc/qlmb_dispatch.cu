@@ -815,11 +815,19 @@ __global__ void __launch_bounds__(256) k_dyp_rows_peer(bf16 *dyp, PeerPtrs dout,
     }
 }
 
-// counts[e] = how many of the K*N slots chose expert e (integer atomics: order independent)
+// counts[e] = how many of the K*N slots chose expert e (integer atomics: order independent);
+// a block counts in shared memory first, so the global array sees E adds per block
 __global__ void __launch_bounds__(256) k_count_assign(int *counts, const int *assign, int KN, int E)
 {
-    const int i = blockIdx.x * 256 + threadIdx.x;
-    if (i < KN) { const int e = assign[i]; if ((unsigned)e < (unsigned)E) atomicAdd(&counts[e], 1); }
+    __shared__ int h[256];
+    for (int e = threadIdx.x; e < E; e += 256) h[e] = 0;
+    __syncthreads();
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < KN; i += gridDim.x * 256) {
+        const int e = assign[i];
+        if ((unsigned)e < (unsigned)E) atomicAdd(&h[e], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += 256) if (h[e]) atomicAdd(&counts[e], h[e]);
 }
 
 int gather_rows_peer(bf16 *Xp, const PeerPtrs &src, int dtype, const int *perm, const int *nrows_dev, int max_rows,
@@ -870,7 +878,9 @@ int unpermute_rows_peer(void *dfnorm, int dtype, const PeerPtrs &dXp, const int 
 int count_assign(int *counts, const int *assign, int KN, int E, cudaStream_t st)
 {
     QLMB_CUDA(cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), st));
-    k_count_assign<<<(KN + 255) / 256, 256, 0, st>>>(counts, assign, KN, E);
+    int cb = (KN + 1023) / 1024;
+    if (cb > 64) cb = 64;
+    k_count_assign<<<cb, 256, 0, st>>>(counts, assign, KN, E);
     QLMB_LAUNCH_CHECK("k_count_assign");
     return QLMB_OK;
 }
