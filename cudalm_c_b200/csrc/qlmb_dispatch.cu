@@ -733,6 +733,78 @@ __global__ void __launch_bounds__(256) k_gather_rows_peer(bf16 *Xp, PeerPtrs src
     }
 }
 
+// The same gather with bulk copies: a warp moves whole rows (D bf16) peer -> shared -> local global
+// memory, two rows in flight per warp, so NVLink sees large requests and no row passes through
+// registers.  Waits are bounded; a timeout sets the device error word and leaves.
+__device__ __forceinline__ uint32_t rk_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool rk_wait(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < (1u << 22); i++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__global__ void __launch_bounds__(256) k_gather_rows_peer_bulk(bf16 *Xp, PeerPtrs src, const int *perm, const int *nrows_dev,
+                                                               int Nh, int KN, int D, int *errword)
+{
+    extern __shared__ __align__(128) uint8_t rowbuf[];         // [8 warps][2][D * 2 bytes]
+    __shared__ __align__(8) uint64_t bars[8][2];
+    const int rows = *nrows_dev, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rb = (uint32_t)D * 2u;
+    uint8_t *buf = rowbuf + (size_t)warp * 2 * rb;
+    if (lane == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(rk_smem(&bars[warp][0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(rk_smem(&bars[warp][1])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const int stride = gridDim.x * 8;
+    int it = 0;
+    uint32_t ph[2] = {0u, 0u};
+    // issue(j, b): start fetching row j into buffer b (or nothing for a filler row)
+    auto issue = [&](int j, int b) {
+        if (lane == 0 && j < rows) {
+            const int g = perm[j];
+            if (g >= 0) {
+                // the buffer's previous store must have finished reading it
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                const int s = g / KN, n = (g % KN) % Nh;
+                const uint32_t bar = rk_smem(&bars[warp][b]);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(rb) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(rk_smem(buf + (size_t)b * rb)), "l"((const bf16 *)src.p[s] + (size_t)n * D), "r"(rb), "r"(bar) : "memory");
+            }
+        }
+    };
+    int j = blockIdx.x * 8 + warp;
+    issue(j, 0);
+    for (; j < rows; j += stride, it++) {
+        const int b = it & 1;
+        issue(j + stride, b ^ 1);
+        const int g = perm[j];
+        if (g < 0) {
+            uint4 *o = reinterpret_cast<uint4 *>(Xp + (size_t)j * D);
+            for (int c = lane; c < D / 8; c += 32) o[c] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        if (!rk_wait(rk_smem(&bars[warp][b]), ph[b])) {
+            if (lane == 0 && errword && atomicCAS(errword, 0, 210) == 0) { errword[1] = j; errword[2] = (int)blockIdx.x; }
+            break;
+        }
+        ph[b] ^= 1u;
+        if (lane == 0) {
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                         ::"l"(Xp + (size_t)j * D), "r"(rk_smem(buf + (size_t)b * rb)), "r"(rb) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        __syncwarp();
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 // home side: rowidx[slot] = row of the slot in the arena of the rank that owns its expert
 __global__ void __launch_bounds__(256) k_pull_rowidx(int *rowidx, const int *assign, PeerPtrs inv, int el, int slot0, int KN)
 {
@@ -835,6 +907,13 @@ int gather_rows_peer(bf16 *Xp, const PeerPtrs &src, int dtype, const int *perm, 
 {
     int blocks = (max_rows + 7) / 8, cap = sm_count() * 8;
     if (blocks > cap) blocks = cap;
+    static int bulk = -1;
+    if (bulk < 0) { const char *e = getenv("QLMB_PEER_BULK"); bulk = (e && atoi(e) == 0) ? 0 : 1; }
+    if (bulk && dtype == QLMB_BF16 && (D % 8) == 0 && (size_t)D * 2 * 16 <= 48 * 1024) {
+        k_gather_rows_peer_bulk<<<blocks, 256, (size_t)D * 2 * 16, st>>>(Xp, src, perm, nrows_dev, Nh, KN, D, device_error_word());
+        QLMB_LAUNCH_CHECK("k_gather_rows_peer_bulk");
+        return QLMB_OK;
+    }
     k_gather_rows_peer<<<blocks, 256, 0, st>>>(Xp, src, dtype, perm, nrows_dev, Nh, KN, D);
     QLMB_LAUNCH_CHECK("k_gather_rows_peer");
     return QLMB_OK;
