@@ -81,13 +81,12 @@ PROTOTYPES = {
     "qlmb_peer_open": (ci, [vp, C.POINTER(vp)]),
     "qlmb_peer_close": (ci, [vp]),
     "qlmb_ep_route": (ci, [C.POINTER(MoeLayer), vp, vp, vp]),
-    "qlmb_ep_experts_forward": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp, ci, ci, ci, vp]),
-    "qlmb_ep_combine": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp, vp]),
-    "qlmb_ep_dgate": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp]),
+    "qlmb_ep_experts_forward": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp, ci, ci, ci, vp, vp]),
+    "qlmb_ep_combine": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
+    "qlmb_ep_dgate": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp]),
     "qlmb_ep_experts_backward": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, ci, ci,
-                                      vp, vp, vp, cf, vp]),
-    "qlmb_ep_route_backward": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp, vp,
-                                    cf, vp]),
+                                      vp, vp, vp, vp, cf, vp]),
+    "qlmb_ep_route_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, cf, vp]),
 }
 
 _lib = None

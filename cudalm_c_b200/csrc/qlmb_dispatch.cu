@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(256) k_combine_rows(void *out, const void *f_i
             size_t slot = (size_t)k * N + n;
             float g = gate[slot];
             float y[8];
-            ld_act8(yp, QLMB_BF16, (size_t)inv[slot] * D + (size_t)c * 8, y);
+            ld_act8(yp, QLMB_BF16, (size_t)(inv ? inv[slot] : (int)slot) * D + (size_t)c * 8, y);
 #pragma unroll
             for (int i = 0; i < 8; i++) acc[i] += g * y[i];
         }
@@ -406,7 +406,7 @@ __global__ void __launch_bounds__(256, 3) k_unpermute_rows_tile(void *dfnorm, in
             int row = -1, own = 0;
             if (n < N) {
                 const size_t slot = (size_t)k * N + n;
-                row = __ldg(rows + slot);
+                row = rows ? __ldg(rows + slot) : (int)slot;
                 if (PEER) own = __ldg(assign + slot) / el;
             }
             srow[t][k] = row; sown[t][k] = own;

@@ -54,6 +54,7 @@ struct GemmParams {
     void *out; int out_dtype; long long ldo;
     const void *resid; float beta;
     bf16 *gp, *up, *ap, *dgp, *dup;
+    const int *scatter_perm; int scatter_kn; bf16 *scatter_out[8];
     int *errword;
 };
 
@@ -311,6 +312,19 @@ __device__ __forceinline__ void blk_load(uint8_t *blk, int lane, const uint8_t *
         *blk_vec(blk, r, c) = x;
     }
 }
+// the block to scattered global rows: lane r's destination row pointer (or nullptr) is `mine`
+__device__ __forceinline__ void blk_store_scattered(uint8_t *blk, int lane, bf16 *mine, int col)
+{
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int r = j * 4 + (lane >> 3), c = lane & 7;
+        const uint4 x = *blk_vec(blk, r, c);
+        bf16 *dst = reinterpret_cast<bf16 *>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(mine), r));
+        if (dst) *reinterpret_cast<uint4 *>(dst + col + c * 8) = x;
+    }
+    __syncwarp();
+}
 // The block layout is the 128-byte swizzle of a bulk tensor copy, so a staged block can leave as
 // one asynchronous store issued by lane 0.  blk_reuse() must precede the next write to the block.
 __device__ __forceinline__ void blk_store_bulk(uint8_t *blk, int lane, const CUtensorMap *map, int x, int y)
@@ -378,9 +392,14 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
     if (EPI == EPI_SWIGLU_BWD && p.o_tma) { swiglu_bwd_bulk(p, stage, ec, lane, tbase, rbase, col0); return; }
     if (EPI == EPI_STORE && p.out_dtype == QLMB_BF16 && !p.resid && p.beta == 0.0f) {
         // plain bf16 store: two blocks of 64 columns, each written with whole 128-byte rows
+        bf16 *mine = nullptr;                                // scattered form: this lane's row destination
+        if (p.scatter_perm && lane < valid) {
+            const int g = p.scatter_perm[rbase + lane];
+            if (g >= 0) mine = p.scatter_out[g / p.scatter_kn] + (size_t)(g % p.scatter_kn) * p.ldo;
+        }
 #pragma unroll 1
         for (int half = 0; half < 2; half++) {
-            if (p.o_tma) blk_reuse(lane);
+            if (p.o_tma && !p.scatter_perm) blk_reuse(lane);
 #pragma unroll 1
             for (int cc = 0; cc < 2; cc++) {
                 uint32_t v[32];
@@ -394,7 +413,8 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &p, uint8_t *stag
 #pragma unroll
                 for (int k = 0; k < 4; k++) *blk_vec(stage, lane, cc * 4 + k) = w[k];
             }
-            if (p.o_tma) blk_store_bulk(stage, lane, &p.o_map[0], (int)(col0 + half * 64), (int)rbase);
+            if (p.scatter_perm) blk_store_scattered(stage, lane, mine, (int)(col0 + half * 64));
+            else if (p.o_tma) blk_store_bulk(stage, lane, &p.o_map[0], (int)(col0 + half * 64), (int)rbase);
             else blk_store(stage, lane, reinterpret_cast<uint8_t *>((bf16 *)p.out + rbase * p.ldo + col0 + half * 64), p.ldo * 2, valid);
         }
     } else if ((EPI == EPI_STORE || EPI == EPI_ACCUM) && p.out_dtype == QLMB_F32 && p.o_tma) {
@@ -1042,6 +1062,8 @@ int gemm_launch(const GemmLaunch &g, cudaStream_t st)
     p.out = g.out; p.out_dtype = g.out_dtype; p.ldo = g.ldo; p.resid = g.resid; p.beta = g.beta;
     p.gp = g.gp; p.up = g.up; p.ap = g.ap; p.dgp = g.dgp; p.dup = g.dup;
     p.errword = device_error_word();
+    p.scatter_perm = g.scatter_perm; p.scatter_kn = g.scatter_kn;
+    for (int i = 0; i < 8; i++) p.scatter_out[i] = (bf16 *)g.scatter_out[i];
     p.scales[0] = g.scales[0]; p.scales[1] = g.scales[1];
     const unsigned long long wrows_total = (unsigned long long)g.E * g.w_rows;
     for (int s = 0; s < (dual ? 2 : g.nseg); s++) {

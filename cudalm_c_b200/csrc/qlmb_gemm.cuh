@@ -44,6 +44,10 @@ struct GemmLaunch {
     void *out; int out_dtype; long long ldo;
     const void *resid; float beta;
     bf16 *gp, *up, *ap, *dgp, *dup;
+    // bf16 EPI_STORE only: rows leave to where they came from instead of to `out` -- output row j goes to
+    // row (scatter_perm[j] % scatter_kn) of the buffer scatter_out[scatter_perm[j] / scatter_kn] (one per
+    // rank, possibly peer-mapped); rows with scatter_perm[j] < 0 are not written
+    const int *scatter_perm; int scatter_kn; const void *scatter_out[8];
     const char *name;              // label for the optional per-kernel timing
 };
 

@@ -83,8 +83,12 @@ static int check_layer(const char *who, const qlmb_moe_layer *L, bool need_exper
     return QLMB_OK;
 }
 
+// Where the rows of an expert-side GEMM output go when they belong to other ranks: row j to row
+// (perm[j] % kn) of out[perm[j] / kn] (see GemmLaunch::scatter_perm).  perm == nullptr: the arena.
+struct Scatter { const int *perm; int kn; const void *out[8]; };
+
 // gate/up (+SwiGLU) and down projections over the expert-grouped rows of `a` (cudalm.cu:4211-4225)
-static int experts_forward_gemms(const qlmb_moe_layer *L, const Arena &a, cudaStream_t st)
+static int experts_forward_gemms(const qlmb_moe_layer *L, const Arena &a, cudaStream_t st, const Scatter *sc = nullptr)
 {
     const int D = L->D, F = L->F, E = L->E, R = (int)a.rows_cap;
     int rc;
@@ -103,6 +107,7 @@ static int experts_forward_gemms(const qlmb_moe_layer *L, const Arena &a, cudaSt
     h.w_rows = F; h.w_cols = D; h.nseg = 1; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
     h.tile_info = a.tile_info; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 256 + E / 2 + 1;
     h.out = a.yp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_down";
+    if (sc && sc->perm) { h.scatter_perm = sc->perm; h.scatter_kn = sc->kn; for (int i = 0; i < 8; i++) h.scatter_out[i] = sc->out[i]; }
     return gemm_launch(h, st);
 }
 
@@ -111,7 +116,7 @@ static int experts_forward_gemms(const qlmb_moe_layer *L, const Arena &a, cudaSt
 // call, dW1/dW3 need d(act)'s outputs; their tiles fill the SMs that the last, partial wave of
 // d(act) and dXp leaves idle.  Everything is joined back into `st` before returning.
 static int experts_backward_gemms(const qlmb_moe_layer *L, const Arena &a, float *dW1, float *dW3, float *dW2,
-                                  float beta, cudaStream_t st)
+                                  float beta, cudaStream_t st, const Scatter *sc = nullptr)
 {
     const int D = L->D, F = L->F, E = L->E, R = (int)a.rows_cap;
     int rc;
@@ -144,6 +149,7 @@ static int experts_backward_gemms(const qlmb_moe_layer *L, const Arena &a, float
     h.w_rows = D; h.w_cols = F; h.nseg = 2; h.ksteps = F / 64; h.M = R; h.N = D; h.E = E;
     h.tile_info = a.tile_info; h.ntiles_dev = a.ntiles; h.max_row_tiles = R / 256 + E / 2 + 1;
     h.out = a.dXp; h.out_dtype = QLMB_BF16; h.ldo = D; h.name = "gemm_dx";
+    if (sc && sc->perm) { h.scatter_perm = sc->perm; h.scatter_kn = sc->kn; for (int i = 0; i < 8; i++) h.scatter_out[i] = sc->out[i]; }
     rc = gemm_launch(h, st);
     if (!rc) rc = wgrad(1, side);
     if (!rc) rc = wgrad(2, side);
@@ -397,12 +403,12 @@ extern "C" int qlmb_ep_route(const qlmb_moe_layer *L, void *harena, const void *
 
 extern "C" int qlmb_ep_experts_forward(const qlmb_moe_layer *L, void *earena, const qlmb_ep_peers *P,
                                        const int *assign_all, const void *f_norm, int x_dtype, int tokens_per_rank,
-                                       int K, void *stream)
+                                       int K, void *Ys, void *stream)
 {
     int rc = check_layer("qlmb_ep_experts_forward", L, true, false);
     if (rc) return rc;
     if ((rc = check_peers("qlmb_ep_experts_forward", P))) return rc;
-    QLMB_REQUIRE(earena && assign_all && f_norm, "qlmb_ep_experts_forward: NULL argument");
+    QLMB_REQUIRE(earena && assign_all && f_norm && Ys, "qlmb_ep_experts_forward: NULL argument");
     QLMB_REQUIRE(x_dtype == QLMB_F32 || x_dtype == QLMB_BF16, "qlmb_ep_experts_forward: dtype %d", x_dtype);
     QLMB_REQUIRE(tokens_per_rank > 0 && K > 0 && L->N == P->world * K * tokens_per_rank,
                  "qlmb_ep_experts_forward: arena holds %d slots, need %d", L->N, P->world * K * tokens_per_rank);
@@ -414,49 +420,44 @@ extern "C" int qlmb_ep_experts_forward(const qlmb_moe_layer *L, void *earena, co
                            a.chunk, st, P->rank * E, 1))) return rc; }
     { ProfScope ps("gather_rows_peer", st);
       if ((rc = gather_rows_peer(a.Xp, peer_view(P, f_norm), x_dtype, a.perm, a.off + E, (int)a.rows_cap, tokens_per_rank, KN, D, st))) return rc; }
-    return experts_forward_gemms(L, a, st);
+    // the down projection's epilogue writes every output row straight into the Ys buffer of the
+    // row's home rank, at the row's slot
+    Scatter sc;
+    sc.perm = a.perm; sc.kn = KN;
+    PeerPtrs yv = peer_view(P, Ys);
+    for (int i = 0; i < 8; i++) sc.out[i] = i < P->world ? yv.p[i] : nullptr;
+    return experts_forward_gemms(L, a, st, &sc);
 }
 
-extern "C" int qlmb_ep_combine(const qlmb_moe_layer *H, void *harena, const qlmb_moe_layer *L, void *earena,
-                               const qlmb_ep_peers *P, void *out, const void *f_in, void *stream)
+extern "C" int qlmb_ep_combine(const qlmb_moe_layer *H, void *harena, const void *Ys, void *out, const void *f_in,
+                               void *stream)
 {
     int rc = check_layer("qlmb_ep_combine", H, false, false);
     if (rc) return rc;
-    if ((rc = check_peers("qlmb_ep_combine", P))) return rc;
-    QLMB_REQUIRE(L && harena && earena && out && f_in, "qlmb_ep_combine: NULL argument");
-    if ((rc = check_ep_shapes("qlmb_ep_combine", H, L, P))) return rc;
+    QLMB_REQUIRE(harena && Ys && out && f_in, "qlmb_ep_combine: NULL argument");
     Arena h = carve(harena, H->N, H->D, H->F, H->E, H->K);
-    Arena e = carve(earena, L->N, L->D, L->F, L->E, 1);
-    cudaStream_t st = as_stream(stream);
-    const int KN = H->K * H->N;
-    { ProfScope ps("pull_rowidx", st);
-      if ((rc = pull_rowidx(h.inv, h.assign, peer_view(P, e.inv), L->E, P->rank * KN, KN, st))) return rc; }
-    ProfScope ps("combine_rows_peer", st);
-    return combine_rows_peer(out, f_in, H->dtype, peer_view(P, e.yp), h.assign, h.inv, h.gate, h.yp, H->N, H->D, H->K, L->E, st);
+    ProfScope ps("combine_rows", as_stream(stream));
+    return combine_rows(out, f_in, H->dtype, (const bf16 *)Ys, nullptr, h.gate, H->N, H->D, H->K, as_stream(stream));
 }
 
-extern "C" int qlmb_ep_dgate(const qlmb_moe_layer *H, void *harena, const qlmb_moe_layer *L, void *earena,
-                             const qlmb_ep_peers *P, const void *dout, void *stream)
+extern "C" int qlmb_ep_dgate(const qlmb_moe_layer *H, void *harena, const void *Ys, const void *dout, void *stream)
 {
     int rc = check_layer("qlmb_ep_dgate", H, false, false);
     if (rc) return rc;
-    if ((rc = check_peers("qlmb_ep_dgate", P))) return rc;
-    QLMB_REQUIRE(L && harena && earena && dout, "qlmb_ep_dgate: NULL argument");
-    if ((rc = check_ep_shapes("qlmb_ep_dgate", H, L, P))) return rc;
+    QLMB_REQUIRE(harena && Ys && dout, "qlmb_ep_dgate: NULL argument");
     Arena h = carve(harena, H->N, H->D, H->F, H->E, H->K);
-    Arena e = carve(earena, L->N, L->D, L->F, L->E, 1);
-    ProfScope ps("dgate_dot_peer", as_stream(stream));
-    return dgate_dot_peer(h.d_gate, dout, H->dtype, h.yp, H->N, H->D, H->K, as_stream(stream));
+    ProfScope ps("dgate_dot", as_stream(stream));
+    return dgate_dot_peer(h.d_gate, dout, H->dtype, (const bf16 *)Ys, H->N, H->D, H->K, as_stream(stream));
 }
 
 extern "C" int qlmb_ep_experts_backward(const qlmb_moe_layer *L, void *earena, const qlmb_moe_layer *H, void *harena,
                                         const qlmb_ep_peers *P, const void *dout, int tokens_per_rank, int K,
-                                        float *dW1, float *dW3, float *dW2, float beta, void *stream)
+                                        void *dXs, float *dW1, float *dW3, float *dW2, float beta, void *stream)
 {
     int rc = check_layer("qlmb_ep_experts_backward", L, true, false);
     if (rc) return rc;
     if ((rc = check_peers("qlmb_ep_experts_backward", P))) return rc;
-    QLMB_REQUIRE(H && earena && harena && dout && dW1 && dW3 && dW2, "qlmb_ep_experts_backward: NULL argument");
+    QLMB_REQUIRE(H && earena && harena && dout && dXs && dW1 && dW3 && dW2, "qlmb_ep_experts_backward: NULL argument");
     QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_ep_experts_backward: beta %g", beta);
     if ((rc = check_ep_shapes("qlmb_ep_experts_backward", H, L, P))) return rc;
     QLMB_REQUIRE(tokens_per_rank == H->N && K == H->K, "qlmb_ep_experts_backward: tokens_per_rank / K differ from the router view");
@@ -466,29 +467,29 @@ extern "C" int qlmb_ep_experts_backward(const qlmb_moe_layer *L, void *earena, c
     { ProfScope ps("dyp_rows_peer", st);
       if ((rc = dyp_rows_peer(e.dyp, peer_view(P, dout), peer_view(P, h.gate), H->dtype, e.perm, e.off + L->E, (int)e.rows_cap,
                               tokens_per_rank, K * tokens_per_rank, L->D, st))) return rc; }
-    return experts_backward_gemms(L, e, dW1, dW3, dW2, beta, st);
+    Scatter sc;                                          // dX rows go straight to their home rank's dXs buffer
+    sc.perm = e.perm; sc.kn = K * tokens_per_rank;
+    PeerPtrs xv = peer_view(P, dXs);
+    for (int i = 0; i < 8; i++) sc.out[i] = i < P->world ? xv.p[i] : nullptr;
+    return experts_backward_gemms(L, e, dW1, dW3, dW2, beta, st, &sc);
 }
 
-extern "C" int qlmb_ep_route_backward(const qlmb_moe_layer *H, void *harena, const qlmb_moe_layer *L, void *earena,
-                                      const qlmb_ep_peers *P, void *dfnorm, const void *f_norm, float *dWr, float beta,
-                                      void *stream)
+extern "C" int qlmb_ep_route_backward(const qlmb_moe_layer *H, void *harena, const void *dXs, void *dfnorm,
+                                      const void *f_norm, float *dWr, float beta, void *stream)
 {
     int rc = check_layer("qlmb_ep_route_backward", H, false, true);
     if (rc) return rc;
-    if ((rc = check_peers("qlmb_ep_route_backward", P))) return rc;
-    QLMB_REQUIRE(L && harena && earena && dfnorm && f_norm && dWr, "qlmb_ep_route_backward: NULL argument");
+    QLMB_REQUIRE(harena && dXs && dfnorm && f_norm && dWr, "qlmb_ep_route_backward: NULL argument");
     QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_ep_route_backward: beta %g", beta);
-    QLMB_REQUIRE(H->E <= 32 && (H->D % 8) == 0, "qlmb_ep_route_backward: needs E <= 32 and D a multiple of 8");
-    if ((rc = check_ep_shapes("qlmb_ep_route_backward", H, L, P))) return rc;
     const int N = H->N, D = H->D, E = H->E, K = H->K;
     Arena h = carve(harena, N, D, H->F, E, K);
-    Arena e = carve(earena, L->N, L->D, L->F, L->E, 1);
     cudaStream_t st = as_stream(stream);
     { ProfScope ps("router_bwd", st); if ((rc = router_bwd(h.drt, h.rprobs, h.assign, h.d_gate, h.counts, N, E, K, H->aux, st))) return rc; }
     cudaStream_t side = side_fork(st, 1);
     { ProfScope ps("router_wgrad", side); rc = router_wgrad(dWr, f_norm, H->dtype, h.drt, h.wr_scratch, N, D, E, beta, side); }
-    if (!rc) { ProfScope ps("unpermute_rows_peer", st);
-               rc = unpermute_rows_peer(dfnorm, H->dtype, peer_view(P, e.dXp), h.assign, h.inv, L->E, h.drt, H->wr, h.wrt, N, D, E, K, st); }
+    // dXs is in slot order (k*N + n): no row index needed
+    if (!rc) { ProfScope ps("unpermute_rows", st);
+               rc = unpermute_rows(dfnorm, H->dtype, (const bf16 *)dXs, nullptr, h.drt, H->wr, h.wrt, N, D, E, K, st); }
     side_join(side, st);
     return rc;
 }

@@ -156,14 +156,15 @@ class _DeviceWindow:
 
 
 class PeerExpertParallelLayer:
-    """The same layer with no exchange step: foreign rows are read through peer-mapped pointers
-    inside the library's row kernels (include/qlm_b200.h, qlmb_ep_*).  Every rank owns one window
+    """The same layer with no exchange step: rows cross NVLink inside kernels that exist anyway -- the
+    expert side's gathers read foreign rows through peer-mapped pointers, the epilogues of its down
+    and dX GEMMs store result rows straight into their home rank's buffers (include/qlm_b200.h, qlmb_ep_*).  Every rank owns one window
     of device memory (token inputs, router-side arena, expert-side arena) with the same layout;
     the ranks of the node map each other's windows once at construction.  Per step the ranks
     exchange only the routing table (one fixed-size all-gather) and two one-element all-reduces
     that act as stream-ordered barriers; nothing waits on the host."""
 
-    launches_per_step = 23          # library kernels per forward+backward on a rank
+    launches_per_step = 22          # library kernels per forward+backward on a rank
 
     def __init__(self, cfg, dev, rank, world, seed=1234, aux=0.03, group=None, weights=None):
         import ctypes as C
@@ -193,7 +194,10 @@ class PeerExpertParallelLayer:
         row_bytes = al(N * D * 2)
         self.off_fn = [0, row_bytes]
         self.off_dout = [2 * row_bytes, 3 * row_bytes]
-        self.off_h = 4 * row_bytes
+        slot_bytes = al(K * N * D * 2)
+        self.off_ys = 4 * row_bytes
+        self.off_dxs = self.off_ys + slot_bytes
+        self.off_h = self.off_dxs + slot_bytes
         self.off_e = self.off_h + al(hb)
         self.win_bytes = self.off_e + al(eb)
         p = C.c_void_p()
@@ -229,6 +233,8 @@ class PeerExpertParallelLayer:
         def view(off, shape, dtype):
             n = int(np.prod(shape)) * torch.empty(0, dtype=dtype).element_size()
             return self.win[off:off + n].view(dtype).view(*shape)
+        self.Ys = view(self.off_ys, (K * N, D), bf)
+        self.dXs = view(self.off_dxs, (K * N, D), bf)
         self.fn_set = [view(o, (N, D), bf) for o in self.off_fn]
         self.dout_set = [view(o, (N, D), bf) for o in self.off_dout]
         self.home = MoeLayer(N, D, F, E, K, BF16, None, None, None, None, None, None, ptr(self.wr), None, 0, aux)
@@ -264,9 +270,10 @@ class PeerExpertParallelLayer:
             dist.all_gather_into_tensor(self.assign_all.view(-1), self.assign, group=self.group)
         else:
             self.assign_all.view(-1).copy_(self.assign)
-        check(L.qlmb_ep_experts_forward(self.loc, self.eptr, self.peers, ptr(self.assign_all), ptr(fn), BF16, self.N, self.K, st))
+        check(L.qlmb_ep_experts_forward(self.loc, self.eptr, self.peers, ptr(self.assign_all), ptr(fn), BF16, self.N, self.K,
+                                        ptr(self.Ys), st))
         self._barrier()
-        check(L.qlmb_ep_combine(self.home, self.hptr, self.loc, self.eptr, self.peers, ptr(out), ptr(fi), st))
+        check(L.qlmb_ep_combine(self.home, self.hptr, ptr(self.Ys), ptr(out), ptr(fi), st))
         return out
 
     def backward(self, dout=None, fn=None, beta=0.0, dfn=None):
@@ -275,12 +282,11 @@ class PeerExpertParallelLayer:
         fn = self.fn if fn is None else fn
         dfn = self.dfn if dfn is None else dfn
         L, st = lib(), stream_ptr()
-        check(L.qlmb_ep_dgate(self.home, self.hptr, self.loc, self.eptr, self.peers, ptr(dout), st))
+        check(L.qlmb_ep_dgate(self.home, self.hptr, ptr(self.Ys), ptr(dout), st))
         check(L.qlmb_ep_experts_backward(self.loc, self.eptr, self.home, self.hptr, self.peers, ptr(dout), self.N, self.K,
-                                         ptr(self.dW[0]), ptr(self.dW[1]), ptr(self.dW[2]), beta, st))
+                                         ptr(self.dXs), ptr(self.dW[0]), ptr(self.dW[1]), ptr(self.dW[2]), beta, st))
         self._barrier()
-        check(L.qlmb_ep_route_backward(self.home, self.hptr, self.loc, self.eptr, self.peers, ptr(dfn), ptr(fn), ptr(self.dWr),
-                                       beta, st))
+        check(L.qlmb_ep_route_backward(self.home, self.hptr, ptr(self.dXs), ptr(dfn), ptr(fn), ptr(self.dWr), beta, st))
         return dfn
 
     def step(self):

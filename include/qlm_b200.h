@@ -259,29 +259,32 @@ int qlmb_statefile_write(const char *path, const qlmb_statefile *v);
 int qlmb_statefile_read_header(const char *path, qlmb_statefile *v);
 int qlmb_statefile_read(const char *path, qlmb_statefile *v);
 
-/* ------------------------------- expert parallelism by peer loads (new, no reference counterpart)
+/* ------------------------- expert parallelism over peer memory (new, no reference counterpart)
  * Same cut of moe_forward / moe_backward (cudalm.cu:4151-4393), but rows never travel in a
- * separate exchange: every rank places its inputs and both arenas in one "window" of device
- * memory that the other ranks of the node map (qlmb_peer_*), all windows have the same layout,
- * and the row kernels read foreign rows through the mapped pointers (plain loads over NVLink).
+ * separate exchange: every rank places its inputs, its Ys / dXs buffers and both arenas in one
+ * "window" of device memory that the other ranks of the node map (qlmb_peer_*), all windows have
+ * the same layout, and rows cross NVLink inside kernels that exist anyway: the expert side's
+ * gather reads token rows (and, in the backward, dout rows and gates) from their home rank with
+ * peer loads; the epilogues of its down-projection and dX GEMMs store every output row straight
+ * into the Ys / dXs buffer of the row's home rank, at the row's slot k*N + n.
  * The caller provides the stream-ordered synchronisation between the calls with collectives of
  * its own (no kernel of this library waits for another GPU):
  *   qlmb_ep_route            every rank
  *   all-gather of arena member "assign" ([K*N] ints per rank) into assign_all[W][K*N]
- *   qlmb_ep_experts_forward  every rank, for the experts it holds
+ *   qlmb_ep_experts_forward  every rank, for the experts it holds; fills the Ys of all ranks
  *   barrier
  *   qlmb_ep_combine          (forward done)
  *   qlmb_ep_dgate
- *   qlmb_ep_experts_backward
+ *   qlmb_ep_experts_backward fills the dXs of all ranks
  *   barrier
  *   qlmb_ep_route_backward
- * The all-gather of the next step is the barrier that protects the arenas from being
+ * The all-gather of the next step is the barrier that protects Ys, dXs and the arenas from being
  * overwritten while a slower rank still reads them.  Global slot g = s*K*N + k*N + n is copy k
  * of token n of rank s.  `home` describes the router side (N tokens of this rank, E experts in
  * total, K, wr); `loc` the expert side (E = experts held by this rank, rank r holds experts
  * [r*E_loc, (r+1)*E_loc), N = W*K*N_home slots, the capacity of `earena` =
- * qlmb_moe_arena_bytes(loc->N, D, F, loc->E, 1)).  Pointers named f_norm / dout / harena /
- * earena must lie inside this rank's window; the same offsets are read in the peers' windows. */
+ * qlmb_moe_arena_bytes(loc->N, D, F, loc->E, 1)).  f_norm, dout, Ys, dXs (bf16 [K*N][D] each),
+ * harena and earena must lie inside this rank's window; the same offsets are used in the peers'. */
 #define QLMB_EP_MAX_WORLD 8
 typedef struct qlmb_ep_peers {
     int rank, world;
@@ -298,17 +301,15 @@ int qlmb_peer_close(void *ptr);
 int qlmb_ep_route(const qlmb_moe_layer *home, void *harena, const void *f_norm, void *stream);
 int qlmb_ep_experts_forward(const qlmb_moe_layer *loc, void *earena, const qlmb_ep_peers *peers,
                             const int *assign_all, const void *f_norm, int x_dtype, int tokens_per_rank,
-                            int K, void *stream);
-int qlmb_ep_combine(const qlmb_moe_layer *home, void *harena, const qlmb_moe_layer *loc, void *earena,
-                    const qlmb_ep_peers *peers, void *out, const void *f_in, void *stream);
-int qlmb_ep_dgate(const qlmb_moe_layer *home, void *harena, const qlmb_moe_layer *loc, void *earena,
-                  const qlmb_ep_peers *peers, const void *dout, void *stream);
+                            int K, void *Ys, void *stream);
+int qlmb_ep_combine(const qlmb_moe_layer *home, void *harena, const void *Ys, void *out, const void *f_in,
+                    void *stream);
+int qlmb_ep_dgate(const qlmb_moe_layer *home, void *harena, const void *Ys, const void *dout, void *stream);
 int qlmb_ep_experts_backward(const qlmb_moe_layer *loc, void *earena, const qlmb_moe_layer *home,
                              void *harena, const qlmb_ep_peers *peers, const void *dout, int tokens_per_rank,
-                             int K, float *dW1, float *dW3, float *dW2, float beta, void *stream);
-int qlmb_ep_route_backward(const qlmb_moe_layer *home, void *harena, const qlmb_moe_layer *loc, void *earena,
-                           const qlmb_ep_peers *peers, void *dfnorm, const void *f_norm, float *dWr,
-                           float beta, void *stream);
+                             int K, void *dXs, float *dW1, float *dW3, float *dW2, float beta, void *stream);
+int qlmb_ep_route_backward(const qlmb_moe_layer *home, void *harena, const void *dXs, void *dfnorm,
+                           const void *f_norm, float *dWr, float beta, void *stream);
 
 #ifdef __cplusplus
 }
