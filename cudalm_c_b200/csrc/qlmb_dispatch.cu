@@ -805,42 +805,6 @@ __global__ void __launch_bounds__(256) k_gather_rows_peer_bulk(bf16 *Xp, PeerPtr
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
-// home side: rowidx[slot] = row of the slot in the arena of the rank that owns its expert
-__global__ void __launch_bounds__(256) k_pull_rowidx(int *rowidx, const int *assign, PeerPtrs inv, int el, int slot0, int KN)
-{
-    const int i = blockIdx.x * 256 + threadIdx.x;
-    if (i >= KN) return;
-    const int re = assign[i] / el;
-    rowidx[i] = ((const int *)inv.p[re])[(size_t)slot0 + i];
-}
-
-// home side: out[n] = f_in[n] + sum_k gate[k,n] * yp_{owner}[rowidx[k,n]], k ascending
-// (ykeep[slot] keeps a local copy of every fetched row for the backward's gate gradient)
-__global__ void __launch_bounds__(256) k_combine_rows_peer(void *out, const void *f_in, int dtype, PeerPtrs yp,
-                                                           const int *assign, const int *rowidx, const float *gate,
-                                                           bf16 *ykeep, int N, int D, int K, int el)
-{
-    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (n >= N) return;
-    for (int c = lane; c < D / 8; c += 32) {
-        float acc[8];
-        ld_act8(f_in, dtype, (size_t)n * D + (size_t)c * 8, acc);
-        for (int k = 0; k < K; k++) {
-            const size_t slot = (size_t)k * N + n;
-            const float g = gate[slot];
-            float y[8];
-            const uint4 q = *reinterpret_cast<const uint4 *>((const bf16 *)yp.p[assign[slot] / el] + (size_t)rowidx[slot] * D + (size_t)c * 8);
-            *reinterpret_cast<uint4 *>(ykeep + slot * D + (size_t)c * 8) = q;
-            const __nv_bfloat162 *hq = reinterpret_cast<const __nv_bfloat162 *>(&q);
-#pragma unroll
-            for (int i = 0; i < 4; i++) { float2 f = __bfloat1622float2(hq[i]); y[2 * i] = f.x; y[2 * i + 1] = f.y; }
-#pragma unroll
-            for (int i = 0; i < 8; i++) acc[i] += g * y[i];
-        }
-        st_act8(out, dtype, (size_t)n * D + (size_t)c * 8, acc);
-    }
-}
-
 // home side: d_gate[slot] = dout[n] . y[slot], y = the row copies kept by the combine (one warp per slot)
 __global__ void __launch_bounds__(256) k_dgate_dot_peer(float *d_gate, const void *dout, int dtype, const bf16 *ykeep,
                                                         int N, int D, int KN)
@@ -918,19 +882,6 @@ int gather_rows_peer(bf16 *Xp, const PeerPtrs &src, int dtype, const int *perm, 
     QLMB_LAUNCH_CHECK("k_gather_rows_peer");
     return QLMB_OK;
 }
-int pull_rowidx(int *rowidx, const int *assign, const PeerPtrs &inv, int el, int slot0, int KN, cudaStream_t st)
-{
-    k_pull_rowidx<<<(KN + 255) / 256, 256, 0, st>>>(rowidx, assign, inv, el, slot0, KN);
-    QLMB_LAUNCH_CHECK("k_pull_rowidx");
-    return QLMB_OK;
-}
-int combine_rows_peer(void *out, const void *f_in, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
-                      const float *gate, bf16 *ykeep, int N, int D, int K, int el, cudaStream_t st)
-{
-    k_combine_rows_peer<<<(N + 7) / 8, 256, 0, st>>>(out, f_in, dtype, yp, assign, rowidx, gate, ykeep, N, D, K, el);
-    QLMB_LAUNCH_CHECK("k_combine_rows_peer");
-    return QLMB_OK;
-}
 int dgate_dot_peer(float *d_gate, const void *dout, int dtype, const bf16 *ykeep, int N, int D, int K, cudaStream_t st)
 {
     k_dgate_dot_peer<<<(K * N + 7) / 8, 256, 0, st>>>(d_gate, dout, dtype, ykeep, N, D, K * N);
@@ -944,14 +895,6 @@ int dyp_rows_peer(bf16 *dyp, const PeerPtrs &dout, const PeerPtrs &gate, int dty
     if (blocks > cap) blocks = cap;
     k_dyp_rows_peer<<<blocks, 256, 0, st>>>(dyp, dout, gate, dtype, perm, nrows_dev, Nh, KN, D);
     QLMB_LAUNCH_CHECK("k_dyp_rows_peer");
-    return QLMB_OK;
-}
-int unpermute_rows_peer(void *dfnorm, int dtype, const PeerPtrs &dXp, const int *assign, const int *rowidx, int el,
-                        const float *drt, const float *Wr, float *wrt_scratch, int N, int D, int E, int K, cudaStream_t st)
-{
-    k_transpose_wr<<<(D * E + 255) / 256, 256, 0, st>>>(wrt_scratch, Wr, D, E);
-    k_unpermute_rows_tile<true><<<unpermute_grid(N, D), 256, 0, st>>>(dfnorm, dtype, nullptr, dXp, rowidx, assign, el, drt, wrt_scratch, N, D, E, K);
-    QLMB_LAUNCH_CHECK("k_unpermute_rows_tile_peer");
     return QLMB_OK;
 }
 int count_assign(int *counts, const int *assign, int KN, int E, cudaStream_t st)

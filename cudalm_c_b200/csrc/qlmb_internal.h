@@ -47,14 +47,9 @@ int router_wgrad(float *dWr, const void *fnorm, int dtype, const float *drt, flo
 struct PeerPtrs { const void *p[QLMB_EP_MAX_WORLD]; };   // the same buffer in every rank's window
 int gather_rows_peer(bf16 *Xp, const PeerPtrs &src, int dtype, const int *perm, const int *nrows_dev, int max_rows,
                      int Nh, int KN, int D, cudaStream_t st);
-int pull_rowidx(int *rowidx, const int *assign, const PeerPtrs &inv, int el, int slot0, int KN, cudaStream_t st);
-int combine_rows_peer(void *out, const void *f_in, int dtype, const PeerPtrs &yp, const int *assign, const int *rowidx,
-                      const float *gate, bf16 *ykeep, int N, int D, int K, int el, cudaStream_t st);
 int dgate_dot_peer(float *d_gate, const void *dout, int dtype, const bf16 *ykeep, int N, int D, int K, cudaStream_t st);
 int dyp_rows_peer(bf16 *dyp, const PeerPtrs &dout, const PeerPtrs &gate, int dtype, const int *perm, const int *nrows_dev,
                   int max_rows, int Nh, int KN, int D, cudaStream_t st);
-int unpermute_rows_peer(void *dfnorm, int dtype, const PeerPtrs &dXp, const int *assign, const int *rowidx, int el,
-                        const float *drt, const float *Wr, float *wrt_scratch, int N, int D, int E, int K, cudaStream_t st);
 int count_assign(int *counts, const int *assign, int KN, int E, cudaStream_t st);
 // fp32 <-> bf16 row conversion helpers
 int convert_f32_to_bf16(bf16 *dst, const float *src, size_t n, cudaStream_t st);
