@@ -431,6 +431,26 @@ __global__ void k_gnorm_final(const double *sub, int nside, int clip_side, float
     gs[1] = gn;
 }
 
+// The fused per-layer update (reference qlm_fused_layer / qlm_fused_tail, cudalm.cu:6105-6187)
+// keeps one slice of 64 float partial sums per layer and closes the norm once per step.
+__global__ void k_sq_fold(const double *sub, float *part64)
+{
+    const int c = threadIdx.x;
+    double t = 0.0;
+    for (int b = 0; b < GN_SUB; b++) t += sub[(size_t)c * GN_SUB + b];
+    part64[c] = (float)t;
+}
+// Close-out: all partials added in ascending order in double, as the reference's host loop does
+// (cudalm.cu:6182-6186); one thread, a few thousand additions once per step.
+__global__ void k_gnorm_close(const float *part, int n, float *gs)
+{
+    double ss = 0.0;
+    for (int i = 0; i < n; i++) ss += (double)part[i];
+    const float gn = (float)sqrt(ss);
+    gs[0] = gn > 1.0f ? 1.0f / gn : 1.0f;
+    gs[1] = gn;
+}
+
 // ------------------------------------------------------ float-span AdamW
 __device__ __forceinline__ float bf_to_f(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 __device__ __forceinline__ uint16_t f_to_bf(float f)
@@ -613,5 +633,35 @@ extern "C" int qlmb_gnorm_noalloc(const float *G, size_t n, const float *const *
         k_sq_partial<<<dim3(GN_SUB, 64), 256, 0, st>>>(side[i], side_n[i], sub + (size_t)64 * GN_SUB * (1 + i));
     k_gnorm_final<<<1, 1, 0, st>>>(sub, nside, clip_side, gs);
     QLMB_LAUNCH_CHECK("qlmb_gnorm_noalloc");
+    return QLMB_OK;
+}
+
+// ------------------------------------------------- fused per-layer update: the norm in slices
+static __device__ __align__(256) double g_sqsum_static_partials[64 * GN_SUB];
+static double *g_sqsum_static_addr[64];
+
+extern "C" int qlmb_sqsum(const float *G, size_t n, float *part64, void *stream)
+{
+    QLMB_REQUIRE(G && part64, "qlmb_sqsum: NULL argument");
+    int dev = 0;
+    QLMB_CUDA(cudaGetDevice(&dev));
+    QLMB_REQUIRE(dev >= 0 && dev < 64, "qlmb_sqsum: device index %d", dev);
+    if (!g_sqsum_static_addr[dev]) {
+        double *p = nullptr;
+        QLMB_CUDA(cudaGetSymbolAddress((void **)&p, g_sqsum_static_partials));
+        g_sqsum_static_addr[dev] = p;
+    }
+    cudaStream_t st = as_stream(stream);
+    k_sq_partial<<<dim3(GN_SUB, 64), 256, 0, st>>>(G, n, g_sqsum_static_addr[dev]);
+    k_sq_fold<<<1, 64, 0, st>>>(g_sqsum_static_addr[dev], part64);
+    QLMB_LAUNCH_CHECK("qlmb_sqsum");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_gnorm_close(const float *part, int nslice, float *gs, void *stream)
+{
+    QLMB_REQUIRE(part && gs && nslice > 0, "qlmb_gnorm_close: bad argument");
+    k_gnorm_close<<<1, 1, 0, as_stream(stream)>>>(part, 64 * nslice, gs);
+    QLMB_LAUNCH_CHECK("qlmb_gnorm_close");
     return QLMB_OK;
 }

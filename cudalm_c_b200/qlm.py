@@ -65,6 +65,16 @@ def adamw(P, G, M, V, lr, b1, b2, wd, bc1, bc2, gs=None):
                            stream_ptr()))
 
 
+def sqsum(G, part64):
+    """k_sqsum into a caller-owned slice of 64 floats (qlm_fused_layer, cudalm.cu:6122)."""
+    check(lib().qlmb_sqsum(ptr(G), G.numel(), ptr(part64), stream_ptr()))
+
+
+def gnorm_close(part, nslice, gs):
+    """The norm of all slices -> gs[0] = next step's clip multiplier, gs[1] = norm (cudalm.cu:6182-6186)."""
+    check(lib().qlmb_gnorm_close(ptr(part), nslice, ptr(gs), stream_ptr()))
+
+
 def bias_corrections(b1, b2, t):
     """(bc1, bc2) in fp32 as gpu_adam derives them with powf (cudalm.cu:6454)."""
     f = np.float32
@@ -207,3 +217,60 @@ class Qlm:
         """qlm_persist_bytes (qlm.cuh:678-683)."""
         return (qd_bytes(self.nq, self.packed) + self.nq + self.nq * (2 if self.adam else 1)
                 + self.ngrp * 4 * (3 if self.adam else 2))
+
+
+class FusedUpdate:
+    """The fused per-layer update (qlm_fused_layer / qlm_fused_tail, cudalm.cu:6105-6187).
+
+    Backward calls layer(l) as soon as layer l's gradients are complete, so all layers can share one
+    gradient block (calc_goffsets, cudalm.cu:6008-6040; the spans' gof then differ from pof, set with
+    set_gof as qlm_set_gof does, qlm.cuh:555-575); tail() updates what keeps private gradient slots
+    and closes the step's norm, which clips the NEXT step.  `gs` (device: multiplier, norm) plays
+    g_prev_gn / g_fgs and never visits the host.
+
+    layer_float[l] and tail_float are lists of (p_off, g_off, n, wd) float spans; a layer owns
+    `spans_per_layer` consecutive quantised spans (7 in the reference's models)."""
+
+    def __init__(self, q, n_layers, layer_g0, layer_gn, layer_float, tail_float, spans_per_layer=7):
+        self.q, self.L, self.spl = q, n_layers, spans_per_layer
+        self.layer_g0, self.layer_gn = layer_g0, layer_gn
+        self.layer_float, self.tail_float = layer_float, tail_float
+        dev = q.device
+        self.gnpart = torch.zeros(64 * (n_layers + len(tail_float)), dtype=torch.float32, device=dev)
+        self.gs = torch.ones(2, dtype=torch.float32, device=dev)          # g_prev_gn = 1 before the first step
+
+    def set_gof(self, gofs):
+        """Point each quantised span's gradient read at the compact map (qlm_set_gof)."""
+        for i, g in enumerate(gofs):
+            self.q.spanH[i]["gof"] = g
+        self.q.spanD = spans_to_device(self.q.spanH, self.q.device)
+
+    def _cs(self, p_off):
+        for off, n, cs in self.q.fs:
+            if off <= p_off < off + n:
+                return cs + (p_off - off)
+        raise ValueError("offset %d is not in a float span" % p_off)
+
+    def _float(self, P, G, spans, lr, b1, b2, t):
+        bc1, bc2 = bias_corrections(b1, b2, t)
+        q = self.q
+        for p_off, g_off, n, wd in spans:
+            cs = self._cs(p_off)
+            adamw(P[p_off:p_off + n], G[g_off:g_off + n], q.Mc[cs:cs + n], q.Vc[cs:cs + n], lr, b1, b2, wd,
+                  bc1, bc2, self.gs)
+
+    def layer(self, P, G, l, lr, t, b1=0.9, b2=0.95, wd=0.1):
+        q = self.q
+        sqsum(G[self.layer_g0:self.layer_g0 + self.layer_gn], self.gnpart[64 * l:64 * l + 64])
+        s0 = self.spl * l
+        gi0 = int(q.spanH[s0]["gi0"])
+        ng = int(sum(int(q.spanH[i]["ngrp"]) for i in range(s0, s0 + self.spl)))
+        q.step(P, G, lr, b1, b2, wd, t, gscale=1.0, gsp=self.gs, gi_base=gi0, ng=ng)
+        self._float(P, G, self.layer_float[l], lr, b1, b2, t)
+
+    def tail(self, P, G, lr, t, b1=0.9, b2=0.95):
+        self._float(P, G, self.tail_float, lr, b1, b2, t)
+        for i, (p_off, g_off, n, wd) in enumerate(self.tail_float):
+            k = self.L + i
+            sqsum(G[g_off:g_off + n], self.gnpart[64 * k:64 * k + 64])
+        gnorm_close(self.gnpart, self.L + len(self.tail_float), self.gs)

@@ -126,6 +126,19 @@ int qlmb_gnorm(const float *G, size_t n, const float *const *side, const size_t 
 int qlmb_gnorm_noalloc(const float *G, size_t n, const float *const *side, const size_t *side_n,
                        int nside, int clip_side, float *gs, void *stream);
 
+/* Fused per-layer update (qlm_fused_layer / qlm_fused_tail, cudalm.cu:6105-6187): the optimizer
+ * consumes a layer's gradients as soon as backward has produced them, so the gradient block of
+ * one layer can be reused by the next, and the clip multiplier comes from the PREVIOUS step's norm.
+ * A layer is: qlmb_sqsum of its gradient block into slice l of a caller-owned float[64 * nslice]
+ * array (k_sqsum overwrites its 64 partials, cudalm.cu:6122), qlmb_step over the layer's groups
+ * [gi0, gi0 + ng) with gsp = the gs word of the previous step, qlmb_adamw on its float spans.
+ * After the last layer qlmb_gnorm_close adds all partials in ascending order in double
+ * (cudalm.cu:6182-6186) and writes gs[0] = clip multiplier for the next step, gs[1] = norm --
+ * on the device, where the reference copies the partials to the host.  qlmb_sqsum uses a fixed
+ * 8 KiB array inside the library (no allocation); calls on one device must be stream-ordered. */
+int qlmb_sqsum(const float *G, size_t n, float *part64, void *stream);
+int qlmb_gnorm_close(const float *part, int nslice, float *gs, void *stream);
+
 /* k_adamw (cudalm.cu:2855-2870) for the unquantised spans: bf16 moments,
  * gs (device, may be NULL) = clip multiplier applied on load. */
 int qlmb_adamw(float *P, const float *G, uint16_t *M, uint16_t *V, size_t n, float lr, float b1,

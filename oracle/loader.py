@@ -102,6 +102,11 @@ class Restatement:
         self.lib.qo_gnorm(_p(G), C.c_size_t(G.size), ptrs, lens, C.c_int(ns), C.c_int(clip_side), _p(gs))
         return gs
 
+    def sqsum(self, G):
+        part = np.zeros(64, np.float32)
+        self.lib.qo_sqsum(_p(G), C.c_size_t(G.size), _p(part))
+        return part
+
     def adamw(self, P, G, M, V, lr, b1, b2, wd, bc1, bc2, gs=None):
         f = C.c_float
         self.lib.qo_adamw(_p(P), _p(G), _p(M), _p(V), C.c_size_t(P.size), f(lr), f(b1), f(b2), f(wd),
@@ -231,6 +236,11 @@ class Reference:
         self.lib.ref_gnorm(_p(G), C.c_size_t(G.size), ptrs, lens, C.c_int(ns), C.c_int(clip_side), _p(gs))
         return gs
 
+    def sqsum(self, G):
+        part = np.zeros(64, np.float32)
+        self.lib.ref_sqsum(_p(G), C.c_size_t(G.size), _p(part))
+        return part
+
     def adamw(self, P, G, M, V, lr, b1, b2, wd, bc1, bc2, gs=None):
         f = C.c_float
         self.lib.ref_adamw(_p(P), _p(G), _p(M), _p(V), C.c_size_t(P.size), f(lr), f(b1), f(b2), f(wd),
@@ -332,3 +342,73 @@ def reference(exact=True):
         path = os.path.join(HERE, "_ref", "libcudalm_ref_%s.so" % key)
         _cache[key] = Reference(path) if os.path.exists(path) else None
     return _cache[key]
+
+
+# ---- the fused per-layer update, composed from an implementation's primitives ----
+def fused_layout(L, D, E, F, V, group=128):
+    """Offsets of a small model in the reference's parameter order (emb, per layer an1 wq wk wv wo an2
+    wr w1 w3 w2, then nf) and its compact gradient map: emb and nf keep private slots, all layers
+    share one block (calc_goffsets, cudalm.cu:6008-6040)."""
+    names = ["an1", "wq", "wk", "wv", "wo", "an2", "wr", "w1", "w3", "w2"]
+    size = dict(an1=D, wq=D * D, wk=D * D, wv=D * D, wo=D * D, an2=D, wr=D * E, w1=E * D * F, w3=E * D * F,
+                w2=E * F * D)
+    quant = ("wq", "wk", "wv", "wo", "w1", "w3", "w2")
+    p = V * D
+    rel = {}
+    b = 0
+    for n in names:
+        rel[n] = b; b += size[n]
+    per = b
+    g_emb, g_nf, g_layer = 0, V * D, V * D + D
+    lay = dict(L=L, per=per, layer_g0=g_layer, layer_gn=per, np=V * D + L * per + D, ng_total=g_layer + per,
+               q_sizes=[], q_pofs=[], q_gofs=[], layer_float=[], tail_float=[])
+    for l in range(L):
+        base = p + l * per
+        for n in quant:
+            lay["q_sizes"].append(size[n]); lay["q_pofs"].append(base + rel[n]); lay["q_gofs"].append(g_layer + rel[n])
+        lay["layer_float"].append([(base + rel[n], g_layer + rel[n], size[n]) for n in ("an1", "an2", "wr")])
+    lay["tail_float"] = [(0, g_emb, V * D), (p + L * per, g_nf, D)]
+    return lay
+
+
+def fused_steps(impl, lay, P, state, Mc, Vc, cs_of, grads, *, group=128, dmax=7, lr=3e-4, b1=0.9, b2=0.95,
+                wd=0.1, wdf=0.0, prev_gn=1.0):
+    """qlm_fused_layer for l = L-1 .. 0 and qlm_fused_tail per step (cudalm.cu:6105-6187), from
+    impl.sqsum / impl.step / impl.adamw.  grads[t] = (list of per-layer blocks, emb, nf).
+    Returns the norms that closed each step."""
+    f32 = np.float32
+    sp = state["sp"]
+    L = lay["L"]
+    G = np.zeros(lay["ng_total"], f32)
+    part = np.zeros(64 * (L + 2), f32)
+    norms = []
+    prev = f32(prev_gn)
+    for t, (blocks, g_emb, g_nf) in enumerate(grads, start=1):
+        gscale = f32(1) / prev if prev > f32(1) else f32(1)
+        gs = np.array([gscale, prev], f32)
+        bc1 = f32(1) - f32(np.power(f32(b1), f32(t))); bc2 = f32(1) - f32(np.power(f32(b2), f32(t)))
+        for l in range(L - 1, -1, -1):
+            g0, gn = lay["layer_g0"], lay["layer_gn"]
+            G[g0:g0 + gn] = blocks[l]
+            part[64 * l:64 * l + 64] = impl.sqsum(G[g0:g0 + gn])
+            gi0 = int(sp[7 * l]["gi0"]); ng = int(sp[7 * l:7 * l + 7]["ngrp"].sum())
+            impl.step(P, G, state["d"], state["r"], state["s"], state["m8"], state["m8s"], state["v8"],
+                      state["v8s"], sp, group=group, dmax=dmax, lr=lr, b1=b1, b2=b2, wd=wd, gscale=float(gscale),
+                      inv_bc1=float(f32(1) / bc1), inv_sqrt_bc2=float(f32(1) / np.sqrt(bc2)), t=t, gi_base=gi0, ng=ng)
+            for p_off, g_off, n in lay["layer_float"][l]:
+                cs = cs_of(p_off)
+                impl.adamw(P[p_off:p_off + n], G[g_off:g_off + n], Mc[cs:cs + n], Vc[cs:cs + n], lr, b1, b2, wdf,
+                           float(bc1), float(bc2), gs)
+        G[0:g_emb.size] = g_emb
+        G[g_emb.size:g_emb.size + g_nf.size] = g_nf
+        for i, (p_off, g_off, n) in enumerate(lay["tail_float"]):
+            cs = cs_of(p_off)
+            impl.adamw(P[p_off:p_off + n], G[g_off:g_off + n], Mc[cs:cs + n], Vc[cs:cs + n], lr, b1, b2, wdf,
+                       float(bc1), float(bc2), gs)
+            part[64 * (L + i):64 * (L + i) + 64] = impl.sqsum(G[g_off:g_off + n])
+        ss = 0.0
+        for v in part:
+            ss += float(v)
+        prev = f32(np.sqrt(ss))
+        norms.append(prev)
+    return np.array(norms, f32)

@@ -291,6 +291,10 @@ static void sq_partials(const float *G, size_t n, float *part)
     }
 }
 
+/* the 64 partials of one buffer, as the fused per-layer update keeps them per layer
+ * (qlm_fused_layer, cudalm.cu:6122; k_sqsum, cpu_kern.h:533-540) */
+void qo_sqsum(const float *G, size_t n, float *part64) { sq_partials(G, n, part64); }
+
 void qo_gnorm(const float *G, size_t n, const float *const *side, const size_t *side_n,
               int nside, int clip_side, float *gs)
 {

@@ -58,6 +58,8 @@ void ref_gnorm(const float *G, size_t n, const float *const *side, const size_t 
     KL(k_gnorm, 1, 1)(part, nside, clip_side, gs);
     free(part);
 }
+/* the 64 partial sums of one buffer, as qlm_fused_layer / qlm_fused_tail take them (cudalm.cu:6122, 6181) */
+void ref_sqsum(const float *G, size_t n, float *part64) { KL(k_sqsum, 64, TPB)(G, n, part64); }
 void ref_adamw(float *P, const float *G, unsigned short *M, unsigned short *V, size_t n, float lr,
                float b1, float b2, float wd, float bc1, float bc2, const float *gs)
 {

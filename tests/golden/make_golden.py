@@ -228,6 +228,60 @@ def golden_statefile(ref):
                         sref=sp["sref"].copy(), cfg=np.array([dmax, group, 1, len(sp), packed, 1234]), prev_gn=np.float32(2.5))
 
 
+def fused_case(impl, P0, grads16):
+    """Three fused-update steps on the small model of the fused fixture with `impl`'s primitives."""
+    lay = loader.fused_layout(3, 20, 4, 32, 32)
+    sp, nq, ng = loader.make_spans(lay["q_sizes"], 128, lay["q_pofs"])
+    P = P0.copy()
+    st = dict(sp=sp, d=np.zeros((nq + 1) // 2, np.int8), r=np.zeros(nq, np.int8), s=np.zeros(ng, f32),
+              m8=np.zeros(nq, np.int8), v8=np.zeros(nq, np.uint8), m8s=np.zeros(ng, f32), v8s=np.zeros(ng, f32))
+    impl.encode(P, st["d"], st["r"], st["s"], sp, 128, 7, 1)
+    set_sref(sp, st["s"])
+    sp["gof"] = lay["q_gofs"]
+    # compact offsets of the float spans: the gaps between the quantised spans in ascending order
+    gaps, cur, acc = [], 0, 0
+    for pof, n in zip(lay["q_pofs"], lay["q_sizes"]):
+        if pof > cur:
+            gaps.append((cur, pof - cur, acc)); acc += pof - cur
+        cur = pof + n
+    if cur < lay["np"]:
+        gaps.append((cur, lay["np"] - cur, acc)); acc += lay["np"] - cur
+    def cs_of(p_off):
+        for off, n, cs in gaps:
+            if off <= p_off < off + n:
+                return cs + p_off - off
+        raise ValueError(p_off)
+    Mc = np.zeros(acc, np.uint16); Vc = np.zeros(acc, np.uint16)
+    grads = [([b.astype(f32) for b in blocks], e.astype(f32), n.astype(f32)) for blocks, e, n in grads16]
+    norms = loader.fused_steps(impl, lay, P, st, Mc, Vc, cs_of, grads, wdf=0.0)
+    return dict(P=P, d=st["d"], r=st["r"], s=st["s"], m8=st["m8"], v8=st["v8"], m8s=st["m8s"], v8s=st["v8s"],
+                Mc=Mc, Vc=Vc, norms=norms, sref=sp["sref"].copy())
+
+
+def fused_inputs(seed=11):
+    lay = loader.fused_layout(3, 20, 4, 32, 32)
+    rng = np.random.default_rng(seed)
+    P0 = (rng.standard_normal(lay["np"]) * 0.02).astype(f32)
+    grads16 = []
+    for t in range(3):
+        sc = (0.02, 0.004, 0.05)[t]                      # norms above and below 1: the clip switches on and off
+        blocks = [(rng.standard_normal(lay["per"]) * sc).astype(np.float16) for _ in range(lay["L"])]
+        grads16.append((blocks, (rng.standard_normal(32 * 20) * sc).astype(np.float16),
+                        (rng.standard_normal(20) * sc).astype(np.float16)))
+    return P0, grads16
+
+
+def golden_fused(ref):
+    """qlm_fused_layer / qlm_fused_tail composed from the reference's own kernels (cudalm.cu:6105-6187)."""
+    P0, grads16 = fused_inputs()
+    out = fused_case(ref, P0, grads16)
+    out = {"out_" + k: v for k, v in out.items()}
+    out["P0"] = P0
+    for t, (blocks, e, n) in enumerate(grads16):
+        out["g%d_layers" % t] = np.stack(blocks); out["g%d_emb" % t] = e; out["g%d_nf" % t] = n
+    np.savez_compressed(os.path.join(OUT, "fused_update.npz"), **out)
+
+
 def main():
     ref = loader.reference(exact=True)
     if ref is None:
@@ -243,6 +297,7 @@ def main():
     golden_linear(ref)
     golden_moe(ref)
     golden_statefile(ref)
+    golden_fused(ref)
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print("%-24s %8d B" % (f, os.path.getsize(os.path.join(OUT, f))))

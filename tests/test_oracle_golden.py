@@ -147,3 +147,18 @@ def test_moe_restatement(oracle):
     assert rel(bw["dWr"].ravel(), g["dWr"]) < 1e-5
     for k in ("dW1", "dW3", "dW2"):            # stored as fp16 in the fixture
         assert rel(bw[k].ravel(), g[k].astype(f32)) < 2e-3
+
+
+def test_fused_per_layer_update(oracle):
+    """The restatement's sqsum / step / adamw composed as qlm_fused_layer / qlm_fused_tail
+    (cudalm.cu:6105-6187) reproduce the reference's bytes on the fused fixture."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    import make_golden as mg
+    g = golden("fused_update")
+    grads16 = [(list(g["g%d_layers" % t]), g["g%d_emb" % t], g["g%d_nf" % t]) for t in range(3)]
+    out = mg.fused_case(oracle, g["P0"], grads16)
+    for k, v in out.items():
+        assert np.array_equal(v, g["out_" + k]), k
+    assert out["norms"][0] > 1.0 > out["norms"][1]          # the clip switches on for step 2 and off for step 3

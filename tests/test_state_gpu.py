@@ -249,3 +249,36 @@ def test_qlm_class_update_with_servo(cuda, oracle):
             oracle.servo(d, r, s, sp, 128, 7, Q.f_hi, Q.f_lo, 1)
         assert (Q.d.cpu().numpy() == d).all() and (Q.r.cpu().numpy() == r).all() and (Q.s.cpu().numpy() == s).all()
         assert (P.cpu().numpy() == Ph).all()
+
+
+def test_fused_per_layer_update_matches_reference(cuda):
+    """qlm_fused_layer / qlm_fused_tail (cudalm.cu:6105-6187): layers share one gradient block, each is
+    consumed as soon as it is complete, the clip multiplier is the previous step's and stays on the
+    device.  Fixture: the reference's own kernels composed the same way, three steps."""
+    from cudalm_c_b200 import qlm
+    g = golden("fused_update")
+    lay = loader.fused_layout(3, 20, 4, 32, 32)
+    Q = qlm.Qlm(list(zip(lay["q_pofs"], lay["q_sizes"])), lay["np"], cuda)
+    P = dev(g["P0"], cuda)
+    Q.init_from(P, render=False)
+    assert (Q.spanH["sref"] == g["out_sref"]).all()
+    fu = qlm.FusedUpdate(Q, lay["L"], lay["layer_g0"], lay["layer_gn"],
+                         [[(p, go, n, 0.0) for p, go, n in fl] for fl in lay["layer_float"]],
+                         [(p, go, n, 0.0) for p, go, n in lay["tail_float"]])
+    fu.set_gof(lay["q_gofs"])
+    G = torch.zeros(lay["ng_total"], device=cuda)
+    g0, gn = lay["layer_g0"], lay["layer_gn"]
+    for t in (1, 2, 3):
+        blocks = g["g%d_layers" % (t - 1)].astype(f32)
+        for l in range(lay["L"] - 1, -1, -1):
+            G[g0:g0 + gn] = dev(blocks[l], cuda)
+            fu.layer(P, G, l, 3e-4, t)
+        emb, nf = g["g%d_emb" % (t - 1)].astype(f32), g["g%d_nf" % (t - 1)].astype(f32)
+        G[0:emb.size] = dev(emb, cuda); G[emb.size:emb.size + nf.size] = dev(nf, cuda)
+        fu.tail(P, G, 3e-4, t)
+        assert fu.gs.cpu().numpy()[1] == g["out_norms"][t - 1], t
+    for k in ("d", "r", "s", "m8", "v8", "m8s", "v8s"):
+        assert (getattr(Q, k).cpu().numpy() == g["out_" + k]).all(), k
+    assert (Q.Mc.cpu().numpy().view(np.uint16) == g["out_Mc"]).all()
+    assert (Q.Vc.cpu().numpy().view(np.uint16) == g["out_Vc"]).all()
+    assert (P.cpu().numpy() == g["out_P"]).all()
