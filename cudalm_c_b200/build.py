@@ -29,6 +29,7 @@ UNITS = {
     "qlmb_gemv.cu": [],
     "qlmb_moe.cu": [],
     "qlmb_statefile.cu": [],
+    "qlmb_attn.cu": [],
 }
 COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
           "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

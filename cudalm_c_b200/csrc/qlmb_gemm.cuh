@@ -1,5 +1,6 @@
 // Host-side launch interface of the tcgen05 GEMM engine (qlmb_gemm.cu).
 #pragma once
+#include <cuda.h>
 #include "qlmb_internal.h"
 
 namespace qlmb {
@@ -52,5 +53,10 @@ struct GemmLaunch {
 };
 
 int gemm_launch(const GemmLaunch &g, cudaStream_t st);
+
+// 2-D row-major tensor map [outer][inner] with `pitch` bytes per row and a box of box_inner x box_outer elements
+int make_map(CUtensorMap *m, const void *base, CUtensorMapDataType dt, int esize, unsigned long long inner,
+             unsigned long long outer, unsigned long long pitch, unsigned box_inner, unsigned box_outer,
+             CUtensorMapSwizzle sw);
 
 }  // namespace qlmb

@@ -324,6 +324,15 @@ int qlmb_ep_experts_backward(const qlmb_moe_layer *loc, void *earena, const qlmb
 int qlmb_ep_route_backward(const qlmb_moe_layer *home, void *harena, const void *dXs, void *dfnorm,
                            const void *f_norm, float *dWr, float beta, void *stream);
 
+/* ---- attention (rows of Q/K/V/O are tokens b*T + t; head h occupies columns [h*hd, (h+1)*hd)) ----
+ * e_attn / k_attn_fwd (cudalm.cu:3705-3730; CPU twin cpu_kern.h:166-229): causal attention with an
+ * optional window (win > 0: keys t-win+1 .. t), grouped-query heads (head h reads K/V head
+ * h / (H/KV)), scores scaled by 1/sqrt(hd); lse[b,h,t] = max + log(sum) of the scaled scores.
+ * Q [B*T, H*hd], K and V [B*T, KV*hd], O [B*T, H*hd] are bf16 with RoPE already applied to Q and K;
+ * hd must be 64. */
+int qlmb_attn_fwd(void *O, float *lse, const void *Q, const void *K, const void *V, int B, int T, int H,
+                  int KV, int hd, int win, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -236,6 +236,22 @@ class Reference:
         self.lib.ref_gnorm(_p(G), C.c_size_t(G.size), ptrs, lens, C.c_int(ns), C.c_int(clip_side), _p(gs))
         return gs
 
+    def attn_fwd(self, Q, K, V, B, T, H, KV, hd, win=0):
+        """k_attn_fwd's CPU twin: Q [B*T, H*hd], K, V [B*T, KV*hd] fp32 -> O, lse [B, H, T]."""
+        O = np.zeros((B * T, H * hd), np.float32)
+        lse = np.zeros((B, H, T), np.float32)
+        self.lib.ref_attn_fwd(_p(Q), _p(K), _p(V), _p(O), _p(lse), C.c_int(win), C.c_int(B), C.c_int(T), C.c_int(H),
+                              C.c_int(KV), C.c_int(hd))
+        return O, lse
+
+    def attn_bwd(self, Q, K, V, O, dA, lse, B, T, H, KV, hd, win=0):
+        """k_attn_drow + cpu_attn_bwd: gradients of Q, K, V (into zeroed buffers)."""
+        dQ = np.zeros_like(Q); dK = np.zeros_like(K); dV = np.zeros_like(V)
+        drow = np.zeros((B, H, T), np.float32)
+        self.lib.ref_attn_bwd(_p(Q), _p(K), _p(V), _p(O), _p(dA), _p(lse), _p(drow), _p(dQ), _p(dK), _p(dV),
+                              C.c_int(win), C.c_int(B), C.c_int(T), C.c_int(H), C.c_int(KV), C.c_int(hd))
+        return dQ, dK, dV, drow
+
     def sqsum(self, G):
         part = np.zeros(64, np.float32)
         self.lib.ref_sqsum(_p(G), C.c_size_t(G.size), _p(part))

@@ -66,6 +66,20 @@ void ref_adamw(float *P, const float *G, unsigned short *M, unsigned short *V, s
     KL(k_adamw, nblk(n, TPB), TPB)(P, G, M, V, n, lr, b1, b2, wd, bc1, bc2, NULL, 0, 0, 0, MU_OFF, gs);
 }
 
+/* ---- attention (cpu_kern.h:166-229 forward, 255-312 backward; call sites cudalm.cu:3705-3730, 5918-5936) ---- */
+void ref_attn_fwd(const float *Q, const float *K, const float *V, float *O, float *lse, int win, int B, int T,
+                  int H, int KV, int hd)
+{
+    KL(k_attn_fwd, 1, 1)(Q, K, V, O, lse, win, B, T, H, KV, hd, H * hd, KV * hd);
+}
+/* dQ, dK, dV are accumulated into (the caller zeroes them, as gpu_backward does) */
+void ref_attn_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dA, const float *lse,
+                  float *drow, float *dQ, float *dK, float *dV, int win, int B, int T, int H, int KV, int hd)
+{
+    KL(k_attn_drow, B * H * T, 32)(dA, O, drow, B, T, H, hd, H * hd, 1.0f);
+    cpu_attn_bwd(Q, K, V, dA, lse, drow, dQ, dK, dV, win, B, T, H, KV, hd, H * hd, KV * hd);
+}
+
 /* ---- router and permutation (cudalm.cu:2515-2534, 3576-3602) ---- */
 void ref_router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N, int E, int K,
                      const float *bias, int bs)
