@@ -58,6 +58,7 @@ PROTOTYPES = {
     "qlmb_sqsum": (ci, [vp, sz, vp, vp]),
     "qlmb_gnorm_close": (ci, [vp, ci, vp, vp]),
     "qlmb_attn_fwd": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
+    "qlmb_attn_bwd": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "qlmb_adamw": (ci, [vp, vp, vp, vp, sz, cf, cf, cf, cf, cf, cf, vp, vp]),
     "qlmb_linear_fwd": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp, ci, vp]),
     "qlmb_linear_dgrad": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, cf, ci, vp]),

@@ -11,3 +11,12 @@ def attn_fwd(Q, K, V, B, T, H, KV, win=0):
     lse = torch.empty(B, H, T, dtype=torch.float32, device=Q.device)
     check(lib().qlmb_attn_fwd(ptr(O), ptr(lse), ptr(Q), ptr(K), ptr(V), B, T, H, KV, 64, win, stream_ptr()))
     return O, lse
+
+
+def attn_bwd(Q, K, V, O, dA, lse, B, T, H, KV, win=0):
+    """Gradients of attn_fwd's inputs: dQ, dK, dV (bf16) and drow = rowsum(dA * O) [B, H, T]."""
+    dQ, dK, dV = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
+    drow = torch.empty(B, H, T, dtype=torch.float32, device=Q.device)
+    check(lib().qlmb_attn_bwd(ptr(dQ), ptr(dK), ptr(dV), ptr(drow), ptr(Q), ptr(K), ptr(V), ptr(O), ptr(dA), ptr(lse),
+                              B, T, H, KV, 64, win, stream_ptr()))
+    return dQ, dK, dV, drow

@@ -333,6 +333,16 @@ int qlmb_ep_route_backward(const qlmb_moe_layer *home, void *harena, const void 
 int qlmb_attn_fwd(void *O, float *lse, const void *Q, const void *K, const void *V, int B, int T, int H,
                   int KV, int hd, int win, void *stream);
 
+/* Attention backward (gpu_backward, cudalm.cu:5918-5960: k_attn_drow, then dQ / dK / dV; CPU twins
+ * cpu_kern.h:255-322).  drow[b,h,t] = sum_d dA * O is written first (B*H*T floats, also an output);
+ * dQ [B*T, H*hd], dK and dV [B*T, KV*hd] are bf16 and are overwritten (the reference zeroes its
+ * buffers and accumulates once).  Every element has one writer and a fixed summation order:
+ * dK/dV come from one CTA per (sequence, K/V head, key tile) that walks the heads of the group and the
+ * query tiles, dQ from one CTA per (sequence, head, query tile). */
+int qlmb_attn_bwd(void *dQ, void *dK, void *dV, float *drow, const void *Q, const void *K, const void *V,
+                  const void *O, const void *dA, const float *lse, int B, int T, int H, int KV, int hd,
+                  int win, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

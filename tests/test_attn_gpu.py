@@ -63,3 +63,31 @@ def test_attn_forward(cuda, B, T, H, KV, win):
         Or, lr = torch_attention(Qh, Kh, Vh, B, T, H, KV, win)
     assert rel(O.float().cpu().numpy(), Or) < 1e-2
     assert np.abs(lse.cpu().numpy() - lr).max() < 1e-3
+
+
+@pytest.mark.parametrize("B,T,H,KV,win", SHAPES)
+def test_attn_backward(cuda, B, T, H, KV, win):
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import attn
+    ref = loader.reference()
+    (Qd, Kd, Vd), (Qh, Kh, Vh) = inputs(B, T, H, KV, 5, cuda)
+    g = torch.Generator(device="cpu"); g.manual_seed(9)
+    dA = torch.randn(B * T, H * 64, generator=g).to(torch.bfloat16)
+    dAh = dA.float().numpy()
+    if ref is not None:
+        Or, lr = ref.attn_fwd(Qh, Kh, Vh, B, T, H, KV, 64, win)
+        Ob = torch.from_numpy(Or).to(torch.bfloat16)
+        dQr, dKr, dVr, drr = ref.attn_bwd(Qh, Kh, Vh, Ob.float().numpy(), dAh, lr, B, T, H, KV, 64, win)
+    else:
+        Or, lr, dQr, dKr, dVr = torch_attention(Qh, Kh, Vh, B, T, H, KV, win, dAh)
+        Ob = torch.from_numpy(Or).to(torch.bfloat16)
+        drr = None
+    dQ, dK, dV, drow = attn.attn_bwd(Qd, Kd, Vd, Ob.to(cuda), dA.to(cuda), torch.from_numpy(lr.astype(np.float32)).to(cuda),
+                                     B, T, H, KV, win)
+    torch.cuda.synchronize()
+    q.check(q.lib().qlmb_check_device(None))
+    if drr is not None:
+        assert np.abs(drow.cpu().numpy() - drr).max() < 1e-3 * max(1.0, np.abs(drr).max())
+    assert rel(dV.float().cpu().numpy(), dVr) < 1e-2
+    assert rel(dK.float().cpu().numpy(), dKr) < 1e-2
+    assert rel(dQ.float().cpu().numpy(), dQr) < 1e-2
