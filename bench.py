@@ -505,6 +505,39 @@ def run_linear(args):
                               cpu_baseline=None, gpu_launches=3 * args.steps)))
 
 
+def run_attn(args):
+    """Secondary lines (the attention of BASELINE config 4: B=8 sequences of T=1024, 12 heads of 64):
+    causal flash attention forward and backward.  FLOPs are counted on the causal half only:
+    forward 2 GEMMs, backward 5 (the two kernels recompute S and dP, that work is not counted)."""
+    import torch
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import attn
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    B, T, H, KV = 8, 1024, 12, 12
+    gen = torch.Generator(device=dev); gen.manual_seed(1)
+    mk = lambda c: torch.randn(B * T, c * 64, device=dev, generator=gen).to(torch.bfloat16)
+    Q, K, V, dA = mk(H), mk(KV), mk(KV), mk(H)
+    O, lse = attn.attn_fwd(Q, K, V, B, T, H, KV)
+    pairs = B * H * (T * (T + 1) // 2)                      # (query, key) pairs inside the causal mask
+    f_fwd, f_bwd = 2 * 2.0 * pairs * 64, 5 * 2.0 * pairs * 64
+    ms_f = _time(lambda: attn.attn_fwd(Q, K, V, B, T, H, KV), args.steps, args.warmup)
+    ms_b = _time(lambda: attn.attn_bwd(Q, K, V, O, dA, lse, B, T, H, KV), args.steps, args.warmup)
+    q.check(q.lib().qlmb_check_device(None))
+    for name, ms, fl, nl in (("forward", ms_f, f_fwd, 1), ("backward", ms_b, f_bwd, 3)):
+        tf = fl / (ms * 1e-3) / 1e12
+        print(json.dumps(dict(metric="causal_attention_tflops", value=round(tf, 1), unit="TFLOP/s", n_gpus=1, steps=args.steps,
+                              warmup=max(args.warmup, 3), ms_per_step=round(ms, 4), higher_is_better=True, scaling="weak",
+                              vs_baseline=None, dtype="bf16", data="synthetic",
+                              config=dict(workload="causal attention %s (BASELINE config 4 shape)" % name, B=B, T=T, H=H, KV=KV, hd=64,
+                                          l2="Q, K, V, O, dA: 5 x 12.6 MB, resident in the 126 MB L2 between steps"),
+                              roofline=dict(bound="tensor", kernel="k_attn_fwd" if nl == 1 else "k_attn_bwd_dkv + k_attn_bwd_dq",
+                                            achieved=round(tf, 1), peak=pk["tf_burst"], unit="TFLOP/s",
+                                            frac=round(tf / pk["tf_burst"], 4), traffic=None, peak_kind="burst bf16, of " + pk["src"]),
+                              cpu_baseline=None, gpu_launches=nl * args.steps)))
+
+
 def run_gemv(args):
     """Secondary lines (decode path, BASELINE config 5's building block): Y[B,N] = X[B,K] deq(W) for
     B live slots; metric = weight bytes streamed (0.53125 B per weight) / time."""
@@ -589,7 +622,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="moe", choices=["moe", "adamw", "linear", "gemv", "state"],
+    ap.add_argument("--workload", default="moe", choices=["moe", "adamw", "linear", "gemv", "state", "attn"],
                     help="moe = the headline line; the others print secondary lines: adamw (config 3), linear (config 1), "
                          "gemv (decode building block), state (encode / render / gnorm passes)")
     ap.add_argument("--params", type=int, default=125829120, help="span size of --workload adamw")
@@ -607,6 +640,8 @@ def main():
         run_gemv(args)
     elif args.workload == "state":
         run_state(args)
+    elif args.workload == "attn":
+        run_attn(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

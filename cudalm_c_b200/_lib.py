@@ -57,6 +57,12 @@ PROTOTYPES = {
     "qlmb_gnorm_noalloc": (ci, [vp, sz, vp, vp, ci, ci, vp, vp]),
     "qlmb_sqsum": (ci, [vp, sz, vp, vp]),
     "qlmb_gnorm_close": (ci, [vp, ci, vp, vp]),
+    "qlmb_embed": (ci, [vp, ci, vp, vp, ci, ci, vp]),
+    "qlmb_embed_bwd": (ci, [vp, vp, ci, vp, ci, ci, ci, vp]),
+    "qlmb_rmsnorm_fwd": (ci, [vp, ci, vp, vp, ci, vp, ci, ci, vp]),
+    "qlmb_rmsnorm_bwd": (ci, [vp, ci, ci, vp, vp, vp, ci, vp, vp, vp, ci, ci, ci, vp]),
+    "qlmb_rope": (ci, [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp]),
+    "qlmb_softmax_ce": (ci, [vp, ci, vp, vp, vp, ci, ci, ci, ci, vp]),
     "qlmb_attn_fwd": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "qlmb_attn_bwd": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "qlmb_adamw": (ci, [vp, vp, vp, vp, sz, cf, cf, cf, cf, cf, cf, vp, vp]),

@@ -1,0 +1,62 @@
+"""Host-side mirror of the reference's operators around the GEMMs of a block (e_rmsf, e_rmsb, e_rope,
+k_embed, k_embed_bwd, k_softmax_ce; cudalm.cu:3630-3645, 5740, 5838, 6000) over the C ABI."""
+import torch
+
+from ._lib import BF16, F32, check, lib, ptr, stream_ptr
+
+
+def _dt(t):
+    if t.dtype == torch.bfloat16:
+        return BF16
+    if t.dtype == torch.float32:
+        return F32
+    raise TypeError("activations are float32 or bfloat16, got %s" % t.dtype)
+
+
+def embed(emb, tok, dtype=torch.float32):
+    N, D = tok.numel(), emb.shape[1]
+    X = torch.empty(N, D, dtype=dtype, device=emb.device)
+    check(lib().qlmb_embed(ptr(X), _dt(X), ptr(emb), ptr(tok), N, D, stream_ptr()))
+    return X
+
+
+def embed_bwd(G, dout, tok):
+    """G[V, D] += scatter of dout rows by token, rows of one token added in ascending position."""
+    check(lib().qlmb_embed_bwd(ptr(G), ptr(dout), _dt(dout), ptr(tok), tok.numel(), G.shape[1], G.shape[0], stream_ptr()))
+
+
+def rmsnorm_fwd(X, gamma, out_dtype=None):
+    N, D = X.shape
+    O = torch.empty(N, D, dtype=out_dtype or X.dtype, device=X.device)
+    rinv = torch.empty(N, dtype=torch.float32, device=X.device)
+    check(lib().qlmb_rmsnorm_fwd(ptr(O), _dt(O), ptr(rinv), ptr(X), _dt(X), ptr(gamma), N, D, stream_ptr()))
+    return O, rinv
+
+
+def rmsnorm_bwd(dx, X, gamma, rinv, dy, dgamma=None, accumulate=True):
+    """dx (+)= the input gradient; dgamma += the gain gradient (e_rmsb accumulates into both)."""
+    N, D = X.shape
+    part = torch.empty(128 * D, dtype=torch.float32, device=X.device) if dgamma is not None else None
+    check(lib().qlmb_rmsnorm_bwd(ptr(dx), _dt(dx), 1 if accumulate else 0, ptr(dgamma), ptr(part), ptr(X), _dt(X), ptr(gamma),
+                                 ptr(rinv), ptr(dy), _dt(dy), N, D, stream_ptr()))
+
+
+def rope_tables(T, hd, base=10000.0, device="cpu"):
+    """cos / sin tables [T, hd/2] (angle t * base^(-2i/hd))."""
+    hf = hd // 2
+    inv = base ** (-torch.arange(hf, dtype=torch.float64) * 2.0 / hd)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * inv[None, :]
+    return ang.cos().float().to(device), ang.sin().float().to(device)
+
+
+def rope(buf, cosb, sinb, nh, hd, T, back=False):
+    """In place on buf[N, nh*hd]."""
+    check(lib().qlmb_rope(ptr(buf), _dt(buf), ptr(cosb), ptr(sinb), buf.shape[0], nh, hd, T, 1 if back else 0, stream_ptr()))
+
+
+def softmax_ce(logits, tgt, n_all, dl_dtype=None):
+    rows, V = logits.shape
+    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    dl = torch.empty(rows, V, dtype=dl_dtype or logits.dtype, device=logits.device)
+    check(lib().qlmb_softmax_ce(ptr(logits), _dt(logits), ptr(tgt), ptr(loss), ptr(dl), _dt(dl), rows, V, n_all, stream_ptr()))
+    return loss, dl

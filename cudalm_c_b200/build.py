@@ -30,6 +30,7 @@ UNITS = {
     "qlmb_moe.cu": [],
     "qlmb_statefile.cu": [],
     "qlmb_attn.cu": [],
+    "qlmb_block.cu": [],
 }
 COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
           "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

@@ -51,16 +51,22 @@ __device__ __forceinline__ unsigned long long at_now()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+__device__ __forceinline__ uint32_t at_test(uint32_t bar, uint32_t parity)     // non-blocking probe
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
 __device__ __forceinline__ bool at_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *errword, int site)
 {
     if (mbar_try(bar, parity)) return true;
     const unsigned long long t0 = at_now();
     for (uint32_t i = 0;; i++) {
-        if (mbar_try(bar, parity)) return true;
-        if ((i & 63u) == 63u) {
+        if (at_test(bar, parity)) return true;
+        if ((i & 1023u) == 1023u) {
             if (*abort_flag) return false;
             if (at_now() - t0 > AT_WAIT_NS) break;
-            __nanosleep(64);
         }
     }
     if (!*abort_flag) {

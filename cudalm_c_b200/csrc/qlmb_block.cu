@@ -1,0 +1,324 @@
+// The memory-bound operators around the GEMMs of a transformer block: embedding gather and its
+// gradient, RMSNorm forward / backward / gain gradient, rotary embedding, softmax + cross-entropy.
+// Activations are fp32 or bf16 (a dtype argument per tensor); all arithmetic is fp32.  Every
+// kernel gives run-to-run identical results: no floating-point atomics, fixed summation orders.
+#include <cuda_bf16.h>
+#include <math.h>
+#include "qlmb_common.cuh"
+
+namespace qlmb {
+
+typedef __nv_bfloat16 bf16_t;
+
+__device__ __forceinline__ float blk_ld(const void *p, int dtype, size_t i)
+{
+    return dtype == QLMB_BF16 ? __bfloat162float(((const bf16_t *)p)[i]) : ((const float *)p)[i];
+}
+__device__ __forceinline__ void blk_st(void *p, int dtype, size_t i, float v)
+{
+    if (dtype == QLMB_BF16) ((bf16_t *)p)[i] = __float2bfloat16_rn(v);
+    else ((float *)p)[i] = v;
+}
+// four consecutive elements (i a multiple of 4, rows 16-byte aligned for fp32 / 8-byte for bf16)
+__device__ __forceinline__ float4 blk_ld4(const void *p, int dtype, size_t i)
+{
+    if (dtype == QLMB_BF16) {
+        const uint2 q = *reinterpret_cast<const uint2 *>((const bf16_t *)p + i);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&q.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    return *reinterpret_cast<const float4 *>((const float *)p + i);
+}
+__device__ __forceinline__ void blk_st4(void *p, int dtype, size_t i, float4 v)
+{
+    if (dtype == QLMB_BF16) {
+        uint2 q;
+        *reinterpret_cast<__nv_bfloat162 *>(&q.x) = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162 *>(&q.y) = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2 *>((bf16_t *)p + i) = q;
+    } else {
+        *reinterpret_cast<float4 *>((float *)p + i) = v;
+    }
+}
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ------------------------------------------------------------------ embedding
+// X[n,:] = emb[tok[n],:]  (k_embed, cpu_kern.h:87-90).  One warp per token row.
+__global__ void __launch_bounds__(256) k_embed(void *X, int x_dtype, const float *emb, const int *tok, int N, int D)
+{
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    const float *src = emb + (size_t)tok[n] * D;
+    for (int j = lane * 4; j < D; j += 128) blk_st4(X, x_dtype, (size_t)n * D + j, *reinterpret_cast<const float4 *>(src + j));
+}
+// G[tok[n],:] += dout[n,:] with the rows of one token added in ascending n (k_embed_bwd,
+// cpu_kern.h:92-98; the reference's GPU kernel uses atomics, its CPU twin this fixed order).
+// One warp per vocabulary row: it scans the token list 32 positions at a time and adds the rows
+// that match, so a row of G has one writer.  Work is V*N/32 warp steps -- sized for vocabularies
+// and batches of tens of thousands.
+template <int NV>
+__global__ void __launch_bounds__(256) k_embed_bwd(float *G, const void *dout, int dtype, const int *tok, int N, int D, int V)
+{
+    __shared__ int stok[2048];
+    const int v = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    float4 acc[NV];
+#pragma unroll
+    for (int k = 0; k < NV; k++) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool any = false;
+    for (int n0 = 0; n0 < N; n0 += 2048) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 2048; i += 256) stok[i] = n0 + i < N ? tok[n0 + i] : -1;
+        __syncthreads();
+        const int lim = N - n0 < 2048 ? N - n0 : 2048;
+        for (int c = 0; c < lim; c += 32) {
+            unsigned m = __ballot_sync(0xffffffffu, stok[c + lane] == v);
+            while (m) {
+                const int n = n0 + c + __ffs(m) - 1;
+                m &= m - 1;
+                any = true;
+#pragma unroll
+                for (int k = 0; k < NV; k++) {
+                    const int j = lane * 4 + k * 128;
+                    if (j < D) {
+                        const float4 d = blk_ld4(dout, dtype, (size_t)n * D + j);
+                        acc[k].x += d.x; acc[k].y += d.y; acc[k].z += d.z; acc[k].w += d.w;
+                    }
+                }
+            }
+        }
+    }
+    if (v < V && any) {
+#pragma unroll
+        for (int k = 0; k < NV; k++) {
+            const int j = lane * 4 + k * 128;
+            if (j < D) {
+                float4 g = *reinterpret_cast<float4 *>(G + (size_t)v * D + j);
+                g.x += acc[k].x; g.y += acc[k].y; g.z += acc[k].z; g.w += acc[k].w;
+                *reinterpret_cast<float4 *>(G + (size_t)v * D + j) = g;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// O = X * rinv * gamma, rinv = 1/sqrt(mean(x^2) + 1e-5)  (k_rmsnorm, cpu_kern.h:103-109).  Warp per row.
+__global__ void __launch_bounds__(256) k_rmsnorm_fwd(void *O, int o_dtype, float *rinv, const void *X, int x_dtype,
+                                                     const float *gamma, int N, int D)
+{
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float ss = 0.0f;
+    for (int j = lane * 4; j < D; j += 128) {
+        const float4 x = blk_ld4(X, x_dtype, (size_t)n * D + j);
+        ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+    ss = warp_sum(ss);
+    const float s = 1.0f / sqrtf(ss / (float)D + 1e-5f);
+    if (lane == 0) rinv[n] = s;
+    for (int j = lane * 4; j < D; j += 128) {
+        const float4 x = blk_ld4(X, x_dtype, (size_t)n * D + j);
+        const float4 g = *reinterpret_cast<const float4 *>(gamma + j);
+        blk_st4(O, o_dtype, (size_t)n * D + j, make_float4(x.x * s * g.x, x.y * s * g.y, x.z * s * g.z, x.w * s * g.w));
+    }
+}
+// dx (+)= s*g*dy - (s^3/D * sum(x*g*dy)) * x   (k_rmsnorm_bwd, cpu_kern.h:110-119)
+__global__ void __launch_bounds__(256) k_rmsnorm_bwd(void *dx, int dx_dtype, int accumulate, const void *X, int x_dtype,
+                                                     const float *gamma, const float *rinv, const void *dy, int dy_dtype,
+                                                     int N, int D)
+{
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float c = 0.0f;
+    for (int j = lane * 4; j < D; j += 128) {
+        const float4 x = blk_ld4(X, x_dtype, (size_t)n * D + j), d = blk_ld4(dy, dy_dtype, (size_t)n * D + j);
+        const float4 g = *reinterpret_cast<const float4 *>(gamma + j);
+        c += x.x * g.x * d.x + x.y * g.y * d.y + x.z * g.z * d.z + x.w * g.w * d.w;
+    }
+    c = warp_sum(c);
+    const float s = rinv[n], cf = s * s * s / (float)D * c;
+    for (int j = lane * 4; j < D; j += 128) {
+        const float4 x = blk_ld4(X, x_dtype, (size_t)n * D + j), d = blk_ld4(dy, dy_dtype, (size_t)n * D + j);
+        const float4 g = *reinterpret_cast<const float4 *>(gamma + j);
+        float4 r = make_float4(s * g.x * d.x - cf * x.x, s * g.y * d.y - cf * x.y, s * g.z * d.z - cf * x.z, s * g.w * d.w - cf * x.w);
+        if (accumulate) {
+            const float4 o = blk_ld4(dx, dx_dtype, (size_t)n * D + j);
+            r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w;
+        }
+        blk_st4(dx, dx_dtype, (size_t)n * D + j, r);
+    }
+}
+// Gain gradient in two deterministic stages (k_gamma_part / k_gamma_sum, cudalm.cu:927-940,
+// cpu_kern.h:128-138): 128 fixed row chunks, each summed over its rows in ascending order, then the
+// chunks in ascending order, added to G.
+#define GAMMA_CH 128
+__global__ void __launch_bounds__(128) k_gamma_part(float *part, const void *X, int x_dtype, const float *rinv, const void *dy,
+                                                    int dy_dtype, int N, int D)
+{
+    const int c = blockIdx.y, j = blockIdx.x * 128 + threadIdx.x;
+    if (j >= D) return;
+    const int r0 = (int)((long long)N * c / GAMMA_CH), r1 = (int)((long long)N * (c + 1) / GAMMA_CH);
+    float acc = 0.0f;
+    for (int n = r0; n < r1; n++) acc += blk_ld(X, x_dtype, (size_t)n * D + j) * rinv[n] * blk_ld(dy, dy_dtype, (size_t)n * D + j);
+    part[(size_t)c * D + j] = acc;
+}
+__global__ void __launch_bounds__(128) k_gamma_sum(float *G, const float *part, int D)
+{
+    const int j = blockIdx.x * 128 + threadIdx.x;
+    if (j >= D) return;
+    float a = 0.0f;
+    for (int c = 0; c < GAMMA_CH; c++) a += part[(size_t)c * D + j];
+    G[j] += a;
+}
+
+// ------------------------------------------------------------------ rotary embedding
+// In place on buf[N, nh, hd]; position of row n is n % T; pairs (i, i + hd/2)  (k_rope, cpu_kern.h:139-152).
+__global__ void __launch_bounds__(256) k_rope(void *buf, int dtype, const float *cosb, const float *sinb, size_t total, int nh,
+                                              int hd, int T, int back)
+{
+    const size_t g = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (g >= total) return;
+    const int hf = hd / 2, i = (int)(g % hf);
+    const size_t vh = g / hf;                            // (row, head)
+    const size_t n = vh / nh;
+    const float cs = cosb[(size_t)(n % T) * hf + i], sn = sinb[(size_t)(n % T) * hf + i];
+    const size_t o = vh * hd + i;
+    const float a = blk_ld(buf, dtype, o), b = blk_ld(buf, dtype, o + hf);
+    float ra, rb;
+    if (back) { ra = a * cs + b * sn; rb = -a * sn + b * cs; }
+    else { ra = a * cs - b * sn; rb = b * cs + a * sn; }
+    blk_st(buf, dtype, o, ra);
+    blk_st(buf, dtype, o + hf, rb);
+}
+
+// ------------------------------------------------------------------ softmax + cross-entropy
+// Per row: loss = -log(p[tgt] + 1e-12), dl = (p - onehot) / n_all; rows with tgt < 0 give loss 0 and a
+// zero gradient row  (k_softmax_ce, cpu_kern.h:489-503, without per-token weights).  Block per row.
+__global__ void __launch_bounds__(256) k_softmax_ce(const void *lg, int lg_dtype, const int *tgt, float *loss, void *dl,
+                                                    int dl_dtype, int V, int n_all)
+{
+    __shared__ float red[8];
+    __shared__ float bc;
+    const size_t row = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, tg = tgt[row];
+    if (tg < 0) {
+        for (int i = tid; i < V; i += 256) blk_st(dl, dl_dtype, row * V + i, 0.0f);
+        if (tid == 0) loss[row] = 0.0f;
+        return;
+    }
+    float mx = -1e30f;
+    for (int i = tid; i < V; i += 256) mx = fmaxf(mx, blk_ld(lg, lg_dtype, row * V + i));
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (tid == 0) { float m = red[0]; for (int w = 1; w < 8; w++) m = fmaxf(m, red[w]); bc = m; }
+    __syncthreads();
+    mx = bc;
+    float sum = 0.0f;
+    for (int i = tid; i < V; i += 256) sum += expf(blk_ld(lg, lg_dtype, row * V + i) - mx);
+    sum = warp_sum(sum);
+    __syncthreads();
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (tid == 0) { float s = 0.0f; for (int w = 0; w < 8; w++) s += red[w]; bc = s; }
+    __syncthreads();
+    const float inv = 1.0f / bc, iN = 1.0f / (float)n_all;
+    for (int i = tid; i < V; i += 256) {
+        const float p = expf(blk_ld(lg, lg_dtype, row * V + i) - mx) * inv;
+        blk_st(dl, dl_dtype, row * V + i, (p - (i == tg ? 1.0f : 0.0f)) * iN);
+        if (i == tg) loss[row] = -logf(p + 1e-12f);
+    }
+}
+
+}  // namespace qlmb
+
+using namespace qlmb;
+
+static bool dtype_ok(int d) { return d == QLMB_F32 || d == QLMB_BF16; }
+
+extern "C" int qlmb_embed(void *X, int x_dtype, const float *emb, const int *tok, int N, int D, void *stream)
+{
+    QLMB_REQUIRE(X && emb && tok && dtype_ok(x_dtype), "qlmb_embed: bad argument");
+    QLMB_REQUIRE(D > 0 && D % 4 == 0, "qlmb_embed: D %d must be a multiple of 4", D);
+    if (N <= 0) return QLMB_OK;
+    k_embed<<<(N + 7) / 8, 256, 0, as_stream(stream)>>>(X, x_dtype, emb, tok, N, D);
+    QLMB_LAUNCH_CHECK("k_embed");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_embed_bwd(float *G, const void *dout, int dtype, const int *tok, int N, int D, int V, void *stream)
+{
+    QLMB_REQUIRE(G && dout && tok && dtype_ok(dtype), "qlmb_embed_bwd: bad argument");
+    QLMB_REQUIRE(D > 0 && D % 4 == 0 && D <= 2048, "qlmb_embed_bwd: D %d must be a multiple of 4, at most 2048", D);
+    if (N <= 0 || V <= 0) return QLMB_OK;
+    const unsigned grid = (unsigned)((V + 7) / 8);
+    cudaStream_t st = as_stream(stream);
+    if (D <= 512) k_embed_bwd<4><<<grid, 256, 0, st>>>(G, dout, dtype, tok, N, D, V);
+    else if (D <= 1024) k_embed_bwd<8><<<grid, 256, 0, st>>>(G, dout, dtype, tok, N, D, V);
+    else k_embed_bwd<16><<<grid, 256, 0, st>>>(G, dout, dtype, tok, N, D, V);
+    QLMB_LAUNCH_CHECK("k_embed_bwd");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_rmsnorm_fwd(void *O, int o_dtype, float *rinv, const void *X, int x_dtype, const float *gamma, int N,
+                                int D, void *stream)
+{
+    QLMB_REQUIRE(O && rinv && X && gamma && dtype_ok(o_dtype) && dtype_ok(x_dtype), "qlmb_rmsnorm_fwd: bad argument");
+    QLMB_REQUIRE(D > 0 && D % 4 == 0 && ((uintptr_t)gamma & 15) == 0, "qlmb_rmsnorm_fwd: D %d must be a multiple of 4, gamma 16-byte aligned", D);
+    if (N <= 0) return QLMB_OK;
+    k_rmsnorm_fwd<<<(N + 7) / 8, 256, 0, as_stream(stream)>>>(O, o_dtype, rinv, X, x_dtype, gamma, N, D);
+    QLMB_LAUNCH_CHECK("k_rmsnorm_fwd");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_rmsnorm_bwd(void *dx, int dx_dtype, int accumulate, float *dgamma, float *part, const void *X, int x_dtype,
+                                const float *gamma, const float *rinv, const void *dy, int dy_dtype, int N, int D,
+                                void *stream)
+{
+    QLMB_REQUIRE(dx && X && gamma && rinv && dy && dtype_ok(dx_dtype) && dtype_ok(x_dtype) && dtype_ok(dy_dtype), "qlmb_rmsnorm_bwd: bad argument");
+    QLMB_REQUIRE(D > 0 && D % 4 == 0 && ((uintptr_t)gamma & 15) == 0, "qlmb_rmsnorm_bwd: D %d must be a multiple of 4, gamma 16-byte aligned", D);
+    QLMB_REQUIRE(!dgamma || part, "qlmb_rmsnorm_bwd: the gain gradient needs the 128 x D scratch");
+    if (N <= 0) return QLMB_OK;
+    cudaStream_t st = as_stream(stream);
+    k_rmsnorm_bwd<<<(N + 7) / 8, 256, 0, st>>>(dx, dx_dtype, accumulate, X, x_dtype, gamma, rinv, dy, dy_dtype, N, D);
+    if (dgamma) {
+        k_gamma_part<<<dim3((D + 127) / 128, GAMMA_CH), 128, 0, st>>>(part, X, x_dtype, rinv, dy, dy_dtype, N, D);
+        k_gamma_sum<<<(D + 127) / 128, 128, 0, st>>>(dgamma, part, D);
+    }
+    QLMB_LAUNCH_CHECK("k_rmsnorm_bwd");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_rope(void *buf, int dtype, const float *cosb, const float *sinb, int N, int nh, int hd, int T, int back,
+                         void *stream)
+{
+    QLMB_REQUIRE(buf && cosb && sinb && dtype_ok(dtype), "qlmb_rope: bad argument");
+    QLMB_REQUIRE(nh > 0 && hd > 0 && hd % 2 == 0 && T > 0, "qlmb_rope: bad shape nh %d hd %d T %d", nh, hd, T);
+    if (N <= 0) return QLMB_OK;
+    const size_t total = (size_t)N * nh * (hd / 2);
+    k_rope<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(buf, dtype, cosb, sinb, total, nh, hd, T, back);
+    QLMB_LAUNCH_CHECK("k_rope");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_softmax_ce(const void *logits, int lg_dtype, const int *tgt, float *loss, void *dlogits, int dl_dtype,
+                               int rows, int V, int n_all, void *stream)
+{
+    QLMB_REQUIRE(logits && tgt && loss && dlogits && dtype_ok(lg_dtype) && dtype_ok(dl_dtype), "qlmb_softmax_ce: bad argument");
+    QLMB_REQUIRE(V > 0 && n_all > 0, "qlmb_softmax_ce: bad shape V %d n_all %d", V, n_all);
+    if (rows <= 0) return QLMB_OK;
+    k_softmax_ce<<<(unsigned)rows, 256, 0, as_stream(stream)>>>(logits, lg_dtype, tgt, loss, dlogits, dl_dtype, V, n_all);
+    QLMB_LAUNCH_CHECK("k_softmax_ce");
+    return QLMB_OK;
+}

@@ -324,6 +324,34 @@ int qlmb_ep_experts_backward(const qlmb_moe_layer *loc, void *earena, const qlmb
 int qlmb_ep_route_backward(const qlmb_moe_layer *home, void *harena, const void *dXs, void *dfnorm,
                            const void *f_norm, float *dWr, float beta, void *stream);
 
+/* ---- the memory-bound operators around the GEMMs of a block ----
+ * Activations are QLMB_F32 or QLMB_BF16 per tensor, arithmetic is fp32, D % 4 == 0.  No floating-point
+ * atomics: results are run-to-run identical.
+ * k_embed (cudalm.cu:5740; cpu_kern.h:87-90): X[n,:] = emb[tok[n],:]. */
+int qlmb_embed(void *X, int x_dtype, const float *emb, const int *tok, int N, int D, void *stream);
+/* k_embed_bwd (cudalm.cu:6000; cpu_kern.h:92-98): G[tok[n],:] += dout[n,:], the rows of one token in
+ * ascending n (the order of the reference's CPU build; its GPU kernel uses atomics).  G is [V, D]. */
+int qlmb_embed_bwd(float *G, const void *dout, int dtype, const int *tok, int N, int D, int V, void *stream);
+/* e_rmsf / k_rmsnorm (cudalm.cu:3635-3637; cpu_kern.h:103-109): O = X * rinv * gamma,
+ * rinv[n] = 1/sqrt(mean(X[n,:]^2) + 1e-5) is saved for the backward pass. */
+int qlmb_rmsnorm_fwd(void *O, int o_dtype, float *rinv, const void *X, int x_dtype, const float *gamma, int N, int D,
+                     void *stream);
+/* e_rmsb (cudalm.cu:3638-3645; cpu_kern.h:110-138): dx = (accumulate ? dx : 0) + rinv*gamma*dy -
+ * (rinv^3/D * sum(x*gamma*dy)) * x; when dgamma is not NULL, dgamma[j] += sum_n x*rinv*dy summed over
+ * 128 fixed row chunks and then over the chunks (k_gamma_part / k_gamma_sum), with `part` a scratch of
+ * 128 * D floats. */
+int qlmb_rmsnorm_bwd(void *dx, int dx_dtype, int accumulate, float *dgamma, float *part, const void *X, int x_dtype,
+                     const float *gamma, const float *rinv, const void *dy, int dy_dtype, int N, int D, void *stream);
+/* e_rope / k_rope (cudalm.cu:3630; cpu_kern.h:139-152): rotate pairs (i, i + hd/2) of every head of
+ * buf[N, nh, hd] in place by the angle of position n % T (tables cosb, sinb [T, hd/2]); back = 1 applies
+ * the transpose (the gradient). */
+int qlmb_rope(void *buf, int dtype, const float *cosb, const float *sinb, int N, int nh, int hd, int T, int back,
+              void *stream);
+/* k_softmax_ce (cudalm.cu:5838; cpu_kern.h:489-503, without per-token weights): per row
+ * loss = -log(p[tgt] + 1e-12) and dlogits = (p - onehot) / n_all; rows with tgt < 0 give 0 and a zero row. */
+int qlmb_softmax_ce(const void *logits, int lg_dtype, const int *tgt, float *loss, void *dlogits, int dl_dtype, int rows,
+                    int V, int n_all, void *stream);
+
 /* ---- attention (rows of Q/K/V/O are tokens b*T + t; head h occupies columns [h*hd, (h+1)*hd)) ----
  * e_attn / k_attn_fwd (cudalm.cu:3705-3730; CPU twin cpu_kern.h:166-229): causal attention with an
  * optional window (win > 0: keys t-win+1 .. t), grouped-query heads (head h reads K/V head

@@ -236,6 +236,31 @@ class Reference:
         self.lib.ref_gnorm(_p(G), C.c_size_t(G.size), ptrs, lens, C.c_int(ns), C.c_int(clip_side), _p(gs))
         return gs
 
+    # ---- block operators (cpu_kern.h:87-152, 489-503) ----
+    def embed(self, emb, tok):
+        X = np.zeros((tok.size, emb.shape[1]), np.float32)
+        self.lib.ref_embed(_p(emb), _p(tok), _p(X), C.c_int(tok.size), C.c_int(emb.shape[1]))
+        return X
+
+    def embed_bwd(self, G, dout, tok):
+        self.lib.ref_embed_bwd(_p(tok), _p(dout), _p(G), C.c_int(tok.size), C.c_int(G.shape[1]))
+
+    def rmsnorm(self, X, gamma):
+        O = np.zeros_like(X); rinv = np.zeros(X.shape[0], np.float32)
+        self.lib.ref_rmsnorm(_p(X), _p(gamma), _p(O), _p(rinv), C.c_int(X.shape[0]), C.c_int(X.shape[1]))
+        return O, rinv
+
+    def rmsnorm_bwd(self, X, gamma, rinv, dy, dx, dgamma):
+        self.lib.ref_rmsnorm_bwd(_p(X), _p(gamma), _p(rinv), _p(dy), _p(dx), _p(dgamma), C.c_int(X.shape[0]), C.c_int(X.shape[1]))
+
+    def rope(self, buf, cosb, sinb, nh, hd, T, back=0):
+        self.lib.ref_rope(_p(buf), _p(cosb), _p(sinb), C.c_int(buf.shape[0]), C.c_int(nh), C.c_int(hd), C.c_int(T), C.c_int(back))
+
+    def softmax_ce(self, lg, tgt, n_all):
+        loss = np.zeros(lg.shape[0], np.float32); dl = np.zeros_like(lg)
+        self.lib.ref_softmax_ce(_p(lg), _p(tgt), _p(loss), _p(dl), C.c_int(lg.shape[0]), C.c_int(lg.shape[1]), C.c_int(n_all))
+        return loss, dl
+
     def attn_fwd(self, Q, K, V, B, T, H, KV, hd, win=0):
         """k_attn_fwd's CPU twin: Q [B*T, H*hd], K, V [B*T, KV*hd] fp32 -> O, lse [B, H, T]."""
         O = np.zeros((B * T, H * hd), np.float32)

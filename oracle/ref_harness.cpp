@@ -66,6 +66,28 @@ void ref_adamw(float *P, const float *G, unsigned short *M, unsigned short *V, s
     KL(k_adamw, nblk(n, TPB), TPB)(P, G, M, V, n, lr, b1, b2, wd, bc1, bc2, NULL, 0, 0, 0, MU_OFF, gs);
 }
 
+/* ---- block operators around the GEMMs (cpu_kern.h:87-152, 489-503; call sites gpu_forward / gpu_backward) ---- */
+void ref_embed(const float *emb, const int *tok, float *X, int N, int D) { KL(k_embed, 1, 1)(emb, 0, tok, X, N, D); }
+void ref_embed_bwd(const int *tok, const float *dout, float *G, int N, int D) { KL(k_embed_bwd, 1, 1)(tok, dout, G, 0, N, D); }
+void ref_rmsnorm(const float *X, const float *gamma, float *O, float *rinv, int N, int D) { KL(k_rmsnorm, N, TPB)(X, gamma, 0, O, rinv, N, D); }
+/* e_rmsb (cudalm.cu:3638-3645): dx += ..., then the gain gradient through GG_CH row chunks */
+void ref_rmsnorm_bwd(const float *X, const float *gamma, const float *rinv, const float *dy, float *dx, float *dgamma, int N, int D)
+{
+    KL(k_rmsnorm_bwd, N, TPB)(X, gamma, 0, rinv, dy, dx, N, D);
+    float *part = (float *)malloc(sizeof(float) * (size_t)GG_CH * D);
+    KL(k_gamma_part, dim3((unsigned)nblk(D, TPB), GG_CH), TPB)(X, rinv, dy, part, N, D);
+    KL(k_gamma_sum, nblk(D, TPB), TPB)(part, dgamma, 0, D);
+    free(part);
+}
+void ref_rope(float *buf, const float *cosb, const float *sinb, int N, int nh, int hd, int T, int back)
+{
+    KL(k_rope, 1, 1)(buf, cosb, sinb, N, nh, hd, hd / 2, T, back);
+}
+void ref_softmax_ce(const float *lg, const int *tgt, float *loss, float *dl, int rows, int V, int n_all)
+{
+    KL(k_softmax_ce<float>, rows, TPB)(lg, tgt, loss, dl, (__nv_fp8_e4m3 *)NULL, rows, V, n_all, (const float *)NULL, 0.05f);
+}
+
 /* ---- attention (cpu_kern.h:166-229 forward, 255-312 backward; call sites cudalm.cu:3705-3730, 5918-5936) ---- */
 void ref_attn_fwd(const float *Q, const float *K, const float *V, float *O, float *lse, int win, int B, int T,
                   int H, int KV, int hd)
