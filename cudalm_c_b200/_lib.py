@@ -57,6 +57,8 @@ PROTOTYPES = {
     "qlmb_gnorm_noalloc": (ci, [vp, sz, vp, vp, ci, ci, vp, vp]),
     "qlmb_sqsum": (ci, [vp, sz, vp, vp]),
     "qlmb_gnorm_close": (ci, [vp, ci, vp, vp]),
+    "qlmb_gemm_nt": (ci, [vp, ci, vp, vp, ci, ci, ci, cf, vp]),
+    "qlmb_cast_bf16": (ci, [vp, vp, vp, ci, ci, vp]),
     "qlmb_embed": (ci, [vp, ci, vp, vp, ci, ci, vp]),
     "qlmb_embed_bwd": (ci, [vp, vp, ci, vp, ci, ci, ci, vp]),
     "qlmb_rmsnorm_fwd": (ci, [vp, ci, vp, vp, ci, vp, ci, ci, vp]),

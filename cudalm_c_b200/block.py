@@ -60,3 +60,42 @@ def softmax_ce(logits, tgt, n_all, dl_dtype=None):
     dl = torch.empty(rows, V, dtype=dl_dtype or logits.dtype, device=logits.device)
     check(lib().qlmb_softmax_ce(ptr(logits), _dt(logits), ptr(tgt), ptr(loss), ptr(dl), _dt(dl), rows, V, n_all, stream_ptr()))
     return loss, dl
+
+
+def gemm_nt(A, B, out_dtype=torch.float32, out=None, beta=0.0):
+    """C[M,N] = A[M,K] B[N,K]^T (+ C); A, B bf16."""
+    M, K = A.shape
+    N = B.shape[0]
+    C_ = out if out is not None else torch.empty(M, N, dtype=out_dtype, device=A.device)
+    check(lib().qlmb_gemm_nt(ptr(C_), _dt(C_), ptr(A), ptr(B), M, K, N, beta, stream_ptr()))
+    return C_
+
+
+def cast_bf16(src, plain=True, transposed=False):
+    R, Cc = src.shape
+    d = torch.empty(R, Cc, dtype=torch.bfloat16, device=src.device) if plain else None
+    dt_ = torch.empty(Cc, R, dtype=torch.bfloat16, device=src.device) if transposed else None
+    check(lib().qlmb_cast_bf16(ptr(d), ptr(dt_), ptr(src), R, Cc, stream_ptr()))
+    return d, dt_
+
+
+def head_bwd(fn, emb, tgt, G_emb, chunk_rows=2048, denom=None):
+    """gpu_head_bwd (cudalm.cu:5790-5872): chunked lm_head over the tied embedding + softmax cross-entropy
+    + its backward.  fn [N, D] bf16 (the final norm's output), emb [V, D] fp32, tgt [N] int32.
+    Returns (loss per row, dfn bf16) and adds dlogits^T fn into G_emb [V, D] (fp32)."""
+    from . import linear
+    from ._lib import NK
+    N, D = fn.shape
+    V = emb.shape[0]
+    denom = denom or N
+    eb, ebt = cast_bf16(emb, plain=True, transposed=True)
+    loss = torch.empty(N, dtype=torch.float32, device=fn.device)
+    dfn = torch.empty(N, D, dtype=torch.bfloat16, device=fn.device)
+    for r0 in range(0, N, chunk_rows):
+        r1 = min(N, r0 + chunk_rows)
+        logits = gemm_nt(fn[r0:r1], eb, torch.float32)
+        ls, dl = softmax_ce(logits, tgt[r0:r1], denom, dl_dtype=torch.bfloat16)
+        loss[r0:r1] = ls
+        gemm_nt(dl, ebt, out=dfn[r0:r1])
+        linear.linear_wgrad(G_emb, dl, fn[r0:r1], NK, beta=1.0)
+    return loss, dfn

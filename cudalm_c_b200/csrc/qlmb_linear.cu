@@ -145,3 +145,49 @@ extern "C" int qlmb_selftest_gemm_bf16(float *C, const void *A, const void *B, i
     g.out = C; g.out_dtype = QLMB_F32; g.ldo = N;
     return gemm_launch(g, as_stream(stream));
 }
+
+// ---- unquantised operands (lm_head over the tied embedding, cudalm.cu:5832-5858) ----
+// C[M,N] = A[M,K] B[N,K]^T (+ beta * C): both operands bf16, delivered by TMA; C is fp32 or bf16.
+extern "C" int qlmb_gemm_nt(void *C, int c_dtype, const void *A, const void *B, int M, int K, int N, float beta, void *stream)
+{
+    QLMB_REQUIRE(C && A && B, "qlmb_gemm_nt: NULL argument");
+    QLMB_REQUIRE(c_dtype == QLMB_F32 || c_dtype == QLMB_BF16, "qlmb_gemm_nt: dtype %d", c_dtype);
+    QLMB_REQUIRE(beta == 0.0f || beta == 1.0f, "qlmb_gemm_nt: beta %g", beta);
+    QLMB_REQUIRE(M >= 0 && K > 0 && N > 0 && K % 64 == 0 && N % 128 == 0, "qlmb_gemm_nt: M=%d K=%d N=%d (K %% 64, N %% 128)", M, K, N);
+    if (M == 0) return QLMB_OK;
+    GemmLaunch g = {};
+    g.bmode = B_TMA_K; g.epi = EPI_STORE; g.sched = SCHED_DENSE;
+    g.a[0] = A; g.a_rows = M; g.a_cols = K;
+    g.w[0] = B; g.w_rows = N; g.w_cols = K;
+    g.nseg = 1; g.ksteps = K / 64; g.M = M; g.N = N; g.E = 1;
+    g.out = C; g.out_dtype = c_dtype; g.ldo = N; g.beta = beta;
+    return gemm_launch(g, as_stream(stream));
+}
+
+namespace qlmb {
+// dst[c][r] = bf16(src[r][c]) through a padded 32 x 32 shared-memory tile
+__global__ void __launch_bounds__(256) k_cast_transpose(bf16 *dst, const float *src, int R, int Cc)
+{
+    __shared__ float t[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32, tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int i = ty; i < 32; i += 8) t[i][tx] = (r0 + i < R && c0 + tx < Cc) ? src[(size_t)(r0 + i) * Cc + c0 + tx] : 0.0f;
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8)
+        if (c0 + i < Cc && r0 + tx < R) dst[(size_t)(c0 + i) * R + r0 + tx] = __float2bfloat16_rn(t[tx][i]);
+}
+}  // namespace qlmb
+
+// bf16 copies of an fp32 matrix src[R][C]: plain (dst, may be NULL) and transposed (dst_t [C][R], may be NULL).
+// The tied embedding is a float span; the head GEMMs read these copies (the reference casts it once per
+// step as well, cudalm.cu:5822-5829).
+extern "C" int qlmb_cast_bf16(void *dst, void *dst_t, const float *src, int R, int Cc, void *stream)
+{
+    QLMB_REQUIRE(src && (dst || dst_t) && R > 0 && Cc > 0, "qlmb_cast_bf16: bad argument");
+    cudaStream_t st = as_stream(stream);
+    if (dst) { int rc = convert_f32_to_bf16((bf16 *)dst, src, (size_t)R * Cc, st); if (rc) return rc; }
+    if (dst_t) {
+        k_cast_transpose<<<dim3((Cc + 31) / 32, (R + 31) / 32), 256, 0, st>>>((bf16 *)dst_t, src, R, Cc);
+        QLMB_LAUNCH_CHECK("k_cast_transpose");
+    }
+    return QLMB_OK;
+}

@@ -324,6 +324,15 @@ int qlmb_ep_experts_backward(const qlmb_moe_layer *loc, void *earena, const qlmb
 int qlmb_ep_route_backward(const qlmb_moe_layer *home, void *harena, const void *dXs, void *dfnorm,
                            const void *f_norm, float *dWr, float beta, void *stream);
 
+/* g_abt / g_ab on unquantised operands (the lm_head over the tied embedding, cudalm.cu:5832-5858):
+ * C[M,N] = A[M,K] B[N,K]^T (+ C when beta = 1); A and B bf16, C fp32 or bf16; K % 64 == 0, N % 128 == 0.
+ * logits = fn emb^T uses B = the bf16 copy of emb [V, D]; dfn = dlogits emb uses B = the transposed copy
+ * [D, V]; dEmb += dlogits^T fn is qlmb_linear_wgrad (layout NK) into the fp32 gradient. */
+int qlmb_gemm_nt(void *C, int c_dtype, const void *A, const void *B, int M, int K, int N, float beta, void *stream);
+/* bf16 copies of an fp32 matrix src[R][C]: dst [R][C] and / or dst_t [C][R] (either may be NULL); the
+ * reference casts the embedding once per step for its head GEMMs too (cudalm.cu:5822-5829). */
+int qlmb_cast_bf16(void *dst, void *dst_t, const float *src, int R, int C, void *stream);
+
 /* ---- the memory-bound operators around the GEMMs of a block ----
  * Activations are QLMB_F32 or QLMB_BF16 per tensor, arithmetic is fp32, D % 4 == 0.  No floating-point
  * atomics: results are run-to-run identical.

@@ -96,3 +96,28 @@ def test_softmax_ce(cuda, ref):
     assert np.abs(loss.cpu().numpy() - lr).max() < 1e-5 * max(1.0, np.abs(lr).max())
     assert rel(dl.cpu().numpy(), dr) < 1e-5
     assert loss[5] == 0 and (dl[5] == 0).all()
+
+
+def test_lm_head_ce_and_backward(cuda, ref):
+    """gpu_head_bwd (cudalm.cu:5790-5872) composed from the library's GEMMs and softmax_ce against the
+    reference's g_abt / k_softmax_ce / g_ab / g_atb on the same bf16-rounded operands; the gradient of
+    the logits is rounded to bf16 before the two backward GEMMs, hence 1e-2."""
+    from cudalm_c_b200 import block
+    rng = np.random.default_rng(4)
+    N, D, V = 512, 256, 1024
+    fn = torch.from_numpy(rng.standard_normal((N, D)).astype(np.float32)).bfloat16()
+    emb = torch.from_numpy((rng.standard_normal((V, D)) * 0.05).astype(np.float32)).bfloat16().float()   # bf16-exact values
+    tgt = rng.integers(0, V, N).astype(np.int32); tgt[3] = -1
+    G0 = (rng.standard_normal((V, D)) * 0.01).astype(np.float32)
+    G = torch.from_numpy(G0.copy()).to(cuda)
+    loss, dfn = block.head_bwd(fn.to(cuda), emb.to(cuda), torch.from_numpy(tgt).to(cuda), G, chunk_rows=256)
+    fnh, embh = fn.float().numpy(), emb.numpy()
+    logits = ref.g_abt(fnh, embh)
+    lr, dl = ref.softmax_ce(logits, tgt, N)
+    dfnr = ref.g_ab(dl, embh)
+    Gr = ref.g_atb(dl, fnh, G0.copy())
+    assert np.abs(loss.cpu().numpy() - lr).max() < 2e-3
+    a, b = dfn.float().cpu().numpy().astype(np.float64), dfnr.astype(np.float64)
+    assert np.linalg.norm(a - b) / np.linalg.norm(b) < 1e-2
+    a, b = (G.cpu().numpy() - G0).astype(np.float64), (Gr - G0).astype(np.float64)
+    assert np.linalg.norm(a - b) / np.linalg.norm(b) < 1e-2
