@@ -538,6 +538,63 @@ def run_attn(args):
                               cpu_baseline=None, gpu_launches=nl * args.steps)))
 
 
+def run_train(args):
+    """Secondary line (BASELINE config 4, one GPU): the reference's training step with QLM on --
+    gpu_forward + gpu_head_bwd + gpu_backward + gpu_adam -- composed from the library's operators
+    (cudalm_c_b200/model.py): L=12, D=768, 12 heads of 64, 32 experts top-2, F=1536, V=16384, B=8 x T=1024.
+    metric = tokens per second; the token ids come from pinned host memory every step and the mean loss
+    is read back, so this is also the end-to-end figure."""
+    import torch
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import model
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    cfg = model.Config()
+    m = model.QlmModel(cfg, dev, seed=1, aux=0.03)
+    N = cfg.B * cfg.T
+    g = torch.Generator(device="cpu"); g.manual_seed(0)
+    toks = [torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).pin_memory() for _ in range(4)]
+    tgts = [torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).pin_memory() for _ in range(4)]
+    losses = []
+
+    def step(i):
+        tok = toks[i % 4].to(dev, non_blocking=True); tgt = tgts[i % 4].to(dev, non_blocking=True)
+        loss = m.train_step(tok, tgt)
+        losses.append(float(loss.mean()))                # device -> host read of the step's result
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    q.check(q.lib().qlmb_check_device(None))
+    pk = peaks()
+    # 6 x active matmul parameters per token + causal attention (forward 2, backward 5 GEMMs of T x T/2 x 64 per head)
+    act = cfg.L * (2 * cfg.D * cfg.D + 2 * cfg.D * cfg.KD + cfg.D * cfg.E + cfg.K * 3 * cfg.D * cfg.F) + cfg.V * cfg.D
+    flops = 6.0 * act * N + cfg.L * 7 * 2.0 * cfg.B * cfg.H * (cfg.T * (cfg.T + 1) // 2) * cfg.hd
+    tps = N / (ms * 1e-3)
+    print(json.dumps(dict(metric="qlm_train_tokens_per_s", value=round(tps, 1), unit="tokens/s", n_gpus=1, steps=args.steps,
+                          warmup=max(args.warmup, 3), ms_per_step=round(ms, 3), higher_is_better=True, scaling="weak",
+                          vs_baseline=None, dtype="bf16", data="synthetic",
+                          config=dict(workload="QLM training step, MoE transformer (BASELINE config 4)", L=cfg.L, D=cfg.D, heads=cfg.H,
+                                      experts=cfg.E, top_k=cfg.K, F=cfg.F, V=cfg.V, B=cfg.B, T=cfg.T,
+                                      params_quantised=int(m.q.nq), params_float=int(m.q.nfloat),
+                                      l2="weights 0.74 GB of codes, activations and gradients several GB per step: far beyond the 126 MB L2"),
+                          roofline=dict(bound="tensor", kernel="whole step", achieved=round(flops / (ms * 1e-3) / 1e12, 1),
+                                        peak=pk["tf_sustained"], unit="TFLOP/s",
+                                        frac=round(flops / (ms * 1e-3) / 1e12 / pk["tf_sustained"], 4),
+                                        traffic=None, peak_kind="sustained bf16, of " + pk["src"], model_flops_per_step=flops),
+                          cpu_baseline=None,
+                          e2e=dict(value=round(tps, 1), unit="tokens/s", h2d_bytes_per_step=2 * N * 4, d2h_bytes_per_step=4,
+                                   how="token ids and targets copied from pinned host memory inside the timed region, mean loss read back every step"),
+                          loss_first=round(losses[0], 4), loss_last=round(losses[-1], 4),
+                          gpu_launches=None)))
+
+
 def run_gemv(args):
     """Secondary lines (decode path, BASELINE config 5's building block): Y[B,N] = X[B,K] deq(W) for
     B live slots; metric = weight bytes streamed (0.53125 B per weight) / time."""
@@ -622,7 +679,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="moe", choices=["moe", "adamw", "linear", "gemv", "state", "attn"],
+    ap.add_argument("--workload", default="moe", choices=["moe", "adamw", "linear", "gemv", "state", "attn", "train"],
                     help="moe = the headline line; the others print secondary lines: adamw (config 3), linear (config 1), "
                          "gemv (decode building block), state (encode / render / gnorm passes)")
     ap.add_argument("--params", type=int, default=125829120, help="span size of --workload adamw")
@@ -642,6 +699,8 @@ def main():
         run_state(args)
     elif args.workload == "attn":
         run_attn(args)
+    elif args.workload == "train":
+        run_train(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -1,0 +1,174 @@
+"""The reference's training step on its MoE transformer, composed from the library's operators:
+gpu_forward (cudalm.cu:5736-5788), gpu_head_bwd (5790-5872), gpu_backward (5874-6002) and gpu_adam
+with QLM on (6438-6465, qlm_gpu_update 6082-6103).
+
+Parameters follow the reference's layout (emb; per layer an1 wq wk wv wo an2 wr w1 w3 w2; nf): the seven
+matrices of a layer are quantised spans of one Qlm (4-bit digits + residual + int8 moments), everything
+else is a float span with bf16 moments.  No fp32 or bf16 copy of a quantised weight exists: the GEMMs
+read the digits.  Activations and their gradients are bf16, weight gradients fp32 in the flat G."""
+import math
+
+import torch
+
+from . import attn, block, linear, moe, qlm
+from ._lib import KN
+
+
+class Config:
+    def __init__(self, L=12, D=768, H=12, KV=12, hd=64, E=32, K=2, F=1536, V=16384, T=1024, B=8):
+        self.L, self.D, self.H, self.KV, self.hd, self.E, self.K, self.F, self.V, self.T, self.B = L, D, H, KV, hd, E, K, F, V, T, B
+        self.KD = KV * hd
+        assert H * hd == D
+
+
+class Offsets:
+    """Off (cudalm.cu:263-275): element offsets of every tensor in the flat parameter vector."""
+
+    def __init__(self, c):
+        p = 0
+        self.emb = p; p += c.V * c.D
+        self.layers = []
+        for _ in range(c.L):
+            o = {}
+            for name, n in (("an1", c.D), ("wq", c.D * c.D), ("wk", c.D * c.KD), ("wv", c.D * c.KD), ("wo", c.D * c.D),
+                            ("an2", c.D), ("wr", c.D * c.E), ("w1", c.E * c.D * c.F), ("w3", c.E * c.D * c.F),
+                            ("w2", c.E * c.F * c.D)):
+                o[name] = (p, n); p += n
+            self.layers.append(o)
+        self.nf = p; p += c.D
+        self.total = p
+
+
+QUANT = ("wq", "wk", "wv", "wo", "w1", "w3", "w2")
+
+
+class QlmModel:
+    def __init__(self, cfg, device, seed=1, aux=0.0):
+        c = self.c = cfg
+        self.dev = device
+        o = self.o = Offsets(c)
+        gen = torch.Generator(device=device); gen.manual_seed(seed)
+        # cmd_new's init (cudalm.cu:7349-7365): N(0, 0.02), wo and w2 scaled by 1/sqrt(2L), norm gains 1
+        P = torch.empty(o.total, dtype=torch.float32, device=device)
+        P.normal_(0.0, 0.02, generator=gen)
+        sc = 1.0 / math.sqrt(2.0 * c.L)
+        for lo in o.layers:
+            for nm in ("wo", "w2"):
+                a, n = lo[nm]; P[a:a + n] *= sc
+            for nm in ("an1", "an2"):
+                a, n = lo[nm]; P[a:a + n] = 1.0
+        P[o.nf:o.nf + c.D] = 1.0
+        mats = [lo[nm] for lo in o.layers for nm in QUANT]
+        self.q = qlm.Qlm(mats, o.total, device)
+        self.q.init_from(P, render=False)
+        # float spans (the gaps between the quantised spans, qlm.cuh:493-502) keep their fp32 values;
+        # the quantised part of P is not kept
+        self.fp = [P[off:off + n].clone() for off, n, _ in self.q.fs]
+        self.emb = self._fview(o.emb, c.V * c.D).view(c.V, c.D)
+        self.nf = self._fview(o.nf, c.D)
+        self.fl = [{nm: self._fview(*lo[nm]) for nm in ("an1", "an2", "wr")} for lo in o.layers]
+        del P
+        self.G = torch.zeros(o.total, dtype=torch.float32, device=device)
+        self.cosb, self.sinb = block.rope_tables(c.T, c.hd, device=device)
+        N = c.B * c.T
+        self.N = N
+        self.layers = []
+        for l, lo in enumerate(o.layers):
+            w = {nm: self._codes(7 * l + i) for i, nm in enumerate(QUANT)}
+            m = moe.MoeLayerState(N, c.D, c.F, c.E, c.K, w["w1"], w["w3"], w["w2"], self.fl[l]["wr"].view(c.D, c.E), aux=aux)
+            self.layers.append(dict(w=w, moe=m))
+        self.t = 0
+        self.gs = torch.ones(2, dtype=torch.float32, device=device)
+
+    def _fview(self, a, n):
+        for (off, m, _), t in zip(self.q.fs, self.fp):
+            if off <= a and a + n <= off + m:
+                return t[a - off:a - off + n]
+        raise ValueError("offset %d is not inside a float span" % a)
+
+    def _codes(self, si):
+        sp = self.q.spanH[si]
+        q0, n, g0, ng = int(sp["qi0"]), int(sp["n"]), int(sp["gi0"]), int(sp["ngrp"])
+        return self.q.d[q0 // 2:(q0 + n) // 2], self.q.s[g0:g0 + ng]
+
+    def _g(self, l, nm):
+        a, n = self.o.layers[l][nm]
+        return self.G[a:a + n]
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, tok):
+        c, N = self.c, self.N
+        bf = torch.bfloat16
+        x = block.embed(self.emb, tok, dtype=bf)
+        self.saved = []
+        for l, ly in enumerate(self.layers):
+            w, f = ly["w"], self.fl[l]
+            a_norm, r1 = block.rmsnorm_fwd(x, f["an1"])
+            qh = linear.linear_fwd(a_norm, *w["wq"], KN, c.D)
+            kh = linear.linear_fwd(a_norm, *w["wk"], KN, c.KD)
+            vh = linear.linear_fwd(a_norm, *w["wv"], KN, c.KD)
+            block.rope(qh, self.cosb, self.sinb, c.H, c.hd, c.T)
+            block.rope(kh, self.cosb, self.sinb, c.KV, c.hd, c.T)
+            att, lse = attn.attn_fwd(qh, kh, vh, c.B, c.T, c.H, c.KV)
+            f_in = linear.linear_fwd(att, *w["wo"], KN, c.D, R=x)
+            f_norm, r2 = block.rmsnorm_fwd(f_in, f["an2"])
+            out = ly["moe"].forward(f_in, f_norm)
+            self.saved.append(dict(a_in=x, a_norm=a_norm, r1=r1, q=qh, k=kh, v=vh, att=att, lse=lse, f_in=f_in, f_norm=f_norm, r2=r2))
+            x = out
+        self.x_final = x
+        self.fn, self.fnr = block.rmsnorm_fwd(x, self.nf)
+        return self.fn
+
+    # ------------------------------------------------------------------ head + backward
+    def backward(self, tok, tgt):
+        c, o, N = self.c, self.o, self.N
+        G = self.G
+        G_emb = G[o.emb:o.emb + c.V * c.D].view(c.V, c.D)
+        G_emb.zero_()
+        loss, dfn = block.head_bwd(self.fn, self.emb, tgt, G_emb, chunk_rows=2048)
+        g_nf = G[o.nf:o.nf + c.D]; g_nf.zero_()
+        dout = torch.empty(N, c.D, dtype=torch.bfloat16, device=self.dev)
+        block.rmsnorm_bwd(dout, self.x_final, self.nf, self.fnr, dfn, dgamma=g_nf, accumulate=False)
+        for l in range(c.L - 1, -1, -1):
+            ly, s, f, w = self.layers[l], self.saved[l], self.fl[l], self.layers[l]["w"]
+            gv = lambda nm, shape: self._g(l, nm).view(*shape)
+            dfnorm = ly["moe"].backward(dout, s["f_norm"], gv("w1", (c.E, c.D, c.F)), gv("w3", (c.E, c.D, c.F)),
+                                        gv("w2", (c.E, c.F, c.D)), gv("wr", (c.D, c.E)), beta=0.0)
+            g = self._g(l, "an2"); g.zero_()
+            block.rmsnorm_bwd(dout, s["f_in"], f["an2"], s["r2"], dfnorm, dgamma=g)          # dout now = d f_in
+            d_att = linear.linear_dgrad(dout, *w["wo"], KN, c.D)
+            linear.linear_wgrad(gv("wo", (c.D, c.D)), dout, s["att"], KN, beta=0.0)
+            dq, dk, dv, _ = attn.attn_bwd(s["q"], s["k"], s["v"], s["att"], d_att, s["lse"], c.B, c.T, c.H, c.KV)
+            block.rope(dq, self.cosb, self.sinb, c.H, c.hd, c.T, back=True)
+            block.rope(dk, self.cosb, self.sinb, c.KV, c.hd, c.T, back=True)
+            d_an = linear.linear_dgrad(dq, *w["wq"], KN, c.D)
+            linear.linear_dgrad(dk, *w["wk"], KN, c.D, beta=1.0, out=d_an)
+            linear.linear_dgrad(dv, *w["wv"], KN, c.D, beta=1.0, out=d_an)
+            linear.linear_wgrad(gv("wq", (c.D, c.D)), dq, s["a_norm"], KN, beta=0.0)
+            linear.linear_wgrad(gv("wk", (c.D, c.KD)), dk, s["a_norm"], KN, beta=0.0)
+            linear.linear_wgrad(gv("wv", (c.D, c.KD)), dv, s["a_norm"], KN, beta=0.0)
+            g = self._g(l, "an1"); g.zero_()
+            block.rmsnorm_bwd(dout, s["a_in"], f["an1"], s["r1"], d_an, dgamma=g)             # dout now = d a_in
+        block.embed_bwd(G_emb, dout, tok)
+        self.saved = None
+        return loss
+
+    # ------------------------------------------------------------------ optimizer
+    def update(self, lr=3e-4, b1=0.9, b2=0.95, wd=0.1, wdf=0.0):
+        """gpu_adam with QLM on: global-norm clip (k_sqsum + k_gnorm), integer AdamW over the quantised
+        spans, bf16-moment AdamW over the float spans, servo tick every 100 steps."""
+        self.t += 1
+        q = self.q
+        qlm.gnorm(self.G, out=self.gs)
+        q.step(None, self.G, lr, b1, b2, wd, self.t, gscale=1.0, gsp=self.gs)
+        bc1, bc2 = qlm.bias_corrections(b1, b2, self.t)
+        for (off, n, cs), pt in zip(q.fs, self.fp):
+            qlm.adamw(pt, self.G[off:off + n], q.Mc[cs:cs + n], q.Vc[cs:cs + n], lr, b1, b2, wdf, bc1, bc2, self.gs)
+        if q.servo_every > 0 and self.t % q.servo_every == 0:
+            q.servo()
+
+    def train_step(self, tok, tgt, lr=3e-4):
+        self.forward(tok)
+        loss = self.backward(tok, tgt)
+        self.update(lr)
+        return loss
