@@ -202,6 +202,39 @@ __global__ void __launch_bounds__(256) k_rope(void *buf, int dtype, const float 
     blk_st(buf, dtype, o + hf, rb);
 }
 
+// hd/2 a multiple of 8: a thread rotates 8 consecutive pairs with 16-byte accesses
+__global__ void __launch_bounds__(256) k_rope8(void *buf, int dtype, const float *cosb, const float *sinb, size_t total, int nh,
+                                               int hd, int T, int back)
+{
+    const size_t g = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (g >= total) return;
+    const int hf = hd / 2, per = hf / 8, i = (int)(g % per) * 8;
+    const size_t vh = g / per, n = vh / nh, o = vh * hd + i;
+    const float *cp = cosb + (size_t)(n % T) * hf + i, *sp = sinb + (size_t)(n % T) * hf + i;
+    float a[8], b[8], cs[8], sn[8];
+    *reinterpret_cast<float4 *>(cs) = *reinterpret_cast<const float4 *>(cp);
+    *reinterpret_cast<float4 *>(cs + 4) = *reinterpret_cast<const float4 *>(cp + 4);
+    *reinterpret_cast<float4 *>(sn) = *reinterpret_cast<const float4 *>(sp);
+    *reinterpret_cast<float4 *>(sn + 4) = *reinterpret_cast<const float4 *>(sp + 4);
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        const float4 x = blk_ld4(buf, dtype, o + 4 * k), y = blk_ld4(buf, dtype, o + hf + 4 * k);
+        a[4 * k] = x.x; a[4 * k + 1] = x.y; a[4 * k + 2] = x.z; a[4 * k + 3] = x.w;
+        b[4 * k] = y.x; b[4 * k + 1] = y.y; b[4 * k + 2] = y.z; b[4 * k + 3] = y.w;
+    }
+    float ra[8], rb[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        if (back) { ra[k] = a[k] * cs[k] + b[k] * sn[k]; rb[k] = -a[k] * sn[k] + b[k] * cs[k]; }
+        else { ra[k] = a[k] * cs[k] - b[k] * sn[k]; rb[k] = b[k] * cs[k] + a[k] * sn[k]; }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        blk_st4(buf, dtype, o + 4 * k, make_float4(ra[4 * k], ra[4 * k + 1], ra[4 * k + 2], ra[4 * k + 3]));
+        blk_st4(buf, dtype, o + hf + 4 * k, make_float4(rb[4 * k], rb[4 * k + 1], rb[4 * k + 2], rb[4 * k + 3]));
+    }
+}
+
 // ------------------------------------------------------------------ softmax + cross-entropy
 // Per row: loss = -log(p[tgt] + 1e-12), dl = (p - onehot) / n_all; rows with tgt < 0 give loss 0 and a
 // zero gradient row  (k_softmax_ce, cpu_kern.h:489-503, without per-token weights).  Block per row.
@@ -306,8 +339,13 @@ extern "C" int qlmb_rope(void *buf, int dtype, const float *cosb, const float *s
     QLMB_REQUIRE(buf && cosb && sinb && dtype_ok(dtype), "qlmb_rope: bad argument");
     QLMB_REQUIRE(nh > 0 && hd > 0 && hd % 2 == 0 && T > 0, "qlmb_rope: bad shape nh %d hd %d T %d", nh, hd, T);
     if (N <= 0) return QLMB_OK;
-    const size_t total = (size_t)N * nh * (hd / 2);
-    k_rope<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(buf, dtype, cosb, sinb, total, nh, hd, T, back);
+    if ((hd / 2) % 8 == 0 && (((uintptr_t)buf | (uintptr_t)cosb | (uintptr_t)sinb) & 15) == 0) {
+        const size_t total = (size_t)N * nh * (hd / 16);
+        k_rope8<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(buf, dtype, cosb, sinb, total, nh, hd, T, back);
+    } else {
+        const size_t total = (size_t)N * nh * (hd / 2);
+        k_rope<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(buf, dtype, cosb, sinb, total, nh, hd, T, back);
+    }
     QLMB_LAUNCH_CHECK("k_rope");
     return QLMB_OK;
 }

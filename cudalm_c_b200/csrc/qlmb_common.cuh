@@ -72,9 +72,19 @@ __device__ __forceinline__ int digit_at(const int8_t *d, uint64_t i, int packed)
 __device__ __forceinline__ int locate_group(const qlmb_span *sp, int nspan, int gi, int group,
                                             uint64_t &j0, int &n)
 {
-    int si = 0;
-    for (int i = 0; i < nspan; i++)
-        if (gi >= sp[i].gi0 && gi < sp[i].gi0 + sp[i].ngrp) { si = i; break; }
+    // spans are appended in ascending group order (qlm_add_span, qlm.cuh:448-455): bisect for the last
+    // span that starts at or before gi; a table that is not ascending falls back to the linear scan
+    int lo = 0, hi = nspan - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if ((int)sp[mid].gi0 <= gi) lo = mid; else hi = mid - 1;
+    }
+    int si = lo;
+    if (!(gi >= sp[si].gi0 && gi < sp[si].gi0 + sp[si].ngrp)) {
+        si = 0;
+        for (int i = 0; i < nspan; i++)
+            if (gi >= sp[i].gi0 && gi < sp[i].gi0 + sp[i].ngrp) { si = i; break; }
+    }
     j0 = (uint64_t)(gi - sp[si].gi0) * (uint64_t)group;
     uint64_t left = sp[si].n - j0;
     n = (int)(left < (uint64_t)group ? left : (uint64_t)group);

@@ -45,6 +45,28 @@ static int check_linear(const char *who, int layout, int M, int K, int N, int dt
     return QLMB_OK;
 }
 
+// row offsets of S equal slices (the `off` table of the grouped weight-gradient schedule)
+__global__ void k_slice_offsets(int *off, int S, int rows)
+{
+    if ((int)threadIdx.x <= S) off[threadIdx.x] = (int)threadIdx.x * rows;
+}
+// dW = beta * dW + part[0] + part[1] + ... in ascending slice order; n is a multiple of 4
+__global__ void __launch_bounds__(256) k_sum_slices(float *dW, const float *part, int S, size_t n, float beta)
+{
+    const size_t i = ((size_t)blockIdx.x * 256 + threadIdx.x) * 4;
+    if (i >= n) return;
+    float4 a = *reinterpret_cast<const float4 *>(part + i);
+    for (int s = 1; s < S; s++) {
+        const float4 b = *reinterpret_cast<const float4 *>(part + (size_t)s * n + i);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    if (beta != 0.0f) {
+        const float4 o = *reinterpret_cast<const float4 *>(dW + i);
+        a.x += beta * o.x; a.y += beta * o.y; a.z += beta * o.z; a.w += beta * o.w;
+    }
+    *reinterpret_cast<float4 *>(dW + i) = a;
+}
+
 }  // namespace qlmb
 
 using namespace qlmb;
@@ -111,21 +133,45 @@ extern "C" int qlmb_linear_wgrad(float *dW, const void *dY, const void *X, int l
         if (beta == 0.0f) QLMB_CUDA(cudaMemsetAsync(dW, 0, (size_t)K * N * sizeof(float), st));
         return QLMB_OK;
     }
+    // dW[K,N] = X^T dY (KN)   or   dW[N,K] = dY^T X (NK)
+    const int Md = layout == QLMB_KN ? K : N, Nd = layout == QLMB_KN ? N : K;
+    // A small weight matrix gives few output tiles (768 x 768: 9 tiles of 256 x 256 for 74 SM pairs) over a
+    // long contraction (the M rows).  Then the rows are cut into S slices that run as the "experts" of the
+    // grouped weight-gradient schedule, each into its own partial, and the partials are added in ascending
+    // slice order: every element still has one writer and a fixed order.
+    int S = 1;
+    {
+        const int tiles = ((Md + 255) / 256) * ((Nd + 255) / 256), pairs = sm_count() / 2;
+        while (S < 16 && tiles * S * 2 <= pairs && M % (256 * S) == 0 && M / (2 * S) >= 512) S *= 2;
+    }
+    const size_t conv = dtype == QLMB_F32 ? ((((size_t)M * K * 2 + 255) & ~(size_t)255) + (((size_t)M * N * 2 + 255) & ~(size_t)255)) : 0;
+    const size_t part_bytes = S > 1 ? (size_t)S * Md * Nd * sizeof(float) + 256 : 0;
     void *ws = nullptr;
-    if (dtype == QLMB_F32) { rc = workspace(((size_t)M * K + (size_t)M * N) * 2 + 256, &ws); if (rc) return rc; }
+    if (conv + part_bytes) { rc = workspace(conv + part_bytes, &ws); if (rc) return rc; }
     const bf16 *xb, *gb;
-    bf16 *slot2 = ws ? (bf16 *)((uint8_t *)ws + (((size_t)M * K * 2 + 255) & ~(size_t)255)) : nullptr;
+    bf16 *slot2 = conv ? (bf16 *)((uint8_t *)ws + (((size_t)M * K * 2 + 255) & ~(size_t)255)) : nullptr;
     rc = as_bf16(X, dtype, (size_t)M * K, (bf16 *)ws, &xb, st);
     if (rc) return rc;
     rc = as_bf16(dY, dtype, (size_t)M * N, slot2, &gb, st);
     if (rc) return rc;
     GemmLaunch g = {};
     g.bmode = AB_TMA_MN; g.epi = EPI_ACCUM; g.sched = SCHED_DENSE;
-    // dW[K,N] = X^T dY (KN)   or   dW[N,K] = dY^T X (NK)
-    const int Md = layout == QLMB_KN ? K : N, Nd = layout == QLMB_KN ? N : K;
-   
     g.a[0] = layout == QLMB_KN ? xb : gb; g.a_rows = M; g.a_cols = Md;
     g.w[0] = layout == QLMB_KN ? gb : xb; g.w_cols = Nd; g.w_rows = 0;
+    if (S > 1) {
+        float *part = (float *)((uint8_t *)ws + conv);
+        int *off = (int *)((uint8_t *)part + (size_t)S * Md * Nd * sizeof(float));
+        k_slice_offsets<<<1, 32, 0, st>>>(off, S, M / S);
+        g.sched = SCHED_GROUPK;
+        g.nseg = 1; g.M = Md; g.N = Nd; g.E = S; g.off = off;
+        g.out = part; g.out_dtype = QLMB_F32; g.ldo = Nd; g.beta = 0.0f; g.name = "gemm_wgrad_slices";
+        rc = gemm_launch(g, st);
+        if (rc) return rc;
+        const size_t n = (size_t)Md * Nd;
+        k_sum_slices<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(dW, part, S, n, beta);
+        QLMB_LAUNCH_CHECK("k_sum_slices");
+        return QLMB_OK;
+    }
     g.nseg = 1; g.ksteps = (M + 63) / 64; g.M = Md; g.N = Nd; g.E = 1;
     g.out = dW; g.out_dtype = QLMB_F32; g.ldo = Nd; g.beta = beta;
     return gemm_launch(g, st);
