@@ -65,6 +65,10 @@ PROTOTYPES = {
     "qlmb_rmsnorm_bwd": (ci, [vp, ci, ci, vp, vp, vp, ci, vp, vp, vp, ci, ci, ci, vp]),
     "qlmb_rope": (ci, [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_softmax_ce": (ci, [vp, ci, vp, vp, vp, ci, ci, ci, ci, vp]),
+    "qlmb_dec_rope": (ci, [vp, ci, vp, vp, vp, ci, ci, ci, vp]),
+    "qlmb_dec_kv": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, vp]),
+    "qlmb_dec_attn": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
+    "qlmb_dec_greedy": (ci, [vp, vp, vp, ci, ci, vp]),
     "qlmb_attn_fwd": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "qlmb_attn_bwd": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "qlmb_adamw": (ci, [vp, vp, vp, vp, sz, cf, cf, cf, cf, cf, cf, vp, vp]),

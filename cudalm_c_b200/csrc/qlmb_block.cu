@@ -274,6 +274,121 @@ __global__ void __launch_bounds__(256) k_softmax_ce(const void *lg, int lg_dtype
     }
 }
 
+
+// ------------------------------------------------------------------ decoder (one new token per live slot)
+// k_dec_rope (cudalm.cu:7023-7027): rotate the single row of slot b by the angle of its position pos[b]
+__global__ void __launch_bounds__(256) k_dec_rope(void *buf, int dtype, const float *cosb, const float *sinb, const int *pos,
+                                                  int B, int nh, int hd)
+{
+    const int hf = hd / 2;
+    const size_t g = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (g >= (size_t)B * nh * hf) return;
+    const int i = (int)(g % hf);
+    const size_t r = g / hf;
+    const int b = (int)(r / nh), t = pos[b];
+    const size_t o = r * hd + i;
+    const float c = cosb[(size_t)t * hf + i], sn = sinb[(size_t)t * hf + i];
+    const float x = blk_ld(buf, dtype, o), y = blk_ld(buf, dtype, o + hf);
+    blk_st(buf, dtype, o, x * c - y * sn);
+    blk_st(buf, dtype, o + hf, y * c + x * sn);
+}
+// k_dec_kv (cudalm.cu:7028-7030): the new key / value rows go to position pos[b] of slot b's cache [B, Tm, KD] (bf16)
+__global__ void __launch_bounds__(256) k_dec_kv(bf16_t *Kc, bf16_t *Vc, const bf16_t *k, const bf16_t *v, const int *pos, int B,
+                                                int Tm, int KD)
+{
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (size_t)B * KD) return;
+    const int b = (int)(i / KD), j = (int)(i % KD);
+    const size_t o = ((size_t)b * Tm + pos[b]) * KD + j;
+    Kc[o] = k[i]; Vc[o] = v[i];
+}
+// k_dec_attn (cudalm.cu:7031-7047): one warp per (slot, head) over the cached keys lo..pos[b].  Pass 1: a lane
+// takes every 32nd key and computes its whole 64-wide dot product (16-byte loads), scores go to shared
+// memory; pass 2: a lane owns two of the 64 output dimensions and walks the keys, reading each value row as
+// one coalesced 128-byte line.  Head dimension 64, bf16 cache.
+#define DEC_TM_MAX 4096
+__global__ void __launch_bounds__(128) k_dec_attn(bf16_t *O, const bf16_t *Q, const bf16_t *Kc, const bf16_t *Vc, const int *pos,
+                                                  int win, int B, int Tm, int H, int KV, float scale)
+{
+    extern __shared__ float dec_sc[];                    // 4 warps x Tm scores
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = blockIdx.x * 4 + warp;
+    if (g >= B * H) return;
+    const int b = g / H, h = g % H, kvh = h / (H / KV), t = pos[b], KD = KV * 64, D = H * 64;
+    float *sc = dec_sc + (size_t)warp * Tm;
+    const int lo = (win > 0 && t >= win) ? t - win + 1 : 0;
+    float q[64];
+    {
+        const uint4 *qp = reinterpret_cast<const uint4 *>(Q + (size_t)b * D + h * 64);
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const uint4 x = __ldg(qp + u);
+            const __nv_bfloat162 *xh = reinterpret_cast<const __nv_bfloat162 *>(&x);
+#pragma unroll
+            for (int k = 0; k < 4; k++) { const float2 f = __bfloat1622float2(xh[k]); q[u * 8 + 2 * k] = f.x; q[u * 8 + 2 * k + 1] = f.y; }
+        }
+    }
+    float mx = -1e30f;
+    for (int s = lo + lane; s <= t; s += 32) {
+        const uint4 *kp = reinterpret_cast<const uint4 *>(Kc + ((size_t)b * Tm + s) * KD + kvh * 64);
+        float dot = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const uint4 x = kp[u];
+            const __nv_bfloat162 *xh = reinterpret_cast<const __nv_bfloat162 *>(&x);
+#pragma unroll
+            for (int k = 0; k < 4; k++) { const float2 f = __bfloat1622float2(xh[k]); dot += q[u * 8 + 2 * k] * f.x + q[u * 8 + 2 * k + 1] * f.y; }
+        }
+        dot *= scale;
+        sc[s] = dot;
+        mx = fmaxf(mx, dot);
+    }
+    mx = warp_max(mx);
+    float l = 0.0f;
+    for (int s = lo + lane; s <= t; s += 32) { const float p = __expf(sc[s] - mx); sc[s] = p; l += p; }
+    l = warp_sum(l);
+    __syncwarp();
+    float a0 = 0.0f, a1 = 0.0f;
+    for (int s = lo; s <= t; s++) {
+        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162 *>(Vc + ((size_t)b * Tm + s) * KD + kvh * 64 + 2 * lane);
+        const float2 f = __bfloat1622float2(v2);
+        const float p = sc[s];
+        a0 += p * f.x; a1 += p * f.y;
+    }
+    const float inv = 1.0f / l;
+    *reinterpret_cast<__nv_bfloat162 *>(O + (size_t)b * D + h * 64 + 2 * lane) = __floats2bfloat162_rn(a0 * inv, a1 * inv);
+}
+// Greedy pick of k_dec_sample (cudalm.cu:7078-7093: temp <= 0): arg-max with the lowest index on ties and the
+// log-probability of the pick.  One block per slot.
+__global__ void __launch_bounds__(256) k_dec_greedy(int *out, float *lp, const float *logits, int V)
+{
+    __shared__ float rv[8], rs[8];
+    __shared__ int ri[8];
+    const int s = blockIdx.x, tid = threadIdx.x, w = tid >> 5, ln = tid & 31;
+    const float *lg = logits + (size_t)s * V;
+    float mx = -INFINITY; int mi = 0;
+    for (int i = tid; i < V; i += 256) { const float v = lg[i]; if (v > mx) { mx = v; mi = i; } }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        const float ov = __shfl_xor_sync(~0u, mx, o); const int oi = __shfl_xor_sync(~0u, mi, o);
+        if (ov > mx || (ov == mx && oi < mi)) { mx = ov; mi = oi; }
+    }
+    if (!ln) { rv[w] = mx; ri[w] = mi; }
+    __syncthreads();
+    mx = rv[0]; mi = ri[0];
+    for (int k = 1; k < 8; k++) if (rv[k] > mx || (rv[k] == mx && ri[k] < mi)) { mx = rv[k]; mi = ri[k]; }
+    float z = 0.0f;
+    for (int i = tid; i < V; i += 256) z += __expf(lg[i] - mx);
+    z = warp_sum(z);
+    if (!ln) rs[w] = z;
+    __syncthreads();
+    if (!tid) {
+        float t = 0.0f;
+        for (int k = 0; k < 8; k++) t += rs[k];
+        out[s] = mi; lp[s] = -logf(t);
+    }
+}
+
 }  // namespace qlmb
 
 using namespace qlmb;
@@ -358,5 +473,56 @@ extern "C" int qlmb_softmax_ce(const void *logits, int lg_dtype, const int *tgt,
     if (rows <= 0) return QLMB_OK;
     k_softmax_ce<<<(unsigned)rows, 256, 0, as_stream(stream)>>>(logits, lg_dtype, tgt, loss, dlogits, dl_dtype, V, n_all);
     QLMB_LAUNCH_CHECK("k_softmax_ce");
+    return QLMB_OK;
+}
+
+// ---- decoder operators (dec_step, cudalm.cu:7166-7212) ----
+extern "C" int qlmb_dec_rope(void *buf, int dtype, const float *cosb, const float *sinb, const int *pos, int B, int nh, int hd,
+                             void *stream)
+{
+    QLMB_REQUIRE(buf && cosb && sinb && pos && dtype_ok(dtype) && nh > 0 && hd > 0 && hd % 2 == 0, "qlmb_dec_rope: bad argument");
+    if (B <= 0) return QLMB_OK;
+    const size_t total = (size_t)B * nh * (hd / 2);
+    k_dec_rope<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(buf, dtype, cosb, sinb, pos, B, nh, hd);
+    QLMB_LAUNCH_CHECK("k_dec_rope");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_dec_kv(void *Kc, void *Vc, const void *k, const void *v, const int *pos, int B, int Tm, int KD, void *stream)
+{
+    QLMB_REQUIRE(Kc && Vc && k && v && pos && Tm > 0 && KD > 0, "qlmb_dec_kv: bad argument");
+    if (B <= 0) return QLMB_OK;
+    const size_t total = (size_t)B * KD;
+    k_dec_kv<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((bf16_t *)Kc, (bf16_t *)Vc, (const bf16_t *)k,
+                                                                              (const bf16_t *)v, pos, B, Tm, KD);
+    QLMB_LAUNCH_CHECK("k_dec_kv");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_dec_attn(void *O, const void *Q, const void *Kc, const void *Vc, const int *pos, int win, int B, int Tm,
+                             int H, int KV, int hd, void *stream)
+{
+    QLMB_REQUIRE(O && Q && Kc && Vc && pos, "qlmb_dec_attn: NULL argument");
+    QLMB_REQUIRE(hd == 64 && H > 0 && KV > 0 && H % KV == 0 && Tm > 0 && Tm <= DEC_TM_MAX, "qlmb_dec_attn: hd %d H %d KV %d Tm %d", hd, H, KV, Tm);
+    if (B <= 0) return QLMB_OK;
+    const size_t smem = (size_t)4 * Tm * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        QLMB_CUDA(cudaFuncSetAttribute(k_dec_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * DEC_TM_MAX * (int)sizeof(float)));
+        configured = true;
+    }
+    k_dec_attn<<<(unsigned)((B * H + 3) / 4), 128, smem, as_stream(stream)>>>((bf16_t *)O, (const bf16_t *)Q, (const bf16_t *)Kc,
+                                                                              (const bf16_t *)Vc, pos, win, B, Tm, H, KV,
+                                                                              1.0f / sqrtf((float)hd));
+    QLMB_LAUNCH_CHECK("k_dec_attn");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_dec_greedy(int *out, float *lp, const float *logits, int B, int V, void *stream)
+{
+    QLMB_REQUIRE(out && lp && logits && V > 0, "qlmb_dec_greedy: bad argument");
+    if (B <= 0) return QLMB_OK;
+    k_dec_greedy<<<(unsigned)B, 256, 0, as_stream(stream)>>>(out, lp, logits, V);
+    QLMB_LAUNCH_CHECK("k_dec_greedy");
     return QLMB_OK;
 }

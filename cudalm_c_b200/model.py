@@ -96,23 +96,27 @@ class QlmModel:
         return self.G[a:a + n]
 
     # ------------------------------------------------------------------ forward
-    def forward(self, tok):
-        c, N = self.c, self.N
+    def forward(self, tok, B=None, T=None, moes=None):
+        """gpu_forward over B sequences of T tokens (default: the training batch); `moes` replaces the
+        layers' MoE states when the row count differs from the training batch (decoder prefill)."""
+        c = self.c
+        B, T = B or c.B, T or c.T
         bf = torch.bfloat16
         x = block.embed(self.emb, tok, dtype=bf)
         self.saved = []
         for l, ly in enumerate(self.layers):
             w, f = ly["w"], self.fl[l]
+            mo = moes[l] if moes is not None else ly["moe"]
             a_norm, r1 = block.rmsnorm_fwd(x, f["an1"])
             qh = linear.linear_fwd(a_norm, *w["wq"], KN, c.D)
             kh = linear.linear_fwd(a_norm, *w["wk"], KN, c.KD)
             vh = linear.linear_fwd(a_norm, *w["wv"], KN, c.KD)
-            block.rope(qh, self.cosb, self.sinb, c.H, c.hd, c.T)
-            block.rope(kh, self.cosb, self.sinb, c.KV, c.hd, c.T)
-            att, lse = attn.attn_fwd(qh, kh, vh, c.B, c.T, c.H, c.KV)
+            block.rope(qh, self.cosb, self.sinb, c.H, c.hd, T)
+            block.rope(kh, self.cosb, self.sinb, c.KV, c.hd, T)
+            att, lse = attn.attn_fwd(qh, kh, vh, B, T, c.H, c.KV)
             f_in = linear.linear_fwd(att, *w["wo"], KN, c.D, R=x)
             f_norm, r2 = block.rmsnorm_fwd(f_in, f["an2"])
-            out = ly["moe"].forward(f_in, f_norm)
+            out = mo.forward(f_in, f_norm)
             self.saved.append(dict(a_in=x, a_norm=a_norm, r1=r1, q=qh, k=kh, v=vh, att=att, lse=lse, f_in=f_in, f_norm=f_norm, r2=r2))
             x = out
         self.x_final = x
@@ -172,3 +176,82 @@ class QlmModel:
         loss = self.backward(tok, tgt)
         self.update(lr)
         return loss
+
+
+class Decoder:
+    """Dec / dec_new / dec_prefill / dec_step (cudalm.cu:7020-7212): B live slots, a bf16 K/V cache of Tm
+    positions per layer, one new token per slot and step.  All per-step state (token, position, pick) stays
+    on the device, so a step has no host round trip and can be captured in a CUDA graph."""
+
+    def __init__(self, model, B, Tm):
+        c, dev = model.c, model.dev
+        self.m, self.B, self.Tm = model, B, Tm
+        bf = torch.bfloat16
+        self.K = [torch.zeros(B, Tm, c.KD, dtype=bf, device=dev) for _ in range(c.L)]
+        self.V = [torch.zeros(B, Tm, c.KD, dtype=bf, device=dev) for _ in range(c.L)]
+        self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.tok = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.otok = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.olp = torch.zeros(B, dtype=torch.float32, device=dev)
+        self.moes = [self._moe(l, B) for l in range(c.L)]
+        self.emb_bf, _ = block.cast_bf16(model.emb, plain=True, transposed=False)
+        self.logits = None
+
+    def _moe(self, l, N):
+        c, m = self.m.c, self.m
+        w = m.layers[l]["w"]
+        return moe.MoeLayerState(N, c.D, c.F, c.E, c.K, w["w1"], w["w3"], w["w2"], m.fl[l]["wr"].view(c.D, c.E), aux=0.0)
+
+    def prefill(self, ids):
+        """dec_prefill for all slots at once: ids [B, n] (equal prompt lengths) through the full forward, keys and
+        values of every layer into the cache, the last row's logits picked greedily as the first new token."""
+        c, m = self.m.c, self.m
+        B, n = ids.shape
+        assert B == self.B and 1 <= n <= self.Tm
+        moes = [self._moe(l, B * n) for l in range(c.L)]
+        fn = m.forward(ids.reshape(-1).contiguous(), B=B, T=n, moes=moes)
+        for l in range(c.L):
+            self.K[l][:, :n] = m.saved[l]["k"].view(B, n, c.KD)
+            self.V[l][:, :n] = m.saved[l]["v"].view(B, n, c.KD)
+        m.saved = None
+        last = fn.view(B, n, c.D)[:, n - 1].contiguous()
+        self.logits = block.gemm_nt(last, self.emb_bf, torch.float32)
+        self._pick()
+        self.pos.fill_(n)
+        self.tok.copy_(self.otok)
+        return self.logits
+
+    def _pick(self):
+        from ._lib import check, lib, ptr, stream_ptr
+        check(lib().qlmb_dec_greedy(ptr(self.otok), ptr(self.olp), ptr(self.logits), self.B, self.m.c.V, stream_ptr()))
+
+    def step(self, advance=True):
+        """dec_step: the token in self.tok at position self.pos for every slot; logits -> self.logits, greedy pick ->
+        self.otok / self.olp; with advance the pick becomes the next step's token."""
+        from ._lib import check, lib, ptr, stream_ptr
+        c, m, B = self.m.c, self.m, self.B
+        L_ = lib()
+        x = block.embed(m.emb, self.tok, dtype=torch.bfloat16)
+        for l, ly in enumerate(m.layers):
+            w, f = ly["w"], m.fl[l]
+            a_norm, _ = block.rmsnorm_fwd(x, f["an1"])
+            qh = linear.gemv_decode(a_norm, *w["wq"], KN, c.D)
+            kh = linear.gemv_decode(a_norm, *w["wk"], KN, c.KD)
+            vh = linear.gemv_decode(a_norm, *w["wv"], KN, c.KD)
+            check(L_.qlmb_dec_rope(ptr(qh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.H, c.hd, stream_ptr()))
+            check(L_.qlmb_dec_rope(ptr(kh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.KV, c.hd, stream_ptr()))
+            check(L_.qlmb_dec_kv(ptr(self.K[l]), ptr(self.V[l]), ptr(kh), ptr(vh), ptr(self.pos), B, self.Tm, c.KD, stream_ptr()))
+            att = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
+            check(L_.qlmb_dec_attn(ptr(att), ptr(qh), ptr(self.K[l]), ptr(self.V[l]), ptr(self.pos), 0, B, self.Tm, c.H, c.KV,
+                                   c.hd, stream_ptr()))
+            f_in = linear.gemv_decode(att, *w["wo"], KN, c.D)
+            f_in += x
+            f_norm, _ = block.rmsnorm_fwd(f_in, f["an2"])
+            x = self.moes[l].forward(f_in, f_norm)
+        fn, _ = block.rmsnorm_fwd(x, m.nf)
+        self.logits = block.gemm_nt(fn, self.emb_bf, torch.float32, out=self.logits)
+        self._pick()
+        if advance:
+            self.pos += 1
+            self.tok.copy_(self.otok)
+        return self.logits

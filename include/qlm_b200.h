@@ -361,6 +361,21 @@ int qlmb_rope(void *buf, int dtype, const float *cosb, const float *sinb, int N,
 int qlmb_softmax_ce(const void *logits, int lg_dtype, const int *tgt, float *loss, void *dlogits, int dl_dtype, int rows,
                     int V, int n_all, void *stream);
 
+/* ---- decoder: one new token per live slot (dec_step, cudalm.cu:7166-7212) ----
+ * The K/V cache of a layer is bf16 [B, Tm, KV*hd]; pos[b] (device) is the position of slot b's new token.
+ * k_dec_rope (cudalm.cu:7023-7027): rotate the single row of each slot by the angle of pos[b]. */
+int qlmb_dec_rope(void *buf, int dtype, const float *cosb, const float *sinb, const int *pos, int B, int nh, int hd,
+                  void *stream);
+/* k_dec_kv (cudalm.cu:7028-7030): append the new key / value rows (bf16 [B, KD]) at pos[b]. */
+int qlmb_dec_kv(void *Kc, void *Vc, const void *k, const void *v, const int *pos, int B, int Tm, int KD, void *stream);
+/* k_dec_attn (cudalm.cu:7031-7047): O[b, h*hd..] = softmax(q k^T / sqrt(hd)) v over cached positions
+ * max(0, pos-win+1) .. pos[b] (win <= 0: all); Q, O bf16 [B, H*hd]; hd = 64, Tm <= 4096. */
+int qlmb_dec_attn(void *O, const void *Q, const void *Kc, const void *Vc, const int *pos, int win, int B, int Tm, int H,
+                  int KV, int hd, void *stream);
+/* The greedy branch of k_dec_sample (cudalm.cu:7078-7093, temp <= 0): out[b] = arg-max of logits[b,:] (lowest
+ * index on ties), lp[b] = its log-probability. */
+int qlmb_dec_greedy(int *out, float *lp, const float *logits, int B, int V, void *stream);
+
 /* ---- attention (rows of Q/K/V/O are tokens b*T + t; head h occupies columns [h*hd, (h+1)*hd)) ----
  * e_attn / k_attn_fwd (cudalm.cu:3705-3730; CPU twin cpu_kern.h:166-229): causal attention with an
  * optional window (win > 0: keys t-win+1 .. t), grouped-query heads (head h reads K/V head
