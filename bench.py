@@ -595,6 +595,82 @@ def run_train(args):
                           gpu_launches=None)))
 
 
+def run_decode(args):
+    """Secondary lines (BASELINE config 5, one GPU): greedy decoding with the K/V-cached decoder
+    (cudalm_c_b200/model.py Decoder = dec_prefill + dec_step) on the config-4 model, random weights:
+    prompts of 128 uniform ids, 256 new tokens, B = 1, 8, 64 live slots, bf16 cache of 1024 positions.
+    A step is one CUDA-graph replay (no host input: token, position and pick stay on the device).
+    metric = generated tokens per second over the 256 steps; prefill is reported beside it.  The roofline is
+    HBM: bytes a step must read = 4-bit attention weights + the distinct experts the step's routing hit
+    (counted on 8 extra steps after the timed run) + router + bf16 embedding for the head + the K/V rows read."""
+    import torch
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import model
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    cfg = model.Config()
+    m = model.QlmModel(cfg, dev, seed=1, aux=0.0)
+    n_prompt, n_new, Tm = 128, 256, 1024
+    for B in (1, 8, 64):
+        g = torch.Generator(device="cpu"); g.manual_seed(B)
+        ids_h = torch.randint(0, cfg.V, (B, n_prompt), generator=g, dtype=torch.int32).pin_memory()
+        dec = model.Decoder(m, B, Tm)
+        t0 = time.perf_counter()
+        ids = ids_h.to(dev, non_blocking=True)
+        dec.prefill(ids)
+        torch.cuda.synchronize()
+        t_prefill = time.perf_counter() - t0
+        for _ in range(3):                                  # warm-up steps (also sizes every scratch buffer)
+            dec.step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            dec.step()
+        gen = torch.zeros(n_new, B, dtype=torch.int32, device=dev)
+        dec.prefill(ids)                                    # back to the end of the prompt
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for j in range(n_new):
+            gen[j].copy_(dec.tok)
+            graph.replay()
+        e1.record()
+        out_h = gen.cpu()                                   # device -> host read of the generated ids
+        t_e2e = time.perf_counter() - t0
+        ms = e0.elapsed_time(e1) / n_new
+        q.check(q.lib().qlmb_check_device(None))
+        # distinct experts per layer on a few more steps -> bytes a step has to read
+        hit = 0.0
+        for _ in range(8):
+            dec.step()
+            for mo in dec.moes:
+                hit += float(torch.unique(mo.member("assign", (cfg.K, B), torch.int32)).numel())
+        hit /= 8.0                                           # summed over the 12 layers
+        w = 0.53125
+        pos_mid = n_prompt + n_new / 2
+        byts = cfg.L * (2 * cfg.D * cfg.D + 2 * cfg.D * cfg.KD) * w + hit * 3 * cfg.D * cfg.F * w + cfg.L * cfg.D * cfg.E * 4 \
+            + cfg.V * cfg.D * 2 + cfg.L * 2 * B * pos_mid * cfg.KD * 2
+        gbs = byts / (ms * 1e-3) / 1e9
+        tps = B / (ms * 1e-3)
+        print(json.dumps(dict(metric="decode_tokens_per_s", value=round(tps, 1), unit="tokens/s", n_gpus=1, steps=n_new, warmup=3,
+                              ms_per_step=round(ms, 4), higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                              data="synthetic",
+                              config=dict(workload="greedy decode, K/V cache (BASELINE config 5)", B=B, prompt=n_prompt, new_tokens=n_new,
+                                          cache_positions=Tm, model="config 4 (L=12, D=768, 32 experts top-2)",
+                                          experts_hit_per_step=round(hit, 1), l2="weights read per step %.0f MB" % (byts / 1e6)),
+                              roofline=dict(bound="hbm", kernel="whole step (one graph replay)", achieved=round(gbs, 1), peak=pk["hbm"],
+                                            unit="GB/s", frac=round(gbs / pk["hbm"], 4), traffic=None, peak_kind="copy, of " + pk["src"],
+                                            bytes_per_step=byts),
+                              cpu_baseline=None,
+                              e2e=dict(value=round(B * n_new / t_e2e, 1), unit="tokens/s", h2d_bytes_per_step=0,
+                                       d2h_bytes_per_step=B * 4, prefill_ms=round(t_prefill * 1e3, 2),
+                                       how="host clock over the 256 replays and the read-back of the generated ids; the prompt upload and prefill are timed separately (prefill_ms, includes the first-use set-up of this batch size)"),
+                              gpu_launches=None, sample=[int(x) for x in out_h[:4, 0]])))
+        del dec, graph
+
+
 def run_gemv(args):
     """Secondary lines (decode path, BASELINE config 5's building block): Y[B,N] = X[B,K] deq(W) for
     B live slots; metric = weight bytes streamed (0.53125 B per weight) / time."""
@@ -679,7 +755,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="moe", choices=["moe", "adamw", "linear", "gemv", "state", "attn", "train"],
+    ap.add_argument("--workload", default="moe", choices=["moe", "adamw", "linear", "gemv", "state", "attn", "train", "decode"],
                     help="moe = the headline line; the others print secondary lines: adamw (config 3), linear (config 1), "
                          "gemv (decode building block), state (encode / render / gnorm passes)")
     ap.add_argument("--params", type=int, default=125829120, help="span size of --workload adamw")
@@ -701,6 +777,8 @@ def main():
         run_attn(args)
     elif args.workload == "train":
         run_train(args)
+    elif args.workload == "decode":
+        run_decode(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -215,7 +215,7 @@ class Decoder:
             self.V[l][:, :n] = m.saved[l]["v"].view(B, n, c.KD)
         m.saved = None
         last = fn.view(B, n, c.D)[:, n - 1].contiguous()
-        self.logits = block.gemm_nt(last, self.emb_bf, torch.float32)
+        self.logits = block.gemm_nt(last, self.emb_bf, torch.float32, out=self.logits)   # same buffer every time: a captured step keeps writing to it
         self._pick()
         self.pos.fill_(n)
         self.tok.copy_(self.otok)
