@@ -611,8 +611,8 @@ def run_decode(args):
     pk = peaks()
     cfg = model.Config()
     m = model.QlmModel(cfg, dev, seed=1, aux=0.0)
-    n_prompt, n_new, Tm = 128, 256, 1024
-    for B in (1, 8, 64):
+    n_prompt, n_new, Tm = 128, args.new_tokens, 1024
+    for B in [int(x) for x in args.decode_b.split(",")]:
         g = torch.Generator(device="cpu"); g.manual_seed(B)
         ids_h = torch.randint(0, cfg.V, (B, n_prompt), generator=g, dtype=torch.int32).pin_memory()
         dec = model.Decoder(m, B, Tm)
@@ -761,6 +761,8 @@ def main():
     ap.add_argument("--params", type=int, default=125829120, help="span size of --workload adamw")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="N>1: peer = foreign rows read by peer loads inside the row kernels; nccl = all-to-all exchanges")
+    ap.add_argument("--decode-b", default="1,8,64", help="live slots of --workload decode (comma list; BASELINE config 5 has 1,8,64)")
+    ap.add_argument("--new-tokens", type=int, default=256, help="generated tokens of --workload decode (256 in BASELINE config 5; fewer for profiler captures)")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the 8192 of config 2); smaller values are for profiler captures")
     args = ap.parse_args()
     if args.tokens > 0:

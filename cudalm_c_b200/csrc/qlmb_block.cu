@@ -302,20 +302,21 @@ __global__ void __launch_bounds__(256) k_dec_kv(bf16_t *Kc, bf16_t *Vc, const bf
     const size_t o = ((size_t)b * Tm + pos[b]) * KD + j;
     Kc[o] = k[i]; Vc[o] = v[i];
 }
-// k_dec_attn (cudalm.cu:7031-7047): one warp per (slot, head) over the cached keys lo..pos[b].  Pass 1: a lane
-// takes every 32nd key and computes its whole 64-wide dot product (16-byte loads), scores go to shared
-// memory; pass 2: a lane owns two of the 64 output dimensions and walks the keys, reading each value row as
-// one coalesced 128-byte line.  Head dimension 64, bf16 cache.
+// k_dec_attn (cudalm.cu:7031-7047): one block of four warps per (slot, head) over the cached keys lo..pos[b].
+// Pass 1: a thread takes every 128th key and computes its whole 64-wide dot product (16-byte loads), scores
+// go to shared memory, block-wide max and sum.  Pass 2: a lane owns two of the 64 output dimensions, each warp
+// walks a quarter of the keys (four value rows in flight, each one coalesced 128-byte line), and the four
+// partial outputs are added in warp order.  Head dimension 64, bf16 cache.
 #define DEC_TM_MAX 4096
 __global__ void __launch_bounds__(128) k_dec_attn(bf16_t *O, const bf16_t *Q, const bf16_t *Kc, const bf16_t *Vc, const int *pos,
                                                   int win, int B, int Tm, int H, int KV, float scale)
 {
-    extern __shared__ float dec_sc[];                    // 4 warps x Tm scores
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = blockIdx.x * 4 + warp;
-    if (g >= B * H) return;
+    extern __shared__ float dec_sc[];                    // Tm scores
+    __shared__ float red[4], part[4][64];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int g = blockIdx.x;
     const int b = g / H, h = g % H, kvh = h / (H / KV), t = pos[b], KD = KV * 64, D = H * 64;
-    float *sc = dec_sc + (size_t)warp * Tm;
+    float *sc = dec_sc;
     const int lo = (win > 0 && t >= win) ? t - win + 1 : 0;
     float q[64];
     {
@@ -329,7 +330,7 @@ __global__ void __launch_bounds__(128) k_dec_attn(bf16_t *O, const bf16_t *Q, co
         }
     }
     float mx = -1e30f;
-    for (int s = lo + lane; s <= t; s += 32) {
+    for (int s = lo + tid; s <= t; s += 128) {
         const uint4 *kp = reinterpret_cast<const uint4 *>(Kc + ((size_t)b * Tm + s) * KD + kvh * 64);
         float dot = 0.0f;
 #pragma unroll
@@ -344,19 +345,43 @@ __global__ void __launch_bounds__(128) k_dec_attn(bf16_t *O, const bf16_t *Q, co
         mx = fmaxf(mx, dot);
     }
     mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
     float l = 0.0f;
-    for (int s = lo + lane; s <= t; s += 32) { const float p = __expf(sc[s] - mx); sc[s] = p; l += p; }
+    for (int s = lo + tid; s <= t; s += 128) { const float p = __expf(sc[s] - mx); sc[s] = p; l += p; }
     l = warp_sum(l);
-    __syncwarp();
+    if (lane == 0) red[warp] = l;
+    __syncthreads();
+    l = (red[0] + red[1]) + (red[2] + red[3]);
+    // pass 2: warp w takes keys lo + w, lo + w + 4, ...
     float a0 = 0.0f, a1 = 0.0f;
-    for (int s = lo; s <= t; s++) {
-        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162 *>(Vc + ((size_t)b * Tm + s) * KD + kvh * 64 + 2 * lane);
-        const float2 f = __bfloat1622float2(v2);
+    const bf16_t *vb = Vc + (size_t)b * Tm * KD + kvh * 64 + 2 * lane;
+    int s = lo + warp;
+    for (; s + 12 <= t; s += 16) {
+        float2 f[4]; float p[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            f[k] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(vb + (size_t)(s + 4 * k) * KD));
+            p[k] = sc[s + 4 * k];
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) { a0 += p[k] * f[k].x; a1 += p[k] * f[k].y; }
+    }
+    for (; s <= t; s += 4) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(vb + (size_t)s * KD));
         const float p = sc[s];
         a0 += p * f.x; a1 += p * f.y;
     }
-    const float inv = 1.0f / l;
-    *reinterpret_cast<__nv_bfloat162 *>(O + (size_t)b * D + h * 64 + 2 * lane) = __floats2bfloat162_rn(a0 * inv, a1 * inv);
+    part[warp][2 * lane] = a0; part[warp][2 * lane + 1] = a1;
+    __syncthreads();
+    if (warp == 0) {
+        const float inv = 1.0f / l;
+        const float o0 = (part[0][2 * lane] + part[1][2 * lane]) + (part[2][2 * lane] + part[3][2 * lane]);
+        const float o1 = (part[0][2 * lane + 1] + part[1][2 * lane + 1]) + (part[2][2 * lane + 1] + part[3][2 * lane + 1]);
+        *reinterpret_cast<__nv_bfloat162 *>(O + (size_t)b * D + h * 64 + 2 * lane) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+    }
 }
 // Greedy pick of k_dec_sample (cudalm.cu:7078-7093: temp <= 0): arg-max with the lowest index on ties and the
 // log-probability of the pick.  One block per slot.
@@ -505,13 +530,13 @@ extern "C" int qlmb_dec_attn(void *O, const void *Q, const void *Kc, const void 
     QLMB_REQUIRE(O && Q && Kc && Vc && pos, "qlmb_dec_attn: NULL argument");
     QLMB_REQUIRE(hd == 64 && H > 0 && KV > 0 && H % KV == 0 && Tm > 0 && Tm <= DEC_TM_MAX, "qlmb_dec_attn: hd %d H %d KV %d Tm %d", hd, H, KV, Tm);
     if (B <= 0) return QLMB_OK;
-    const size_t smem = (size_t)4 * Tm * sizeof(float);
+    const size_t smem = (size_t)Tm * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        QLMB_CUDA(cudaFuncSetAttribute(k_dec_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * DEC_TM_MAX * (int)sizeof(float)));
+        QLMB_CUDA(cudaFuncSetAttribute(k_dec_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_TM_MAX * (int)sizeof(float)));
         configured = true;
     }
-    k_dec_attn<<<(unsigned)((B * H + 3) / 4), 128, smem, as_stream(stream)>>>((bf16_t *)O, (const bf16_t *)Q, (const bf16_t *)Kc,
+    k_dec_attn<<<(unsigned)(B * H), 128, smem, as_stream(stream)>>>((bf16_t *)O, (const bf16_t *)Q, (const bf16_t *)Kc,
                                                                               (const bf16_t *)Vc, pos, win, B, Tm, H, KV,
                                                                               1.0f / sqrtf((float)hd));
     QLMB_LAUNCH_CHECK("k_dec_attn");
