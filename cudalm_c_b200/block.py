@@ -25,9 +25,9 @@ def embed_bwd(G, dout, tok):
     check(lib().qlmb_embed_bwd(ptr(G), ptr(dout), _dt(dout), ptr(tok), tok.numel(), G.shape[1], G.shape[0], stream_ptr()))
 
 
-def rmsnorm_fwd(X, gamma, out_dtype=None):
+def rmsnorm_fwd(X, gamma, out_dtype=None, out=None):
     N, D = X.shape
-    O = torch.empty(N, D, dtype=out_dtype or X.dtype, device=X.device)
+    O = out if out is not None else torch.empty(N, D, dtype=out_dtype or X.dtype, device=X.device)
     rinv = torch.empty(N, dtype=torch.float32, device=X.device)
     check(lib().qlmb_rmsnorm_fwd(ptr(O), _dt(O), ptr(rinv), ptr(X), _dt(X), ptr(gamma), N, D, stream_ptr()))
     return O, rinv

@@ -166,7 +166,10 @@ class PeerExpertParallelLayer:
 
     launches_per_step = 22          # library kernels per forward+backward on a rank
 
-    def __init__(self, cfg, dev, rank, world, seed=1234, aux=0.03, group=None, weights=None):
+    def __init__(self, cfg, dev, rank, world, seed=1234, aux=0.03, group=None, weights=None, ext=None):
+        """ext (a model's own storage instead of the synthetic weights and inputs of the bench):
+        dict(q=[(codes, scales) of the local experts' W1, W3, W2], wr=router [D, E], dW=[three fp32 gradient
+        tensors of the local experts], dWr=[D, E])."""
         import ctypes as C
         from . import qlm
         from ._lib import EpPeers
@@ -177,15 +180,18 @@ class PeerExpertParallelLayer:
         self.el = el = E // world
         L = lib()
         gen = torch.Generator(device=dev); gen.manual_seed(seed)
-        self.q = []
-        for wi, (rows, cols) in enumerate(((D, F), (D, F), (F, D))):
+        self.q = list(ext["q"]) if ext is not None else []
+        for wi, (rows, cols) in enumerate(((D, F), (D, F), (F, D)) if ext is None else ()):
             full = weights[wi] if weights is not None else torch.randn(E * rows * cols, device=dev, generator=gen) * 0.02
             n = el * rows * cols
             Q = qlm.Qlm([(0, n)], n, dev)
             Q.init_from(full[rank * n:(rank + 1) * n].clone(), render=False)
             self.q.append((Q.d, Q.s))
             del full
-        self.wr = weights[3] if weights is not None else torch.randn(D, E, device=dev, generator=gen) * 0.02
+        if ext is not None:
+            self.wr = ext["wr"]
+        else:
+            self.wr = weights[3] if weights is not None else torch.randn(D, E, device=dev, generator=gen) * 0.02
         # window layout (identical on every rank)
         self.slots = world * K * N
         hb = L.qlmb_moe_arena_bytes(N, D, F, E, K)
@@ -244,14 +250,20 @@ class PeerExpertParallelLayer:
         self.assign = view(ap - self.win_ptr, (K * N,), torch.int32)
         self.assign_all = torch.empty(world, K * N, dtype=torch.int32, device=dev)
         self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.dW = [torch.zeros(el, D, F, device=dev), torch.zeros(el, D, F, device=dev), torch.zeros(el, F, D, device=dev)]
-        self.dWr = torch.zeros(D, E, device=dev)
-        g2 = torch.Generator(device=dev); g2.manual_seed(seed + 1000 + rank)
         self.fn, self.dout = self.fn_set[0], self.dout_set[0]
-        self.fn.copy_(torch.randn(N, D, device=dev, generator=g2).bfloat16())
-        self.fi = torch.randn(N, D, device=dev, generator=g2).bfloat16()
-        self.dout.copy_(torch.randn(N, D, device=dev, generator=g2).bfloat16())
-        self.out = torch.empty_like(self.fi); self.dfn = torch.empty_like(self.fi)
+        # inside a model the gradient arrives in the window just before backward(): the ranks then meet once more
+        # before the expert side pulls it (in forward the all-gather of the routing table already orders f_norm)
+        self.dynamic_inputs = ext is not None
+        if ext is not None:
+            self.dW, self.dWr = list(ext["dW"]), ext["dWr"]
+        else:
+            self.dW = [torch.zeros(el, D, F, device=dev), torch.zeros(el, D, F, device=dev), torch.zeros(el, F, D, device=dev)]
+            self.dWr = torch.zeros(D, E, device=dev)
+            g2 = torch.Generator(device=dev); g2.manual_seed(seed + 1000 + rank)
+            self.fn.copy_(torch.randn(N, D, device=dev, generator=g2).bfloat16())
+            self.fi = torch.randn(N, D, device=dev, generator=g2).bfloat16()
+            self.dout.copy_(torch.randn(N, D, device=dev, generator=g2).bfloat16())
+            self.out = torch.empty_like(self.fi); self.dfn = torch.empty_like(self.fi)
         if world > 1:
             dist.barrier(group=group)           # every window is mapped before the first step reads one
 
@@ -283,6 +295,8 @@ class PeerExpertParallelLayer:
         dfn = self.dfn if dfn is None else dfn
         L, st = lib(), stream_ptr()
         check(L.qlmb_ep_dgate(self.home, self.hptr, ptr(self.Ys), ptr(dout), st))
+        if self.dynamic_inputs:
+            self._barrier()         # every rank's dout is in its window before another rank's expert side reads it
         check(L.qlmb_ep_experts_backward(self.loc, self.eptr, self.home, self.hptr, self.peers, ptr(dout), self.N, self.K,
                                          ptr(self.dXs), ptr(self.dW[0]), ptr(self.dW[1]), ptr(self.dW[2]), beta, st))
         self._barrier()

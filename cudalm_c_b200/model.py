@@ -24,15 +24,16 @@ class Config:
 class Offsets:
     """Off (cudalm.cu:263-275): element offsets of every tensor in the flat parameter vector."""
 
-    def __init__(self, c):
+    def __init__(self, c, experts=None):
+        E_ = experts if experts is not None else c.E     # experts stored on this rank (expert parallelism)
         p = 0
         self.emb = p; p += c.V * c.D
         self.layers = []
         for _ in range(c.L):
             o = {}
             for name, n in (("an1", c.D), ("wq", c.D * c.D), ("wk", c.D * c.KD), ("wv", c.D * c.KD), ("wo", c.D * c.D),
-                            ("an2", c.D), ("wr", c.D * c.E), ("w1", c.E * c.D * c.F), ("w3", c.E * c.D * c.F),
-                            ("w2", c.E * c.F * c.D)):
+                            ("an2", c.D), ("wr", c.D * c.E), ("w1", E_ * c.D * c.F), ("w3", E_ * c.D * c.F),
+                            ("w2", E_ * c.F * c.D)):
                 o[name] = (p, n); p += n
             self.layers.append(o)
         self.nf = p; p += c.D
@@ -43,14 +44,43 @@ QUANT = ("wq", "wk", "wv", "wo", "w1", "w3", "w2")
 
 
 class QlmModel:
-    def __init__(self, cfg, device, seed=1, aux=0.0):
+    """With world > 1 (one process per GPU, torch.distributed): data parallel over the batch with the experts
+    sharded (rank r owns experts r*E/W .. of every layer, PeerExpertParallelLayer), everything else replicated;
+    the replicated gradients are all-reduced, the clip norm is global, every rank steps its own spans."""
+
+    def __init__(self, cfg, device, seed=1, aux=0.0, rank=0, world=1, group=None, init_blocks=None):
         c = self.c = cfg
         self.dev = device
-        o = self.o = Offsets(c)
-        gen = torch.Generator(device=device); gen.manual_seed(seed)
-        # cmd_new's init (cudalm.cu:7349-7365): N(0, 0.02), wo and w2 scaled by 1/sqrt(2L), norm gains 1
+        self.rank, self.world, self.group = rank, world, group
+        assert c.E % world == 0
+        self.el = el = c.E // world
+        o = self.o = Offsets(c, el)
+        # cmd_new's init (cudalm.cu:7349-7365): N(0, 0.02), wo and w2 scaled by 1/sqrt(2L), norm gains 1.
+        # Every tensor has its own generator (seed, layer, tensor), and the expert weights one per block of
+        # E / init_blocks experts, so that a rank of an expert-parallel run and a single-GPU run
+        # (init_blocks = that run's world) hold the same values whatever the local layout is.
         P = torch.empty(o.total, dtype=torch.float32, device=device)
-        P.normal_(0.0, 0.02, generator=gen)
+
+        def fill(dst, key):
+            gb = torch.Generator(device=device); gb.manual_seed(seed * 1000003 + key)
+            dst.normal_(0.0, 0.02, generator=gb)
+        fill(P[o.emb:o.emb + c.V * c.D], 1)
+        nb = init_blocks or world
+        eb = c.E // nb                                    # experts per block
+        for l, lo in enumerate(o.layers):
+            for ti, nm in enumerate(("wq", "wk", "wv", "wo", "wr")):
+                a, n = lo[nm]
+                fill(P[a:a + n], 1000 + l * 16 + ti)
+            for wi, nm in enumerate(("w1", "w3", "w2")):
+                a, n = lo[nm]
+                per = n // el
+                blk = None
+                for e in range(el):
+                    ge = rank * el + e                    # global expert
+                    if blk is None or ge % eb == 0:
+                        blk = torch.empty(eb * per, dtype=torch.float32, device=device)
+                        fill(blk, 100000 + ((l * 3 + wi) * 64 + ge // eb) * 7)
+                    P[a + e * per:a + (e + 1) * per] = blk[(ge % eb) * per:(ge % eb + 1) * per]
         sc = 1.0 / math.sqrt(2.0 * c.L)
         for lo in o.layers:
             for nm in ("wo", "w2"):
@@ -75,8 +105,17 @@ class QlmModel:
         self.layers = []
         for l, lo in enumerate(o.layers):
             w = {nm: self._codes(7 * l + i) for i, nm in enumerate(QUANT)}
-            m = moe.MoeLayerState(N, c.D, c.F, c.E, c.K, w["w1"], w["w3"], w["w2"], self.fl[l]["wr"].view(c.D, c.E), aux=aux)
+            if world > 1:
+                from . import dist_moe
+                gv = lambda nm, shape: self._g(l, nm).view(*shape)
+                ext = dict(q=[w["w1"], w["w3"], w["w2"]], wr=self.fl[l]["wr"].view(c.D, c.E),
+                           dW=[gv("w1", (el, c.D, c.F)), gv("w3", (el, c.D, c.F)), gv("w2", (el, c.F, c.D))], dWr=gv("wr", (c.D, c.E)))
+                m = dist_moe.PeerExpertParallelLayer(dict(N=N, D=c.D, F=c.F, E=c.E, K=c.K), device, rank, world, aux=aux,
+                                                     group=group, ext=ext)
+            else:
+                m = moe.MoeLayerState(N, c.D, c.F, c.E, c.K, w["w1"], w["w3"], w["w2"], self.fl[l]["wr"].view(c.D, c.E), aux=aux)
             self.layers.append(dict(w=w, moe=m))
+        self.pending = []
         self.t = 0
         self.gs = torch.ones(2, dtype=torch.float32, device=device)
 
@@ -115,8 +154,12 @@ class QlmModel:
             block.rope(kh, self.cosb, self.sinb, c.KV, c.hd, T)
             att, lse = attn.attn_fwd(qh, kh, vh, B, T, c.H, c.KV)
             f_in = linear.linear_fwd(att, *w["wo"], KN, c.D, R=x)
-            f_norm, r2 = block.rmsnorm_fwd(f_in, f["an2"])
-            out = mo.forward(f_in, f_norm)
+            if self.world > 1 and moes is None:
+                f_norm, r2 = block.rmsnorm_fwd(f_in, f["an2"], out=mo.fn_set[0])       # read by the other ranks
+                out = mo.forward(fi=f_in, fn=f_norm, out=torch.empty_like(f_in))
+            else:
+                f_norm, r2 = block.rmsnorm_fwd(f_in, f["an2"])
+                out = mo.forward(f_in, f_norm)
             self.saved.append(dict(a_in=x, a_norm=a_norm, r1=r1, q=qh, k=kh, v=vh, att=att, lse=lse, f_in=f_in, f_norm=f_norm, r2=r2))
             x = out
         self.x_final = x
@@ -129,15 +172,20 @@ class QlmModel:
         G = self.G
         G_emb = G[o.emb:o.emb + c.V * c.D].view(c.V, c.D)
         G_emb.zero_()
-        loss, dfn = block.head_bwd(self.fn, self.emb, tgt, G_emb, chunk_rows=2048)
+        loss, dfn = block.head_bwd(self.fn, self.emb, tgt, G_emb, chunk_rows=2048, denom=N * self.world)
         g_nf = G[o.nf:o.nf + c.D]; g_nf.zero_()
         dout = torch.empty(N, c.D, dtype=torch.bfloat16, device=self.dev)
         block.rmsnorm_bwd(dout, self.x_final, self.nf, self.fnr, dfn, dgamma=g_nf, accumulate=False)
         for l in range(c.L - 1, -1, -1):
             ly, s, f, w = self.layers[l], self.saved[l], self.fl[l], self.layers[l]["w"]
             gv = lambda nm, shape: self._g(l, nm).view(*shape)
-            dfnorm = ly["moe"].backward(dout, s["f_norm"], gv("w1", (c.E, c.D, c.F)), gv("w3", (c.E, c.D, c.F)),
-                                        gv("w2", (c.E, c.F, c.D)), gv("wr", (c.D, c.E)), beta=0.0)
+            if self.world > 1:
+                mo = ly["moe"]
+                mo.dout_set[0].copy_(dout)                                                   # read by the other ranks
+                dfnorm = mo.backward(dout=mo.dout_set[0], fn=s["f_norm"], beta=0.0, dfn=torch.empty_like(dout))
+            else:
+                dfnorm = ly["moe"].backward(dout, s["f_norm"], gv("w1", (c.E, c.D, c.F)), gv("w3", (c.E, c.D, c.F)),
+                                            gv("w2", (c.E, c.F, c.D)), gv("wr", (c.D, c.E)), beta=0.0)
             g = self._g(l, "an2"); g.zero_()
             block.rmsnorm_bwd(dout, s["f_in"], f["an2"], s["r2"], dfnorm, dgamma=g)          # dout now = d f_in
             d_att = linear.linear_dgrad(dout, *w["wo"], KN, c.D)
@@ -153,7 +201,13 @@ class QlmModel:
             linear.linear_wgrad(gv("wv", (c.D, c.KD)), dv, s["a_norm"], KN, beta=0.0)
             g = self._g(l, "an1"); g.zero_()
             block.rmsnorm_bwd(dout, s["a_in"], f["an1"], s["r1"], d_an, dgamma=g)             # dout now = d a_in
+            if self.world > 1:      # an1 wq wk wv wo an2 wr are one contiguous range of G: sum over the ranks, overlapped
+                a0, a1 = o.layers[l]["an1"][0], o.layers[l]["wr"][0] + o.layers[l]["wr"][1]
+                self.pending.append(torch.distributed.all_reduce(G[a0:a1], group=self.group, async_op=True))
         block.embed_bwd(G_emb, dout, tok)
+        if self.world > 1:
+            self.pending.append(torch.distributed.all_reduce(G_emb, group=self.group, async_op=True))
+            self.pending.append(torch.distributed.all_reduce(g_nf, group=self.group, async_op=True))
         self.saved = None
         return loss
 
@@ -163,7 +217,27 @@ class QlmModel:
         spans, bf16-moment AdamW over the float spans, servo tick every 100 steps."""
         self.t += 1
         q = self.q
-        qlm.gnorm(self.G, out=self.gs)
+        for w in self.pending:
+            w.wait()
+        self.pending = []
+        if self.world > 1:
+            # replicated ranges are identical on every rank after the all-reduce; the expert ranges are this rank's
+            # share of the squared norm: their 64-float partial sums are added over the ranks, then the norm is closed
+            c, o = self.c, self.o
+            L_ = c.L
+            if not hasattr(self, "gpart"):
+                self.gpart = torch.zeros(64 * (2 * L_ + 2), dtype=torch.float32, device=self.dev)
+            k = 0
+            rep = [(o.emb, c.V * c.D), (o.nf, c.D)] + [(lo["an1"][0], lo["wr"][0] + lo["wr"][1] - lo["an1"][0]) for lo in o.layers]
+            for a, n in rep:
+                qlm.sqsum(self.G[a:a + n], self.gpart[64 * k:64 * k + 64]); k += 1
+            for lo in o.layers:
+                a, n = lo["w1"][0], lo["w2"][0] + lo["w2"][1] - lo["w1"][0]
+                qlm.sqsum(self.G[a:a + n], self.gpart[64 * k:64 * k + 64]); k += 1
+            torch.distributed.all_reduce(self.gpart[64 * (L_ + 2):], group=self.group)
+            qlm.gnorm_close(self.gpart, 2 * L_ + 2, self.gs)
+        else:
+            qlm.gnorm(self.G, out=self.gs)
         q.step(None, self.G, lr, b1, b2, wd, self.t, gscale=1.0, gsp=self.gs)
         bc1, bc2 = qlm.bias_corrections(b1, b2, self.t)
         for (off, n, cs), pt in zip(q.fs, self.fp):

@@ -25,7 +25,7 @@ def rel(a, b):
     return max(float((a - b).norm() / b.norm()), float((a - b).abs().max() / b.abs().max()))
 
 
-def worker(rank, world, port, ret, mode):
+def worker(rank, world, port, ret, mode, cfg=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
@@ -33,7 +33,7 @@ def worker(rank, world, port, ret, mode):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     import cudalm_c_b200 as q
     from cudalm_c_b200 import dist_moe, moe, qlm
-    c = CFG
+    c = cfg or CFG
     N, D, F, E, K = c["N"], c["D"], c["F"], c["E"], c["K"]
     gen = torch.Generator(device=dev); gen.manual_seed(7)
     full = [torch.randn(E * D * F, device=dev, generator=gen) * 0.02 for _ in range(3)]
@@ -77,4 +77,74 @@ def test_expert_parallel_matches_single_call(cuda, mode):
     with mp.Manager() as m:
         ret = m.dict()
         mp.spawn(worker, args=(world, free_port(), ret, mode), nprocs=world, join=True)
+        assert all(ret.get(r) for r in range(world))
+
+
+def test_expert_parallel_small_layer(cuda):
+    """The peer form on the smallest layer the training-step test uses (256 tokens, 4 experts of 128 x 128)."""
+    world = min(torch.cuda.device_count(), 2)
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(worker, args=(world, free_port(), ret, "peer", dict(N=256, D=128, F=128, E=4, K=2)), nprocs=world, join=True)
+        assert all(ret.get(r) for r in range(world))
+
+
+def worker_dp(rank, world, port, ret):
+    """Data-parallel training step with sharded experts (cudalm_c_b200/model.py, world > 1) against the
+    single-GPU step on the concatenated batch: same losses, same gradients (replicated tensors after the
+    all-reduce, this rank's experts), same clip norm."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import model
+    kw = dict(L=2, D=128, H=2, KV=2, hd=64, E=4, K=2, F=128, V=256, T=128)
+    Bl = 2
+    g = torch.Generator(device="cpu"); g.manual_seed(0)
+    Nall = world * Bl * kw["T"]
+    tok_all = torch.randint(0, kw["V"], (Nall,), generator=g, dtype=torch.int32).to(dev)
+    tgt_all = torch.randint(0, kw["V"], (Nall,), generator=g, dtype=torch.int32).to(dev)
+    N = Bl * kw["T"]
+    sl = slice(rank * N, (rank + 1) * N)
+    m = model.QlmModel(model.Config(B=Bl, **kw), dev, seed=3, rank=rank, world=world, init_blocks=world)
+    m.forward(tok_all[sl].contiguous())
+    loss = m.backward(tok_all[sl].contiguous(), tgt_all[sl].contiguous())
+    m.update()
+    torch.cuda.synchronize()
+    ref = model.QlmModel(model.Config(B=world * Bl, **kw), dev, seed=3, init_blocks=world)
+    ref.forward(tok_all)
+    loss_ref = ref.backward(tok_all, tgt_all)
+    ref.update()
+    torch.cuda.synchronize()
+    q.check(q.lib().qlmb_check_device(None))
+    assert float((loss - loss_ref[sl]).abs().max()) < 2e-3
+    c, el = m.c, m.el
+
+    def rel(a, b):
+        return float((a.double() - b.double()).norm() / b.double().norm())
+    errs = {}
+    for l in range(c.L):
+        for nm in ("an1", "wq", "wk", "wv", "wo", "an2", "wr"):
+            errs[(l, nm)] = rel(m._g(l, nm), ref._g(l, nm))
+        for nm in ("w1", "w3", "w2"):
+            n = m.o.layers[l][nm][1]
+            errs[(l, nm)] = rel(m._g(l, nm), ref._g(l, nm)[rank * n:(rank + 1) * n])
+    errs["emb"] = rel(m.G[:c.V * c.D], ref.G[:c.V * c.D])
+    bad = {k: round(v, 4) for k, v in errs.items() if not v < 2e-2}
+    assert not bad, (bad, {k: round(v, 5) for k, v in errs.items()})
+    assert abs(float(m.gs[1]) - float(ref.gs[1])) < 1e-2 * float(ref.gs[1])
+    if world > 1:
+        for ly in m.layers:
+            ly["moe"].close()
+    ret[rank] = True
+    dist.destroy_process_group()
+
+
+def test_data_parallel_training_step(cuda):
+    world = min(torch.cuda.device_count(), 2)
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(worker_dp, args=(world, free_port(), ret), nprocs=world, join=True)
         assert all(ret.get(r) for r in range(world))
