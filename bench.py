@@ -547,12 +547,17 @@ def run_train(args):
     import torch
     import cudalm_c_b200 as q
     from cudalm_c_b200 import model
+    import torch.distributed as dist
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     cfg = model.Config()
-    m = model.QlmModel(cfg, dev, seed=1, aux=0.03)
+    m = model.QlmModel(cfg, dev, seed=1, aux=0.03, rank=rank, world=world)
     N = cfg.B * cfg.T
-    g = torch.Generator(device="cpu"); g.manual_seed(0)
+    g = torch.Generator(device="cpu"); g.manual_seed(rank)
     toks = [torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).pin_memory() for _ in range(4)]
     tgts = [torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).pin_memory() for _ in range(4)]
     losses = []
@@ -565,6 +570,9 @@ def run_train(args):
     for i in range(max(args.warmup, 3)):
         step(i)
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
@@ -572,19 +580,31 @@ def run_train(args):
     e1.record(); torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     q.check(q.lib().qlmb_check_device(None))
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)            # the slowest rank sets the step time
+        ms = float(t)
+        dist.barrier()
+        for ly in m.layers:
+            ly["moe"].close()
+        if rank != 0:
+            dist.destroy_process_group()
+            return
     pk = peaks()
     # 6 x active matmul parameters per token + causal attention (forward 2, backward 5 GEMMs of T x T/2 x 64 per head)
     act = cfg.L * (2 * cfg.D * cfg.D + 2 * cfg.D * cfg.KD + cfg.D * cfg.E + cfg.K * 3 * cfg.D * cfg.F) + cfg.V * cfg.D
     flops = 6.0 * act * N + cfg.L * 7 * 2.0 * cfg.B * cfg.H * (cfg.T * (cfg.T + 1) // 2) * cfg.hd
-    tps = N / (ms * 1e-3)
-    print(json.dumps(dict(metric="qlm_train_tokens_per_s", value=round(tps, 1), unit="tokens/s", n_gpus=1, steps=args.steps,
+    tps = world * N / (ms * 1e-3)
+    print(json.dumps(dict(metric="qlm_train_tokens_per_s", value=round(tps, 1), unit="tokens/s", n_gpus=world, steps=args.steps,
                           warmup=max(args.warmup, 3), ms_per_step=round(ms, 3), higher_is_better=True, scaling="weak",
                           vs_baseline=None, dtype="bf16", data="synthetic",
-                          config=dict(workload="QLM training step, MoE transformer (BASELINE config 4)", L=cfg.L, D=cfg.D, heads=cfg.H,
+                          config=dict(workload="QLM training step, MoE transformer (BASELINE config 4)",
+                                      parallelism="single" if world == 1 else "dp%d x ep%d (batch split, experts sharded over peer memory, replicated gradients all-reduced)" % (world, world),
+                                      L=cfg.L, D=cfg.D, heads=cfg.H,
                                       experts=cfg.E, top_k=cfg.K, F=cfg.F, V=cfg.V, B=cfg.B, T=cfg.T,
                                       params_quantised=int(m.q.nq), params_float=int(m.q.nfloat),
                                       l2="weights 0.74 GB of codes, activations and gradients several GB per step: far beyond the 126 MB L2"),
-                          roofline=dict(bound="tensor", kernel="whole step", achieved=round(flops / (ms * 1e-3) / 1e12, 1),
+                          roofline=dict(bound="tensor", kernel="whole step", achieved=round(flops / (ms * 1e-3) / 1e12, 1),   # per GPU
                                         peak=pk["tf_sustained"], unit="TFLOP/s",
                                         frac=round(flops / (ms * 1e-3) / 1e12 / pk["tf_sustained"], 4),
                                         traffic=None, peak_kind="sustained bf16, of " + pk["src"], model_flops_per_step=flops),
@@ -593,6 +613,8 @@ def run_train(args):
                                    how="token ids and targets copied from pinned host memory inside the timed region, mean loss read back every step"),
                           loss_first=round(losses[0], 4), loss_last=round(losses[-1], 4),
                           gpu_launches=None)))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_decode(args):
