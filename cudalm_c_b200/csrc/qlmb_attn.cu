@@ -77,6 +77,13 @@ __device__ __forceinline__ bool at_wait(uint32_t bar, uint32_t parity, volatile 
 }
 __device__ __forceinline__ bool at_error_seen(const int *errword) { return errword && *reinterpret_cast<const volatile int *>(errword) != 0; }
 
+// 2^x on the special-function unit (ex2.approx: 2 ulp, flushes denormal results to zero, -inf -> 0)
+__device__ __forceinline__ float ex2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ bool attn_valid(int key, int i, int T, int win)
 {
     return key <= i && key < T && (win <= 0 || key > i - win);
@@ -209,13 +216,14 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
         for (int d = 0; d < AT_HD; d++) o[d] = 0.0f;
         bool ok = true;
         auto fold_pv = [&]() {                 // O = O * corr + PV for the tile whose PV just completed
+            uint32_t v0[32], v1[32];             // both TMEM loads in flight: one round trip
+            tmem_ld32(tPV + lane_base, v0);
+            tmem_ld32(tPV + lane_base + 32, v1);
+            tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                uint32_t v[32];
-                tmem_ld32(tPV + lane_base + c * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; j++) o[c * 32 + j] = o[c * 32 + j] * corr_pend + __uint_as_float(v[j]);
+            for (int j = 0; j < 32; j++) {
+                o[j] = o[j] * corr_pend + __uint_as_float(v0[j]);
+                o[32 + j] = o[32 + j] * corr_pend + __uint_as_float(v1[j]);
             }
         };
         for (int t = 0; ok && t < nt; t++) {
@@ -227,21 +235,25 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
             // pass 1: row maximum
             float mx = -1e30f;
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[32];
-                tmem_ld32(tS + lane_base + c * 32, v);
+            for (int c = 0; c < 4; c += 2) {             // two 32-column loads per round trip
+                uint32_t v[2][32];
+                tmem_ld32(tS + lane_base + c * 32, v[0]);
+                tmem_ld32(tS + lane_base + c * 32 + 32, v[1]);
                 tmem_ld_wait();
-                if (masked) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (attn_valid(k0 + c * 32 + j, i, p.T, p.win)) mx = fmaxf(mx, __uint_as_float(v[j]));
-                } else {
+                for (int cc = 0; cc < 2; cc++) {
+                    if (masked) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(v[j]));
+                        for (int j = 0; j < 32; j++)
+                            if (attn_valid(k0 + (c + cc) * 32 + j, i, p.T, p.win)) mx = fmaxf(mx, __uint_as_float(v[cc][j]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(v[cc][j]));
+                    }
                 }
             }
             const float m_new = fmaxf(m, mx * p.scale_log2);
-            const float corr = exp2f(m - m_new);
+            const float corr = ex2(m - m_new);
             // the previous tile's PV: its MMA was issued before this tile's S, so it has completed
             if (t > 0) {
                 ok = at_wait(smem_u32(o_full), (uint32_t)(t - 1) & 1u, abort_flag, p.errword, 121);
@@ -260,8 +272,8 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
                 uint32_t pk[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
-                    float p0 = exp2f(__uint_as_float(v[j]) * p.scale_log2 - m_new);
-                    float p1 = exp2f(__uint_as_float(v[j + 1]) * p.scale_log2 - m_new);
+                    float p0 = ex2(__uint_as_float(v[j]) * p.scale_log2 - m_new);
+                    float p1 = ex2(__uint_as_float(v[j + 1]) * p.scale_log2 - m_new);
                     if (masked) {
                         if (!attn_valid(k0 + c * 32 + j, i, p.T, p.win)) p0 = 0.0f;
                         if (!attn_valid(k0 + c * 32 + j + 1, i, p.T, p.win)) p1 = 0.0f;
@@ -530,12 +542,15 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
             if (!ok) break;
             tc_fence_after();
             const float *L2 = sL + st * 128 + hf * 64, *Dq = sD + st * 128 + hf * 64;
+            uint32_t svv[2][32], dvv[2][32];         // all four TMEM loads of the step in flight: one round trip
+            tmem_ld32(tS + lane_base + hf * 64, svv[0]);
+            tmem_ld32(tP + lane_base + hf * 64, dvv[0]);
+            tmem_ld32(tS + lane_base + hf * 64 + 32, svv[1]);
+            tmem_ld32(tP + lane_base + hf * 64 + 32, dvv[1]);
+            tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < 2; c++) {
-                uint32_t sv[32], dv[32];
-                tmem_ld32(tS + lane_base + hf * 64 + c * 32, sv);
-                tmem_ld32(tP + lane_base + hf * 64 + c * 32, dv);
-                tmem_ld_wait();
+                const uint32_t *sv = svv[c], *dv = dvv[c];
                 uint32_t pp[16], ds[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
@@ -543,7 +558,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
 #pragma unroll
                     for (int e = 0; e < 2; e++) {
                         const int col = c * 32 + j + e, qi = q0 + hf * 64 + col;
-                        float pe = exp2f(__uint_as_float(sv[j + e]) * p.scale_log2 - L2[col]);
+                        float pe = ex2(__uint_as_float(sv[j + e]) * p.scale_log2 - L2[col]);
                         if (masked && !(key <= qi && (p.win <= 0 || key > qi - p.win))) pe = 0.0f;
                         pv[e] = pe;
                         dsv[e] = pe * (__uint_as_float(dv[j + e]) - Dq[col]) * p.scale;
@@ -709,12 +724,15 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
             if (ok && t > 0) ok = at_wait(smem_u32(acc_done), (uint32_t)(t - 1) & 1u, abort_flag, p.errword, 322);
             if (!ok) break;
             tc_fence_after();
+            uint32_t svv[2][32], dvv[2][32];         // all four TMEM loads of the step in flight: one round trip
+            tmem_ld32(tS + lane_base + hf * 64, svv[0]);
+            tmem_ld32(tP + lane_base + hf * 64, dvv[0]);
+            tmem_ld32(tS + lane_base + hf * 64 + 32, svv[1]);
+            tmem_ld32(tP + lane_base + hf * 64 + 32, dvv[1]);
+            tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < 2; c++) {
-                uint32_t sv[32], dv[32];
-                tmem_ld32(tS + lane_base + hf * 64 + c * 32, sv);
-                tmem_ld32(tP + lane_base + hf * 64 + c * 32, dv);
-                tmem_ld_wait();
+                const uint32_t *sv = svv[c], *dv = dvv[c];
                 uint32_t ds[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
@@ -722,7 +740,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
 #pragma unroll
                     for (int e = 0; e < 2; e++) {
                         const int key = k0 + hf * 64 + c * 32 + j + e;
-                        float pe = exp2f(__uint_as_float(sv[j + e]) * p.scale_log2 - L2);
+                        float pe = ex2(__uint_as_float(sv[j + e]) * p.scale_log2 - L2);
                         if (masked && !attn_valid(key, i, p.T, p.win)) pe = 0.0f;
                         dsv[e] = pe * (__uint_as_float(dv[j + e]) - Dq) * p.scale;
                     }
