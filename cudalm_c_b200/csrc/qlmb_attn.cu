@@ -265,10 +265,15 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
             // pass 2: P = exp2(s - m) as bf16 into the swizzled K-major tile, row sum
             float rs = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[32];
-                tmem_ld32(tS + lane_base + c * 32, v);
-                tmem_ld_wait();
+            for (int cp = 0; cp < 2; cp++) {
+              uint32_t vv[2][32];                        // two 32-column loads per round trip
+              tmem_ld32(tS + lane_base + cp * 64, vv[0]);
+              tmem_ld32(tS + lane_base + cp * 64 + 32, vv[1]);
+              tmem_ld_wait();
+#pragma unroll
+              for (int cc = 0; cc < 2; cc++) {
+                const int c = cp * 2 + cc;
+                const uint32_t *v = vv[cc];
                 uint32_t pk[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
@@ -288,6 +293,7 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
                     const int unit = ((c & 1) * 4 + u) ^ (r & 7);
                     *reinterpret_cast<uint4 *>(rowp + unit * 16) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
                 }
+              }
             }
             l = l * corr + rs;
             m = m_new;
