@@ -69,6 +69,7 @@ PROTOTYPES = {
     "qlmb_dec_kv": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, vp]),
     "qlmb_dec_attn": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "qlmb_dec_greedy": (ci, [vp, vp, vp, ci, ci, vp]),
+    "qlmb_dec_sample": (ci, [vp, vp, vp, vp, ci, ci, vp]),
     "qlmb_attn_fwd": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "qlmb_attn_bwd": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "qlmb_adamw": (ci, [vp, vp, vp, vp, sz, cf, cf, cf, cf, cf, cf, vp, vp]),

@@ -815,10 +815,14 @@ extern "C" int qlmb_attn_fwd(void *O, float *lse, const void *Q, const void *K, 
     p.nqt = (T + AT_BM - 1) / AT_BM;
     p.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
     p.errword = device_error_word();
-    static bool configured = false;
-    if (!configured) {
+    // the attribute belongs to a device's copy of the kernel: set it once per device of this process
+    static bool configured_dev[64];
+    int dev_ = 0;
+    QLMB_CUDA(cudaGetDevice(&dev_));
+    QLMB_REQUIRE(dev_ >= 0 && dev_ < 64, "device index %d", dev_);
+    if (!configured_dev[dev_]) {
         QLMB_CUDA(cudaFuncSetAttribute(k_attn_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_FWD_SMEM));
-        configured = true;
+        configured_dev[dev_] = true;
     }
     k_attn_fwd<<<(unsigned)(p.nqt * B * H), 192, AT_FWD_SMEM, as_stream(stream)>>>(p);
     QLMB_LAUNCH_CHECK("k_attn_fwd");
@@ -850,11 +854,15 @@ extern "C" int qlmb_attn_bwd(void *dQ, void *dK, void *dV, float *drow, const vo
     p.scale = 1.0f / sqrtf((float)hd);
     p.scale_log2 = 1.4426950408889634f * p.scale;
     p.errword = device_error_word();
-    static bool configured = false;
-    if (!configured) {
+    // the attribute belongs to a device's copy of the kernel: set it once per device of this process
+    static bool configured_dev[64];
+    int dev_ = 0;
+    QLMB_CUDA(cudaGetDevice(&dev_));
+    QLMB_REQUIRE(dev_ >= 0 && dev_ < 64, "device index %d", dev_);
+    if (!configured_dev[dev_]) {
         QLMB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_DKV_SMEM));
         QLMB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_DQ_SMEM));
-        configured = true;
+        configured_dev[dev_] = true;
     }
     cudaStream_t st = as_stream(stream);
     const size_t nrow = (size_t)B * T * H;

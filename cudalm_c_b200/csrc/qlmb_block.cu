@@ -414,6 +414,112 @@ __global__ void __launch_bounds__(256) k_dec_greedy(int *out, float *lp, const f
     }
 }
 
+
+// The sampling branch of k_dec_sample (cudalm.cu:7078-7108): top_k -> top_p -> temperature.
+// One block of 1024 threads per slot.  (1) arg-max and log-sum-exp as in the greedy pick; (2) a value
+// threshold, starting 30 below the maximum and halving its distance to it until at most DEC_SCAP
+// logits pass; (3) the passing (value, index) pairs are compacted into shared memory and sorted by
+// value descending, index ascending (bitonic network; the index as tie-break makes the order, and
+// with it the pick, independent of the order the compaction's counter handed out slots);
+// (4) thread 0 cuts the list at top_k, then at the first prefix whose probability reaches top_p,
+// and draws from exp((v - v0) / temp) with a uniform number hashed from (seed, step).
+#define DEC_SCAP 2048
+__device__ __forceinline__ bool samp_before(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+__global__ void __launch_bounds__(1024) k_dec_sample(int *out, float *lp, const float *logits, const qlmb_dec_sampling *sp, int V)
+{
+    __shared__ float sv[DEC_SCAP];
+    __shared__ int si[DEC_SCAP];
+    __shared__ float rv[32], rz[32];
+    __shared__ int ri[32];
+    __shared__ int cnt;
+    __shared__ float sth;
+    const int s = blockIdx.x, t = threadIdx.x, w = t >> 5, ln = t & 31;
+    const float *lg = logits + (size_t)s * V;
+    const qlmb_dec_sampling prm = sp[s];
+    float mx = -INFINITY; int mi = 0;
+    for (int i = t; i < V; i += 1024) { const float v = lg[i]; if (v > mx) { mx = v; mi = i; } }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        const float ov = __shfl_xor_sync(~0u, mx, o); const int oi = __shfl_xor_sync(~0u, mi, o);
+        if (samp_before(ov, oi, mx, mi)) { mx = ov; mi = oi; }
+    }
+    if (!ln) { rv[w] = mx; ri[w] = mi; }
+    __syncthreads();
+    mx = rv[0]; mi = ri[0];
+    for (int k = 1; k < 32; k++) if (samp_before(rv[k], ri[k], mx, mi)) { mx = rv[k]; mi = ri[k]; }
+    const float M = mx;
+    float z = 0.0f;
+    for (int i = t; i < V; i += 1024) z += __expf(lg[i] - M);
+    z = warp_sum(z);
+    if (!ln) rz[w] = z;
+    __syncthreads();
+    float ssum = 0.0f;
+    for (int k = 0; k < 32; k++) ssum += rz[k];
+    const float ls = M + logf(ssum);
+    if (prm.temp <= 0.0f || prm.top_k == 1) {
+        if (!t) { out[s] = mi; lp[s] = M - ls; }
+        return;
+    }
+    // (2) threshold
+    float th = M - 30.0f;
+    for (int round = 0; round < 64; round++) {
+        __syncthreads();
+        if (!t) cnt = 0;
+        __syncthreads();
+        int c = 0;
+        for (int i = t; i < V; i += 1024) c += lg[i] >= th;
+        c = (int)warp_sum((float)c);
+        if (!ln && c) atomicAdd(&cnt, c);
+        __syncthreads();
+        if (cnt <= DEC_SCAP) break;
+        th = 0.5f * (th + M);
+    }
+    // (3) compaction and sort
+    __syncthreads();
+    if (!t) cnt = 0;
+    __syncthreads();
+    for (int i = t; i < V; i += 1024) {
+        const float v = lg[i];
+        if (v >= th) { const int k = atomicAdd(&cnt, 1); if (k < DEC_SCAP) { sv[k] = v; si[k] = i; } }
+    }
+    __syncthreads();
+    const int n = cnt < DEC_SCAP ? cnt : DEC_SCAP;
+    int P2 = 1;
+    while (P2 < n) P2 <<= 1;
+    for (int i = n + t; i < P2; i += 1024) { sv[i] = -INFINITY; si[i] = 0x7fffffff; }
+    __syncthreads();
+    for (int k = 2; k <= P2; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = t; i < P2; i += 1024) {
+                const int ij = i ^ j;
+                if (ij > i) {
+                    const float a = sv[i], b = sv[ij]; const int ia = si[i], ib = si[ij];
+                    const bool up = (i & k) == 0;              // this pair sorts towards "best first"
+                    if (up ? samp_before(b, ib, a, ia) : samp_before(a, ia, b, ib)) { sv[i] = b; sv[ij] = a; si[i] = ib; si[ij] = ia; }
+                }
+            }
+            __syncthreads();
+        }
+    if (t) return;
+    // (4) cut and draw
+    int k = prm.top_k > 0 ? (prm.top_k < n ? prm.top_k : n) : n;
+    float zz = 0.0f;
+    for (int i = 0; i < k; i++) zz += __expf(sv[i] - sv[0]);
+    if (prm.top_p < 1.0f) {
+        float c = 0.0f;
+        for (int i = 0; i < k; i++) { c += __expf(sv[i] - sv[0]) / zz; if (c >= prm.top_p) { k = i + 1; break; } }
+    }
+    const float it = 1.0f / prm.temp;
+    zz = 0.0f;
+    for (int i = 0; i < k; i++) zz += __expf((sv[i] - sv[0]) * it);
+    unsigned long long h = prm.seed * 0x9E3779B97F4A7C15ull + (unsigned long long)(prm.step + 1) * 0xD1B54A32D192ED03ull;
+    h ^= h >> 30; h *= 0xBF58476D1CE4E5B9ull; h ^= h >> 27; h *= 0x94D049BB133111EBull; h ^= h >> 31;
+    float u = (float)(h >> 40) * (1.0f / 16777216.0f) * zz;
+    int pick = k - 1;
+    for (int i = 0; i < k; i++) { u -= __expf((sv[i] - sv[0]) * it); if (u <= 0.0f) { pick = i; break; } }
+    out[s] = si[pick]; lp[s] = sv[pick] - ls;
+}
+
 }  // namespace qlmb
 
 using namespace qlmb;
@@ -531,10 +637,14 @@ extern "C" int qlmb_dec_attn(void *O, const void *Q, const void *Kc, const void 
     QLMB_REQUIRE(hd == 64 && H > 0 && KV > 0 && H % KV == 0 && Tm > 0 && Tm <= DEC_TM_MAX, "qlmb_dec_attn: hd %d H %d KV %d Tm %d", hd, H, KV, Tm);
     if (B <= 0) return QLMB_OK;
     const size_t smem = (size_t)Tm * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
+    // the attribute belongs to a device's copy of the kernel: set it once per device of this process
+    static bool configured_dev[64];
+    int dev_ = 0;
+    QLMB_CUDA(cudaGetDevice(&dev_));
+    QLMB_REQUIRE(dev_ >= 0 && dev_ < 64, "device index %d", dev_);
+    if (!configured_dev[dev_]) {
         QLMB_CUDA(cudaFuncSetAttribute(k_dec_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_TM_MAX * (int)sizeof(float)));
-        configured = true;
+        configured_dev[dev_] = true;
     }
     k_dec_attn<<<(unsigned)(B * H), 128, smem, as_stream(stream)>>>((bf16_t *)O, (const bf16_t *)Q, (const bf16_t *)Kc,
                                                                               (const bf16_t *)Vc, pos, win, B, Tm, H, KV,
@@ -549,5 +659,15 @@ extern "C" int qlmb_dec_greedy(int *out, float *lp, const float *logits, int B, 
     if (B <= 0) return QLMB_OK;
     k_dec_greedy<<<(unsigned)B, 256, 0, as_stream(stream)>>>(out, lp, logits, V);
     QLMB_LAUNCH_CHECK("k_dec_greedy");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_dec_sample(int *out, float *lp, const float *logits, const qlmb_dec_sampling *params, int B, int V,
+                               void *stream)
+{
+    QLMB_REQUIRE(out && lp && logits && params && V > 0, "qlmb_dec_sample: bad argument");
+    if (B <= 0) return QLMB_OK;
+    k_dec_sample<<<(unsigned)B, 1024, 0, as_stream(stream)>>>(out, lp, logits, params, V);
+    QLMB_LAUNCH_CHECK("k_dec_sample");
     return QLMB_OK;
 }

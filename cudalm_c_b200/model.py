@@ -295,9 +295,35 @@ class Decoder:
         self.tok.copy_(self.otok)
         return self.logits
 
+    def set_sampling(self, temp=0.0, top_p=1.0, top_k=0, seed=0):
+        """Per-slot sampling parameters (the reference's DSP, cudalm.cu:7020); scalars or one value per slot.
+        temp <= 0 keeps the greedy pick.  The step counter the draw is hashed from advances on the device."""
+        import numpy as np
+        dt = np.dtype(dict(names=["temp", "top_p", "top_k", "seed", "step"], formats=["<f4", "<f4", "<i4", "<u8", "<i4"],
+                           offsets=[0, 4, 8, 16, 24], itemsize=32))
+        a = np.zeros(self.B, dt)
+        a["temp"], a["top_p"], a["top_k"], a["seed"] = temp, top_p, top_k, seed
+        self.sp = torch.from_numpy(a.view(np.uint8).reshape(self.B, 32).copy()).to(self.m.dev)
+        self.sp_step = self.sp.view(torch.int32)[:, 6]          # the `step` field of every slot
+
     def _pick(self):
         from ._lib import check, lib, ptr, stream_ptr
-        check(lib().qlmb_dec_greedy(ptr(self.otok), ptr(self.olp), ptr(self.logits), self.B, self.m.c.V, stream_ptr()))
+        if getattr(self, "sp", None) is not None:
+            check(lib().qlmb_dec_sample(ptr(self.otok), ptr(self.olp), ptr(self.logits), ptr(self.sp), self.B, self.m.c.V,
+                                        stream_ptr()))
+            self.sp_step += 1
+        else:
+            check(lib().qlmb_dec_greedy(ptr(self.otok), ptr(self.olp), ptr(self.logits), self.B, self.m.c.V, stream_ptr()))
+
+    def move(self, s, t):
+        """dec_move (cudalm.cu:7222-7231): slot s's state into slot t (continuous batching keeps live slots first)."""
+        n = int(self.pos[s])
+        for l in range(self.m.c.L):
+            self.K[l][t, :n] = self.K[l][s, :n]
+            self.V[l][t, :n] = self.V[l][s, :n]
+        self.pos[t] = self.pos[s]; self.tok[t] = self.tok[s]
+        if getattr(self, "sp", None) is not None:
+            self.sp[t] = self.sp[s]
 
     def step(self, advance=True):
         """dec_step: the token in self.tok at position self.pos for every slot; logits -> self.logits, greedy pick ->

@@ -372,6 +372,19 @@ int qlmb_dec_kv(void *Kc, void *Vc, const void *k, const void *v, const int *pos
  * max(0, pos-win+1) .. pos[b] (win <= 0: all); Q, O bf16 [B, H*hd]; hd = 64, Tm <= 4096. */
 int qlmb_dec_attn(void *O, const void *Q, const void *Kc, const void *Vc, const int *pos, int win, int B, int Tm, int H,
                   int KV, int hd, void *stream);
+/* Per-slot sampling parameters, the layout of the reference's DSP (cudalm.cu:7020). */
+typedef struct {
+    float temp, top_p;          /* temp <= 0: greedy; top_p >= 1: no nucleus cut */
+    int top_k;                  /* 0: no cut; 1: greedy */
+    unsigned long long seed;
+    int step;                   /* the draw is hashed from (seed, step) */
+} qlmb_dec_sampling;
+/* k_dec_sample (cudalm.cu:7048-7108): top_k -> top_p -> temperature over logits[b,:], greedy when
+ * temp <= 0 or top_k == 1; out[b] = the picked token, lp[b] = its log-probability under the
+ * unmodified distribution.  params is a device array of B entries.  Candidates are ordered by value
+ * and then by token index, so the pick does not depend on scheduling. */
+int qlmb_dec_sample(int *out, float *lp, const float *logits, const qlmb_dec_sampling *params, int B, int V,
+                    void *stream);
 /* The greedy branch of k_dec_sample (cudalm.cu:7078-7093, temp <= 0): out[b] = arg-max of logits[b,:] (lowest
  * index on ties), lp[b] = its log-probability. */
 int qlmb_dec_greedy(int *out, float *lp, const float *logits, int B, int V, void *stream);

@@ -44,3 +44,67 @@ def test_decoder_matches_full_forward(cuda):
     # greedy continuation runs without host input and picks the arg-max
     dec.step()
     assert torch.equal(dec.otok.long(), dec.logits.argmax(-1))
+
+
+def test_sampler_topk_topp_temperature(cuda):
+    """k_dec_sample (cudalm.cu:7048-7108) against a float64 restatement of its algorithm: arg-max and
+    log-probability, the top-k / top-p cut, and the pick that the (seed, step) hash selects from the tempered
+    distribution.  The device adds float32 exponentials, so the pick is accepted when the hashed number falls
+    within 1e-4 of the pick's interval of the cumulative distribution."""
+    import numpy as np
+    import cudalm_c_b200 as q
+    from cudalm_c_b200._lib import check, lib, ptr, stream_ptr
+    rng = np.random.default_rng(0)
+    V, B = 16384, 12
+    lg = (rng.standard_normal((B, V)) * 2.5).astype(np.float32)
+    lg[3, 100] = lg[3].max() + 3.0                               # a dominant token
+    dt = np.dtype(dict(names=["temp", "top_p", "top_k", "seed", "step"], formats=["<f4", "<f4", "<i4", "<u8", "<i4"],
+                       offsets=[0, 4, 8, 16, 24], itemsize=32))
+    prm = np.zeros(B, dt)
+    cases = [(0.0, 1.0, 0), (1.0, 1.0, 1), (1.0, 1.0, 0), (0.7, 0.9, 40), (1.3, 0.5, 0), (0.5, 1.0, 5),
+             (1.0, 0.95, 200), (2.0, 0.99, 0), (0.9, 0.8, 3), (1.0, 0.3, 0), (0.8, 1.0, 1000), (1.5, 0.7, 64)]
+    for b, (temp, top_p, top_k) in enumerate(cases):
+        prm[b] = (temp, top_p, top_k, 1234 + 77 * b, 5 + b)
+    d_lg = torch.from_numpy(lg).to(cuda)
+    d_prm = torch.from_numpy(prm.view(np.uint8).reshape(B, 32).copy()).to(cuda)
+    out = torch.zeros(B, dtype=torch.int32, device=cuda); lp = torch.zeros(B, device=cuda)
+    check(lib().qlmb_dec_sample(ptr(out), ptr(lp), ptr(d_lg), ptr(d_prm), B, V, stream_ptr()))
+    torch.cuda.synchronize()
+    out, lp = out.cpu().numpy(), lp.cpu().numpy()
+    M64 = (1 << 64) - 1
+    for b, (temp, top_p, top_k) in enumerate(cases):
+        l = lg[b].astype(np.float64)
+        ls = l.max() + np.log(np.exp(l - l.max()).sum())
+        assert abs(lp[b] - (l[out[b]] - ls)) < 1e-3
+        if temp <= 0 or top_k == 1:
+            assert out[b] == int(np.argmax(l))
+            continue
+        th = l.max() - 30.0
+        while (lg[b] >= np.float32(th)).sum() > 2048:
+            th = 0.5 * (th + l.max())
+        idx = np.nonzero(lg[b] >= np.float32(th))[0]
+        order = idx[np.lexsort((idx, -l[idx]))]                   # value descending, index ascending
+        sv = l[order]
+        k = min(top_k, len(order)) if top_k > 0 else len(order)
+        e = np.exp(sv[:k] - sv[0])
+        if top_p < 1.0:
+            c = np.cumsum(e / e.sum())
+            hit = np.nonzero(c >= top_p - 1e-6)[0]
+            k_lo = int(np.nonzero(c >= top_p + 1e-6)[0][0]) + 1 if (c >= top_p + 1e-6).any() else k
+            k = int(hit[0]) + 1 if len(hit) else k
+        else:
+            k_lo = k
+        h = ((1234 + 77 * b) * 0x9E3779B97F4A7C15 + (5 + b + 1) * 0xD1B54A32D192ED03) & M64
+        h ^= h >> 30; h = (h * 0xBF58476D1CE4E5B9) & M64; h ^= h >> 27; h = (h * 0x94D049BB133111EB) & M64; h ^= h >> 31
+        u01 = (h >> 40) / 16777216.0
+        ok = False
+        for kk in {k, k_lo}:                                      # a cumulative sum within rounding of top_p may cut one later
+            w = np.exp((sv[:kk] - sv[0]) / temp)
+            cum = np.cumsum(w) / w.sum()
+            pos = np.nonzero(order[:kk] == out[b])[0]
+            if len(pos):
+                i = int(pos[0])
+                lo = cum[i - 1] if i else 0.0
+                ok |= lo - 1e-4 <= u01 <= cum[i] + 1e-4
+        assert ok, (b, cases[b], int(out[b]))
+    q.check(q.lib().qlmb_check_device(None))
