@@ -82,6 +82,7 @@ PROTOTYPES = {
     "qlmb_moe_arena_bytes": (sz, [ci, ci, ci, ci, ci]),
     "qlmb_moe_arena_member": (vp, [vp, ci, ci, ci, ci, ci, C.c_char_p]),
     "qlmb_moe_forward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
+    "qlmb_moe_decode": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
     "qlmb_moe_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, vp, vp, vp, cf, vp]),
     "qlmb_moe_route": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp]),
     "qlmb_moe_experts_forward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, ci, vp]),

@@ -35,8 +35,19 @@ __device__ __forceinline__ void unpack8(uint32_t w, float d[8])
 // part[ks][b][n] receives the slice sums.
 template <int BT>
 __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, const void *X, int dtype, const uint8_t *codes,
-                                                 const float *scales, int B, int K, int N, int kslice)
+                                                 const float *scales, int B, int K, int N, int kslice,
+                                                 const int *row_expert = nullptr, size_t e_codes = 0, size_t e_scales = 0,
+                                                 int ntok = 1)
 {
+    // routed form (experts of a decode step): blockIdx.z is an output row, it reads activation row
+    // z % ntok and the matrix of expert row_expert[z]; B must be 1 then
+    size_t xrow = 0, prow = 0;
+    int PB = B;
+    if (row_expert) {
+        const int e = row_expert[blockIdx.z];
+        codes += (size_t)e * e_codes; scales += (size_t)e * e_scales;
+        xrow = blockIdx.z % ntok; prow = blockIdx.z; PB = gridDim.z;
+    }
     extern __shared__ float xs[];               // [BT][kslice]
     constexpr bool PAR = BT <= 2;               // every warp parks its sums, one pass adds them in warp order
     __shared__ float red[PAR ? 8 * BT : BT][256];
@@ -51,7 +62,7 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
         __syncthreads();
         for (int i = threadIdx.x; i < BT * kslice; i += 256) {
             const int b = b0 + i / kslice, k = k0 + i % kslice;
-            xs[i] = (b < B && k < k1) ? ld_x(X, dtype, (size_t)b * K + k) : 0.0f;
+            xs[i] = (b < B && k < k1) ? ld_x(X, dtype, ((size_t)b + xrow) * K + k) : 0.0f;
         }
         if (!PAR) for (int i = threadIdx.x; i < BT * 256; i += 256) red[i / 256][i % 256] = 0.0f;
         __syncthreads();
@@ -112,7 +123,7 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
                 float v = 0.0f;
 #pragma unroll
                 for (int w8 = 0; w8 < 8; w8++) v += red[w8 * BT + bb][c];
-                if (b < B && n < N) part[((size_t)blockIdx.y * B + b) * N + n] = v;
+                if (b < B && n < N) part[((size_t)blockIdx.y * PB + b + prow) * N + n] = v;
             }
         } else {
             for (int w8 = 0; w8 < 8; w8++) {
@@ -126,7 +137,7 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
             }
             for (int i = threadIdx.x; i < BT * 256; i += 256) {
                 const int b = b0 + i / 256, n = blockIdx.x * 256 + i % 256;
-                if (b < B && n < N) part[((size_t)blockIdx.y * B + b) * N + n] = red[i / 256][i % 256];
+                if (b < B && n < N) part[((size_t)blockIdx.y * PB + b + prow) * N + n] = red[i / 256][i % 256];
             }
         }
     }
@@ -205,6 +216,72 @@ __global__ void __launch_bounds__(256) k_gemv_finish(void *Y, int dtype, const f
     for (int k = 0; k < nslice; k++) s += part[(size_t)k * BN_ + i];
     if (dtype == QLMB_BF16) ((bf16 *)Y)[i] = __float2bfloat16_rn(s);
     else ((float *)Y)[i] = s;
+}
+
+// act[r,f] = silu(g) * u with g, u the K-slice sums (ascending) of the gate and up partials
+__global__ void __launch_bounds__(256) k_gemv_finish_swiglu(bf16 *act, const float *pg, const float *pu, int nslice, size_t RN)
+{
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= RN) return;
+    float g = 0.0f, u = 0.0f;
+    for (int k = 0; k < nslice; k++) { g += pg[(size_t)k * RN + i]; u += pu[(size_t)k * RN + i]; }
+    // the stash of the training path holds g and u as bf16; round the same way before the product
+    g = __bfloat162float(__float2bfloat16_rn(g)); u = __bfloat162float(__float2bfloat16_rn(u));
+    act[i] = __float2bfloat16_rn(g * __fdividef(1.0f, 1.0f + __expf(-g)) * u);
+}
+// out[n,j] = f_in[n,j] + sum_k gate[k,n] * y[k*ntok+n, j]   (k ascending, cudalm.cu:4027), y = slice sums of the down partials
+__global__ void __launch_bounds__(256) k_gemv_finish_combine(bf16 *out, const bf16 *f_in, const float *part, const float *gate,
+                                                             int nslice, int ntok, int Kk, int D)
+{
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (size_t)ntok * D) return;
+    const int n = (int)(i / D), j = (int)(i % D);
+    const size_t RN = (size_t)Kk * ntok * D;
+    float acc = __bfloat162float(f_in[i]);
+    for (int k = 0; k < Kk; k++) {
+        const size_t o = ((size_t)k * ntok + n) * D + j;
+        float y = 0.0f;
+        for (int s = 0; s < nslice; s++) y += part[(size_t)s * RN + o];
+        y = __bfloat162float(__float2bfloat16_rn(y));
+        acc += gate[(size_t)k * ntok + n] * y;
+    }
+    out[i] = __float2bfloat16_rn(acc);
+}
+
+// Experts of a decode step with at most 32 routed rows: three routed GEMVs that read only the chosen experts'
+// codes (W1, W3: [E][D][F]; W2: [E][F][D]), SwiGLU and the gate-weighted combination in the slice-sum kernels.
+int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, const void *f_norm, const int *assign,
+                       const float *gate, cudaStream_t st)
+{
+    const int N = L->N, D = L->D, F = L->F, K = L->K, R = K * N;
+    auto slices = [](int Kdim, int Ncols, int rows, int &kslice, int &nslice) {
+        const int nblk = (Ncols + 255) / 256;
+        nslice = (4 * sm_count()) / (nblk * rows);
+        if (nslice > Kdim / 64) nslice = Kdim / 64;
+        if (nslice < 1) nslice = 1;
+        kslice = ((Kdim + nslice - 1) / nslice + 127) / 128 * 128;
+        nslice = (Kdim + kslice - 1) / kslice;
+    };
+    int ks1, ns1, ks2, ns2;
+    slices(D, F, 2 * R, ks1, ns1);
+    slices(F, D, R, ks2, ns2);
+    const size_t pg_n = (size_t)ns1 * R * F, pd_n = (size_t)ns2 * R * D;
+    void *ws = nullptr;
+    int rc = workspace((2 * pg_n + pd_n) * sizeof(float) + (size_t)R * F * sizeof(bf16) + 256, &ws);
+    if (rc) return rc;
+    float *pg = (float *)ws, *pu = pg + pg_n, *pd = pu + pg_n;
+    bf16 *act = (bf16 *)(pd + pd_n);
+    const size_t ec = (size_t)D * F / 2, es = (size_t)D * F / 128;
+    k_gemv_kn<1><<<dim3((F + 255) / 256, ns1, R), 256, (size_t)ks1 * sizeof(float), st>>>(
+        pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N);
+    k_gemv_kn<1><<<dim3((F + 255) / 256, ns1, R), 256, (size_t)ks1 * sizeof(float), st>>>(
+        pu, f_norm, QLMB_BF16, (const uint8_t *)L->w3_codes, L->w3_scales, 1, D, F, ks1, assign, ec, es, N);
+    k_gemv_finish_swiglu<<<(unsigned)(((size_t)R * F + 255) / 256), 256, 0, st>>>(act, pg, pu, ns1, (size_t)R * F);
+    k_gemv_kn<1><<<dim3((D + 255) / 256, ns2, R), 256, (size_t)ks2 * sizeof(float), st>>>(
+        pd, act, QLMB_BF16, (const uint8_t *)L->w2_codes, L->w2_scales, 1, F, D, ks2, assign, ec, es, R);
+    k_gemv_finish_combine<<<(unsigned)(((size_t)N * D + 255) / 256), 256, 0, st>>>((bf16 *)out, (const bf16 *)f_in, pd, gate, ns2, N, K, D);
+    QLMB_LAUNCH_CHECK("moe_decode_experts");
+    return QLMB_OK;
 }
 
 }  // namespace qlmb

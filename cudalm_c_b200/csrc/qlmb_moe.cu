@@ -209,6 +209,26 @@ extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out,
     return combine_rows(out, f_in, L->dtype, a.yp, a.inv, a.gate, N, D, K, st);
 }
 
+// Forward of a decode step (dec_step's moe_forward call, cudalm.cu:7199): no stash for a backward pass.  With at
+// most 32 routed rows (K * N) and bf16 activations the experts run as routed GEMVs that read only the chosen
+// experts' codes; larger batches take qlmb_moe_forward.
+extern "C" int qlmb_moe_decode(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in, const void *f_norm,
+                               void *stream)
+{
+    int rc = check_layer("qlmb_moe_decode", L);
+    if (rc) return rc;
+    QLMB_REQUIRE(arena && out && f_in && f_norm, "qlmb_moe_decode: NULL argument");
+    if (L->K * L->N > 32 || L->dtype != QLMB_BF16 || (L->D % 128) || (L->F % 128))
+        return qlmb_moe_forward(L, arena, out, f_in, f_norm, stream);
+    QLMB_REQUIRE(((uintptr_t)arena & 255) == 0, "qlmb_moe_decode: arena must be 256-byte aligned");
+    const int N = L->N, D = L->D, F = L->F, E = L->E, K = L->K;
+    Arena a = carve(arena, N, D, F, E, K);
+    cudaStream_t st = as_stream(stream);
+    if ((rc = router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc;
+    if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc;
+    return moe_decode_experts(L, out, f_in, f_norm, a.assign, a.gate, st);
+}
+
 extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const void *dout,
                                  const void *f_norm, float *dW1, float *dW3, float *dW2, float *dWr,
                                  float beta, void *stream)

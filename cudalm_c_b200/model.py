@@ -347,7 +347,7 @@ class Decoder:
             f_in = linear.gemv_decode(att, *w["wo"], KN, c.D)
             f_in += x
             f_norm, _ = block.rmsnorm_fwd(f_in, f["an2"])
-            x = self.moes[l].forward(f_in, f_norm)
+            x = self.moes[l].decode(f_in, f_norm)
         fn, _ = block.rmsnorm_fwd(x, m.nf)
         self.logits = block.gemm_nt(fn, self.emb_bf, torch.float32, out=self.logits)
         self._pick()

@@ -79,6 +79,12 @@ class MoeLayerState:
         check(lib().qlmb_moe_forward(self.c, self.arena_ptr, ptr(out), ptr(f_in), ptr(f_norm), stream_ptr()))
         return out
 
+    def decode(self, f_in, f_norm, out=None):
+        """The forward of a decode step: no stash; routed GEMVs when K*N <= 32."""
+        out = out if out is not None else torch.empty_like(f_in)
+        check(lib().qlmb_moe_decode(self.c, self.arena_ptr, ptr(out), ptr(f_in), ptr(f_norm), stream_ptr()))
+        return out
+
     def backward(self, dout, f_norm, dW1, dW3, dW2, dWr, beta=1.0, dfnorm=None):
         dfnorm = dfnorm if dfnorm is not None else torch.empty_like(dout)
         check(lib().qlmb_moe_backward(self.c, self.arena_ptr, ptr(dfnorm), ptr(dout), ptr(f_norm), ptr(dW1),
