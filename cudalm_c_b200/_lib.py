@@ -65,6 +65,7 @@ PROTOTYPES = {
     "qlmb_rmsnorm_bwd": (ci, [vp, ci, ci, vp, vp, vp, ci, vp, vp, vp, ci, ci, ci, vp]),
     "qlmb_rope": (ci, [vp, ci, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_softmax_ce": (ci, [vp, ci, vp, vp, vp, ci, ci, ci, ci, vp]),
+    "qlmb_gemv_decode_stack": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_dec_rope": (ci, [vp, ci, vp, vp, vp, ci, ci, ci, vp]),
     "qlmb_dec_kv": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, vp]),
     "qlmb_dec_attn": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),

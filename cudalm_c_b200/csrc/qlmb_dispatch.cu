@@ -189,6 +189,40 @@ __global__ void __launch_bounds__(256) k_router_logits(float *rt, const void *X,
     }
 }
 
+// A handful of rows (a decode step): one block per token, lane = expert, eight warps each sum one eighth of the
+// features in ascending order (loads of Wr rows are independent of the running sums, so they pipeline), and the
+// eight partial sums are added in warp order.  Deterministic, but a different summation order than the tiled
+// kernel, hence only used where no backward pass reads the logits.
+__global__ void __launch_bounds__(256) k_router_logits_small(float *rt, const void *X, int x_dtype, const float *Wr, int D, int E)
+{
+    extern __shared__ float rl_x[];                      // D activations
+    __shared__ float part[8][32];
+    const int n = blockIdx.x, warp = threadIdx.x >> 5, e = threadIdx.x & 31;
+    for (int j = threadIdx.x; j < D; j += 256) rl_x[j] = ld_act(X, x_dtype, (size_t)n * D + j);
+    __syncthreads();
+    const int per = (D + 7) / 8, j0 = warp * per, j1 = j0 + per < D ? j0 + per : D;
+    float acc = 0.0f;
+    if (e < E) {
+#pragma unroll 8
+        for (int j = j0; j < j1; j++) acc += rl_x[j] * __ldg(Wr + (size_t)j * E + e);
+    }
+    part[warp][e] = acc;
+    __syncthreads();
+    if (warp == 0 && e < E) {
+        float s = part[0][e];
+#pragma unroll
+        for (int w = 1; w < 8; w++) s += part[w][e];
+        rt[(size_t)n * E + e] = s;
+    }
+}
+int router_logits_small(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E, cudaStream_t st)
+{
+    if (N > 64 || E > 32 || D > 8192) return router_logits(rt, X, x_dtype, Wr, N, D, E, st);
+    k_router_logits_small<<<N, 256, (size_t)D * sizeof(float), st>>>(rt, X, x_dtype, Wr, D, E);
+    QLMB_LAUNCH_CHECK("k_router_logits_small");
+    return QLMB_OK;
+}
+
 int router_logits(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E, cudaStream_t st)
 {
     if (E <= 32 && (D % 8) == 0 && (((uintptr_t)X | (uintptr_t)Wr) & 15) == 0) {

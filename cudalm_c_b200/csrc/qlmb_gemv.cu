@@ -39,12 +39,12 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
                                                  const int *row_expert = nullptr, size_t e_codes = 0, size_t e_scales = 0,
                                                  int ntok = 1)
 {
-    // routed form (experts of a decode step): blockIdx.z is an output row, it reads activation row
-    // z % ntok and the matrix of expert row_expert[z]; B must be 1 then
+    // routed form: blockIdx.z is an output row, it reads activation row z % ntok and one matrix of a stack; B must be 1 then
     size_t xrow = 0, prow = 0;
     int PB = B;
-    if (row_expert) {
-        const int e = row_expert[blockIdx.z];
+    if (e_codes) {
+        // the matrix of a row: looked up (experts of a step), or z / ntok for a stack of matrices applied to the same ntok rows
+        const int e = row_expert ? row_expert[blockIdx.z] : (int)blockIdx.z / ntok;
         codes += (size_t)e * e_codes; scales += (size_t)e * e_scales;
         xrow = blockIdx.z % ntok; prow = blockIdx.z; PB = gridDim.z;
     }
@@ -334,5 +334,32 @@ extern "C" int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, con
 #undef GV_LAUNCH
     k_gemv_finish<<<(unsigned)(((size_t)B * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)B * N);
     QLMB_LAUNCH_CHECK("qlmb_gemv_decode");
+    return QLMB_OK;
+}
+
+// Y[m*B + b, :] = X[b, :] deq(W_m) for nmat equally shaped matrices stored one after the other (codes W_m[K][N]):
+// the q, k and v projections of a decode step in one launch pair (cudalm.cu:7178-7180) when KD = D.
+extern "C" int qlmb_gemv_decode_stack(void *Y, const void *X, const int8_t *codes, const float *scales, int nmat, int B,
+                                      int K, int N, int dtype, void *stream)
+{
+    QLMB_REQUIRE(Y && X && codes && scales, "qlmb_gemv_decode_stack: NULL argument");
+    QLMB_REQUIRE(dtype == QLMB_F32 || dtype == QLMB_BF16, "qlmb_gemv_decode_stack: dtype %d", dtype);
+    QLMB_REQUIRE(nmat > 0 && B > 0 && nmat * B <= 64 && K > 0 && N > 0 && (K % 128) == 0 && (N % 128) == 0,
+                 "qlmb_gemv_decode_stack: nmat=%d B=%d K=%d N=%d", nmat, B, K, N);
+    cudaStream_t st = as_stream(stream);
+    const int R = nmat * B, nblk = (N + 255) / 256;
+    int nslice = (4 * sm_count()) / (nblk * R);
+    if (nslice > K / 64) nslice = K / 64;
+    if (nslice < 1) nslice = 1;
+    int kslice = ((K + nslice - 1) / nslice + 127) / 128 * 128;
+    nslice = (K + kslice - 1) / kslice;
+    void *ws = nullptr;
+    int rc = workspace((size_t)nslice * R * N * sizeof(float), &ws);
+    if (rc) return rc;
+    float *part = (float *)ws;
+    k_gemv_kn<1><<<dim3(nblk, nslice, R), 256, (size_t)kslice * sizeof(float), st>>>(
+        part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B);
+    k_gemv_finish<<<(unsigned)(((size_t)R * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)R * N);
+    QLMB_LAUNCH_CHECK("qlmb_gemv_decode_stack");
     return QLMB_OK;
 }

@@ -224,7 +224,7 @@ extern "C" int qlmb_moe_decode(const qlmb_moe_layer *L, void *arena, void *out, 
     const int N = L->N, D = L->D, F = L->F, E = L->E, K = L->K;
     Arena a = carve(arena, N, D, F, E, K);
     cudaStream_t st = as_stream(stream);
-    if ((rc = router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc;
+    if ((rc = router_logits_small(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc;
     if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc;
     return moe_decode_experts(L, out, f_in, f_norm, a.assign, a.gate, st);
 }

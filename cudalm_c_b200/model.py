@@ -263,7 +263,8 @@ class Decoder:
         bf = torch.bfloat16
         self.K = [torch.zeros(B, Tm, c.KD, dtype=bf, device=dev) for _ in range(c.L)]
         self.V = [torch.zeros(B, Tm, c.KD, dtype=bf, device=dev) for _ in range(c.L)]
-        self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.pos2 = torch.zeros(2 * B, dtype=torch.int32, device=dev)     # positions of the q rows and of the k rows
+        self.pos = self.pos2[:B]
         self.tok = torch.zeros(B, dtype=torch.int32, device=dev)
         self.otok = torch.zeros(B, dtype=torch.int32, device=dev)
         self.olp = torch.zeros(B, dtype=torch.float32, device=dev)
@@ -291,7 +292,7 @@ class Decoder:
         last = fn.view(B, n, c.D)[:, n - 1].contiguous()
         self.logits = block.gemm_nt(last, self.emb_bf, torch.float32, out=self.logits)   # same buffer every time: a captured step keeps writing to it
         self._pick()
-        self.pos.fill_(n)
+        self.pos2.fill_(n)
         self.tok.copy_(self.otok)
         return self.logits
 
@@ -305,6 +306,10 @@ class Decoder:
         a["temp"], a["top_p"], a["top_k"], a["seed"] = temp, top_p, top_k, seed
         self.sp = torch.from_numpy(a.view(np.uint8).reshape(self.B, 32).copy()).to(self.m.dev)
         self.sp_step = self.sp.view(torch.int32)[:, 6]          # the `step` field of every slot
+
+    def advance(self):
+        """Move every slot to its next position (step(advance=True) does this itself)."""
+        self.pos2 += 1
 
     def _pick(self):
         from ._lib import check, lib, ptr, stream_ptr
@@ -321,7 +326,7 @@ class Decoder:
         for l in range(self.m.c.L):
             self.K[l][t, :n] = self.K[l][s, :n]
             self.V[l][t, :n] = self.V[l][s, :n]
-        self.pos[t] = self.pos[s]; self.tok[t] = self.tok[s]
+        self.pos2[t] = self.pos2[s]; self.pos2[self.B + t] = self.pos2[s]; self.tok[t] = self.tok[s]
         if getattr(self, "sp", None) is not None:
             self.sp[t] = self.sp[s]
 
@@ -335,11 +340,18 @@ class Decoder:
         for l, ly in enumerate(m.layers):
             w, f = ly["w"], m.fl[l]
             a_norm, _ = block.rmsnorm_fwd(x, f["an1"])
-            qh = linear.gemv_decode(a_norm, *w["wq"], KN, c.D)
-            kh = linear.gemv_decode(a_norm, *w["wk"], KN, c.KD)
-            vh = linear.gemv_decode(a_norm, *w["wv"], KN, c.KD)
-            check(L_.qlmb_dec_rope(ptr(qh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.H, c.hd, stream_ptr()))
-            check(L_.qlmb_dec_rope(ptr(kh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.KV, c.hd, stream_ptr()))
+            if c.KD == c.D and 3 * B <= 24:
+                # wq, wk, wv are consecutive spans of one shape: one GEMV launch pair for the three, one rotation for q and k
+                qkv = torch.empty(3 * B, c.D, dtype=torch.bfloat16, device=m.dev)
+                check(L_.qlmb_gemv_decode_stack(ptr(qkv), ptr(a_norm), ptr(w["wq"][0]), ptr(w["wq"][1]), 3, B, c.D, c.D, 1, stream_ptr()))
+                qh, kh, vh = qkv[:B], qkv[B:2 * B], qkv[2 * B:]
+                check(L_.qlmb_dec_rope(ptr(qkv), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos2), 2 * B, c.H, c.hd, stream_ptr()))
+            else:
+                qh = linear.gemv_decode(a_norm, *w["wq"], KN, c.D)
+                kh = linear.gemv_decode(a_norm, *w["wk"], KN, c.KD)
+                vh = linear.gemv_decode(a_norm, *w["wv"], KN, c.KD)
+                check(L_.qlmb_dec_rope(ptr(qh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.H, c.hd, stream_ptr()))
+                check(L_.qlmb_dec_rope(ptr(kh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.KV, c.hd, stream_ptr()))
             check(L_.qlmb_dec_kv(ptr(self.K[l]), ptr(self.V[l]), ptr(kh), ptr(vh), ptr(self.pos), B, self.Tm, c.KD, stream_ptr()))
             att = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
             check(L_.qlmb_dec_attn(ptr(att), ptr(qh), ptr(self.K[l]), ptr(self.V[l]), ptr(self.pos), 0, B, self.Tm, c.H, c.KV,
@@ -352,6 +364,6 @@ class Decoder:
         self.logits = block.gemm_nt(fn, self.emb_bf, torch.float32, out=self.logits)
         self._pick()
         if advance:
-            self.pos += 1
+            self.pos2 += 1
             self.tok.copy_(self.otok)
         return self.logits

@@ -366,6 +366,11 @@ int qlmb_rope(void *buf, int dtype, const float *cosb, const float *sinb, int N,
 int qlmb_softmax_ce(const void *logits, int lg_dtype, const int *tgt, float *loss, void *dlogits, int dl_dtype, int rows,
                     int V, int n_all, void *stream);
 
+/* The q, k, v projections of a decode step in one call (cudalm.cu:7178-7180): nmat matrices of the same shape
+ * stored one after the other (codes W_m[K][N], groups along N), Y[m*B + b, :] = X[b, :] deq(W_m); nmat*B <= 64. */
+int qlmb_gemv_decode_stack(void *Y, const void *X, const int8_t *codes, const float *scales, int nmat, int B, int K,
+                           int N, int dtype, void *stream);
+
 /* ---- decoder: one new token per live slot (dec_step, cudalm.cu:7166-7212) ----
  * The K/V cache of a layer is bf16 [B, Tm, KV*hd]; pos[b] (device) is the position of slot b's new token.
  * k_dec_rope (cudalm.cu:7023-7027): rotate the single row of each slot by the angle of pos[b]. */

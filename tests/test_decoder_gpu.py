@@ -35,7 +35,7 @@ def test_decoder_matches_full_forward(cuda):
     for j in range(k):
         dec.tok.copy_(ids[:, n + j])
         lg = dec.step(advance=False)
-        dec.pos += 1
+        dec.advance()
         cmp(lg, ref[:, n + j])
     torch.cuda.synchronize()
     q.check(q.lib().qlmb_check_device(None))
