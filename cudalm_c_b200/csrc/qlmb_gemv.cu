@@ -344,7 +344,7 @@ extern "C" int qlmb_gemv_decode_stack(void *Y, const void *X, const int8_t *code
 {
     QLMB_REQUIRE(Y && X && codes && scales, "qlmb_gemv_decode_stack: NULL argument");
     QLMB_REQUIRE(dtype == QLMB_F32 || dtype == QLMB_BF16, "qlmb_gemv_decode_stack: dtype %d", dtype);
-    QLMB_REQUIRE(nmat > 0 && B > 0 && nmat * B <= 64 && K > 0 && N > 0 && (K % 128) == 0 && (N % 128) == 0,
+    QLMB_REQUIRE(nmat > 0 && B > 0 && nmat * B <= 256 && K > 0 && N > 0 && (K % 128) == 0 && (N % 128) == 0,
                  "qlmb_gemv_decode_stack: nmat=%d B=%d K=%d N=%d", nmat, B, K, N);
     cudaStream_t st = as_stream(stream);
     const int R = nmat * B, nblk = (N + 255) / 256;

@@ -179,8 +179,17 @@ extern "C" void *qlmb_moe_arena_member(void *arena, int N, int D, int F, int E, 
     return nullptr;
 }
 
+static int moe_forward_impl(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in, const void *f_norm,
+                            void *stream, bool small_router);
 extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in,
                                 const void *f_norm, void *stream)
+{
+    return moe_forward_impl(L, arena, out, f_in, f_norm, stream, false);
+}
+// small_router: the logits of a decode step's few rows come from k_router_logits_small (another summation order
+// than the tiled kernel; nothing reads them in a backward pass)
+static int moe_forward_impl(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in, const void *f_norm,
+                            void *stream, bool small_router)
 {
     int rc = check_layer("qlmb_moe_forward", L);
     if (rc) return rc;
@@ -192,7 +201,9 @@ extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out,
     const int R = (int)a.rows_cap;
 
     // router: logits, softmax top-k (cudalm.cu:4158, 4174)
-    { ProfScope ps("router_logits", st); if ((rc = router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc; }
+    { ProfScope ps("router_logits", st);
+      rc = small_router ? router_logits_small(a.rt, f_norm, L->dtype, L->wr, N, D, E, st) : router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st);
+      if (rc) return rc; }
     { ProfScope ps("router_topk", st);
     if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc; }
     // expert grouping, padded to 128-row tiles (cudalm.cu:4189)
@@ -219,7 +230,7 @@ extern "C" int qlmb_moe_decode(const qlmb_moe_layer *L, void *arena, void *out, 
     if (rc) return rc;
     QLMB_REQUIRE(arena && out && f_in && f_norm, "qlmb_moe_decode: NULL argument");
     if (L->K * L->N > 32 || L->dtype != QLMB_BF16 || (L->D % 128) || (L->F % 128))
-        return qlmb_moe_forward(L, arena, out, f_in, f_norm, stream);
+        return moe_forward_impl(L, arena, out, f_in, f_norm, stream, L->N <= 64);
     QLMB_REQUIRE(((uintptr_t)arena & 255) == 0, "qlmb_moe_decode: arena must be 256-byte aligned");
     const int N = L->N, D = L->D, F = L->F, E = L->E, K = L->K;
     Arena a = carve(arena, N, D, F, E, K);

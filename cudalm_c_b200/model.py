@@ -340,7 +340,7 @@ class Decoder:
         for l, ly in enumerate(m.layers):
             w, f = ly["w"], m.fl[l]
             a_norm, _ = block.rmsnorm_fwd(x, f["an1"])
-            if c.KD == c.D and 3 * B <= 24:
+            if c.KD == c.D and 3 * B <= 256:
                 # wq, wk, wv are consecutive spans of one shape: one GEMV launch pair for the three, one rotation for q and k
                 qkv = torch.empty(3 * B, c.D, dtype=torch.bfloat16, device=m.dev)
                 check(L_.qlmb_gemv_decode_stack(ptr(qkv), ptr(a_norm), ptr(w["wq"][0]), ptr(w["wq"][1]), 3, B, c.D, c.D, 1, stream_ptr()))
@@ -356,7 +356,11 @@ class Decoder:
             att = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
             check(L_.qlmb_dec_attn(ptr(att), ptr(qh), ptr(self.K[l]), ptr(self.V[l]), ptr(self.pos), 0, B, self.Tm, c.H, c.KV,
                                    c.hd, stream_ptr()))
-            f_in = linear.gemv_decode(att, *w["wo"], KN, c.D)
+            if 4 < B <= 256:
+                f_in = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
+                check(L_.qlmb_gemv_decode_stack(ptr(f_in), ptr(att), ptr(w["wo"][0]), ptr(w["wo"][1]), 1, B, c.D, c.D, 1, stream_ptr()))
+            else:
+                f_in = linear.gemv_decode(att, *w["wo"], KN, c.D)
             f_in += x
             f_norm, _ = block.rmsnorm_fwd(f_in, f["an2"])
             x = self.moes[l].decode(f_in, f_norm)

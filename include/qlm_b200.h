@@ -367,7 +367,9 @@ int qlmb_softmax_ce(const void *logits, int lg_dtype, const int *tgt, float *los
                     int V, int n_all, void *stream);
 
 /* The q, k, v projections of a decode step in one call (cudalm.cu:7178-7180): nmat matrices of the same shape
- * stored one after the other (codes W_m[K][N], groups along N), Y[m*B + b, :] = X[b, :] deq(W_m); nmat*B <= 64. */
+ * stored one after the other (codes W_m[K][N], groups along N), Y[m*B + b, :] = X[b, :] deq(W_m); nmat*B <= 256.
+ * Every output row is computed by its own blocks (the matrices of a projection fit the L2), so this is for small
+ * matrices and few rows; nmat = 1 is a plain GEMV without row batching. */
 int qlmb_gemv_decode_stack(void *Y, const void *X, const int8_t *codes, const float *scales, int nmat, int B, int K,
                            int N, int dtype, void *stream);
 
