@@ -33,6 +33,7 @@ struct StepArgs {
     uint8_t *v8; float *v8s; const qlmb_span *sp; int nspan; int group; int dmax;
     float lr, b1, b2, wd, gscale; const float *gsp; float inv_bc1, inv_sqrt_bc2;
     int lrmode; uint64_t t; int adam; unsigned long long *stat; int packed; int gi_base, ng;
+    int v4;       // QLM_V4 (qlm.cuh:62-67): v8 holds the fourth root of the second moment instead of its square root
 };
 
 // Per-element update shared by both paths (reference qlm.cuh:206-242).
@@ -42,7 +43,7 @@ __device__ __forceinline__ ElemOut elem_update(float g, int m8v, int v8v, int dd
                                                float gs, float ms_old, float vs_old, float b1,
                                                float b2, float omb1, float omb2, float inv_bc1,
                                                float inv_sqrt_bc2, float L, float dec, int dmax,
-                                               int adam, uint64_t key_t)
+                                               int adam, uint64_t key_t, int v4 = 0)
 {
     ElemOut o;
     float gr = g * gs;
@@ -51,13 +52,15 @@ __device__ __forceinline__ ElemOut elem_update(float g, int m8v, int v8v, int dd
     o.rv = 0.0f;
     if (adam) {
         float sv = (float)v8v * vs_old;
+        if (v4) sv = sv * sv;                            // qv_dec
         float vv = sv * sv;
         o.mn = b1 * mv + omb1 * gr;
         vv = b2 * vv + omb2 * gr * gr;
         o.rv = sqrtf(vv);
-        float veps = fmaxf(vs_old, 1e-8f);
+        float veps = fmaxf(v4 ? vs_old * vs_old : vs_old, 1e-8f);
         u = (o.mn * inv_bc1) / (o.rv * inv_sqrt_bc2 + veps);
         u = fmaxf(-8.0f, fminf(8.0f, u));
+        if (v4) o.rv = sqrtf(o.rv);                      // qv_enc: what is quantised and maximised
     } else {
         float cc = b1 * mv + omb1 * gr;
         u = (float)((cc > 0.0f) - (cc < 0.0f));
@@ -105,7 +108,7 @@ __device__ void step_group_team(const StepArgs &a, int gi, int tl, unsigned tmas
             int dd = digit_at(a.d, qi, a.packed);
             ElemOut o = elem_update(a.G[g0 + j], a.m8[qi], a.adam ? a.v8[qi] : 0, dd, a.r[qi], gs,
                                     ms_old, vs_old, a.b1, a.b2, omb1, omb2, a.inv_bc1,
-                                    a.inv_sqrt_bc2, L, dec, a.dmax, a.adam, qi * QLMB_HASH_I + kt);
+                                    a.inv_sqrt_bc2, L, dec, a.dmax, a.adam, qi * QLMB_HASH_I + kt, a.v4);
             dig[h] = o.dd;
             a.r[qi] = (int8_t)o.rr;
             if (a.P) a.P[p0 + j] = sg * (float)o.dd;
@@ -139,10 +142,13 @@ __device__ void step_group_team(const StepArgs &a, int gi, int tl, unsigned tmas
             float gr = a.G[g0 + j] * gs;
             float mv = (float)a.m8[qi] * ms_old, mn, rv = 0.0f;
             if (a.adam) {
-                float sv = (float)a.v8[qi] * vs_old, vv = sv * sv;
+                float sv = (float)a.v8[qi] * vs_old;
+                if (a.v4) sv = sv * sv;
+                float vv = sv * sv;
                 mn = a.b1 * mv + omb1 * gr;
                 vv = a.b2 * vv + omb2 * gr * gr;
                 rv = sqrtf(vv);
+                if (a.v4) rv = sqrtf(rv);
             } else {
                 mn = a.b2 * mv + omb2 * gr;
             }
@@ -507,6 +513,11 @@ extern "C" int qlmb_render(float *P, const int8_t *d, const float *s, const qlmb
     return QLMB_OK;
 }
 
+// QLM_V4 is a process-wide switch in the reference too (device global d_qv4, set from the environment by
+// qlm_v4_init, qlm.cuh:68-72)
+static int g_qv4 = 0;
+extern "C" int qlmb_set_v4(int on) { g_qv4 = on ? 1 : 0; return QLMB_OK; }
+
 extern "C" int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const float *s, int8_t *m8,
                          float *m8s, uint8_t *v8, float *v8s, const qlmb_span *sp, int nspan,
                          int group, int dmax, float lr, float b1, float b2, float wd, float gscale,
@@ -519,9 +530,9 @@ extern "C" int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const f
     QLMB_REQUIRE(dmax >= 1 && dmax <= 127 && (!packed || dmax <= 7), "qlmb_step: dmax %d", dmax);
     if (ng <= 0) return QLMB_OK;
     StepArgs a = {P, G, d, r, s, m8, m8s, v8, v8s, sp, nspan, group, dmax, lr, b1, b2, wd, gscale, gsp,
-                  inv_bc1, inv_sqrt_bc2, lrmode, t, adam, (unsigned long long *)stat, packed, gi_base, ng};
+                  inv_bc1, inv_sqrt_bc2, lrmode, t, adam, (unsigned long long *)stat, packed, gi_base, ng, g_qv4};
     auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
-    bool fast = group == 128 && packed && adam && !stat && al16(G) && al16(d) && al16(r) && al16(m8) &&
+    bool fast = group == 128 && packed && adam && !stat && !g_qv4 && al16(G) && al16(d) && al16(r) && al16(m8) &&
                 al16(v8) && (!P || al16(P));
     cudaStream_t st = as_stream(stream);
     if (fast) {

@@ -103,6 +103,11 @@ int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const float *s, in
               float inv_bc1, float inv_sqrt_bc2, int lrmode, uint64_t t, int adam, int64_t *stat,
               int packed, int gi_base, int ng, void *stream);
 
+/* QLM_V4 (qlm.cuh:62-72, qv_dec / qv_enc): v8 stores the fourth root of the second moment instead of its square
+ * root, so that small-gradient elements of a group do not sit on the uint8 floor.  A process-wide switch, as in
+ * the reference (its device global d_qv4); affects qlmb_step. */
+int qlmb_set_v4(int on);
+
 /* k_qlm_servo (qlm.cuh:404-441). */
 int qlmb_servo(int8_t *d, int8_t *r, float *s, const qlmb_span *sp, int nspan, int ngrp, int group,
                int dmax, float f_hi, float f_lo, int packed, void *stream);

@@ -89,6 +89,9 @@ class Restatement:
                          f(gscale), f(inv_bc1), f(inv_sqrt_bc2), C.c_int(lrmode), C.c_uint64(t),
                          C.c_int(adam), _p(stat), C.c_int(packed), C.c_int(gi_base), C.c_int(ng))
 
+    def set_v4(self, on):
+        self.lib.qo_set_v4(C.c_int(1 if on else 0))
+
     def servo(self, d, r, s, sp, group=128, dmax=7, f_hi=0.0, f_lo=0.0, packed=1):
         self.lib.qo_servo(_p(d), _p(r), _p(s), _p(sp), C.c_int(len(sp)), C.c_int(len(s)),
                           C.c_int(group), C.c_int(dmax), C.c_float(f_hi), C.c_float(f_lo),
@@ -222,6 +225,9 @@ class Reference:
                           C.c_int(len(sp)), C.c_int(group), C.c_int(dmax), f(lr), f(b1), f(b2), f(wd),
                           f(gscale), None, f(inv_bc1), f(inv_sqrt_bc2), C.c_int(lrmode), C.c_uint64(t),
                           C.c_int(adam), _p(stat), C.c_int(packed), C.c_int(gi_base), C.c_int(ng))
+
+    def set_v4(self, on):
+        self.lib.ref_set_v4(C.c_int(1 if on else 0))
 
     def servo(self, d, r, s, sp, group=128, dmax=7, f_hi=0.0, f_lo=0.0, packed=1):
         self.lib.ref_servo(_p(d), _p(r), _p(s), _p(sp), C.c_int(len(sp)), C.c_int(len(s)),

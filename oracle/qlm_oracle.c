@@ -153,6 +153,10 @@ void qo_render(float *P, const int8_t *d, const float *s, const QoSpan *sp,
  *   v8 = clamp(sround(rv/vs, qi, t+0xBEEF), 0, 255), kept >= 1 while rv > 0.
  * adam==0 is the sign-momentum variant (qlm.cuh:225-229).  P may be NULL
  * (no fp32 view wanted); stat may be NULL (qlm.cuh:243-250). */
+/* QLM_V4 (qlm.cuh:62-72): v8 holds v^(1/4); process-wide switch like the reference's d_qv4 */
+static int qo_v4 = 0;
+void qo_set_v4(int on) { qo_v4 = on ? 1 : 0; }
+
 void qo_step(float *P, const float *G, int8_t *d, int8_t *r, const float *s,
              int8_t *m8, float *m8s, uint8_t *v8, float *v8s, const QoSpan *sp,
              int nspan, int group, int dmax, float lr, float b1, float b2, float wd,
@@ -180,13 +184,15 @@ void qo_step(float *P, const float *G, int8_t *d, int8_t *r, const float *s,
             rnew[j] = 0.0f;
             if (adam) {
                 float sv = (float)v8[qi] * vs_old;
+                if (qo_v4) sv = sv * sv;                 /* qv_dec, qlm.cuh:66 */
                 float vv = sv * sv;
                 mnew[j] = b1 * mv + (1.0f - b1) * gr;
                 vv = b2 * vv + (1.0f - b2) * gr * gr;
                 rnew[j] = sqrtf(vv);
-                float veps = fmaxf(vs_old, 1e-8f);
+                float veps = fmaxf(qo_v4 ? vs_old * vs_old : vs_old, 1e-8f);
                 u = (mnew[j] * inv_bc1) / (rnew[j] * inv_sqrt_bc2 + veps);
                 u = fmaxf(-8.0f, fminf(8.0f, u));
+                if (qo_v4) rnew[j] = sqrtf(rnew[j]);     /* qv_enc, qlm.cuh:67 */
             } else {
                 float cc = b1 * mv + (1.0f - b1) * gr;
                 u = (float)((cc > 0.0f) - (cc < 0.0f));

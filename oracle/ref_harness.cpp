@@ -40,6 +40,8 @@ void ref_step(float *P, const float *G, signed char *d, signed char *r, float *s
     qlm_step_launch(P, G, d, r, s, m8, m8s, v8, v8s, sp, nspan, group, dmax, lr, b1, b2, wd,
                     gscale, gsp, inv_bc1, inv_sqrt_bc2, lrmode, t, adam, stat, packed, gi_base, ng);
 }
+/* QLM_V4: the CPU build's copy of the device global (qlm.cuh:65) */
+void ref_set_v4(int on) { d_qv4 = on ? 1 : 0; }
 void ref_servo(signed char *d, signed char *r, float *s, const QSpanD *sp, int nspan, int ngrp,
                int group, int dmax, float f_hi, float f_lo, int packed)
 {

@@ -282,6 +282,15 @@ def golden_fused(ref):
     np.savez_compressed(os.path.join(OUT, "fused_update.npz"), **out)
 
 
+def golden_state_v4(ref):
+    """QLM_V4 (qlm.cuh:62-72): the same ragged state sequence with v8 holding the fourth root of the second moment."""
+    ref.set_v4(1)
+    try:
+        golden_state(ref, "state_g128_v4", [128 * 12, 1000, 78], 128, 7, 1, 5, seed=6)
+    finally:
+        ref.set_v4(0)
+
+
 def main():
     ref = loader.reference(exact=True)
     if ref is None:
@@ -298,6 +307,7 @@ def main():
     golden_moe(ref)
     golden_statefile(ref)
     golden_fused(ref)
+    golden_state_v4(ref)
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print("%-24s %8d B" % (f, os.path.getsize(os.path.join(OUT, f))))

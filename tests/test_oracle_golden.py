@@ -74,6 +74,15 @@ def test_state_sequences(oracle, name):
     assert (P == g["P_final"]).all()
 
 
+def test_state_sequence_v4(oracle):
+    """QLM_V4 (qlm.cuh:62-72): v8 holds the fourth root of the second moment."""
+    oracle.set_v4(1)
+    try:
+        test_state_sequences(oracle, "state_g128_v4")
+    finally:
+        oracle.set_v4(0)
+
+
 def test_gnorm(oracle):
     g = golden("gnorm")
     assert (oracle.gnorm(g["G"]) == g["gs_plain"]).all()

@@ -251,6 +251,16 @@ def test_qlm_class_update_with_servo(cuda, oracle):
         assert (P.cpu().numpy() == Ph).all()
 
 
+def test_state_sequence_v4(cuda):
+    """QLM_V4 (qlm.cuh:62-72) through qlmb_set_v4: same bytes as the reference with d_qv4 = 1."""
+    import cudalm_c_b200 as q
+    q.check(q.lib().qlmb_set_v4(1))
+    try:
+        test_state_sequences_match_reference(cuda, "state_g128_v4")
+    finally:
+        q.check(q.lib().qlmb_set_v4(0))
+
+
 def test_fused_per_layer_update_matches_reference(cuda):
     """qlm_fused_layer / qlm_fused_tail (cudalm.cu:6105-6187): layers share one gradient block, each is
     consumed as soon as it is complete, the clip multiplier is the previous step's and stays on the
