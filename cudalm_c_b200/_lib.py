@@ -53,6 +53,9 @@ PROTOTYPES = {
     "qlmb_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, cf, cf, cf, cf, cf, vp, cf, cf,
                        ci, u64, ci, vp, ci, ci, ci, vp]),
     "qlmb_set_v4": (ci, [ci]),
+    "qlmb_ng_touched": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp]),
+    "qlmb_ng_scatter_compact": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
+    "qlmb_ng_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, cf, cf, cf, cf, cf, cf, cf, u64, u64, vp, vp]),
     "qlmb_servo": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, cf, cf, ci, vp]),
     "qlmb_gnorm": (ci, [vp, sz, vp, vp, ci, ci, vp, vp]),
     "qlmb_gnorm_noalloc": (ci, [vp, sz, vp, vp, ci, ci, vp, vp]),

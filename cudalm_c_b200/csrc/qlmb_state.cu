@@ -34,6 +34,9 @@ struct StepArgs {
     float lr, b1, b2, wd, gscale; const float *gsp; float inv_bc1, inv_sqrt_bc2;
     int lrmode; uint64_t t; int adam; unsigned long long *stat; int packed; int gi_base, ng;
     int v4;       // QLM_V4 (qlm.cuh:62-67): v8 holds the fourth root of the second moment instead of its square root
+    // sparse form (k_ng_q4_step, cudalm.cu:4476-4530): group w of the launch is touched[w], its gradients are the w-th
+    // row of a compact buffer; only the first *touched_count entries are live
+    const int *touched; const int *touched_count;
 };
 
 // Per-element update shared by both paths (reference qlm.cuh:206-242).
@@ -83,12 +86,12 @@ __device__ __forceinline__ ElemOut elem_update(float g, int m8v, int v8v, int dd
 // the new moments from the still-unmodified m8/v8/G and re-quantises them, so
 // no per-lane arrays are needed for any group size up to 256.
 template <int T>
-__device__ void step_group_team(const StepArgs &a, int gi, int tl, unsigned tmask)
+__device__ void step_group_team(const StepArgs &a, int gi, int tl, unsigned tmask, long long g_row = -1)
 {
     uint64_t j0; int n;
     int si = locate_group(a.sp, a.nspan, gi, a.group, j0, n);
     const qlmb_span &S = a.sp[si];
-    uint64_t q0 = S.qi0 + j0, p0 = S.pof + j0, g0 = S.gof + j0;
+    uint64_t q0 = S.qi0 + j0, p0 = S.pof + j0, g0 = g_row >= 0 ? (uint64_t)g_row * (uint64_t)a.group : S.gof + j0;
     float gs = a.gsp ? *a.gsp : a.gscale;
     float sg = a.s[gi];
     float L = a.lr * 128.0f / (a.lrmode ? sg : S.sref);
@@ -173,7 +176,93 @@ __global__ void __launch_bounds__(256) k_step_generic(StepArgs a)
 {
     int w = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (w >= a.ng) return;
+    if (a.touched) {
+        if (w >= *a.touched_count) return;
+        step_group_team<32>(a, a.touched[w], threadIdx.x & 31, 0xffffffffu, w);
+        return;
+    }
     step_group_team<32>(a, a.gi_base + w, threadIdx.x & 31, 0xffffffffu);
+}
+
+// ------------------------------------------------ sparse table update: touched groups and their compact gradients
+// (ng_build_touched + k_ng_scatter_compact, cudalm.cu:4465-4475, 4673-4700.)  The reference claims slots with a CAS
+// and an atomic counter and adds gradients with float atomics; here every step has a fixed order: groups are marked,
+// compacted in ascending group order by one block, and each gradient element is summed by one warp over the keys
+// in ascending position -- the order of the reference's CPU build.
+__global__ void __launch_bounds__(256) k_ng_mark(int *flag, const int *key, int NK, int De, int group)
+{
+    const int n = blockIdx.x * 256 + threadIdx.x;
+    if (n >= NK) return;
+    const int r = key[n];
+    if (r >= 0) flag[(int)(((long long)r * De) / group)] = 1;
+}
+// one block: tgi[0..count) = the marked groups in ascending order; the flags are cleared for the next step
+__global__ void __launch_bounds__(1024) k_ng_compact(int *tgi, int *count, int *flag, int ngrp)
+{
+    __shared__ int wsum[32];
+    __shared__ int base;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) base = 0;
+    __syncthreads();
+    for (int g0 = 0; g0 < ngrp; g0 += 1024) {
+        const int gi = g0 + tid;
+        const int f = gi < ngrp ? flag[gi] : 0;
+        if (f) flag[gi] = 0;
+        int x = f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+        if (lane == 31) wsum[warp] = x;
+        __syncthreads();
+        if (warp == 0) {
+            int v = wsum[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += y; }
+            wsum[lane] = v;                              // inclusive sums of the warps
+        }
+        __syncthreads();
+        const int before = base + (warp ? wsum[warp - 1] : 0) + x - f;
+        if (f) tgi[before] = gi;
+        __syncthreads();
+        if (tid == 0) base += wsum[31];
+        __syncthreads();
+    }
+    if (tid == 0) *count = base;
+}
+// Gc[c*group + o] = sum over positions n (ascending) whose key is the row of element o: warp = (slot c, row of the group)
+__global__ void __launch_bounds__(256) k_ng_scatter_compact(float *Gc, const int *key, const int *tgi, const int *count,
+                                                            const float *dbuf, int NK, int De, int group, int Nd)
+{
+    __shared__ int skey[2048];
+    const int rpg = group / De;                          // rows per group (group % De == 0)
+    const int w = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int c = w / rpg, rr = w % rpg;
+    const int cnt = *count;
+    if (blockIdx.x * 8 / rpg >= cnt) return;             // the whole block is past the live slots
+    const bool live = c < cnt;
+    const int row = live ? (int)(((long long)tgi[c] * group) / De) + rr : -2;
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) acc[k] = 0.0f;
+    for (int n0 = 0; n0 < NK; n0 += 2048) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 2048; i += 256) skey[i] = n0 + i < NK ? key[n0 + i] : -1;
+        __syncthreads();
+        const int lim = NK - n0 < 2048 ? NK - n0 : 2048;
+        for (int q = 0; q < lim; q += 32) {
+            unsigned m = __ballot_sync(0xffffffffu, skey[q + lane] == row);
+            while (m) {
+                const int n = n0 + q + __ffs(m) - 1;
+                m &= m - 1;
+                const float *src = dbuf + (size_t)(n % Nd) * De;
+#pragma unroll
+                for (int k = 0; k < 8; k++) { const int e = lane + 32 * k; if (e < De) acc[k] += src[e]; }
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int k = 0; k < 8; k++) { const int e = lane + 32 * k; if (e < De) Gc[(size_t)c * group + rr * De + e] = acc[k]; }
+    }
 }
 
 // ------------------------------------------------------- fast step, group 128
@@ -530,7 +619,7 @@ extern "C" int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const f
     QLMB_REQUIRE(dmax >= 1 && dmax <= 127 && (!packed || dmax <= 7), "qlmb_step: dmax %d", dmax);
     if (ng <= 0) return QLMB_OK;
     StepArgs a = {P, G, d, r, s, m8, m8s, v8, v8s, sp, nspan, group, dmax, lr, b1, b2, wd, gscale, gsp,
-                  inv_bc1, inv_sqrt_bc2, lrmode, t, adam, (unsigned long long *)stat, packed, gi_base, ng, g_qv4};
+                  inv_bc1, inv_sqrt_bc2, lrmode, t, adam, (unsigned long long *)stat, packed, gi_base, ng, g_qv4, nullptr, nullptr};
     auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
     bool fast = group == 128 && packed && adam && !stat && !g_qv4 && al16(G) && al16(d) && al16(r) && al16(m8) &&
                 al16(v8) && (!P || al16(P));
@@ -674,5 +763,56 @@ extern "C" int qlmb_gnorm_close(const float *part, int nslice, float *gs, void *
     QLMB_REQUIRE(part && gs && nslice > 0, "qlmb_gnorm_close: bad argument");
     k_gnorm_close<<<1, 1, 0, as_stream(stream)>>>(part, 64 * nslice, gs);
     QLMB_LAUNCH_CHECK("qlmb_gnorm_close");
+    return QLMB_OK;
+}
+
+// ------------------------------------------------- 4-bit n-gram / engram table: sparse integer AdamW
+extern "C" int qlmb_ng_touched(int *tgi, int *count, int *flag, const int *key, int NK, int De, int group, int ngrp,
+                               void *stream)
+{
+    QLMB_REQUIRE(tgi && count && flag && key, "qlmb_ng_touched: NULL argument");
+    QLMB_REQUIRE(NK >= 0 && De > 0 && group > 0 && group % De == 0 && ngrp > 0, "qlmb_ng_touched: NK %d De %d group %d ngrp %d", NK, De, group, ngrp);
+    cudaStream_t st = as_stream(stream);
+    if (NK > 0) k_ng_mark<<<(NK + 255) / 256, 256, 0, st>>>(flag, key, NK, De, group);
+    k_ng_compact<<<1, 1024, 0, st>>>(tgi, count, flag, ngrp);
+    QLMB_LAUNCH_CHECK("qlmb_ng_touched");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_ng_scatter_compact(float *Gc, const int *key, const int *tgi, const int *count, const float *dbuf,
+                                       int NK, int De, int group, int Nd, int max_touched, void *stream)
+{
+    QLMB_REQUIRE(Gc && key && tgi && count && dbuf, "qlmb_ng_scatter_compact: NULL argument");
+    QLMB_REQUIRE(De > 0 && De <= 256 && group > 0 && group % De == 0 && Nd > 0 && max_touched >= 0, "qlmb_ng_scatter_compact: De %d group %d", De, group);
+    if (max_touched == 0 || NK <= 0) return QLMB_OK;
+    const long long warps = (long long)max_touched * (group / De);
+    k_ng_scatter_compact<<<(unsigned)((warps + 7) / 8), 256, 0, as_stream(stream)>>>(Gc, key, tgi, count, dbuf, NK, De, group, Nd);
+    QLMB_LAUNCH_CHECK("k_ng_scatter_compact");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_ng_step(float *P, const float *Gc, int8_t *d, int8_t *r, const float *s, int8_t *m8, float *m8s,
+                            uint8_t *v8, float *v8s, const int *tgi, const int *count, int max_touched, int group,
+                            int dmax, float lr, float b1, float b2, float wd, float sref, float inv_bc1,
+                            float inv_sqrt_bc2, uint64_t t, uint64_t nt, const float *gs, void *stream)
+{
+    QLMB_REQUIRE(Gc && d && r && s && m8 && m8s && v8 && v8s && tgi && count, "qlmb_ng_step: NULL argument");
+    QLMB_REQUIRE(group >= 32 && group <= 256 && (group % 2) == 0 && dmax >= 1 && dmax <= 7 && nt > 0, "qlmb_ng_step: group %d dmax %d", group, dmax);
+    if (max_touched <= 0) return QLMB_OK;
+    // the table is one packed span that starts at element 0 (ngram_q4_setup, cudalm.cu:4541-4543)
+    int dev = 0;
+    QLMB_CUDA(cudaGetDevice(&dev));
+    QLMB_REQUIRE(dev >= 0 && dev < 64, "qlmb_ng_step: device index %d", dev);
+    static qlmb_span *g_span[64];
+    if (!g_span[dev]) QLMB_CUDA(cudaMalloc(&g_span[dev], sizeof(qlmb_span)));
+    qlmb_span h;
+    memset(&h, 0, sizeof h);
+    h.pof = 0; h.gof = 0; h.qi0 = 0; h.n = nt; h.gi0 = 0; h.ngrp = (int)((nt + group - 1) / group); h.sref = sref;
+    cudaStream_t st = as_stream(stream);
+    QLMB_CUDA(cudaMemcpyAsync(g_span[dev], &h, sizeof h, cudaMemcpyHostToDevice, st));
+    StepArgs a = {P, Gc, d, r, s, m8, m8s, v8, v8s, g_span[dev], 1, group, dmax, lr, b1, b2, wd, 1.0f, gs,
+                  inv_bc1, inv_sqrt_bc2, 0, t, 1, nullptr, 1, 0, max_touched, g_qv4, tgi, count};
+    k_step_generic<<<(max_touched + 7) / 8, 256, 0, st>>>(a);
+    QLMB_LAUNCH_CHECK("qlmb_ng_step");
     return QLMB_OK;
 }

@@ -108,6 +108,27 @@ int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const float *s, in
  * the reference (its device global d_qv4); affects qlmb_step. */
 int qlmb_set_v4(int on);
 
+/* ---- 4-bit n-gram / engram table: sparse integer AdamW over the groups a step touched
+ * (NGRAM_Q4_FOLD: ng_build_touched, k_ng_scatter_compact, k_ng_q4_step; cudalm.cu:4465-4530, 4673-4745).
+ * The table is one packed span of nt elements starting at element 0; key[n] is the table row of position n
+ * (-1: masked), a row has De elements, group % De == 0.  Nothing is copied to the host: the number of touched
+ * groups stays in *count (device) and the launches are sized by max_touched (an upper bound, e.g. min(NK, ngrp)).
+ * Every step has a fixed order (no atomics on floats, no CAS race for slots), so results are run-to-run identical.
+ *
+ * qlmb_ng_touched: tgi[0..*count) = the groups some key falls into, ascending (the reference's slot order is
+ * arbitrary).  flag is a scratch of ngrp ints that must be zero on entry and is zero again on exit. */
+int qlmb_ng_touched(int *tgi, int *count, int *flag, const int *key, int NK, int De, int group, int ngrp, void *stream);
+/* Gc[c*group + o] = sum over positions n (ascending) with key[n] = row of element o of group tgi[c], of
+ * dbuf[(n % Nd)*De + e]; every element of the first *count rows of Gc is written (no memset needed). */
+int qlmb_ng_scatter_compact(float *Gc, const int *key, const int *tgi, const int *count, const float *dbuf, int NK,
+                            int De, int group, int Nd, int max_touched, void *stream);
+/* k_ng_q4_step: the integer AdamW step of qlmb_step (packed, adam, relative learning rate against the frozen
+ * sref, gradient multiplier gs[0] when gs is not NULL) on groups tgi[0..*count), gradients from Gc. */
+int qlmb_ng_step(float *P, const float *Gc, int8_t *d, int8_t *r, const float *s, int8_t *m8, float *m8s, uint8_t *v8,
+                 float *v8s, const int *tgi, const int *count, int max_touched, int group, int dmax, float lr, float b1,
+                 float b2, float wd, float sref, float inv_bc1, float inv_sqrt_bc2, uint64_t t, uint64_t nt,
+                 const float *gs, void *stream);
+
 /* k_qlm_servo (qlm.cuh:404-441). */
 int qlmb_servo(int8_t *d, int8_t *r, float *s, const qlmb_span *sp, int nspan, int ngrp, int group,
                int dmax, float f_hi, float f_lo, int packed, void *stream);

@@ -242,6 +242,21 @@ class Reference:
         self.lib.ref_gnorm(_p(G), C.c_size_t(G.size), ptrs, lens, C.c_int(ns), C.c_int(clip_side), _p(gs))
         return gs
 
+    # ---- 4-bit n-gram table update (cpu_kern.h:615-660) ----
+    def ng_touched(self, key, De, group, ngrp):
+        slot = np.full(ngrp, -1, np.int32); tgi = np.zeros(key.size, np.int32); cidx = np.zeros(key.size, np.int32)
+        cnt = self.lib.ref_ng_touched(_p(key), _p(slot), _p(tgi), _p(cidx), C.c_int(key.size), C.c_int(De), C.c_int(group))
+        return tgi[:cnt].copy(), cidx
+
+    def ng_scatter_compact(self, Gc, key, cidx, dbuf, De, group, Nd):
+        self.lib.ref_ng_scatter_compact(_p(Gc), _p(key), _p(cidx), _p(dbuf), C.c_int(key.size), C.c_int(De), C.c_int(group), C.c_int(Nd))
+
+    def ng_step(self, P, Gc, d, r, s, m8, m8s, v8, v8s, tgi, group, dmax, lr, b1, b2, wd, sref, inv_bc1, inv_sqrt_bc2, t, nt, gs=None):
+        f = C.c_float
+        self.lib.ref_ng_step(_p(P), _p(Gc), _p(d), _p(r), _p(s), _p(m8), _p(m8s), _p(v8), _p(v8s), _p(tgi), C.c_int(tgi.size),
+                             C.c_int(group), C.c_int(dmax), f(lr), f(b1), f(b2), f(wd), f(sref), f(inv_bc1), f(inv_sqrt_bc2),
+                             C.c_ulonglong(t), C.c_ulonglong(nt), _p(gs))
+
     # ---- block operators (cpu_kern.h:87-152, 489-503) ----
     def embed(self, emb, tok):
         X = np.zeros((tok.size, emb.shape[1]), np.float32)

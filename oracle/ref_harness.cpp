@@ -104,6 +104,28 @@ void ref_attn_bwd(const float *Q, const float *K, const float *V, const float *O
     cpu_attn_bwd(Q, K, V, dA, lse, drow, dQ, dK, dV, win, B, T, H, KV, hd, H * hd, KV * hd);
 }
 
+/* ---- 4-bit n-gram table update (cpu_kern.h:615-660; ng_build_touched / ng_tbl_step, cudalm.cu:4673-4745) ---- */
+int ref_ng_touched(const int *key, int *slot /* ngrp ints, all -1 */, int *tgi, int *cidx, int N, int De, int grp)
+{
+    int cnt = 0;
+    KL(k_ng_claim, 1, 1)(key, slot, tgi, &cnt, N, De, grp);
+    KL(k_ng_cidx, 1, 1)(key, slot, cidx, N, De, grp);
+    if (cnt) KL(k_ng_unclaim, 1, 1)(slot, tgi, cnt);
+    return cnt;
+}
+void ref_ng_scatter_compact(float *Gc, const int *key, const int *cidx, const float *dbuf, int N, int De, int group, int Nd)
+{
+    KL(k_ng_scatter_compact, 1, 1)(Gc, key, cidx, dbuf, N, De, group, Nd);
+}
+void ref_ng_step(float *P, const float *Gc, signed char *d, signed char *r, float *s, signed char *m8, float *m8s,
+                 unsigned char *v8, float *v8s, const int *tgi, int Gt, int group, int dmax, float lr, float b1, float b2,
+                 float wd, float sref, float inv_bc1, float inv_sqrt_bc2, unsigned long long t, unsigned long long nt,
+                 const float *gs)
+{
+    if (Gt) KL(k_ng_q4_step, (unsigned)Gt, group, group)(P, Gc, d, r, s, m8, m8s, v8, v8s, tgi, group, dmax, lr, b1, b2, wd, sref,
+                                                         inv_bc1, inv_sqrt_bc2, t, nt, gs);
+}
+
 /* ---- router and permutation (cudalm.cu:2515-2534, 3576-3602) ---- */
 void ref_router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N, int E, int K,
                      const float *bias, int bs)

@@ -291,6 +291,39 @@ def golden_state_v4(ref):
         ref.set_v4(0)
 
 
+def golden_ngram(ref):
+    """The 4-bit n-gram table update (NGRAM_Q4_FOLD; ng_build_touched, k_ng_scatter_compact, k_ng_q4_step,
+    cudalm.cu:4465-4530, 4673-4745) through the reference's CPU kernels: three steps on a table of 1024 rows x 32."""
+    rng = np.random.default_rng(21)
+    R, De, group, dmax = 1024, 32, 128, 7
+    nt = R * De
+    sp, nq, ng = loader.make_spans([nt], group)
+    P = (rng.standard_normal(nt) * 0.02).astype(f32)
+    d = np.zeros(nt // 2, np.int8); r = np.zeros(nt, np.int8); s = np.zeros(ng, f32)
+    Praw = P.copy()
+    ref.encode(P, d, r, s, sp, group, dmax, 1)
+    sref = f32(s.astype(np.float64).sum() / ng)
+    ref.render(P, d, s, sp, group, 1)
+    out = dict(Praw=Praw, P0=P.copy(), d0=d.copy(), r0=r.copy(), s0=s.copy(), sref=np.array([sref], f32), cfg=np.array([R, De, group, dmax]))
+    m8 = np.zeros(nt, np.int8); v8 = np.zeros(nt, np.uint8); m8s = np.zeros(ng, f32); v8s = np.zeros(ng, f32)
+    Nd = 300
+    for t in (1, 2, 3):
+        key = rng.integers(0, R, 2 * Nd).astype(np.int32)
+        key[rng.integers(0, 2 * Nd, 40)] = -1                       # masked positions
+        key[100:140] = key[50]                                      # one heavily repeated row
+        dbuf = (rng.standard_normal((Nd, De)) * 1e-3).astype(f32)
+        gs = np.array([0.5 if t == 2 else 1.0, 0.0], f32)
+        tgi, cidx = ref.ng_touched(key, De, group, ng)
+        Gc = np.zeros(tgi.size * group, f32)
+        ref.ng_scatter_compact(Gc, key, cidx, dbuf, De, group, Nd)
+        i1, i2 = bias_corr(0.9, 0.95, t)
+        ref.ng_step(P, Gc, d, r, s, m8, m8s, v8, v8s, tgi, group, dmax, 3e-3, 0.9, 0.95, 0.0, float(sref), i1, i2, t, nt, gs)
+        out["key%d" % t] = key; out["dbuf%d" % t] = dbuf; out["gs%d" % t] = gs
+        out["touched%d" % t] = np.sort(tgi)
+    out.update(P=P, d=d, r=r, m8=m8, v8=v8, m8s=m8s, v8s=v8s)
+    np.savez_compressed(os.path.join(OUT, "ngram_q4.npz"), **out)
+
+
 def main():
     ref = loader.reference(exact=True)
     if ref is None:
@@ -308,6 +341,7 @@ def main():
     golden_statefile(ref)
     golden_fused(ref)
     golden_state_v4(ref)
+    golden_ngram(ref)
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print("%-24s %8d B" % (f, os.path.getsize(os.path.join(OUT, f))))

@@ -292,3 +292,45 @@ def test_fused_per_layer_update_matches_reference(cuda):
     assert (Q.Mc.cpu().numpy().view(np.uint16) == g["out_Mc"]).all()
     assert (Q.Vc.cpu().numpy().view(np.uint16) == g["out_Vc"]).all()
     assert (P.cpu().numpy() == g["out_P"]).all()
+
+
+def test_ngram_q4_table_update(cuda):
+    """NGRAM_Q4_FOLD (cudalm.cu:4465-4530, 4673-4745): touched-group map, compact gradient scatter and the
+    list-driven integer AdamW step, three steps, against the reference's CPU kernels: same touched groups, same
+    bytes of state and the same rendered table.  The device never learns the touched count on the host."""
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import qlm
+    from cudalm_c_b200._lib import check, lib, ptr, stream_ptr
+    g = golden("ngram_q4")
+    R, De, group, dmax = [int(x) for x in g["cfg"]]
+    nt = R * De
+    st = DevState(cuda, [nt], group, dmax, 1)
+    st.encode(dev(g["Praw"], cuda))
+    h = st.host()
+    assert (h["d"] == g["d0"]).all() and (h["r"] == g["r0"]).all() and (h["s"] == g["s0"]).all()
+    P = dev(g["P0"], cuda)                                               # the rendered table the gather reads
+    sref = float(g["sref"][0])
+    ngrp = st.ng
+    flag = torch.zeros(ngrp, dtype=torch.int32, device=cuda)
+    count = torch.zeros(1, dtype=torch.int32, device=cuda)
+    L = lib()
+    for t in (1, 2, 3):
+        key = dev(g["key%d" % t], cuda); dbuf = dev(g["dbuf%d" % t], cuda); gs = dev(g["gs%d" % t], cuda)
+        NK, Nd = key.numel(), dbuf.shape[0]
+        cap = min(NK, ngrp)
+        tgi = torch.zeros(cap, dtype=torch.int32, device=cuda)
+        Gc = torch.full((cap * group,), float("nan"), device=cuda)          # every live element must be overwritten
+        check(L.qlmb_ng_touched(ptr(tgi), ptr(count), ptr(flag), ptr(key), NK, De, group, ngrp, stream_ptr()))
+        check(L.qlmb_ng_scatter_compact(ptr(Gc), ptr(key), ptr(tgi), ptr(count), ptr(dbuf), NK, De, group, Nd, cap, stream_ptr()))
+        bc1 = f32(1) - f32(np.power(f32(0.9), f32(t))); bc2 = f32(1) - f32(np.power(f32(0.95), f32(t)))
+        check(L.qlmb_ng_step(ptr(P), ptr(Gc), ptr(st.d), ptr(st.r), ptr(st.s), ptr(st.m8), ptr(st.m8s), ptr(st.v8), ptr(st.v8s),
+                             ptr(tgi), ptr(count), cap, group, dmax, 3e-3, 0.9, 0.95, 0.0, sref, float(f32(1) / bc1),
+                             float(f32(1) / np.sqrt(bc2)), t, nt, ptr(gs), stream_ptr()))
+        n = int(count[0])
+        assert (tgi[:n].cpu().numpy() == g["touched%d" % t]).all()
+        assert int(flag.sum()) == 0
+    h = st.host()
+    for k in ("d", "r", "m8", "v8", "m8s", "v8s"):
+        assert (h[k] == g[k]).all(), k
+    assert (P.cpu().numpy() == g["P"]).all()
+    q.check(q.lib().qlmb_check_device(None))
