@@ -341,9 +341,9 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
 //   warp 0      TMA producer   resident tiles once, the walked tiles through a two-stage ring
 //   warp 1      MMA issuer     scores and dP (two 128 x 128 x 64 MMAs into TMEM), then the two
 //                              accumulating products from P / dS in shared memory
-//   warps 2-9   element-wise   thread = one TMEM lane (a key for dkv, a query for dq) x 64 of the
+//   warps 2-17  element-wise   thread = one TMEM lane (a key for dkv, a query for dq) x 32 of the
 //                              128 columns: P and dS as bf16 into swizzled K-major tiles
-constexpr int AT_BWD_THREADS = 320;
+constexpr int AT_BWD_THREADS = 576;             // TMA warp, MMA warp, 16 element-wise warps
 constexpr int AT_DKV_SMEM = 2 * AT_TILE + 4 * AT_TILE + 2 * AT_P_BYTES + 2 * 2 * 128 * 4 + 256;
 constexpr int AT_DQ_SMEM = 2 * AT_TILE + 4 * AT_TILE + AT_P_BYTES + 256;
 
@@ -379,6 +379,23 @@ __global__ void __launch_bounds__(256) k_attn_drow(float *drow, const bf16 *dA, 
     drow[((size_t)b * H + h) * T + t] = acc;
 }
 
+// 32 fp32 TMEM columns of this thread's lane -> 64 bytes of bf16 in global memory (the load runs in every lane)
+__device__ __forceinline__ void attn_store_row32(bf16 *dst, uint32_t taddr, bool live)
+{
+    uint32_t v[32];
+    tmem_ld32(taddr, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 2 * k]), __uint_as_float(v[u * 8 + 2 * k + 1]));
+            w[k] = *reinterpret_cast<uint32_t *>(&h2);
+        }
+        if (live) *reinterpret_cast<uint4 *>(dst + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
 // 64 fp32 TMEM columns of this thread's lane -> one 128-byte row of bf16 in global memory
 // (tcgen05.ld is warp-collective: every lane runs it, only live lanes store)
 __device__ __forceinline__ void attn_store_row64(bf16 *dst, uint32_t taddr, bool live)
@@ -423,7 +440,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
         mbar_init(smem_u32(kv_full), 1);
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&qd_full[i]), 2); mbar_init(smem_u32(&qd_empty[i]), 1); }
         mbar_init(smem_u32(s_full), 1);
-        mbar_init(smem_u32(pds_full), 8);
+        mbar_init(smem_u32(pds_full), 16);
         mbar_init(smem_u32(acc_done), 1);
         mbar_init(smem_u32(spare), 1);
         *abort_flag = 0;
@@ -536,7 +553,8 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
         }
     } else {
         // =============================== element-wise ===============================
-        const int qr = warp & 3, hf = (warp - 2) >> 2, r = qr * 32 + lane, key = k0 + r;
+        // warp = (TMEM lane quarter qr, 32-column chunk cq of the 128): hf = which 64-column sub-tile, c = chunk in it
+        const int qr = warp & 3, cq = (warp - 2) >> 2, hf = cq >> 1, c = cq & 1, r = qr * 32 + lane, key = k0 + r;
         const uint32_t lane_base = (uint32_t)(qr * 32) << 16;
         bool ok = true;
         for (int it = 0; ok && it < nit; it++) {
@@ -548,15 +566,11 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
             if (!ok) break;
             tc_fence_after();
             const float *L2 = sL + st * 128 + hf * 64, *Dq = sD + st * 128 + hf * 64;
-            uint32_t svv[2][32], dvv[2][32];         // all four TMEM loads of the step in flight: one round trip
-            tmem_ld32(tS + lane_base + hf * 64, svv[0]);
-            tmem_ld32(tP + lane_base + hf * 64, dvv[0]);
-            tmem_ld32(tS + lane_base + hf * 64 + 32, svv[1]);
-            tmem_ld32(tP + lane_base + hf * 64 + 32, dvv[1]);
+            uint32_t sv[32], dv[32];                 // both TMEM loads of the step in flight: one round trip
+            tmem_ld32(tS + lane_base + cq * 32, sv);
+            tmem_ld32(tP + lane_base + cq * 32, dv);
             tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 2; c++) {
-                const uint32_t *sv = svv[c], *dv = dvv[c];
+            {
                 uint32_t pp[16], ds[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
@@ -590,8 +604,9 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
         if (ok) ok = at_wait(smem_u32(acc_done), (uint32_t)(nit - 1) & 1u, abort_flag, p.errword, 223);
         if (ok) {
             tc_fence_after();
-            bf16 *dst = (hf ? p.dK : p.dV) + ((size_t)b * p.T + key) * ((size_t)p.KV * AT_HD) + (size_t)kvh * AT_HD;
-            attn_store_row64(dst, (hf ? tdK : tdV) + lane_base, key < p.T);
+            // chunks 0, 1: the two halves of the dV row; chunks 2, 3: of the dK row
+            bf16 *dst = (hf ? p.dK : p.dV) + ((size_t)b * p.T + key) * ((size_t)p.KV * AT_HD) + (size_t)kvh * AT_HD + c * 32;
+            attn_store_row32(dst, (hf ? tdK : tdV) + lane_base + c * 32, key < p.T);
         }
         tc_fence_before();
     }
@@ -619,7 +634,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
         mbar_init(smem_u32(qa_full), 1);
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&kv_full[i]), 1); mbar_init(smem_u32(&kv_empty[i]), 1); }
         mbar_init(smem_u32(s_full), 1);
-        mbar_init(smem_u32(ds_full), 8);
+        mbar_init(smem_u32(ds_full), 16);
         mbar_init(smem_u32(acc_done), 1);
         mbar_init(smem_u32(spare), 1);
         *abort_flag = 0;
@@ -717,7 +732,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
             for (uint32_t i = 0; i < AT_WAIT_LIMIT && !mbar_try(smem_u32(spare), 0); i++) {}
         }
     } else {
-        const int qr = warp & 3, hf = (warp - 2) >> 2, r = qr * 32 + lane, i = q0 + r;
+        const int qr = warp & 3, cq = (warp - 2) >> 2, hf = cq >> 1, c = cq & 1, r = qr * 32 + lane, i = q0 + r;
         const uint32_t lane_base = (uint32_t)(qr * 32) << 16;
         const size_t rowb = ((size_t)b * p.H + h) * p.T;
         const float L2 = i < p.T ? p.lse[rowb + i] * 1.4426950408889634f : 1e30f;
@@ -730,15 +745,11 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
             if (ok && t > 0) ok = at_wait(smem_u32(acc_done), (uint32_t)(t - 1) & 1u, abort_flag, p.errword, 322);
             if (!ok) break;
             tc_fence_after();
-            uint32_t svv[2][32], dvv[2][32];         // all four TMEM loads of the step in flight: one round trip
-            tmem_ld32(tS + lane_base + hf * 64, svv[0]);
-            tmem_ld32(tP + lane_base + hf * 64, dvv[0]);
-            tmem_ld32(tS + lane_base + hf * 64 + 32, svv[1]);
-            tmem_ld32(tP + lane_base + hf * 64 + 32, dvv[1]);
+            uint32_t sv[32], dv[32];                 // both TMEM loads of the step in flight: one round trip
+            tmem_ld32(tS + lane_base + cq * 32, sv);
+            tmem_ld32(tP + lane_base + cq * 32, dv);
             tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 2; c++) {
-                const uint32_t *sv = svv[c], *dv = dvv[c];
+            {
                 uint32_t ds[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
@@ -768,13 +779,13 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
         if (ok) ok = at_wait(smem_u32(acc_done), (uint32_t)(nt - 1) & 1u, abort_flag, p.errword, 323);
         if (ok) {
             tc_fence_after();
-            {                                  // each of the row's two threads stores 32 of its 64 columns
-                bf16 *dst = p.dQ + ((size_t)b * p.T + i) * ((size_t)p.H * AT_HD) + (size_t)h * AT_HD + hf * 32;
-                uint32_t v[32];
-                tmem_ld32(tdQ + lane_base + hf * 32, v);          // warp-collective: all lanes, also those past the sequence
+            {                                  // each of the row's four threads stores 16 of its 64 columns
+                bf16 *dst = p.dQ + ((size_t)b * p.T + i) * ((size_t)p.H * AT_HD) + (size_t)h * AT_HD + cq * 16;
+                uint32_t v[16];
+                tmem_ld16(tdQ + lane_base + cq * 16, v);          // warp-collective: all lanes, also those past the sequence
                 tmem_ld_wait();
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < 2; u++) {
                     uint32_t w[4];
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
