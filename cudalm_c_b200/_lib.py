@@ -56,6 +56,9 @@ PROTOTYPES = {
     "qlmb_ng_touched": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp]),
     "qlmb_ng_scatter_compact": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_ng_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, cf, cf, cf, cf, cf, cf, cf, u64, u64, vp, vp]),
+    "qlmb_modelfile_write": (ci, [C.c_char_p, vp, vp, u64, vp, ci]),
+    "qlmb_modelfile_read_header": (ci, [C.c_char_p, vp, vp, vp]),
+    "qlmb_modelfile_read": (ci, [C.c_char_p, vp, u64, vp, ci, vp]),
     "qlmb_servo": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, cf, cf, ci, vp]),
     "qlmb_gnorm": (ci, [vp, sz, vp, vp, ci, ci, vp, vp]),
     "qlmb_gnorm_noalloc": (ci, [vp, sz, vp, vp, ci, ci, vp, vp]),

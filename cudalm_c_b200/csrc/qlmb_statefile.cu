@@ -99,3 +99,81 @@ extern "C" int qlmb_statefile_read(const char *path, qlmb_statefile *v)
     fclose(f);
     return QLMB_OK;
 }
+
+// ------------------------------------------------------------------ model file (TLM4 / TLM5)
+// model_save_bundle / model_load_full (cudalm.cu:554-565, 431-466): magic, 11 (TLM4) or 13 (TLM5, window > 0)
+// header ints {V, D, L, H, KV, F, T, eot, tmpl, n_mtp, n_exp[, win, full_every]}, the fp32 parameter vector, the
+// tokenizer blob's length and bytes.  A model whose quantised weights exist only as digits writes their rendered
+// values (digit * scale), which the reference re-encodes to the same digits.
+extern "C" int qlmb_modelfile_write(const char *path, const int *hdr13, const float *P, unsigned long long n,
+                                    const void *tok_blob, int tok_bytes)
+{
+    QLMB_REQUIRE(path && hdr13 && (P || n == 0), "qlmb_modelfile_write: NULL argument");
+    QLMB_REQUIRE(tok_bytes >= 0 && (tok_bytes == 0 || tok_blob), "qlmb_modelfile_write: tokenizer blob missing");
+    char tmp[1400];
+    QLMB_REQUIRE(strlen(path) < 1300, "qlmb_modelfile_write: path too long");
+    snprintf(tmp, sizeof tmp, "%s.tmp", path);
+    FILE *f = fopen(tmp, "wb");
+    if (!f) { set_error("qlmb_modelfile_write: cannot create %s", tmp); return QLMB_E_ARG; }
+    const bool win = hdr13[11] > 0;
+    bool ok = wr(f, win ? "TLM5" : "TLM4", 1, 4) && wr(f, hdr13, 4, win ? 13 : 11) && wr(f, P, 4, n) && wr(f, &tok_bytes, 4, 1)
+           && (tok_bytes == 0 || wr(f, tok_blob, 1, (unsigned long long)tok_bytes));
+    ok = ok && fflush(f) == 0 && fsync(fileno(f)) == 0;
+    if (fclose(f) != 0) ok = false;
+    if (!ok) { remove(tmp); set_error("qlmb_modelfile_write: write to %s failed (the previous file is kept)", tmp); return QLMB_E_ARG; }
+    if (rename(tmp, path) != 0) { remove(tmp); set_error("qlmb_modelfile_write: cannot replace %s", path); return QLMB_E_ARG; }
+    return QLMB_OK;
+}
+
+// Header of a TLM1..TLM5 file into hdr13 (ints a version lacks are 0); *n_params = fp32 values that follow, derived
+// from the file length and the tokenizer trailer (the caller checks it against its own layout); *tok_bytes likewise.
+extern "C" int qlmb_modelfile_read_header(const char *path, int *hdr13, unsigned long long *n_params, int *tok_bytes)
+{
+    QLMB_REQUIRE(path && hdr13 && n_params, "qlmb_modelfile_read_header: NULL argument");
+    FILE *f = fopen(path, "rb");
+    if (!f) { set_error("qlmb_modelfile_read_header: cannot open %s", path); return QLMB_E_ARG; }
+    char m[4];
+    int nh = 0;
+    bool ok = fread(m, 1, 4, f) == 4;
+    if (ok) {
+        if (!memcmp(m, "TLM5", 4)) nh = 13; else if (!memcmp(m, "TLM4", 4)) nh = 11; else if (!memcmp(m, "TLM3", 4)) nh = 10;
+        else if (!memcmp(m, "TLM2", 4)) nh = 9; else if (!memcmp(m, "TLM1", 4)) nh = 8;
+    }
+    if (!ok || !nh) { fclose(f); set_error("qlmb_modelfile_read_header: %s is not a TLM1..TLM5 model file", path); return QLMB_E_UNSUPPORTED; }
+    memset(hdr13, 0, 13 * sizeof(int));
+    ok = fread(hdr13, 4, (size_t)nh, f) == (size_t)nh;
+    fseek(f, 0, SEEK_END);
+    const long long len = ftell(f);
+    fclose(f);
+    if (!ok) { set_error("qlmb_modelfile_read_header: %s: truncated header", path); return QLMB_E_ARG; }
+    const long long body = len - 4 - 4LL * nh;
+    // with a tokenizer trailer the body is n*4 + 4 + tok_bytes; the caller's parameter count decides, so report the
+    // largest n the file can hold and let qlmb_modelfile_read verify the trailer
+    *n_params = body > 0 ? (unsigned long long)(body / 4) : 0;
+    if (tok_bytes) *tok_bytes = -1;
+    return QLMB_OK;
+}
+
+// Reads exactly n fp32 parameters after the header; *tok_bytes = length of the tokenizer blob that follows (0: none),
+// copied into tok_blob when it is not NULL and tok_cap is large enough.
+extern "C" int qlmb_modelfile_read(const char *path, float *P, unsigned long long n, void *tok_blob, int tok_cap, int *tok_bytes)
+{
+    QLMB_REQUIRE(path && (P || n == 0), "qlmb_modelfile_read: NULL argument");
+    FILE *f = fopen(path, "rb");
+    if (!f) { set_error("qlmb_modelfile_read: cannot open %s", path); return QLMB_E_ARG; }
+    char m[4];
+    int nh = 0;
+    if (fread(m, 1, 4, f) == 4) {
+        if (!memcmp(m, "TLM5", 4)) nh = 13; else if (!memcmp(m, "TLM4", 4)) nh = 11; else if (!memcmp(m, "TLM3", 4)) nh = 10;
+        else if (!memcmp(m, "TLM2", 4)) nh = 9; else if (!memcmp(m, "TLM1", 4)) nh = 8;
+    }
+    if (!nh) { fclose(f); set_error("qlmb_modelfile_read: %s is not a TLM1..TLM5 model file", path); return QLMB_E_UNSUPPORTED; }
+    bool ok = fseek(f, 4 + 4L * nh, SEEK_SET) == 0 && fread(P, 4, n, f) == n;
+    if (!ok) { fclose(f); set_error("qlmb_modelfile_read: %s: model body truncated", path); return QLMB_E_ARG; }
+    int tl = 0;
+    if (fread(&tl, 4, 1, f) != 1) tl = 0;
+    if (tl > 0 && tok_blob && tok_cap >= tl && fread(tok_blob, 1, (size_t)tl, f) != (size_t)tl) tl = 0;
+    if (tok_bytes) *tok_bytes = tl > 0 ? tl : 0;
+    fclose(f);
+    return QLMB_OK;
+}

@@ -134,6 +134,26 @@ class QlmModel:
         a, n = self.o.layers[l][nm]
         return self.G[a:a + n]
 
+    # ------------------------------------------------------------------ model file
+    def params(self):
+        """The fp32 parameter vector in the reference's layout: rendered digits (digit * scale) + the float spans."""
+        P = torch.zeros(self.o.total, dtype=torch.float32, device=self.dev)
+        self.q.render(P)
+        for (off, n, _), t in zip(self.q.fs, self.fp):
+            P[off:off + n] = t
+        return P
+
+    def save_model(self, path, eot=0):
+        """model_save_bundle (cudalm.cu:554-565): a TLM4 file the reference loads (single-GPU layout only)."""
+        import ctypes as C
+        import numpy as np
+        from ._lib import check, lib
+        assert self.world == 1, "gather the experts first"
+        c = self.c
+        hdr = np.array([c.V, c.D, c.L, c.H, c.KV, c.F, c.T, eot, 0, 0, c.E, 0, 0], np.int32)
+        P = self.params().cpu().numpy()
+        check(lib().qlmb_modelfile_write(path.encode(), hdr.ctypes.data_as(C.c_void_p), P.ctypes.data_as(C.c_void_p), P.size, None, 0))
+
     # ------------------------------------------------------------------ forward
     def forward(self, tok, B=None, T=None, moes=None):
         """gpu_forward over B sequences of T tokens (default: the training batch); `moes` replaces the

@@ -303,6 +303,16 @@ int qlmb_statefile_write(const char *path, const qlmb_statefile *v);
 int qlmb_statefile_read_header(const char *path, qlmb_statefile *v);
 int qlmb_statefile_read(const char *path, qlmb_statefile *v);
 
+/* Model file of the reference (model_save_bundle / model_load_full, cudalm.cu:554-565, 431-466): "TLM4" + 11 ints
+ * {V, D, L, H, KV, F, T, eot, tmpl, n_mtp, n_exp} ("TLM5" + 13 ints with {win, full_every} when win > 0), the fp32
+ * parameter vector in the reference's layout, the tokenizer blob's length and bytes.  hdr13 always has 13 ints.
+ * Written through a temporary file and an atomic rename, like the reference.  A run whose quantised weights exist
+ * only as digits writes their rendered values (qlmb_render into a host-bound buffer). */
+int qlmb_modelfile_write(const char *path, const int *hdr13, const float *P, unsigned long long n, const void *tok_blob,
+                         int tok_bytes);
+int qlmb_modelfile_read_header(const char *path, int *hdr13, unsigned long long *n_params, int *tok_bytes);
+int qlmb_modelfile_read(const char *path, float *P, unsigned long long n, void *tok_blob, int tok_cap, int *tok_bytes);
+
 /* ------------------------- expert parallelism over peer memory (new, no reference counterpart)
  * Same cut of moe_forward / moe_backward (cudalm.cu:4151-4393), but rows never travel in a
  * separate exchange: every rank places its inputs, its Ys / dXs buffers and both arenas in one

@@ -242,6 +242,20 @@ class Reference:
         self.lib.ref_gnorm(_p(G), C.c_size_t(G.size), ptrs, lens, C.c_int(ns), C.c_int(clip_side), _p(gs))
         return gs
 
+    # ---- model file (cudalm.cu:431-466, 554-565) ----
+    def param_count(self, hdr13):
+        self.lib.ref_param_count.restype = C.c_ulonglong
+        return int(self.lib.ref_param_count(_p(hdr13)))
+
+    def model_save(self, path, hdr13, P):
+        self.lib.ref_model_save(path.encode(), _p(hdr13), _p(P), C.c_ulonglong(P.size))
+
+    def model_load(self, path, cap):
+        self.lib.ref_model_load.restype = C.c_ulonglong
+        hdr = np.zeros(13, np.int32); P = np.zeros(cap, np.float32)
+        n = int(self.lib.ref_model_load(path.encode(), _p(hdr), _p(P), C.c_ulonglong(cap)))
+        return hdr, P[:n]
+
     # ---- 4-bit n-gram table update (cpu_kern.h:615-660) ----
     def ng_touched(self, key, De, group, ngrp):
         slot = np.full(ngrp, -1, np.int32); tgi = np.zeros(key.size, np.int32); cidx = np.zeros(key.size, np.int32)

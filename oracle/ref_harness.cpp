@@ -126,6 +126,27 @@ void ref_ng_step(float *P, const float *Gc, signed char *d, signed char *r, floa
                                                          inv_bc1, inv_sqrt_bc2, t, nt, gs);
 }
 
+/* ---- model file (model_save_bundle / model_load_full, cudalm.cu:554-565, 431-466) ---- */
+static void cfg_from_ints(Cfg *c, const int *h) { cfg_from_hdr(c, h, h[11] > 0 ? 5 : 4); }
+unsigned long long ref_param_count(const int *hdr13) { Cfg c; cfg_from_ints(&c, hdr13); return (unsigned long long)param_count(&c); }
+void ref_model_save(const char *path, const int *hdr13, const float *P, unsigned long long n)
+{
+    Cfg c; cfg_from_ints(&c, hdr13);
+    model_save_bundle(path, &c, P, (size_t)n, NULL, 0);
+}
+/* returns the parameter count, fills hdr13 and P (capacity cap floats) */
+unsigned long long ref_model_load(const char *path, int *hdr13, float *P, unsigned long long cap)
+{
+    Cfg c; Tok *tk = NULL;
+    float *Ph = model_load_full(path, &c, &tk);
+    size_t n = param_count(&c);
+    int h[13] = {c.V, c.D, c.L, c.H, c.KV, c.F, c.T, c.eot, c.tmpl, c.n_mtp, c.n_exp, c.win, c.full_every};
+    memcpy(hdr13, h, sizeof h);
+    if (n <= cap) memcpy(P, Ph, n * 4);
+    free(Ph);
+    return (unsigned long long)n;
+}
+
 /* ---- router and permutation (cudalm.cu:2515-2534, 3576-3602) ---- */
 void ref_router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N, int E, int K,
                      const float *bias, int bs)

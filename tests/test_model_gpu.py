@@ -95,3 +95,19 @@ def test_training_step_matches_fp32_autograd(cuda):
     q.check(q.lib().qlmb_check_device(None))
     assert not torch.equal(d0, m.q.r)
     print("worst relative gradient error", worst)
+
+
+def test_model_file_is_loadable_by_the_reference(cuda, tmp_path):
+    """QlmModel.save_model writes the rendered weights as a TLM4 file; the reference's model_load_full returns them."""
+    from cudalm_c_b200 import model
+    from oracle import loader
+    ref = loader.reference()
+    if ref is None:
+        pytest.skip("compiled reference not present (make -C oracle ref)")
+    cfg = model.Config(L=2, D=128, H=2, KV=2, hd=64, E=4, K=2, F=128, V=256, T=128, B=2)
+    m = model.QlmModel(cfg, cuda, seed=4)
+    path = str(tmp_path / "m.bin")
+    m.save_model(path, eot=7)
+    hdr, P = ref.model_load(path, m.o.total)
+    assert list(hdr[:11]) == [256, 128, 2, 2, 2, 128, 128, 7, 0, 0, 4]
+    assert (P == m.params().cpu().numpy()).all()

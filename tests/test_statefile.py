@@ -103,3 +103,39 @@ def test_round_trip_through_the_reference_loader(tmp_path):
     for name in ("d", "r", "m8", "v8", "s", "m8s", "v8s", "Mc", "Vc"):
         assert np.array_equal(st[name], g[name]), name
     assert np.array_equal(sp["sref"], g["sref"])
+
+
+def test_model_file_interchange(tmp_path):
+    """TLM4 model files (model_save_bundle / model_load_full, cudalm.cu:554-565, 431-466): what the library
+    writes the reference loads, what the reference writes the library reads, and both write the same bytes.
+    Also pins the parameter layout of cudalm_c_b200/model.py to the reference's calc_offsets."""
+    import ctypes as C
+    import numpy as np
+    import cudalm_c_b200 as q
+    from oracle import loader
+    ref = loader.reference()
+    if ref is None:
+        import pytest
+        pytest.skip("compiled reference not present (make -C oracle ref)")
+    L = q.lib()
+    hdr = np.array([64, 32, 2, 2, 2, 48, 16, 3, 0, 0, 4, 0, 0], np.int32)     # V D L H KV F T eot tmpl n_mtp n_exp win full_every
+    n = ref.param_count(hdr)
+    from cudalm_c_b200 import model
+    cfg = model.Config(L=2, D=32, H=2, KV=2, hd=16, E=4, K=2, F=48, V=64, T=16, B=1)
+    assert model.Offsets(cfg).total == n
+    rng = np.random.default_rng(0)
+    P = rng.standard_normal(n).astype(np.float32)
+    mine, theirs = str(tmp_path / "mine.bin"), str(tmp_path / "theirs.bin")
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    q.check(L.qlmb_modelfile_write(mine.encode(), p(hdr), p(P), n, None, 0))
+    ref.model_save(theirs, hdr, P)
+    assert open(mine, "rb").read() == open(theirs, "rb").read()
+    h2, P2 = ref.model_load(mine, n)
+    assert (h2 == hdr).all() and (P2 == P).all()
+    h3 = np.zeros(13, np.int32); cap = C.c_ulonglong(0); tb = C.c_int(0)
+    q.check(L.qlmb_modelfile_read_header(theirs.encode(), p(h3), C.byref(cap), C.byref(tb)))
+    assert (h3 == hdr).all() and cap.value >= n
+    P3 = np.zeros(n, np.float32)
+    q.check(L.qlmb_modelfile_read(theirs.encode(), p(P3), n, None, 0, C.byref(tb)))
+    assert (P3 == P).all() and tb.value == 0
+    assert L.qlmb_modelfile_read(theirs.encode(), p(np.zeros(n + 8, np.float32)), n + 8, None, 0, None) != 0   # truncated body is refused
