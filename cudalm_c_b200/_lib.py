@@ -53,6 +53,9 @@ PROTOTYPES = {
     "qlmb_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, cf, cf, cf, cf, cf, vp, cf, cf,
                        ci, u64, ci, vp, ci, ci, ci, vp]),
     "qlmb_set_v4": (ci, [ci]),
+    "qlmb_ngram_key": (ci, [vp, vp, ci, ci, ci, ci, ci, vp]),
+    "qlmb_dec_ngkey": (ci, [vp, vp, vp, ci, ci, ci, ci, vp]),
+    "qlmb_ngram_gather": (ci, [vp, vp, vp, ci, ci, ci, vp]),
     "qlmb_ng_touched": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp]),
     "qlmb_ng_scatter_compact": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_ng_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, cf, cf, cf, cf, cf, cf, cf, u64, u64, vp, vp]),

@@ -520,6 +520,43 @@ __global__ void __launch_bounds__(1024) k_dec_sample(int *out, float *lp, const 
     out[s] = si[pick]; lp[s] = sv[pick] - ls;
 }
 
+
+// ------------------------------------------------------------------ n-gram table: keys and gather
+// k_ngram_key (cudalm.cu:4438-4445): the table row of position n from the hash of its last `order` tokens
+// (FNV-1a over the token ids, folded, modulo R, plus base); -1 for the first order-1 positions of a sequence.
+__global__ void __launch_bounds__(256) k_ngram_key(int *key, const int *tok, int N, int T, int R, int order, int base)
+{
+    const int n = blockIdx.x * 256 + threadIdx.x;
+    if (n >= N) return;
+    if (n % T < order - 1) { key[n] = -1; return; }
+    unsigned h = 2166136261u;
+    for (int j = order - 1; j >= 0; j--) h = (h ^ (unsigned)tok[n - j]) * 16777619u;
+    h ^= h >> 15;
+    key[n] = base + (int)(h % (unsigned)R);
+}
+// k_dec_ngkey (cudalm.cu:7056-7062): the same key for a decoder slot from its window of last tokens tokw[b*4 .. b*4+3]
+__global__ void __launch_bounds__(256) k_dec_ngkey(int *key, const int *tokw, const int *pos, int B, int R, int order, int base)
+{
+    const int b = blockIdx.x * 256 + threadIdx.x;
+    if (b >= B) return;
+    if (pos[b] < order - 1) { key[b] = -1; return; }
+    unsigned h = 2166136261u;
+    for (int j = order - 1; j >= 0; j--) h = (h ^ (unsigned)tokw[b * 4 + 3 - j]) * 16777619u;
+    h ^= h >> 15;
+    key[b] = base + (int)(h % (unsigned)R);
+}
+// k_ngram_gather (cudalm.cu:4446-4451): buf[n,:] = sum over the nk key sets (ascending) of the table rows, masked keys skipped
+__global__ void __launch_bounds__(256) k_ngram_gather(float *buf, const float *tbl, const int *key, int N, int De, int nk)
+{
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (size_t)N * De) return;
+    const int n = (int)(i / De), e = (int)(i % De);
+    int k = key[n];
+    float s = k >= 0 ? tbl[(size_t)k * De + e] : 0.0f;
+    for (int j = 1; j < nk; j++) { k = key[(size_t)j * N + n]; if (k >= 0) s += tbl[(size_t)k * De + e]; }
+    buf[i] = s;
+}
+
 }  // namespace qlmb
 
 using namespace qlmb;
@@ -669,5 +706,32 @@ extern "C" int qlmb_dec_sample(int *out, float *lp, const float *logits, const q
     if (B <= 0) return QLMB_OK;
     k_dec_sample<<<(unsigned)B, 1024, 0, as_stream(stream)>>>(out, lp, logits, params, V);
     QLMB_LAUNCH_CHECK("k_dec_sample");
+    return QLMB_OK;
+}
+
+// ---- n-gram table forward (ngram_forward, cudalm.cu:4701-4716) ----
+extern "C" int qlmb_ngram_key(int *key, const int *tok, int N, int T, int R, int order, int base, void *stream)
+{
+    QLMB_REQUIRE(key && tok && T > 0 && R > 0 && order >= 1, "qlmb_ngram_key: bad argument");
+    if (N <= 0) return QLMB_OK;
+    k_ngram_key<<<(N + 255) / 256, 256, 0, as_stream(stream)>>>(key, tok, N, T, R, order, base);
+    QLMB_LAUNCH_CHECK("k_ngram_key");
+    return QLMB_OK;
+}
+extern "C" int qlmb_dec_ngkey(int *key, const int *tokw, const int *pos, int B, int R, int order, int base, void *stream)
+{
+    QLMB_REQUIRE(key && tokw && pos && R > 0 && order >= 1 && order <= 4, "qlmb_dec_ngkey: bad argument");
+    if (B <= 0) return QLMB_OK;
+    k_dec_ngkey<<<(B + 255) / 256, 256, 0, as_stream(stream)>>>(key, tokw, pos, B, R, order, base);
+    QLMB_LAUNCH_CHECK("k_dec_ngkey");
+    return QLMB_OK;
+}
+extern "C" int qlmb_ngram_gather(float *buf, const float *tbl, const int *key, int N, int De, int nk, void *stream)
+{
+    QLMB_REQUIRE(buf && tbl && key && De > 0 && nk >= 1, "qlmb_ngram_gather: bad argument");
+    if (N <= 0) return QLMB_OK;
+    const size_t total = (size_t)N * De;
+    k_ngram_gather<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(buf, tbl, key, N, De, nk);
+    QLMB_LAUNCH_CHECK("k_ngram_gather");
     return QLMB_OK;
 }

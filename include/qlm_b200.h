@@ -129,6 +129,14 @@ int qlmb_ng_step(float *P, const float *Gc, int8_t *d, int8_t *r, const float *s
                  float b2, float wd, float sref, float inv_bc1, float inv_sqrt_bc2, uint64_t t, uint64_t nt,
                  const float *gs, void *stream);
 
+/* The table's forward (ngram_forward, cudalm.cu:4701-4716).  k_ngram_key (4438-4445): key[n] = base + hash of the
+ * last `order` token ids of position n, modulo R; -1 for the first order-1 positions of a sequence of T.
+ * k_dec_ngkey (7056-7062): the same from a decoder slot's window of its last four tokens and its position.
+ * k_ngram_gather (4446-4451): buf[n,:] = sum over the nk key sets (key[j*N + n], ascending j) of the table rows. */
+int qlmb_ngram_key(int *key, const int *tok, int N, int T, int R, int order, int base, void *stream);
+int qlmb_dec_ngkey(int *key, const int *tokw, const int *pos, int B, int R, int order, int base, void *stream);
+int qlmb_ngram_gather(float *buf, const float *tbl, const int *key, int N, int De, int nk, void *stream);
+
 /* k_qlm_servo (qlm.cuh:404-441). */
 int qlmb_servo(int8_t *d, int8_t *r, float *s, const qlmb_span *sp, int nspan, int ngrp, int group,
                int dmax, float f_hi, float f_lo, int packed, void *stream);

@@ -256,6 +256,17 @@ class Reference:
         n = int(self.lib.ref_model_load(path.encode(), _p(hdr), _p(P), C.c_ulonglong(cap)))
         return hdr, P[:n]
 
+    # ---- n-gram table forward (cpu_kern.h:598-610) ----
+    def ngram_key(self, tok, T, R, order, base):
+        key = np.zeros(tok.size, np.int32)
+        self.lib.ref_ngram_key(_p(tok), _p(key), C.c_int(tok.size), C.c_int(T), C.c_int(R), C.c_int(order), C.c_int(base))
+        return key
+
+    def ngram_gather(self, tbl, key, N, De, nk):
+        buf = np.zeros((N, De), np.float32)
+        self.lib.ref_ngram_gather(_p(tbl), _p(key), _p(buf), C.c_int(N), C.c_int(De), C.c_int(nk))
+        return buf
+
     # ---- 4-bit n-gram table update (cpu_kern.h:615-660) ----
     def ng_touched(self, key, De, group, ngrp):
         slot = np.full(ngrp, -1, np.int32); tgi = np.zeros(key.size, np.int32); cidx = np.zeros(key.size, np.int32)

@@ -104,6 +104,10 @@ void ref_attn_bwd(const float *Q, const float *K, const float *V, const float *O
     cpu_attn_bwd(Q, K, V, dA, lse, drow, dQ, dK, dV, win, B, T, H, KV, hd, H * hd, KV * hd);
 }
 
+/* ---- n-gram table forward (cpu_kern.h:598-610) ---- */
+void ref_ngram_key(const int *tok, int *key, int N, int T, int R, int order, int base) { KL(k_ngram_key, 1, 1)(tok, key, N, T, R, order, base); }
+void ref_ngram_gather(const float *tbl, const int *key, float *buf, int N, int De, int nk) { KL(k_ngram_gather, 1, 1)(tbl, key, buf, N, De, nk); }
+
 /* ---- 4-bit n-gram table update (cpu_kern.h:615-660; ng_build_touched / ng_tbl_step, cudalm.cu:4673-4745) ---- */
 int ref_ng_touched(const int *key, int *slot /* ngrp ints, all -1 */, int *tgi, int *cidx, int N, int De, int grp)
 {

@@ -121,3 +121,37 @@ def test_lm_head_ce_and_backward(cuda, ref):
     assert np.linalg.norm(a - b) / np.linalg.norm(b) < 1e-2
     a, b = (G.cpu().numpy() - G0).astype(np.float64), (Gr - G0).astype(np.float64)
     assert np.linalg.norm(a - b) / np.linalg.norm(b) < 1e-2
+
+
+def test_ngram_keys_and_gather(cuda, ref):
+    """k_ngram_key / k_ngram_gather (cudalm.cu:4438-4451) against the reference's CPU kernels: keys bit-exact, the
+    gathered sums bit-exact (same order); k_dec_ngkey gives the key the training kernel gives at the same position."""
+    import cudalm_c_b200 as q
+    from cudalm_c_b200._lib import check, lib, ptr, stream_ptr
+    rng = np.random.default_rng(5)
+    B, T, V, R, De = 3, 50, 500, 300, 32
+    N = B * T
+    tok = rng.integers(0, V, N).astype(np.int32)
+    L = lib()
+    d_tok = torch.from_numpy(tok).to(cuda)
+    keys = []
+    for order, base in ((2, 0), (3, R)):
+        k = torch.zeros(N, dtype=torch.int32, device=cuda)
+        check(L.qlmb_ngram_key(ptr(k), ptr(d_tok), N, T, R, order, base, stream_ptr()))
+        kr = ref.ngram_key(tok, T, R, order, base)
+        assert (k.cpu().numpy() == kr).all()
+        keys.append(kr)
+    key2 = np.concatenate(keys)                                     # two key sets, as with the trigram half on
+    tbl = rng.standard_normal((2 * R, De)).astype(np.float32)
+    buf = torch.zeros(N, De, device=cuda)
+    d_tbl, d_key2 = torch.from_numpy(tbl).to(cuda), torch.from_numpy(key2).to(cuda)      # kept alive across the call
+    check(L.qlmb_ngram_gather(ptr(buf), ptr(d_tbl), ptr(d_key2), N, De, 2, stream_ptr()))
+    assert (buf.cpu().numpy() == ref.ngram_gather(tbl, key2, N, De, 2)).all()
+    # decoder: slot b sits at position p of sequence b; its window holds the last four tokens
+    p = 17
+    tokw = np.stack([tok[b * T + p - 3:b * T + p + 1] for b in range(B)]).astype(np.int32)
+    dk = torch.zeros(B, dtype=torch.int32, device=cuda)
+    d_tokw, d_pos = torch.from_numpy(tokw).to(cuda), torch.full((B,), p, dtype=torch.int32, device=cuda)
+    check(L.qlmb_dec_ngkey(ptr(dk), ptr(d_tokw), ptr(d_pos), B, R, 3, R, stream_ptr()))
+    assert (dk.cpu().numpy() == keys[1].reshape(B, T)[:, p]).all()
+    q.check(q.lib().qlmb_check_device(None))
