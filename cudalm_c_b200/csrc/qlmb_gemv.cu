@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(256) k_gemv_finish_combine(bf16 *out, const bf
     out[i] = __float2bfloat16_rn(acc);
 }
 
-// Experts of a decode step with at most 32 routed rows: three routed GEMVs that read only the chosen experts'
+// Experts of a decode step with at most 64 routed rows: three routed GEMVs that read only the chosen experts'
 // codes (W1, W3: [E][D][F]; W2: [E][F][D]), SwiGLU and the gate-weighted combination in the slice-sum kernels.
 int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, const void *f_norm, const int *assign,
                        const float *gate, cudaStream_t st)
