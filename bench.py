@@ -562,14 +562,34 @@ def run_train(args):
     tgts = [torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).pin_memory() for _ in range(4)]
     losses = []
 
+    tok_d = torch.zeros(N, dtype=torch.int32, device=dev); tgt_d = torch.zeros(N, dtype=torch.int32, device=dev)
+    graph = None
+    loss_d = None
+
     def step(i):
-        tok = toks[i % 4].to(dev, non_blocking=True); tgt = tgts[i % 4].to(dev, non_blocking=True)
-        loss = m.train_step(tok, tgt)
-        losses.append(float(loss.mean()))                # device -> host read of the step's result
+        nonlocal loss_d
+        tok_d.copy_(toks[i % 4], non_blocking=True); tgt_d.copy_(tgts[i % 4], non_blocking=True)
+        if graph is not None:
+            graph.replay()                               # forward + head + backward: about 700 launches, no host work
+        else:
+            m.forward(tok_d)
+            loss_d = m.backward(tok_d, tgt_d)
+        m.update()                                       # the step counter and bias corrections change every step: not captured
+        losses.append(float(loss_d.mean()))              # device -> host read of the step's result
 
     for i in range(max(args.warmup, 3)):
         step(i)
     torch.cuda.synchronize()
+    if world == 1 and not args.no_graph:
+        # one GPU: the host needs about as long to issue the step's launches as the GPU to run them, so forward
+        # and backward are replayed from a CUDA graph (same kernels, same order; the library keeps its side streams off
+        # while a stream is captured)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            m.forward(tok_d)
+            loss_d = m.backward(tok_d, tgt_d)
+        step(0)
+        torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
@@ -783,6 +803,7 @@ def main():
     ap.add_argument("--params", type=int, default=125829120, help="span size of --workload adamw")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="N>1: peer = foreign rows read by peer loads inside the row kernels; nccl = all-to-all exchanges")
+    ap.add_argument("--no-graph", action="store_true", help="--workload train: issue every launch from the host instead of replaying forward + backward from a CUDA graph")
     ap.add_argument("--decode-b", default="1,8,64", help="live slots of --workload decode (comma list; BASELINE config 5 has 1,8,64)")
     ap.add_argument("--new-tokens", type=int, default=256, help="generated tokens of --workload decode (256 in BASELINE config 5; fewer for profiler captures)")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the 8192 of config 2); smaller values are for profiler captures")

@@ -170,7 +170,17 @@ __global__ void __launch_bounds__(128) k_gamma_part(float *part, const void *X, 
     if (j >= D) return;
     const int r0 = (int)((long long)N * c / GAMMA_CH), r1 = (int)((long long)N * (c + 1) / GAMMA_CH);
     float acc = 0.0f;
-    for (int n = r0; n < r1; n++) acc += blk_ld(X, x_dtype, (size_t)n * D + j) * rinv[n] * blk_ld(dy, dy_dtype, (size_t)n * D + j);
+    int n = r0;
+    for (; n + 8 <= r1; n += 8) {                        // eight rows of loads in flight, added in row order
+        float x[8], d[8], r[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            x[k] = blk_ld(X, x_dtype, (size_t)(n + k) * D + j); d[k] = blk_ld(dy, dy_dtype, (size_t)(n + k) * D + j); r[k] = __ldg(rinv + n + k);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc += x[k] * r[k] * d[k];
+    }
+    for (; n < r1; n++) acc += blk_ld(X, x_dtype, (size_t)n * D + j) * rinv[n] * blk_ld(dy, dy_dtype, (size_t)n * D + j);
     part[(size_t)c * D + j] = acc;
 }
 __global__ void __launch_bounds__(128) k_gamma_sum(float *G, const float *part, int D)
