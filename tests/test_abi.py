@@ -40,6 +40,30 @@ def test_argument_errors_are_reported_not_fatal():
         q.check(rc)
 
 
+def test_shape_errors_of_the_step_operators():
+    """The attention / block / decoder entry points check their shapes before touching a device: a bad call returns a
+    status and a message (the reference would exit), so it can be tried without a GPU."""
+    import cudalm_c_b200 as q
+    L = q.lib()
+    one = ctypes.c_void_p(16)                              # any non-NULL pointer; the checks come first
+    cases = [
+        (lambda: L.qlmb_attn_fwd(one, one, one, one, one, 1, 128, 2, 2, 32, 0, None), b"head dimension"),
+        (lambda: L.qlmb_attn_fwd(one, one, one, one, one, 1, 128, 3, 2, 64, 0, None), b"bad shape"),
+        (lambda: L.qlmb_attn_bwd(one, one, one, one, one, one, one, one, one, one, 1, 128, 2, 2, 128, 0, None), b"head dimension"),
+        (lambda: L.qlmb_rope(one, 1, one, one, 8, 2, 63, 16, 0, None), b"qlmb_rope"),
+        (lambda: L.qlmb_rmsnorm_fwd(one, 1, one, one, 1, one, 8, 30, None), b"multiple of 4"),
+        (lambda: L.qlmb_gemm_nt(one, 0, one, one, 8, 100, 128, 0.0, None), b"qlmb_gemm_nt"),
+        (lambda: L.qlmb_dec_attn(one, one, one, one, one, 0, 1, 8192, 2, 2, 64, None), b"qlmb_dec_attn"),
+        (lambda: L.qlmb_gemv_decode_stack(one, one, one, one, 3, 100, 768, 768, 1, None), b"qlmb_gemv_decode_stack"),
+        (lambda: L.qlmb_ng_touched(one, one, one, one, 8, 32, 100, 4, None), b"qlmb_ng_touched"),
+        (lambda: L.qlmb_softmax_ce(one, 5, one, one, one, 0, 4, 16, 4, None), b"qlmb_softmax_ce"),
+    ]
+    for call, needle in cases:
+        rc = call()
+        assert rc != 0
+        assert needle in L.qlmb_last_error(), (needle, L.qlmb_last_error())
+
+
 def test_no_fallback_when_library_missing(monkeypatch):
     import cudalm_c_b200._lib as m
     monkeypatch.setattr(m, "_lib", None)
