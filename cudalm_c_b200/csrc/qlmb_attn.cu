@@ -5,10 +5,10 @@
 //   warp 0      TMA producer   Q tile once; K and V tiles of 128 keys through a two-stage ring
 //   warp 1      MMA issuer     S = Q K^T (128 x 128 x 64) and PV = P V (128 x 64 x 128) with
 //                              tcgen05.mma, fp32 results in TMEM (S: 128 columns, PV: 64 columns)
-//   warps 2-5   softmax        a thread owns one query row: tcgen05.ld of its S row, running
-//                              max / sum in the exp2 domain, P as bf16 into shared memory in the
-//                              128-byte-swizzled K-major layout the PV MMA reads, and
-//                              O = O * corr + PV in registers
+//   warps 2-9   softmax        two threads per query row (64 keys and 32 output dimensions each):
+//                              tcgen05.ld of the S row, running max / sum in the exp2 domain, P as
+//                              bf16 into shared memory in the 128-byte-swizzled K-major layout the
+//                              PV MMA reads, and O = O * corr + PV in registers
 //
 // The MMA warp issues PV(t) and S(t+1) back to back as soon as P(t) is in shared memory, so the
 // tensor core works on the next scores while the softmax warps fold PV(t) into O; the second CTA
@@ -28,7 +28,7 @@ constexpr int AT_BN = 128;                    // keys per step
 constexpr int AT_HD = 64;
 constexpr int AT_TILE = AT_BM * AT_HD * 2;    // bytes of a Q, K or V tile
 constexpr int AT_P_BYTES = AT_BM * AT_BN * 2;
-constexpr int AT_FWD_SMEM = AT_TILE + 4 * AT_TILE + AT_P_BYTES + 256;
+constexpr int AT_FWD_SMEM = AT_TILE + 4 * AT_TILE + AT_P_BYTES + 768;   // + barriers (256 B) + one exchange word per query row
 
 struct AttnFwdParams {
     alignas(64) CUtensorMap q_map, k_map, v_map;
@@ -89,15 +89,17 @@ __device__ __forceinline__ bool attn_valid(int key, int i, int T, int win)
     return key <= i && key < T && (win <= 0 || key > i - win);
 }
 
-__global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ AttnFwdParams p)
+__global__ void __launch_bounds__(320, 2) k_attn_fwd(const __grid_constant__ AttnFwdParams p)
 {
     extern __shared__ __align__(1024) uint8_t at_smem[];
     uint8_t *sQ = at_smem, *sK = sQ + AT_TILE, *sV = sK + 2 * AT_TILE, *sP = sV + 2 * AT_TILE;
     uint64_t *bars = reinterpret_cast<uint64_t *>(sP + AT_P_BYTES);
     uint64_t *q_full = bars, *kv_full = bars + 1, *kv_empty = bars + 3, *s_full = bars + 5, *p_full = bars + 6,
              *o_full = bars + 7, *spare = bars + 8;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 10);
+    uint64_t *pair_bar = bars + 10;           // one per TMEM lane quarter: the two warps that share a query row meet here
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    int *xrow = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(bars) + 256);   // 128 words: running row maximum, then row sum
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (smem_u32(at_smem) & 1023u) {          // the swizzled tiles need a 1 KiB-aligned base
@@ -109,12 +111,14 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
         mbar_init(smem_u32(q_full), 1);
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&kv_full[i]), 1); mbar_init(smem_u32(&kv_empty[i]), 1); }
         mbar_init(smem_u32(s_full), 1);
-        mbar_init(smem_u32(p_full), 4);
+        mbar_init(smem_u32(p_full), 8);
+        for (int i = 0; i < 4; i++) mbar_init(smem_u32(&pair_bar[i]), 2);
         mbar_init(smem_u32(o_full), 1);
         mbar_init(smem_u32(spare), 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
+    if (threadIdx.x >= 64 && threadIdx.x < 192) xrow[threadIdx.x - 64] = (int)0x80000000;      // below every encoded maximum
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 256); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
@@ -208,53 +212,65 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
         }
     } else {
         // =============================== softmax + output ===============================
-        const int q = warp & 3, r = q * 32 + lane, i = q0 + r;       // tile row = TMEM lane, query index
+        // Two threads per query row: warps w and w + 4 share a TMEM lane quarter; thread (r, hf) takes keys
+        // [64 hf, 64 hf + 64) of every step and output dimensions [32 hf, 32 hf + 32).  The row maximum is a running
+        // atomicMax on one shared word per row (order-preserving integer image of the float): both threads add their
+        // half's maximum, meet on the quarter's mbarrier and read the same value.  No reset is needed: the running
+        // maximum only grows, and the next step's atomicMax cannot come before the partner has read this step's value,
+        // because the next scores are only issued after both warps arrived on p_full.
+        const int q = warp & 3, hf = (warp - 2) >> 2, r = q * 32 + lane, i = q0 + r;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        const uint32_t pb = smem_u32(&pair_bar[q]);
+        uint32_t pphase = 0;
         float m = -1e30f, l = 0.0f, corr_pend = 1.0f;
-        float o[AT_HD];
+        float o[32];
 #pragma unroll
-        for (int d = 0; d < AT_HD; d++) o[d] = 0.0f;
+        for (int d = 0; d < 32; d++) o[d] = 0.0f;
         bool ok = true;
-        auto fold_pv = [&]() {                 // O = O * corr + PV for the tile whose PV just completed
-            uint32_t v0[32], v1[32];             // both TMEM loads in flight: one round trip
-            tmem_ld32(tPV + lane_base, v0);
-            tmem_ld32(tPV + lane_base + 32, v1);
+        auto pair_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pb);
+            const bool got = at_wait(pb, pphase, abort_flag, p.errword, 123);
+            pphase ^= 1u;
+            return got;
+        };
+        auto enc = [](float f) { const int b = __float_as_int(f); return b >= 0 ? b : b ^ 0x7fffffff; };
+        auto dec = [](int b) { return __int_as_float(b >= 0 ? b : b ^ 0x7fffffff); };
+        auto fold_pv = [&]() {                 // O = O * corr + PV for this thread's 32 output dimensions
+            uint32_t v[32];
+            tmem_ld32(tPV + lane_base + hf * 32, v);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-                o[j] = o[j] * corr_pend + __uint_as_float(v0[j]);
-                o[32 + j] = o[32 + j] * corr_pend + __uint_as_float(v1[j]);
-            }
+            for (int j = 0; j < 32; j++) o[j] = o[j] * corr_pend + __uint_as_float(v[j]);
         };
         for (int t = 0; ok && t < nt; t++) {
-            const int k0 = (kt_lo + t) * AT_BN;
-            const bool masked = (k0 + AT_BN - 1 > q0) || p.win > 0 || (k0 + AT_BN > p.T);
+            const int k0 = (kt_lo + t) * AT_BN + hf * 64;               // first key of this thread's half
+            const bool masked = (k0 + 63 > q0) || p.win > 0 || (k0 + 64 > p.T);
             ok = at_wait(smem_u32(s_full), (uint32_t)t & 1u, abort_flag, p.errword, 120);
             if (!ok) break;
             tc_fence_after();
-            // pass 1: row maximum
+            // pass 1: maximum of this half of the row
             float mx = -1e30f;
 #pragma unroll
-            for (int c = 0; c < 4; c += 2) {             // two 32-column loads per round trip
-                uint32_t v[2][32];
-                tmem_ld32(tS + lane_base + c * 32, v[0]);
-                tmem_ld32(tS + lane_base + c * 32 + 32, v[1]);
+            for (int c = 0; c < 2; c++) {
+                uint32_t v[32];
+                tmem_ld32(tS + lane_base + hf * 64 + c * 32, v);
                 tmem_ld_wait();
+                if (masked) {
 #pragma unroll
-                for (int cc = 0; cc < 2; cc++) {
-                    if (masked) {
+                    for (int j = 0; j < 32; j++)
+                        if (attn_valid(k0 + c * 32 + j, i, p.T, p.win)) mx = fmaxf(mx, __uint_as_float(v[j]));
+                } else {
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (attn_valid(k0 + (c + cc) * 32 + j, i, p.T, p.win)) mx = fmaxf(mx, __uint_as_float(v[cc][j]));
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(v[cc][j]));
-                    }
+                    for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(v[j]));
                 }
             }
-            const float m_new = fmaxf(m, mx * p.scale_log2);
+            atomicMax(&xrow[r], enc(fmaxf(mx * p.scale_log2, -1e30f)));
+            ok = pair_sync();
+            if (!ok) break;
+            const float m_new = dec(*reinterpret_cast<volatile int *>(&xrow[r]));
             const float corr = ex2(m - m_new);
-            // the previous tile's PV: its MMA was issued before this tile's S, so it has completed
+            // the previous step's PV: its MMA was issued before this step's S, so it has completed
             if (t > 0) {
                 ok = at_wait(smem_u32(o_full), (uint32_t)(t - 1) & 1u, abort_flag, p.errword, 121);
                 if (!ok) break;
@@ -262,18 +278,14 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
                 fold_pv();
             }
             corr_pend = corr;
-            // pass 2: P = exp2(s - m) as bf16 into the swizzled K-major tile, row sum
+            // pass 2: P = exp2(s - m) as bf16 into this half's swizzled K-major sub-tile, partial row sum
             float rs = 0.0f;
+            uint8_t *rowp = sP + hf * (AT_BM * 128) + r * 128;
 #pragma unroll
-            for (int cp = 0; cp < 2; cp++) {
-              uint32_t vv[2][32];                        // two 32-column loads per round trip
-              tmem_ld32(tS + lane_base + cp * 64, vv[0]);
-              tmem_ld32(tS + lane_base + cp * 64 + 32, vv[1]);
-              tmem_ld_wait();
-#pragma unroll
-              for (int cc = 0; cc < 2; cc++) {
-                const int c = cp * 2 + cc;
-                const uint32_t *v = vv[cc];
+            for (int c = 0; c < 2; c++) {
+                uint32_t v[32];
+                tmem_ld32(tS + lane_base + hf * 64 + c * 32, v);
+                tmem_ld_wait();
                 uint32_t pk[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
@@ -287,13 +299,11 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                     pk[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                 }
-                uint8_t *rowp = sP + (c >> 1) * (AT_BM * 128) + r * 128;
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
-                    const int unit = ((c & 1) * 4 + u) ^ (r & 7);
+                    const int unit = (c * 4 + u) ^ (r & 7);
                     *reinterpret_cast<uint4 *>(rowp + unit * 16) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
                 }
-              }
             }
             l = l * corr + rs;
             m = m_new;
@@ -306,20 +316,31 @@ __global__ void __launch_bounds__(192, 2) k_attn_fwd(const __grid_constant__ Att
         if (ok) {
             tc_fence_after();
             fold_pv();
-            if (i < p.T) {
-                const float inv = 1.0f / l;
-                bf16 *orow = p.O + ((size_t)b * p.T + i) * ((size_t)p.H * AT_HD) + (size_t)h * AT_HD;
+            // the row sum: the upper half hands its partial sum over, the lower half returns the total
+            float *xl = reinterpret_cast<float *>(xrow);
+            if (hf == 1) xl[r] = l;
+            ok = pair_sync();
+            if (ok) {
+                if (hf == 0) { l += *reinterpret_cast<volatile float *>(&xl[r]); xl[r] = l; }
+                ok = pair_sync();
+            }
+            if (ok) {
+                if (hf == 1) l = *reinterpret_cast<volatile float *>(&xl[r]);
+                if (i < p.T) {
+                    const float inv = 1.0f / l;
+                    bf16 *orow = p.O + ((size_t)b * p.T + i) * ((size_t)p.H * AT_HD) + (size_t)h * AT_HD + hf * 32;
 #pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    uint32_t w[4];
+                    for (int u = 0; u < 4; u++) {
+                        uint32_t w[4];
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(o[u * 8 + 2 * k] * inv, o[u * 8 + 2 * k + 1] * inv);
-                        w[k] = *reinterpret_cast<uint32_t *>(&h2);
+                        for (int k = 0; k < 4; k++) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(o[u * 8 + 2 * k] * inv, o[u * 8 + 2 * k + 1] * inv);
+                            w[k] = *reinterpret_cast<uint32_t *>(&h2);
+                        }
+                        *reinterpret_cast<uint4 *>(orow + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    *reinterpret_cast<uint4 *>(orow + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (hf == 0) p.lse[((size_t)b * p.H + h) * p.T + i] = (m + log2f(l)) * 0.6931471805599453f;
                 }
-                p.lse[((size_t)b * p.H + h) * p.T + i] = (m + log2f(l)) * 0.6931471805599453f;
             }
         }
         tc_fence_before();
@@ -835,7 +856,7 @@ extern "C" int qlmb_attn_fwd(void *O, float *lse, const void *Q, const void *K, 
         QLMB_CUDA(cudaFuncSetAttribute(k_attn_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_FWD_SMEM));
         configured_dev[dev_] = true;
     }
-    k_attn_fwd<<<(unsigned)(p.nqt * B * H), 192, AT_FWD_SMEM, as_stream(stream)>>>(p);
+    k_attn_fwd<<<(unsigned)(p.nqt * B * H), 320, AT_FWD_SMEM, as_stream(stream)>>>(p);
     QLMB_LAUNCH_CHECK("k_attn_fwd");
     return QLMB_OK;
 }
