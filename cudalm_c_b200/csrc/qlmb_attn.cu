@@ -187,6 +187,15 @@ __global__ void __launch_bounds__(320, 2) k_attn_fwd(const __grid_constant__ Att
             ok = at_wait(smem_u32(p_full), (uint32_t)t & 1u, abort_flag, p.errword, 112);
             if (!ok) break;
             tc_fence_after();
+            // the next scores first (the S columns are free once P is written): the softmax warps start on them while
+            // this step's PV runs; they fold PV(t) after their first pass and only then overwrite P
+            if (t + 1 < nt) {
+                ok = at_wait(smem_u32(&kv_full[st ^ 1]), ((uint32_t)(t + 1) >> 1) & 1u, abort_flag, p.errword, 113);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) issue_s(st ^ 1);
+                __syncwarp();
+            }
             if (lane == 0) {
                 const uint32_t a0 = smem_u32(sP), b0 = smem_u32(sV + st * AT_TILE);
 #pragma unroll
@@ -197,13 +206,6 @@ __global__ void __launch_bounds__(320, 2) k_attn_fwd(const __grid_constant__ Att
                 tc_commit(smem_u32(&kv_empty[st]));
             }
             __syncwarp();
-            if (t + 1 < nt) {
-                ok = at_wait(smem_u32(&kv_full[st ^ 1]), ((uint32_t)(t + 1) >> 1) & 1u, abort_flag, p.errword, 113);
-                if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) issue_s(st ^ 1);
-                __syncwarp();
-            }
         }
         if (*abort_flag) {                    // let issued MMAs retire (bounded) before TMEM is released
             if (lane == 0) tc_commit(smem_u32(spare));
@@ -545,6 +547,15 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
             ok = at_wait(smem_u32(pds_full), (uint32_t)it & 1u, abort_flag, p.errword, 212);
             if (!ok) break;
             tc_fence_after();
+            // the next step's scores first (their TMEM columns are free once P / dS are written), so that the
+            // element-wise warps work on them while the two accumulating products of this step run
+            if (it + 1 < nit) {
+                ok = at_wait(smem_u32(&qd_full[st ^ 1]), ((uint32_t)(it + 1) >> 1) & 1u, abort_flag, p.errword, 213);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) issue_scores(st ^ 1);
+                __syncwarp();
+            }
             if (lane == 0) {
                 const uint32_t pt = smem_u32(sPt), dst = smem_u32(sSt), q_ = smem_u32(sQ + st * AT_TILE), a_ = smem_u32(sA + st * AT_TILE);
 #pragma unroll
@@ -559,13 +570,6 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
                 tc_commit(smem_u32(&qd_empty[st]));
             }
             __syncwarp();
-            if (it + 1 < nit) {
-                ok = at_wait(smem_u32(&qd_full[st ^ 1]), ((uint32_t)(it + 1) >> 1) & 1u, abort_flag, p.errword, 213);
-                if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) issue_scores(st ^ 1);
-                __syncwarp();
-            }
         }
         if (*abort_flag) {
             if (lane == 0) tc_commit(smem_u32(spare));
@@ -583,7 +587,6 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
             const bool masked = (q0 < k0 + AT_BN - 1) || p.win > 0;
             ok = at_wait(smem_u32(&qd_full[st]), ((uint32_t)it >> 1) & 1u, abort_flag, p.errword, 220);      // lse / D in shared memory
             if (ok) ok = at_wait(smem_u32(s_full), (uint32_t)it & 1u, abort_flag, p.errword, 221);
-            if (ok && it > 0) ok = at_wait(smem_u32(acc_done), (uint32_t)(it - 1) & 1u, abort_flag, p.errword, 222);   // P / dS tiles free again
             if (!ok) break;
             tc_fence_after();
             const float *L2 = sL + st * 128 + hf * 64, *Dq = sD + st * 128 + hf * 64;
@@ -609,14 +612,19 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dkv(const __grid
                     h2 = __floats2bfloat162_rn(dsv[0], dsv[1]);
                     ds[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                 }
+                // the previous step's products must have read the P / dS tiles before they are overwritten
+                if (it > 0) ok = at_wait(smem_u32(acc_done), (uint32_t)(it - 1) & 1u, abort_flag, p.errword, 222);
                 uint8_t *prow = sPt + hf * (AT_BN * 128) + r * 128, *srow = sSt + hf * (AT_BN * 128) + r * 128;
+                if (ok) {
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int unit = (c * 4 + u) ^ (r & 7);
-                    *reinterpret_cast<uint4 *>(prow + unit * 16) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
-                    *reinterpret_cast<uint4 *>(srow + unit * 16) = make_uint4(ds[4 * u], ds[4 * u + 1], ds[4 * u + 2], ds[4 * u + 3]);
+                    for (int u = 0; u < 4; u++) {
+                        const int unit = (c * 4 + u) ^ (r & 7);
+                        *reinterpret_cast<uint4 *>(prow + unit * 16) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+                        *reinterpret_cast<uint4 *>(srow + unit * 16) = make_uint4(ds[4 * u], ds[4 * u + 1], ds[4 * u + 2], ds[4 * u + 3]);
+                    }
                 }
             }
+            if (!ok) break;
             fence_proxy_async();
             tc_fence_before();
             __syncwarp();
@@ -729,6 +737,13 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
             ok = at_wait(smem_u32(ds_full), (uint32_t)t & 1u, abort_flag, p.errword, 312);
             if (!ok) break;
             tc_fence_after();
+            if (t + 1 < nt) {                                 // next scores first, see k_attn_bwd_dkv
+                ok = at_wait(smem_u32(&kv_full[st ^ 1]), ((uint32_t)(t + 1) >> 1) & 1u, abort_flag, p.errword, 313);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) issue_scores(st ^ 1);
+                __syncwarp();
+            }
             if (lane == 0) {
                 const uint32_t s_ = smem_u32(sS), k_ = smem_u32(sK + st * AT_TILE);
 #pragma unroll
@@ -739,13 +754,6 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
                 tc_commit(smem_u32(&kv_empty[st]));
             }
             __syncwarp();
-            if (t + 1 < nt) {
-                ok = at_wait(smem_u32(&kv_full[st ^ 1]), ((uint32_t)(t + 1) >> 1) & 1u, abort_flag, p.errword, 313);
-                if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) issue_scores(st ^ 1);
-                __syncwarp();
-            }
         }
         if (*abort_flag) {
             if (lane == 0) tc_commit(smem_u32(spare));
@@ -763,7 +771,6 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
             const int k0 = (kt_lo + t) * AT_BN;
             const bool masked = (k0 + AT_BN - 1 > q0) || p.win > 0 || (k0 + AT_BN > p.T);
             ok = at_wait(smem_u32(s_full), (uint32_t)t & 1u, abort_flag, p.errword, 321);
-            if (ok && t > 0) ok = at_wait(smem_u32(acc_done), (uint32_t)(t - 1) & 1u, abort_flag, p.errword, 322);
             if (!ok) break;
             tc_fence_after();
             uint32_t sv[32], dv[32];                 // both TMEM loads of the step in flight: one round trip
@@ -785,13 +792,17 @@ __global__ void __launch_bounds__(AT_BWD_THREADS, 1) k_attn_bwd_dq(const __grid_
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(dsv[0], dsv[1]);
                     ds[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                 }
+                if (t > 0) ok = at_wait(smem_u32(acc_done), (uint32_t)(t - 1) & 1u, abort_flag, p.errword, 322);   // dS tile free again
                 uint8_t *srow = sS + hf * (AT_BM * 128) + r * 128;
+                if (ok) {
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int unit = (c * 4 + u) ^ (r & 7);
-                    *reinterpret_cast<uint4 *>(srow + unit * 16) = make_uint4(ds[4 * u], ds[4 * u + 1], ds[4 * u + 2], ds[4 * u + 3]);
+                    for (int u = 0; u < 4; u++) {
+                        const int unit = (c * 4 + u) ^ (r & 7);
+                        *reinterpret_cast<uint4 *>(srow + unit * 16) = make_uint4(ds[4 * u], ds[4 * u + 1], ds[4 * u + 2], ds[4 * u + 3]);
+                    }
                 }
             }
+            if (!ok) break;
             fence_proxy_async();
             tc_fence_before();
             __syncwarp();
