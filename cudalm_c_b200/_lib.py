@@ -89,6 +89,7 @@ PROTOTYPES = {
     "qlmb_linear_wgrad": (ci, [vp, vp, vp, ci, ci, ci, ci, cf, ci, vp]),
     "qlmb_gemv_decode": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_router_topk": (ci, [vp, vp, vp, ci, vp, vp, ci, vp, vp, vp, ci, ci, ci, ci, vp]),
+    "qlmb_router_bias_update": (ci, [vp, vp, ci, ci, ci, ci, cf, ci, vp]),
     "qlmb_perm_build": (ci, [vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]),
     "qlmb_moe_arena_bytes": (sz, [ci, ci, ci, ci, ci]),
     "qlmb_moe_arena_member": (vp, [vp, ci, ci, ci, ci, ci, C.c_char_p]),

@@ -257,6 +257,34 @@ int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N,
     return QLMB_OK;
 }
 
+// ---------------------------------------------------------------- selection bias
+// mbias_upd (cudalm.cu:3791-3802): aux-free balancing.  After routing, the selection-only bias of expert e moves
+// towards the target load m: b += u * (m - count_e) / m (proportional form) or b += u * sign(m - count_e).
+// With one bias row per top-k pass (the reference's default) block k counts pass k's assignments, otherwise one
+// block counts all K*N.  The counts are integer histograms in shared memory, so the result does not depend on
+// scheduling; the reference copies the counts to the host and the bias back, here nothing leaves the device.
+__global__ void __launch_bounds__(256) k_bias_update(float *bias, const int *assign, int N, int E, int K, int per_slot,
+                                                     float u, int proportional)
+{
+    __shared__ int hist[256];
+    const int s = blockIdx.x;
+    for (int e = threadIdx.x; e < E; e += 256) hist[e] = 0;
+    __syncthreads();
+    const int *a = per_slot ? assign + (size_t)s * N : assign;
+    const int n = per_slot ? N : K * N;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        const int e = a[i];
+        if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+    }
+    __syncthreads();
+    const float m = per_slot ? (float)N / (float)E : (float)K * (float)N / (float)E;
+    for (int e = threadIdx.x; e < E; e += 256) {
+        const float c = (float)hist[e];
+        const float d = proportional ? (m - c) / m : (c < m ? 1.0f : c > m ? -1.0f : 0.0f);
+        bias[(size_t)s * E + e] += u * d;
+    }
+}
+
 // lazily grown per-device scratch for the public perm entry point
 static int *g_perm_scratch[64];
 static size_t g_perm_cap[64];
@@ -282,4 +310,15 @@ extern "C" int qlmb_perm_build(const int *assign, int N, int E, int K, int merge
     }
     return perm_build(assign, N, E, K, merged, pad, perm, inv, off, counts, bad_flag, nullptr, nullptr,
                       g_perm_scratch[dev], as_stream(stream));
+}
+
+extern "C" int qlmb_router_bias_update(float *bias, const int *assign, int N, int E, int K, int per_slot, float u,
+                                       int proportional, void *stream)
+{
+    QLMB_REQUIRE(bias && assign, "qlmb_router_bias_update: NULL argument");
+    QLMB_REQUIRE(N > 0 && E > 0 && E <= 256 && K > 0 && K <= 8, "qlmb_router_bias_update: N=%d E=%d K=%d", N, E, K);
+    if (u == 0.0f) return QLMB_OK;
+    k_bias_update<<<per_slot ? K : 1, 256, 0, as_stream(stream)>>>(bias, assign, N, E, K, per_slot, u, proportional);
+    QLMB_LAUNCH_CHECK("k_bias_update");
+    return QLMB_OK;
 }

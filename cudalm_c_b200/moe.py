@@ -45,6 +45,13 @@ def moe_perm_all(assign, E, merged=False, pad=1):
     return perm, inv, off, counts, bad
 
 
+def router_bias_update(bias, assign, E, per_slot=True, u=0.001, proportional=True):
+    """mbias_upd (cudalm.cu:3791-3802) on the device: bias [K, E] (per_slot) or [E]; assign [K, N]."""
+    K, N = assign.shape
+    check(lib().qlmb_router_bias_update(ptr(bias), ptr(assign), N, E, K, 1 if per_slot else 0, u, 1 if proportional else 0,
+                                        stream_ptr()))
+
+
 class MoeLayerState:
     """One MoE layer's 4-bit expert weights, router and activation arena: the
     slice of the reference's GA / P that moe_forward and moe_backward touch."""

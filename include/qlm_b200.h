@@ -212,6 +212,13 @@ int qlmb_router_topk(const float *rt_in, float *rt_out, const void *X, int x_dty
                      const float *bias, int bias_stride, float *rprobs, int *assign, float *gate,
                      int N, int D, int E, int K, void *stream);
 
+/* mbias_upd (cudalm.cu:3791-3802): the selection-only bias the router adds to its probabilities (qlmb_router_topk's
+ * `bias`, [K][E] with per_slot, else [E]) moves towards the target load m after a step's routing:
+ * b += u * (m - count) / m (proportional) or u * sign(m - count); m = N/E per pass, K*N/E combined.  assign is the
+ * [K][N] table the router wrote.  The reference counts on the host and copies the bias back; this stays on the device. */
+int qlmb_router_bias_update(float *bias, const int *assign, int N, int E, int K, int per_slot, float u, int proportional,
+                            void *stream);
+
 /* moe_perm_all / moe_gperm (cudalm.cu:3537-3602): stable grouping of token
  * slots by expert.  merged=0: K sorts of N entries, off[K*(E+1)], perm[k*N+pos];
  * merged=1: one sort of the K*N entries n' = k*N+n, off[E+1].

@@ -99,3 +99,27 @@ def test_perm_out_of_range_expert_is_flagged(cuda):
     with pytest.raises(q.QlmbError):
         q.check(q.lib().qlmb_check_device(None))     # the error word was set ...
     q.check(q.lib().qlmb_check_device(None))         # ... and cleared by the read
+
+
+@pytest.mark.parametrize("per_slot,prop", [(True, True), (True, False), (False, True), (False, False)])
+def test_router_bias_update(cuda, per_slot, prop):
+    """mbias_upd (cudalm.cu:3793-3798) restated in numpy float32; three updates in a row, bit-exact."""
+    from cudalm_c_b200 import moe
+    rng = np.random.default_rng(31 + 2 * per_slot + prop)
+    N, E, K = 4096, 64, 2
+    u = f32(0.001) * f32(1.5)
+    rows = K if per_slot else 1
+    b = (rng.standard_normal((rows, E)) * 0.01).astype(f32)
+    db = dev(b, cuda)
+    for it in range(3):
+        asg = rng.integers(0, E, (K, N)).astype(np.int32)
+        asg[0, : N // 4] = 3                       # a hot expert, and one that gets exactly the target load
+        if per_slot:
+            asg[1] = np.arange(N) % E
+        moe.router_bias_update(db, dev(asg, cuda), E, per_slot=per_slot, u=float(u), proportional=prop)
+        m = f32(N) / f32(E) if per_slot else f32(K) * f32(N) / f32(E)
+        for s in range(rows):
+            c = np.bincount((asg[s] if per_slot else asg.ravel()), minlength=E).astype(f32)
+            d = (m - c) / m if prop else np.where(c < m, f32(1), np.where(c > m, f32(-1), f32(0))).astype(f32)
+            b[s] = b[s] + (u * d.astype(f32)).astype(f32)
+    assert np.array_equal(db.cpu().numpy(), b)
