@@ -81,6 +81,14 @@ class MoeLayerState:
         esz = torch.empty(0, dtype=dtype).element_size()
         return self.arena[off:off + n * esz].view(dtype).view(*shape)
 
+    def update_bias(self, u=0.001, proportional=True):
+        """After a training forward: move the selection bias towards balanced load (mbias_upd, cudalm.cu:4385).
+        bias_stride = E means one bias row per top-k pass, 0 one shared row."""
+        if self.bias is None:
+            raise ValueError("update_bias: the layer has no selection bias")
+        router_bias_update(self.bias, self.member("assign", (self.K, self.N), torch.int32), self.E,
+                           per_slot=self.c.bias_stride != 0, u=u, proportional=proportional)
+
     def forward(self, f_in, f_norm, out=None):
         out = out if out is not None else torch.empty_like(f_in)
         check(lib().qlmb_moe_forward(self.c, self.arena_ptr, ptr(out), ptr(f_in), ptr(f_norm), stream_ptr()))

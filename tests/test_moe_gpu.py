@@ -109,6 +109,27 @@ def test_midsize_vs_oracle(cuda, oracle):
         assert rel(dW2, dev(bw["dW2"], cuda)) < TOL_B
 
 
+def test_selection_bias_balances_the_load(cuda):
+    """Aux-free balancing on a layer (mbias_upd after moe_forward, cudalm.cu:4385): each update follows the
+    reference's formula on the counts of the forward that preceded it, and the hot expert's load falls."""
+    from cudalm_c_b200 import moe
+    N, D, F, E, K = 2048, 256, 256, 16, 2
+    L0, qs, wr, (fn, fi, _) = build_layer(cuda, N, D, F, E, K, 23)
+    bias = torch.zeros(K, E, device=cuda)
+    bias[:, 3] = 0.05                                # expert 3 starts over-selected in both passes
+    L = moe.MoeLayerState(N, D, F, E, K, qs[0], qs[1], qs[2], wr, bias=bias, bias_stride=E)
+    u, m, peak = f32(0.01), f32(N) / f32(E), []
+    for it in range(12):
+        L.forward(fi, fn)
+        asg = L.member("assign", (K, N), torch.int32).cpu().numpy()
+        before = bias.cpu().numpy().copy()
+        L.update_bias(u=float(u))
+        c = np.stack([np.bincount(asg[k], minlength=E) for k in range(K)]).astype(f32)
+        assert np.array_equal(bias.cpu().numpy(), before + u * ((m - c) / m))
+        peak.append(int(c.max()))
+    assert peak[0] > 2 * int(m) and peak[-1] < peak[0] // 2, peak
+
+
 def test_config2_full_size_properties(cuda):
     """BASELINE config 2 (8192 tokens, 32 experts, top-2, 768/1536): checks that do
     not need an fp32 recomputation of 348 GFLOP -- conservation of rows through the
