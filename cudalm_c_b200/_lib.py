@@ -56,6 +56,8 @@ PROTOTYPES = {
     "qlmb_ngram_key": (ci, [vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_dec_ngkey": (ci, [vp, vp, vp, ci, ci, ci, ci, vp]),
     "qlmb_ngram_gather": (ci, [vp, vp, vp, ci, ci, ci, vp]),
+    "qlmb_nggate_fwd": (ci, [vp, vp, vp, vp, ci, vp, vp, vp, ci, ci, vp]),
+    "qlmb_nggate_bwd": (ci, [vp, vp, vp, vp, ci, vp, vp, vp, vp, vp, ci, ci, vp]),
     "qlmb_ng_touched": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp]),
     "qlmb_ng_scatter_compact": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_ng_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, cf, cf, cf, cf, cf, cf, cf, u64, u64, vp, vp]),

@@ -99,3 +99,35 @@ def head_bwd(fn, emb, tgt, G_emb, chunk_rows=2048, denom=None):
         gemm_nt(dl, ebt, out=dfn[r0:r1])
         linear.linear_wgrad(G_emb, dl, fn[r0:r1], NK, beta=1.0)
     return loss, dfn
+
+
+def ngram_key(tok, T, R, order, base=0):
+    """k_ngram_key (cudalm.cu:4438-4445): table row of every position's last `order` tokens; -1 where masked."""
+    key = torch.empty(tok.numel(), dtype=torch.int32, device=tok.device)
+    check(lib().qlmb_ngram_key(ptr(key), ptr(tok), tok.numel(), T, R, order, base, stream_ptr()))
+    return key
+
+
+def ngram_gather(tbl, key, N, nk=1):
+    """k_ngram_gather (cudalm.cu:4446-4451): buf[n] = sum of the nk table rows key[j * N + n]."""
+    buf = torch.empty((N, tbl.shape[1]), dtype=torch.float32, device=tbl.device)
+    check(lib().qlmb_ngram_gather(ptr(buf), ptr(tbl), ptr(key), N, tbl.shape[1], nk, stream_ptr()))
+    return buf
+
+
+def nggate_fwd(h, v, k):
+    """k_nggate_f (cudalm.cu:3362-3368): h += g * v in place, k -> rms(k) in place; returns (hn, g, rh, rk)."""
+    N, D = h.shape
+    hn = torch.empty_like(h)
+    g, rh, rk = (torch.empty(N, dtype=torch.float32, device=h.device) for _ in range(3))
+    check(lib().qlmb_nggate_fwd(ptr(h), ptr(v), ptr(k), ptr(hn), _dt(h), ptr(g), ptr(rh), ptr(rk), N, D, stream_ptr()))
+    return hn, g, rh, rk
+
+
+def nggate_bwd(dy, v, hn, kn, g, rh, rk):
+    """k_nggate_b (cudalm.cu:3370-3378): dy += the gate's share of dh in place; returns (dv, dk)."""
+    N, D = dy.shape
+    dv, dk = torch.empty_like(dy), torch.empty_like(dy)
+    check(lib().qlmb_nggate_bwd(ptr(dy), ptr(v), ptr(hn), ptr(kn), _dt(dy), ptr(g), ptr(rh), ptr(rk), ptr(dv), ptr(dk), N, D,
+                                stream_ptr()))
+    return dv, dk

@@ -567,6 +567,61 @@ __global__ void __launch_bounds__(256) k_ngram_gather(float *buf, const float *t
     buf[i] = s;
 }
 
+
+// ---------------------------------------------------------------- n-gram context gate
+// k_nggate_f (cudalm.cu:3362-3368): per row, g = sigmoid(<rms(h), rms(k)> / sqrt(D)); h += g * v.  Leaves rms(h) in hn,
+// rms(k) in k (in place) and g, 1/rms(h), 1/rms(k) per row for the backward pass.  Warp per row, three sums in one pass.
+__global__ void __launch_bounds__(256) k_nggate_fwd(void *h, const void *v, void *k, void *hn, int dtype, float *g, float *rh,
+                                                    float *rk, int N, int D)
+{
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    const size_t o = (size_t)n * D;
+    float a = 0.0f, b = 0.0f, c = 0.0f;
+    for (int j = lane * 4; j < D; j += 128) {
+        const float4 x = blk_ld4(h, dtype, o + j), y = blk_ld4(k, dtype, o + j);
+        a += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+        b += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
+        c += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+    }
+    a = warp_sum(a); b = warp_sum(b); c = warp_sum(c);
+    const float r1 = 1.0f / sqrtf(a / (float)D + 1e-6f), r2 = 1.0f / sqrtf(b / (float)D + 1e-6f);
+    const float gg = 1.0f / (1.0f + expf(-(c * r1 * r2 / sqrtf((float)D))));
+    for (int j = lane * 4; j < D; j += 128) {
+        const float4 x = blk_ld4(h, dtype, o + j), y = blk_ld4(k, dtype, o + j), w = blk_ld4(v, dtype, o + j);
+        blk_st4(hn, dtype, o + j, make_float4(x.x * r1, x.y * r1, x.z * r1, x.w * r1));
+        blk_st4(k, dtype, o + j, make_float4(y.x * r2, y.y * r2, y.z * r2, y.w * r2));
+        blk_st4(h, dtype, o + j, make_float4(x.x + gg * w.x, x.y + gg * w.y, x.z + gg * w.z, x.w + gg * w.w));
+    }
+    if (lane == 0) { g[n] = gg; rh[n] = r1; rk[n] = r2; }
+}
+// k_nggate_b (cudalm.cu:3370-3378): dv = g * dy; dk and the part of dh that flows through the gate's logit; dy += that
+// part in place.
+__global__ void __launch_bounds__(256) k_nggate_bwd(void *dy, const void *v, const void *hn, const void *kn, int dtype,
+                                                    const float *g, const float *rh, const float *rk, void *dv, void *dk,
+                                                    int N, int D)
+{
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    const size_t o = (size_t)n * D;
+    float a = 0.0f, b = 0.0f;
+    for (int j = lane * 4; j < D; j += 128) {
+        const float4 d = blk_ld4(dy, dtype, o + j), w = blk_ld4(v, dtype, o + j);
+        const float4 x = blk_ld4(hn, dtype, o + j), y = blk_ld4(kn, dtype, o + j);
+        a += d.x * w.x + d.y * w.y + d.z * w.z + d.w * w.w;
+        b += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+    }
+    a = warp_sum(a); b = warp_sum(b);
+    const float gg = g[n], cz = a * gg * (1.0f - gg) / sqrtf((float)D), m = b / (float)D, r1 = rh[n], r2 = rk[n];
+    for (int j = lane * 4; j < D; j += 128) {
+        const float4 d = blk_ld4(dy, dtype, o + j), x = blk_ld4(hn, dtype, o + j), y = blk_ld4(kn, dtype, o + j);
+        blk_st4(dv, dtype, o + j, make_float4(gg * d.x, gg * d.y, gg * d.z, gg * d.w));
+        blk_st4(dk, dtype, o + j, make_float4(cz * (x.x - y.x * m) * r2, cz * (x.y - y.y * m) * r2, cz * (x.z - y.z * m) * r2,
+                                              cz * (x.w - y.w * m) * r2));
+        blk_st4(dy, dtype, o + j, make_float4(d.x + cz * (y.x - x.x * m) * r1, d.y + cz * (y.y - x.y * m) * r1,
+                                              d.z + cz * (y.z - x.z * m) * r1, d.w + cz * (y.w - x.w * m) * r1));
+    }
+}
 }  // namespace qlmb
 
 using namespace qlmb;
@@ -743,5 +798,27 @@ extern "C" int qlmb_ngram_gather(float *buf, const float *tbl, const int *key, i
     const size_t total = (size_t)N * De;
     k_ngram_gather<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(buf, tbl, key, N, De, nk);
     QLMB_LAUNCH_CHECK("k_ngram_gather");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_nggate_fwd(void *h, const void *v, void *k, void *hn, int dtype, float *g, float *rh, float *rk, int N,
+                               int D, void *stream)
+{
+    QLMB_REQUIRE(h && v && k && hn && g && rh && rk && dtype_ok(dtype), "qlmb_nggate_fwd: bad argument");
+    QLMB_REQUIRE(D > 0 && D % 4 == 0, "qlmb_nggate_fwd: D %d must be a multiple of 4", D);
+    if (N <= 0) return QLMB_OK;
+    k_nggate_fwd<<<(N + 7) / 8, 256, 0, as_stream(stream)>>>(h, v, k, hn, dtype, g, rh, rk, N, D);
+    QLMB_LAUNCH_CHECK("k_nggate_fwd");
+    return QLMB_OK;
+}
+
+extern "C" int qlmb_nggate_bwd(void *dy, const void *v, const void *hn, const void *kn, int dtype, const float *g,
+                               const float *rh, const float *rk, void *dv, void *dk, int N, int D, void *stream)
+{
+    QLMB_REQUIRE(dy && v && hn && kn && g && rh && rk && dv && dk && dtype_ok(dtype), "qlmb_nggate_bwd: bad argument");
+    QLMB_REQUIRE(D > 0 && D % 4 == 0, "qlmb_nggate_bwd: D %d must be a multiple of 4", D);
+    if (N <= 0) return QLMB_OK;
+    k_nggate_bwd<<<(N + 7) / 8, 256, 0, as_stream(stream)>>>(dy, v, hn, kn, dtype, g, rh, rk, dv, dk, N, D);
+    QLMB_LAUNCH_CHECK("k_nggate_bwd");
     return QLMB_OK;
 }

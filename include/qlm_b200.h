@@ -136,6 +136,14 @@ int qlmb_ng_step(float *P, const float *Gc, int8_t *d, int8_t *r, const float *s
 int qlmb_ngram_key(int *key, const int *tok, int N, int T, int R, int order, int base, void *stream);
 int qlmb_dec_ngkey(int *key, const int *tokw, const int *pos, int B, int R, int order, int base, void *stream);
 int qlmb_ngram_gather(float *buf, const float *tbl, const int *key, int N, int De, int nk, void *stream);
+/* The table's context gate (k_nggate_f / k_nggate_b, cudalm.cu:3362-3378; ngram_forward 4717-4718, ngram_backward 4725).
+ * Forward, per row of D: g = sigmoid(<rms(h), rms(k)> / sqrt(D)); hn = rms(h); k = rms(k) in place; h += g * v in place;
+ * g, rh = 1/rms(h), rk = 1/rms(k) are kept per row.  Backward: dv = g * dy; dk and the gate's share of dh from the
+ * logit's gradient; dy += that share in place.  h, v, k, hn, dy, dv, dk share one element type (QLMB_F32 / QLMB_BF16). */
+int qlmb_nggate_fwd(void *h, const void *v, void *k, void *hn, int dtype, float *g, float *rh, float *rk, int N, int D,
+                    void *stream);
+int qlmb_nggate_bwd(void *dy, const void *v, const void *hn, const void *kn, int dtype, const float *g, const float *rh,
+                    const float *rk, void *dv, void *dk, int N, int D, void *stream);
 
 /* k_qlm_servo (qlm.cuh:404-441). */
 int qlmb_servo(int8_t *d, int8_t *r, float *s, const qlmb_span *sp, int nspan, int ngrp, int group,

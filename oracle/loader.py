@@ -267,6 +267,19 @@ class Reference:
         self.lib.ref_ngram_gather(_p(tbl), _p(key), _p(buf), C.c_int(N), C.c_int(De), C.c_int(nk))
         return buf
 
+    # ---- the table's context gate (cpu_kern.h:573-589); h, k and dy are updated in place ----
+    def nggate_f(self, h, v, k):
+        N, D = h.shape
+        hn = np.zeros_like(h); g, rh, rk = (np.zeros(N, np.float32) for _ in range(3))
+        self.lib.ref_nggate_f(_p(h), _p(v), _p(k), _p(hn), _p(g), _p(rh), _p(rk), C.c_int(N), C.c_int(D))
+        return hn, g, rh, rk
+
+    def nggate_b(self, dy, v, hn, kn, g, rh, rk):
+        N, D = dy.shape
+        dv, dk = np.zeros_like(dy), np.zeros_like(dy)
+        self.lib.ref_nggate_b(_p(dy), _p(v), _p(hn), _p(kn), _p(g), _p(rh), _p(rk), _p(dv), _p(dk), C.c_int(N), C.c_int(D))
+        return dv, dk
+
     # ---- 4-bit n-gram table update (cpu_kern.h:615-660) ----
     def ng_touched(self, key, De, group, ngrp):
         slot = np.full(ngrp, -1, np.int32); tgi = np.zeros(key.size, np.int32); cidx = np.zeros(key.size, np.int32)

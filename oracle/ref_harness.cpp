@@ -108,6 +108,11 @@ void ref_attn_bwd(const float *Q, const float *K, const float *V, const float *O
 void ref_ngram_key(const int *tok, int *key, int N, int T, int R, int order, int base) { KL(k_ngram_key, 1, 1)(tok, key, N, T, R, order, base); }
 void ref_ngram_gather(const float *tbl, const int *key, float *buf, int N, int De, int nk) { KL(k_ngram_gather, 1, 1)(tbl, key, buf, N, De, nk); }
 
+/* ---- the table's context gate (cpu_kern.h:573-589) ---- */
+void ref_nggate_f(float *h, const float *v, float *k, float *hn, float *g, float *rh, float *rk, int N, int D) { KL(k_nggate_f, N, 128)(h, v, k, hn, g, rh, rk, D); }
+void ref_nggate_b(float *dy, const float *v, const float *hn, const float *kn, const float *g, const float *rh, const float *rk, float *dv, float *dk, int N, int D)
+{ KL(k_nggate_b, N, 128)(dy, v, hn, kn, g, rh, rk, dv, dk, D); }
+
 /* ---- 4-bit n-gram table update (cpu_kern.h:615-660; ng_build_touched / ng_tbl_step, cudalm.cu:4673-4745) ---- */
 int ref_ng_touched(const int *key, int *slot /* ngrp ints, all -1 */, int *tgi, int *cidx, int N, int De, int grp)
 {

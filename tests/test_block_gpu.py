@@ -155,3 +155,34 @@ def test_ngram_keys_and_gather(cuda, ref):
     check(L.qlmb_dec_ngkey(ptr(dk), ptr(d_tokw), ptr(d_pos), B, R, 3, R, stream_ptr()))
     assert (dk.cpu().numpy() == keys[1].reshape(B, T)[:, p]).all()
     q.check(q.lib().qlmb_check_device(None))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ngram_context_gate(cuda, ref, dtype):
+    """k_nggate_f / k_nggate_b (cudalm.cu:3362-3378) against the reference's CPU kernels.  fp32: 1e-5 relative (the
+    row sums are taken in another order); bf16 storage: 1e-2, inputs rounded to bf16 on both sides."""
+    from cudalm_c_b200 import block
+    rng = np.random.default_rng(9)
+    N, D = 203, 768
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    rnd = lambda a: torch.from_numpy(a).to(dtype).float().numpy()
+    h, v, k, dy = [rnd(rng.standard_normal((N, D)).astype(np.float32)) for _ in range(4)]
+    k *= 3.0; k = rnd(k)
+    k[:, :64] += h[:, :64]                                   # correlated rows: gates away from 1/2
+    k = rnd(k)
+    d = lambda a: torch.from_numpy(a).to(cuda).to(dtype)
+    dh, dv_, dk_, ddy = d(h), d(v), d(k), d(dy)
+    hn, g, rh, rk = block.nggate_fwd(dh, dv_, dk_)
+    h2, k2 = h.copy(), k.copy()
+    hn_r, g_r, rh_r, rk_r = ref.nggate_f(h2, v, k2)
+    rel = lambda a, b: float(np.abs(a.float().cpu().numpy() - b).max() / np.abs(b).max())
+    assert g_r.std() > 0.02
+    assert rel(g, g_r) < tol and rel(rh, rh_r) < 1e-5 and rel(rk, rk_r) < 1e-5
+    assert rel(hn, hn_r) < tol and rel(dk_, k2) < tol and rel(dh, h2) < tol
+    # backward from the reference's own forward state, so that both sides start from the same numbers
+    st = [rnd(a) for a in (hn_r, k2)]
+    gd, rhd, rkd = [torch.from_numpy(a).to(cuda) for a in (g_r, rh_r, rk_r)]
+    dvo, dko = block.nggate_bwd(ddy, dv_, d(st[0]), d(st[1]), gd, rhd, rkd)
+    dy2 = dy.copy()
+    dv_r, dk_r = ref.nggate_b(dy2, v, st[0], st[1], g_r, rh_r, rk_r)
+    assert rel(dvo, dv_r) < tol and rel(dko, dk_r) < 5 * tol and rel(ddy, dy2) < tol
