@@ -37,7 +37,7 @@ template <int BT>
 __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, const void *X, int dtype, const uint8_t *codes,
                                                  const float *scales, int B, int K, int N, int kslice,
                                                  const int *row_expert = nullptr, size_t e_codes = 0, size_t e_scales = 0,
-                                                 int ntok = 1)
+                                                 int ntok = 1, const float *gamma = nullptr)
 {
     // routed form: blockIdx.z is an output row, it reads activation row z % ntok and one matrix of a stack; B must be 1 then
     size_t xrow = 0, prow = 0;
@@ -58,11 +58,28 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
     const bool live = n0 < N;
     const uint8_t *cp = codes + (size_t)n0 / 2;
     const float *sp = scales + n0 / 128;
+    // gamma (routed form, one activation row per block): the row is normalised on the way in, x * rinv * gamma rounded
+    // to bf16 as the separate norm kernel stores it (e_rmsf in front of the q, k, v projections, cudalm.cu:7176)
+    float rinv = 1.0f;
+    if (gamma) {
+        float ss = 0.0f;
+        for (int k = threadIdx.x; k < K; k += 256) { const float x = ld_x(X, dtype, xrow * K + k); ss += x * x; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[0][warp] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int w8 = 0; w8 < 8; w8++) tot += red[0][w8];
+        rinv = 1.0f / sqrtf(tot / (float)K + 1e-5f);
+    }
     for (int b0 = 0; b0 < B; b0 += BT) {
         __syncthreads();
         for (int i = threadIdx.x; i < BT * kslice; i += 256) {
             const int b = b0 + i / kslice, k = k0 + i % kslice;
-            xs[i] = (b < B && k < k1) ? ld_x(X, dtype, ((size_t)b + xrow) * K + k) : 0.0f;
+            float x = (b < B && k < k1) ? ld_x(X, dtype, ((size_t)b + xrow) * K + k) : 0.0f;
+            if (gamma && k < k1) x = __bfloat162float(__float2bfloat16_rn(x * rinv * gamma[k]));
+            xs[i] = x;
         }
         if (!PAR) for (int i = threadIdx.x; i < BT * 256; i += 256) red[i / 256][i % 256] = 0.0f;
         __syncthreads();
@@ -218,6 +235,44 @@ __global__ void __launch_bounds__(256) k_gemv_finish(void *Y, int dtype, const f
     else ((float *)Y)[i] = s;
 }
 
+// The finish of a decode step's output projection (dec_step, cudalm.cu:7188-7190: wo, the residual add and the norm in
+// front of the FFN) in one launch, one block per slot: F[b,:] = bf16(slice sums) + res[b,:] (rounded to bf16 as the
+// separate kernels do), Fn[b,:] = F * rinv * gamma with rinv = 1/sqrt(mean(F^2) + 1e-5).  N <= 2048.
+__global__ void __launch_bounds__(256) k_gemv_finish_res_norm(bf16 *F, bf16 *Fn, const float *part, int nslice, int B, int N,
+                                                              const bf16 *res, const float *gamma)
+{
+    __shared__ float red[8];
+    const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float v[8], ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+        const int n = threadIdx.x + 256 * c;
+        v[c] = 0.0f;
+        if (n < N) {
+            float y = 0.0f;
+            for (int k = 0; k < nslice; k++) y += part[((size_t)k * B + b) * N + n];
+            y = __bfloat162float(__float2bfloat16_rn(y));
+            const bf16 f = __float2bfloat16_rn(y + __bfloat162float(res[(size_t)b * N + n]));
+            F[(size_t)b * N + n] = f;
+            v[c] = __bfloat162float(f);
+            ss += v[c] * v[c];
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot += red[w];
+    const float rinv = 1.0f / sqrtf(tot / (float)N + 1e-5f);
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+        const int n = threadIdx.x + 256 * c;
+        if (n < N) Fn[(size_t)b * N + n] = __float2bfloat16_rn(v[c] * rinv * gamma[n]);
+    }
+}
+
 // act[r,f] = silu(g) * u with g, u the K-slice sums (ascending) of the gate and up partials
 __global__ void __launch_bounds__(256) k_gemv_finish_swiglu(bf16 *act, const float *pg, const float *pu, int nslice, size_t RN)
 {
@@ -288,8 +343,11 @@ int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, con
 
 using namespace qlmb;
 
-extern "C" int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, const float *scales, int layout,
-                                int B, int K, int N, int dtype, void *stream)
+// the fused finish of the output projection: F (written through Y), Fn, the residual and the norm's gain
+struct FinishResNorm { void *Fn; const void *res; const float *gamma; };
+
+static int gemv_decode_impl(void *Y, const void *X, const int8_t *codes, const float *scales, int layout, int B, int K, int N,
+                            int dtype, void *stream, const FinishResNorm *fr)
 {
     QLMB_REQUIRE(layout == QLMB_KN || layout == QLMB_NK, "qlmb_gemv_decode: layout %d", layout);
     QLMB_REQUIRE(dtype == QLMB_F32 || dtype == QLMB_BF16, "qlmb_gemv_decode: dtype %d", dtype);
@@ -303,7 +361,7 @@ extern "C" int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, con
     cudaStream_t st = as_stream(stream);
     // more than 4 live slots with bf16 activations: the tensor-core engine streams the weights
     // faster than fp32 FMAs can consume them (fp32 activations keep the exact fp32 path)
-    if (B > 4 && dtype == QLMB_BF16 && (K % 64) == 0)
+    if (!fr && B > 4 && dtype == QLMB_BF16 && (K % 64) == 0)
         return qlmb_linear_fwd(Y, X, codes, scales, layout, B, K, N, nullptr, dtype, stream);
     const int bt = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
     // K slices: enough blocks to fill the device once, at least 64 rows each,
@@ -332,15 +390,22 @@ extern "C" int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, con
     if (layout == QLMB_KN) GV_LAUNCH(k_gemv_kn);
     else GV_LAUNCH(k_gemv_nk);
 #undef GV_LAUNCH
-    k_gemv_finish<<<(unsigned)(((size_t)B * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)B * N);
+    if (fr) k_gemv_finish_res_norm<<<B, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, part, nslice, B, N, (const bf16 *)fr->res, fr->gamma);
+    else k_gemv_finish<<<(unsigned)(((size_t)B * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)B * N);
     QLMB_LAUNCH_CHECK("qlmb_gemv_decode");
     return QLMB_OK;
 }
 
+extern "C" int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, const float *scales, int layout,
+                                int B, int K, int N, int dtype, void *stream)
+{
+    return gemv_decode_impl(Y, X, codes, scales, layout, B, K, N, dtype, stream, nullptr);
+}
+
 // Y[m*B + b, :] = X[b, :] deq(W_m) for nmat equally shaped matrices stored one after the other (codes W_m[K][N]):
 // the q, k and v projections of a decode step in one launch pair (cudalm.cu:7178-7180) when KD = D.
-extern "C" int qlmb_gemv_decode_stack(void *Y, const void *X, const int8_t *codes, const float *scales, int nmat, int B,
-                                      int K, int N, int dtype, void *stream)
+static int gemv_stack_impl(void *Y, const void *X, const int8_t *codes, const float *scales, int nmat, int B, int K, int N,
+                           int dtype, void *stream, const FinishResNorm *fr, const float *gamma = nullptr)
 {
     QLMB_REQUIRE(Y && X && codes && scales, "qlmb_gemv_decode_stack: NULL argument");
     QLMB_REQUIRE(dtype == QLMB_F32 || dtype == QLMB_BF16, "qlmb_gemv_decode_stack: dtype %d", dtype);
@@ -358,8 +423,33 @@ extern "C" int qlmb_gemv_decode_stack(void *Y, const void *X, const int8_t *code
     if (rc) return rc;
     float *part = (float *)ws;
     k_gemv_kn<1><<<dim3(nblk, nslice, R), 256, (size_t)kslice * sizeof(float), st>>>(
-        part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B);
-    k_gemv_finish<<<(unsigned)(((size_t)R * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)R * N);
+        part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
+    if (fr) k_gemv_finish_res_norm<<<R, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, part, nslice, R, N, (const bf16 *)fr->res, fr->gamma);
+    else k_gemv_finish<<<(unsigned)(((size_t)R * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)R * N);
     QLMB_LAUNCH_CHECK("qlmb_gemv_decode_stack");
     return QLMB_OK;
+}
+
+extern "C" int qlmb_gemv_decode_stack(void *Y, const void *X, const int8_t *codes, const float *scales, int nmat, int B,
+                                      int K, int N, int dtype, void *stream)
+{
+    return gemv_stack_impl(Y, X, codes, scales, nmat, B, K, N, dtype, stream, nullptr);
+}
+
+extern "C" int qlmb_gemv_decode_norm_stack(void *Y, const void *X, const float *gamma, const int8_t *codes, const float *scales,
+                                          int nmat, int B, int K, int N, int dtype, void *stream)
+{
+    QLMB_REQUIRE(gamma, "qlmb_gemv_decode_norm_stack: NULL argument");
+    return gemv_stack_impl(Y, X, codes, scales, nmat, B, K, N, dtype, stream, nullptr, gamma);
+}
+
+extern "C" int qlmb_gemv_decode_res_norm(void *F, void *Fn, const void *X, const int8_t *codes, const float *scales,
+                                         const void *res, const float *gamma, int B, int K, int N, void *stream)
+{
+    QLMB_REQUIRE(F && Fn && X && codes && scales && res && gamma, "qlmb_gemv_decode_res_norm: NULL argument");
+    QLMB_REQUIRE(B > 0 && B <= 256 && K > 0 && N > 0 && N <= 2048 && (K % 128) == 0 && (N % 128) == 0,
+                 "qlmb_gemv_decode_res_norm: B=%d K=%d N=%d", B, K, N);
+    const FinishResNorm fr = {Fn, res, gamma};
+    if (B <= 4) return gemv_decode_impl(F, X, codes, scales, QLMB_KN, B, K, N, QLMB_BF16, stream, &fr);
+    return gemv_stack_impl(F, X, codes, scales, 1, B, K, N, QLMB_BF16, stream, &fr);
 }

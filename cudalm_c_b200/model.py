@@ -359,14 +359,16 @@ class Decoder:
         x = block.embed(m.emb, self.tok, dtype=torch.bfloat16)
         for l, ly in enumerate(m.layers):
             w, f = ly["w"], m.fl[l]
-            a_norm, _ = block.rmsnorm_fwd(x, f["an1"])
             if c.KD == c.D and 3 * B <= 256:
-                # wq, wk, wv are consecutive spans of one shape: one GEMV launch pair for the three, one rotation for q and k
+                # wq, wk, wv are consecutive spans of one shape: one GEMV launch pair for the three (the norm in front of
+                # them is applied while the row is staged), one rotation for q and k
                 qkv = torch.empty(3 * B, c.D, dtype=torch.bfloat16, device=m.dev)
-                check(L_.qlmb_gemv_decode_stack(ptr(qkv), ptr(a_norm), ptr(w["wq"][0]), ptr(w["wq"][1]), 3, B, c.D, c.D, 1, stream_ptr()))
+                check(L_.qlmb_gemv_decode_norm_stack(ptr(qkv), ptr(x), ptr(f["an1"]), ptr(w["wq"][0]), ptr(w["wq"][1]), 3, B, c.D,
+                                                     c.D, 1, stream_ptr()))
                 qh, kh, vh = qkv[:B], qkv[B:2 * B], qkv[2 * B:]
                 check(L_.qlmb_dec_rope(ptr(qkv), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos2), 2 * B, c.H, c.hd, stream_ptr()))
             else:
+                a_norm, _ = block.rmsnorm_fwd(x, f["an1"])
                 qh = linear.gemv_decode(a_norm, *w["wq"], KN, c.D)
                 kh = linear.gemv_decode(a_norm, *w["wk"], KN, c.KD)
                 vh = linear.gemv_decode(a_norm, *w["wv"], KN, c.KD)
@@ -376,13 +378,16 @@ class Decoder:
             att = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
             check(L_.qlmb_dec_attn(ptr(att), ptr(qh), ptr(self.K[l]), ptr(self.V[l]), ptr(self.pos), 0, B, self.Tm, c.H, c.KV,
                                    c.hd, stream_ptr()))
-            if 4 < B <= 256:
+            if B <= 256 and c.D <= 2048:
+                # wo, the residual add and the FFN's input norm: one GEMV launch pair
                 f_in = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
-                check(L_.qlmb_gemv_decode_stack(ptr(f_in), ptr(att), ptr(w["wo"][0]), ptr(w["wo"][1]), 1, B, c.D, c.D, 1, stream_ptr()))
+                f_norm = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
+                check(L_.qlmb_gemv_decode_res_norm(ptr(f_in), ptr(f_norm), ptr(att), ptr(w["wo"][0]), ptr(w["wo"][1]), ptr(x),
+                                                   ptr(f["an2"]), B, c.D, c.D, stream_ptr()))
             else:
                 f_in = linear.gemv_decode(att, *w["wo"], KN, c.D)
-            f_in += x
-            f_norm, _ = block.rmsnorm_fwd(f_in, f["an2"])
+                f_in += x
+                f_norm, _ = block.rmsnorm_fwd(f_in, f["an2"])
             x = self.moes[l].decode(f_in, f_norm)
         fn, _ = block.rmsnorm_fwd(x, m.nf)
         self.logits = block.gemm_nt(fn, self.emb_bf, torch.float32, out=self.logits)

@@ -431,6 +431,16 @@ int qlmb_softmax_ce(const void *logits, int lg_dtype, const int *tgt, float *los
  * matrices and few rows; nmat = 1 is a plain GEMV without row batching. */
 int qlmb_gemv_decode_stack(void *Y, const void *X, const int8_t *codes, const float *scales, int nmat, int B, int K,
                            int N, int dtype, void *stream);
+/* qlmb_gemv_decode_stack on the normalised rows: X is multiplied by rinv * gamma (rinv = 1/sqrt(mean(x^2) + 1e-5)) and
+ * rounded to bf16 while it is staged, so the norm in front of the q, k, v projections (e_rmsf, cudalm.cu:7176) needs no
+ * launch and no buffer of its own. */
+int qlmb_gemv_decode_norm_stack(void *Y, const void *X, const float *gamma, const int8_t *codes, const float *scales, int nmat,
+                                int B, int K, int N, int dtype, void *stream);
+/* The output projection of a decode step with what follows it (dec_step, cudalm.cu:7188-7190: g_ab on wo, the
+ * residual add, the norm in front of the FFN) in one launch pair: F = bf16(X deq(W)) + res, Fn = F * rinv * gamma with
+ * rinv = 1/sqrt(mean(F^2) + 1e-5).  bf16 activations, codes W[K][N], B <= 256 slots, N <= 2048. */
+int qlmb_gemv_decode_res_norm(void *F, void *Fn, const void *X, const int8_t *codes, const float *scales, const void *res,
+                              const float *gamma, int B, int K, int N, void *stream);
 
 /* ---- decoder: one new token per live slot (dec_step, cudalm.cu:7166-7212) ----
  * The K/V cache of a layer is bf16 [B, Tm, KV*hd]; pos[b] (device) is the position of slot b's new token.

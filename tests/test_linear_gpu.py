@@ -170,3 +170,51 @@ def test_gemv_rejects_more_than_64_slots(cuda):
     Q, W = quantise(cuda, 128, 128, 9)
     with pytest.raises(q.QlmbError):
         linear.gemv_decode(torch.zeros(65, 128, device=cuda), Q.d, Q.s, KN, 128)
+
+
+@pytest.mark.parametrize("B", [1, 3, 8, 64])
+def test_gemv_decode_res_norm_equals_the_separate_kernels(cuda, B):
+    """wo + residual + norm of a decode step in one launch pair (dec_step, cudalm.cu:7188-7190): F is the same bf16
+    values as the GEMV followed by the bf16 add; Fn agrees with the separate norm kernel to one bf16 rounding."""
+    from cudalm_c_b200 import block, linear
+    from cudalm_c_b200._lib import KN, check, lib, ptr, stream_ptr
+    for K, N in ((768, 768), (1536, 2048)):
+        Q, W = quantise(cuda, K, N, 12)
+        X = torch.randn(B, K, device=cuda).to(torch.bfloat16)
+        res = torch.randn(B, N, device=cuda).to(torch.bfloat16)
+        gamma = 1.0 + 0.1 * torch.randn(N, device=cuda)
+        F = torch.empty(B, N, dtype=torch.bfloat16, device=cuda); Fn = torch.empty_like(F)
+        check(lib().qlmb_gemv_decode_res_norm(ptr(F), ptr(Fn), ptr(X), ptr(Q.d), ptr(Q.s), ptr(res), ptr(gamma), B, K, N,
+                                              stream_ptr()))
+        if B <= 4:
+            Y = linear.gemv_decode(X, Q.d, Q.s, KN, N)
+        else:
+            Y = torch.empty(B, N, dtype=torch.bfloat16, device=cuda)
+            check(lib().qlmb_gemv_decode_stack(ptr(Y), ptr(X), ptr(Q.d), ptr(Q.s), 1, B, K, N, 1, stream_ptr()))
+        Y += res
+        assert torch.equal(F, Y)
+        Yn, _ = block.rmsnorm_fwd(Y, gamma)
+        assert rel(Fn, Yn) < 8e-3
+        assert (Fn.float() - Yn.float()).abs().max() <= 2.0 ** -7 * Yn.float().abs().max()
+        assert rel(F, X.float() @ W + res.float()) < 8e-3
+
+
+@pytest.mark.parametrize("B", [1, 8, 64])
+def test_gemv_decode_norm_stack(cuda, B):
+    """The norm in front of the q, k, v projections applied while the rows are staged (e_rmsf + three g_ab,
+    cudalm.cu:7176-7180): the same numbers as the norm kernel followed by the stacked GEMV, up to one bf16 rounding
+    of a normalised input where the two row sums differ in their last bit."""
+    from cudalm_c_b200 import block
+    from cudalm_c_b200._lib import check, lib, ptr, stream_ptr
+    K = N = 768
+    Q, W = quantise(cuda, 3 * K, N, 14)                       # three [K, N] matrices one after the other
+    X = torch.randn(B, K, device=cuda).to(torch.bfloat16)
+    gamma = 1.0 + 0.1 * torch.randn(K, device=cuda)
+    Y = torch.empty(3 * B, N, dtype=torch.bfloat16, device=cuda); Y2 = torch.empty_like(Y)
+    check(lib().qlmb_gemv_decode_norm_stack(ptr(Y), ptr(X), ptr(gamma), ptr(Q.d), ptr(Q.s), 3, B, K, N, 1, stream_ptr()))
+    Xn, _ = block.rmsnorm_fwd(X, gamma)
+    check(lib().qlmb_gemv_decode_stack(ptr(Y2), ptr(Xn), ptr(Q.d), ptr(Q.s), 3, B, K, N, 1, stream_ptr()))
+    assert rel(Y, Y2) < 2e-3
+    assert (Y == Y2).float().mean() > 0.99
+    ref = torch.cat([Xn.float() @ W[m * K:(m + 1) * K] for m in range(3)])
+    assert rel(Y, ref) < 8e-3
