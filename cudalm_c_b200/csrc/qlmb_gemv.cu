@@ -273,6 +273,37 @@ __global__ void __launch_bounds__(256) k_gemv_finish_res_norm(bf16 *F, bf16 *Fn,
     }
 }
 
+// The finish of a decode step's stacked q, k, v projections with what follows them (dec_step, cudalm.cu:7181-7183):
+// rows [3][B][N] of slice sums -> bf16; the q and k rows are rotated by the angle of their slot's position
+// (k_dec_rope: pairs (i, i + hd/2) of every head), the k and v rows go to position pos[b] of the slot's cache
+// (k_dec_kv).  One thread per pair; Y receives all three rows as the separate kernels would leave them.
+__global__ void __launch_bounds__(256) k_gemv_finish_qkv(bf16 *Y, bf16 *Kc, bf16 *Vc, const float *part, int nslice, int B, int N,
+                                                         int hd, const float *cosb, const float *sinb, const int *pos, int Tm)
+{
+    const int hf = hd / 2, nh = N / hd;
+    const size_t g = (size_t)blockIdx.x * 256 + threadIdx.x, RN = (size_t)3 * B * N;
+    if (g >= RN / 2) return;
+    const int i = (int)(g % hf);
+    const size_t r = g / hf;
+    const int row = (int)(r / nh), h = (int)(r % nh), m = row / B, b = row % B, t = pos[b];
+    const size_t o = (size_t)row * N + (size_t)h * hd + i;
+    float x = 0.0f, y = 0.0f;
+    for (int k = 0; k < nslice; k++) { x += part[(size_t)k * RN + o]; y += part[(size_t)k * RN + o + hf]; }
+    x = __bfloat162float(__float2bfloat16_rn(x)); y = __bfloat162float(__float2bfloat16_rn(y));
+    if (m < 2) {
+        const float c = cosb[(size_t)t * hf + i], sn = sinb[(size_t)t * hf + i];
+        const float xr = x * c - y * sn, yr = y * c + x * sn;
+        x = xr; y = yr;
+    }
+    const bf16 xo = __float2bfloat16_rn(x), yo = __float2bfloat16_rn(y);
+    Y[o] = xo; Y[o + hf] = yo;
+    if (m >= 1) {
+        bf16 *cache = m == 1 ? Kc : Vc;
+        const size_t co = ((size_t)b * Tm + t) * N + (size_t)h * hd + i;
+        cache[co] = xo; cache[co + hf] = yo;
+    }
+}
+
 // act[r,f] = silu(g) * u with g, u the K-slice sums (ascending) of the gate and up partials
 __global__ void __launch_bounds__(256) k_gemv_finish_swiglu(bf16 *act, const float *pg, const float *pu, int nslice, size_t RN)
 {
@@ -404,8 +435,11 @@ extern "C" int qlmb_gemv_decode(void *Y, const void *X, const int8_t *codes, con
 
 // Y[m*B + b, :] = X[b, :] deq(W_m) for nmat equally shaped matrices stored one after the other (codes W_m[K][N]):
 // the q, k and v projections of a decode step in one launch pair (cudalm.cu:7178-7180) when KD = D.
+// fq: the q, k, v finish (rotation tables, positions, the slot caches)
+struct FinishQkv { void *Kc; void *Vc; const float *cosb; const float *sinb; const int *pos; int hd; int Tm; };
 static int gemv_stack_impl(void *Y, const void *X, const int8_t *codes, const float *scales, int nmat, int B, int K, int N,
-                           int dtype, void *stream, const FinishResNorm *fr, const float *gamma = nullptr)
+                           int dtype, void *stream, const FinishResNorm *fr, const float *gamma = nullptr,
+                           const FinishQkv *fq = nullptr)
 {
     QLMB_REQUIRE(Y && X && codes && scales, "qlmb_gemv_decode_stack: NULL argument");
     QLMB_REQUIRE(dtype == QLMB_F32 || dtype == QLMB_BF16, "qlmb_gemv_decode_stack: dtype %d", dtype);
@@ -425,6 +459,8 @@ static int gemv_stack_impl(void *Y, const void *X, const int8_t *codes, const fl
     k_gemv_kn<1><<<dim3(nblk, nslice, R), 256, (size_t)kslice * sizeof(float), st>>>(
         part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
     if (fr) k_gemv_finish_res_norm<<<R, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, part, nslice, R, N, (const bf16 *)fr->res, fr->gamma);
+    else if (fq) k_gemv_finish_qkv<<<(unsigned)(((size_t)R * N / 2 + 255) / 256), 256, 0, st>>>(
+        (bf16 *)Y, (bf16 *)fq->Kc, (bf16 *)fq->Vc, part, nslice, B, N, fq->hd, fq->cosb, fq->sinb, fq->pos, fq->Tm);
     else k_gemv_finish<<<(unsigned)(((size_t)R * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)R * N);
     QLMB_LAUNCH_CHECK("qlmb_gemv_decode_stack");
     return QLMB_OK;
@@ -441,6 +477,16 @@ extern "C" int qlmb_gemv_decode_norm_stack(void *Y, const void *X, const float *
 {
     QLMB_REQUIRE(gamma, "qlmb_gemv_decode_norm_stack: NULL argument");
     return gemv_stack_impl(Y, X, codes, scales, nmat, B, K, N, dtype, stream, nullptr, gamma);
+}
+
+extern "C" int qlmb_dec_qkv(void *Y, void *Kc, void *Vc, const void *X, const float *gamma, const int8_t *codes,
+                            const float *scales, const float *cosb, const float *sinb, const int *pos, int B, int D, int hd,
+                            int Tm, void *stream)
+{
+    QLMB_REQUIRE(Y && Kc && Vc && X && gamma && cosb && sinb && pos, "qlmb_dec_qkv: NULL argument");
+    QLMB_REQUIRE(hd > 0 && hd % 2 == 0 && D % hd == 0 && Tm > 0, "qlmb_dec_qkv: D=%d hd=%d Tm=%d", D, hd, Tm);
+    const FinishQkv fq = {Kc, Vc, cosb, sinb, pos, hd, Tm};
+    return gemv_stack_impl(Y, X, codes, scales, 3, B, D, D, QLMB_BF16, stream, nullptr, gamma, &fq);
 }
 
 extern "C" int qlmb_gemv_decode_res_norm(void *F, void *Fn, const void *X, const int8_t *codes, const float *scales,

@@ -59,6 +59,9 @@ struct GemmProblem;   // see qlmb_gemm.cuh
 
 // router logits of a few rows (decode): deterministic, not the tiled kernel's summation order
 int router_logits_small(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E, cudaStream_t st);
+// the same logits and the selection in one launch (qlmb_route.cu); larger shapes fall back to the two kernels
+int router_small(float *rt, const void *X, int x_dtype, const float *Wr, float *rprobs, int *assign, float *gate, int N, int D,
+                 int E, int K, const float *bias, int bs, cudaStream_t st);
 // experts of a decode step with at most 64 routed rows (qlmb_gemv.cu): routed GEMVs over the chosen experts' codes
 int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, const void *f_norm, const int *assign,
                        const float *gate, cudaStream_t st);

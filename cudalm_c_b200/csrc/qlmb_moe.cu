@@ -201,11 +201,14 @@ static int moe_forward_impl(const qlmb_moe_layer *L, void *arena, void *out, con
     const int R = (int)a.rows_cap;
 
     // router: logits, softmax top-k (cudalm.cu:4158, 4174)
-    { ProfScope ps("router_logits", st);
-      rc = small_router ? router_logits_small(a.rt, f_norm, L->dtype, L->wr, N, D, E, st) : router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st);
-      if (rc) return rc; }
-    { ProfScope ps("router_topk", st);
-    if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc; }
+    if (small_router) {
+        if ((rc = router_small(a.rt, f_norm, L->dtype, L->wr, a.rprobs, a.assign, a.gate, N, D, E, K, L->bias, L->bias_stride, st))) return rc;
+    } else {
+        { ProfScope ps("router_logits", st);
+        if ((rc = router_logits(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc; }
+        { ProfScope ps("router_topk", st);
+        if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc; }
+    }
     // expert grouping, padded to 128-row tiles (cudalm.cu:4189)
     { ProfScope ps("perm_build", st);
     if ((rc = perm_build(a.assign, N, E, K, 1, 128, a.perm, a.inv, a.off, a.counts, a.bad, a.tile_info, a.ntiles, a.chunk, st))) return rc; }
@@ -235,8 +238,7 @@ extern "C" int qlmb_moe_decode(const qlmb_moe_layer *L, void *arena, void *out, 
     const int N = L->N, D = L->D, F = L->F, E = L->E, K = L->K;
     Arena a = carve(arena, N, D, F, E, K);
     cudaStream_t st = as_stream(stream);
-    if ((rc = router_logits_small(a.rt, f_norm, L->dtype, L->wr, N, D, E, st))) return rc;
-    if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc;
+    if ((rc = router_small(a.rt, f_norm, L->dtype, L->wr, a.rprobs, a.assign, a.gate, N, D, E, K, L->bias, L->bias_stride, st))) return rc;
     return moe_decode_experts(L, out, f_in, f_norm, a.assign, a.gate, st);
 }
 

@@ -64,14 +64,11 @@ __global__ void __launch_bounds__(128) k_router_topk(const float *rt, float *rpr
 // lane adds the 32 shuffled terms sequentially) and the K selection rounds are
 // warp arg-max reductions with the lowest index winning ties, so the outputs are
 // bit-identical to the thread-per-token form above.
-__global__ void __launch_bounds__(256) k_router_topk_warp(const float *rt, float *rprobs, int *assign,
-                                                          float *gate, int N, int E, int K,
-                                                          const float *bias, int bs)
+// the softmax and the K selection rounds of token n by one warp; lg = the logit of expert `lane` (0 beyond E)
+__device__ __forceinline__ void router_topk_row(float lg, int n, int lane, float *rprobs, int *assign, float *gate, int N,
+                                                int E, int K, const float *bias, int bs)
 {
-    int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (n >= N) return;
     const bool live = lane < E;
-    float lg = live ? rt[(size_t)n * E + lane] : 0.0f;
     float top = (live && lg > -1e30f) ? lg : -1e30f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
@@ -99,6 +96,46 @@ __global__ void __launch_bounds__(256) k_router_topk_warp(const float *rt, float
         if (lane == 0) { assign[(size_t)k * N + n] = pick; gate[(size_t)k * N + n] = g; }
         taken = taken || (lane == pick);
     }
+}
+__global__ void __launch_bounds__(256) k_router_topk_warp(const float *rt, float *rprobs, int *assign,
+                                                          float *gate, int N, int E, int K,
+                                                          const float *bias, int bs)
+{
+    int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    router_topk_row(lane < E ? rt[(size_t)n * E + lane] : 0.0f, n, lane, rprobs, assign, gate, N, E, K, bias, bs);
+}
+
+// A decode step's few rows: logits and selection in one launch, one block per token.  The logits are those of
+// k_router_logits_small (lane = expert, eight warps each sum one eighth of the features in ascending order with fused
+// multiply-adds, the eight partial sums added in warp order); warp 0 then runs the selection above on them.
+__global__ void __launch_bounds__(256) k_router_small(float *rt, const void *X, int x_dtype, const float *Wr, float *rprobs,
+                                                      int *assign, float *gate, int N, int D, int E, int K,
+                                                      const float *bias, int bs)
+{
+    extern __shared__ float rs_x[];                      // D activations
+    __shared__ float part[8][32];
+    const int n = blockIdx.x, warp = threadIdx.x >> 5, e = threadIdx.x & 31;
+    for (int j = threadIdx.x; j < D; j += 256)
+        rs_x[j] = x_dtype == QLMB_BF16 ? __bfloat162float(((const bf16 *)X)[(size_t)n * D + j]) : ((const float *)X)[(size_t)n * D + j];
+    __syncthreads();
+    const int per = (D + 7) / 8, j0 = warp * per, j1 = j0 + per < D ? j0 + per : D;
+    float acc = 0.0f;
+    if (e < E) {
+#pragma unroll 8
+        for (int j = j0; j < j1; j++) acc = __fmaf_rn(rs_x[j], __ldg(Wr + (size_t)j * E + e), acc);
+    }
+    part[warp][e] = acc;
+    __syncthreads();
+    if (warp != 0) return;
+    float lg = 0.0f;
+    if (e < E) {
+        lg = part[0][e];
+#pragma unroll
+        for (int w = 1; w < 8; w++) lg += part[w][e];
+        rt[(size_t)n * E + e] = lg;
+    }
+    router_topk_row(lg, n, e, rprobs, assign, gate, N, E, K, bias, bs);
 }
 
 // ------------------------------------------------------------- permutation
@@ -254,6 +291,18 @@ int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N,
     if (E <= 32) k_router_topk_warp<<<(N + 7) / 8, 256, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
     else k_router_topk<<<(N + 127) / 128, 128, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
     QLMB_LAUNCH_CHECK("k_router_topk");
+    return QLMB_OK;
+}
+
+int router_small(float *rt, const void *X, int x_dtype, const float *Wr, float *rprobs, int *assign, float *gate, int N, int D,
+                 int E, int K, const float *bias, int bs, cudaStream_t st)
+{
+    if (N > 64 || E > 32 || D > 8192) {
+        int rc = router_logits_small(rt, X, x_dtype, Wr, N, D, E, st);
+        return rc ? rc : router_topk(rt, rprobs, assign, gate, N, E, K, bias, bs, st);
+    }
+    k_router_small<<<N, 256, (size_t)D * sizeof(float), st>>>(rt, X, x_dtype, Wr, rprobs, assign, gate, N, D, E, K, bias, bs);
+    QLMB_LAUNCH_CHECK("k_router_small");
     return QLMB_OK;
 }
 

@@ -360,13 +360,12 @@ class Decoder:
         for l, ly in enumerate(m.layers):
             w, f = ly["w"], m.fl[l]
             if c.KD == c.D and 3 * B <= 256:
-                # wq, wk, wv are consecutive spans of one shape: one GEMV launch pair for the three (the norm in front of
-                # them is applied while the row is staged), one rotation for q and k
+                # wq, wk, wv are consecutive spans of one shape: one GEMV launch pair for the three; the norm in front of
+                # them is applied while the row is staged, the finish rotates q and k and appends k, v to the caches
                 qkv = torch.empty(3 * B, c.D, dtype=torch.bfloat16, device=m.dev)
-                check(L_.qlmb_gemv_decode_norm_stack(ptr(qkv), ptr(x), ptr(f["an1"]), ptr(w["wq"][0]), ptr(w["wq"][1]), 3, B, c.D,
-                                                     c.D, 1, stream_ptr()))
-                qh, kh, vh = qkv[:B], qkv[B:2 * B], qkv[2 * B:]
-                check(L_.qlmb_dec_rope(ptr(qkv), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos2), 2 * B, c.H, c.hd, stream_ptr()))
+                check(L_.qlmb_dec_qkv(ptr(qkv), ptr(self.K[l]), ptr(self.V[l]), ptr(x), ptr(f["an1"]), ptr(w["wq"][0]),
+                                      ptr(w["wq"][1]), ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.D, c.hd, self.Tm, stream_ptr()))
+                qh = qkv[:B]
             else:
                 a_norm, _ = block.rmsnorm_fwd(x, f["an1"])
                 qh = linear.gemv_decode(a_norm, *w["wq"], KN, c.D)
@@ -374,7 +373,7 @@ class Decoder:
                 vh = linear.gemv_decode(a_norm, *w["wv"], KN, c.KD)
                 check(L_.qlmb_dec_rope(ptr(qh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.H, c.hd, stream_ptr()))
                 check(L_.qlmb_dec_rope(ptr(kh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.KV, c.hd, stream_ptr()))
-            check(L_.qlmb_dec_kv(ptr(self.K[l]), ptr(self.V[l]), ptr(kh), ptr(vh), ptr(self.pos), B, self.Tm, c.KD, stream_ptr()))
+                check(L_.qlmb_dec_kv(ptr(self.K[l]), ptr(self.V[l]), ptr(kh), ptr(vh), ptr(self.pos), B, self.Tm, c.KD, stream_ptr()))
             att = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
             check(L_.qlmb_dec_attn(ptr(att), ptr(qh), ptr(self.K[l]), ptr(self.V[l]), ptr(self.pos), 0, B, self.Tm, c.H, c.KV,
                                    c.hd, stream_ptr()))

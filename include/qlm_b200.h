@@ -436,6 +436,12 @@ int qlmb_gemv_decode_stack(void *Y, const void *X, const int8_t *codes, const fl
  * launch and no buffer of its own. */
 int qlmb_gemv_decode_norm_stack(void *Y, const void *X, const float *gamma, const int8_t *codes, const float *scales, int nmat,
                                 int B, int K, int N, int dtype, void *stream);
+/* The attention input of a decode step in one launch pair (dec_step, cudalm.cu:7176-7183: e_rmsf, g_ab on wq / wk / wv,
+ * k_dec_rope on q and k, k_dec_kv) for models whose key width equals D: Y[3][B][D] = the q, k, v rows (q and k rotated
+ * by the angle of pos[b]), and the k, v rows are stored at position pos[b] of the bf16 caches Kc, Vc [B][Tm][D].
+ * wq, wk, wv are three [D][D] code matrices stored one after the other; bf16 activations; 3 * B <= 256. */
+int qlmb_dec_qkv(void *Y, void *Kc, void *Vc, const void *X, const float *gamma, const int8_t *codes, const float *scales,
+                 const float *cosb, const float *sinb, const int *pos, int B, int D, int hd, int Tm, void *stream);
 /* The output projection of a decode step with what follows it (dec_step, cudalm.cu:7188-7190: g_ab on wo, the
  * residual add, the norm in front of the FFN) in one launch pair: F = bf16(X deq(W)) + res, Fn = F * rinv * gamma with
  * rinv = 1/sqrt(mean(F^2) + 1e-5).  bf16 activations, codes W[K][N], B <= 256 slots, N <= 2048. */

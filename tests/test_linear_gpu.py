@@ -218,3 +218,32 @@ def test_gemv_decode_norm_stack(cuda, B):
     assert (Y == Y2).float().mean() > 0.99
     ref = torch.cat([Xn.float() @ W[m * K:(m + 1) * K] for m in range(3)])
     assert rel(Y, ref) < 8e-3
+
+
+@pytest.mark.parametrize("B", [1, 5, 64])
+def test_dec_qkv_equals_the_separate_kernels(cuda, B):
+    """Norm, q / k / v projections, rotation and cache append of a decode step in one launch pair (dec_step,
+    cudalm.cu:7176-7183) against the chain of separate kernels: same rows, same cache contents, nothing else touched."""
+    from cudalm_c_b200 import block
+    from cudalm_c_b200._lib import check, lib, ptr, stream_ptr
+    D, hd, Tm = 768, 64, 96
+    H = D // hd
+    Q, W = quantise(cuda, 3 * D, D, 21)
+    X = torch.randn(B, D, device=cuda).to(torch.bfloat16)
+    gamma = 1.0 + 0.1 * torch.randn(D, device=cuda)
+    cosb, sinb = block.rope_tables(Tm, hd, device=cuda)
+    pos = torch.randint(0, Tm, (B,), device=cuda, dtype=torch.int32)
+    Kc = torch.full((B, Tm, D), 7.0, dtype=torch.bfloat16, device=cuda); Vc = Kc.clone()
+    Y = torch.empty(3 * B, D, dtype=torch.bfloat16, device=cuda)
+    check(lib().qlmb_dec_qkv(ptr(Y), ptr(Kc), ptr(Vc), ptr(X), ptr(gamma), ptr(Q.d), ptr(Q.s), ptr(cosb), ptr(sinb), ptr(pos),
+                             B, D, hd, Tm, stream_ptr()))
+    Y2 = torch.empty_like(Y)
+    check(lib().qlmb_gemv_decode_norm_stack(ptr(Y2), ptr(X), ptr(gamma), ptr(Q.d), ptr(Q.s), 3, B, D, D, 1, stream_ptr()))
+    pos2 = torch.cat([pos, pos])
+    check(lib().qlmb_dec_rope(ptr(Y2), 1, ptr(cosb), ptr(sinb), ptr(pos2), 2 * B, H, hd, stream_ptr()))
+    Kc2 = torch.full((B, Tm, D), 7.0, dtype=torch.bfloat16, device=cuda); Vc2 = Kc2.clone()
+    check(lib().qlmb_dec_kv(ptr(Kc2), ptr(Vc2), ptr(Y2[B:2 * B]), ptr(Y2[2 * B:]), ptr(pos), B, Tm, D, stream_ptr()))
+    assert rel(Y, Y2) < 1e-3 and (Y == Y2).float().mean() > 0.999
+    assert torch.equal(Kc[torch.arange(B), pos.long()], Y[B:2 * B]) and torch.equal(Vc[torch.arange(B), pos.long()], Y[2 * B:])
+    assert rel(Kc, Kc2) < 1e-3 and rel(Vc, Vc2) < 1e-3
+    assert int((Kc != 7.0).sum()) <= B * D and int((Vc != 7.0).sum()) <= B * D

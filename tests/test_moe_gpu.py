@@ -130,6 +130,31 @@ def test_selection_bias_balances_the_load(cuda):
     assert peak[0] > 2 * int(m) and peak[-1] < peak[0] // 2, peak
 
 
+@pytest.mark.parametrize("N", [1, 8, 32, 48])
+def test_decode_step_matches_the_training_forward(cuda, N):
+    """qlmb_moe_decode (dec_step's moe_forward on a few rows, cudalm.cu:7193): routed GEMVs up to 64 routed rows (one launch
+    for logits + selection), the grouped-GEMM path above; the same experts and the same output as qlmb_moe_forward
+    within bf16 rounding.  A selection bias takes part in the choice."""
+    from cudalm_c_b200 import moe
+    D, F, E, K = 768, 1536, 32, 2
+    L0, qs, wr, _ = build_layer(cuda, N, D, F, E, K, 29)
+    gen = torch.Generator(device=cuda); gen.manual_seed(N)
+    fn = torch.randn(N, D, device=cuda, generator=gen).to(torch.bfloat16)
+    fi = torch.randn(N, D, device=cuda, generator=gen).to(torch.bfloat16)
+    bias = torch.randn(K, E, device=cuda, generator=gen) * 0.01
+    A = moe.MoeLayerState(N, D, F, E, K, qs[0], qs[1], qs[2], wr, bias=bias, bias_stride=E)
+    Bd = moe.MoeLayerState(N, D, F, E, K, qs[0], qs[1], qs[2], wr, bias=bias, bias_stride=E)
+    out_f = A.forward(fi, fn)
+    out_d = Bd.decode(fi, fn)
+    asg_f, asg_d = A.member("assign", (K, N), torch.int32), Bd.member("assign", (K, N), torch.int32)
+    assert rel(Bd.member("rt", (N, E), torch.float32), A.member("rt", (N, E), torch.float32)) < 1e-5
+    same = (asg_f == asg_d).all(0)
+    assert same.float().mean() > 0.9                      # the two logit kernels sum in different orders: near-ties may flip
+    assert torch.equal(Bd.member("gate", (K, N), torch.float32)[:, same] > 0, torch.ones(K, int(same.sum()), dtype=torch.bool, device=cuda))
+    assert rel(out_d[same], out_f[same]) < TOL_F
+    assert torch.equal(out_d, Bd.decode(fi, fn))         # deterministic
+
+
 def test_config2_full_size_properties(cuda):
     """BASELINE config 2 (8192 tokens, 32 experts, top-2, 768/1536): checks that do
     not need an fp32 recomputation of 348 GFLOP -- conservation of rows through the
