@@ -37,16 +37,20 @@ template <int BT>
 __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, const void *X, int dtype, const uint8_t *codes,
                                                  const float *scales, int B, int K, int N, int kslice,
                                                  const int *row_expert = nullptr, size_t e_codes = 0, size_t e_scales = 0,
-                                                 int ntok = 1, const float *gamma = nullptr)
+                                                 int ntok = 1, const float *gamma = nullptr, int dual_rows = 0,
+                                                 const uint8_t *codes2 = nullptr, const float *scales2 = nullptr)
 {
     // routed form: blockIdx.z is an output row, it reads activation row z % ntok and one matrix of a stack; B must be 1 then
     size_t xrow = 0, prow = 0;
     int PB = B;
     if (e_codes) {
         // the matrix of a row: looked up (experts of a step), or z / ntok for a stack of matrices applied to the same ntok rows
-        const int e = row_expert ? row_expert[blockIdx.z] : (int)blockIdx.z / ntok;
+        // dual_rows: rows dual_rows.. repeat the first dual_rows rows on a second stack of matrices (gate and up of an expert)
+        int zr = blockIdx.z;
+        if (dual_rows && zr >= dual_rows) { zr -= dual_rows; codes = codes2; scales = scales2; }
+        const int e = row_expert ? row_expert[zr] : zr / ntok;
         codes += (size_t)e * e_codes; scales += (size_t)e * e_scales;
-        xrow = blockIdx.z % ntok; prow = blockIdx.z; PB = gridDim.z;
+        xrow = zr % ntok; prow = blockIdx.z; PB = gridDim.z;
     }
     extern __shared__ float xs[];               // [BT][kslice]
     constexpr bool PAR = BT <= 2;               // every warp parks its sums, one pass adds them in warp order
@@ -245,12 +249,20 @@ __global__ void __launch_bounds__(256) k_gemv_finish_res_norm(bf16 *F, bf16 *Fn,
     const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float v[8], ss = 0.0f;
 #pragma unroll
+    for (int c = 0; c < 8; c++) v[c] = 0.0f;
+    for (int k = 0; k < nslice; k++) {                   // slice order ascending per column, the columns' loads independent
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            const int n = threadIdx.x + 256 * c;
+            if (n < N) v[c] += part[((size_t)k * B + b) * N + n];
+        }
+    }
+#pragma unroll
     for (int c = 0; c < 8; c++) {
         const int n = threadIdx.x + 256 * c;
-        v[c] = 0.0f;
         if (n < N) {
-            float y = 0.0f;
-            for (int k = 0; k < nslice; k++) y += part[((size_t)k * B + b) * N + n];
+            float y = v[c];
+            v[c] = 0.0f;
             y = __bfloat162float(__float2bfloat16_rn(y));
             const bf16 f = __float2bfloat16_rn(y + __bfloat162float(res[(size_t)b * N + n]));
             F[(size_t)b * N + n] = f;
@@ -305,12 +317,13 @@ __global__ void __launch_bounds__(256) k_gemv_finish_qkv(bf16 *Y, bf16 *Kc, bf16
 }
 
 // act[r,f] = silu(g) * u with g, u the K-slice sums (ascending) of the gate and up partials
-__global__ void __launch_bounds__(256) k_gemv_finish_swiglu(bf16 *act, const float *pg, const float *pu, int nslice, size_t RN)
+__global__ void __launch_bounds__(256) k_gemv_finish_swiglu(bf16 *act, const float *pg, const float *pu, int nslice, size_t RN,
+                                                            size_t slice_stride)
 {
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= RN) return;
     float g = 0.0f, u = 0.0f;
-    for (int k = 0; k < nslice; k++) { g += pg[(size_t)k * RN + i]; u += pu[(size_t)k * RN + i]; }
+    for (int k = 0; k < nslice; k++) { g += pg[(size_t)k * slice_stride + i]; u += pu[(size_t)k * slice_stride + i]; }
     // the stash of the training path holds g and u as bf16; round the same way before the product
     g = __bfloat162float(__float2bfloat16_rn(g)); u = __bfloat162float(__float2bfloat16_rn(u));
     act[i] = __float2bfloat16_rn(g * __fdividef(1.0f, 1.0f + __expf(-g)) * u);
@@ -355,14 +368,14 @@ int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, con
     void *ws = nullptr;
     int rc = workspace((2 * pg_n + pd_n) * sizeof(float) + (size_t)R * F * sizeof(bf16) + 256, &ws);
     if (rc) return rc;
-    float *pg = (float *)ws, *pu = pg + pg_n, *pd = pu + pg_n;
+    // gate and up share one launch: rows 0..R-1 of a slice are the gate partials, rows R..2R-1 the up partials
+    float *pg = (float *)ws, *pu = pg + (size_t)R * F, *pd = pg + 2 * pg_n;
     bf16 *act = (bf16 *)(pd + pd_n);
     const size_t ec = (size_t)D * F / 2, es = (size_t)D * F / 128;
-    k_gemv_kn<1><<<dim3((F + 255) / 256, ns1, R), 256, (size_t)ks1 * sizeof(float), st>>>(
-        pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N);
-    k_gemv_kn<1><<<dim3((F + 255) / 256, ns1, R), 256, (size_t)ks1 * sizeof(float), st>>>(
-        pu, f_norm, QLMB_BF16, (const uint8_t *)L->w3_codes, L->w3_scales, 1, D, F, ks1, assign, ec, es, N);
-    k_gemv_finish_swiglu<<<(unsigned)(((size_t)R * F + 255) / 256), 256, 0, st>>>(act, pg, pu, ns1, (size_t)R * F);
+    k_gemv_kn<1><<<dim3((F + 255) / 256, ns1, 2 * R), 256, (size_t)ks1 * sizeof(float), st>>>(
+        pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N, nullptr, R,
+        (const uint8_t *)L->w3_codes, L->w3_scales);
+    k_gemv_finish_swiglu<<<(unsigned)(((size_t)R * F + 255) / 256), 256, 0, st>>>(act, pg, pu, ns1, (size_t)R * F, (size_t)2 * R * F);
     k_gemv_kn<1><<<dim3((D + 255) / 256, ns2, R), 256, (size_t)ks2 * sizeof(float), st>>>(
         pd, act, QLMB_BF16, (const uint8_t *)L->w2_codes, L->w2_scales, 1, F, D, ks2, assign, ec, es, R);
     k_gemv_finish_combine<<<(unsigned)(((size_t)N * D + 255) / 256), 256, 0, st>>>((bf16 *)out, (const bf16 *)f_in, pd, gate, ns2, N, K, D);

@@ -122,8 +122,15 @@ __global__ void __launch_bounds__(256) k_router_small(float *rt, const void *X, 
     const int per = (D + 7) / 8, j0 = warp * per, j1 = j0 + per < D ? j0 + per : D;
     float acc = 0.0f;
     if (e < E) {
-#pragma unroll 8
-        for (int j = j0; j < j1; j++) acc = __fmaf_rn(rs_x[j], __ldg(Wr + (size_t)j * E + e), acc);
+        // 32 rows of Wr in flight per lane (the loads do not depend on the sum); the sum itself stays in ascending order
+        for (int j = j0; j < j1; j += 32) {
+            float w[32];
+#pragma unroll
+            for (int u = 0; u < 32; u++) w[u] = j + u < j1 ? __ldg(Wr + (size_t)(j + u) * E + e) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 32; u++)
+                if (j + u < j1) acc = __fmaf_rn(rs_x[j + u], w[u], acc);
+        }
     }
     part[warp][e] = acc;
     __syncthreads();
