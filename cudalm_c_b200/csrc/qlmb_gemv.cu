@@ -62,6 +62,22 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
     const bool live = n0 < N;
     const uint8_t *cp = codes + (size_t)n0 / 2;
     const float *sp = scales + n0 / 128;
+    // four rows per batch (k, k+8, k+16, k+24), two batches in flight; the first two are requested before the
+    // activations are staged (the weights do not depend on them)
+    uint32_t w[2][4];
+    float sc[2][4];
+    auto fetch = [&](int buf, int k) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int kk = k + 8 * u;
+            w[buf][u] = 0u; sc[buf][u] = 0.0f;
+            if (kk < k1) {
+                w[buf][u] = __ldcs(reinterpret_cast<const uint32_t *>(cp + (size_t)kk * N / 2));
+                sc[buf][u] = __ldg(sp + (size_t)kk * gpr);
+            }
+        }
+    };
+    if (live) { fetch(0, k0 + warp); fetch(1, k0 + warp + 32); }
     // gamma (routed form, one activation row per block): the row is normalised on the way in, x * rinv * gamma rounded
     // to bf16 as the separate norm kernel stores it (e_rmsf in front of the q, k, v projections, cudalm.cu:7176)
     float rinv = 1.0f;
@@ -93,20 +109,6 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
 #pragma unroll
             for (int j = 0; j < 8; j++) acc[b][j] = 0.0f;
         if (live) {
-            // four rows per batch (k, k+8, k+16, k+24); the next batch is loaded before the current one is used
-            uint32_t w[2][4];
-            float sc[2][4];
-            auto fetch = [&](int buf, int k) {
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int kk = k + 8 * u;
-                    w[buf][u] = 0u; sc[buf][u] = 0.0f;
-                    if (kk < k1) {
-                        w[buf][u] = __ldcs(reinterpret_cast<const uint32_t *>(cp + (size_t)kk * N / 2));
-                        sc[buf][u] = __ldg(sp + (size_t)kk * gpr);
-                    }
-                }
-            };
             auto use = [&](int buf, int k) {
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
@@ -124,12 +126,12 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
                 }
             };
             int k = k0 + warp;
-            fetch(0, k);
+            if (b0 > 0) { fetch(0, k); fetch(1, k + 32); }
             for (; k < k1; k += 64) {
-                fetch(1, k + 32);
                 use(0, k);
                 fetch(0, k + 64);
                 use(1, k + 32);
+                fetch(1, k + 96);
             }
         }
         // fixed-order combination of the 8 warps
