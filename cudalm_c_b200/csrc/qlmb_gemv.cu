@@ -249,9 +249,13 @@ __global__ void __launch_bounds__(256) k_gemv_finish_res_norm(bf16 *F, bf16 *Fn,
 {
     __shared__ float red[8];
     const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float v[8], ss = 0.0f;
+    float v[8], rs[8], gm[8], ss = 0.0f;
 #pragma unroll
-    for (int c = 0; c < 8; c++) v[c] = 0.0f;
+    for (int c = 0; c < 8; c++) {                        // residual and gain are requested together with the slices
+        const int n = threadIdx.x + 256 * c;
+        v[c] = 0.0f; rs[c] = 0.0f; gm[c] = 0.0f;
+        if (n < N) { rs[c] = __bfloat162float(res[(size_t)b * N + n]); gm[c] = gamma[n]; }
+    }
     for (int k = 0; k < nslice; k++) {                   // slice order ascending per column, the columns' loads independent
 #pragma unroll
         for (int c = 0; c < 8; c++) {
@@ -266,7 +270,7 @@ __global__ void __launch_bounds__(256) k_gemv_finish_res_norm(bf16 *F, bf16 *Fn,
             float y = v[c];
             v[c] = 0.0f;
             y = __bfloat162float(__float2bfloat16_rn(y));
-            const bf16 f = __float2bfloat16_rn(y + __bfloat162float(res[(size_t)b * N + n]));
+            const bf16 f = __float2bfloat16_rn(y + rs[c]);
             F[(size_t)b * N + n] = f;
             v[c] = __bfloat162float(f);
             ss += v[c] * v[c];
@@ -283,7 +287,7 @@ __global__ void __launch_bounds__(256) k_gemv_finish_res_norm(bf16 *F, bf16 *Fn,
 #pragma unroll
     for (int c = 0; c < 8; c++) {
         const int n = threadIdx.x + 256 * c;
-        if (n < N) Fn[(size_t)b * N + n] = __float2bfloat16_rn(v[c] * rinv * gamma[n]);
+        if (n < N) Fn[(size_t)b * N + n] = __float2bfloat16_rn(v[c] * rinv * gm[c]);
     }
 }
 

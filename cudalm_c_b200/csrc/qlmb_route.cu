@@ -116,17 +116,24 @@ __global__ void __launch_bounds__(256) k_router_small(float *rt, const void *X, 
     extern __shared__ float rs_x[];                      // D activations
     __shared__ float part[8][32];
     const int n = blockIdx.x, warp = threadIdx.x >> 5, e = threadIdx.x & 31;
+    const int per = (D + 7) / 8, j0 = warp * per, j1 = j0 + per < D ? j0 + per : D;
+    // 32 rows of Wr in flight per lane (the loads depend neither on the sum nor on the activations: the first batch is
+    // requested before the row is staged); the sum itself stays in ascending order
+    float w[32];
+    if (e < E) {
+#pragma unroll
+        for (int u = 0; u < 32; u++) w[u] = j0 + u < j1 ? __ldg(Wr + (size_t)(j0 + u) * E + e) : 0.0f;
+    }
     for (int j = threadIdx.x; j < D; j += 256)
         rs_x[j] = x_dtype == QLMB_BF16 ? __bfloat162float(((const bf16 *)X)[(size_t)n * D + j]) : ((const float *)X)[(size_t)n * D + j];
     __syncthreads();
-    const int per = (D + 7) / 8, j0 = warp * per, j1 = j0 + per < D ? j0 + per : D;
     float acc = 0.0f;
     if (e < E) {
-        // 32 rows of Wr in flight per lane (the loads do not depend on the sum); the sum itself stays in ascending order
         for (int j = j0; j < j1; j += 32) {
-            float w[32];
+            if (j > j0) {
 #pragma unroll
-            for (int u = 0; u < 32; u++) w[u] = j + u < j1 ? __ldg(Wr + (size_t)(j + u) * E + e) : 0.0f;
+                for (int u = 0; u < 32; u++) w[u] = j + u < j1 ? __ldg(Wr + (size_t)(j + u) * E + e) : 0.0f;
+            }
 #pragma unroll
             for (int u = 0; u < 32; u++)
                 if (j + u < j1) acc = __fmaf_rn(rs_x[j + u], w[u], acc);
