@@ -33,8 +33,10 @@ __device__ __forceinline__ void unpack8(uint32_t w, float d[8])
 // k0+w, k0+w+8, ..., eight of them in flight per step; lane = 8 consecutive columns (one code word).
 // BT activation rows are multiplied per pass (BT = 1, 2, 4 or 8: no arithmetic on absent rows);
 // part[ks][b][n] receives the slice sums.
-template <int BT>
-__global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, const void *X, int dtype, const uint8_t *codes,
+// NB batches of four rows in flight per lane: 2 (four blocks per SM for up to two rows) when the grid fills the device,
+// 4 (two blocks per SM) for the small grids of a decode step, where the latency of each round of loads is what counts
+template <int BT, int NB = 2>
+__global__ void __launch_bounds__(256, NB == 4 ? 2 : (BT <= 2 ? 4 : 2)) k_gemv_kn(float *part, const void *X, int dtype, const uint8_t *codes,
                                                  const float *scales, int B, int K, int N, int kslice,
                                                  const int *row_expert = nullptr, size_t e_codes = 0, size_t e_scales = 0,
                                                  int ntok = 1, const float *gamma = nullptr, int dual_rows = 0,
@@ -62,10 +64,10 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
     const bool live = n0 < N;
     const uint8_t *cp = codes + (size_t)n0 / 2;
     const float *sp = scales + n0 / 128;
-    // four rows per batch (k, k+8, k+16, k+24), two batches in flight; the first two are requested before the
+    // four rows per batch (k, k+8, k+16, k+24), NB batches in flight; the first NB are requested before the
     // activations are staged (the weights do not depend on them)
-    uint32_t w[2][4];
-    float sc[2][4];
+    uint32_t w[NB][4];
+    float sc[NB][4];
     auto fetch = [&](int buf, int k) {
 #pragma unroll
         for (int u = 0; u < 4; u++) {
@@ -77,7 +79,10 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
             }
         }
     };
-    if (live) { fetch(0, k0 + warp); fetch(1, k0 + warp + 32); }
+    if (live) {
+#pragma unroll
+        for (int u = 0; u < NB; u++) fetch(u, k0 + warp + 32 * u);
+    }
     // gamma (routed form, one activation row per block): the row is normalised on the way in, x * rinv * gamma rounded
     // to bf16 as the separate norm kernel stores it (e_rmsf in front of the q, k, v projections, cudalm.cu:7176)
     float rinv = 1.0f;
@@ -126,12 +131,13 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_kn(float *part, c
                 }
             };
             int k = k0 + warp;
-            if (b0 > 0) { fetch(0, k); fetch(1, k + 32); }
-            for (; k < k1; k += 64) {
-                use(0, k);
-                fetch(0, k + 64);
-                use(1, k + 32);
-                fetch(1, k + 96);
+            if (b0 > 0) {
+#pragma unroll
+                for (int u = 0; u < NB; u++) fetch(u, k + 32 * u);
+            }
+            for (; k < k1; k += 32 * NB) {
+#pragma unroll
+                for (int u = 0; u < NB; u++) { use(u, k + 32 * u); fetch(u, k + 32 * u + 32 * NB); }
             }
         }
         // fixed-order combination of the 8 warps
@@ -378,12 +384,23 @@ int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, con
     float *pg = (float *)ws, *pu = pg + (size_t)R * F, *pd = pg + 2 * pg_n;
     bf16 *act = (bf16 *)(pd + pd_n);
     const size_t ec = (size_t)D * F / 2, es = (size_t)D * F / 128;
-    k_gemv_kn<1><<<dim3((F + 255) / 256, ns1, 2 * R), 256, (size_t)ks1 * sizeof(float), st>>>(
-        pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N, nullptr, R,
-        (const uint8_t *)L->w3_codes, L->w3_scales);
+    const dim3 g1((F + 255) / 256, ns1, 2 * R), g2((D + 255) / 256, ns2, R);
+    const size_t small_grid = (size_t)2 * sm_count();
+    if ((size_t)g1.x * g1.y * g1.z <= small_grid)
+        k_gemv_kn<1, 4><<<g1, 256, (size_t)ks1 * sizeof(float), st>>>(
+            pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N, nullptr, R,
+            (const uint8_t *)L->w3_codes, L->w3_scales);
+    else
+        k_gemv_kn<1><<<g1, 256, (size_t)ks1 * sizeof(float), st>>>(
+            pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N, nullptr, R,
+            (const uint8_t *)L->w3_codes, L->w3_scales);
     k_gemv_finish_swiglu<<<(unsigned)(((size_t)R * F + 255) / 256), 256, 0, st>>>(act, pg, pu, ns1, (size_t)R * F, (size_t)2 * R * F);
-    k_gemv_kn<1><<<dim3((D + 255) / 256, ns2, R), 256, (size_t)ks2 * sizeof(float), st>>>(
-        pd, act, QLMB_BF16, (const uint8_t *)L->w2_codes, L->w2_scales, 1, F, D, ks2, assign, ec, es, R);
+    if ((size_t)g2.x * g2.y * g2.z <= small_grid)
+        k_gemv_kn<1, 4><<<g2, 256, (size_t)ks2 * sizeof(float), st>>>(
+            pd, act, QLMB_BF16, (const uint8_t *)L->w2_codes, L->w2_scales, 1, F, D, ks2, assign, ec, es, R);
+    else
+        k_gemv_kn<1><<<g2, 256, (size_t)ks2 * sizeof(float), st>>>(
+            pd, act, QLMB_BF16, (const uint8_t *)L->w2_codes, L->w2_scales, 1, F, D, ks2, assign, ec, es, R);
     k_gemv_finish_combine<<<(unsigned)(((size_t)N * D + 255) / 256), 256, 0, st>>>((bf16 *)out, (const bf16 *)f_in, pd, gate, ns2, N, K, D);
     QLMB_LAUNCH_CHECK("moe_decode_experts");
     return QLMB_OK;
@@ -417,7 +434,7 @@ static int gemv_decode_impl(void *Y, const void *X, const int8_t *codes, const f
     // K slices: enough blocks to fill the device once, at least 64 rows each,
     // a multiple of 8 rows, and small enough for the activation tile in shared memory
     const int nblk = layout == QLMB_KN ? (N + 255) / 256 : (N + 31) / 32;
-    // one full wave: 4 (bt <= 2) or 2 resident blocks per SM
+    // K slices for 4 (bt <= 2) or 2 blocks per SM
     int nslice = ((bt <= 2 ? 4 : 2) * sm_count()) / nblk;
     if (nslice > K / 64) nslice = K / 64;
     if (nslice < 1) nslice = 1;
@@ -437,7 +454,9 @@ static int gemv_decode_impl(void *Y, const void *X, const int8_t *codes, const f
         else if (bt == 4) KERN<4><<<grid, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice); \
         else KERN<8><<<grid, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice); \
     } while (0)
-    if (layout == QLMB_KN) GV_LAUNCH(k_gemv_kn);
+    if (layout == QLMB_KN && bt == 1 && (size_t)nblk * nslice <= (size_t)2 * sm_count())
+        k_gemv_kn<1, 4><<<grid, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice);
+    else if (layout == QLMB_KN) GV_LAUNCH(k_gemv_kn);
     else GV_LAUNCH(k_gemv_nk);
 #undef GV_LAUNCH
     if (fr) k_gemv_finish_res_norm<<<B, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, part, nslice, B, N, (const bf16 *)fr->res, fr->gamma);
@@ -475,8 +494,12 @@ static int gemv_stack_impl(void *Y, const void *X, const int8_t *codes, const fl
     int rc = workspace((size_t)nslice * R * N * sizeof(float), &ws);
     if (rc) return rc;
     float *part = (float *)ws;
-    k_gemv_kn<1><<<dim3(nblk, nslice, R), 256, (size_t)kslice * sizeof(float), st>>>(
-        part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
+    if ((size_t)nblk * nslice * R <= (size_t)2 * sm_count())
+        k_gemv_kn<1, 4><<<dim3(nblk, nslice, R), 256, (size_t)kslice * sizeof(float), st>>>(
+            part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
+    else
+        k_gemv_kn<1><<<dim3(nblk, nslice, R), 256, (size_t)kslice * sizeof(float), st>>>(
+            part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
     if (fr) k_gemv_finish_res_norm<<<R, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, part, nslice, R, N, (const bf16 *)fr->res, fr->gamma);
     else if (fq) k_gemv_finish_qkv<<<(unsigned)(((size_t)R * N / 2 + 255) / 256), 256, 0, st>>>(
         (bf16 *)Y, (bf16 *)fq->Kc, (bf16 *)fq->Vc, part, nslice, B, N, fq->hd, fq->cosb, fq->sinb, fq->pos, fq->Tm);
