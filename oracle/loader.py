@@ -267,6 +267,11 @@ class Reference:
         self.lib.ref_ngram_gather(_p(tbl), _p(key), _p(buf), C.c_int(N), C.c_int(De), C.c_int(nk))
         return buf
 
+    # ---- selection bias update (mbias_upd, cudalm.cu:3793-3802); b [ns, E] is updated in place ----
+    def mbias_upd(self, b, counts, m, u, lmul, prop):
+        ns, E = counts.shape
+        self.lib.ref_mbias_upd(_p(b), _p(counts), C.c_int(ns), C.c_int(E), C.c_float(m), C.c_float(u), C.c_float(lmul), C.c_int(prop))
+
     # ---- the table's context gate (cpu_kern.h:573-589); h, k and dy are updated in place ----
     def nggate_f(self, h, v, k):
         N, D = h.shape
@@ -425,6 +430,22 @@ class RefMoeLayer:
 
 
 _cache = {}
+
+
+def bias_update_np(b, assign, E, per_slot, u, prop):
+    """numpy float32 restatement of mbias_upd and its two call forms (cudalm.cu:3793-3798, 4385): b [K, E] with one
+    count row per top-k pass and target N/E, or b [1, E] with the combined counts and target K*N/E.  Returns the new b."""
+    f32 = np.float32
+    K, N = assign.shape
+    u = f32(u)
+    m = f32(N) / f32(E) if per_slot else f32(K) * f32(N) / f32(E)
+    rows = [assign[k] for k in range(K)] if per_slot else [assign.ravel()]
+    out = b.astype(f32).copy()
+    for s, a in enumerate(rows):
+        c = np.bincount(a, minlength=E).astype(f32)
+        d = (m - c) / m if prop else np.where(c < m, f32(1), np.where(c > m, f32(-1), f32(0))).astype(f32)
+        out[s] = out[s] + (u * d.astype(f32)).astype(f32)
+    return out
 
 
 def restatement():

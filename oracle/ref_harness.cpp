@@ -108,6 +108,21 @@ void ref_attn_bwd(const float *Q, const float *K, const float *V, const float *O
 void ref_ngram_key(const int *tok, int *key, int N, int T, int R, int order, int base) { KL(k_ngram_key, 1, 1)(tok, key, N, T, R, order, base); }
 void ref_ngram_gather(const float *tbl, const int *key, float *buf, int N, int De, int nk) { KL(k_ngram_gather, 1, 1)(tbl, key, buf, N, De, nk); }
 
+/* ---- aux-free balancing: the selection bias after a step's routing (mbias_upd, cudalm.cu:3793-3802) on the caller's
+ * rows b[ns][E]; cs = ns count rows, m = target load, u and lmul = CUDALM_MOE_BIAS and the layer's multiplier ---- */
+void ref_mbias_upd(float *b, const int *cs, int ns, int E, float m, float u, float lmul, int prop)
+{
+    float su = g_mbias_u, *sH = g_mbiasH, *sD = g_mbiasD, sl = g_biaslm[0];
+    int sp = g_mbias_p, ss = g_mbias_slot, sn = g_biaslm_n, sE = gC.n_exp, sk = g_topk;
+    float *dev = (float *)malloc(sizeof(float) * (size_t)ns * E);       /* the CPU build's "device" copy */
+    g_mbias_u = u; g_mbias_p = prop; g_mbias_slot = ns > 1; g_topk = ns; gC.n_exp = E; g_biaslm[0] = lmul; g_biaslm_n = 1;
+    g_mbiasH = b; g_mbiasD = dev;
+    mbias_upd(0, cs, ns, E, m);
+    g_mbias_u = su; g_mbiasH = sH; g_mbiasD = sD; g_biaslm[0] = sl;
+    g_mbias_p = sp; g_mbias_slot = ss; g_biaslm_n = sn; gC.n_exp = sE; g_topk = sk;
+    free(dev);
+}
+
 /* ---- the table's context gate (cpu_kern.h:573-589) ---- */
 void ref_nggate_f(float *h, const float *v, float *k, float *hn, float *g, float *rh, float *rk, int N, int D) { KL(k_nggate_f, N, 128)(h, v, k, hn, g, rh, rk, D); }
 void ref_nggate_b(float *dy, const float *v, const float *hn, const float *kn, const float *g, const float *rh, const float *rk, float *dv, float *dk, int N, int D)

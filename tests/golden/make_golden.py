@@ -324,10 +324,41 @@ def golden_ngram(ref):
     np.savez_compressed(os.path.join(OUT, "ngram_q4.npz"), **out)
 
 
+def golden_router_bias(ref):
+    """The selection-bias update after a step's routing (mbias_upd, cudalm.cu:3793-3802, called as at 4385): three
+    updates in a row for the per-pass and the combined form, proportional and sign rule, u = 0.001 x a layer multiplier."""
+    out = {}
+    N, E, K = 4096, 64, 2
+    for per_slot in (1, 0):
+        for prop in (1, 0):
+            rng = np.random.default_rng(31 + 2 * per_slot + prop)
+            rows = K if per_slot else 1
+            b = (rng.standard_normal((rows, E)) * 0.01).astype(f32)
+            tag = "s%d_p%d" % (per_slot, prop)
+            out["b0_" + tag] = b.copy()
+            for it in range(3):
+                asg = rng.integers(0, E, (K, N)).astype(np.int32)
+                asg[0, : N // 4] = 3                       # a hot expert
+                if per_slot:
+                    asg[1] = np.arange(N) % E              # every expert exactly at the target load
+                cs = (np.stack([np.bincount(asg[k], minlength=E) for k in range(K)]) if per_slot
+                      else np.bincount(asg.ravel(), minlength=E)[None]).astype(np.int32)
+                m = f32(N) / f32(E) if per_slot else f32(K) * f32(N) / f32(E)
+                ref.mbias_upd(b, np.ascontiguousarray(cs), float(m), 0.001, 1.5, prop)
+                out["asg%d_%s" % (it, tag)] = asg
+            out["b_" + tag] = b.copy()
+    out["cfg"] = np.array([N, E, K])
+    out["u"] = np.array([f32(0.001) * f32(1.5)], f32)
+    np.savez_compressed(os.path.join(OUT, "router_bias.npz"), **out)
+
+
 def main():
     ref = loader.reference(exact=True)
     if ref is None:
         sys.exit("oracle/_ref/libcudalm_ref_exact.so missing: run `make -C oracle ref` first")
+    if sys.argv[1:] == ["router_bias"]:                    # one fixture alone: python make_golden.py router_bias
+        golden_router_bias(ref)
+        return
     golden_hash(ref)
     golden_one_group(ref)
     golden_state(ref, "state_g128", [128 * 40, 1000, 78, 128 * 3 + 2], 128, 7, 1, 6, seed=1)
@@ -342,6 +373,7 @@ def main():
     golden_fused(ref)
     golden_state_v4(ref)
     golden_ngram(ref)
+    golden_router_bias(ref)
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print("%-24s %8d B" % (f, os.path.getsize(os.path.join(OUT, f))))

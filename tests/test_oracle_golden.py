@@ -171,3 +171,19 @@ def test_fused_per_layer_update(oracle):
     for k, v in out.items():
         assert np.array_equal(v, g["out_" + k]), k
     assert out["norms"][0] > 1.0 > out["norms"][1]          # the clip switches on for step 2 and off for step 3
+
+
+def test_router_bias_update_restatement():
+    """The float32 restatement of mbias_upd (oracle/loader.py, cudalm.cu:3793-3798, 4385) against the reference's own
+    function on the same assignments: per-pass and combined counts, proportional and sign rule, three updates each."""
+    g = golden("router_bias")
+    N, E, K = [int(x) for x in g["cfg"]]
+    u = float(g["u"][0])
+    for per_slot in (1, 0):
+        for prop in (1, 0):
+            tag = "s%d_p%d" % (per_slot, prop)
+            b = g["b0_" + tag].copy()
+            for it in range(3):
+                b = loader.bias_update_np(b, g["asg%d_%s" % (it, tag)], E, per_slot, u, prop)
+            assert np.array_equal(b, g["b_" + tag]), tag
+            assert not np.array_equal(b, g["b0_" + tag])

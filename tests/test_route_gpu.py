@@ -123,3 +123,19 @@ def test_router_bias_update(cuda, per_slot, prop):
             d = (m - c) / m if prop else np.where(c < m, f32(1), np.where(c > m, f32(-1), f32(0))).astype(f32)
             b[s] = b[s] + (u * d.astype(f32)).astype(f32)
     assert np.array_equal(db.cpu().numpy(), b)
+
+
+def test_router_bias_update_matches_reference(cuda):
+    """qlmb_router_bias_update against the bias rows the reference's mbias_upd leaves (fixture): bit-exact."""
+    from cudalm_c_b200 import moe
+    g = golden("router_bias")
+    N, E, K = [int(x) for x in g["cfg"]]
+    u = float(g["u"][0])
+    for per_slot in (1, 0):
+        for prop in (1, 0):
+            tag = "s%d_p%d" % (per_slot, prop)
+            db = dev(g["b0_" + tag], cuda)
+            for it in range(3):
+                moe.router_bias_update(db, dev(g["asg%d_%s" % (it, tag)], cuda), E, per_slot=bool(per_slot), u=u,
+                                       proportional=bool(prop))
+            assert np.array_equal(db.cpu().numpy(), g["b_" + tag]), tag
