@@ -57,6 +57,13 @@ def test_shape_errors_of_the_step_operators():
         (lambda: L.qlmb_gemv_decode_stack(one, one, one, one, 3, 100, 768, 768, 1, None), b"qlmb_gemv_decode_stack"),
         (lambda: L.qlmb_ng_touched(one, one, one, one, 8, 32, 100, 4, None), b"qlmb_ng_touched"),
         (lambda: L.qlmb_softmax_ce(one, 5, one, one, one, 0, 4, 16, 4, None), b"qlmb_softmax_ce"),
+        (lambda: L.qlmb_router_bias_update(one, one, 64, 300, 2, 1, 0.001, 1, None), b"qlmb_router_bias_update"),
+        (lambda: L.qlmb_router_bias_update(None, one, 64, 32, 2, 1, 0.001, 1, None), b"NULL"),
+        (lambda: L.qlmb_nggate_fwd(one, one, one, one, 1, one, one, one, 8, 30, None), b"multiple of 4"),
+        (lambda: L.qlmb_nggate_bwd(one, one, one, one, 7, one, one, one, one, one, 8, 32, None), b"qlmb_nggate_bwd"),
+        (lambda: L.qlmb_gemv_decode_res_norm(one, one, one, one, one, one, one, 4, 768, 4096, None), b"qlmb_gemv_decode_res_norm"),
+        (lambda: L.qlmb_gemv_decode_norm_stack(one, one, None, one, one, 3, 4, 768, 768, 1, None), b"qlmb_gemv_decode_norm_stack"),
+        (lambda: L.qlmb_dec_qkv(one, one, one, one, one, one, one, one, one, one, 4, 768, 63, 128, None), b"qlmb_dec_qkv"),
     ]
     for call, needle in cases:
         rc = call()
