@@ -105,6 +105,22 @@ class Restatement:
         self.lib.qo_gnorm(_p(G), C.c_size_t(G.size), ptrs, lens, C.c_int(ns), C.c_int(clip_side), _p(gs))
         return gs
 
+    def bias_update(self, b, counts, m, u, prop):
+        ns, E = counts.shape
+        self.lib.qo_bias_update(_p(b), _p(counts), C.c_int(ns), C.c_int(E), C.c_float(m), C.c_float(u), C.c_int(prop))
+
+    def nggate_f(self, h, v, k):
+        N, D = h.shape
+        hn = np.zeros_like(h); g, rh, rk = (np.zeros(N, np.float32) for _ in range(3))
+        self.lib.qo_nggate_f(_p(h), _p(v), _p(k), _p(hn), _p(g), _p(rh), _p(rk), C.c_int(N), C.c_int(D))
+        return hn, g, rh, rk
+
+    def nggate_b(self, dy, v, hn, kn, g, rh, rk):
+        N, D = dy.shape
+        dv, dk = np.zeros_like(dy), np.zeros_like(dy)
+        self.lib.qo_nggate_b(_p(dy), _p(v), _p(hn), _p(kn), _p(g), _p(rh), _p(rk), _p(dv), _p(dk), C.c_int(N), C.c_int(D))
+        return dv, dk
+
     def sqsum(self, G):
         part = np.zeros(64, np.float32)
         self.lib.qo_sqsum(_p(G), C.c_size_t(G.size), _p(part))

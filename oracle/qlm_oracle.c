@@ -670,3 +670,45 @@ void qo_moe_bwd(float *dfnorm, float *dW1, float *dW3, float *dW2, float *dWr, f
         }
     free(drt); free(cnt);
 }
+
+/* ---- aux-free balancing (mbias_upd, cudalm.cu:3793-3798; call forms at 4385) ----
+ * b[ns][E] += u * ((m - c) / m  or  sign(m - c)), c = the count of expert e in row s of cs, all in float. */
+void qo_bias_update(float *b, const int *cs, int ns, int E, float m, float u, int prop)
+{
+    for (int s = 0; s < ns; s++)
+        for (int e = 0; e < E; e++) {
+            float c = (float)cs[s * E + e];
+            float d = prop ? (m - c) / m : (c < m ? 1.0f : c > m ? -1.0f : 0.0f);
+            float step = u * d;
+            b[s * E + e] = b[s * E + e] + step;
+        }
+}
+
+/* ---- n-gram context gate (k_nggate_f / k_nggate_b, cudalm.cu:3362-3378; CPU twins cpu_kern.h:573-589) ----
+ * Row sums in double (the reference's kernels sum in float in their own orders; the comparison is to 1e-5). */
+void qo_nggate_f(float *h, const float *v, float *k, float *hn, float *g, float *rh, float *rk, int N, int D)
+{
+    for (int r = 0; r < N; r++) {
+        size_t o = (size_t)r * D;
+        double a = 0, b = 0, c = 0;
+        for (int i = 0; i < D; i++) { a += (double)h[o + i] * h[o + i]; b += (double)k[o + i] * k[o + i]; c += (double)h[o + i] * k[o + i]; }
+        float r1 = 1.0f / sqrtf((float)a / D + 1e-6f), r2 = 1.0f / sqrtf((float)b / D + 1e-6f);
+        float gg = sigm((float)c * r1 * r2 / sqrtf((float)D));
+        for (int i = 0; i < D; i++) { hn[o + i] = h[o + i] * r1; k[o + i] *= r2; h[o + i] += gg * v[o + i]; }
+        g[r] = gg; rh[r] = r1; rk[r] = r2;
+    }
+}
+void qo_nggate_b(float *dy, const float *v, const float *hn, const float *kn, const float *g, const float *rh,
+                 const float *rk, float *dv, float *dk, int N, int D)
+{
+    for (int r = 0; r < N; r++) {
+        size_t o = (size_t)r * D;
+        double a = 0, b = 0;
+        for (int i = 0; i < D; i++) { a += (double)dy[o + i] * v[o + i]; b += (double)hn[o + i] * kn[o + i]; }
+        float gg = g[r], cz = (float)a * gg * (1.0f - gg) / sqrtf((float)D), m = (float)b / D, r1 = rh[r], r2 = rk[r];
+        for (int i = 0; i < D; i++) {
+            float d = dy[o + i], x = hn[o + i], y = kn[o + i];
+            dv[o + i] = gg * d; dk[o + i] = cz * (x - y * m) * r2; dy[o + i] = d + cz * (y - x * m) * r1;
+        }
+    }
+}

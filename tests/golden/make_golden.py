@@ -352,12 +352,28 @@ def golden_router_bias(ref):
     np.savez_compressed(os.path.join(OUT, "router_bias.npz"), **out)
 
 
+def golden_nggate(ref):
+    """The n-gram table's context gate through the reference's CPU kernels (k_nggate_f / k_nggate_b, cpu_kern.h:573-589):
+    12 rows of 256, keys correlated with the stream so that the gates spread."""
+    rng = np.random.default_rng(9)
+    N, D = 12, 256
+    h, v, k, dy = [rng.standard_normal((N, D)).astype(f32) for _ in range(4)]
+    k = (3.0 * k).astype(f32)
+    k[:, :64] += 4.0 * h[:, :64] * np.linspace(-1, 1, N, dtype=f32)[:, None]
+    out = dict(h0=h.copy(), v=v, k0=k.copy(), dy0=dy.copy())
+    hn, g, rh, rk = ref.nggate_f(h, v, k)
+    dv, dk = ref.nggate_b(dy, v, hn, k, g, rh, rk)
+    out.update(h=h, k=k, hn=hn, g=g, rh=rh, rk=rk, dy=dy, dv=dv, dk=dk)
+    np.savez_compressed(os.path.join(OUT, "nggate.npz"), **out)
+
+
 def main():
     ref = loader.reference(exact=True)
     if ref is None:
         sys.exit("oracle/_ref/libcudalm_ref_exact.so missing: run `make -C oracle ref` first")
-    if sys.argv[1:] == ["router_bias"]:                    # one fixture alone: python make_golden.py router_bias
-        golden_router_bias(ref)
+    single = {"router_bias": golden_router_bias, "nggate": golden_nggate}
+    if len(sys.argv) == 2 and sys.argv[1] in single:       # one fixture alone: python make_golden.py router_bias
+        single[sys.argv[1]](ref)
         return
     golden_hash(ref)
     golden_one_group(ref)
@@ -374,6 +390,7 @@ def main():
     golden_state_v4(ref)
     golden_ngram(ref)
     golden_router_bias(ref)
+    golden_nggate(ref)
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print("%-24s %8d B" % (f, os.path.getsize(os.path.join(OUT, f))))

@@ -186,3 +186,19 @@ def test_ngram_context_gate(cuda, ref, dtype):
     dy2 = dy.copy()
     dv_r, dk_r = ref.nggate_b(dy2, v, st[0], st[1], g_r, rh_r, rk_r)
     assert rel(dvo, dv_r) < tol and rel(dko, dk_r) < 5 * tol and rel(ddy, dy2) < tol
+
+
+def test_ngram_context_gate_fixture(cuda):
+    """The gate kernels against the committed vectors of the reference's CPU kernels (fp32, 1e-5 relative)."""
+    from conftest import golden
+    from cudalm_c_b200 import block
+    g = golden("nggate")
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    rel = lambda a, b: float(np.abs(a.cpu().numpy() - b).max() / np.abs(b).max())
+    h, k, dy = d(g["h0"]), d(g["k0"]), d(g["dy0"])
+    hn, gg, rh, rk = block.nggate_fwd(h, d(g["v"]), k)
+    for a, b in ((gg, g["g"]), (rh, g["rh"]), (rk, g["rk"]), (hn, g["hn"]), (k, g["k"]), (h, g["h"])):
+        assert rel(a, b) < 1e-5
+    dv, dk = block.nggate_bwd(dy, d(g["v"]), d(g["hn"]), d(g["k"]), d(g["g"]), d(g["rh"]), d(g["rk"]))
+    for a, b in ((dv, g["dv"]), (dk, g["dk"]), (dy, g["dy"])):
+        assert rel(a, b) < 1e-5

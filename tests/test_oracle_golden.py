@@ -187,3 +187,36 @@ def test_router_bias_update_restatement():
                 b = loader.bias_update_np(b, g["asg%d_%s" % (it, tag)], E, per_slot, u, prop)
             assert np.array_equal(b, g["b_" + tag]), tag
             assert not np.array_equal(b, g["b0_" + tag])
+
+
+def test_router_bias_update_c_restatement(oracle):
+    """qo_bias_update (oracle/qlm_oracle.c) on the fixture's counts: the reference's rows bit for bit."""
+    g = golden("router_bias")
+    N, E, K = [int(x) for x in g["cfg"]]
+    u = float(g["u"][0])
+    for per_slot in (1, 0):
+        for prop in (1, 0):
+            tag = "s%d_p%d" % (per_slot, prop)
+            b = g["b0_" + tag].copy()
+            for it in range(3):
+                asg = g["asg%d_%s" % (it, tag)]
+                cs = (np.stack([np.bincount(asg[k], minlength=E) for k in range(K)]) if per_slot
+                      else np.bincount(asg.ravel(), minlength=E)[None]).astype(np.int32)
+                m = np.float32(N) / np.float32(E) if per_slot else np.float32(K) * np.float32(N) / np.float32(E)
+                oracle.bias_update(b, np.ascontiguousarray(cs), float(m), u, prop)
+            assert np.array_equal(b, g["b_" + tag]), tag
+
+
+def test_ngram_context_gate_restatement(oracle):
+    """qo_nggate_f / qo_nggate_b against the reference's CPU kernels (fixture): 1e-5 relative, the row sums are taken in
+    double here and in the kernels' own float orders there."""
+    g = golden("nggate")
+    rel = lambda a, b: float(np.abs(a - b).max() / np.abs(b).max())
+    h, k, dy = g["h0"].copy(), g["k0"].copy(), g["dy0"].copy()
+    hn, gg, rh, rk = oracle.nggate_f(h, g["v"], k)
+    assert g["g"].std() > 0.05
+    for a, b in ((gg, g["g"]), (rh, g["rh"]), (rk, g["rk"]), (hn, g["hn"]), (k, g["k"]), (h, g["h"])):
+        assert rel(a, b) < 1e-5
+    dv, dk = oracle.nggate_b(dy, g["v"], g["hn"], g["k"], g["g"], g["rh"], g["rk"])
+    for a, b in ((dv, g["dv"]), (dk, g["dk"]), (dy, g["dy"])):
+        assert rel(a, b) < 1e-5
