@@ -45,6 +45,8 @@ PROTOTYPES = {
     "qlmb_last_error": (C.c_char_p, []),
     "qlmb_version": (ci, []),
     "qlmb_check_device": (ci, [vp]),
+    "qlmb_selftest_wait_expires": (ci, [ci, vp]),
+    "qlmb_skipped_steps": (ci, [vp, ci, vp]),
     "qlmb_prof_enable": (ci, [ci]),
     "qlmb_side_stream_enable": (ci, [ci]),
     "qlmb_prof_read": (ci, [vp, vp, ci]),
@@ -100,6 +102,7 @@ PROTOTYPES = {
     "qlmb_moe_arena_member": (vp, [vp, ci, ci, ci, ci, ci, C.c_char_p]),
     "qlmb_moe_forward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
     "qlmb_moe_decode": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp]),
+    "qlmb_moe_forward_routed": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, vp]),
     "qlmb_moe_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, vp, vp, vp, cf, vp]),
     "qlmb_moe_route": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp]),
     "qlmb_moe_experts_forward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, ci, vp]),

@@ -304,12 +304,14 @@ __global__ void __launch_bounds__(256) k_dec_rope(void *buf, int dtype, const fl
 }
 // k_dec_kv (cudalm.cu:7028-7030): the new key / value rows go to position pos[b] of slot b's cache [B, Tm, KD] (bf16)
 __global__ void __launch_bounds__(256) k_dec_kv(bf16_t *Kc, bf16_t *Vc, const bf16_t *k, const bf16_t *v, const int *pos, int B,
-                                                int Tm, int KD)
+                                                int Tm, int KD, int *errword)
 {
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= (size_t)B * KD) return;
     const int b = (int)(i / KD), j = (int)(i % KD);
-    const size_t o = ((size_t)b * Tm + pos[b]) * KD + j;
+    const int t = pos[b];
+    if (t < 0 || t >= Tm) { if (j == 0) report_bad_index(errword, 301, b, t); return; }   // the slot ran past its cache: nothing is written
+    const size_t o = ((size_t)b * Tm + t) * KD + j;
     Kc[o] = k[i]; Vc[o] = v[i];
 }
 // k_dec_attn (cudalm.cu:7031-7047): one block of four warps per (slot, head) over the cached keys lo..pos[b].
@@ -319,13 +321,14 @@ __global__ void __launch_bounds__(256) k_dec_kv(bf16_t *Kc, bf16_t *Vc, const bf
 // partial outputs are added in warp order.  Head dimension 64, bf16 cache.
 #define DEC_TM_MAX 4096
 __global__ void __launch_bounds__(128) k_dec_attn(bf16_t *O, const bf16_t *Q, const bf16_t *Kc, const bf16_t *Vc, const int *pos,
-                                                  int win, int B, int Tm, int H, int KV, float scale)
+                                                  int win, int B, int Tm, int H, int KV, float scale, int *errword)
 {
     extern __shared__ float dec_sc[];                    // Tm scores
     __shared__ float red[4], part[4][64];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int g = blockIdx.x;
     const int b = g / H, h = g % H, kvh = h / (H / KV), t = pos[b], KD = KV * 64, D = H * 64;
+    if (t < 0 || t >= Tm) { if (tid == 0 && h == 0) report_bad_index(errword, 302, b, t); return; }   // whole block: no score past the cache
     float *sc = dec_sc;
     const int lo = (win > 0 && t >= win) ? t - win + 1 : 0;
     float q[64];
@@ -737,7 +740,7 @@ extern "C" int qlmb_dec_kv(void *Kc, void *Vc, const void *k, const void *v, con
     if (B <= 0) return QLMB_OK;
     const size_t total = (size_t)B * KD;
     k_dec_kv<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((bf16_t *)Kc, (bf16_t *)Vc, (const bf16_t *)k,
-                                                                              (const bf16_t *)v, pos, B, Tm, KD);
+                                                                              (const bf16_t *)v, pos, B, Tm, KD, device_error_word());
     QLMB_LAUNCH_CHECK("k_dec_kv");
     return QLMB_OK;
 }
@@ -760,7 +763,7 @@ extern "C" int qlmb_dec_attn(void *O, const void *Q, const void *Kc, const void 
     }
     k_dec_attn<<<(unsigned)(B * H), 128, smem, as_stream(stream)>>>((bf16_t *)O, (const bf16_t *)Q, (const bf16_t *)Kc,
                                                                               (const bf16_t *)Vc, pos, win, B, Tm, H, KV,
-                                                                              1.0f / sqrtf((float)hd));
+                                                                              1.0f / sqrtf((float)hd), device_error_word());
     QLMB_LAUNCH_CHECK("k_dec_attn");
     return QLMB_OK;
 }

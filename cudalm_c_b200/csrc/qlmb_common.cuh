@@ -59,6 +59,13 @@ __host__ __device__ __forceinline__ int clampi(int v, int lo, int hi)
     return v < lo ? lo : (v > hi ? hi : v);
 }
 
+// A kernel that finds an argument it must not act on (a cache position outside the cache) records code 201 with the
+// site, the slot and the value in the device error word and skips the access; qlmb_check_device reports it.
+__device__ __forceinline__ void report_bad_index(int *errword, int site, int slot, int value)
+{
+    if (errword && atomicCAS(errword, 0, 201) == 0) { errword[1] = site; errword[2] = slot; errword[3] = value; }
+}
+
 // digit i of a digit array (qlm.cuh:96-101)
 __device__ __forceinline__ int digit_at(const int8_t *d, uint64_t i, int packed)
 {

@@ -302,7 +302,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish_res_norm(bf16 *F, bf16 *Fn,
 // (k_dec_rope: pairs (i, i + hd/2) of every head), the k and v rows go to position pos[b] of the slot's cache
 // (k_dec_kv).  One thread per pair; Y receives all three rows as the separate kernels would leave them.
 __global__ void __launch_bounds__(256) k_gemv_finish_qkv(bf16 *Y, bf16 *Kc, bf16 *Vc, const float *part, int nslice, int B, int N,
-                                                         int hd, const float *cosb, const float *sinb, const int *pos, int Tm)
+                                                         int hd, const float *cosb, const float *sinb, const int *pos, int Tm,
+                                                         int *errword)
 {
     const int hf = hd / 2, nh = N / hd;
     const size_t g = (size_t)blockIdx.x * 256 + threadIdx.x, RN = (size_t)3 * B * N;
@@ -310,6 +311,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish_qkv(bf16 *Y, bf16 *Kc, bf16
     const int i = (int)(g % hf);
     const size_t r = g / hf;
     const int row = (int)(r / nh), h = (int)(r % nh), m = row / B, b = row % B, t = pos[b];
+    // a slot past its cache (or past the rotation tables, which cover the cache): no table read, no cache write
+    if (t < 0 || t >= Tm) { if (i == 0 && h == 0 && m == 0) report_bad_index(errword, 303, b, t); return; }
     const size_t o = (size_t)row * N + (size_t)h * hd + i;
     float x = 0.0f, y = 0.0f;
     for (int k = 0; k < nslice; k++) { x += part[(size_t)k * RN + o]; y += part[(size_t)k * RN + o + hf]; }
@@ -502,7 +505,7 @@ static int gemv_stack_impl(void *Y, const void *X, const int8_t *codes, const fl
             part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
     if (fr) k_gemv_finish_res_norm<<<R, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, part, nslice, R, N, (const bf16 *)fr->res, fr->gamma);
     else if (fq) k_gemv_finish_qkv<<<(unsigned)(((size_t)R * N / 2 + 255) / 256), 256, 0, st>>>(
-        (bf16 *)Y, (bf16 *)fq->Kc, (bf16 *)fq->Vc, part, nslice, B, N, fq->hd, fq->cosb, fq->sinb, fq->pos, fq->Tm);
+        (bf16 *)Y, (bf16 *)fq->Kc, (bf16 *)fq->Vc, part, nslice, B, N, fq->hd, fq->cosb, fq->sinb, fq->pos, fq->Tm, device_error_word());
     else k_gemv_finish<<<(unsigned)(((size_t)R * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)R * N);
     QLMB_LAUNCH_CHECK("qlmb_gemv_decode_stack");
     return QLMB_OK;

@@ -180,16 +180,25 @@ extern "C" void *qlmb_moe_arena_member(void *arena, int N, int D, int F, int E, 
 }
 
 static int moe_forward_impl(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in, const void *f_norm,
-                            void *stream, bool small_router);
+                            void *stream, bool small_router, const float *rt_in = nullptr);
 extern "C" int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in,
                                 const void *f_norm, void *stream)
 {
     return moe_forward_impl(L, arena, out, f_in, f_norm, stream, false);
 }
+// The same layer with the router's logits given by the caller (rt_in [N][E], as qlmb_router_topk takes them):
+// two implementations can then be compared on identical expert choices, which a near-tie of two logits would
+// otherwise make differ between bf16 and fp32 activations.
+extern "C" int qlmb_moe_forward_routed(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in,
+                                       const void *f_norm, const float *rt_in, void *stream)
+{
+    QLMB_REQUIRE(rt_in, "qlmb_moe_forward_routed: NULL logits");
+    return moe_forward_impl(L, arena, out, f_in, f_norm, stream, false, rt_in);
+}
 // small_router: the logits of a decode step's few rows come from k_router_logits_small (another summation order
 // than the tiled kernel; nothing reads them in a backward pass)
 static int moe_forward_impl(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in, const void *f_norm,
-                            void *stream, bool small_router)
+                            void *stream, bool small_router, const float *rt_in)
 {
     int rc = check_layer("qlmb_moe_forward", L);
     if (rc) return rc;
@@ -201,7 +210,11 @@ static int moe_forward_impl(const qlmb_moe_layer *L, void *arena, void *out, con
     const int R = (int)a.rows_cap;
 
     // router: logits, softmax top-k (cudalm.cu:4158, 4174)
-    if (small_router) {
+    if (rt_in) {
+        QLMB_CUDA(cudaMemcpyAsync(a.rt, rt_in, (size_t)N * E * sizeof(float), cudaMemcpyDeviceToDevice, st));
+        ProfScope ps("router_topk", st);
+        if ((rc = router_topk(a.rt, a.rprobs, a.assign, a.gate, N, E, K, L->bias, L->bias_stride, st))) return rc;
+    } else if (small_router) {
         if ((rc = router_small(a.rt, f_norm, L->dtype, L->wr, a.rprobs, a.assign, a.gate, N, D, E, K, L->bias, L->bias_stride, st))) return rc;
     } else {
         { ProfScope ps("router_logits", st);

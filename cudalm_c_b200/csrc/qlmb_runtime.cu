@@ -1,6 +1,7 @@
 // Status plumbing of libqlm_b200: thread-local error text, the per-device error
 // word that kernels with bounded waits report into, and device queries.
 #include "qlmb_common.cuh"
+#include "qlmb_tc.cuh"
 #include <string.h>
 #include <stdlib.h>
 
@@ -167,6 +168,33 @@ extern "C" int qlmb_check_device(void *stream)
         QLMB_CUDA(cudaMemsetAsync(w, 0, sizeof h, qlmb::as_stream(stream)));
         return QLMB_E_DEVICE;
     }
+    return QLMB_OK;
+}
+
+// ---- the error path of the bounded waits, exercised without a fault ----
+// One warp initialises an mbarrier that nothing ever arrives at and polls it `polls` times, exactly as the
+// waits of the tcgen05 kernels do (mbarrier.try_wait, then give up, record the site in the device error word
+// and return).  The kernel ends normally; the context stays usable.
+namespace qlmb {
+__global__ void k_selftest_wait(int *errword, uint32_t polls)
+{
+    __shared__ __align__(8) uint64_t bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) { mbar_init(b, 1); fence_barrier_init(); }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    for (uint32_t i = 0; i < polls; i++)
+        if (mbar_try(b, 0)) return;                      // cannot happen: no arrival is ever made
+    if (errword && atomicCAS(errword, 0, 200) == 0) { errword[1] = 9999; errword[2] = (int)blockIdx.x; errword[3] = (int)polls; }
+}
+}  // namespace qlmb
+extern "C" int qlmb_selftest_wait_expires(int polls, void *stream)
+{
+    QLMB_REQUIRE(polls > 0 && polls <= (1 << 16), "qlmb_selftest_wait_expires: polls %d", polls);
+    int *w = qlmb::device_error_word();
+    if (!w) return qlmb::cuda_fail(cudaGetLastError(), "device_error_word");
+    qlmb::k_selftest_wait<<<1, 32, 0, qlmb::as_stream(stream)>>>(w, (uint32_t)polls);
+    QLMB_LAUNCH_CHECK("k_selftest_wait");
     return QLMB_OK;
 }
 

@@ -37,7 +37,22 @@ struct StepArgs {
     // sparse form (k_ng_q4_step, cudalm.cu:4476-4530): group w of the launch is touched[w], its gradients are the w-th
     // row of a compact buffer; only the first *touched_count entries are live
     const int *touched; const int *touched_count;
+    unsigned long long *skipped;    // device counter of launches that found a non-finite norm and wrote nothing
+    qlmb_span inl; int use_inl;     // one span carried in the launch arguments (the n-gram table) instead of a table in memory
 };
+
+// gpu_adam returns without stepping when the gradient norm is not finite (cudalm.cu:6446-6447; the caller prints
+// "[nan] ... step skipped", 8651-8656).  The reference reads the norm back to the host for that; here every step
+// kernel looks at the norm word that follows the clip multiplier (gs[1], as k_gnorm leaves it) and returns before
+// its first store, so a bad step costs no host round trip and leaves every state byte as it was.
+__device__ __forceinline__ bool step_is_skipped(const StepArgs &a)
+{
+    if (!a.gsp) return false;
+    const float gn = a.gsp[1];
+    if (isfinite(gn)) return false;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && a.skipped) atomicAdd(a.skipped, 1ULL);
+    return true;
+}
 
 // Per-element update shared by both paths (reference qlm.cuh:206-242).
 // Returns the new digit; writes mn / rv (the un-quantised new moments).
@@ -172,8 +187,11 @@ __device__ void step_group_team(const StepArgs &a, int gi, int tl, unsigned tmas
     }
 }
 
-__global__ void __launch_bounds__(256) k_step_generic(StepArgs a)
+__global__ void __launch_bounds__(256) k_step_generic(const __grid_constant__ StepArgs a0)
 {
+    if (step_is_skipped(a0)) return;
+    StepArgs a = a0;
+    if (a0.use_inl) a.sp = &a0.inl;
     int w = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (w >= a.ng) return;
     if (a.touched) {
@@ -300,6 +318,7 @@ __global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
 {
     constexpr int TEAM = 128 / EPL;                      // lanes per group
     constexpr int GPW = 32 / TEAM;                       // groups per warp
+    if (step_is_skipped(a)) return;
     const int lane = threadIdx.x & 31, tl = lane % TEAM, team = lane / TEAM;
     const unsigned tmask = (TEAM == 32) ? 0xffffffffu : (((1u << TEAM) - 1u) << (team * TEAM));
     long long w = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * GPW + team;
@@ -562,6 +581,7 @@ __global__ void __launch_bounds__(256) k_adamw_bf16(float *P, const float *G, ui
 {
     size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
+    if (gs && !isfinite(gs[1])) return;                  // the step is skipped on a non-finite norm (cudalm.cu:6446-6447)
     float g = gs ? G[i] * gs[0] : G[i];
     float m = b1 * bf_to_f(M[i]) + (1.0f - b1) * g;
     float v = b2 * bf_to_f(V[i]) + (1.0f - b2) * g * g;
@@ -602,6 +622,23 @@ extern "C" int qlmb_render(float *P, const int8_t *d, const float *s, const qlmb
     return QLMB_OK;
 }
 
+// the count of skipped step launches lives behind the per-device error word (ints 8..9 of its 16)
+static unsigned long long *skip_counter(void)
+{
+    int *w = device_error_word();
+    return w ? reinterpret_cast<unsigned long long *>(w + 8) : nullptr;
+}
+extern "C" int qlmb_skipped_steps(unsigned long long *count, int reset, void *stream)
+{
+    QLMB_REQUIRE(count, "qlmb_skipped_steps: NULL argument");
+    unsigned long long *c = skip_counter();
+    if (!c) return cuda_fail(cudaGetLastError(), "device_error_word");
+    QLMB_CUDA(cudaMemcpyAsync(count, c, sizeof *count, cudaMemcpyDeviceToHost, as_stream(stream)));
+    QLMB_CUDA(cudaStreamSynchronize(as_stream(stream)));
+    if (reset) QLMB_CUDA(cudaMemsetAsync(c, 0, sizeof *c, as_stream(stream)));
+    return QLMB_OK;
+}
+
 // QLM_V4 is a process-wide switch in the reference too (device global d_qv4, set from the environment by
 // qlm_v4_init, qlm.cuh:68-72)
 static int g_qv4 = 0;
@@ -619,7 +656,8 @@ extern "C" int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const f
     QLMB_REQUIRE(dmax >= 1 && dmax <= 127 && (!packed || dmax <= 7), "qlmb_step: dmax %d", dmax);
     if (ng <= 0) return QLMB_OK;
     StepArgs a = {P, G, d, r, s, m8, m8s, v8, v8s, sp, nspan, group, dmax, lr, b1, b2, wd, gscale, gsp,
-                  inv_bc1, inv_sqrt_bc2, lrmode, t, adam, (unsigned long long *)stat, packed, gi_base, ng, g_qv4, nullptr, nullptr};
+                  inv_bc1, inv_sqrt_bc2, lrmode, t, adam, (unsigned long long *)stat, packed, gi_base, ng, g_qv4, nullptr, nullptr,
+                  skip_counter(), {}, 0};
     auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
     bool fast = group == 128 && packed && adam && !stat && !g_qv4 && al16(G) && al16(d) && al16(r) && al16(m8) &&
                 al16(v8) && (!P || al16(P));
@@ -799,19 +837,14 @@ extern "C" int qlmb_ng_step(float *P, const float *Gc, int8_t *d, int8_t *r, con
     QLMB_REQUIRE(Gc && d && r && s && m8 && m8s && v8 && v8s && tgi && count, "qlmb_ng_step: NULL argument");
     QLMB_REQUIRE(group >= 32 && group <= 256 && (group % 2) == 0 && dmax >= 1 && dmax <= 7 && nt > 0, "qlmb_ng_step: group %d dmax %d", group, dmax);
     if (max_touched <= 0) return QLMB_OK;
-    // the table is one packed span that starts at element 0 (ngram_q4_setup, cudalm.cu:4541-4543)
-    int dev = 0;
-    QLMB_CUDA(cudaGetDevice(&dev));
-    QLMB_REQUIRE(dev >= 0 && dev < 64, "qlmb_ng_step: device index %d", dev);
-    static qlmb_span *g_span[64];
-    if (!g_span[dev]) QLMB_CUDA(cudaMalloc(&g_span[dev], sizeof(qlmb_span)));
+    // the table is one packed span that starts at element 0 (ngram_q4_setup, cudalm.cu:4541-4543); it travels in the
+    // launch arguments, so tables stepped on different streams share nothing and the call can be captured
     qlmb_span h;
     memset(&h, 0, sizeof h);
     h.pof = 0; h.gof = 0; h.qi0 = 0; h.n = nt; h.gi0 = 0; h.ngrp = (int)((nt + group - 1) / group); h.sref = sref;
     cudaStream_t st = as_stream(stream);
-    QLMB_CUDA(cudaMemcpyAsync(g_span[dev], &h, sizeof h, cudaMemcpyHostToDevice, st));
-    StepArgs a = {P, Gc, d, r, s, m8, m8s, v8, v8s, g_span[dev], 1, group, dmax, lr, b1, b2, wd, 1.0f, gs,
-                  inv_bc1, inv_sqrt_bc2, 0, t, 1, nullptr, 1, 0, max_touched, g_qv4, tgi, count};
+    StepArgs a = {P, Gc, d, r, s, m8, m8s, v8, v8s, nullptr, 1, group, dmax, lr, b1, b2, wd, 1.0f, gs,
+                  inv_bc1, inv_sqrt_bc2, 0, t, 1, nullptr, 1, 0, max_touched, g_qv4, tgi, count, skip_counter(), h, 1};
     k_step_generic<<<(max_touched + 7) / 8, 256, 0, st>>>(a);
     QLMB_LAUNCH_CHECK("qlmb_ng_step");
     return QLMB_OK;

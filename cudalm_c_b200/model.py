@@ -48,7 +48,7 @@ class QlmModel:
     sharded (rank r owns experts r*E/W .. of every layer, PeerExpertParallelLayer), everything else replicated;
     the replicated gradients are all-reduced, the clip norm is global, every rank steps its own spans."""
 
-    def __init__(self, cfg, device, seed=1, aux=0.0, rank=0, world=1, group=None, init_blocks=None):
+    def __init__(self, cfg, device, seed=1, aux=0.0, rank=0, world=1, group=None, init_blocks=None, P_init=None):
         c = self.c = cfg
         self.dev = device
         self.rank, self.world, self.group = rank, world, group
@@ -64,10 +64,15 @@ class QlmModel:
         def fill(dst, key):
             gb = torch.Generator(device=device); gb.manual_seed(seed * 1000003 + key)
             dst.normal_(0.0, 0.02, generator=gb)
-        fill(P[o.emb:o.emb + c.V * c.D], 1)
+        if P_init is not None:
+            # a caller-made fp32 parameter vector in the reference's layout (what model_load_full returns): used as is
+            assert world == 1 and P_init.numel() == o.total
+            P.copy_(torch.as_tensor(P_init).reshape(-1))
+        else:
+            fill(P[o.emb:o.emb + c.V * c.D], 1)
         nb = init_blocks or world
         eb = c.E // nb                                    # experts per block
-        for l, lo in enumerate(o.layers):
+        for l, lo in enumerate(o.layers if P_init is None else []):
             for ti, nm in enumerate(("wq", "wk", "wv", "wo", "wr")):
                 a, n = lo[nm]
                 fill(P[a:a + n], 1000 + l * 16 + ti)
@@ -82,12 +87,13 @@ class QlmModel:
                         fill(blk, 100000 + ((l * 3 + wi) * 64 + ge // eb) * 7)
                     P[a + e * per:a + (e + 1) * per] = blk[(ge % eb) * per:(ge % eb + 1) * per]
         sc = 1.0 / math.sqrt(2.0 * c.L)
-        for lo in o.layers:
+        for lo in (o.layers if P_init is None else []):
             for nm in ("wo", "w2"):
                 a, n = lo[nm]; P[a:a + n] *= sc
             for nm in ("an1", "an2"):
                 a, n = lo[nm]; P[a:a + n] = 1.0
-        P[o.nf:o.nf + c.D] = 1.0
+        if P_init is None:
+            P[o.nf:o.nf + c.D] = 1.0
         mats = [lo[nm] for lo in o.layers for nm in QUANT]
         self.q = qlm.Qlm(mats, o.total, device)
         self.q.init_from(P, render=False)
@@ -155,9 +161,10 @@ class QlmModel:
         check(lib().qlmb_modelfile_write(path.encode(), hdr.ctypes.data_as(C.c_void_p), P.ctypes.data_as(C.c_void_p), P.size, None, 0))
 
     # ------------------------------------------------------------------ forward
-    def forward(self, tok, B=None, T=None, moes=None):
+    def forward(self, tok, B=None, T=None, moes=None, route_logits=None):
         """gpu_forward over B sequences of T tokens (default: the training batch); `moes` replaces the
-        layers' MoE states when the row count differs from the training batch (decoder prefill)."""
+        layers' MoE states when the row count differs from the training batch (decoder prefill);
+        route_logits[l] ([N, E] fp32) replaces layer l's router logits (parity runs on given routing)."""
         c = self.c
         B, T = B or c.B, T or c.T
         bf = torch.bfloat16
@@ -179,7 +186,7 @@ class QlmModel:
                 out = mo.forward(fi=f_in, fn=f_norm, out=torch.empty_like(f_in))
             else:
                 f_norm, r2 = block.rmsnorm_fwd(f_in, f["an2"])
-                out = mo.forward(f_in, f_norm)
+                out = mo.forward(f_in, f_norm, rt=route_logits[l] if route_logits is not None else None)
             self.saved.append(dict(a_in=x, a_norm=a_norm, r1=r1, q=qh, k=kh, v=vh, att=att, lse=lse, f_in=f_in, f_norm=f_norm, r2=r2))
             x = out
         self.x_final = x
@@ -280,6 +287,14 @@ class Decoder:
     def __init__(self, model, B, Tm):
         c, dev = model.c, model.dev
         self.m, self.B, self.Tm = model, B, Tm
+        # k_dec_attn keeps one score per cached position in shared memory (at most 4096); the rotation tables must
+        # cover every position a slot can reach, so the decoder makes its own when the cache is longer than the
+        # model's training context
+        assert 1 <= Tm <= 4096, "cache length %d: 1..4096 positions" % Tm
+        if Tm <= c.T:
+            self.cosb, self.sinb = model.cosb, model.sinb
+        else:
+            self.cosb, self.sinb = block.rope_tables(Tm, c.hd, device=dev)
         bf = torch.bfloat16
         self.K = [torch.zeros(B, Tm, c.KD, dtype=bf, device=dev) for _ in range(c.L)]
         self.V = [torch.zeros(B, Tm, c.KD, dtype=bf, device=dev) for _ in range(c.L)]
@@ -302,7 +317,7 @@ class Decoder:
         values of every layer into the cache, the last row's logits picked greedily as the first new token."""
         c, m = self.m.c, self.m
         B, n = ids.shape
-        assert B == self.B and 1 <= n <= self.Tm
+        assert B == self.B and 1 <= n <= self.Tm and n <= c.T, "prompt of %d tokens: cache %d, model context %d" % (n, self.Tm, c.T)
         moes = [self._moe(l, B * n) for l in range(c.L)]
         fn = m.forward(ids.reshape(-1).contiguous(), B=B, T=n, moes=moes)
         for l in range(c.L):
@@ -352,7 +367,9 @@ class Decoder:
 
     def step(self, advance=True):
         """dec_step: the token in self.tok at position self.pos for every slot; logits -> self.logits, greedy pick ->
-        self.otok / self.olp; with advance the pick becomes the next step's token."""
+        self.otok / self.olp; with advance the pick becomes the next step's token.  Positions live on the device
+        only: a slot that has reached the end of its cache (pos == Tm) is not written or read by the kernels, which
+        record error 201 in the device error word instead (qlmb_check_device); the caller bounds the step count."""
         from ._lib import check, lib, ptr, stream_ptr
         c, m, B = self.m.c, self.m, self.B
         L_ = lib()
@@ -364,15 +381,15 @@ class Decoder:
                 # them is applied while the row is staged, the finish rotates q and k and appends k, v to the caches
                 qkv = torch.empty(3 * B, c.D, dtype=torch.bfloat16, device=m.dev)
                 check(L_.qlmb_dec_qkv(ptr(qkv), ptr(self.K[l]), ptr(self.V[l]), ptr(x), ptr(f["an1"]), ptr(w["wq"][0]),
-                                      ptr(w["wq"][1]), ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.D, c.hd, self.Tm, stream_ptr()))
+                                      ptr(w["wq"][1]), ptr(self.cosb), ptr(self.sinb), ptr(self.pos), B, c.D, c.hd, self.Tm, stream_ptr()))
                 qh = qkv[:B]
             else:
                 a_norm, _ = block.rmsnorm_fwd(x, f["an1"])
                 qh = linear.gemv_decode(a_norm, *w["wq"], KN, c.D)
                 kh = linear.gemv_decode(a_norm, *w["wk"], KN, c.KD)
                 vh = linear.gemv_decode(a_norm, *w["wv"], KN, c.KD)
-                check(L_.qlmb_dec_rope(ptr(qh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.H, c.hd, stream_ptr()))
-                check(L_.qlmb_dec_rope(ptr(kh), 1, ptr(m.cosb), ptr(m.sinb), ptr(self.pos), B, c.KV, c.hd, stream_ptr()))
+                check(L_.qlmb_dec_rope(ptr(qh), 1, ptr(self.cosb), ptr(self.sinb), ptr(self.pos), B, c.H, c.hd, stream_ptr()))
+                check(L_.qlmb_dec_rope(ptr(kh), 1, ptr(self.cosb), ptr(self.sinb), ptr(self.pos), B, c.KV, c.hd, stream_ptr()))
                 check(L_.qlmb_dec_kv(ptr(self.K[l]), ptr(self.V[l]), ptr(kh), ptr(vh), ptr(self.pos), B, self.Tm, c.KD, stream_ptr()))
             att = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
             check(L_.qlmb_dec_attn(ptr(att), ptr(qh), ptr(self.K[l]), ptr(self.V[l]), ptr(self.pos), 0, B, self.Tm, c.H, c.KV,

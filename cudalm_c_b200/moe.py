@@ -89,9 +89,13 @@ class MoeLayerState:
         router_bias_update(self.bias, self.member("assign", (self.K, self.N), torch.int32), self.E,
                            per_slot=self.c.bias_stride != 0, u=u, proportional=proportional)
 
-    def forward(self, f_in, f_norm, out=None):
+    def forward(self, f_in, f_norm, out=None, rt=None):
+        """moe_forward; with rt [N, E] the router's logits are taken from it (parity runs on identical routing)."""
         out = out if out is not None else torch.empty_like(f_in)
-        check(lib().qlmb_moe_forward(self.c, self.arena_ptr, ptr(out), ptr(f_in), ptr(f_norm), stream_ptr()))
+        if rt is not None:
+            check(lib().qlmb_moe_forward_routed(self.c, self.arena_ptr, ptr(out), ptr(f_in), ptr(f_norm), ptr(rt), stream_ptr()))
+        else:
+            check(lib().qlmb_moe_forward(self.c, self.arena_ptr, ptr(out), ptr(f_in), ptr(f_norm), stream_ptr()))
         return out
 
     def decode(self, f_in, f_norm, out=None):

@@ -64,6 +64,11 @@ int qlmb_version(void);
 /* Reads and clears the per-device error word kernels set when a bounded
  * wait expires (QLMB_E_DEVICE); synchronises `stream`. */
 int qlmb_check_device(void *stream);
+/* No counterpart in the reference (its kernels have no waits).  Runs the give-up path of the library's
+ * bounded waits on purpose and harmlessly: one warp polls an mbarrier that nothing arrives at `polls`
+ * times (1..65536), records error code 200 / site 9999 in the device error word and returns.  The next
+ * qlmb_check_device reports QLMB_E_DEVICE and clears the word; later launches run as usual. */
+int qlmb_selftest_wait_expires(int polls, void *stream);
 
 /* Work that does not depend on each other inside one call (the three expert weight-gradient GEMMs
  * of the MoE backward against d(act) and dX, the router's backward chain against all of them) runs on
@@ -94,7 +99,11 @@ int qlmb_render(float *P, const int8_t *d, const float *s, const qlmb_span *sp, 
 
 /* qlm_step_launch (qlm.cuh:377-397): one integer-AdamW step over groups
  * [gi_base, gi_base+ng).  P may be NULL (no fp32 view is written); gsp, when
- * not NULL, is a device float that replaces gscale (the clip multiplier);
+ * not NULL, points at the TWO device floats k_gnorm writes (qlmb_gnorm,
+ * qlmb_gnorm_close): gsp[0] replaces gscale (the clip multiplier), gsp[1] is
+ * the gradient norm.  When that norm is not finite the launch writes nothing
+ * and counts itself in qlmb_skipped_steps: gpu_adam's "step skipped"
+ * (cudalm.cu:6446-6447, 8651-8656) without its copy to the host.
  * stat may be NULL.  Element indices in the rounding hash are global, so a
  * step split over several calls / GPUs gives the same bytes as one call. */
 int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const float *s, int8_t *m8,
@@ -102,6 +111,12 @@ int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const float *s, in
               int dmax, float lr, float b1, float b2, float wd, float gscale, const float *gsp,
               float inv_bc1, float inv_sqrt_bc2, int lrmode, uint64_t t, int adam, int64_t *stat,
               int packed, int gi_base, int ng, void *stream);
+
+/* Number of qlmb_step / qlmb_ng_step launches on the current device that found a non-finite norm
+ * in gsp[1] and left the state untouched (the reference prints "[nan] ... step skipped" and counts
+ * them in a row, cudalm.cu:8651-8656).  count is a HOST pointer; synchronises `stream`;
+ * reset != 0 clears the counter afterwards. */
+int qlmb_skipped_steps(unsigned long long *count, int reset, void *stream);
 
 /* QLM_V4 (qlm.cuh:62-72, qv_dec / qv_enc): v8 stores the fourth root of the second moment instead of its square
  * root, so that small-gradient elements of a group do not sit on the uint8 floor.  A process-wide switch, as in
@@ -123,7 +138,8 @@ int qlmb_ng_touched(int *tgi, int *count, int *flag, const int *key, int NK, int
 int qlmb_ng_scatter_compact(float *Gc, const int *key, const int *tgi, const int *count, const float *dbuf, int NK,
                             int De, int group, int Nd, int max_touched, void *stream);
 /* k_ng_q4_step: the integer AdamW step of qlmb_step (packed, adam, relative learning rate against the frozen
- * sref, gradient multiplier gs[0] when gs is not NULL) on groups tgi[0..*count), gradients from Gc. */
+ * sref, gradient multiplier gs[0] when gs is not NULL, skipped like qlmb_step when gs[1] is not finite) on groups
+ * tgi[0..*count), gradients from Gc. */
 int qlmb_ng_step(float *P, const float *Gc, int8_t *d, int8_t *r, const float *s, int8_t *m8, float *m8s, uint8_t *v8,
                  float *v8s, const int *tgi, const int *count, int max_touched, int group, int dmax, float lr, float b1,
                  float b2, float wd, float sref, float inv_bc1, float inv_sqrt_bc2, uint64_t t, uint64_t nt,
@@ -182,7 +198,9 @@ int qlmb_sqsum(const float *G, size_t n, float *part64, void *stream);
 int qlmb_gnorm_close(const float *part, int nslice, float *gs, void *stream);
 
 /* k_adamw (cudalm.cu:2855-2870) for the unquantised spans: bf16 moments,
- * gs (device, may be NULL) = clip multiplier applied on load. */
+ * gs (device, may be NULL) = the two floats k_gnorm writes: gs[0] is the clip
+ * multiplier applied on load; a non-finite norm in gs[1] leaves P, M, V as they
+ * were (the skipped step of cudalm.cu:6446-6447). */
 int qlmb_adamw(float *P, const float *G, uint16_t *M, uint16_t *V, size_t n, float lr, float b1,
                float b2, float wd, float bc1, float bc2, const float *gs, void *stream);
 
@@ -269,6 +287,14 @@ int qlmb_moe_decode(const qlmb_moe_layer *L, void *arena, void *out, const void 
 /* moe_forward (cudalm.cu:4151-4229): out = f_in + sum_k gate_k * FFN_e(f_norm). */
 int qlmb_moe_forward(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in,
                      const void *f_norm, void *stream);
+
+/* qlmb_moe_forward with the router's logits supplied by the caller instead of computed from f_norm
+ * (rt_in [N][E] fp32, the `rt_in` of qlmb_router_topk); everything after the logits is the same code, and
+ * qlmb_moe_backward works on the result as usual.  The reference has no such switch: it exists so that this
+ * library and the reference's CPU build can be compared on identical expert choices (a near-tie of two
+ * logits is decided differently by bf16 and fp32 activations). */
+int qlmb_moe_forward_routed(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in,
+                            const void *f_norm, const float *rt_in, void *stream);
 
 /* moe_backward (cudalm.cu:4233-4393): consumes dout, produces dfnorm and adds
  * the weight gradients into dW1/dW3/dW2/dWr (fp32; beta=1 as the reference,

@@ -420,6 +420,71 @@ class Reference:
         h = self.lib.ref_moe_new(C.c_int(N), C.c_int(D), C.c_int(F), C.c_int(E), C.c_int(K), C.c_float(aux))
         return RefMoeLayer(self, h, N, D, F, E, K)
 
+    # the whole model (gpu_forward / gpu_loss / gpu_backward / gpu_adam with QLM on)
+    def model_new(self, V, D, L, H, KV, F, T, E, K, B, aux=0.0):
+        self.lib.ref_model_new.restype = C.c_void_p
+        h = self.lib.ref_model_new(*[C.c_int(x) for x in (V, D, L, H, KV, F, T, E, K, B)], C.c_float(aux))
+        return RefModel(self, h, B * T, D, V)
+
+
+class RefModel:
+    """One model inside the compiled reference (it keeps configuration and Qlm in globals: one at a time)."""
+
+    def __init__(self, ref, h, N, D, V):
+        L = ref.lib
+        self.ref, self.h, self.N, self.D, self.V = ref, C.c_void_p(h), N, D, V
+        L.ref_model_np.restype = C.c_ulonglong
+        L.ref_model_np.argtypes = [C.c_void_p]
+        L.ref_model_buf.restype = C.c_void_p
+        L.ref_model_buf.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
+        L.ref_model_loss.restype = C.c_double
+        L.ref_model_backward.restype = C.c_double
+        L.ref_model_adam.restype = C.c_int
+        self.np = int(L.ref_model_np(self.h))
+        self.P = self.buf("P", (self.np,))
+        self.G = self.buf("G", (self.np,))
+
+    def buf(self, name, shape, dtype=np.float32, l=0):
+        ptr = self.ref.lib.ref_model_buf(self.h, name.encode(), l)
+        assert ptr, name
+        n = int(np.prod(shape))
+        ct = {np.float32: C.c_float, np.int32: C.c_int32, np.int8: C.c_int8, np.uint8: C.c_uint8, np.uint16: C.c_uint16}[dtype]
+        return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(ct)), shape=(n,)).reshape(shape)
+
+    def qlm_init(self):
+        """qlm_gpu_init: quantise the matrices of P in place; returns the state arrays as numpy views."""
+        self.ref.lib.ref_model_qlm_init(self.h)
+        dims = (C.c_ulonglong * 4)()
+        self.ref.lib.ref_model_qlm_dims(dims)
+        nq, ngrp, nspan, nfloat = (int(x) for x in dims)
+        ptr = self.ref.lib.ref_model_buf(self.h, b"q.span", 0)
+        sp = np.frombuffer((C.c_char * (48 * nspan)).from_address(ptr), dtype=SPAN_DTYPE)
+        self.q = dict(nq=nq, ngrp=ngrp, nfloat=nfloat, sp=sp,
+                      d=self.buf("q.d", (nq // 2,), np.int8), r=self.buf("q.r", (nq,), np.int8),
+                      m8=self.buf("q.m8", (nq,), np.int8), v8=self.buf("q.v8", (nq,), np.uint8),
+                      s=self.buf("q.s", (ngrp,)), m8s=self.buf("q.m8s", (ngrp,)), v8s=self.buf("q.v8s", (ngrp,)),
+                      Mc=self.buf("q.Mc", (nfloat,), np.uint16), Vc=self.buf("q.Vc", (nfloat,), np.uint16))
+        return self.q
+
+    def forward(self, tok):
+        tok = np.ascontiguousarray(tok, np.int32)
+        assert tok.size == self.N
+        self.ref.lib.ref_model_forward(self.h, _p(tok))
+        return self.buf("fn", (self.N, self.D))
+
+    def loss(self, tgt, perpos=None):
+        tgt = np.ascontiguousarray(tgt, np.int32)
+        return float(self.ref.lib.ref_model_loss(self.h, _p(tgt), _p(perpos)))
+
+    def backward(self, tgt):
+        tgt = np.ascontiguousarray(tgt, np.int32)
+        return float(self.ref.lib.ref_model_backward(self.h, _p(tgt)))
+
+    def adam(self, lr, t):
+        gn = C.c_float(0.0)
+        ok = self.ref.lib.ref_model_adam(self.h, C.c_float(lr), C.c_int(t), C.byref(gn))
+        return ok, gn.value
+
 
 class RefMoeLayer:
     def __init__(self, ref, h, N, D, F, E, K):

@@ -263,6 +263,106 @@ void ref_moe_backward(void *hv)
     moe_backward(h->P, h->G, &h->o, h->a, 0, h->N);
 }
 
+/* ---- the whole training step: gpu_forward (cudalm.cu:5736-5787), gpu_loss (8834-8847), gpu_head_bwd + gpu_backward
+ * (5799-6002), gpu_adam with QLM on (6438-6465 -> qlm_gpu_update 6082-6103), set up the way cmd_train does it
+ * (qlm_gpu_init, g_qlm_on = 1, g_muon = 0; 8223-8226, 8301).  One model at a time: the reference keeps the
+ * configuration, the rope tables and the Qlm in file-scope globals. ---- */
+struct RefModel {
+    Cfg c; Off o; size_t np; int N; float *P, *G; GA *a; int *tok, *tgt; int qlm;
+};
+void *ref_model_new(int V, int D, int L, int H, int KV, int F, int T, int E, int K, int B, float aux)
+{
+    gemm_flags_off();
+    memset(&gC, 0, sizeof gC);
+    gC.V = V; gC.D = D; gC.L = L; gC.H = H; gC.KV = KV; gC.F = F; gC.T = T; gC.n_exp = E; gC.rope_base = 10000.0f;
+    cfg_derive(&gC);
+    g_topk = K; g_mbias_u = 0.0f; g_moe_aux = aux; g_moe_stash = 1; g_moe_train = 0; g_prof = 0;
+    g_qlm_on = 0; g_muon = 0; g_fused = 0; g_pscratch = 0; g_nkeep = 0; g_loss_denom = 0;
+    RefModel *h = (RefModel *)calloc(1, sizeof(RefModel));
+    h->c = gC; h->N = B * T;
+    h->np = calc_offsets(&gC, &h->o);
+    h->P = (float *)calloc(h->np, 4);
+    h->G = (float *)calloc(h->np, 4);
+    h->tok = (int *)calloc(h->N, 4); h->tgt = (int *)calloc(h->N, 4);
+    rope_tables(&gC);
+    h->a = ga_new(h->N, 1);
+    h->a->tr = 1;
+    return h;
+}
+unsigned long long ref_model_np(void *hv) { return (unsigned long long)((RefModel *)hv)->np; }
+/* named buffers: the parameter and gradient vectors, the Qlm's state arrays, activations of layer l */
+void *ref_model_buf(void *hv, const char *name, int l)
+{
+    RefModel *h = (RefModel *)hv; GA *a = h->a;
+    if (!strcmp(name, "P")) return h->P;
+    if (!strcmp(name, "G")) return h->G;
+    if (!strcmp(name, "fn")) return a->fn;
+    if (!strcmp(name, "x_final")) return a->x_final;
+    if (!strcmp(name, "lossb")) return a->lossb;
+    if (!strcmp(name, "a_in")) return a->a_in[l];
+    if (!strcmp(name, "f_in")) return a->f_in[l];
+    if (!strcmp(name, "f_norm")) return a->f_norm[l];
+    if (!strcmp(name, "att")) return a->att[l];
+    if (!strcmp(name, "assign")) return a->assign[l];
+    if (!strcmp(name, "gate")) return a->gate[l];
+    if (!strcmp(name, "rprobs")) return a->rprobs[l];
+    if (!strcmp(name, "q.d")) return QQ.d;
+    if (!strcmp(name, "q.r")) return QQ.r;
+    if (!strcmp(name, "q.s")) return QQ.s;
+    if (!strcmp(name, "q.m8")) return QQ.m8;
+    if (!strcmp(name, "q.v8")) return QQ.v8;
+    if (!strcmp(name, "q.m8s")) return QQ.m8s;
+    if (!strcmp(name, "q.v8s")) return QQ.v8s;
+    if (!strcmp(name, "q.span")) return QQ.spanH;
+    if (!strcmp(name, "q.Mc")) return QQ.Mc;
+    if (!strcmp(name, "q.Vc")) return QQ.Vc;
+    return NULL;
+}
+/* nq, ngrp, nspan, nfloat of the Qlm that ref_model_qlm_init built */
+void ref_model_qlm_dims(unsigned long long *out4)
+{
+    out4[0] = QQ.nq; out4[1] = QQ.ngrp; out4[2] = (unsigned long long)QQ.nspan; out4[3] = QQ.nfloat;
+}
+/* cmd_train with CUDALM_QLM=1: quantise P in place (P becomes the rendered view s*d) */
+void ref_model_qlm_init(void *hv)
+{
+    RefModel *h = (RefModel *)hv;
+    gC = h->c;
+    qlm_gpu_init(&QQ, &h->c, &h->o, h->P, h->np);
+    g_qlm_on = 1; g_muon = 0; h->qlm = 1;
+}
+void ref_model_forward(void *hv, const int *tok)
+{
+    RefModel *h = (RefModel *)hv;
+    gC = h->c;
+    memcpy(h->tok, tok, (size_t)h->N * 4);
+    gpu_forward(h->P, &h->o, h->a, h->tok);
+}
+/* mean cross-entropy of the last forward (gpu_loss; perpos = N floats or NULL) */
+double ref_model_loss(void *hv, const int *tgt, float *perpos)
+{
+    RefModel *h = (RefModel *)hv;
+    memcpy(h->tgt, tgt, (size_t)h->N * 4);
+    return gpu_loss(h->P, &h->o, h->a, h->tgt, h->N, perpos);
+}
+/* gpu_backward after ref_model_forward on the same tokens; returns the mean of the per-row losses the head wrote */
+double ref_model_backward(void *hv, const int *tgt)
+{
+    RefModel *h = (RefModel *)hv;
+    memcpy(h->tgt, tgt, (size_t)h->N * 4);
+    gpu_backward(h->P, h->G, &h->o, h->a, h->tok, h->tgt);
+    double s = 0; for (int i = 0; i < h->N; i++) s += h->a->lossb[i];
+    return s / h->N;
+}
+/* gpu_adam; returns its own return value (0 = step skipped on a non-finite norm); gn = the norm it read back */
+int ref_model_adam(void *hv, float lr, int t, float *gn)
+{
+    RefModel *h = (RefModel *)hv;
+    int ok = gpu_adam(h->P, h->G, NULL, NULL, h->np, lr, t);
+    if (gn) *gn = g_gn;
+    return ok;
+}
+
 /* ---- QLMH optimizer-state file (qlm.cuh:703-788), on caller-owned host arrays ---- */
 static void fill_qlm(Qlm *q, int dmax, int group, int adam, int packed, QSpanD *spans, int nspan,
                      unsigned long long nq, unsigned long long ngrp, unsigned long long nfloat,

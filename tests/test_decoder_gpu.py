@@ -46,6 +46,33 @@ def test_decoder_matches_full_forward(cuda):
     assert torch.equal(dec.otok.long(), dec.logits.argmax(-1))
 
 
+def test_slot_past_its_cache_is_reported_not_written(cuda):
+    """Positions live on the device: a slot whose position equals the cache length must not touch the cache, the
+    score buffer or the rotation tables.  The kernels skip it and leave error 201 in the device error word."""
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import model
+    cfg = model.Config(L=1, D=128, H=2, KV=2, hd=64, E=4, K=2, F=128, V=256, T=64, B=2)
+    m = model.QlmModel(cfg, cuda, seed=6)
+    dec = model.Decoder(m, 2, 32)
+    g = torch.Generator(device="cpu"); g.manual_seed(2)
+    ids = torch.randint(0, cfg.V, (2, 8), generator=g, dtype=torch.int32).to(cuda)
+    dec.prefill(ids)
+    dec.step()
+    torch.cuda.synchronize()
+    q.check(q.lib().qlmb_check_device(None))
+    K0, V0 = dec.K[0].clone(), dec.V[0].clone()
+    dec.pos2.fill_(32)                                   # one past the last cache position
+    dec.step(advance=False)
+    torch.cuda.synchronize()
+    assert q.lib().qlmb_check_device(None) == 4          # QLMB_E_DEVICE
+    assert b"error code 201" in q.lib().qlmb_last_error()
+    assert torch.equal(K0, dec.K[0]) and torch.equal(V0, dec.V[0])
+    dec.pos2.fill_(9)
+    dec.step()                                           # the context is intact: the next step runs
+    torch.cuda.synchronize()
+    q.check(q.lib().qlmb_check_device(None))
+
+
 def test_sampler_topk_topp_temperature(cuda):
     """k_dec_sample (cudalm.cu:7048-7108) against a float64 restatement of its algorithm: arg-max and
     log-probability, the top-k / top-p cut, and the pick that the (seed, step) hash selects from the tempered

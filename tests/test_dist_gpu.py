@@ -1,7 +1,10 @@
 """Expert-parallel layer, in both forms (split C-ABI calls + NCCL all-to-all; peer loads
 inside the row kernels, no exchange step), against the
-single-call layer with the same weights and tokens.  Runs on every visible GPU
-(1, or 2 when the box has them): rows of an expert GEMM are independent, so the
+single-call layer with the same weights and tokens; the data-parallel training step against
+the single-GPU step on the concatenated batch; the sharded (ZeRO-1) integer AdamW against the
+whole-state step.  These need two GPUs and are SKIPPED on a one-GPU box (a run with one rank
+would compare the single-GPU code with itself); `*_one_rank` keeps a smoke run of the
+multi-rank code paths with world = 1.  Rows of an expert GEMM are independent, so the
 layer output and the input gradient must be bit-identical to the single-GPU
 result; weight gradients are sums over rows in another order (1e-2)."""
 import os
@@ -14,6 +17,12 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 CFG = dict(N=1024, D=256, F=512, E=8, K=2)
+
+
+def two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs: %d visible (not run, which is not a pass)" % torch.cuda.device_count())
+    return 2
 
 
 def free_port():
@@ -72,8 +81,17 @@ def worker(rank, world, port, ret, mode, cfg=None):
 
 
 @pytest.mark.parametrize("mode", ["nccl", "peer"])
+def test_expert_parallel_one_rank(cuda, mode):
+    """World = 1: the split calls and the window code run, nothing crosses a GPU."""
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(worker, args=(1, free_port(), ret, mode, dict(N=256, D=128, F=128, E=4, K=2)), nprocs=1, join=True)
+        assert ret.get(0)
+
+
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
 def test_expert_parallel_matches_single_call(cuda, mode):
-    world = min(torch.cuda.device_count(), 2)
+    world = two_gpus()
     with mp.Manager() as m:
         ret = m.dict()
         mp.spawn(worker, args=(world, free_port(), ret, mode), nprocs=world, join=True)
@@ -82,7 +100,7 @@ def test_expert_parallel_matches_single_call(cuda, mode):
 
 def test_expert_parallel_small_layer(cuda):
     """The peer form on the smallest layer the training-step test uses (256 tokens, 4 experts of 128 x 128)."""
-    world = min(torch.cuda.device_count(), 2)
+    world = two_gpus()
     with mp.Manager() as m:
         ret = m.dict()
         mp.spawn(worker, args=(world, free_port(), ret, "peer", dict(N=256, D=128, F=128, E=4, K=2)), nprocs=world, join=True)
@@ -143,8 +161,51 @@ def worker_dp(rank, world, port, ret):
 
 
 def test_data_parallel_training_step(cuda):
-    world = min(torch.cuda.device_count(), 2)
+    world = two_gpus()
     with mp.Manager() as m:
         ret = m.dict()
         mp.spawn(worker_dp, args=(world, free_port(), ret), nprocs=world, join=True)
+        assert all(ret.get(r) for r in range(world))
+
+
+def worker_zero1(rank, world, port, ret):
+    """ZeRO-1 form of the integer AdamW: rank r steps its share of the groups of one span and the state is
+    all-gathered; every gathered array must equal the whole-span step's bytes (the rounding hash uses global
+    element indices, so the split cannot show)."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from cudalm_c_b200 import qlm
+    n = 128 * 65536
+    ngrp = n // 128
+    per = ngrp // world
+    gen = torch.Generator(device=dev); gen.manual_seed(5)          # same seed: every rank holds the same P and G
+    P = torch.randn(n, device=dev, generator=gen) * 0.02
+    whole = qlm.Qlm([(0, n)], n, dev); whole.init_from(P.clone(), render=False)
+    shard = qlm.Qlm([(0, n)], n, dev); shard.init_from(P.clone(), render=False)
+    gi0 = rank * per
+    for t in range(1, 4):
+        G = torch.randn(n, device=dev, generator=gen) * 1e-3
+        whole.step(None, G, 3e-4, 0.9, 0.95, 0.1, t)
+        shard.step(None, G, 3e-4, 0.9, 0.95, 0.1, t, gi_base=gi0, ng=per)
+        e0, e1 = gi0 * 128, (gi0 + per) * 128
+        dist.all_gather_into_tensor(shard.d[:n // 2], shard.d[e0 // 2:e1 // 2].clone())
+        for a in (shard.r, shard.m8, shard.v8):
+            dist.all_gather_into_tensor(a[:n], a[e0:e1].clone())
+        for a in (shard.m8s, shard.v8s):
+            dist.all_gather_into_tensor(a, a[gi0:gi0 + per].clone())
+        torch.cuda.synchronize()
+        for k in ("d", "r", "m8", "v8", "m8s", "v8s"):
+            assert torch.equal(getattr(whole, k), getattr(shard, k)), (k, t)
+    ret[rank] = True
+    dist.destroy_process_group()
+
+
+def test_zero1_sharded_state_equals_whole(cuda):
+    world = two_gpus()
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(worker_zero1, args=(world, free_port(), ret), nprocs=world, join=True)
         assert all(ret.get(r) for r in range(world))

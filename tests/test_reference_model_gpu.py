@@ -1,0 +1,253 @@
+"""The composed training step and the decoder against the REFERENCE ITSELF: its CPU build (compiled from its own
+sources into oracle/_ref) runs gpu_forward, gpu_loss, gpu_backward and gpu_adam with QLM on (cudalm.cu:5736-6002,
+6438-6465, 8834-8847; set up as cmd_train does, 8223-8226, 8301) on the same parameter vector and the same tokens.
+
+Bars (the ones the hot path's specification states): initial 4-bit state bit-exact; mean loss within 1e-3; every
+gradient tensor within 2e-2 relative (bf16 activations on the device, fp32 on the CPU); with the reference's own
+gradients fed to the device optimizer, all seven integer state arrays and the float spans bit-exact after the step;
+logits within 5e-2 of the reference's full forward (the bar of its `decheck`, cudalm.cu:7233-7253).
+
+Expert choices: the device's bf16 activations move the router's logits by a few 1e-3, which decides a near-tie
+between the second and third expert of a token differently from the fp32 CPU build for a few per cent of the
+tokens.  The loss bar is checked with the device's own routing; gradients and logits are compared on identical
+routing, by handing the device the reference's router probabilities (qlmb_moe_forward_routed)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref():
+    from oracle import loader
+    r = loader.reference(True)
+    if r is None:
+        pytest.skip("compiled reference not present (make -C oracle ref)")
+    return r
+
+
+def _init(np_total, o, c, seed):
+    """cmd_new's initialisation (cudalm.cu:7349-7365) on the host: N(0, 0.02), wo and w2 scaled by 1/sqrt(2L), gains 1."""
+    rng = np.random.default_rng(seed)
+    P = (rng.standard_normal(np_total) * 0.02).astype(np.float32)
+    sc = np.float32(1.0 / np.sqrt(2.0 * c.L))
+    for lo in o.layers:
+        for nm in ("wo", "w2"):
+            a, n = lo[nm]; P[a:a + n] *= sc
+        for nm in ("an1", "an2"):
+            a, n = lo[nm]; P[a:a + n] = 1.0
+    P[o.nf:o.nf + c.D] = 1.0
+    return P
+
+
+def _pair(cfg, cuda, seed, aux):
+    from cudalm_c_b200 import model
+    R = _ref()
+    rm = R.model_new(cfg.V, cfg.D, cfg.L, cfg.H, cfg.KV, cfg.F, cfg.T, cfg.E, cfg.K, cfg.B, aux=aux)
+    o = model.Offsets(cfg)
+    assert rm.np == o.total
+    P0 = _init(rm.np, o, cfg, seed)
+    rm.P[:] = P0
+    q = rm.qlm_init()
+    m = model.QlmModel(cfg, cuda, aux=aux, P_init=torch.from_numpy(P0).to(cuda))
+    return rm, q, m
+
+
+def _ref_routing(rm, cfg, cuda):
+    """log of the reference's router probabilities per layer: logits that reproduce its expert choice and gates."""
+    N = cfg.B * cfg.T
+    return [torch.from_numpy(np.log(rm.buf("rprobs", (N, cfg.E), l=l))).to(cuda) for l in range(cfg.L)]
+
+
+def _state_equal(m, q):
+    Q = m.q
+    assert np.array_equal(Q.d.cpu().numpy()[:q["nq"] // 2], q["d"]), "digits"
+    assert np.array_equal(Q.r.cpu().numpy()[:q["nq"]], q["r"]), "residuals"
+    assert np.array_equal(Q.s.cpu().numpy(), q["s"]), "scales"
+    assert np.array_equal(Q.m8.cpu().numpy()[:q["nq"]], q["m8"]), "m8"
+    assert np.array_equal(Q.v8.cpu().numpy()[:q["nq"]], q["v8"]), "v8"
+    assert np.array_equal(Q.m8s.cpu().numpy(), q["m8s"]), "m8s"
+    assert np.array_equal(Q.v8s.cpu().numpy(), q["v8s"]), "v8s"
+
+
+@pytest.mark.parametrize("shape", ["small", "mid"])
+def test_step_matches_reference(cuda, shape):
+    import cudalm_c_b200 as qb
+    from cudalm_c_b200 import model
+    if shape == "small":
+        cfg, aux = model.Config(L=2, D=128, H=2, KV=2, hd=64, E=4, K=2, F=128, V=256, T=128, B=2), 0.03
+    else:
+        cfg, aux = model.Config(L=2, D=768, H=12, KV=12, hd=64, E=32, K=2, F=1536, V=4096, T=256, B=1), 0.0
+    rm, q, m = _pair(cfg, cuda, seed=11, aux=aux)
+    # qlm_gpu_init: same spans, same frozen reference scales, same codes
+    assert np.array_equal(m.q.spanH["sref"], q["sp"]["sref"])
+    for f in ("pof", "gof", "qi0", "n", "gi0", "ngrp"):
+        assert np.array_equal(m.q.spanH[f], q["sp"][f]), f
+    _state_equal(m, q)
+    rng = np.random.default_rng(5)
+    N = cfg.B * cfg.T
+    tok = rng.integers(0, cfg.V, N).astype(np.int32); tgt = rng.integers(0, cfg.V, N).astype(np.int32)
+    # ---- forward + loss
+    rm.forward(tok)
+    ref_loss = rm.loss(tgt)
+    d_tok, d_tgt = torch.from_numpy(tok).to(cuda), torch.from_numpy(tgt).to(cuda)
+    m.forward(d_tok)
+    agree = np.mean([np.mean(np.sort(m.layers[l]["moe"].member("assign", (cfg.K, N), torch.int32).cpu().numpy(), 0)
+                             == np.sort(rm.buf("assign", (cfg.K, N), np.int32, l=l), 0)) for l in range(cfg.L)])
+    loss = m.backward(d_tok, d_tgt)
+    torch.cuda.synchronize()
+    qb.check(qb.lib().qlmb_check_device(None))
+    mine = float(loss.double().mean())
+    print("own routing: loss device %.6f reference %.6f |delta| %.2e, expert choices equal %.2f %%"
+          % (mine, ref_loss, abs(mine - ref_loss), 100 * agree))
+    assert abs(mine - ref_loss) < 1e-3
+    assert agree > 0.9
+    # ---- the same step on the reference's routing: loss again, then every gradient tensor
+    m.forward(d_tok, route_logits=_ref_routing(rm, cfg, cuda))
+    for l in range(cfg.L):
+        assert np.array_equal(m.layers[l]["moe"].member("assign", (cfg.K, N), torch.int32).cpu().numpy(),
+                              rm.buf("assign", (cfg.K, N), np.int32, l=l))
+    loss = m.backward(d_tok, d_tgt)
+    torch.cuda.synchronize()
+    mine = float(loss.double().mean())
+    print("reference routing: loss device %.6f reference %.6f |delta| %.2e" % (mine, ref_loss, abs(mine - ref_loss)))
+    assert abs(mine - ref_loss) < 1e-3
+    assert abs(rm.backward(tgt) - ref_loss) < 1e-6
+    o = m.o
+    names = [("emb", o.emb, cfg.V * cfg.D), ("nf", o.nf, cfg.D)]
+    for l, lo in enumerate(o.layers):
+        names += [("%s[%d]" % (nm, l), lo[nm][0], lo[nm][1]) for nm in lo]
+    G = m.G.cpu().numpy().astype(np.float64)
+    worst = ("", 0.0)
+    for nm, a, n in names:
+        ref = rm.G[a:a + n].astype(np.float64)
+        rel = float(np.linalg.norm(G[a:a + n] - ref) / max(np.linalg.norm(ref), 1e-30))
+        if rel > worst[1]:
+            worst = (nm, rel)
+        assert rel < 2e-2, (nm, rel)
+    print("worst relative gradient error %.3e (%s)" % (worst[1], worst[0]))
+    # ---- optimizer: the reference's gradients through the device update must leave the reference's bytes
+    m.G.copy_(torch.from_numpy(rm.G).to(cuda))
+    ok, gn = rm.adam(3e-4, 1)
+    assert ok == 1
+    m.update(lr=3e-4, b1=0.9, b2=0.95, wd=0.1, wdf=0.1)
+    torch.cuda.synchronize()
+    assert float(m.gs[1]) == gn
+    _state_equal(m, q)
+    for (off, n, cs), pt in zip(m.q.fs, m.fp):
+        assert np.array_equal(pt.cpu().numpy(), rm.P[off:off + n]), "float span at %d" % off
+        assert np.array_equal(m.q.Mc[cs:cs + n].cpu().numpy().view(np.uint16), q["Mc"][cs:cs + n])
+        assert np.array_equal(m.q.Vc[cs:cs + n].cpu().numpy().view(np.uint16), q["Vc"][cs:cs + n])
+    # the rendered view the reference keeps in P equals scale * digit of the device state
+    Pd = m.params().cpu().numpy()
+    assert np.array_equal(Pd, rm.P)
+
+
+def test_nonfinite_norm_skips_the_step(cuda):
+    """gpu_adam returns 0 and changes nothing when the gradient norm is not finite (cudalm.cu:6446-6447).  The
+    failure is injected on the host: one NaN written into G."""
+    import ctypes as C
+    import cudalm_c_b200 as qb
+    from cudalm_c_b200 import model
+    cfg = model.Config(L=1, D=128, H=2, KV=2, hd=64, E=4, K=2, F=128, V=256, T=128, B=1)
+    rm, q, m = _pair(cfg, cuda, seed=3, aux=0.0)
+    rng = np.random.default_rng(1)
+    g = (rng.standard_normal(rm.np) * 1e-3).astype(np.float32)
+    g[m.o.layers[0]["w1"][0] + 17] = np.nan
+    rm.G[:] = g
+    m.G.copy_(torch.from_numpy(g).to(cuda))
+    before_ref = {k: q[k].copy() for k in ("d", "r", "m8", "v8", "m8s", "v8s")}
+    ok, gn = rm.adam(3e-4, 1)
+    assert ok == 0 and not np.isfinite(gn)
+    for k, v in before_ref.items():
+        assert np.array_equal(q[k], v)
+    cnt = C.c_ulonglong(0)
+    qb.check(qb.lib().qlmb_skipped_steps(C.byref(cnt), 1, None))
+    snap = [t.clone() for t in (m.q.d, m.q.r, m.q.s, m.q.m8, m.q.v8, m.q.m8s, m.q.v8s, m.q.Mc, m.q.Vc)] + [t.clone() for t in m.fp]
+    m.update(lr=3e-4, wdf=0.1)
+    torch.cuda.synchronize()
+    now = [m.q.d, m.q.r, m.q.s, m.q.m8, m.q.v8, m.q.m8s, m.q.v8s, m.q.Mc, m.q.Vc] + list(m.fp)
+    for a, b in zip(snap, now):
+        assert torch.equal(a, b)
+    qb.check(qb.lib().qlmb_skipped_steps(C.byref(cnt), 1, None))
+    assert cnt.value == 1
+    _state_equal(m, q)
+    # the next, finite step runs and matches the reference again
+    g[np.isnan(g)] = 0.0
+    rm.G[:] = g
+    m.G.copy_(torch.from_numpy(g).to(cuda))
+    ok, gn = rm.adam(3e-4, 2)
+    m.update(lr=3e-4, wdf=0.1)
+    torch.cuda.synchronize()
+    assert ok == 1
+    _state_equal(m, q)
+    qb.check(qb.lib().qlmb_skipped_steps(C.byref(cnt), 0, None))
+    assert cnt.value == 0
+
+
+def test_bounded_wait_reports_and_the_device_stays_usable(cuda):
+    """A wait that nothing ends runs out after its poll limit, leaves an error code in the device error word and
+    returns; qlmb_check_device reports it once, and later launches work."""
+    import cudalm_c_b200 as qb
+    L = qb.lib()
+    qb.check(L.qlmb_check_device(None))
+    qb.check(L.qlmb_selftest_wait_expires(1024, None))
+    assert L.qlmb_check_device(None) == 4                       # QLMB_E_DEVICE
+    assert b"site 9999" in L.qlmb_last_error()
+    assert L.qlmb_check_device(None) == 0
+    x = torch.arange(1024, device=cuda, dtype=torch.float32)
+    gs = qb.qlm.gnorm(x)
+    torch.cuda.synchronize()
+    assert abs(float(gs[1]) - float(np.sqrt((np.arange(1024.0) ** 2).sum()))) < 1e-2
+
+
+def test_decoder_matches_reference_forward(cuda):
+    """Config 5's oracle: the reference's full forward over prompt + continuation (teacher forcing), B = 8 slots,
+    a cache of 1024 positions, the model's full width.  Chain of checks: (1) the device's full forward on the
+    reference's routing against the reference's logits, 5e-2 everywhere; (2) the K/V-cached decoder's per-step
+    logits against the device's own full forward (own routing on both sides), 5e-2 everywhere: the reference's
+    `decheck`; (3) the decoder against the reference directly: rows whose experts all agree must meet 5e-2 too,
+    which shows as a large share of rows within the bar and an equal arg-max almost everywhere."""
+    import cudalm_c_b200 as qb
+    from cudalm_c_b200 import block, model
+    B, n, k = 8, 96, 32
+    T = n + k
+    cfg = model.Config(L=2, D=768, H=12, KV=12, hd=64, E=32, K=2, F=1536, V=4096, T=T, B=B)
+    rm, q, m = _pair(cfg, cuda, seed=21, aux=0.0)
+    rng = np.random.default_rng(9)
+    ids = rng.integers(0, cfg.V, (B, T)).astype(np.int32)
+    fn = rm.forward(ids.reshape(-1))
+    emb = rm.P[:cfg.V * cfg.D].reshape(cfg.V, cfg.D)
+    ref = (fn.astype(np.float64) @ emb.astype(np.float64).T).reshape(B, T, cfg.V)
+    d_ids = torch.from_numpy(ids).to(cuda)
+    emb_bf, _ = block.cast_bf16(m.emb)
+    # (1) full forward, reference routing
+    fn_d = m.forward(d_ids.reshape(-1).contiguous(), route_logits=_ref_routing(rm, cfg, cuda))
+    full_r = block.gemm_nt(fn_d, emb_bf, torch.float32).view(B, T, cfg.V).double().cpu().numpy()
+    w1 = float(np.abs(full_r - ref).max())
+    print("full forward (reference routing) vs reference: worst |dlogit| %.3e" % w1)
+    assert w1 < 5e-2
+    # (2) decoder vs the device's own full forward
+    fn_o = m.forward(d_ids.reshape(-1).contiguous())
+    full_o = block.gemm_nt(fn_o, emb_bf, torch.float32).view(B, T, cfg.V).double().cpu().numpy()
+    m.saved = None
+    dec = model.Decoder(m, B, 1024)
+    rows = [dec.prefill(d_ids[:, :n].contiguous()).double().cpu().numpy()]
+    for j in range(k):
+        dec.tok.copy_(d_ids[:, n + j])
+        rows.append(dec.step(advance=False).double().cpu().numpy())
+        dec.advance()
+    torch.cuda.synchronize()
+    qb.check(qb.lib().qlmb_check_device(None))
+    got = np.stack(rows, 1)                                        # [B, k + 1, V]: positions n-1 .. n+k-1
+    want_o, want_r = full_o[:, n - 1:], ref[:, n - 1:]
+    w2 = float(np.abs(got - want_o).max())
+    am2 = float(np.mean(got.argmax(-1) == want_o.argmax(-1)))
+    print("decoder vs own full forward: worst |dlogit| %.3e, arg-max equal %.1f %%" % (w2, 100 * am2))
+    assert w2 < 5e-2 and am2 == 1.0
+    # (3) decoder vs the reference
+    err = np.abs(got - want_r).max(-1)
+    inside = float(np.mean(err < 5e-2)); am3 = float(np.mean(got.argmax(-1) == want_r.argmax(-1)))
+    print("decoder vs reference: rows within 5e-2: %.1f %%, median %.3e, worst %.3e, arg-max equal %.1f %%"
+          % (100 * inside, float(np.median(err)), float(err.max()), 100 * am3))
+    assert inside > 0.5 and float(np.median(err)) < 5e-2 and am3 > 0.9

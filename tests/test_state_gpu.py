@@ -172,6 +172,43 @@ def test_config3_full_size_properties(cuda):
     assert torch.equal(R, P)
 
 
+def test_config3_ten_steps_match_reference(cuda):
+    """BASELINE config 3 as written: a flat span of 125 829 120 parameters ~ N(0, 0.02) encoded by the reference,
+    moments from zero, ten steps with a fresh seeded gradient ~ N(0, 1e-3) each (lr 3e-4, betas 0.9 / 0.95,
+    wd 0.1, relative learning rate against the frozen mean scale).  After every step the digits, residuals, both
+    moment arrays and their scales must equal the compiled reference's (qlm_step_launch of its CPU build) bit
+    for bit, and so must the fp32 view after the last one."""
+    ref = loader.reference(True)
+    if ref is None:
+        pytest.skip("compiled reference not present (make -C oracle ref)")
+    n = 125829120
+    rng = np.random.default_rng(2024)
+    P0 = rng.standard_normal(n, dtype=np.float32) * f32(0.02)
+    sp, nq, ng = loader.make_spans([n])
+    h = dict(d=np.zeros(n // 2, np.int8), r=np.zeros(n, np.int8), s=np.zeros(ng, np.float32), m8=np.zeros(n, np.int8),
+             v8=np.zeros(n, np.uint8), m8s=np.zeros(ng, np.float32), v8s=np.zeros(ng, np.float32))
+    ref.encode(P0, h["d"], h["r"], h["s"], sp)
+    st = DevState(cuda, [n], 128, 7, 1)
+    st.encode(dev(P0, cuda))
+    sref = f32(np.cumsum(h["s"].astype(np.float64))[-1] / float(ng))       # qlm_gpu_init's double mean (qlm.cuh:528-533)
+    sp[0]["sref"] = sref; st.sp[0]["sref"] = sref; st.push_spans()
+    for k in ("d", "r", "s"):
+        assert torch.equal(getattr(st, k), dev(h[k], cuda)), ("encode", k)
+    Ph = P0                                                                # the reference renders into it
+    P = torch.zeros(n, device=cuda)
+    G = torch.empty(n, device=cuda)
+    for t in range(1, 11):
+        Gh = rng.standard_normal(n, dtype=np.float32) * f32(1e-3)
+        bc1 = f32(1) - f32(np.power(f32(0.9), f32(t))); bc2 = f32(1) - f32(np.power(f32(0.95), f32(t)))
+        ref.step(Ph, Gh, h["d"], h["r"], h["s"], h["m8"], h["m8s"], h["v8"], h["v8s"], sp, lr=3e-4, b1=0.9, b2=0.95, wd=0.1,
+                 inv_bc1=float(f32(1) / bc1), inv_sqrt_bc2=float(f32(1) / np.sqrt(bc2)), t=t)
+        G.copy_(torch.from_numpy(Gh))
+        st.step(P if t == 10 else None, G, t)
+        for k in ("d", "r", "m8", "v8", "m8s", "v8s"):
+            assert torch.equal(getattr(st, k), dev(h[k], cuda)), (k, t)
+    assert torch.equal(P, dev(Ph, cuda))
+
+
 def test_empty_and_bad_arguments(cuda):
     import cudalm_c_b200 as q
     st = DevState(cuda, [256], 128, 7, 1)
