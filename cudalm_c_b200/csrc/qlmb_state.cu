@@ -409,6 +409,194 @@ __global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
     st_vec<EPL>(a.v8 + qe, vo);
 }
 
+// ------------------------------------------------------- packed step, group 128
+// The same arithmetic as k_step_fast, operation for operation and rounding for rounding, written for the
+// instruction-issue limit that bounds this kernel (it is not the memory system: the update needs three 64-bit
+// hashes, three stochastic roundings, three divisions and a square root per element).  What changes is only how
+// many instructions carry the work:
+//  * floating-point work runs on PAIRS of elements with the sm_100 two-wide fp32 instructions (__fadd2_rn,
+//    __fmul2_rn, __ffma2_rn: each lane of a pair is an IEEE round-to-nearest operation, so results are those
+//    of the scalar sequence);
+//  * small integers live in floats (exactly representable), so bytes and nibbles are unpacked and packed with
+//    byte permutes and a magic-number add instead of integer<->float conversions;
+//  * x / ms and x / vs (one denominator per group) use the correctly rounded reciprocal r = RN(1 / y) computed
+//    once per group: q0 = x*r, two residual corrections q <- q + (x - q*y)*r.  With r correctly rounded and q
+//    faithful after the first correction, the second one returns RN(x / y) (Markstein's theorem), as long as no
+//    intermediate underflows: the path is taken only for y in [2^-40, 1]; below |x| = 2^-100 the quotient is so
+//    small that only its sign and whether it is zero reach the rounding, and both are preserved.  Any other
+//    group divides with the IEEE operator;
+//  * the carry c with rr - 128c in [-64, 64] (rr = +-64 does not carry) is RN((rr -+ 1/2) / 128), which has no
+//    ties, taken with the magic-number add;
+//  * the hash is written on 32-bit halves (one widening multiply and two multiply-adds per 64-bit product).
+// Element values that cannot take this path (|L*8 + dec*7| >= 2^20, a short or unaligned group) go through the
+// generic team walk.
+__device__ __forceinline__ uint32_t mix32(uint64_t x)
+{
+    // x already holds key + 0x9E3779B97F4A7C15; returns the low 32 bits of the splitmix64 finaliser (qlm.cuh:78-82)
+    uint32_t lo = (uint32_t)x, hi = (uint32_t)(x >> 32);
+    lo ^= __funnelshift_r(lo, hi, 30); hi ^= hi >> 30;
+    uint64_t p = (uint64_t)lo * 0x1CE4E5B9u;
+    hi = (uint32_t)(p >> 32) + lo * 0xBF58476Du + hi * 0x1CE4E5B9u;
+    lo = (uint32_t)p;
+    lo ^= __funnelshift_r(lo, hi, 27); hi ^= hi >> 27;
+    p = (uint64_t)lo * 0x133111EBu;
+    hi = (uint32_t)(p >> 32) + lo * 0x94D049BBu + hi * 0x133111EBu;
+    lo = (uint32_t)p;
+    return lo ^ __funnelshift_r(lo, hi, 31);
+}
+__device__ __forceinline__ float2 bc2(float x) { return make_float2(x, x); }
+// floor(v) + [24-bit draw < frac(v)] for a pair, as floats (qsri, qlm.cuh:83-87)
+__device__ __forceinline__ float2 sround_pair(float2 v, uint32_t h0, uint32_t h1)
+{
+    const float2 fl = make_float2(floorf(v.x), floorf(v.y));
+    const float2 fr = __ffma2_rn(fl, bc2(-1.0f), v);                  // v - fl, one rounding
+    const float2 y = __fmul2_rn(fr, bc2(16777216.0f));                // u * 2^-24 < fr  <=>  (h >> 8) < fr * 2^24 (both exact)
+    const float p0 = (float)(h0 >> 8) < y.x ? 1.0f : 0.0f, p1 = (float)(h1 >> 8) < y.y ? 1.0f : 0.0f;
+    return __fadd2_rn(fl, make_float2(p0, p1));
+}
+// x / y for a pair with one denominator; r = RN(1 / y)
+__device__ __forceinline__ float2 div_pair(float2 x, float y, float r, bool fast)
+{
+    if (!fast) return make_float2(x.x / y, x.y / y);
+    const float2 ny = bc2(-y), rr = bc2(r);
+    float2 q = __fmul2_rn(x, rr);
+    q = __ffma2_rn(__ffma2_rn(q, ny, x), rr, q);
+    q = __ffma2_rn(__ffma2_rn(q, ny, x), rr, q);
+    return q;
+}
+// byte-permute selector that replaces byte j of the first operand by the low byte of the second
+__host__ __device__ constexpr uint32_t ins_sel(int j) { return j == 0 ? 0x3214u : j == 1 ? 0x3240u : j == 2 ? 0x3410u : 0x4210u; }
+#define QLMB_MAGIC_RN 12582912.0f        // 1.5 * 2^23: adding it leaves the integer nearest to x in the low mantissa bits
+#define QLMB_MAGIC_U 8388608.0f          // 2^23 under a byte: as_float(0x4B000000 | b) = 2^23 + b
+
+template <bool WRITE_P>
+__global__ void __launch_bounds__(256) k_step_pk(const __grid_constant__ StepArgs a)
+{
+    constexpr int EPL = 8, TEAM = 16, NP = EPL / 2;
+    if (step_is_skipped(a)) return;
+    const int lane = threadIdx.x & 31, tl = lane % TEAM, team = lane / TEAM;
+    const unsigned tmask = 0xffffu << (team * TEAM);
+    const long long w = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * 2 + team;
+    if (w >= a.ng) return;
+    const int gi = a.gi_base + (int)w;
+    uint64_t j0; int n;
+    const int si = locate_group(a.sp, a.nspan, gi, 128, j0, n);
+    const qlmb_span &S = a.sp[si];
+    const uint64_t q0 = S.qi0 + j0, p0 = S.pof + j0, g0 = S.gof + j0;
+    const float sg = a.s[gi];
+    const float L = a.lr * 128.0f / (a.lrmode ? sg : S.sref);
+    const float dec = a.lr * a.wd * 128.0f;
+    if (n != 128 || (q0 & 15) || (g0 & 3) || (WRITE_P && (p0 & 3)) || !(fabsf(L) * 8.0f + fabsf(dec) * 7.0f < 1048576.0f)) {
+        step_group_team<TEAM>(a, gi, tl, tmask);
+        return;
+    }
+    const uint64_t qe = q0 + (uint64_t)tl * EPL;
+    const float4 *gp = reinterpret_cast<const float4 *>(a.G + g0 + tl * EPL);
+    const float4 ga = __ldcs(gp), gb = __ldcs(gp + 1);
+    const uint2 rw = *reinterpret_cast<const uint2 *>(a.r + qe);
+    const uint2 mw = *reinterpret_cast<const uint2 *>(a.m8 + qe);
+    const uint2 vw = *reinterpret_cast<const uint2 *>(a.v8 + qe);
+    const uint32_t dw = *reinterpret_cast<const uint32_t *>(a.d + (qe >> 1));
+    const float gs = a.gsp ? *a.gsp : a.gscale;
+    const float ms_old = a.m8s[gi], vs_old = a.v8s[gi];
+    const float omb1 = 1.0f - a.b1, omb2 = 1.0f - a.b2;
+    const float veps = fmaxf(vs_old, 1e-8f), dmaxf = (float)a.dmax;
+    // keys: element index term of this lane + the three step terms (the finaliser's first add is folded in)
+    const uint64_t kbase = qe * QLMB_HASH_I + 0x9E3779B97F4A7C15ULL;
+    const uint64_t kd = kbase + a.t * QLMB_HASH_T, km = kbase + (a.t + 0x5EEDULL) * QLMB_HASH_T,
+                   kv = kbase + (a.t + 0xBEEFULL) * QLMB_HASH_T;
+
+    const float2 g2[NP] = {make_float2(ga.x, ga.y), make_float2(ga.z, ga.w), make_float2(gb.x, gb.y), make_float2(gb.z, gb.w)};
+    // bytes -> floats: signed bytes are biased by 128 first, nibbles by 8
+    const uint32_t rx[2] = {rw.x ^ 0x80808080u, rw.y ^ 0x80808080u}, mx[2] = {mw.x ^ 0x80808080u, mw.y ^ 0x80808080u};
+    const uint32_t vx[2] = {vw.x, vw.y};
+    const uint32_t dx = dw ^ 0x88888888u, dev = dx & 0x0F0F0F0Fu, dod = (dx >> 4) & 0x0F0F0F0Fu;
+    float2 mn[NP], rv[NP];
+    float am = 0.0f, vm = 0.0f;
+    uint32_t rout[2] = {0u, 0u}, dout = 0u;
+    float4 pv[2];
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        const int e0 = 2 * p, wd_ = e0 >> 2, b0 = e0 & 3;            // word and byte of the pair's first element
+        auto byte2 = [&](const uint32_t *src, float bias) {
+            const float x0 = __uint_as_float(__byte_perm(src[wd_], 0x4B000000u, 0x7440 + b0));
+            const float x1 = __uint_as_float(__byte_perm(src[wd_], 0x4B000000u, 0x7441 + b0));
+            return __fadd2_rn(make_float2(x0, x1), bc2(bias));
+        };
+        const float2 rold = byte2(rx, -(QLMB_MAGIC_U + 128.0f)), m8f = byte2(mx, -(QLMB_MAGIC_U + 128.0f)), v8f = byte2(vx, -QLMB_MAGIC_U);
+        const float2 ddf = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(dev, 0x4B000000u, 0x7440 + p)),
+                                                  __uint_as_float(__byte_perm(dod, 0x4B000000u, 0x7440 + p))), bc2(-(QLMB_MAGIC_U + 8.0f)));
+        // moments (qlm.cuh:206-222)
+        const float2 gr = __fmul2_rn(g2[p], bc2(gs));
+        const float2 mv = __fmul2_rn(m8f, bc2(ms_old));
+        const float2 sv = __fmul2_rn(v8f, bc2(vs_old));
+        float2 vv = __fmul2_rn(sv, sv);
+        mn[p] = __fadd2_rn(__fmul2_rn(bc2(a.b1), mv), __fmul2_rn(bc2(omb1), gr));
+        vv = __fadd2_rn(__fmul2_rn(bc2(a.b2), vv), __fmul2_rn(__fmul2_rn(bc2(omb2), gr), gr));
+        rv[p] = make_float2(sqrtf(vv.x), sqrtf(vv.y));
+        const float2 num = __fmul2_rn(mn[p], bc2(a.inv_bc1));
+        const float2 den = __fadd2_rn(__fmul2_rn(rv[p], bc2(a.inv_sqrt_bc2)), bc2(veps));
+        float2 u = make_float2(num.x / den.x, num.y / den.y);
+        u.x = fmaxf(-8.0f, fminf(8.0f, u.x)); u.y = fmaxf(-8.0f, fminf(8.0f, u.y));
+        am = fmaxf(am, fmaxf(fabsf(mn[p].x), fabsf(mn[p].y)));
+        vm = fmaxf(vm, fmaxf(rv[p].x, rv[p].y));
+        // digit and residual (qlm.cuh:231-242): -(L*u + dec*d), rounded stochastically, added to the residual
+        const float2 v = __fadd2_rn(__fmul2_rn(bc2(-L), u), __fmul2_rn(bc2(-dec), ddf));
+        const float2 idl = sround_pair(v, mix32(kd + (uint64_t)e0 * QLMB_HASH_I), mix32(kd + (uint64_t)(e0 + 1) * QLMB_HASH_I));
+        const float2 rr = __fadd2_rn(rold, idl);
+        const float2 half = make_float2(__uint_as_float(0xBB800000u ^ (__float_as_uint(rr.x) & 0x80000000u)),
+                                        __uint_as_float(0xBB800000u ^ (__float_as_uint(rr.y) & 0x80000000u)));   // -+ 2^-8
+        const float2 c = __fadd2_rn(__fadd2_rn(__ffma2_rn(rr, bc2(0.0078125f), half), bc2(QLMB_MAGIC_RN)), bc2(-QLMB_MAGIC_RN));
+        const float2 rnew = __ffma2_rn(c, bc2(-128.0f), rr);
+        float2 dn = __fadd2_rn(ddf, c);
+        dn.x = fminf(fmaxf(dn.x, -dmaxf), dmaxf); dn.y = fminf(fmaxf(dn.y, -dmaxf), dmaxf);
+        const float2 rb = __fadd2_rn(rnew, bc2(QLMB_MAGIC_RN)), db = __fadd2_rn(dn, bc2(QLMB_MAGIC_RN));
+        rout[wd_] = __byte_perm(rout[wd_], __float_as_uint(rb.x), ins_sel(b0));
+        rout[wd_] = __byte_perm(rout[wd_], __float_as_uint(rb.y), ins_sel(b0 + 1));
+        const uint32_t nb = (__float_as_uint(db.x) & 15u) | (__float_as_uint(db.y) << 4);
+        dout = __byte_perm(dout, nb, ins_sel(p));
+        if (WRITE_P) {
+            const float2 pp = __fmul2_rn(bc2(sg), dn);
+            if (p & 1) { pv[p >> 1].z = pp.x; pv[p >> 1].w = pp.y; } else { pv[p >> 1].x = pp.x; pv[p >> 1].y = pp.y; }
+        }
+    }
+    *reinterpret_cast<uint2 *>(a.r + qe) = make_uint2(rout[0], rout[1]);
+    *reinterpret_cast<uint32_t *>(a.d + (qe >> 1)) = dout;
+    if (WRITE_P) {
+        float4 *pp = reinterpret_cast<float4 *>(a.P + p0 + tl * EPL);
+        pp[0] = pv[0]; pp[1] = pv[1];
+    }
+#pragma unroll
+    for (int o = TEAM / 2; o > 0; o >>= 1) {
+        am = fmaxf(am, __shfl_xor_sync(tmask, am, o));
+        vm = fmaxf(vm, __shfl_xor_sync(tmask, vm, o));
+    }
+    const float ms = am > 0.0f ? am / 127.0f : 1e-12f;
+    const float vs = vm > 0.0f ? vm / 255.0f : 1e-12f;
+    if (tl == 0) { a.m8s[gi] = ms; a.v8s[gi] = vs; }
+    // 2^-40 <= y <= 1: the reciprocal path is exact there (see above); NaN fails both comparisons
+    const bool fm = ms >= 9.094947e-13f && ms <= 1.0f, fv = vs >= 9.094947e-13f && vs <= 1.0f;
+    const float rms = 1.0f / ms, rvs = 1.0f / vs;
+    uint32_t mo[2] = {0u, 0u}, vo[2] = {0u, 0u};
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        const int e0 = 2 * p, wd_ = e0 >> 2, b0 = e0 & 3;
+        const uint64_t ei = (uint64_t)e0 * QLMB_HASH_I, ej = (uint64_t)(e0 + 1) * QLMB_HASH_I;
+        float2 mq = sround_pair(div_pair(mn[p], ms, rms, fm), mix32(km + ei), mix32(km + ej));
+        mq.x = fminf(fmaxf(mq.x, -127.0f), 127.0f); mq.y = fminf(fmaxf(mq.y, -127.0f), 127.0f);
+        float2 vq = sround_pair(div_pair(rv[p], vs, rvs, fv), mix32(kv + ei), mix32(kv + ej));
+        // clamp to [0, 255]; a value that rounded to 0 while rv > 0 becomes 1 (qlm.cuh:275-277)
+        vq.x = fminf(fmaxf(vq.x, rv[p].x > 0.0f ? 1.0f : 0.0f), 255.0f); vq.y = fminf(fmaxf(vq.y, rv[p].y > 0.0f ? 1.0f : 0.0f), 255.0f);
+        const float2 mb = __fadd2_rn(mq, bc2(QLMB_MAGIC_RN)), vb = __fadd2_rn(vq, bc2(QLMB_MAGIC_U));
+        mo[wd_] = __byte_perm(mo[wd_], __float_as_uint(mb.x), ins_sel(b0));
+        mo[wd_] = __byte_perm(mo[wd_], __float_as_uint(mb.y), ins_sel(b0 + 1));
+        vo[wd_] = __byte_perm(vo[wd_], __float_as_uint(vb.x), ins_sel(b0));
+        vo[wd_] = __byte_perm(vo[wd_], __float_as_uint(vb.y), ins_sel(b0 + 1));
+    }
+    *reinterpret_cast<uint2 *>(a.m8 + qe) = make_uint2(mo[0], mo[1]);
+    *reinterpret_cast<uint2 *>(a.v8 + qe) = make_uint2(vo[0], vo[1]);
+}
+
 // ------------------------------------------------------------------ encode
 // One warp per group, lanes walk byte pairs (reference qlm.cuh:136-167).
 __global__ void __launch_bounds__(256) k_encode(const float *P, int8_t *d, int8_t *r, float *s,
@@ -662,7 +850,13 @@ extern "C" int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const f
     bool fast = group == 128 && packed && adam && !stat && !g_qv4 && al16(G) && al16(d) && al16(r) && al16(m8) &&
                 al16(v8) && (!P || al16(P));
     cudaStream_t st = as_stream(stream);
-    if (fast) {
+    static int impl = -1;
+    if (impl < 0) { const char *e = getenv("QLMB_STEP_IMPL"); impl = (e && !strcmp(e, "scalar")) ? 0 : 1; }
+    if (fast && impl == 1) {
+        // the packed form (two-wide fp32 instructions, reciprocal divisions); QLMB_STEP_IMPL=scalar keeps the older kernels
+        unsigned nb = (unsigned)((ng + 15) / 16);
+        if (P) k_step_pk<true><<<nb, 256, 0, st>>>(a); else k_step_pk<false><<<nb, 256, 0, st>>>(a);
+    } else if (fast) {
         // elements per lane: 8 by default (measured fastest); QLMB_STEP_EPL=4|16 selects the other forms
         static int epl = 0;
         if (!epl) { const char *e = getenv("QLMB_STEP_EPL"); epl = e ? atoi(e) : 8; if (epl != 4 && epl != 16) epl = 8; }
