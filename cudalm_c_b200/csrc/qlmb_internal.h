@@ -16,7 +16,8 @@ int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N,
 size_t perm_scratch_ints(int N, int E, int K, int merged);
 int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
                int *off, int *counts, int *bad_flag, int *tile_info, int *ntiles,
-               int *chunk_scratch, cudaStream_t st, int e_lo = 0, int skip = 0);
+               int *chunk_scratch, cudaStream_t st, int e_lo = 0, int skip = 0, int *rank_counts = nullptr,
+               int experts_per_rank = 0);
 
 // ---- row kernels (qlmb_dispatch.cu) ----
 int router_logits(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E,

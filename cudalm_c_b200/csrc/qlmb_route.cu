@@ -26,39 +26,6 @@ __device__ __forceinline__ float exp_poly(float x)
     return p * __uint_as_float((uint32_t)((int)k + 127) << 23);
 }
 
-// One thread per token (reference cudalm.cu:2515-2534).  The probabilities
-// live in rprobs (global, L1-resident) so any E up to 256 needs no local array.
-__global__ void __launch_bounds__(128) k_router_topk(const float *rt, float *rprobs, int *assign,
-                                                     float *gate, int N, int E, int K,
-                                                     const float *bias, int bs)
-{
-    int n = blockIdx.x * blockDim.x + threadIdx.x;
-    if (n >= N) return;
-    const float *lg = rt + (size_t)n * E;
-    float *pr = rprobs + (size_t)n * E;
-    float top = -1e30f;
-    for (int e = 0; e < E; e++) { float v = lg[e]; if (v > top) top = v; }
-    float sum = 0.0f;
-    for (int e = 0; e < E; e++) { float p = exp_poly(lg[e] - top); pr[e] = p; sum += p; }
-    float inv = 1.0f / sum;
-    for (int e = 0; e < E; e++) pr[e] *= inv;
-    int took[8];
-    for (int k = 0; k < K; k++) {
-        int pick = -1; float best = -1e30f;
-        for (int e = 0; e < E; e++) {
-            bool used = false;
-            for (int j = 0; j < k; j++) used |= (took[j] == e);
-            if (used) continue;
-            float sc = pr[e] + (bias ? bias[k * bs + e] : 0.0f);
-            if (sc > best) { best = sc; pick = e; }
-        }
-        if (pick < 0) pick = k;                     // NaN scores: stay in range
-        took[k] = pick;
-        assign[(size_t)k * N + n] = pick;
-        gate[(size_t)k * N + n] = pr[pick];
-    }
-}
-
 // Same arithmetic with one warp per token and lane = expert (E <= 32): the
 // maximum is order-free, the softmax sum is still taken in expert order (every
 // lane adds the 32 shuffled terms sequentially) and the K selection rounds are
@@ -97,6 +64,68 @@ __device__ __forceinline__ void router_topk_row(float lg, int n, int lane, float
         taken = taken || (lane == pick);
     }
 }
+// More than 32 experts (up to 256): still one warp per token, lane l holds experts l, l + 32, ... (EPT per lane).
+// The softmax sum runs over the experts in ascending order (the term of expert e is fetched from lane e % 32), as the
+// reference's CPU kernel adds them (cpu_kern.h:413-425); each selection round takes every lane's best unused expert
+// (lowest index on ties) and then the best over the lanes, again with the lowest index winning.
+template <int EPT>
+__global__ void __launch_bounds__(256) k_router_topk_wide(const float *rt, float *rprobs, int *assign, float *gate, int N,
+                                                          int E, int K, const float *bias, int bs)
+{
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float lg[EPT], pr[EPT];
+    float top = -1e30f;
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        const int e = j * 32 + lane;
+        lg[j] = e < E ? rt[(size_t)n * E + e] : -1e30f;
+        if (lg[j] > top) top = lg[j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        pr[j] = (j * 32 + lane < E) ? exp_poly(lg[j] - top) : 0.0f;
+        const int live = E - j * 32 < 32 ? E - j * 32 : 32;           // experts of this slice
+        for (int l = 0; l < live; l++) sum += __shfl_sync(0xffffffffu, pr[j], l);
+    }
+    const float inv = 1.0f / sum;
+    unsigned used = 0u;                                               // bit j: this lane's expert j * 32 + lane was picked
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        pr[j] *= inv;
+        if (j * 32 + lane < E) rprobs[(size_t)n * E + j * 32 + lane] = pr[j];
+    }
+    for (int k = 0; k < K; k++) {
+        float sc = 0.0f; int idx = 0x7fffffff; bool ok = false;
+#pragma unroll
+        for (int j = 0; j < EPT; j++) {
+            const int e = j * 32 + lane;
+            if (e >= E || ((used >> j) & 1u)) continue;
+            const float v = pr[j] + (bias ? bias[k * bs + e] : 0.0f);
+            if (v > -1e30f && (!ok || v > sc)) { sc = v; idx = e; ok = true; }      // ascending e: the first best stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float osc = __shfl_xor_sync(0xffffffffu, sc, o);
+            const int oidx = __shfl_xor_sync(0xffffffffu, idx, o);
+            const bool ook = __shfl_xor_sync(0xffffffffu, (int)ok, o) != 0;
+            if (ook && (!ok || osc > sc || (osc == sc && oidx < idx))) { sc = osc; idx = oidx; ok = true; }
+        }
+        const int pick = ok ? idx : k;                                // NaN scores: stay in range
+        float g = 0.0f;
+#pragma unroll
+        for (int j = 0; j < EPT; j++) {
+            const float v = __shfl_sync(0xffffffffu, pr[j], pick & 31);
+            if ((pick >> 5) == j) g = v;
+        }
+        if (lane == 0) { assign[(size_t)k * N + n] = pick; gate[(size_t)k * N + n] = g; }
+        if ((pick & 31) == lane) used |= 1u << (pick >> 5);
+    }
+}
+
 __global__ void __launch_bounds__(256) k_router_topk_warp(const float *rt, float *rprobs, int *assign,
                                                           float *gate, int N, int E, int K,
                                                           const float *bias, int bs)
@@ -153,157 +182,233 @@ __global__ void __launch_bounds__(256) k_router_small(float *rt, const void *X, 
 }
 
 // ------------------------------------------------------------- permutation
-// Stable counting sort in three launches (chunks of 1024 entries):
-//   hist    : per-chunk expert histogram
-//   scan    : expert offsets (each segment rounded up to `pad`), per-chunk
-//             bases, filler entries (-1), the row-tile table for the grouped
-//             GEMMs and the unpadded counts
-//   scatter : in-chunk stable rank (warp match + per-warp prefix) -> perm, inv
-#define PERM_CHUNK 1024
+// Stable grouping of `len` slots by expert in ONE launch (the reference takes a histogram, a scan and a scatter
+// kernel with a host-visible scratch between them, cudalm.cu:3504-3530).  A thread-block cluster of C CTAs of
+// 1024 threads owns one sort; CTA c owns a contiguous range of slots and warp w of it a contiguous piece of that
+// range, so "stable" means: slots are placed in (CTA, warp, row of 32, lane) order.  Every thread keeps its slots'
+// expert ids in registers (at most PERM_RPT), so the input is read once.
+//   count    warp-private histograms in shared memory (shared-memory atomics, order irrelevant)
+//   scan     per expert: exclusive prefix of the 32 warp counts by warp shuffles (lane = warp), the CTA totals are
+//            exchanged through distributed shared memory after one cluster barrier, and every CTA derives the
+//            padded expert offsets itself (an exclusive scan of at most 256 totals by one warp)
+//   place    row by row: the lanes holding the same expert are found with one ballot per bit of the expert id,
+//            a lane's position is offset + CTA base + warp base + running count + its rank among those lanes
+// CTA 0 also writes what depends only on the totals: offsets, counts, filler slots (-1), the row-tile table of the
+// grouped GEMMs, the per-rank send counts of the expert-parallel exchange and the out-of-range flag.
+#define PERM_THREADS 1024
+#define PERM_RPT 16                 // rows (slots per thread) a CTA can hold: 16384 slots per CTA, 131072 per cluster of 8
+#define PERM_EMAX 256
 
-// e_lo / skip: expert ids are taken relative to e_lo; with skip != 0 a slot whose id falls outside
-// [e_lo, e_lo + E) is left out (inv = -1) instead of being reported as an error
-__global__ void __launch_bounds__(PERM_CHUNK) k_perm_hist(const int *asn, int len, int E, int NC,
-                                                          int *ch, int *bad, int e_lo, int skip)
+struct PermArgs {
+    const int *asn; int len, E, pad, plen;
+    int *perm, *inv, *off, *counts, *tile_info, *ntiles, *bad, *errword;
+    int e_lo, skip;
+    int *rank_counts; int experts_per_rank;      // optional: slots per destination rank (experts_per_rank experts each)
+};
+
+__device__ __forceinline__ uint32_t perm_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t perm_cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void perm_cluster_sync()
 {
-    extern __shared__ int h[];
-    int c = blockIdx.x, k = blockIdx.y, i = c * PERM_CHUNK + threadIdx.x;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) h[e] = 0;
-    __syncthreads();
-    if (i < len) {
-        int e = asn[(size_t)k * len + i] - e_lo;
-        if ((unsigned)e >= (unsigned)E) { if (!skip) atomicExch(bad, (e + e_lo) | 0x40000000); }
-        else atomicAdd(&h[e], 1);
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < E; e += blockDim.x) ch[((size_t)k * E + e) * NC + c] = h[e];
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ int perm_ld_remote(const int *local, uint32_t rank)
+{
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(local), r; int v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(r) : "memory");
+    return v;
 }
 
-__global__ void __launch_bounds__(256) k_perm_scan(int *ch, int E, int NC, int pad, int plen,
-                                                   int *off, int *counts, int *perm,
-                                                   int *tile_info, int *ntiles,
-                                                   const int *bad, int *errword)
+__global__ void __launch_bounds__(PERM_THREADS) k_perm_cluster(const PermArgs a0, int sorts_stride_asn)
 {
-    extern __shared__ int sm[];           // [E] totals, [E+1] padded offsets, then (when it fits) the E*NC chunk counts
-    int *tot = sm, *po = sm + E, *cs = sm + 2 * E + 1;
-    const int k = blockIdx.x;
-    int *cp = ch + (size_t)k * E * NC;
-    const bool staged = (size_t)E * NC <= 8192;          // chunk counts through shared memory: no dependent global accesses
-    if (staged) {
-        for (int i = threadIdx.x; i < E * NC; i += blockDim.x) cs[i] = cp[i];
-        __syncthreads();
-    }
-    const int *src = staged ? cs : cp;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int s = 0;
-        for (int c = 0; c < NC; c++) s += src[(size_t)e * NC + c];
-        tot[e] = s;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int s = 0;
-        for (int e = 0; e < E; e++) {
-            po[e] = s;
-            s += (tot[e] + pad - 1) / pad * pad;
-        }
-        po[E] = s;
-        if (*bad && errword) { errword[0] = 100; errword[1] = *bad & ~0x40000000; }
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e <= E; e += blockDim.x) off[(size_t)k * (E + 1) + e] = po[e];
-    if (counts) for (int e = threadIdx.x; e < E; e += blockDim.x) counts[(size_t)k * E + e] = tot[e];
-    // chunk bases
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int s = po[e];
-        if (staged) {
-            for (int c = 0; c < NC; c++) { int t = cs[e * NC + c]; cs[e * NC + c] = s; s += t; }
-        } else {
-            for (int c = 0; c < NC; c++) { int t = cp[(size_t)e * NC + c]; cp[(size_t)e * NC + c] = s; s += t; }
-        }
-    }
-    if (staged) {
-        __syncthreads();
-        for (int i = threadIdx.x; i < E * NC; i += blockDim.x) cp[i] = cs[i];
-    }
-    // filler rows: the padded tail of every expert segment, all experts at once
-    if (pad > 1)
-        for (int i = threadIdx.x; i < E * (pad - 1); i += blockDim.x) {
-            const int e = i / (pad - 1), p = po[e] + tot[e] + i % (pad - 1);
-            if (p < po[e + 1]) perm[(size_t)k * plen + p] = -1;
-        }
-    // row tiles of the grouped GEMMs (pad must be 128): up to 256 rows of one expert each,
-    // packed as first row / 128 | expert << 20 | (halves - 1) << 30; expert e's tiles start
-    // at the number of tiles of the experts before it
-    if (tile_info && k == 0) {
-        __shared__ int tbase[257];
-        if (threadIdx.x == 0) {
-            int nt = 0;
-            for (int e = 0; e < E; e++) { tbase[e] = nt; nt += ((po[e + 1] - po[e]) / 128 + 1) / 2; }
-            tbase[E] = nt;
-            *ntiles = nt;
-        }
-        __syncthreads();
-        for (int e = threadIdx.x; e < E; e += blockDim.x) {
-            const int n128 = (po[e + 1] - po[e]) / 128;
-            int nt = tbase[e];
-            for (int i = 0; i < n128; i += 2)
-                tile_info[nt++] = (po[e] / 128 + i) | (e << 20) | ((i + 1 < n128 ? 1 : 0) << 30);
-        }
-    }
-}
+    extern __shared__ int psm[];
+    PermArgs a = a0;
+    const int E = a.E, sort = blockIdx.y;
+    int *wh = psm;                          // [32][E] warp histograms, then exclusive warp prefixes
+    int *tot = wh + 32 * E;                 // [E] this CTA's totals (read by the other CTAs of the cluster)
+    int *base = tot + E;                    // [E] offset + slots of the CTAs before this one
+    int *gtot = base + E;                   // [E] totals of the sort
+    int *po = gtot + E;                     // [E + 1] padded offsets
+    int *sbad = po + E + 1;                 // [1]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t crank = perm_cluster_rank(), csize = perm_cluster_size();
+    a.asn += (size_t)sort * sorts_stride_asn;
+    a.perm += (size_t)sort * a.plen;
+    if (a.inv) a.inv += (size_t)sort * a.len;
+    a.off += (size_t)sort * (E + 1);
+    if (a.counts) a.counts += (size_t)sort * E;
 
-__global__ void __launch_bounds__(PERM_CHUNK) k_perm_scatter(const int *asn, int len, int E, int NC,
-                                                             const int *base, int *perm, int plen,
-                                                             int *inv, int e_lo)
-{
-    extern __shared__ int wc[];           // [32 warps][E] counts of the chunk
-    int c = blockIdx.x, k = blockIdx.y, i = c * PERM_CHUNK + threadIdx.x;
-    int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
-    for (int j = threadIdx.x; j < 32 * E; j += blockDim.x) wc[j] = 0;
+    // slots of this CTA and of this warp (rows of 32 slots, whole rows per warp)
+    const int rows_total = (a.len + 31) / 32;
+    const int rows_cta = (rows_total + (int)csize - 1) / (int)csize;
+    const int rows_warp = (rows_cta + 31) / 32;
+    const int row0 = (int)crank * rows_cta + warp * rows_warp;
+    int row1 = row0 + rows_warp;
+    const int cta_end = ((int)crank + 1) * rows_cta < rows_total ? ((int)crank + 1) * rows_cta : rows_total;
+    if (row1 > cta_end) row1 = cta_end;
+
+    for (int i = tid; i < 32 * E; i += PERM_THREADS) wh[i] = 0;
+    if (tid == 0) *sbad = 0;
     __syncthreads();
-    int e = -1;
-    if (i < len) { e = asn[(size_t)k * len + i] - e_lo; if ((unsigned)e >= (unsigned)E) e = -1; }
-    unsigned peers = __match_any_sync(0xffffffffu, e);
-    int rank = __popc(peers & ((1u << ln) - 1u));
-    if (e >= 0 && rank == 0) wc[w * E + e] = __popc(peers);
+    // ---- count
+    int ex[PERM_RPT];
+#pragma unroll
+    for (int r = 0; r < PERM_RPT; r++) {
+        ex[r] = -1;
+        const int i = (row0 + r) * 32 + lane;
+        if (row0 + r < row1 && i < a.len) {
+            const int e = a.asn[i] - a.e_lo;
+            if ((unsigned)e < (unsigned)E) { ex[r] = e; atomicAdd(&wh[warp * E + e], 1); }
+            else if (!a.skip) atomicMax(reinterpret_cast<unsigned *>(sbad), (unsigned)((e + a.e_lo) | 0x40000000));
+        }
+    }
     __syncthreads();
-    if (e < 0) { if (inv && i < len) inv[(size_t)k * len + i] = -1; return; }
-    int pos = base[((size_t)k * E + e) * NC + c] + rank;
-    for (int j = 0; j < w; j++) pos += wc[j * E + e];
-    perm[(size_t)k * plen + pos] = i;
-    if (inv) inv[(size_t)k * len + i] = pos;
+    // ---- scan over the warps: warp v takes experts v, v + 32, ...; lane = the warp whose count it holds
+    for (int e = warp; e < E; e += 32) {
+        const int c = wh[lane * E + e];
+        int x = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+        wh[lane * E + e] = x - c;
+        if (lane == 31) tot[e] = x;
+    }
+    perm_cluster_sync();                    // totals of every CTA are visible (also orders this CTA's shared memory)
+    for (int e = tid; e < E; e += PERM_THREADS) {
+        int before = 0, all = 0;
+        for (uint32_t c = 0; c < csize; c++) {
+            const int t = (c == crank) ? tot[e] : perm_ld_remote(&tot[e], c);
+            if (c < crank) before += t;
+            all += t;
+        }
+        base[e] = before; gtot[e] = all;
+    }
+    __syncthreads();
+    if (warp == 0) {                        // padded offsets: lane l scans experts 8l .. 8l + 7
+        int v[8], s = 0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) { const int e = lane * 8 + k; v[k] = e < E ? (gtot[e] + a.pad - 1) / a.pad * a.pad : 0; s += v[k]; }
+        int x = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+        int run = x - s;
+#pragma unroll
+        for (int k = 0; k < 8; k++) { const int e = lane * 8 + k; if (e < E) po[e] = run; run += v[k]; }
+        if (lane == 31) po[E] = x;
+    }
+    __syncthreads();
+    // ---- place
+    const int nbits = 32 - __clz(E - 1 > 0 ? E - 1 : 1);
+#pragma unroll
+    for (int r = 0; r < PERM_RPT; r++) {
+        if (row0 + r >= row1) break;        // whole warp leaves together
+        const int e = ex[r];
+        unsigned same = __ballot_sync(0xffffffffu, e >= 0);
+        for (int b = 0; b < nbits; b++) {
+            const unsigned m = __ballot_sync(0xffffffffu, (e >> b) & 1);
+            same &= ((e >> b) & 1) ? m : ~m;
+        }
+        const int i = (row0 + r) * 32 + lane;
+        if (e >= 0) {
+            const int before = __popc(same & ((1u << lane) - 1u));
+            const int pos = po[e] + base[e] + wh[warp * E + e] + before;
+            a.perm[pos] = i;
+            if (a.inv) a.inv[i] = pos;
+        } else if (a.inv && i < a.len) a.inv[i] = -1;
+        __syncwarp();
+        if (e >= 0 && (same >> lane) >> 1 == 0) wh[warp * E + e] += __popc(same);     // the highest lane of each expert advances the run
+        __syncwarp();
+    }
+    // ---- what depends only on the totals (CTA 0)
+    if (crank == 0) {
+        for (int e = tid; e <= E; e += PERM_THREADS) a.off[e] = po[e];
+        if (a.counts) for (int e = tid; e < E; e += PERM_THREADS) a.counts[e] = gtot[e];
+        if (a.pad > 1)
+            for (int i = tid; i < E * (a.pad - 1); i += PERM_THREADS) {
+                const int e = i / (a.pad - 1), p = po[e] + gtot[e] + i % (a.pad - 1);
+                if (p < po[e + 1]) a.perm[p] = -1;
+            }
+        if (a.rank_counts && sort == 0 && a.experts_per_rank > 0)
+            for (int r = tid; r * a.experts_per_rank < E; r += PERM_THREADS) {
+                int s = 0;
+                for (int e = r * a.experts_per_rank; e < (r + 1) * a.experts_per_rank && e < E; e++) s += gtot[e];
+                a.rank_counts[r] = s;
+            }
+        // row tiles of the grouped GEMMs (pad = 128): up to 256 rows of one expert each, packed as
+        // first row / 128 | expert << 20 | (halves - 1) << 30, in expert order
+        if (a.tile_info && sort == 0 && warp == 1) {
+            int v[8], s = 0;
+#pragma unroll
+            for (int k = 0; k < 8; k++) { const int e = lane * 8 + k; v[k] = e < E ? ((po[e + 1] - po[e]) / 128 + 1) / 2 : 0; s += v[k]; }
+            int x = s;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+            int nt = x - s;
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int e = lane * 8 + k;
+                if (e < E) {
+                    const int n128 = (po[e + 1] - po[e]) / 128;
+                    for (int i = 0; i < n128; i += 2) a.tile_info[nt++] = (po[e] / 128 + i) | (e << 20) | ((i + 1 < n128 ? 1 : 0) << 30);
+                }
+            }
+            if (lane == 31) *a.ntiles = x;
+        }
+    }
+    // the out-of-range flag: the other CTAs' findings are read after a second barrier, which also keeps every
+    // CTA's shared memory alive until its neighbours have finished reading the totals
+    perm_cluster_sync();
+    if (crank == 0 && tid == 0) {
+        unsigned b = (unsigned)*sbad;
+        for (uint32_t c = 1; c < csize; c++) { const unsigned t = (unsigned)perm_ld_remote(sbad, c); b = t > b ? t : b; }
+        // one sort: this thread is the flag's only writer; several sorts: the flag was zeroed before the launch
+        if (gridDim.y == 1) *a.bad = (int)b; else if (b) atomicMax(reinterpret_cast<unsigned *>(a.bad), b);
+        if (b && a.errword) { a.errword[0] = 100; a.errword[1] = (int)b & ~0x40000000; }
+    }
+    perm_cluster_sync();
 }
 
 int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
                int *off, int *counts, int *bad_flag, int *tile_info, int *ntiles,
-               int *chunk_scratch, cudaStream_t st, int e_lo, int skip)
+               int *chunk_scratch, cudaStream_t st, int e_lo, int skip, int *rank_counts, int experts_per_rank)
 {
-    int sorts = merged ? 1 : K, len = merged ? K * N : N;
-    int NC = (len + PERM_CHUNK - 1) / PERM_CHUNK;
-    int plen = len + E * (pad - 1);
-    QLMB_CUDA(cudaMemsetAsync(bad_flag, 0, sizeof(int), st));
-    k_perm_hist<<<dim3(NC, sorts), PERM_CHUNK, E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, bad_flag, e_lo, skip);
-    k_perm_scan<<<sorts, 256, (2 * E + 1 + ((size_t)E * NC <= 8192 ? (size_t)E * NC : 0)) * sizeof(int), st>>>(chunk_scratch, E, NC, pad, plen, off, counts, perm,
-                                                             tile_info, ntiles, bad_flag,
-                                                             device_error_word());
-    k_perm_scatter<<<dim3(NC, sorts), PERM_CHUNK, 32 * E * sizeof(int), st>>>(assign, len, E, NC, chunk_scratch, perm,
-                                                                            plen, inv, e_lo);
+    (void)chunk_scratch;
+    const int sorts = merged ? 1 : K, len = merged ? K * N : N;
+    QLMB_REQUIRE(E >= 1 && E <= PERM_EMAX, "perm_build: %d experts (at most %d)", E, PERM_EMAX);
+    const int rows = (len + 31) / 32;
+    int C = 1;
+    while (C < 8 && (rows + C - 1) / C > 4 * 32) C *= 2;             // about four rows per warp when the cluster may grow
+    QLMB_REQUIRE((rows + C - 1) / C <= PERM_RPT * 32, "perm_build: %d slots exceed one cluster's capacity (%d)", len, 8 * PERM_RPT * 1024);
+    PermArgs a = {assign, len, E, pad, len + E * (pad - 1), perm, inv, off, counts, tile_info, ntiles, bad_flag,
+                  device_error_word(), e_lo, skip, rank_counts, experts_per_rank};
+    const size_t smem = ((size_t)32 * E + 4 * (size_t)E + 2) * sizeof(int);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(C, sorts, 1); cfg.blockDim = dim3(PERM_THREADS, 1, 1); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (sorts > 1) QLMB_CUDA(cudaMemsetAsync(bad_flag, 0, sizeof(int), st));
+    QLMB_CUDA(cudaLaunchKernelEx(&cfg, k_perm_cluster, a, len));
     QLMB_LAUNCH_CHECK("perm_build");
     return QLMB_OK;
 }
 
+// the permutation needs no scratch any more; callers that carve one out of their arena get a token size
 size_t perm_scratch_ints(int N, int E, int K, int merged)
 {
-    int sorts = merged ? 1 : K, len = merged ? K * N : N;
-    int NC = (len + PERM_CHUNK - 1) / PERM_CHUNK;
-    return (size_t)sorts * E * NC;
+    (void)N; (void)E; (void)K; (void)merged;
+    return 64;
 }
 
 int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N, int E, int K,
                 const float *bias, int bs, cudaStream_t st)
 {
     if (E <= 32) k_router_topk_warp<<<(N + 7) / 8, 256, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
-    else k_router_topk<<<(N + 127) / 128, 128, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
+    else if (E <= 64) k_router_topk_wide<2><<<(N + 7) / 8, 256, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
+    else if (E <= 128) k_router_topk_wide<4><<<(N + 7) / 8, 256, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
+    else k_router_topk_wide<8><<<(N + 7) / 8, 256, 0, st>>>(rt, rprobs, assign, gate, N, E, K, bias, bs);
     QLMB_LAUNCH_CHECK("k_router_topk");
     return QLMB_OK;
 }
@@ -348,10 +453,6 @@ __global__ void __launch_bounds__(256) k_bias_update(float *bias, const int *ass
     }
 }
 
-// lazily grown per-device scratch for the public perm entry point
-static int *g_perm_scratch[64];
-static size_t g_perm_cap[64];
-
 }  // namespace qlmb
 
 using namespace qlmb;
@@ -361,18 +462,7 @@ extern "C" int qlmb_perm_build(const int *assign, int N, int E, int K, int merge
 {
     QLMB_REQUIRE(assign && perm && off && bad_flag, "qlmb_perm_build: NULL argument");
     QLMB_REQUIRE(N > 0 && E > 0 && E <= 256 && K > 0 && K <= 8 && pad >= 1, "qlmb_perm_build: N=%d E=%d K=%d pad=%d", N, E, K, pad);
-    int dev = 0;
-    QLMB_CUDA(cudaGetDevice(&dev));
-    QLMB_REQUIRE(dev >= 0 && dev < 64, "qlmb_perm_build: device index %d", dev);
-    size_t need = perm_scratch_ints(N, E, K, merged);
-    if (g_perm_cap[dev] < need) {
-        if (g_perm_scratch[dev]) QLMB_CUDA(cudaFree(g_perm_scratch[dev]));
-        g_perm_scratch[dev] = nullptr; g_perm_cap[dev] = 0;
-        QLMB_CUDA(cudaMalloc(&g_perm_scratch[dev], need * sizeof(int)));
-        g_perm_cap[dev] = need;
-    }
-    return perm_build(assign, N, E, K, merged, pad, perm, inv, off, counts, bad_flag, nullptr, nullptr,
-                      g_perm_scratch[dev], as_stream(stream));
+    return perm_build(assign, N, E, K, merged, pad, perm, inv, off, counts, bad_flag, nullptr, nullptr, nullptr, as_stream(stream));
 }
 
 extern "C" int qlmb_router_bias_update(float *bias, const int *assign, int N, int E, int K, int per_slot, float u,

@@ -39,6 +39,7 @@ struct StepArgs {
     const int *touched; const int *touched_count;
     unsigned long long *skipped;    // device counter of launches that found a non-finite norm and wrote nothing
     qlmb_span inl; int use_inl;     // one span carried in the launch arguments (the n-gram table) instead of a table in memory
+    float one;                      // 1.0f, as a run-time value (see pk_add)
 };
 
 // gpu_adam returns without stepping when the gradient norm is not finite (cudalm.cu:6446-6447; the caller prints
@@ -414,8 +415,7 @@ __global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
 // instruction-issue limit that bounds this kernel (it is not the memory system: the update needs three 64-bit
 // hashes, three stochastic roundings, three divisions and a square root per element).  What changes is only how
 // many instructions carry the work:
-//  * floating-point work runs on PAIRS of elements with the sm_100 two-wide fp32 instructions (__fadd2_rn,
-//    __fmul2_rn, __ffma2_rn: each lane of a pair is an IEEE round-to-nearest operation, so results are those
+//  * floating-point work runs on PAIRS of elements with the sm_100 two-wide fp32 instructions (add / mul / fma .rn.f32x2: each lane of a pair is an IEEE round-to-nearest operation, so results are those
 //    of the scalar sequence);
 //  * small integers live in floats (exactly representable), so bytes and nibbles are unpacked and packed with
 //    byte permutes and a magic-number add instead of integer<->float conversions;
@@ -432,7 +432,9 @@ __global__ void __launch_bounds__(256) k_step_fast(StepArgs a)
 // generic team walk.
 __device__ __forceinline__ uint32_t mix32(uint64_t x)
 {
-    // x already holds key + 0x9E3779B97F4A7C15; returns the low 32 bits of the splitmix64 finaliser (qlm.cuh:78-82)
+    // x already holds key + 0x9E3779B97F4A7C15; returns the low 32 bits of the splitmix64 finaliser (qlm.cuh:78-82).
+    // (Taking the shifts as widening multiplies by a power of two, to move them off the half-rate integer pipe,
+    // was measured 22 % slower: 0.926 ms against 0.757 ms per 125.8 M parameters.)
     uint32_t lo = (uint32_t)x, hi = (uint32_t)(x >> 32);
     lo ^= __funnelshift_r(lo, hi, 30); hi ^= hi >> 30;
     uint64_t p = (uint64_t)lo * 0x1CE4E5B9u;
@@ -445,23 +447,31 @@ __device__ __forceinline__ uint32_t mix32(uint64_t x)
     return lo ^ __funnelshift_r(lo, hi, 31);
 }
 __device__ __forceinline__ float2 bc2(float x) { return make_float2(x, x); }
+// Two-wide fp32 arithmetic.  ptxas contracts a two-wide multiply that feeds a two-wide add into a fused multiply-add
+// even under --fmad=false and with explicit .rn instructions (measured: the scales came out as fma(b1, mv, .)), which
+// the integer state's reproducibility cannot tolerate.  A sum of products is therefore written as
+// fma(p, one, q) with `one` a kernel argument equal to 1.0f: RN(p * 1 + q) = RN(p + q), and a multiply cannot be
+// folded into an existing fma.
+__device__ __forceinline__ float2 pk_add(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 pk_mul(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 pk_fma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 // floor(v) + [24-bit draw < frac(v)] for a pair, as floats (qsri, qlm.cuh:83-87)
 __device__ __forceinline__ float2 sround_pair(float2 v, uint32_t h0, uint32_t h1)
 {
     const float2 fl = make_float2(floorf(v.x), floorf(v.y));
-    const float2 fr = __ffma2_rn(fl, bc2(-1.0f), v);                  // v - fl, one rounding
-    const float2 y = __fmul2_rn(fr, bc2(16777216.0f));                // u * 2^-24 < fr  <=>  (h >> 8) < fr * 2^24 (both exact)
+    const float2 fr = pk_fma(fl, bc2(-1.0f), v);                  // v - fl, one rounding
+    const float2 y = pk_mul(fr, bc2(16777216.0f));                // u * 2^-24 < fr  <=>  (h >> 8) < fr * 2^24 (both exact)
     const float p0 = (float)(h0 >> 8) < y.x ? 1.0f : 0.0f, p1 = (float)(h1 >> 8) < y.y ? 1.0f : 0.0f;
-    return __fadd2_rn(fl, make_float2(p0, p1));
+    return pk_add(fl, make_float2(p0, p1));
 }
 // x / y for a pair with one denominator; r = RN(1 / y)
 __device__ __forceinline__ float2 div_pair(float2 x, float y, float r, bool fast)
 {
     if (!fast) return make_float2(x.x / y, x.y / y);
     const float2 ny = bc2(-y), rr = bc2(r);
-    float2 q = __fmul2_rn(x, rr);
-    q = __ffma2_rn(__ffma2_rn(q, ny, x), rr, q);
-    q = __ffma2_rn(__ffma2_rn(q, ny, x), rr, q);
+    float2 q = pk_mul(x, rr);
+    q = pk_fma(pk_fma(q, ny, x), rr, q);
+    q = pk_fma(pk_fma(q, ny, x), rr, q);
     return q;
 }
 // byte-permute selector that replaces byte j of the first operand by the low byte of the second
@@ -473,6 +483,8 @@ template <bool WRITE_P>
 __global__ void __launch_bounds__(256) k_step_pk(const __grid_constant__ StepArgs a)
 {
     constexpr int EPL = 8, TEAM = 16, NP = EPL / 2;
+    constexpr bool CVT = true;      // bytes -> floats by conversion instructions (0.7455 ms) or by byte permutes and a magic add (0.7569 ms)
+#define MIX(x) mix32(x)
     if (step_is_skipped(a)) return;
     const int lane = threadIdx.x & 31, tl = lane % TEAM, team = lane / TEAM;
     const unsigned tmask = 0xffffu << (team * TEAM);
@@ -506,6 +518,7 @@ __global__ void __launch_bounds__(256) k_step_pk(const __grid_constant__ StepArg
     const uint64_t kd = kbase + a.t * QLMB_HASH_T, km = kbase + (a.t + 0x5EEDULL) * QLMB_HASH_T,
                    kv = kbase + (a.t + 0xBEEFULL) * QLMB_HASH_T;
 
+    const float2 one2 = bc2(a.one);
     const float2 g2[NP] = {make_float2(ga.x, ga.y), make_float2(ga.z, ga.w), make_float2(gb.x, gb.y), make_float2(gb.z, gb.w)};
     // bytes -> floats: signed bytes are biased by 128 first, nibbles by 8
     const uint32_t rx[2] = {rw.x ^ 0x80808080u, rw.y ^ 0x80808080u}, mx[2] = {mw.x ^ 0x80808080u, mw.y ^ 0x80808080u};
@@ -521,42 +534,50 @@ __global__ void __launch_bounds__(256) k_step_pk(const __grid_constant__ StepArg
         auto byte2 = [&](const uint32_t *src, float bias) {
             const float x0 = __uint_as_float(__byte_perm(src[wd_], 0x4B000000u, 0x7440 + b0));
             const float x1 = __uint_as_float(__byte_perm(src[wd_], 0x4B000000u, 0x7441 + b0));
-            return __fadd2_rn(make_float2(x0, x1), bc2(bias));
+            return pk_add(make_float2(x0, x1), bc2(bias));
         };
-        const float2 rold = byte2(rx, -(QLMB_MAGIC_U + 128.0f)), m8f = byte2(mx, -(QLMB_MAGIC_U + 128.0f)), v8f = byte2(vx, -QLMB_MAGIC_U);
-        const float2 ddf = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(dev, 0x4B000000u, 0x7440 + p)),
+        float2 rold, m8f, v8f;
+        if (CVT) {
+            const uint32_t rs = wd_ ? rw.y : rw.x, ms_ = wd_ ? mw.y : mw.x, vs_ = wd_ ? vw.y : vw.x;
+            rold = make_float2((float)(int8_t)(rs >> (8 * b0)), (float)(int8_t)(rs >> (8 * b0 + 8)));
+            m8f = make_float2((float)(int8_t)(ms_ >> (8 * b0)), (float)(int8_t)(ms_ >> (8 * b0 + 8)));
+            v8f = make_float2((float)(uint8_t)(vs_ >> (8 * b0)), (float)(uint8_t)(vs_ >> (8 * b0 + 8)));
+        } else {
+            rold = byte2(rx, -(QLMB_MAGIC_U + 128.0f)); m8f = byte2(mx, -(QLMB_MAGIC_U + 128.0f)); v8f = byte2(vx, -QLMB_MAGIC_U);
+        }
+        const float2 ddf = pk_add(make_float2(__uint_as_float(__byte_perm(dev, 0x4B000000u, 0x7440 + p)),
                                                   __uint_as_float(__byte_perm(dod, 0x4B000000u, 0x7440 + p))), bc2(-(QLMB_MAGIC_U + 8.0f)));
         // moments (qlm.cuh:206-222)
-        const float2 gr = __fmul2_rn(g2[p], bc2(gs));
-        const float2 mv = __fmul2_rn(m8f, bc2(ms_old));
-        const float2 sv = __fmul2_rn(v8f, bc2(vs_old));
-        float2 vv = __fmul2_rn(sv, sv);
-        mn[p] = __fadd2_rn(__fmul2_rn(bc2(a.b1), mv), __fmul2_rn(bc2(omb1), gr));
-        vv = __fadd2_rn(__fmul2_rn(bc2(a.b2), vv), __fmul2_rn(__fmul2_rn(bc2(omb2), gr), gr));
+        const float2 gr = pk_mul(g2[p], bc2(gs));
+        const float2 mv = pk_mul(m8f, bc2(ms_old));
+        const float2 sv = pk_mul(v8f, bc2(vs_old));
+        float2 vv = pk_mul(sv, sv);
+        mn[p] = pk_fma(pk_mul(bc2(a.b1), mv), one2, pk_mul(bc2(omb1), gr));
+        vv = pk_fma(pk_mul(bc2(a.b2), vv), one2, pk_mul(pk_mul(bc2(omb2), gr), gr));
         rv[p] = make_float2(sqrtf(vv.x), sqrtf(vv.y));
-        const float2 num = __fmul2_rn(mn[p], bc2(a.inv_bc1));
-        const float2 den = __fadd2_rn(__fmul2_rn(rv[p], bc2(a.inv_sqrt_bc2)), bc2(veps));
+        const float2 num = pk_mul(mn[p], bc2(a.inv_bc1));
+        const float2 den = pk_fma(pk_mul(rv[p], bc2(a.inv_sqrt_bc2)), one2, bc2(veps));
         float2 u = make_float2(num.x / den.x, num.y / den.y);
         u.x = fmaxf(-8.0f, fminf(8.0f, u.x)); u.y = fmaxf(-8.0f, fminf(8.0f, u.y));
         am = fmaxf(am, fmaxf(fabsf(mn[p].x), fabsf(mn[p].y)));
         vm = fmaxf(vm, fmaxf(rv[p].x, rv[p].y));
         // digit and residual (qlm.cuh:231-242): -(L*u + dec*d), rounded stochastically, added to the residual
-        const float2 v = __fadd2_rn(__fmul2_rn(bc2(-L), u), __fmul2_rn(bc2(-dec), ddf));
-        const float2 idl = sround_pair(v, mix32(kd + (uint64_t)e0 * QLMB_HASH_I), mix32(kd + (uint64_t)(e0 + 1) * QLMB_HASH_I));
-        const float2 rr = __fadd2_rn(rold, idl);
+        const float2 v = pk_fma(pk_mul(bc2(-L), u), one2, pk_mul(bc2(-dec), ddf));
+        const float2 idl = sround_pair(v, MIX(kd + (uint64_t)e0 * QLMB_HASH_I), MIX(kd + (uint64_t)(e0 + 1) * QLMB_HASH_I));
+        const float2 rr = pk_add(rold, idl);
         const float2 half = make_float2(__uint_as_float(0xBB800000u ^ (__float_as_uint(rr.x) & 0x80000000u)),
                                         __uint_as_float(0xBB800000u ^ (__float_as_uint(rr.y) & 0x80000000u)));   // -+ 2^-8
-        const float2 c = __fadd2_rn(__fadd2_rn(__ffma2_rn(rr, bc2(0.0078125f), half), bc2(QLMB_MAGIC_RN)), bc2(-QLMB_MAGIC_RN));
-        const float2 rnew = __ffma2_rn(c, bc2(-128.0f), rr);
-        float2 dn = __fadd2_rn(ddf, c);
+        const float2 c = pk_add(pk_add(pk_fma(rr, bc2(0.0078125f), half), bc2(QLMB_MAGIC_RN)), bc2(-QLMB_MAGIC_RN));
+        const float2 rnew = pk_fma(c, bc2(-128.0f), rr);
+        float2 dn = pk_add(ddf, c);
         dn.x = fminf(fmaxf(dn.x, -dmaxf), dmaxf); dn.y = fminf(fmaxf(dn.y, -dmaxf), dmaxf);
-        const float2 rb = __fadd2_rn(rnew, bc2(QLMB_MAGIC_RN)), db = __fadd2_rn(dn, bc2(QLMB_MAGIC_RN));
+        const float2 rb = pk_add(rnew, bc2(QLMB_MAGIC_RN)), db = pk_add(dn, bc2(QLMB_MAGIC_RN));
         rout[wd_] = __byte_perm(rout[wd_], __float_as_uint(rb.x), ins_sel(b0));
         rout[wd_] = __byte_perm(rout[wd_], __float_as_uint(rb.y), ins_sel(b0 + 1));
         const uint32_t nb = (__float_as_uint(db.x) & 15u) | (__float_as_uint(db.y) << 4);
         dout = __byte_perm(dout, nb, ins_sel(p));
         if (WRITE_P) {
-            const float2 pp = __fmul2_rn(bc2(sg), dn);
+            const float2 pp = pk_mul(bc2(sg), dn);
             if (p & 1) { pv[p >> 1].z = pp.x; pv[p >> 1].w = pp.y; } else { pv[p >> 1].x = pp.x; pv[p >> 1].y = pp.y; }
         }
     }
@@ -582,12 +603,12 @@ __global__ void __launch_bounds__(256) k_step_pk(const __grid_constant__ StepArg
     for (int p = 0; p < NP; p++) {
         const int e0 = 2 * p, wd_ = e0 >> 2, b0 = e0 & 3;
         const uint64_t ei = (uint64_t)e0 * QLMB_HASH_I, ej = (uint64_t)(e0 + 1) * QLMB_HASH_I;
-        float2 mq = sround_pair(div_pair(mn[p], ms, rms, fm), mix32(km + ei), mix32(km + ej));
+        float2 mq = sround_pair(div_pair(mn[p], ms, rms, fm), MIX(km + ei), MIX(km + ej));
         mq.x = fminf(fmaxf(mq.x, -127.0f), 127.0f); mq.y = fminf(fmaxf(mq.y, -127.0f), 127.0f);
-        float2 vq = sround_pair(div_pair(rv[p], vs, rvs, fv), mix32(kv + ei), mix32(kv + ej));
+        float2 vq = sround_pair(div_pair(rv[p], vs, rvs, fv), MIX(kv + ei), MIX(kv + ej));
         // clamp to [0, 255]; a value that rounded to 0 while rv > 0 becomes 1 (qlm.cuh:275-277)
         vq.x = fminf(fmaxf(vq.x, rv[p].x > 0.0f ? 1.0f : 0.0f), 255.0f); vq.y = fminf(fmaxf(vq.y, rv[p].y > 0.0f ? 1.0f : 0.0f), 255.0f);
-        const float2 mb = __fadd2_rn(mq, bc2(QLMB_MAGIC_RN)), vb = __fadd2_rn(vq, bc2(QLMB_MAGIC_U));
+        const float2 mb = pk_add(mq, bc2(QLMB_MAGIC_RN)), vb = pk_add(vq, bc2(QLMB_MAGIC_U));
         mo[wd_] = __byte_perm(mo[wd_], __float_as_uint(mb.x), ins_sel(b0));
         mo[wd_] = __byte_perm(mo[wd_], __float_as_uint(mb.y), ins_sel(b0 + 1));
         vo[wd_] = __byte_perm(vo[wd_], __float_as_uint(vb.x), ins_sel(b0));
@@ -595,6 +616,7 @@ __global__ void __launch_bounds__(256) k_step_pk(const __grid_constant__ StepArg
     }
     *reinterpret_cast<uint2 *>(a.m8 + qe) = make_uint2(mo[0], mo[1]);
     *reinterpret_cast<uint2 *>(a.v8 + qe) = make_uint2(vo[0], vo[1]);
+#undef MIX
 }
 
 // ------------------------------------------------------------------ encode
@@ -845,7 +867,7 @@ extern "C" int qlmb_step(float *P, const float *G, int8_t *d, int8_t *r, const f
     if (ng <= 0) return QLMB_OK;
     StepArgs a = {P, G, d, r, s, m8, m8s, v8, v8s, sp, nspan, group, dmax, lr, b1, b2, wd, gscale, gsp,
                   inv_bc1, inv_sqrt_bc2, lrmode, t, adam, (unsigned long long *)stat, packed, gi_base, ng, g_qv4, nullptr, nullptr,
-                  skip_counter(), {}, 0};
+                  skip_counter(), {}, 0, 1.0f};
     auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
     bool fast = group == 128 && packed && adam && !stat && !g_qv4 && al16(G) && al16(d) && al16(r) && al16(m8) &&
                 al16(v8) && (!P || al16(P));
@@ -1038,7 +1060,7 @@ extern "C" int qlmb_ng_step(float *P, const float *Gc, int8_t *d, int8_t *r, con
     h.pof = 0; h.gof = 0; h.qi0 = 0; h.n = nt; h.gi0 = 0; h.ngrp = (int)((nt + group - 1) / group); h.sref = sref;
     cudaStream_t st = as_stream(stream);
     StepArgs a = {P, Gc, d, r, s, m8, m8s, v8, v8s, nullptr, 1, group, dmax, lr, b1, b2, wd, 1.0f, gs,
-                  inv_bc1, inv_sqrt_bc2, 0, t, 1, nullptr, 1, 0, max_touched, g_qv4, tgi, count, skip_counter(), h, 1};
+                  inv_bc1, inv_sqrt_bc2, 0, t, 1, nullptr, 1, 0, max_touched, g_qv4, tgi, count, skip_counter(), h, 1, 1.0f};
     k_step_generic<<<(max_touched + 7) / 8, 256, 0, st>>>(a);
     QLMB_LAUNCH_CHECK("qlmb_ng_step");
     return QLMB_OK;

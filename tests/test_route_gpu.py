@@ -44,7 +44,28 @@ def test_router_logits_fused(cuda, oracle):
         assert (rp.cpu().numpy() == rp2).all() and (asg.cpu().numpy() == asg2).all() and (gt.cpu().numpy() == gt2).all()
 
 
-@pytest.mark.parametrize("N,E,K", [(5000, 7, 2), (8192, 32, 2), (64, 4, 1), (1500, 256, 8), (1, 3, 1)])
+@pytest.mark.parametrize("E,K", [(33, 2), (48, 3), (64, 8), (100, 2), (128, 1), (200, 4), (256, 8)])
+def test_router_topk_wide_matches_oracle(cuda, oracle, E, K):
+    """More than 32 experts (one warp per token, several experts per lane): probabilities, choices and gates equal
+    the oracle's bit for bit, with and without a selection bias, including exact ties between logits."""
+    from cudalm_c_b200 import moe
+    rng = np.random.default_rng(E * 10 + K)
+    N = 777
+    rt = (rng.standard_normal((N, E)) * 2.0).astype(f32)
+    rt[:50, 5] = rt[:50, 40 % E]                     # exact ties: the lower index must win
+    rt[50:60] = 0.25                                 # a whole row of ties
+    bias = (rng.standard_normal((K, E)) * 0.01).astype(f32)
+    for b in (None, bias):
+        db = dev(b, cuda) if b is not None else None
+        _, rp, asg, gt = moe.router_topk(rt=dev(rt, cuda), K=K, bias=db, bias_stride=E if b is not None else 0)
+        rp2, asg2, gt2 = oracle.router_topk(rt, K, bias=b, bs=E if b is not None else 0)
+        assert (rp.cpu().numpy() == rp2).all()
+        assert (asg.cpu().numpy() == asg2).all()
+        assert (gt.cpu().numpy() == gt2).all()
+
+
+@pytest.mark.parametrize("N,E,K", [(5000, 7, 2), (8192, 32, 2), (64, 4, 1), (1500, 256, 8), (1, 3, 1), (16384, 32, 8), (33, 2, 1),
+                                   (4097, 5, 2), (65536, 64, 2)])
 def test_perm_matches_oracle(cuda, oracle, N, E, K):
     from cudalm_c_b200 import moe
     rng = np.random.default_rng(N + E)
