@@ -208,32 +208,34 @@ struct PermArgs {
 
 __device__ __forceinline__ uint32_t perm_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ uint32_t perm_cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ void perm_cluster_sync()
+__device__ __forceinline__ void perm_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void perm_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// store into the same shared-memory location of CTA `rank` of the cluster
+__device__ __forceinline__ void perm_st_remote(int *local, uint32_t rank, int v)
 {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ int perm_ld_remote(const int *local, uint32_t rank)
-{
-    uint32_t a = (uint32_t)__cvta_generic_to_shared(local), r; int v;
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(local), r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
-    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(r) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(r), "r"(v) : "memory");
 }
 
+// RPT = rows of 32 slots per warp (slots per thread kept in registers)
+template <int RPT>
 __global__ void __launch_bounds__(PERM_THREADS) k_perm_cluster(const PermArgs a0, int sorts_stride_asn)
 {
     extern __shared__ int psm[];
     PermArgs a = a0;
     const int E = a.E, sort = blockIdx.y;
     int *wh = psm;                          // [32][E] warp histograms, then exclusive warp prefixes
-    int *tot = wh + 32 * E;                 // [E] this CTA's totals (read by the other CTAs of the cluster)
-    int *base = tot + E;                    // [E] offset + slots of the CTAs before this one
+    int *tot = wh + 32 * E;                 // [E] this CTA's totals
+    int *rtot = tot + E;                    // [8][E] every CTA's totals, written by their owners (remote stores)
+    int *base = rtot + 8 * E;               // [E] slots of the CTAs before this one
     int *gtot = base + E;                   // [E] totals of the sort
     int *po = gtot + E;                     // [E + 1] padded offsets
-    int *sbad = po + E + 1;                 // [1]
+    int *rbad = po + E + 1;                 // [8] every CTA's out-of-range finding
+    int *sbad = rbad + 8;                   // [1]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t crank = perm_cluster_rank(), csize = perm_cluster_size();
+    perm_cluster_arrive();                  // phase 0: "this CTA runs"; waited for just before the first remote store
     a.asn += (size_t)sort * sorts_stride_asn;
     a.perm += (size_t)sort * a.plen;
     if (a.inv) a.inv += (size_t)sort * a.len;
@@ -243,25 +245,29 @@ __global__ void __launch_bounds__(PERM_THREADS) k_perm_cluster(const PermArgs a0
     // slots of this CTA and of this warp (rows of 32 slots, whole rows per warp)
     const int rows_total = (a.len + 31) / 32;
     const int rows_cta = (rows_total + (int)csize - 1) / (int)csize;
-    const int rows_warp = (rows_cta + 31) / 32;
-    const int row0 = (int)crank * rows_cta + warp * rows_warp;
-    int row1 = row0 + rows_warp;
-    const int cta_end = ((int)crank + 1) * rows_cta < rows_total ? ((int)crank + 1) * rows_cta : rows_total;
+    const int row0 = (int)crank * rows_cta + warp * RPT;
+    int row1 = row0 + RPT;
+    int cta_end = ((int)crank + 1) * rows_cta;
+    if (cta_end > rows_total) cta_end = rows_total;
     if (row1 > cta_end) row1 = cta_end;
 
+    // ---- count: the slots are requested first, the histograms zeroed while they travel
+    int ex[RPT];
+#pragma unroll
+    for (int r = 0; r < RPT; r++) {
+        const int i = (row0 + r) * 32 + lane;
+        ex[r] = (row0 + r < row1 && i < a.len) ? a.asn[i] - a.e_lo : -0x40000000;
+    }
     for (int i = tid; i < 32 * E; i += PERM_THREADS) wh[i] = 0;
     if (tid == 0) *sbad = 0;
     __syncthreads();
-    // ---- count
-    int ex[PERM_RPT];
 #pragma unroll
-    for (int r = 0; r < PERM_RPT; r++) {
-        ex[r] = -1;
-        const int i = (row0 + r) * 32 + lane;
-        if (row0 + r < row1 && i < a.len) {
-            const int e = a.asn[i] - a.e_lo;
-            if ((unsigned)e < (unsigned)E) { ex[r] = e; atomicAdd(&wh[warp * E + e], 1); }
-            else if (!a.skip) atomicMax(reinterpret_cast<unsigned *>(sbad), (unsigned)((e + a.e_lo) | 0x40000000));
+    for (int r = 0; r < RPT; r++) {
+        const int e = ex[r];
+        if ((unsigned)e < (unsigned)E) atomicAdd(&wh[warp * E + e], 1);
+        else {
+            if (e != -0x40000000 && !a.skip) atomicMax(reinterpret_cast<unsigned *>(sbad), (unsigned)((e + a.e_lo) | 0x40000000));
+            ex[r] = -1;
         }
     }
     __syncthreads();
@@ -274,14 +280,15 @@ __global__ void __launch_bounds__(PERM_THREADS) k_perm_cluster(const PermArgs a0
         wh[lane * E + e] = x - c;
         if (lane == 31) tot[e] = x;
     }
-    perm_cluster_sync();                    // totals of every CTA are visible (also orders this CTA's shared memory)
+    __syncthreads();
+    perm_cluster_wait();                    // phase 0 complete: every CTA of the cluster has started
+    for (int i = tid; i < E * (int)csize; i += PERM_THREADS) perm_st_remote(&rtot[crank * E + i % E], (uint32_t)(i / E), tot[i % E]);
+    if (tid < (int)csize) perm_st_remote(&rbad[crank], (uint32_t)tid, *sbad);
+    perm_cluster_arrive();
+    perm_cluster_wait();                    // phase 1: all totals have landed; nothing remote is touched after this
     for (int e = tid; e < E; e += PERM_THREADS) {
         int before = 0, all = 0;
-        for (uint32_t c = 0; c < csize; c++) {
-            const int t = (c == crank) ? tot[e] : perm_ld_remote(&tot[e], c);
-            if (c < crank) before += t;
-            all += t;
-        }
+        for (int c = 0; c < (int)csize; c++) { const int t = rtot[c * E + e]; if (c < (int)crank) before += t; all += t; }
         base[e] = before; gtot[e] = all;
     }
     __syncthreads();
@@ -301,43 +308,44 @@ __global__ void __launch_bounds__(PERM_THREADS) k_perm_cluster(const PermArgs a0
     // ---- place
     const int nbits = 32 - __clz(E - 1 > 0 ? E - 1 : 1);
 #pragma unroll
-    for (int r = 0; r < PERM_RPT; r++) {
-        if (row0 + r >= row1) break;        // whole warp leaves together
-        const int e = ex[r];
-        unsigned same = __ballot_sync(0xffffffffu, e >= 0);
-        for (int b = 0; b < nbits; b++) {
-            const unsigned m = __ballot_sync(0xffffffffu, (e >> b) & 1);
-            same &= ((e >> b) & 1) ? m : ~m;
+    for (int r = 0; r < RPT; r++) {
+        if (row0 + r < row1) {              // the same for every lane of the warp
+            const int e = ex[r];
+            unsigned same = __ballot_sync(0xffffffffu, e >= 0);
+            for (int b = 0; b < nbits; b++) {
+                const unsigned m = __ballot_sync(0xffffffffu, (e >> b) & 1);
+                same &= ((e >> b) & 1) ? m : ~m;
+            }
+            const int i = (row0 + r) * 32 + lane;
+            if (e >= 0) {
+                const int pos = po[e] + base[e] + wh[warp * E + e] + __popc(same & ((1u << lane) - 1u));
+                a.perm[pos] = i;
+                if (a.inv) a.inv[i] = pos;
+            } else if (a.inv && i < a.len) a.inv[i] = -1;
+            __syncwarp();
+            if (e >= 0 && (same >> lane) >> 1 == 0) wh[warp * E + e] += __popc(same);     // the highest lane of each expert advances the run
+            __syncwarp();
         }
-        const int i = (row0 + r) * 32 + lane;
-        if (e >= 0) {
-            const int before = __popc(same & ((1u << lane) - 1u));
-            const int pos = po[e] + base[e] + wh[warp * E + e] + before;
-            a.perm[pos] = i;
-            if (a.inv) a.inv[i] = pos;
-        } else if (a.inv && i < a.len) a.inv[i] = -1;
-        __syncwarp();
-        if (e >= 0 && (same >> lane) >> 1 == 0) wh[warp * E + e] += __popc(same);     // the highest lane of each expert advances the run
-        __syncwarp();
     }
     // ---- what depends only on the totals (CTA 0)
-    if (crank == 0) {
-        for (int e = tid; e <= E; e += PERM_THREADS) a.off[e] = po[e];
-        if (a.counts) for (int e = tid; e < E; e += PERM_THREADS) a.counts[e] = gtot[e];
-        if (a.pad > 1)
-            for (int i = tid; i < E * (a.pad - 1); i += PERM_THREADS) {
-                const int e = i / (a.pad - 1), p = po[e] + gtot[e] + i % (a.pad - 1);
-                if (p < po[e + 1]) a.perm[p] = -1;
-            }
-        if (a.rank_counts && sort == 0 && a.experts_per_rank > 0)
-            for (int r = tid; r * a.experts_per_rank < E; r += PERM_THREADS) {
-                int s = 0;
-                for (int e = r * a.experts_per_rank; e < (r + 1) * a.experts_per_rank && e < E; e++) s += gtot[e];
-                a.rank_counts[r] = s;
-            }
-        // row tiles of the grouped GEMMs (pad = 128): up to 256 rows of one expert each, packed as
-        // first row / 128 | expert << 20 | (halves - 1) << 30, in expert order
-        if (a.tile_info && sort == 0 && warp == 1) {
+    if (crank != 0) return;
+    for (int e = tid; e <= E; e += PERM_THREADS) a.off[e] = po[e];
+    if (a.counts) for (int e = tid; e < E; e += PERM_THREADS) a.counts[e] = gtot[e];
+    if (a.pad > 1)
+        for (int i = tid; i < E * (a.pad - 1); i += PERM_THREADS) {
+            const int e = i / (a.pad - 1), p = po[e] + gtot[e] + i % (a.pad - 1);
+            if (p < po[e + 1]) a.perm[p] = -1;
+        }
+    if (a.rank_counts && sort == 0 && a.experts_per_rank > 0)
+        for (int r = tid; r * a.experts_per_rank < E; r += PERM_THREADS) {
+            int s = 0;
+            for (int e = r * a.experts_per_rank; e < (r + 1) * a.experts_per_rank && e < E; e++) s += gtot[e];
+            a.rank_counts[r] = s;
+        }
+    // row tiles of the grouped GEMMs (pad = 128): up to 256 rows of one expert each, packed as
+    // first row / 128 | expert << 20 | (halves - 1) << 30, in expert order; one thread per (expert, tile)
+    if (a.tile_info && sort == 0) {
+        if (warp == 1) {
             int v[8], s = 0;
 #pragma unroll
             for (int k = 0; k < 8; k++) { const int e = lane * 8 + k; v[k] = e < E ? ((po[e + 1] - po[e]) / 128 + 1) / 2 : 0; s += v[k]; }
@@ -346,27 +354,23 @@ __global__ void __launch_bounds__(PERM_THREADS) k_perm_cluster(const PermArgs a0
             for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
             int nt = x - s;
 #pragma unroll
-            for (int k = 0; k < 8; k++) {
-                const int e = lane * 8 + k;
-                if (e < E) {
-                    const int n128 = (po[e + 1] - po[e]) / 128;
-                    for (int i = 0; i < n128; i += 2) a.tile_info[nt++] = (po[e] / 128 + i) | (e << 20) | ((i + 1 < n128 ? 1 : 0) << 30);
-                }
-            }
+            for (int k = 0; k < 8; k++) { const int e = lane * 8 + k; if (e < E) base[e] = nt; nt += v[k]; }     // base is free now: first tile of e
             if (lane == 31) *a.ntiles = x;
         }
+        __syncthreads();
+        for (int e = warp; e < E; e += 32) {
+            const int n128 = (po[e + 1] - po[e]) / 128;
+            for (int t = lane; 2 * t < n128; t += 32)
+                a.tile_info[base[e] + t] = (po[e] / 128 + 2 * t) | (e << 20) | ((2 * t + 1 < n128 ? 1 : 0) << 30);
+        }
     }
-    // the out-of-range flag: the other CTAs' findings are read after a second barrier, which also keeps every
-    // CTA's shared memory alive until its neighbours have finished reading the totals
-    perm_cluster_sync();
-    if (crank == 0 && tid == 0) {
-        unsigned b = (unsigned)*sbad;
-        for (uint32_t c = 1; c < csize; c++) { const unsigned t = (unsigned)perm_ld_remote(sbad, c); b = t > b ? t : b; }
+    if (tid == 0) {
+        unsigned b = 0u;
+        for (int c = 0; c < (int)csize; c++) { const unsigned t = (unsigned)rbad[c]; b = t > b ? t : b; }
         // one sort: this thread is the flag's only writer; several sorts: the flag was zeroed before the launch
         if (gridDim.y == 1) *a.bad = (int)b; else if (b) atomicMax(reinterpret_cast<unsigned *>(a.bad), b);
         if (b && a.errword) { a.errword[0] = 100; a.errword[1] = (int)b & ~0x40000000; }
     }
-    perm_cluster_sync();
 }
 
 int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int *perm, int *inv,
@@ -378,11 +382,12 @@ int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int 
     QLMB_REQUIRE(E >= 1 && E <= PERM_EMAX, "perm_build: %d experts (at most %d)", E, PERM_EMAX);
     const int rows = (len + 31) / 32;
     int C = 1;
-    while (C < 8 && (rows + C - 1) / C > 4 * 32) C *= 2;             // about four rows per warp when the cluster may grow
-    QLMB_REQUIRE((rows + C - 1) / C <= PERM_RPT * 32, "perm_build: %d slots exceed one cluster's capacity (%d)", len, 8 * PERM_RPT * 1024);
+    while (C < 8 && (rows + C - 1) / C > 2 * 32) C *= 2;             // two rows per warp while the cluster may grow
+    const int rpw = ((rows + C - 1) / C + 31) / 32;                  // rows per warp
+    QLMB_REQUIRE(rpw <= PERM_RPT, "perm_build: %d slots exceed one cluster's capacity (%d)", len, 8 * PERM_RPT * 1024);
     PermArgs a = {assign, len, E, pad, len + E * (pad - 1), perm, inv, off, counts, tile_info, ntiles, bad_flag,
                   device_error_word(), e_lo, skip, rank_counts, experts_per_rank};
-    const size_t smem = ((size_t)32 * E + 4 * (size_t)E + 2) * sizeof(int);
+    const size_t smem = ((size_t)32 * E + 12 * (size_t)E + 1 + 9) * sizeof(int);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(C, sorts, 1); cfg.blockDim = dim3(PERM_THREADS, 1, 1); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute at[1];
@@ -390,7 +395,13 @@ int perm_build(const int *assign, int N, int E, int K, int merged, int pad, int 
     at[0].val.clusterDim.x = C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     if (sorts > 1) QLMB_CUDA(cudaMemsetAsync(bad_flag, 0, sizeof(int), st));
-    QLMB_CUDA(cudaLaunchKernelEx(&cfg, k_perm_cluster, a, len));
+    cudaError_t le;
+    if (rpw <= 1) le = cudaLaunchKernelEx(&cfg, k_perm_cluster<1>, a, len);
+    else if (rpw <= 2) le = cudaLaunchKernelEx(&cfg, k_perm_cluster<2>, a, len);
+    else if (rpw <= 4) le = cudaLaunchKernelEx(&cfg, k_perm_cluster<4>, a, len);
+    else if (rpw <= 8) le = cudaLaunchKernelEx(&cfg, k_perm_cluster<8>, a, len);
+    else le = cudaLaunchKernelEx(&cfg, k_perm_cluster<16>, a, len);
+    QLMB_CUDA(le);
     QLMB_LAUNCH_CHECK("perm_build");
     return QLMB_OK;
 }
