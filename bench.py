@@ -6,15 +6,21 @@ d_ff 1536, 8192 tokens of bf16 activations per GPU).
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 A step is one qlmb_moe_forward + qlmb_moe_backward over one batch of synthetic
-tokens.  `value` times K steps with inputs resident in HBM (CUDA events, max over
-ranks); `e2e` runs the same calls from pinned HOST buffers with the H2D / D2H
-copies inside the timed region.  FLOPs are counted on routed rows only
-(347.9 GFLOP per step and GPU), never on the zero filler rows.
+tokens.  Inputs are resident in HBM; batches of K steps run back to back (CUDA
+events around every batch, max over ranks) until the timed region is at least
+--min-seconds long: `value` / `ms_per_step` are the mean over that whole region,
+`burst` is its first batch of exactly K steps.  `e2e` runs the same calls from
+pinned HOST buffers with the H2D / D2H copies inside the timed region.  FLOPs are
+counted on routed rows only (347.9 GFLOP per step and GPU), never on the zero
+filler rows.  After the headline the same process measures the training step of
+config 4 and the sharded integer AdamW of config 3 for a few iterations and puts
+them into the line's `secondary` object (--no-secondary skips them).
 --impl reference times the unmodified reference's CPU build (moe_forward +
 moe_backward on the same shapes) on this machine's host cores.
 """
 import argparse
 import ctypes as C
+import hashlib
 import json
 import os
 import subprocess
@@ -44,6 +50,43 @@ def peaks():
     return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, src="fallback")
 
 
+def host_threads():
+    """Host threads the CPU baseline may use: the cores this process may run on.  A launcher
+    (torch.distributed.run) exports OMP_NUM_THREADS=1 for its workers; the baseline is not one of them."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def kernel_sources_digest():
+    """sha256 over the sources of the GEMM engine and the MoE control flow: recorded DRAM traffic is only
+    quoted while these files are the ones the capture was taken with."""
+    h = hashlib.sha256()
+    base = os.path.join(ROOT, "cudalm_c_b200", "csrc")
+    for f in ("qlmb_gemm.cu", "qlmb_gemm.cuh", "qlmb_gemm_pair.cuh", "qlmb_tc.cuh", "qlmb_moe.cu"):
+        with open(os.path.join(base, f), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
+def recorded_traffic():
+    """DRAM bytes per launch from the committed ncu capture of this workload: lines `traffic <kernel> <bytes>` and
+    `sources <digest>` of the summary file.  Returns {} when the kernels' sources changed since."""
+    path = os.path.join(ROOT, "profiles", "k_gemm_pair_dram_traffic.md")
+    out, digest = {}, None
+    try:
+        for ln in open(path):
+            w = ln.split()
+            if len(w) == 3 and w[0] == "traffic":
+                out[w[1]] = float(w[2])
+            elif len(w) == 2 and w[0] == "sources":
+                digest = w[1]
+    except OSError:
+        return {}
+    return out if digest == kernel_sources_digest() else {}
+
+
 class ClockSampler(threading.Thread):
     """SM clock and throttle reasons while the timed region runs (NVML reads, ~1 ms apart;
     nvidia-smi as the fallback when the NVML binding is missing)."""
@@ -53,6 +96,7 @@ class ClockSampler(threading.Thread):
     def __init__(self, index):
         super().__init__(daemon=True)
         self.index, self.mhz, self.max_mhz, self.mask, self.stop_flag, self.active = index, [], None, 0, False, False
+        self.stamp, self.watts = [], []
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -70,41 +114,49 @@ class ClockSampler(threading.Thread):
             try:
                 if self.nv is not None:
                     self.mhz.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                    self.stamp.append(time.perf_counter())
                     self.mask |= int(self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                    self.watts.append(self.nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
                 else:
                     out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=clocks.sm,clocks.max.sm",
                                           "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
                     a, b = [int(x) for x in out.strip().split(",")]
-                    self.mhz.append(a); self.max_mhz = b
+                    self.mhz.append(a); self.max_mhz = b; self.stamp.append(time.perf_counter())
             except Exception:
                 pass
             time.sleep(0.001)
+
+    def median(self, t0=None, t1=None):
+        m = sorted(v for v, t in zip(self.mhz, self.stamp) if (t0 is None or t >= t0) and (t1 is None or t <= t1))
+        return m[len(m) // 2] if m else None
 
     def summary(self):
         if not self.mhz:
             return dict(sm_mhz=None, sm_max_mhz=self.max_mhz, reasons=["unsampled"])
         m = sorted(self.mhz)
         return dict(sm_mhz=m[len(m) // 2], sm_max_mhz=self.max_mhz, samples=len(m),
+                    power_w_max=round(max(self.watts), 1) if self.watts else None,
                     reasons=[n for bit, n in self.REASONS.items() if self.mask & bit])
 
 
-def make_layer(dev, seed):
+def make_layer(dev, seed, weights=None):
     """Synthetic layer of the config-2 shape: expert weights ~ N(0,0.02) quantised
     by the library's own encode kernel (bit-identical to the reference's, see the
-    parity tests), router ~ N(0,0.02), activations ~ N(0,1) in bf16."""
+    parity tests), router ~ N(0,0.02), activations ~ N(0,1) in bf16.  weights = [w1, w3, w2, wr]
+    (fp32, flat) replaces the generated ones."""
     import torch
     from cudalm_c_b200 import moe, qlm
     c = CFG
     gen = torch.Generator(device=dev); gen.manual_seed(seed)
     qs = []
-    for rows, cols in ((c["E"] * c["D"], c["F"]), (c["E"] * c["D"], c["F"]), (c["E"] * c["F"], c["D"])):
+    for wi, (rows, cols) in enumerate(((c["E"] * c["D"], c["F"]), (c["E"] * c["D"], c["F"]), (c["E"] * c["F"], c["D"]))):
         n = rows * cols
         Q = qlm.Qlm([(0, n)], n, dev)
-        P = torch.randn(n, device=dev, generator=gen) * 0.02
+        P = weights[wi].clone() if weights is not None else torch.randn(n, device=dev, generator=gen) * 0.02
         Q.init_from(P, render=False)
         qs.append((Q.d, Q.s))
         del P
-    wr = torch.randn(c["D"], c["E"], device=dev, generator=gen) * 0.02
+    wr = weights[3] if weights is not None else torch.randn(c["D"], c["E"], device=dev, generator=gen) * 0.02
     L = moe.MoeLayerState(c["N"], c["D"], c["F"], c["E"], c["K"], qs[0], qs[1], qs[2], wr, dtype=torch.bfloat16)
     acts = [torch.randn(c["N"], c["D"], device=dev, generator=gen).bfloat16() for _ in range(3)]
     grads = [torch.zeros(c["E"], c["D"], c["F"], device=dev), torch.zeros(c["E"], c["D"], c["F"], device=dev),
@@ -113,9 +165,9 @@ def make_layer(dev, seed):
 
 
 def run_ours(args):
+    import gc
     import torch
     import torch.distributed as dist
-    import cudalm_c_b200 as q
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -123,17 +175,41 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    line = _headline(args, dev, rank, world, local)          # its buffers are gone when it returns
+    gc.collect(); torch.cuda.empty_cache()
+    if not args.no_secondary:
+        # secondary measurements in the same process, so that a scaling run records them at every N
+        sec = run_secondary(args, dev, rank, world, peaks())
+        if line is not None:
+            line["secondary"] = sec
+    if rank == 0:
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(steps=2)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _headline(args, dev, rank, world, local):
+    import torch
+    import torch.distributed as dist
+    import cudalm_c_b200 as q
     lib = q.lib()
     pk = peaks()
     c = CFG
     fn_dev = None
+    parity = None
     if world > 1:
         from cudalm_c_b200 import dist_moe
+        # the same full synthetic weights on every rank (same seed); every rank keeps its experts' slice
+        gen = torch.Generator(device=dev); gen.manual_seed(1234)
+        full = [torch.randn(c["E"] * c["D"] * c["F"], device=dev, generator=gen) * 0.02 for _ in range(3)]
+        full.append(torch.randn(c["D"], c["E"], device=dev, generator=gen) * 0.02)
         if args.ep == "nccl":
-            runner = dist_moe.ExpertParallelLayer(c, dev, rank, world, seed=1234)
+            runner = dist_moe.ExpertParallelLayer(c, dev, rank, world, seed=1234, weights=full)
             parallelism = "ep%d (experts sharded, token all-to-all over NCCL)" % world
         else:
-            runner = dist_moe.PeerExpertParallelLayer(c, dev, rank, world, seed=1234)
+            runner = dist_moe.PeerExpertParallelLayer(c, dev, rank, world, seed=1234, weights=full)
             parallelism = "ep%d (experts sharded, foreign rows read by peer loads inside the row kernels)" % world
         step = runner.step
         fn, fi, dout, out, dfn = runner.fn, runner.fi, runner.dout, runner.out, runner.dfn
@@ -145,7 +221,7 @@ def run_ours(args):
         def step():
             L.forward(fi, fn, out=out)
             L.backward(dout, fn, grads[0], grads[1], grads[2], grads[3], beta=0.0, dfnorm=dfn)
-        launches_per_step = 20
+        launches_per_step = 18
         parallelism = "single"
 
     def barrier():
@@ -157,25 +233,61 @@ def run_ours(args):
         step()
     barrier()
     q.check(lib.qlmb_check_device(None))
+    if world > 1:
+        # correctness of the sharded run, once, before timing: this rank's layer output and input gradient against
+        # the single-call layer that holds all experts on this GPU (rows of an expert GEMM are independent, so the
+        # two must agree bit for bit); every rank checks its own tokens, the verdicts are combined
+        Lr, _, gr = make_layer(dev, 1234, weights=full)
+        o_ref = Lr.forward(fi, fn)
+        d_ref = Lr.backward(dout, fn, gr[0], gr[1], gr[2], gr[3], beta=0.0)
+        torch.cuda.synchronize()
+        okv = torch.tensor([1 if (torch.equal(o_ref, out) and torch.equal(d_ref, dfn)) else 0], device=dev)
+        dist.all_reduce(okv, op=dist.ReduceOp.MIN)
+        parity = "ok: out and dfnorm of every rank bit-identical to the single-call layer with all experts" if int(okv.item()) == 1 \
+            else "MISMATCH against the single-call layer"
+        del Lr, gr, o_ref, d_ref, full
+        torch.cuda.empty_cache()
+        barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # batch 0: exactly --steps steps (the burst figure); then as many more batches as fill --min-seconds
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     barrier()
     sampler.active = True
-    e0.record()
+    w_start = time.perf_counter()
+    ev[0].record()
     for _ in range(args.steps):
         step()
-    e1.record()
+    ev[1].record()
+    torch.cuda.synchronize()
+    w_burst = time.perf_counter()
+    ms0 = ev[0].elapsed_time(ev[1]) / args.steps
+    nb = int(min(2000, max(0, (args.min_seconds * 1e3 - ms0 * args.steps) / max(ms0 * args.steps, 1e-3) + 1)))
+    if world > 1:
+        tnb = torch.tensor([nb], device=dev)
+        dist.all_reduce(tnb, op=dist.ReduceOp.MAX)
+        nb = int(tnb.item())
+    ev += [torch.cuda.Event(enable_timing=True) for _ in range(nb)]
+    for b in range(nb):
+        for _ in range(args.steps):
+            step()
+        ev[2 + b].record()
     barrier()
+    w_end = time.perf_counter()
     sampler.active = False
-    sampler.stop_flag = True
-    ms = e0.elapsed_time(e1) / args.steps
-    t = torch.tensor([ms], device=dev)
+    batch_ms = [ev[0].elapsed_time(ev[1])] + [ev[1 + b].elapsed_time(ev[2 + b]) for b in range(nb)]
+    ms_burst = batch_ms[0] / args.steps
+    ms = sum(batch_ms) / (len(batch_ms) * args.steps)
+    t = torch.tensor([ms, ms_burst], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    ms, ms_burst = float(t[0].item()), float(t[1].item())
     value = world * flops_per_step(c) / (ms * 1e-3) / 1e12
+    burst = dict(value=round(world * flops_per_step(c) / (ms_burst * 1e-3) / 1e12, 2), ms_per_step=round(ms_burst, 4), steps=args.steps,
+                 sm_mhz=sampler.median(w_start, w_burst))
+    region = dict(batches=len(batch_ms), steps_per_batch=args.steps, seconds=round(sum(batch_ms) * 1e-3, 3),
+                  sm_mhz_steady=sampler.median(w_burst, w_end))
 
     # per-kernel durations (events inside the library) over a few extra steps
     roof, kern = None, {}
@@ -200,15 +312,16 @@ def run_ours(args):
               "gemm_wgrad_w2": 2.0 * rows * c["D"] * c["F"]}
         top = max((k for k in kern if k in fl), key=lambda k: kern[k])
         ach = fl[top] / (kern[top] * 1e-3) / 1e12
-        long_run = ms * args.steps > 1000.0
-        peak = pk["tf_sustained"] if long_run else pk["tf_burst"]
-        # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of one ncu capture of this very
-        # workload (profiles/k_gemm_pair_dram_traffic.md); only valid for the default configuration on one GPU
-        ncu_dram = {"gemm_gate_up_swiglu": 183.2e6, "gemm_down": 82.6e6, "gemm_dact_swiglu_bwd": 237.5e6, "gemm_dx": 168.5e6,
-                    "gemm_wgrad_w1": 175.1e6, "gemm_wgrad_w3": 174.6e6, "gemm_wgrad_w2": 174.5e6}
-        traffic = ncu_dram.get(top) if (world == 1 and c == dict(N=8192, D=768, F=1536, E=32, K=2)) else None
+        # the kernels were timed right after a region of a second or more: the burst peak (a GEMM timed alone at the
+        # maximum clock) is the comparator while the SM clock stayed near its maximum, else the sustained one
+        clk, clk_max = sampler.median(w_burst, w_end), sampler.max_mhz
+        held = clk is None or clk_max is None or clk >= 0.9 * clk_max
+        peak = pk["tf_burst"] if held else pk["tf_sustained"]
+        # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu capture of this
+        # very workload; quoted only for the default configuration on one GPU and unchanged kernel sources
+        traffic = recorded_traffic().get(top) if (world == 1 and c == dict(N=8192, D=768, F=1536, E=32, K=2)) else None
         roof = dict(bound="tensor", kernel=top, achieved=round(ach, 1), peak=peak, unit="TFLOP/s", frac=round(ach / peak, 4),
-                    traffic=traffic, peak_kind=("sustained" if long_run else "burst") + " bf16, of " + pk["src"],
+                    traffic=traffic, peak_kind=("burst" if held else "sustained") + " bf16 (SM clock %s of %s MHz over the timed region), of %s" % (clk, clk_max, pk["src"]),
                     kernel_ms={k: round(v, 4) for k, v in sorted(kern.items(), key=lambda kv: -kv[1])},
                     gemm_phase_tflops=round(sum(fl.values()) / (sum(kern[k] for k in fl) * 1e-3) / 1e12, 1))
 
@@ -278,25 +391,129 @@ def run_ours(args):
                    how="copies on two copy streams, device buffers double-buffered; wall clock over drained streams")
     q.check(lib.qlmb_check_device(None))
 
+    sampler.stop_flag = True
+    clocks = sampler.summary()
+    if world > 1:
+        barrier()
+        if hasattr(runner, "close"):
+            runner.close()                               # unmap the peers' windows before the buffers go
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        cpu = cpu_baseline(steps=2)
+    line = None
     if rank == 0:
         line = dict(metric=METRIC, value=round(value, 2), unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                     ms_per_step=round(ms, 4), higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
-                    data="synthetic",
+                    data="synthetic", burst=burst, timed_region=region, parity_check=parity, secondary=None,
                     config=dict(workload="MoE expert FFN layer fwd+bwd, 4-bit weights (BASELINE config 2)", tokens_per_gpu=c["N"],
                                 d_model=c["D"], d_ff=c["F"], experts=c["E"], top_k=c["K"], parallelism=parallelism,
                                 flops_per_step_per_gpu=flops_per_step(c), weight_grad="beta=0 (overwrite; one writer per expert)",
                                 l2="per-step working set ~1.3 GB (arena 447 MB + 453 MB of weight gradients) exceeds the 126 MB L2"),
-                    roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=launches_per_step * args.steps,
-                    clocks=sampler.summary())
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+                    roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=launches_per_step * args.steps * region["batches"],
+                    clocks=clocks)
+    return line
 
 
-def cpu_baseline(steps=2, fast=True):
+def run_secondary(args, dev, rank, world, pk):
+    """After the headline: a few iterations of (1) the training step of BASELINE config 4 (data parallel over the
+    batch, experts sharded: cudalm_c_b200/model.py) and (2) the integer AdamW of config 3 with its groups sharded
+    over the ranks and the digits all-gathered (ZeRO-1 form), so that one scaling run carries all three curves.
+    Efficiency of the training step: the N = 1 step holds and updates all 1.39 G quantised parameters, a rank of an
+    N-rank run only its E/N experts, so tokens/s grows faster than N x the one-GPU figure in the optimizer part;
+    forward + backward time per rank is what weak scaling should hold constant (train_fb_ms)."""
+    import gc
+    import torch
+    import torch.distributed as dist
+    import cudalm_c_b200 as q
+    from cudalm_c_b200 import model, qlm
+    out = {}
+    # ---- (1) training step
+    try:
+        cfg = model.Config()
+        m = model.QlmModel(cfg, dev, seed=1, aux=0.03, rank=rank, world=world)
+        N = cfg.B * cfg.T
+        g = torch.Generator(device="cpu"); g.manual_seed(rank)
+        tok = torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).pin_memory()
+        tgt = torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).pin_memory()
+        tok_d = torch.zeros(N, dtype=torch.int32, device=dev); tgt_d = torch.zeros(N, dtype=torch.int32, device=dev)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        losses = []
+
+        def one(timed):
+            tok_d.copy_(tok, non_blocking=True); tgt_d.copy_(tgt, non_blocking=True)
+            if timed: ev[0].record()
+            m.forward(tok_d)
+            loss = m.backward(tok_d, tgt_d)
+            if timed: ev[1].record()
+            m.update()
+            if timed: ev[2].record()
+            losses.append(float(loss.mean()))
+        for _ in range(3):
+            one(False)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        fb, up = [], []
+        for _ in range(4):
+            one(True)
+            torch.cuda.synchronize()
+            fb.append(ev[0].elapsed_time(ev[1])); up.append(ev[1].elapsed_time(ev[2]))
+        q.check(q.lib().qlmb_check_device(None))
+        t = torch.tensor([sum(fb) / len(fb), sum(up) / len(up)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            for ly in m.layers:
+                ly["moe"].close()
+        fb_ms, up_ms = float(t[0]), float(t[1])
+        out.update(train_tokens_per_s=round(world * N / ((fb_ms + up_ms) * 1e-3), 1), train_ms_per_step=round(fb_ms + up_ms, 3),
+                   train_fb_ms=round(fb_ms, 3), train_update_ms=round(up_ms, 3), train_loss_first=round(losses[0], 4),
+                   train_loss_last=round(losses[-1], 4),
+                   train_config="config 4: L=12 D=768 E=32 top-2 F=1536 V=16384, 8 x 1024 tokens per GPU, dp%d x ep%d, launches issued from the host" % (world, world))
+        del m
+    except Exception as e:                               # a secondary line must not take the headline down
+        out["train_error"] = repr(e)[:200]
+    gc.collect(); torch.cuda.empty_cache()
+    # ---- (2) ZeRO-1 integer AdamW, 125 829 120 parameters in total
+    try:
+        n = 125829120
+        Q = qlm.Qlm([(0, n)], n, dev)
+        gen = torch.Generator(device=dev); gen.manual_seed(3)
+        P = torch.randn(n, device=dev, generator=gen) * 0.02
+        Q.init_from(P, render=False)
+        del P
+        G = torch.randn(n, device=dev, generator=gen) * 1e-3
+        ngrp = n // 128
+        per = ngrp // world
+        gi0 = rank * per
+
+        def one_step(t):
+            Q.step(None, G, 3e-4, 0.9, 0.95, 0.1, t, gi_base=gi0, ng=per)
+            if world > 1:
+                dist.all_gather_into_tensor(Q.d, Q.d[gi0 * 64:(gi0 + per) * 64])
+        for t in range(1, 4):
+            one_step(t)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for t in range(4, 24):
+            one_step(t)
+        e1.record(); torch.cuda.synchronize()
+        tm = torch.tensor([e0.elapsed_time(e1) / 20], device=dev)
+        if world > 1:
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ms = float(tm)
+        out.update(adamw_zero1_gbs=round(n * 11.15625 / (ms * 1e-3) / 1e9, 1), adamw_zero1_ms=round(ms, 4),
+                   adamw_config="config 3: 125 829 120 parameters in total (strong scaling), groups sharded over %d rank(s), packed digits all-gathered in place; 11.15625 B per parameter" % world,
+                   adamw_frac_of_hbm=round(n * 11.15625 / (ms * 1e-3) / 1e9 / (pk["hbm"] * world), 4))
+        del Q, G
+    except Exception as e:
+        out["adamw_error"] = repr(e)[:200]
+    gc.collect(); torch.cuda.empty_cache()
+    return out
+
+
+def cpu_baseline(steps=2, fast=True, warmup=1):
     """The reference's own moe_forward + moe_backward (CPU build, all host threads)
     on the config-2 shapes; weights are the rendered view of encoded N(0,0.02)."""
     import numpy as np
@@ -305,6 +522,7 @@ def cpu_baseline(steps=2, fast=True):
     kind = "reference"
     if ref is None:
         return dict(value=None, unit=UNIT, cores=0, kind="reference", sample="oracle/_ref not built on this machine")
+    ref.set_threads(host_threads())
     c = CFG
     rng = np.random.default_rng(1234)
     L = ref.moe_new(c["N"], c["D"], c["F"], c["E"], c["K"], 0.03)
@@ -321,36 +539,185 @@ def cpu_baseline(steps=2, fast=True):
     P[L.off("wr"):L.off("wr") + c["D"] * c["E"]] = rng.standard_normal(c["D"] * c["E"], dtype=np.float32) * np.float32(0.02)
     for nm in ("f_norm", "f_in", "dout"):
         L.buf(nm, (c["N"], c["D"]))[:] = rng.standard_normal((c["N"], c["D"]), dtype=np.float32)
-    L.forward(); L.backward()                       # warm-up (page faults, thread pool)
+    for _ in range(max(warmup, 1)):
+        L.forward(); L.backward()                   # warm-up (page faults, thread pool)
     t0 = time.perf_counter()
     for _ in range(steps):
         L.forward(); L.backward()
     dt = (time.perf_counter() - t0) / steps
     return dict(value=round(flops_per_step(c) / dt / 1e12, 4), unit=UNIT, cores=ref.threads, kind=kind,
-                sample="%d full steps (8192 tokens) after 1 warm-up, %.2f s/step, reference CPU build, stock flags" % (steps, dt),
+                sample="%d full steps (%d tokens) after %d warm-up, %.2f s/step, reference CPU build (moe_forward + moe_backward), stock flags, %d threads" % (steps, c["N"], max(warmup, 1), dt, ref.threads),
                 ms_per_step=round(dt * 1e3, 1))
 
 
 def run_reference(args):
+    """The reference arm: the reference's own CPU implementation of the path (moe_forward + moe_backward of its CPU
+    build, compiled from its sources into oracle/_ref) on this machine's host cores, the same shapes, --steps timed
+    steps after --warmup.  Under torch.distributed.run rank 0 alone works, with all host threads (the launcher's
+    OMP_NUM_THREADS=1 is meant for its GPU workers)."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 5))
-    cpu = cpu_baseline(steps=steps)
+    steps, warm = max(1, args.steps), max(1, args.warmup)
+    cpu = cpu_baseline(steps=steps, warmup=warm)
     if cpu["value"] is None:
         print(json.dumps(dict(impl="reference", unavailable=cpu["sample"])))
         return
     c = CFG
-    line = dict(impl="reference", metric=METRIC, value=cpu["value"], unit=UNIT, n_gpus=world, steps=steps, warmup=1,
+    line = dict(impl="reference", metric=METRIC, value=cpu["value"], unit=UNIT, n_gpus=world, steps=steps, warmup=warm,
                 ms_per_step=cpu["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32",
                 data="synthetic",
                 config=dict(workload="MoE expert FFN layer fwd+bwd, 4-bit weights (BASELINE config 2)", tokens_per_gpu=c["N"],
-                            d_model=c["D"], d_ff=c["F"], experts=c["E"], top_k=c["K"], parallelism="cpu",
+                            d_model=c["D"], d_ff=c["F"], experts=c["E"], top_k=c["K"], parallelism="cpu, %d threads" % cpu["cores"],
                             flops_per_step_per_gpu=flops_per_step(c)),
                 cpu_baseline=cpu, e2e=dict(value=cpu["value"], unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                 gpu_launches=0)
     print(json.dumps(line))
+
+
+# ---------------------------------------------------------------- CPU baselines of the secondary workloads
+# Each one times the reference's own CPU code for that piece (oracle/_ref, stock flags, all host threads) on a bounded
+# sample of the workload and says what the sample was.  Reported beside the GPU number, not a target.
+def _ref_fast():
+    from oracle import loader
+    ref = loader.reference(exact=False)
+    if ref is not None:
+        ref.set_threads(host_threads())
+    return ref
+
+
+def cpu_linear(M, K, N):
+    """config 1: the three SGEMMs of the reference (g_abt, g_ab, g_atb; cudalm.cu:3133-3202) on the rendered weights."""
+    import numpy as np
+    ref = _ref_fast()
+    if ref is None:
+        return None
+    rng = np.random.default_rng(1)
+    X = rng.standard_normal((M, K), dtype=np.float32); dY = rng.standard_normal((M, N), dtype=np.float32)
+    W = rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)
+    dW = np.zeros((N, K), np.float32)
+    run = lambda: (ref.g_abt(X, W), ref.g_ab(dY, W), ref.g_atb(dY, X, dW))
+    run()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        run()
+    dt = (time.perf_counter() - t0) / 3
+    return dict(value=round(3 * 2.0 * M * K * N / dt / 1e12, 4), unit="TFLOP/s", cores=ref.threads, kind="reference",
+                sample="3 full steps (forward, input gradient, weight gradient as fp32 SGEMMs on the rendered weights), %.1f ms/step" % (dt * 1e3))
+
+
+def cpu_train(cfg):
+    """config 4: gpu_forward + gpu_backward + gpu_adam of the reference's CPU build with QLM on, one step.  The full model
+    needs about 30 GB of host memory; with less available a two-layer slice of the same widths is timed and scaled."""
+    import numpy as np
+    ref = _ref_fast()
+    if ref is None:
+        return None
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:
+        avail = 0
+    L = cfg.L if avail > 64e9 else 2
+    m = ref.model_new(cfg.V, cfg.D, L, cfg.H, cfg.KV, cfg.F, cfg.T, cfg.E, cfg.K, cfg.B, aux=0.03)
+    rng = np.random.default_rng(4)
+    blk = (rng.standard_normal(1 << 24, dtype=np.float32) * np.float32(0.02))
+    for a in range(0, m.np, blk.size):
+        m.P[a:a + blk.size] = blk[:min(blk.size, m.np - a)]
+    m.qlm_init()
+    N = cfg.B * cfg.T
+    tok = rng.integers(0, cfg.V, N).astype(np.int32); tgt = rng.integers(0, cfg.V, N).astype(np.int32)
+    t0 = time.perf_counter()
+    m.forward(tok); m.backward(tgt); m.adam(3e-4, 1)
+    dt = time.perf_counter() - t0
+    scale = cfg.L / L
+    return dict(value=round(N / (dt * scale), 1), unit="tokens/s", cores=ref.threads, kind="reference",
+                sample=("one step of the %d-layer model (8192 tokens), %.1f s" % (L, dt)) +
+                       ("" if L == cfg.L else "; scaled by %g to the 12-layer model (embedding and head counted %g times)" % (scale, scale)))
+
+
+def cpu_decode(cfg, n_prompt):
+    """config 5: the reference's CPU build has no K/V decoder; cmd_run there runs the full forward over the whole
+    context for every new token (cudalm.cu:7431-7443).  Timed: that forward at a context of n_prompt + 3 tokens, B = 1."""
+    import numpy as np
+    ref = _ref_fast()
+    if ref is None:
+        return None
+    T = n_prompt + 3
+    m = ref.model_new(cfg.V, cfg.D, cfg.L, cfg.H, cfg.KV, cfg.F, T, cfg.E, cfg.K, 1, aux=0.0)
+    rng = np.random.default_rng(5)
+    blk = (rng.standard_normal(1 << 24, dtype=np.float32) * np.float32(0.02))
+    for a in range(0, m.np, blk.size):
+        m.P[a:a + blk.size] = blk[:min(blk.size, m.np - a)]
+    tok = rng.integers(0, cfg.V, T).astype(np.int32)
+    m.forward(tok)
+    t0 = time.perf_counter()
+    for _ in range(3):
+        m.forward(tok)
+    dt = (time.perf_counter() - t0) / 3
+    return dict(value=round(1.0 / dt, 2), unit="tokens/s", cores=ref.threads, kind="reference",
+                sample="3 full-context forwards at %d tokens of context, B = 1 (what the reference's CPU generation costs per new token at the start of the continuation; it grows with the context), %.1f ms each" % (T, dt * 1e3))
+
+
+def cpu_gemv(K, N, B):
+    import numpy as np
+    ref = _ref_fast()
+    if ref is None:
+        return None
+    rng = np.random.default_rng(6)
+    W = rng.standard_normal((K, N), dtype=np.float32); X = rng.standard_normal((B, K), dtype=np.float32)
+    ref.g_ab(X, W)
+    t0 = time.perf_counter()
+    for _ in range(5):
+        ref.g_ab(X, W)
+    dt = (time.perf_counter() - t0) / 5
+    return dict(value=round(K * N * 4 / dt / 1e9, 2), unit="GB/s", cores=ref.threads, kind="reference",
+                sample="5 calls of g_ab on the rendered fp32 weights (4 B per weight streamed), %.2f ms each" % (dt * 1e3))
+
+
+def cpu_attn(T, H, KV):
+    import numpy as np
+    ref = _ref_fast()
+    if ref is None:
+        return None
+    rng = np.random.default_rng(7)
+    mk = lambda c: rng.standard_normal((T, c * 64), dtype=np.float32)
+    Q, K_, V, dA = mk(H), mk(KV), mk(KV), mk(H)
+    t0 = time.perf_counter()
+    O, lse = ref.attn_fwd(Q, K_, V, 1, T, H, KV, 64)
+    t1 = time.perf_counter()
+    ref.attn_bwd(Q, K_, V, O, dA, lse, 1, T, H, KV, 64)
+    t2 = time.perf_counter()
+    pairs = H * (T * (T + 1) // 2)
+    return (dict(value=round(2 * 2.0 * pairs * 64 / (t1 - t0) / 1e12, 4), unit="TFLOP/s", cores=ref.threads, kind="reference",
+                 sample="one sequence of the eight (B = 1), forward, %.0f ms" % ((t1 - t0) * 1e3)),
+            dict(value=round(5 * 2.0 * pairs * 64 / (t2 - t1) / 1e12, 4), unit="TFLOP/s", cores=ref.threads, kind="reference",
+                 sample="one sequence of the eight (B = 1), backward, %.0f ms" % ((t2 - t1) * 1e3)))
+
+
+def cpu_state():
+    import numpy as np
+    from oracle import loader
+    ref = _ref_fast()
+    if ref is None:
+        return {}
+    n = 128 * 131072
+    rng = np.random.default_rng(8)
+    sp, nq, ng = loader.make_spans([n])
+    P = rng.standard_normal(n, dtype=np.float32) * np.float32(0.02)
+    d = np.zeros(n // 2, np.int8); r = np.zeros(n, np.int8); sc = np.zeros(ng, np.float32)
+    out = {}
+    for name, fn, bpp in (("encode", lambda: ref.encode(P, d, r, sc, sp), 4 + 1.53125), ("render", lambda: ref.render(P, d, sc, sp), 0.53125 + 4),
+                          ("gnorm", lambda: ref.gnorm(P), 4.0)):
+        fn()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            fn()
+        dt = (time.perf_counter() - t0) / 3
+        out[name] = dict(value=round(n * bpp / dt / 1e9, 2), unit="GB/s", cores=ref.threads, kind="reference",
+                         sample="3 passes over a 16.8 M-parameter span, %.1f ms each" % (dt * 1e3))
+    return out
 
 
 def run_adamw(args):
@@ -490,6 +857,7 @@ def run_linear(args):
             linear.linear_wgrad(dW, dY, X, NK, beta=0.0)
         ms = _time(step, args.steps, args.warmup)
         q.check(q.lib().qlmb_check_device(None))
+        cpu = None if args.no_cpu else cpu_linear(M, K, N)
         tf = flops / (ms * 1e-3) / 1e12
         # bytes per step: fwd X + Y + codes, dgrad dY + dX + codes, wgrad dY + X + dW(fp32)
         byts = (M * K + M * N) * io_bytes * 3 + 2 * N * K * 0.53125 + N * K * 4
@@ -502,7 +870,7 @@ def run_linear(args):
                                             frac=round(tf / pk["tf_burst"], 4), traffic=None, peak_kind="burst bf16, of " + pk["src"],
                                             byte_bound_ms=round(byts / (pk["hbm"] * 1e9) * 1e3, 4),
                                             flop_bound_ms=round(flops / (pk["tf_burst"] * 1e12) * 1e3, 4)),
-                              cpu_baseline=None, gpu_launches=3 * args.steps)))
+                              cpu_baseline=cpu, gpu_launches=3 * args.steps)))
 
 
 def run_attn(args):
@@ -525,6 +893,7 @@ def run_attn(args):
     ms_f = _time(lambda: attn.attn_fwd(Q, K, V, B, T, H, KV), args.steps, args.warmup)
     ms_b = _time(lambda: attn.attn_bwd(Q, K, V, O, dA, lse, B, T, H, KV), args.steps, args.warmup)
     q.check(q.lib().qlmb_check_device(None))
+    cpus = (None, None) if args.no_cpu else (cpu_attn(T, H, KV) or (None, None))
     for name, ms, fl, nl in (("forward", ms_f, f_fwd, 1), ("backward", ms_b, f_bwd, 3)):
         tf = fl / (ms * 1e-3) / 1e12
         print(json.dumps(dict(metric="causal_attention_tflops", value=round(tf, 1), unit="TFLOP/s", n_gpus=1, steps=args.steps,
@@ -535,7 +904,7 @@ def run_attn(args):
                               roofline=dict(bound="tensor", kernel="k_attn_fwd" if nl == 1 else "k_attn_bwd_dkv + k_attn_bwd_dq",
                                             achieved=round(tf, 1), peak=pk["tf_burst"], unit="TFLOP/s",
                                             frac=round(tf / pk["tf_burst"], 4), traffic=None, peak_kind="burst bf16, of " + pk["src"]),
-                              cpu_baseline=None, gpu_launches=nl * args.steps)))
+                              cpu_baseline=cpus[0 if nl == 1 else 1], gpu_launches=nl * args.steps)))
 
 
 def run_train(args):
@@ -628,7 +997,7 @@ def run_train(args):
                                         peak=pk["tf_sustained"], unit="TFLOP/s",
                                         frac=round(flops / (ms * 1e-3) / 1e12 / pk["tf_sustained"], 4),
                                         traffic=None, peak_kind="sustained bf16, of " + pk["src"], model_flops_per_step=flops),
-                          cpu_baseline=None,
+                          cpu_baseline=None if (args.no_cpu or world > 1) else cpu_train(cfg),
                           e2e=dict(value=round(tps, 1), unit="tokens/s", h2d_bytes_per_step=2 * N * 4, d2h_bytes_per_step=4,
                                    how="token ids and targets copied from pinned host memory inside the timed region, mean loss read back every step"),
                           loss_first=round(losses[0], 4), loss_last=round(losses[-1], 4),
@@ -654,6 +1023,8 @@ def run_decode(args):
     cfg = model.Config()
     m = model.QlmModel(cfg, dev, seed=1, aux=0.0)
     n_prompt, n_new, Tm = 128, args.new_tokens, 1024
+    assert n_prompt + n_new + 12 <= Tm, "prompt + new tokens + warm-up and probe steps must fit the cache of %d positions" % Tm
+    cpu_dec = None if args.no_cpu else cpu_decode(cfg, n_prompt)
     for B in [int(x) for x in args.decode_b.split(",")]:
         g = torch.Generator(device="cpu"); g.manual_seed(B)
         ids_h = torch.randint(0, cfg.V, (B, n_prompt), generator=g, dtype=torch.int32).pin_memory()
@@ -705,7 +1076,7 @@ def run_decode(args):
                               roofline=dict(bound="hbm", kernel="whole step (one graph replay)", achieved=round(gbs, 1), peak=pk["hbm"],
                                             unit="GB/s", frac=round(gbs / pk["hbm"], 4), traffic=None, peak_kind="copy, of " + pk["src"],
                                             bytes_per_step=byts),
-                              cpu_baseline=None,
+                              cpu_baseline=cpu_dec if B == 1 else None,
                               e2e=dict(value=round(B * n_new / t_e2e, 1), unit="tokens/s", h2d_bytes_per_step=0,
                                        d2h_bytes_per_step=B * 4, prefill_ms=round(t_prefill * 1e3, 2),
                                        how="host clock over the 256 replays and the read-back of the generated ids; the prompt upload and prefill are timed separately (prefill_ms, includes the first-use set-up of this batch size)"),
@@ -774,6 +1145,7 @@ def run_state(args):
     G = torch.randn(n, device=dev, generator=gen) * 1e-3
     out = torch.zeros(2, device=dev)
     Q.init_from(P, render=False)
+    cpus = {} if args.no_cpu else cpu_state()
     for name, fn, bpp in (("encode", lambda: qlm.qlm_encode(P, Q.d, Q.r, Q.s, Q.spanD, Q.nspan, Q.group, Q.dmax, Q.packed), 4 + 1.53125),
                           ("render", lambda: Q.render(P), 0.53125 + 4),
                           ("gnorm", lambda: qlm.gnorm(G, out=out), 4.0)):
@@ -786,7 +1158,7 @@ def run_state(args):
                                           bytes_per_param=bpp, l2="inputs exceed the 126 MB L2"),
                               roofline=dict(bound="hbm", kernel="k_" + name, achieved=round(gbs, 1), peak=pk["hbm"], unit="GB/s",
                                             frac=round(gbs / pk["hbm"], 4), traffic=None, peak_kind="copy bandwidth, of " + pk["src"]),
-                              cpu_baseline=None, gpu_launches=args.steps)))
+                              cpu_baseline=cpus.get(name), gpu_launches=args.steps)))
     q.check(q.lib().qlmb_check_device(None))
 
 
@@ -797,6 +1169,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--min-seconds", type=float, default=1.2, help="length of the headline's timed region (batches of --steps steps are repeated until it is reached)")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the training-step and ZeRO-1 AdamW measurements after the headline")
     ap.add_argument("--workload", default="moe", choices=["moe", "adamw", "linear", "gemv", "state", "attn", "train", "decode"],
                     help="moe = the headline line; the others print secondary lines: adamw (config 3), linear (config 1), "
                          "gemv (decode building block), state (encode / render / gnorm passes)")

@@ -217,6 +217,12 @@ class Reference:
         L.ref_moe_backward.argtypes = [C.c_void_p]
         self.threads = L.ref_threads()
 
+    def set_threads(self, n):
+        """omp_set_num_threads for the compiled reference (a launcher may have forced OMP_NUM_THREADS=1)."""
+        self.lib.ref_set_threads(C.c_int(int(n)))
+        self.threads = self.lib.ref_threads()
+        return self.threads
+
     def hash(self, x):
         return self.lib.ref_hash(x)
 

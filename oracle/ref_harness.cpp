@@ -19,6 +19,8 @@
 extern "C" {
 
 int ref_threads(void) { return omp_get_max_threads(); }
+/* a launcher may have exported OMP_NUM_THREADS=1 for its workers: the timed baseline sets its own count */
+void ref_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
 
 /* ---- QLM state ops (qlm.cuh:136-178, 377-397, 404-441) ---- */
 void ref_encode(const float *P, signed char *d, signed char *r, float *s, const QSpanD *sp,
