@@ -1095,36 +1095,52 @@ def run_gemv(args):
     torch.cuda.set_device(dev)
     pk = peaks()
     gen = torch.Generator(device=dev); gen.manual_seed(5)
-    for K, N, lay, tag in ((768, 1536, KN, "KN 768x1536 (expert up-projection)"), (4096, 16384, KN, "KN 4096x16384"),
-                           (4096, 16384, NK, "NK 16384x4096")):
+    cases = ((768, 1536, KN, "KN 768x1536 (expert up-projection)"), (4096, 16384, KN, "KN 4096x16384"), (4096, 16384, NK, "NK 16384x4096"))
+    slots = (1, 2, 4, 8, 64)
+    if args.gemv_case:                                   # "KN 4096x16384:1" = one matrix, one slot count (profiler captures)
+        nm, b = args.gemv_case.split(":")
+        cases = tuple(c_ for c_ in cases if c_[3].startswith(nm))
+        slots = (int(b),)
+    for K, N, lay, tag in cases:
+        # several copies of the weights, used in turn, so that a call never finds its weights in the 126 MB L2
+        ncopy = max(2, int(160e6 / (K * N * 0.53125)) + 1)
+        ncopy = min(ncopy, 40)
         W = torch.randn(K * N, device=dev, generator=gen) * 0.02
-        Q = qlm.Qlm([(0, K * N)], K * N, dev); Q.init_from(W, render=False)
-        for B in (1, 8, 64):
+        Qs = []
+        for _ in range(ncopy):
+            Q = qlm.Qlm([(0, K * N)], K * N, dev); Q.init_from(W.clone(), render=False); Qs.append(Q)
+        cpu = None if args.no_cpu else cpu_gemv(K, N, 1)
+        for B in slots:
             X = torch.randn(B, K, device=dev, generator=gen).bfloat16()
             Y = torch.empty(B, N, device=dev, dtype=torch.bfloat16)
-            call = lambda: linear.gemv_decode(X, Q.d, Q.s, lay, N, out=Y)
+            turn = [0]
+
+            def call():
+                Q = Qs[turn[0] % ncopy]; turn[0] += 1
+                linear.gemv_decode(X, Q.d, Q.s, lay, N, out=Y)
             ms_call = _time(call, args.steps, args.warmup)      # one host call per GEMV (host overhead included)
-            # device time: 20 calls captured in a CUDA graph, replayed
+            # device time: 2 rounds over the copies captured in a CUDA graph, replayed
+            ncall = 2 * ncopy
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side):
-                    for _ in range(20):
+                    for _ in range(ncall):
                         call()
             torch.cuda.current_stream().wait_stream(side)
-            ms = _time(graph.replay, max(args.steps // 4, 3), 3) / 20
+            ms = _time(graph.replay, max(args.steps // 4, 3), 3) / ncall
             gbs = K * N * 0.53125 / (ms * 1e-3) / 1e9
             print(json.dumps(dict(metric="decode_gemv_weight_gbs", value=round(gbs, 1), unit="GB/s", n_gpus=1, steps=args.steps,
                                   warmup=max(args.warmup, 3), ms_per_step=round(ms, 5), higher_is_better=True, scaling="weak",
                                   vs_baseline=None, dtype="bf16", data="synthetic",
                                   config=dict(workload="decode GEMV, 4-bit weights " + tag, slots=B,
-                                              timing="20 calls in a replayed CUDA graph; one host call per GEMV takes %.1f us" % (ms_call * 1e3),
-                                              l2="weights %.1f MB per call (the small matrix stays in L2)" % (K * N * 0.53125 / 1e6)),
+                                              timing="%d calls in a replayed CUDA graph; one host call per GEMV takes %.1f us" % (ncall, ms_call * 1e3),
+                                              l2="weights %.1f MB per call, %d copies used in turn (%.0f MB, more than the 126 MB L2)" % (K * N * 0.53125 / 1e6, ncopy, ncopy * K * N * 0.53125 / 1e6)),
                                   roofline=dict(bound="hbm", kernel="k_gemv", achieved=round(gbs, 1), peak=pk["hbm"], unit="GB/s",
                                                 frac=round(gbs / pk["hbm"], 4), traffic=None, peak_kind="copy bandwidth, of " + pk["src"]),
-                                  cpu_baseline=None, gpu_launches=2 * args.steps)))
-        del Q, W
+                                  cpu_baseline=cpu if B == 1 else None, gpu_launches=2 * args.steps)))
+        del Qs, W
     q.check(q.lib().qlmb_check_device(None))
 
 
@@ -1180,6 +1196,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="--workload train: issue every launch from the host instead of replaying forward + backward from a CUDA graph")
     ap.add_argument("--decode-b", default="1,8,64", help="live slots of --workload decode (comma list; BASELINE config 5 has 1,8,64)")
     ap.add_argument("--new-tokens", type=int, default=256, help="generated tokens of --workload decode (256 in BASELINE config 5; fewer for profiler captures)")
+    ap.add_argument("--gemv-case", default="", help="--workload gemv: one case only, e.g. 'KN 4096x16384:1' (matrix tag prefix : slots)")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the 8192 of config 2); smaller values are for profiler captures")
     args = ap.parse_args()
     if args.tokens > 0:

@@ -3,6 +3,7 @@
 // cudalm.cu:7178-7198).  Weight streaming kernels: every code byte is read once
 // from HBM per call, activations sit in shared memory, accumulation is fp32.
 // Results do not depend on scheduling: partial sums are combined in a fixed order.
+#include <stdlib.h>
 #include "qlmb_common.cuh"
 #include "qlmb_internal.h"
 
@@ -170,6 +171,167 @@ __global__ void __launch_bounds__(256, NB == 4 ? 2 : (BT <= 2 ? 4 : 2)) k_gemv_k
             }
         }
     }
+}
+
+// ---- streaming form for codes W[K][N] and up to four activation rows: the whole product in one launch.
+// Block = 32 * CPL output columns (a lane owns CPL = 8 or 16 consecutive columns, one 4- or 8-byte load per row, so a
+// lane's columns share a scale group) x a K slice; warp w takes rows k0 + w, k0 + w + 8, ..., eight of them
+// requested ahead of the eight being multiplied.  The eight warps' sums are combined by a fixed tree in shared
+// memory; with several K slices every block leaves its sums in `part`, takes a ticket for its column block, and the
+// block that draws the last ticket adds the slices in ascending order and writes Y (no second launch, and the order
+// of the additions does not depend on which block came last).
+// Nibbles become floats without a conversion and with few integer-pipe instructions: one three-input logic
+// operation turns two nibbles i and i+4 of a code word into the two bf16 patterns of 136 + d (as the GEMM engine's
+// expansion does); read as ONE fp32 that word is 136 + d_hi + (0x4308 + d_lo) / 65536, and shifted left by 16 it is
+// 136 + d_lo exactly.  Both are multiplied as they are; the constants and the small cross term are taken out of the
+// finished sums with the sum of the multipliers: y_lo = acc_lo - 136 S, y_hi = acc_hi - (136 + 0x4308 / 65536) S -
+// y_lo / 65536, S = sum over the rows of x * scale.  The shift is written as a multiply by a run-time 65536 so that
+// it runs on the multiply-add pipe rather than on the half-rate integer pipe.
+__device__ unsigned g_gemv_ticket[2048];
+
+__device__ __forceinline__ uint32_t nib_pair_f(uint32_t w)
+{
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x43084308, 0x6A;" : "=r"(r) : "r"(w));
+    return r;
+}
+
+template <int BT, int CPL>
+__global__ void __launch_bounds__(256, BT <= 2 ? 3 : 2) k_gemv_stream(void *Y, int dtype, float *part, const void *X, const uint8_t *codes,
+                                                     const float *scales, int B, int K, int N, int kslice, uint32_t k65536)
+{
+    // kslice is a multiple of 64 that divides K: every warp owns kslice / 8 rows, a whole number of batches
+    constexpr int WPL = CPL / 8, CW = 32 * CPL, U = 4;
+    extern __shared__ float gsm[];                       // activations [BT][kslice]; later the reduction tree [4][BT][CW]
+    __shared__ int s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int n0 = blockIdx.x * CW + lane * CPL;
+    const bool live = n0 < N;
+    if (!live) n0 = N - CPL;                             // lanes past the last column repeat valid loads and store nothing
+    const int k0 = blockIdx.y * kslice;
+    const size_t cstep = (size_t)8 * (N / 2), sstep = (size_t)8 * (N / 128);
+    const uint8_t *cp = codes + (size_t)(k0 + warp) * (N / 2) + n0 / 2;
+    const float *sp = scales + (size_t)(k0 + warp) * (N / 128) + n0 / 128;
+    uint32_t w[2][U][WPL];
+    float sc[2][U];
+    auto fetch = [&](int buf) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (WPL == 2) { const uint2 t = __ldcs(reinterpret_cast<const uint2 *>(cp)); w[buf][u][0] = t.x; w[buf][u][WPL - 1] = t.y; }
+            else w[buf][u][0] = __ldcs(reinterpret_cast<const uint32_t *>(cp));
+            sc[buf][u] = __ldg(sp);
+            cp += cstep; sp += sstep;
+        }
+    };
+    fetch(0);                                            // the weights do not depend on the activations: request them first
+    for (int i = threadIdx.x; i < BT * kslice; i += 256) {
+        const int b = i / kslice, k = k0 + i % kslice;
+        gsm[i] = b < B ? ld_x(X, dtype, (size_t)b * K + k) : 0.0f;
+    }
+    __syncthreads();
+    float acc[BT][CPL], s0[BT];
+#pragma unroll
+    for (int b = 0; b < BT; b++) {
+        s0[b] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < CPL; j++) acc[b][j] = 0.0f;
+    }
+    const float *xr = gsm + warp;                        // this warp's activation of the batch's first row
+    auto use = [&](int buf) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            float xv[BT];
+#pragma unroll
+            for (int b = 0; b < BT; b++) { xv[b] = xr[b * kslice + 8 * u] * sc[buf][u]; s0[b] += xv[b]; }
+#pragma unroll
+            for (int i = 0; i < WPL; i++) {
+                const uint32_t ww = w[buf][u][i];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t qq = nib_pair_f(ww >> (4 * j));
+                    const float vlo = __uint_as_float(qq * k65536), vhi = __uint_as_float(qq);
+#pragma unroll
+                    for (int b = 0; b < BT; b++) {
+                        acc[b][8 * i + j] = fmaf(xv[b], vlo, acc[b][8 * i + j]);
+                        acc[b][8 * i + j + 4] = fmaf(xv[b], vhi, acc[b][8 * i + j + 4]);
+                    }
+                }
+            }
+        }
+        xr += 8 * U;
+    };
+    for (int r = 0; r < kslice / 8; r += 2 * U) {        // two batches per round: the buffer indices stay compile-time constants
+        fetch(1);
+        use(0);
+        if (r + 2 * U < kslice / 8) fetch(0);
+        use(1);
+    }
+    float y[BT][CPL];
+#pragma unroll
+    for (int b = 0; b < BT; b++)
+#pragma unroll
+        for (int i = 0; i < WPL; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float lo = acc[b][8 * i + j] - 136.0f * s0[b];
+                y[b][8 * i + j] = lo;
+                y[b][8 * i + j + 4] = acc[b][8 * i + j + 4] - 136.26184082031250f * s0[b] - lo * (1.0f / 65536.0f);
+            }
+    // the eight warps' sums: 4..7 -> 0..3, 2..3 -> 0..1, 1 -> 0 (fixed pairs)
+    __syncthreads();                                     // the activations are no longer needed
+    float *red = gsm;
+#pragma unroll
+    for (int half = 4; half >= 1; half >>= 1) {
+        if (warp >= half && warp < 2 * half) {
+#pragma unroll
+            for (int b = 0; b < BT; b++)
+#pragma unroll
+                for (int c = 0; c < CPL; c++) red[((warp - half) * BT + b) * CW + c * 32 + lane] = y[b][c];
+        }
+        __syncthreads();
+        if (warp < half) {
+#pragma unroll
+            for (int b = 0; b < BT; b++)
+#pragma unroll
+                for (int c = 0; c < CPL; c++) y[b][c] += red[(warp * BT + b) * CW + c * 32 + lane];
+        }
+        __syncthreads();
+    }
+    const int nslice = gridDim.y;
+    if (warp == 0 && live) {
+#pragma unroll
+        for (int b = 0; b < BT; b++) {
+            if (b >= B) break;
+            if (nslice == 1) {
+#pragma unroll
+                for (int c = 0; c < CPL; c++) {
+                    if (dtype == QLMB_BF16) ((bf16 *)Y)[(size_t)b * N + n0 + c] = __float2bfloat16_rn(y[b][c]);
+                    else ((float *)Y)[(size_t)b * N + n0 + c] = y[b][c];
+                }
+            } else {
+                float *dst = part + ((size_t)blockIdx.y * B + b) * N + n0;
+#pragma unroll
+                for (int c = 0; c < CPL; c += 4) __stcg(reinterpret_cast<float4 *>(dst + c), make_float4(y[b][c], y[b][c + 1], y[b][c + 2], y[b][c + 3]));
+            }
+        }
+    }
+    if (nslice == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(&g_gemv_ticket[blockIdx.x], 1u) == (unsigned)(nslice - 1));
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < BT * CW; i += 256) {
+        const int b = i / CW, n = blockIdx.x * CW + i % CW;
+        if (b < B && n < N) {
+            float v = 0.0f;
+            for (int s = 0; s < nslice; s++) v += __ldcg(part + ((size_t)s * B + b) * N + n);
+            if (dtype == QLMB_BF16) ((bf16 *)Y)[(size_t)b * N + n] = __float2bfloat16_rn(v);
+            else ((float *)Y)[(size_t)b * N + n] = v;
+        }
+    }
+    if (threadIdx.x == 0) g_gemv_ticket[blockIdx.x] = 0u;     // ready for the next call on this stream
 }
 
 // ---- codes W[N][K] (groups along K).  A warp owns 4 consecutive output columns (rows of W) and a
@@ -434,6 +596,38 @@ static int gemv_decode_impl(void *Y, const void *X, const int8_t *codes, const f
     if (!fr && B > 4 && dtype == QLMB_BF16 && (K % 64) == 0)
         return qlmb_linear_fwd(Y, X, codes, scales, layout, B, K, N, nullptr, dtype, stream);
     const int bt = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
+    static int stream_on = -1;
+    if (stream_on < 0) { const char *e = getenv("QLMB_GEMV_STREAM"); stream_on = (e && atoi(e) == 0) ? 0 : 1; }
+    if (stream_on && !fr && layout == QLMB_KN && bt <= 4) {
+        // one launch: streaming kernel with the slice sums combined by the last block of every column block
+        const int cpl = N >= 8192 ? 16 : 8, cw = 32 * cpl;
+        const int nb = (N + cw - 1) / cw;
+        QLMB_REQUIRE(nb <= 2048, "qlmb_gemv_decode: N=%d", N);
+        // K slices: a divisor of K / 64 (slices are whole multiples of 64 rows), about six blocks per SM in total
+        const int units = K / 64;
+        int want = (6 * sm_count() + nb / 2) / nb, ns = 1;
+        for (int d = 1; d <= units; d++)
+            if (units % d == 0 && d <= want && (size_t)bt * (K / d) * sizeof(float) <= 64 * 1024) ns = d;
+        while ((size_t)bt * (K / ns) * sizeof(float) > 64 * 1024 && ns < units) { ns++; while (units % ns) ns++; }
+        const int ksl = K / ns;
+        void *ws2 = nullptr;
+        int rc2 = workspace((size_t)ns * B * N * sizeof(float), &ws2);
+        if (rc2) return rc2;
+        size_t sm_b = (size_t)bt * ksl * sizeof(float), red_b = (size_t)4 * bt * cw * sizeof(float);
+        if (red_b > sm_b) sm_b = red_b;
+        const dim3 g(nb, ns);
+#define GS_LAUNCH(BT_, CPL_) \
+        do { \
+            static bool attr_done[64]; int dv = 0; QLMB_CUDA(cudaGetDevice(&dv)); \
+            if (dv >= 0 && dv < 64 && !attr_done[dv]) { QLMB_CUDA(cudaFuncSetAttribute(k_gemv_stream<BT_, CPL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)); attr_done[dv] = true; } \
+            k_gemv_stream<BT_, CPL_><<<g, 256, sm_b, st>>>(Y, dtype, (float *)ws2, X, (const uint8_t *)codes, scales, B, K, N, ksl, 65536u); \
+        } while (0)
+        if (cpl == 16) { if (bt == 1) GS_LAUNCH(1, 16); else if (bt == 2) GS_LAUNCH(2, 16); else GS_LAUNCH(4, 16); }
+        else { if (bt == 1) GS_LAUNCH(1, 8); else if (bt == 2) GS_LAUNCH(2, 8); else GS_LAUNCH(4, 8); }
+#undef GS_LAUNCH
+        QLMB_LAUNCH_CHECK("k_gemv_stream");
+        return QLMB_OK;
+    }
     // K slices: enough blocks to fill the device once, at least 64 rows each,
     // a multiple of 8 rows, and small enough for the activation tile in shared memory
     const int nblk = layout == QLMB_KN ? (N + 255) / 256 : (N + 31) / 32;
