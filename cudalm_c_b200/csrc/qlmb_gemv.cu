@@ -196,12 +196,12 @@ __device__ __forceinline__ uint32_t nib_pair_f(uint32_t w)
     return r;
 }
 
-template <int BT, int CPL>
+template <int BT, int CPL, int U = 4>
 __global__ void __launch_bounds__(256, BT <= 2 ? 3 : 2) k_gemv_stream(void *Y, int dtype, float *part, const void *X, const uint8_t *codes,
                                                      const float *scales, int B, int K, int N, int kslice, uint32_t k65536)
 {
     // kslice is a multiple of 64 that divides K: every warp owns kslice / 8 rows, a whole number of batches
-    constexpr int WPL = CPL / 8, CW = 32 * CPL, U = 4;
+    constexpr int WPL = CPL / 8, CW = 32 * CPL;
     extern __shared__ float gsm[];                       // activations [BT][kslice]; later the reduction tree [4][BT][CW]
     __shared__ int s_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -603,9 +603,12 @@ static int gemv_decode_impl(void *Y, const void *X, const int8_t *codes, const f
         const int cpl = N >= 8192 ? 16 : 8, cw = 32 * cpl;
         const int nb = (N + cw - 1) / cw;
         QLMB_REQUIRE(nb <= 2048, "qlmb_gemv_decode: N=%d", N);
-        // K slices: a divisor of K / 64 (slices are whole multiples of 64 rows), about six blocks per SM in total
+        // K slices: a divisor of K / 64 (slices are whole multiples of 64 rows), about three blocks per SM in total
         const int units = K / 64;
-        int want = (6 * sm_count() + nb / 2) / nb, ns = 1;
+        // (measured at 4096 x 16384, one row: 3 blocks per SM in total 14.3 us, 6: 16.4 us, 12: 18.6 us -- the staging,
+        // the warp tree and the ticket are a fixed cost per block; a ring of bulk copies per row into shared memory
+        // instead of register prefetch was slower, 29 us)
+        int want = (3 * sm_count() + nb / 2) / nb, ns = 1;
         for (int d = 1; d <= units; d++)
             if (units % d == 0 && d <= want && (size_t)bt * (K / d) * sizeof(float) <= 64 * 1024) ns = d;
         while ((size_t)bt * (K / ns) * sizeof(float) > 64 * 1024 && ns < units) { ns++; while (units % ns) ns++; }
