@@ -334,6 +334,428 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 3 : 2) k_gemv_stream(void *Y, i
     if (threadIdx.x == 0) g_gemv_ticket[blockIdx.x] = 0u;     // ready for the next call on this stream
 }
 
+// ---- up to 64 rows against one pass over the weights: groups of eight rows.
+// A decode step with more than four live slots used to send every output row to its own blocks (each re-reading the
+// matrix from L2) or, for the experts, through the 256-row tensor-core tiles (a few routed rows per expert in a
+// 128-row tile).  Here a block owns 256 output columns x a K slice x a GROUP of up to eight rows that share a
+// matrix: the weights are expanded once per group and multiplied with eight activation values (64 fp32 multiply-adds
+// per code word), the same arithmetic as k_gemv_stream.  Two ways to form the groups:
+//   dense   rows b of a batch B against a stack of nmat matrices of one shape (q, k, v; wo): group z = (m, g),
+//           rows 8g .. 8g+7, output row m * B + b
+//   routed  the K*N routed slots of a decode step sorted by expert (perm / off of the permutation kernel): expert e's
+//           slots in groups of eight; a slot s reads activation row s % ntok (gate, up) or s (down) and writes
+//           partial row s (+ R for the second stack of matrices: gate and up in one launch)
+// part[ks][row][n] receives the slice sums; the finish kernels are the ones of the one-row path.
+struct Rows8 {
+    float *part; const void *X; int x_dtype; int K, N, kslice;
+    const uint8_t *codes; const float *scales; size_t e_codes, e_scales;
+    const uint8_t *codes2; const float *scales2;         // routed: second stack for groups z >= zdual
+    int B, nmat, rows_out;                               // dense: batch and stack; rows_out = rows of `part` per slice
+    const int *perm, *off; int E, ntok, x_by_token, zdual, R;   // routed (perm != nullptr)
+    const float *gamma;                                  // dense: rows are normalised on the way in (rinv * gamma, bf16)
+    uint32_t k65536;
+};
+
+__global__ void __launch_bounds__(256, 2) k_gemv_rows8(const __grid_constant__ Rows8 a)
+{
+    constexpr int BT = 8, CPL = 8, CW = 256, U = 4;
+    extern __shared__ float gsm[];                       // activations [BT][kslice]; later the reduction tree [4][BT][CW]
+    __shared__ int s_n, s_mat, s_x[BT], s_o[BT];
+    __shared__ float s_rinv[BT];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kslice = a.kslice, K = a.K, N = a.N;
+    if (threadIdx.x == 0) {
+        int n = 0, mat = 0;
+        if (!a.perm) {
+            const int G = (a.B + BT - 1) / BT;
+            const int m = blockIdx.z / G, g = blockIdx.z % G;
+            n = a.B - g * BT < BT ? a.B - g * BT : BT;
+            mat = m;
+            for (int i = 0; i < n; i++) { s_x[i] = g * BT + i; s_o[i] = m * a.B + g * BT + i; }
+        } else {
+            int z = blockIdx.z, second = 0;
+            if (a.zdual && z >= a.zdual) { z -= a.zdual; second = 1; }
+            for (int e = 0; e < a.E; e++) {
+                const int c = a.off[e + 1] - a.off[e], ng = (c + BT - 1) / BT;
+                if (z < ng) {
+                    n = c - z * BT < BT ? c - z * BT : BT;
+                    mat = e | (second << 16);
+                    for (int i = 0; i < n; i++) {
+                        const int sl = a.perm[a.off[e] + z * BT + i];
+                        s_x[i] = a.x_by_token ? sl % a.ntok : sl;
+                        s_o[i] = sl + second * a.R;
+                    }
+                    break;
+                }
+                z -= ng;
+            }
+        }
+        s_n = n; s_mat = mat;
+    }
+    __syncthreads();
+    const int nrow = s_n;
+    if (nrow == 0) return;
+    const int mat = s_mat & 0xffff, second = s_mat >> 16;
+    const uint8_t *codes = (second ? a.codes2 : a.codes) + (size_t)mat * a.e_codes;
+    const float *scales = (second ? a.scales2 : a.scales) + (size_t)mat * a.e_scales;
+    int n0 = blockIdx.x * CW + lane * CPL;
+    const bool live = n0 < N;
+    if (!live) n0 = N - CPL;
+    const int k0 = blockIdx.y * kslice;
+    const size_t cstep = (size_t)8 * (N / 2), sstep = (size_t)8 * (N / 128);
+    const uint8_t *cp = codes + (size_t)(k0 + warp) * (N / 2) + n0 / 2;
+    const float *sp = scales + (size_t)(k0 + warp) * (N / 128) + n0 / 128;
+    uint32_t w[2][U];
+    float sc[2][U];
+    auto fetch = [&](int buf) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            w[buf][u] = __ldg(reinterpret_cast<const uint32_t *>(cp));
+            sc[buf][u] = __ldg(sp);
+            cp += cstep; sp += sstep;
+        }
+    };
+    fetch(0);
+    if (a.gamma) {                                       // warp w: 1 / rms of row w over the whole K
+        if (warp < nrow) {
+            float ss = 0.0f;
+            for (int k = lane; k < K; k += 32) { const float x = ld_x(a.X, a.x_dtype, (size_t)s_x[warp] * K + k); ss += x * x; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) s_rinv[warp] = 1.0f / sqrtf(ss / (float)K + 1e-5f);
+        }
+        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < BT * kslice; i += 256) {
+        const int b = i / kslice, k = k0 + i % kslice;
+        float x = 0.0f;
+        if (b < nrow) {
+            x = ld_x(a.X, a.x_dtype, (size_t)s_x[b] * K + k);
+            if (a.gamma) x = __bfloat162float(__float2bfloat16_rn(x * s_rinv[b] * a.gamma[k]));
+        }
+        gsm[i] = x;
+    }
+    __syncthreads();
+    float acc[BT][CPL], s0[BT];
+#pragma unroll
+    for (int b = 0; b < BT; b++) {
+        s0[b] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < CPL; j++) acc[b][j] = 0.0f;
+    }
+    const float *xr = gsm + warp;
+    const uint32_t k65536 = a.k65536;
+    auto use = [&](int buf) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            float xv[BT];
+#pragma unroll
+            for (int b = 0; b < BT; b++) { xv[b] = xr[b * kslice + 8 * u] * sc[buf][u]; s0[b] += xv[b]; }
+            const uint32_t ww = w[buf][u];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t qq = nib_pair_f(ww >> (4 * j));
+                const float vlo = __uint_as_float(qq * k65536), vhi = __uint_as_float(qq);
+#pragma unroll
+                for (int b = 0; b < BT; b++) {
+                    acc[b][j] = fmaf(xv[b], vlo, acc[b][j]);
+                    acc[b][j + 4] = fmaf(xv[b], vhi, acc[b][j + 4]);
+                }
+            }
+        }
+        xr += 8 * U;
+    };
+    for (int r = 0; r < kslice / 8; r += 2 * U) {
+        fetch(1);
+        use(0);
+        if (r + 2 * U < kslice / 8) fetch(0);
+        use(1);
+    }
+#pragma unroll
+    for (int b = 0; b < BT; b++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float lo = acc[b][j] - 136.0f * s0[b];
+            acc[b][j] = lo;
+            acc[b][j + 4] = acc[b][j + 4] - 136.26184082031250f * s0[b] - lo * (1.0f / 65536.0f);
+        }
+    __syncthreads();
+    float *red = gsm;
+#pragma unroll
+    for (int half = 4; half >= 1; half >>= 1) {
+        if (warp >= half && warp < 2 * half) {
+#pragma unroll
+            for (int b = 0; b < BT; b++)
+#pragma unroll
+                for (int c = 0; c < CPL; c++) red[((warp - half) * BT + b) * CW + c * 32 + lane] = acc[b][c];
+        }
+        __syncthreads();
+        if (warp < half) {
+#pragma unroll
+            for (int b = 0; b < BT; b++)
+#pragma unroll
+                for (int c = 0; c < CPL; c++) acc[b][c] += red[(warp * BT + b) * CW + c * 32 + lane];
+        }
+        __syncthreads();
+    }
+    if (warp == 0 && live) {
+#pragma unroll
+        for (int b = 0; b < BT; b++) {
+            if (b < nrow) {
+                float *dst = a.part + ((size_t)blockIdx.y * a.rows_out + s_o[b]) * N + n0;
+                *reinterpret_cast<float4 *>(dst) = make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
+                *reinterpret_cast<float4 *>(dst + 4) = make_float4(acc[b][4], acc[b][5], acc[b][6], acc[b][7]);
+            }
+        }
+    }
+}
+
+// ---- the same groups with the multiplies on the warp-level tensor-core instruction (mma.sync m16n8k16, bf16 operands,
+// fp32 accumulators), operands straight from registers.  k_gemv_rows8 spends 64 fp32 multiply-adds per code word
+// on eight rows; here a group holds sixteen (or thirty-two) rows and a code word costs the expansion plus a quarter
+// of eight MMAs.  tcgen05.mma takes its operands from shared memory, which for a kernel that streams every weight
+// exactly once would add a store, a proxy fence and a barrier round trip per stage; the register form needs none.
+// Warp = 64 output columns x the K slice; lane (g = lane / 4, t = lane % 4) loads the code word of columns 8g .. 8g+7
+// for the rows 2t, 2t+1, 2t+8, 2t+9 of every 16-row step, expands it to exact bf16 digits (d = (136 + d) - 136),
+// and pairs the rows with byte permutes into the B fragments of eight MMAs: MMA c uses column 8q + c of the tile
+// for q = 0..7.  The group scale of a row (one per row for the 64 columns, which lie in one group of 128) multiplies
+// the activations: A = bf16(x * bf16(s)), the rounding the GEMM engine applies to its rendered weights.
+__device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// four registers of exact bf16 digit pairs (elements j and j + 4 of the word in register j)
+__device__ __forceinline__ void digits_bf16(uint32_t w, uint32_t q[4])
+{
+    const uint32_t k136 = 0x43084308u;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        uint32_t x = nib_pair_f(w >> (4 * j));
+        __nv_bfloat162 v = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&x), *reinterpret_cast<const __nv_bfloat162 *>(&k136));
+        q[j] = *reinterpret_cast<uint32_t *>(&v);
+    }
+}
+
+template <int MT>
+__global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) k_gemv_mma(const __grid_constant__ Rows8 a)
+{
+    constexpr int GR = 16 * MT, CW = 512, PADK = 8;
+    extern __shared__ __align__(16) uint8_t msm[];       // activations bf16 [GR][kslice + PADK], then scales [kslice][4]
+    __shared__ int s_n, s_mat, s_x[GR], s_o[GR];
+    __shared__ float s_rinv[GR];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int kslice = a.kslice, K = a.K, N = a.N, ldx = kslice + PADK;
+    bf16 *xs = reinterpret_cast<bf16 *>(msm);
+    if (threadIdx.x == 0) {
+        int n = 0, mat = 0;
+        if (!a.perm) {
+            const int G = (a.B + GR - 1) / GR;
+            const int m = blockIdx.z / G, gg = blockIdx.z % G;
+            n = a.B - gg * GR < GR ? a.B - gg * GR : GR;
+            mat = m;
+            for (int i = 0; i < n; i++) { s_x[i] = gg * GR + i; s_o[i] = m * a.B + gg * GR + i; }
+        } else {
+            int z = blockIdx.z, second = 0;
+            if (a.zdual && z >= a.zdual) { z -= a.zdual; second = 1; }
+            for (int e = 0; e < a.E; e++) {
+                const int c = a.off[e + 1] - a.off[e], ng = (c + GR - 1) / GR;
+                if (z < ng) {
+                    n = c - z * GR < GR ? c - z * GR : GR;
+                    mat = e | (second << 16);
+                    for (int i = 0; i < n; i++) {
+                        const int sl = a.perm[a.off[e] + z * GR + i];
+                        s_x[i] = a.x_by_token ? sl % a.ntok : sl;
+                        s_o[i] = sl + second * a.R;
+                    }
+                    break;
+                }
+                z -= ng;
+            }
+        }
+        s_n = n; s_mat = mat;
+    }
+    __syncthreads();
+    const int nrow = s_n;
+    if (nrow == 0) return;
+    const int mat = s_mat & 0xffff, second = s_mat >> 16;
+    const uint8_t *codes = (second ? a.codes2 : a.codes) + (size_t)mat * a.e_codes;
+    const float *scales = (second ? a.scales2 : a.scales) + (size_t)mat * a.e_scales;
+    const int c0 = blockIdx.x * CW + warp * 64;          // this warp's 64 columns
+    const bool live = c0 < N;
+    const int cc = live ? c0 : N - 64;
+    const int k0 = blockIdx.y * kslice;
+    const size_t crow = (size_t)(N / 2), srow = (size_t)(N / 128);
+    // lane's rows of a step: 2t, 2t+1, 2t+8, 2t+9; four steps (sixteen code words) are kept in flight per lane
+    const uint8_t *cp = codes + (size_t)(k0 + 2 * t) * crow + (cc + 8 * g) / 2;
+    uint32_t w[4][4];
+    auto fetch = [&](int slot) {
+        w[slot][0] = __ldg(reinterpret_cast<const uint32_t *>(cp));
+        w[slot][1] = __ldg(reinterpret_cast<const uint32_t *>(cp + crow));
+        w[slot][2] = __ldg(reinterpret_cast<const uint32_t *>(cp + 8 * crow));
+        w[slot][3] = __ldg(reinterpret_cast<const uint32_t *>(cp + 9 * crow));
+        cp += 16 * crow;
+    };
+    const int steps = kslice / 16;                       // a multiple of four: kslice is a multiple of 64
+#pragma unroll
+    for (int u = 0; u < 4; u++) fetch(u);
+    // the slice's group scales for the block's four column groups: [kslice][4] floats behind the activations
+    float *ssc = reinterpret_cast<float *>(msm + (size_t)GR * ldx * sizeof(bf16));
+    {
+        const int g0 = blockIdx.x * (CW / 128), gmax = N / 128 - 1;
+        for (int i = threadIdx.x; i < kslice * 4; i += 256) {
+            const int gq = g0 + (i & 3) < gmax ? g0 + (i & 3) : gmax;
+            ssc[i] = __ldg(scales + (size_t)(k0 + (i >> 2)) * srow + gq);
+        }
+    }
+    if (a.gamma) {                                       // 1 / rms of every row over the whole K: warp w takes rows w, w + 8, ...
+        for (int r = warp; r < nrow; r += 8) {
+            float ss = 0.0f;
+            for (int k = lane; k < K; k += 32) { const float x = ld_x(a.X, a.x_dtype, (size_t)s_x[r] * K + k); ss += x * x; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) s_rinv[r] = 1.0f / sqrtf(ss / (float)K + 1e-5f);
+        }
+        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < GR * kslice; i += 256) {
+        const int b = i / kslice, kk = i % kslice;
+        float x = 0.0f;
+        if (b < nrow) {
+            x = ld_x(a.X, a.x_dtype, (size_t)s_x[b] * K + k0 + kk);
+            if (a.gamma) x = x * s_rinv[b] * a.gamma[k0 + kk];
+        }
+        xs[b * ldx + kk] = __float2bfloat16_rn(x);
+    }
+    __syncthreads();
+    float acc[MT][8][4];
+#pragma unroll
+    for (int m = 0; m < MT; m++)
+#pragma unroll
+        for (int c = 0; c < 8; c++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[m][c][i] = 0.0f;
+    const bf16 *xa = xs + g * ldx + 2 * t;               // A fragment of step 0: rows g, g + 8 (per 16-row tile), columns 2t.., 2t + 8..
+    const float *sl = ssc + (2 * t) * 4 + (warp >> 1);   // scale of the lane's first row of step 0 for this warp's column group
+    auto use = [&](int slot) {
+        uint32_t q[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) digits_bf16(w[slot][r], q[r]);
+        const __nv_bfloat162 s01 = __floats2bfloat162_rn(sl[0], sl[4]), s23 = __floats2bfloat162_rn(sl[32], sl[36]);
+        sl += 64;
+        uint32_t af[MT][4];
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            const bf16 *p = xa + m * 16 * ldx;
+            __nv_bfloat162 a0 = *reinterpret_cast<const __nv_bfloat162 *>(p), a1 = *reinterpret_cast<const __nv_bfloat162 *>(p + 8 * ldx);
+            __nv_bfloat162 a2 = *reinterpret_cast<const __nv_bfloat162 *>(p + 8), a3 = *reinterpret_cast<const __nv_bfloat162 *>(p + 8 * ldx + 8);
+            a0 = __hmul2(a0, s01); a1 = __hmul2(a1, s01); a2 = __hmul2(a2, s23); a3 = __hmul2(a3, s23);
+            af[m][0] = *reinterpret_cast<uint32_t *>(&a0); af[m][1] = *reinterpret_cast<uint32_t *>(&a1);
+            af[m][2] = *reinterpret_cast<uint32_t *>(&a2); af[m][3] = *reinterpret_cast<uint32_t *>(&a3);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // column j: the low halves of rows (2t, 2t+1) and (2t+8, 2t+9); column j + 4: the high halves
+            const uint32_t b0l = __byte_perm(q[0][j], q[1][j], 0x5410), b1l = __byte_perm(q[2][j], q[3][j], 0x5410);
+            const uint32_t b0h = __byte_perm(q[0][j], q[1][j], 0x7632), b1h = __byte_perm(q[2][j], q[3][j], 0x7632);
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                mma_bf16_16816(acc[m][j], af[m], b0l, b1l);
+                mma_bf16_16816(acc[m][j + 4], af[m], b0h, b1h);
+            }
+        }
+        xa += 16;
+    };
+    for (int i = 0; i < steps; i += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            use(u);
+            if (i + u + 4 < steps) fetch(u);
+        }
+    }
+    if (!live) return;
+    // acc[m][c][0..1]: row 16m + g, columns c0 + 8 (2t) + c and c0 + 8 (2t + 1) + c; [2..3]: row 16m + g + 8
+#pragma unroll
+    for (int m = 0; m < MT; m++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int r = 16 * m + g + 8 * h;
+            if (r < nrow) {
+                float *dst = a.part + ((size_t)blockIdx.y * a.rows_out + s_o[r]) * N + c0 + 16 * t;
+#pragma unroll
+                for (int v = 0; v < 2; v++) {
+                    *reinterpret_cast<float4 *>(dst + 8 * v) = make_float4(acc[m][0][2 * h + v], acc[m][1][2 * h + v], acc[m][2][2 * h + v], acc[m][3][2 * h + v]);
+                    *reinterpret_cast<float4 *>(dst + 8 * v + 4) = make_float4(acc[m][4][2 * h + v], acc[m][5][2 * h + v], acc[m][6][2 * h + v], acc[m][7][2 * h + v]);
+                }
+            }
+        }
+}
+
+// K slices of a k_gemv_rows8 launch with nz groups: a divisor of K / 64, about three blocks per SM in total
+static int rows8_slices(int K, int N, int nz)
+{
+    const int nb = (N + 255) / 256, units = K / 64;
+    int want = (3 * sm_count() + nb * nz / 2) / (nb * nz), ns = 1;
+    if (want < 1) want = 1;
+    for (int d = 1; d <= units; d++)
+        if (units % d == 0 && d <= want) ns = d;
+    while ((size_t)8 * (K / ns) * sizeof(float) > 48 * 1024 && ns < units) { ns++; while (units % ns) ns++; }
+    return ns;
+}
+// launches k_gemv_rows8 over nz groups (grid.z) and ns K slices; a.part holds ns * a.rows_out * N floats
+static int rows8_launch(Rows8 a, int nz, int ns, cudaStream_t st)
+{
+    const int nb = (a.N + 255) / 256;
+    a.kslice = a.K / ns;
+    a.k65536 = 65536u;
+    size_t sm_b = (size_t)8 * a.kslice * sizeof(float), red_b = (size_t)4 * 8 * 256 * sizeof(float);
+    if (red_b > sm_b) sm_b = red_b;
+    static bool attr_done[64];
+    int dv = 0;
+    QLMB_CUDA(cudaGetDevice(&dv));
+    if (dv >= 0 && dv < 64 && !attr_done[dv]) {
+        QLMB_CUDA(cudaFuncSetAttribute(k_gemv_rows8, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        attr_done[dv] = true;
+    }
+    k_gemv_rows8<<<dim3(nb, ns, nz), 256, sm_b, st>>>(a);
+    QLMB_LAUNCH_CHECK("k_gemv_rows8");
+    return QLMB_OK;
+}
+
+// K slices of a k_gemv_mma launch with nz groups of 16 * mt rows: a divisor of K / 64 such that the activation tile
+// fits 64 KiB of shared memory, about two blocks per SM in total
+static int mma_slices(int K, int N, int nz, int mt)
+{
+    const int nb = (N + 511) / 512, units = K / 64, kmax = mt == 1 ? 1024 : 512;
+    int want = (2 * sm_count() + nb * nz / 2) / (nb * nz), best = 0, smallest = 0;
+    if (want < 1) want = 1;
+    for (int d = 1; d <= units; d++) {
+        if (units % d || K / d > kmax) continue;
+        if (!smallest) smallest = d;
+        if (d <= want) best = d;
+    }
+    return best ? best : smallest;
+}
+static int mma_launch(Rows8 a, int nz, int ns, int mt, cudaStream_t st)
+{
+    const int nb = (a.N + 511) / 512;
+    a.kslice = a.K / ns;
+    a.k65536 = 65536u;
+    const size_t sm_b = (size_t)16 * mt * (a.kslice + 8) * sizeof(bf16) + (size_t)a.kslice * 4 * sizeof(float);
+    static bool attr_done[64];
+    int dv = 0;
+    QLMB_CUDA(cudaGetDevice(&dv));
+    if (dv >= 0 && dv < 64 && !attr_done[dv]) {
+        QLMB_CUDA(cudaFuncSetAttribute(k_gemv_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        QLMB_CUDA(cudaFuncSetAttribute(k_gemv_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        attr_done[dv] = true;
+    }
+    if (mt == 1) k_gemv_mma<1><<<dim3(nb, ns, nz), 256, sm_b, st>>>(a);
+    else k_gemv_mma<2><<<dim3(nb, ns, nz), 256, sm_b, st>>>(a);
+    QLMB_LAUNCH_CHECK("k_gemv_mma");
+    return QLMB_OK;
+}
+
 // ---- codes W[N][K] (groups along K).  A warp owns 4 consecutive output columns (rows of W) and a
 // K slice; lanes stride over the code words of the slice, 4 words (one per column) per step share the
 // activation values; the scale multiplies the 8-element partial dot product of each word.
@@ -524,12 +946,40 @@ __global__ void __launch_bounds__(256) k_gemv_finish_combine(bf16 *out, const bf
     out[i] = __float2bfloat16_rn(acc);
 }
 
-// Experts of a decode step with at most 64 routed rows: three routed GEMVs that read only the chosen experts'
+// Experts of a decode step with at most 128 routed rows: three routed GEMVs that read only the chosen experts'
 // codes (W1, W3: [E][D][F]; W2: [E][F][D]), SwiGLU and the gate-weighted combination in the slice-sum kernels.
 int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, const void *f_norm, const int *assign,
-                       const float *gate, cudaStream_t st)
+                       const float *gate, cudaStream_t st, int *perm, int *off, int *counts, int *bad)
 {
     const int N = L->N, D = L->D, F = L->F, K = L->K, R = K * N;
+    if (R > 16 && perm && off && bad) {
+        // many routed rows: sort the slots by expert once, then every expert's matrices are read once per group of
+        // sixteen of its slots instead of once per slot
+        int rc = perm_build(assign, N, L->E, K, 1, 1, perm, nullptr, off, counts, bad, nullptr, nullptr, nullptr, st);
+        if (rc) return rc;
+        const int zmax = L->E + R / 16;                  // sum over the experts of ceil(count / 16) never exceeds this
+        const int ns1 = mma_slices(D, F, 2 * L->E, 1), ns2 = mma_slices(F, D, L->E, 1);
+        const size_t pg_n = (size_t)ns1 * 2 * R * F, pd_n = (size_t)ns2 * R * D;
+        void *ws = nullptr;
+        if ((rc = workspace((pg_n + pd_n) * sizeof(float) + (size_t)R * F * sizeof(bf16) + 256, &ws))) return rc;
+        float *pg = (float *)ws, *pd = pg + pg_n;
+        bf16 *act = (bf16 *)(pd + pd_n);
+        Rows8 a = {};
+        a.part = pg; a.X = f_norm; a.x_dtype = QLMB_BF16; a.K = D; a.N = F;
+        a.codes = (const uint8_t *)L->w1_codes; a.scales = L->w1_scales; a.codes2 = (const uint8_t *)L->w3_codes; a.scales2 = L->w3_scales;
+        a.e_codes = (size_t)D * F / 2; a.e_scales = (size_t)D * F / 128;
+        a.rows_out = 2 * R; a.perm = perm; a.off = off; a.E = L->E; a.ntok = N; a.x_by_token = 1; a.zdual = zmax; a.R = R;
+        if ((rc = mma_launch(a, 2 * zmax, ns1, 1, st))) return rc;
+        k_gemv_finish_swiglu<<<(unsigned)(((size_t)R * F + 255) / 256), 256, 0, st>>>(act, pg, pg + (size_t)R * F, ns1, (size_t)R * F, (size_t)2 * R * F);
+        Rows8 b = {};
+        b.part = pd; b.X = act; b.x_dtype = QLMB_BF16; b.K = F; b.N = D;
+        b.codes = (const uint8_t *)L->w2_codes; b.scales = L->w2_scales; b.e_codes = (size_t)D * F / 2; b.e_scales = (size_t)D * F / 128;
+        b.rows_out = R; b.perm = perm; b.off = off; b.E = L->E; b.ntok = N; b.x_by_token = 0; b.zdual = 0; b.R = R;
+        if ((rc = mma_launch(b, zmax, ns2, 1, st))) return rc;
+        k_gemv_finish_combine<<<(unsigned)(((size_t)N * D + 255) / 256), 256, 0, st>>>((bf16 *)out, (const bf16 *)f_in, pd, gate, ns2, N, K, D);
+        QLMB_LAUNCH_CHECK("moe_decode_experts");
+        return QLMB_OK;
+    }
     auto slices = [](int Kdim, int Ncols, int rows, int &kslice, int &nslice) {
         const int nblk = (Ncols + 255) / 256;
         nslice = (4 * sm_count()) / (nblk * rows);
@@ -593,6 +1043,24 @@ static int gemv_decode_impl(void *Y, const void *X, const int8_t *codes, const f
     cudaStream_t st = as_stream(stream);
     // more than 4 live slots with bf16 activations: the tensor-core engine streams the weights
     // faster than fp32 FMAs can consume them (fp32 activations keep the exact fp32 path)
+    if (layout == QLMB_KN && B > 4) {
+        // groups of eight rows per pass over the weights (fp32 multiply-adds; the 256-row tensor-core tiles would be
+        // seven eighths padding for a handful of rows)
+        const bool tc = dtype == QLMB_BF16 && (N % 64) == 0;
+        const int mt = B > 16 ? 2 : 1;
+        const int nz = tc ? (B + 16 * mt - 1) / (16 * mt) : (B + 7) / 8, ns = tc ? mma_slices(K, N, nz, mt) : rows8_slices(K, N, nz);
+        void *wsr = nullptr;
+        int rcr = workspace((size_t)ns * B * N * sizeof(float), &wsr);
+        if (rcr) return rcr;
+        Rows8 a = {};
+        a.part = (float *)wsr; a.X = X; a.x_dtype = dtype; a.K = K; a.N = N;
+        a.codes = (const uint8_t *)codes; a.scales = scales; a.B = B; a.nmat = 1; a.rows_out = B;
+        if ((rcr = tc ? mma_launch(a, nz, ns, mt, st) : rows8_launch(a, nz, ns, st))) return rcr;
+        if (fr) k_gemv_finish_res_norm<<<B, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, a.part, ns, B, N, (const bf16 *)fr->res, fr->gamma);
+        else k_gemv_finish<<<(unsigned)(((size_t)B * N + 255) / 256), 256, 0, st>>>(Y, dtype, a.part, ns, (size_t)B * N);
+        QLMB_LAUNCH_CHECK("qlmb_gemv_decode");
+        return QLMB_OK;
+    }
     if (!fr && B > 4 && dtype == QLMB_BF16 && (K % 64) == 0)
         return qlmb_linear_fwd(Y, X, codes, scales, layout, B, K, N, nullptr, dtype, stream);
     const int bt = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
@@ -690,11 +1158,22 @@ static int gemv_stack_impl(void *Y, const void *X, const int8_t *codes, const fl
     if (nslice < 1) nslice = 1;
     int kslice = ((K + nslice - 1) / nslice + 127) / 128 * 128;
     nslice = (K + kslice - 1) / kslice;
+    const bool groups = B > 4;                           // more than four rows: groups share one pass over a matrix
+    const bool tc = groups && dtype == QLMB_BF16 && (N % 64) == 0;   // bf16 rows: warp-level MMAs, 16 or 32 rows per group
+    const int mt = B > 16 ? 2 : 1;
+    const int nz = tc ? nmat * ((B + 16 * mt - 1) / (16 * mt)) : nmat * ((B + 7) / 8);
+    if (groups) nslice = tc ? mma_slices(K, N, nz, mt) : rows8_slices(K, N, nz);
     void *ws = nullptr;
     int rc = workspace((size_t)nslice * R * N * sizeof(float), &ws);
     if (rc) return rc;
     float *part = (float *)ws;
-    if ((size_t)nblk * nslice * R <= (size_t)2 * sm_count())
+    if (groups) {
+        Rows8 a = {};
+        a.part = part; a.X = X; a.x_dtype = dtype; a.K = K; a.N = N;
+        a.codes = (const uint8_t *)codes; a.scales = scales; a.e_codes = (size_t)K * N / 2; a.e_scales = (size_t)K * N / 128;
+        a.B = B; a.nmat = nmat; a.rows_out = R; a.gamma = gamma;
+        if ((rc = tc ? mma_launch(a, nz, nslice, mt, st) : rows8_launch(a, nz, nslice, st))) return rc;
+    } else if ((size_t)nblk * nslice * R <= (size_t)2 * sm_count())
         k_gemv_kn<1, 4><<<dim3(nblk, nslice, R), 256, (size_t)kslice * sizeof(float), st>>>(
             part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
     else

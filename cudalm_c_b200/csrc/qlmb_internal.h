@@ -64,7 +64,9 @@ int router_logits_small(float *rt, const void *X, int x_dtype, const float *Wr, 
 int router_small(float *rt, const void *X, int x_dtype, const float *Wr, float *rprobs, int *assign, float *gate, int N, int D,
                  int E, int K, const float *bias, int bs, cudaStream_t st);
 // experts of a decode step with at most 64 routed rows (qlmb_gemv.cu): routed GEMVs over the chosen experts' codes
+// perm / off / counts / bad: scratch of the permutation (K*N, E + 1, E and 1 ints) for steps with more than 16 routed rows
 int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, const void *f_norm, const int *assign,
-                       const float *gate, cudaStream_t st);
+                       const float *gate, cudaStream_t st, int *perm = nullptr, int *off = nullptr, int *counts = nullptr,
+                       int *bad = nullptr);
 
 }  // namespace qlmb

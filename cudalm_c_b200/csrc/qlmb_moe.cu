@@ -237,7 +237,7 @@ static int moe_forward_impl(const qlmb_moe_layer *L, void *arena, void *out, con
 }
 
 // Forward of a decode step (dec_step's moe_forward call, cudalm.cu:7199): no stash for a backward pass.  With at
-// most 64 routed rows (K * N) and bf16 activations the experts run as routed GEMVs that read only the chosen
+// most 128 routed rows (K * N) and bf16 activations the experts run as routed GEMVs that read only the chosen
 // experts' codes; larger batches take qlmb_moe_forward.
 extern "C" int qlmb_moe_decode(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in, const void *f_norm,
                                void *stream)
@@ -245,14 +245,14 @@ extern "C" int qlmb_moe_decode(const qlmb_moe_layer *L, void *arena, void *out, 
     int rc = check_layer("qlmb_moe_decode", L);
     if (rc) return rc;
     QLMB_REQUIRE(arena && out && f_in && f_norm, "qlmb_moe_decode: NULL argument");
-    if (L->K * L->N > 64 || L->dtype != QLMB_BF16 || (L->D % 128) || (L->F % 128))
+    if (L->K * L->N > 128 || L->dtype != QLMB_BF16 || (L->D % 128) || (L->F % 128))
         return moe_forward_impl(L, arena, out, f_in, f_norm, stream, L->N <= 64);
     QLMB_REQUIRE(((uintptr_t)arena & 255) == 0, "qlmb_moe_decode: arena must be 256-byte aligned");
     const int N = L->N, D = L->D, F = L->F, E = L->E, K = L->K;
     Arena a = carve(arena, N, D, F, E, K);
     cudaStream_t st = as_stream(stream);
     if ((rc = router_small(a.rt, f_norm, L->dtype, L->wr, a.rprobs, a.assign, a.gate, N, D, E, K, L->bias, L->bias_stride, st))) return rc;
-    return moe_decode_experts(L, out, f_in, f_norm, a.assign, a.gate, st);
+    return moe_decode_experts(L, out, f_in, f_norm, a.assign, a.gate, st, a.perm, a.off, a.counts, a.bad);
 }
 
 extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const void *dout,

@@ -99,7 +99,7 @@ class MoeLayerState:
         return out
 
     def decode(self, f_in, f_norm, out=None):
-        """The forward of a decode step: no stash; routed GEMVs when K*N <= 64."""
+        """The forward of a decode step: no stash; routed GEMVs when K*N <= 128."""
         out = out if out is not None else torch.empty_like(f_in)
         check(lib().qlmb_moe_decode(self.c, self.arena_ptr, ptr(out), ptr(f_in), ptr(f_norm), stream_ptr()))
         return out

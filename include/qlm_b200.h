@@ -280,7 +280,7 @@ size_t qlmb_moe_arena_bytes(int N, int D, int F, int E, int K);
 void *qlmb_moe_arena_member(void *arena, int N, int D, int F, int E, int K, const char *name);
 
 /* The same forward for a decode step (dec_step, cudalm.cu:7199): nothing is stashed for a backward pass.
- * With K*N <= 64 routed rows and bf16 activations the experts run as GEMVs over the chosen experts' codes
+ * With K*N <= 128 routed rows and bf16 activations the experts run as GEMVs over the chosen experts' codes
  * only; otherwise this is qlmb_moe_forward.  The arena's "assign", "gate", "rprobs" members are filled. */
 int qlmb_moe_decode(const qlmb_moe_layer *L, void *arena, void *out, const void *f_in, const void *f_norm,
                     void *stream);

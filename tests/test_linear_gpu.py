@@ -142,8 +142,10 @@ def test_empty_and_unsupported(cuda):
 
 @pytest.mark.parametrize("B", [1, 8, 64])
 def test_gemv_decode(cuda, oracle, B):
-    """Decode path (M = live slots <= 64): fp32 accumulation of exact dequantised
-    weights, so the result agrees with the fp32 reference to round-off (1e-5)."""
+    """Decode path (M = live slots <= 64).  fp32 activations: fp32 accumulation of exact dequantised weights (the
+    digits are multiplied as 136 + d and the constant is taken out of the finished sums, which costs about five of
+    the 24 mantissa bits), so the result agrees with the fp32 reference to round-off (3e-5).  bf16 activations with
+    more than four slots run on warp-level MMAs with bf16(x * scale) operands: 8e-3."""
     from cudalm_c_b200 import linear
     from cudalm_c_b200._lib import KN, NK
     for K, N in ((768, 1536), (1536, 768), (768, 16384), (2048, 4096)):
@@ -154,7 +156,7 @@ def test_gemv_decode(cuda, oracle, B):
                 X = torch.randn(B, K, device=cuda).to(dt)
                 Y = linear.gemv_decode(X, Q.d, Q.s, lay, N)
                 ref = X.float() @ Wm
-                assert rel(Y, ref) < (1e-5 if dt == torch.float32 else 8e-3), (K, N, lay, dt)
+                assert rel(Y, ref) < (3e-5 if dt == torch.float32 else 8e-3), (K, N, lay, dt)
                 assert torch.equal(Y, linear.gemv_decode(X, Q.d, Q.s, lay, N))      # deterministic
     # oracle on one case
     Q, W = quantise(cuda, 256, 384, 6)
