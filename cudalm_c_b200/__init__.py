@@ -7,4 +7,4 @@ PyTorch fallback: importing works anywhere, but every compute call needs the
 library built (python -m cudalm_c_b200.build) and a CUDA device.
 """
 from ._lib import lib, check, QlmbError, SPAN_DTYPE, lib_path  # noqa: F401
-from . import qlm, moe, linear  # noqa: F401
+from . import qlm, moe, linear, q4n  # noqa: F401

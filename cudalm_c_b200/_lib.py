@@ -62,10 +62,21 @@ PROTOTYPES = {
     "qlmb_nggate_bwd": (ci, [vp, vp, vp, vp, ci, vp, vp, vp, vp, vp, ci, ci, vp]),
     "qlmb_ng_touched": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp]),
     "qlmb_ng_scatter_compact": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
+    "qlmb_eg_key": (ci, [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]),
+    "qlmb_eg_gather": (ci, [vp, vp, vp, ci, ci, ci, vp]),
+    "qlmb_eg_scatter_compact": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_ng_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, cf, cf, cf, cf, cf, cf, cf, u64, u64, vp, vp]),
     "qlmb_modelfile_write": (ci, [C.c_char_p, vp, vp, u64, vp, ci]),
     "qlmb_modelfile_read_header": (ci, [C.c_char_p, vp, vp, vp]),
     "qlmb_modelfile_read": (ci, [C.c_char_p, vp, u64, vp, ci, vp]),
+    "qlmb_q4n_work_bytes": (u64, [u64, ci]),
+    "qlmb_q4n_max_bytes": (u64, [u64, ci]),
+    "qlmb_q4n_export": (ci, [vp, u64, vp, vp, u64, ci, vp, vp]),
+    "qlmb_q4n_index": (ci, [vp, u64, u64, ci, vp]),
+    "qlmb_q4n_decode": (ci, [vp, vp, vp, u64, ci, vp]),
+    "qlmb_qfile_write": (ci, [C.c_char_p, vp, ci, ci, vp, u64, vp, ci]),
+    "qlmb_qfile_read_header": (ci, [C.c_char_p, vp, vp, vp, vp]),
+    "qlmb_qfile_read": (ci, [C.c_char_p, vp, u64]),
     "qlmb_servo": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, cf, cf, ci, vp]),
     "qlmb_gnorm": (ci, [vp, sz, vp, vp, ci, ci, vp, vp]),
     "qlmb_gnorm_noalloc": (ci, [vp, sz, vp, vp, ci, ci, vp, vp]),
@@ -125,6 +136,25 @@ PROTOTYPES = {
     "qlmb_ep_experts_backward": (ci, [C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, ci, ci,
                                       vp, vp, vp, vp, cf, vp]),
     "qlmb_ep_route_backward": (ci, [C.POINTER(MoeLayer), vp, vp, vp, vp, vp, cf, vp]),
+    "qlmb_comm_unique_id": (ci, [vp]),
+    "qlmb_comm_init": (ci, [C.POINTER(vp), vp, ci, ci]),
+    "qlmb_comm_destroy": (ci, [vp]),
+    "qlmb_comm_rank": (ci, [vp]),
+    "qlmb_comm_world": (ci, [vp]),
+    "qlmb_comm_allreduce_f32": (ci, [vp, vp, u64, ci, vp]),
+    "qlmb_comm_allgather": (ci, [vp, vp, vp, u64, vp]),
+    "qlmb_comm_barrier": (ci, [vp, vp]),
+    "qlmb_dp_grad_sync": (ci, [vp, vp, u64, vp]),
+    "qlmb_dp_gnorm_close": (ci, [vp, vp, ci, ci, vp, vp]),
+    "qlmb_zero1_step": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, cf, cf, cf, cf, cf, vp, cf, cf,
+                             ci, u64, ci, vp, ci, vp]),
+    "qlmb_zero1_gather_scales": (ci, [vp, vp, ci, vp]),
+    "qlmb_ep_window_open": (ci, [vp, vp, C.POINTER(EpPeers), vp]),
+    "qlmb_ep_window_close": (ci, [vp, C.POINTER(EpPeers), vp]),
+    "qlmb_ep_layer_forward": (ci, [vp, C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp, ci, vp,
+                                   vp, vp, vp]),
+    "qlmb_ep_layer_backward": (ci, [vp, C.POINTER(MoeLayer), vp, C.POINTER(MoeLayer), vp, C.POINTER(EpPeers), vp, vp, vp, vp,
+                                    vp, vp, vp, vp, vp, cf, ci, vp]),
 }
 
 _lib = None

@@ -29,6 +29,8 @@ UNITS = {
     "qlmb_gemv.cu": [],
     "qlmb_moe.cu": [],
     "qlmb_statefile.cu": [],
+    "qlmb_q4n.cu": ["--fmad=false"],
+    "qlmb_comm.cu": [],
     "qlmb_attn.cu": [],
     "qlmb_block.cu": [],
 }

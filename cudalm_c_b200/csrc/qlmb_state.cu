@@ -248,8 +248,10 @@ __global__ void __launch_bounds__(1024) k_ng_compact(int *tgi, int *count, int *
     if (tid == 0) *count = base;
 }
 // Gc[c*group + o] = sum over positions n (ascending) whose key is the row of element o: warp = (slot c, row of the group)
+// the gradient row of key position n is dbuf + (n % Nd) * ld + (n / Nd) * sub: ld = De, sub = 0 for the n-gram table (every
+// key set of a position reads the same row), ld = S * De, sub = De for the engram's S sub-tables (k_eg_scatter_c)
 __global__ void __launch_bounds__(256) k_ng_scatter_compact(float *Gc, const int *key, const int *tgi, const int *count,
-                                                            const float *dbuf, int NK, int De, int group, int Nd)
+                                                            const float *dbuf, int NK, int De, int group, int Nd, int ld, int sub)
 {
     __shared__ int skey[2048];
     const int rpg = group / De;                          // rows per group (group % De == 0)
@@ -272,7 +274,7 @@ __global__ void __launch_bounds__(256) k_ng_scatter_compact(float *Gc, const int
             while (m) {
                 const int n = n0 + q + __ffs(m) - 1;
                 m &= m - 1;
-                const float *src = dbuf + (size_t)(n % Nd) * De;
+                const float *src = dbuf + (size_t)(n % Nd) * ld + (size_t)(n / Nd) * sub;
 #pragma unroll
                 for (int k = 0; k < 8; k++) { const int e = lane + 32 * k; if (e < De) acc[k] += src[e]; }
             }
@@ -1040,8 +1042,63 @@ extern "C" int qlmb_ng_scatter_compact(float *Gc, const int *key, const int *tgi
     QLMB_REQUIRE(De > 0 && De <= 256 && group > 0 && group % De == 0 && Nd > 0 && max_touched >= 0, "qlmb_ng_scatter_compact: De %d group %d", De, group);
     if (max_touched == 0 || NK <= 0) return QLMB_OK;
     const long long warps = (long long)max_touched * (group / De);
-    k_ng_scatter_compact<<<(unsigned)((warps + 7) / 8), 256, 0, as_stream(stream)>>>(Gc, key, tgi, count, dbuf, NK, De, group, Nd);
+    k_ng_scatter_compact<<<(unsigned)((warps + 7) / 8), 256, 0, as_stream(stream)>>>(Gc, key, tgi, count, dbuf, NK, De, group, Nd, De, 0);
     QLMB_LAUNCH_CHECK("k_ng_scatter_compact");
+    return QLMB_OK;
+}
+
+// ---- sparse engram: S hashed sub-tables inside the one 4-bit table (cudalm.cu:4963-5098, CPU twins cpu_kern.h:665-688)
+// k_eg_key: key s*N + n = row of sub-table s for the last ord[s] token ids at position n (-1 without enough history)
+__global__ void __launch_bounds__(256) k_eg_key(int *key, const int *tok, const unsigned short *canon, const int *ord, const int *prime,
+                                                const unsigned long long *mult, int N, int T, int S, int Rp)
+{
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (long long)S * N) return;
+    const int sidx = (int)(i / N), n = (int)(i % N), o = ord[sidx];
+    if (n % T < o - 1) { key[i] = -1; return; }
+    unsigned long long m = 0;
+    for (int k = 0; k < o; k++) {
+        unsigned t = (unsigned)tok[n - k];
+        if (canon) t = canon[t];
+        m ^= (unsigned long long)t * mult[sidx * 4 + k];
+    }
+    key[i] = (int)(m % (unsigned long long)prime[sidx]) + sidx * Rp;
+}
+// k_eg_gather: buf[n][s][:] = table row key[s*N + n] (zeros where the key is -1)
+__global__ void __launch_bounds__(256) k_eg_gather(float *buf, const float *tbl, const int *key, int N, int S, int De)
+{
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x, SD = (size_t)S * De;
+    if (i >= (size_t)N * SD) return;
+    const int n = (int)(i / SD), r = (int)(i % SD), sidx = r / De, e = r % De, k = key[(size_t)sidx * N + n];
+    buf[i] = k >= 0 ? tbl[(size_t)k * De + e] : 0.0f;
+}
+extern "C" int qlmb_eg_key(int *key, const int *tok, const unsigned short *canon, const int *ord, const int *prime,
+                           const unsigned long long *mult, int N, int T, int S, int Rp, void *stream)
+{
+    QLMB_REQUIRE(key && tok && ord && prime && mult, "qlmb_eg_key: NULL argument");
+    QLMB_REQUIRE(N > 0 && T > 0 && S > 0 && S <= 32 && Rp > 0, "qlmb_eg_key: N %d T %d S %d Rp %d", N, T, S, Rp);
+    k_eg_key<<<(unsigned)(((long long)S * N + 255) / 256), 256, 0, as_stream(stream)>>>(key, tok, canon, ord, prime, mult, N, T, S, Rp);
+    QLMB_LAUNCH_CHECK("k_eg_key");
+    return QLMB_OK;
+}
+extern "C" int qlmb_eg_gather(float *buf, const float *tbl, const int *key, int N, int S, int De, void *stream)
+{
+    QLMB_REQUIRE(buf && tbl && key && N > 0 && S > 0 && De > 0, "qlmb_eg_gather: bad argument");
+    k_eg_gather<<<(unsigned)(((size_t)N * S * De + 255) / 256), 256, 0, as_stream(stream)>>>(buf, tbl, key, N, S, De);
+    QLMB_LAUNCH_CHECK("k_eg_gather");
+    return QLMB_OK;
+}
+// k_eg_scatter_c: the compact gradient rows of the touched groups from db [N][S][De]; per element the positions are added
+// in ascending order (the reference's CPU build; its GPU kernel uses float atomics)
+extern "C" int qlmb_eg_scatter_compact(float *Gc, const int *key, const int *tgi, const int *count, const float *db, int N, int S,
+                                       int De, int group, int max_touched, void *stream)
+{
+    QLMB_REQUIRE(Gc && key && tgi && count && db, "qlmb_eg_scatter_compact: NULL argument");
+    QLMB_REQUIRE(N > 0 && S > 0 && De > 0 && De <= 256 && group > 0 && group % De == 0 && max_touched >= 0, "qlmb_eg_scatter_compact: N %d S %d De %d group %d", N, S, De, group);
+    if (max_touched == 0) return QLMB_OK;
+    const long long warps = (long long)max_touched * (group / De);
+    k_ng_scatter_compact<<<(unsigned)((warps + 7) / 8), 256, 0, as_stream(stream)>>>(Gc, key, tgi, count, db, S * N, De, group, N, S * De, De);
+    QLMB_LAUNCH_CHECK("qlmb_eg_scatter_compact");
     return QLMB_OK;
 }
 

@@ -160,6 +160,16 @@ class QlmModel:
         P = self.params().cpu().numpy()
         check(lib().qlmb_modelfile_write(path.encode(), hdr.ctypes.data_as(C.c_void_p), P.ctypes.data_as(C.c_void_p), P.size, None, 0))
 
+    def save_model_q4n(self, path, eot=0):
+        """`quantize <model> <out> q4n` (cudalm.cu:9753-9793) straight from the device: the rendered 4-bit weights
+        export without loss; the float spans (gains) are stored raw where they lie on no 4-bit grid."""
+        import numpy as np
+        from . import q4n
+        assert self.world == 1, "gather the experts first"
+        c = self.c
+        hdr = np.array([c.V, c.D, c.L, c.H, c.KV, c.F, c.T, eot, 0, 0, c.E, 0, 0], np.int32)
+        return q4n.save(path, hdr, self.params())
+
     # ------------------------------------------------------------------ forward
     def forward(self, tok, B=None, T=None, moes=None, route_logits=None):
         """gpu_forward over B sequences of T tokens (default: the training batch); `moes` replaces the

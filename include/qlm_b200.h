@@ -145,6 +145,19 @@ int qlmb_ng_step(float *P, const float *Gc, int8_t *d, int8_t *r, const float *s
                  float b2, float wd, float sref, float inv_bc1, float inv_sqrt_bc2, uint64_t t, uint64_t nt,
                  const float *gs, void *stream);
 
+/* Sparse engram (cudalm.cu:4963-5098): S = orders x heads hashed sub-tables share the one 4-bit table (sub-table s owns rows
+ * [s*Rp, s*Rp + prime[s])), so its update is the three calls above with NK = S*N keys.  k_eg_key (5077-5083): key[s*N + n] =
+ * s*Rp + (xor over the last ord[s] token ids of tok * mult[s*4 + k]) mod prime[s], -1 for the first ord[s]-1 positions of a
+ * sequence of T; canon (may be NULL) maps token ids first.  ord, prime [S] and mult [S*4] are DEVICE arrays the caller fills
+ * (engram_setup's primes below the row count and splitmix64 multipliers, 5040-5047).  k_eg_gather (5084-5087): buf[n][s][:] =
+ * the table row of key[s*N + n] (zeros for -1).  k_eg_scatter_c (5092-5097): compact gradient rows of the touched groups from
+ * db [N][S][De], each element's positions added in ascending order. */
+int qlmb_eg_key(int *key, const int *tok, const unsigned short *canon, const int *ord, const int *prime,
+                const unsigned long long *mult, int N, int T, int S, int Rp, void *stream);
+int qlmb_eg_gather(float *buf, const float *tbl, const int *key, int N, int S, int De, void *stream);
+int qlmb_eg_scatter_compact(float *Gc, const int *key, const int *tgi, const int *count, const float *db, int N, int S, int De,
+                            int group, int max_touched, void *stream);
+
 /* The table's forward (ngram_forward, cudalm.cu:4701-4716).  k_ngram_key (4438-4445): key[n] = base + hash of the
  * last `order` token ids of position n, modulo R; -1 for the first order-1 positions of a sequence of T.
  * k_dec_ngkey (7056-7062): the same from a decoder slot's window of its last four tokens and its position.
@@ -362,6 +375,35 @@ int qlmb_modelfile_write(const char *path, const int *hdr13, const float *P, uns
 int qlmb_modelfile_read_header(const char *path, int *hdr13, unsigned long long *n_params, int *tok_bytes);
 int qlmb_modelfile_read(const char *path, float *P, unsigned long long n, void *tok_blob, int tok_cap, int *tok_bytes);
 
+/* Exact 4-bit export ("q4n") of a parameter vector and the quantised container file (quantize_params /
+ * dequantize_params with qtype 3, cudalm.cu:639-656, 688-695; the quantize command's TLQ1 / TLQ2 writer, 9783-9793, and
+ * model_load_full's reader, 438-450).  Per group of `group` values (the reference uses 128): a fp32 scale and ceil(g/2)
+ * nibble-pair bytes, or, where no scale puts the group on a 4-bit grid, a NaN scale and the g raw fp32 values.  The scale
+ * search is the reference's (amax/k for k = 7..1 with its +-1 and +-2 ulp neighbours), so a vector rendered from 4-bit
+ * digits exports without loss and the stream is byte-identical to the reference's.
+ *   qlmb_q4n_export   P, out, work on the device; totals (device) receives {stream bytes, raw groups}; nothing is
+ *                     written to out when the stream would exceed cap (check totals[0] <= cap after the stream is done).
+ *                     out 4-byte aligned; work = qlmb_q4n_work_bytes(n, group) bytes, 8-byte aligned; group % 8 == 0.
+ *   qlmb_q4n_index    HOST walk of a stream (host memory) that yields the byte offset of every group, off[groups + 1];
+ *                     the position of a group depends on the kind of every group before it.
+ *   qlmb_q4n_decode   P[i] = digit * scale (or the raw value) on the device from the stream and its offsets, both on
+ *                     the device.
+ * qlmb_qfile_*: "TLQ1" + 11 header ints ("TLQ2" + 13 when hdr13[11], the window, is set), qtype, group, the body, the
+ * tokenizer blob's length and bytes.  read_header gives the number of bytes after `group`; read copies them to a host
+ * buffer, whose body part qlmb_q4n_index measures (off[groups] = body bytes; the tokenizer trailer follows). */
+unsigned long long qlmb_q4n_work_bytes(unsigned long long n, int group);
+unsigned long long qlmb_q4n_max_bytes(unsigned long long n, int group);
+int qlmb_q4n_export(unsigned char *out, unsigned long long cap, unsigned long long *totals, const float *P,
+                    unsigned long long n, int group, void *work, void *stream);
+int qlmb_q4n_index(const unsigned char *host_stream, unsigned long long len, unsigned long long n, int group,
+                   unsigned long long *off);
+int qlmb_q4n_decode(float *P, const unsigned char *in, const unsigned long long *off, unsigned long long n, int group,
+                    void *stream);
+int qlmb_qfile_write(const char *path, const int *hdr13, int qtype, int group, const void *body, unsigned long long body_len,
+                     const void *tok_blob, int tok_bytes);
+int qlmb_qfile_read_header(const char *path, int *hdr13, int *qtype, int *group, unsigned long long *rest);
+int qlmb_qfile_read(const char *path, void *buf, unsigned long long rest);
+
 /* ------------------------- expert parallelism over peer memory (new, no reference counterpart)
  * Same cut of moe_forward / moe_backward (cudalm.cu:4151-4393), but rows never travel in a
  * separate exchange: every rank places its inputs, its Ys / dXs buffers and both arenas in one
@@ -413,6 +455,53 @@ int qlmb_ep_experts_backward(const qlmb_moe_layer *loc, void *earena, const qlmb
                              int K, void *dXs, float *dW1, float *dW3, float *dW2, float beta, void *stream);
 int qlmb_ep_route_backward(const qlmb_moe_layer *home, void *harena, const void *dXs, void *dfnorm,
                            const void *f_norm, float *dWr, float beta, void *stream);
+
+/* ------------------------- native multi-GPU host layer (new, no reference counterpart: the reference is single-GPU)
+ * One process per GPU.  NCCL is bound at run time (the libnccl.so.2 the process has loaded, else the system's, else
+ * the path in QLMB_NCCL_LIB); without it these calls return QLMB_E_UNSUPPORTED and the rest of the library works.
+ * Rank 0 makes the 128-byte id (qlmb_comm_unique_id) and hands it to the other ranks by any host channel; every
+ * rank then calls qlmb_comm_init with its device current.  All collectives are enqueued on the caller's stream.
+ *   qlmb_comm_allreduce_f32   sum (avg = 0) or mean (avg = 1), in place
+ *   qlmb_comm_allgather       recv[r*bytes..] = rank r's bytes; send == recv + rank*bytes gathers in place
+ *   qlmb_comm_barrier         stream-ordered meeting point (a one-int all-reduce); nothing waits on the host
+ *   qlmb_dp_grad_sync         data parallelism: the replicated parameters' gradient becomes the mean over the ranks
+ *   qlmb_dp_gnorm_close       qlmb_gnorm_close after the partial sums of rank-local buffers (expert shards),
+ *                             slices [first_local, nslice), have been summed over the ranks
+ *   qlmb_zero1_step           qlmb_step on this rank's share of the groups (ngrp % world == 0), then an all-gather of
+ *                             the new codes: every rank ends with the codes qlmb_step on the whole span gives, bit
+ *                             for bit, while residuals and moments of a share never leave its rank
+ *   qlmb_zero1_gather_scales  after a servo pass over the share: the scales of all groups on every rank
+ *   qlmb_ep_window_open       maps every rank's window (qlmb_peer_alloc) into this process; _close unmaps them
+ *   qlmb_ep_layer_forward     qlmb_ep_route, all-gather of the routing table into assign_all [world][K*N],
+ *                             qlmb_ep_experts_forward, meeting point, qlmb_ep_combine
+ *   qlmb_ep_layer_backward    qlmb_ep_dgate, (meeting point when dout was written this step: inputs_fresh),
+ *                             qlmb_ep_experts_backward, meeting point, qlmb_ep_route_backward */
+typedef struct qlmb_comm qlmb_comm;
+int qlmb_comm_unique_id(unsigned char id[128]);
+int qlmb_comm_init(qlmb_comm **comm, const unsigned char id[128], int rank, int world);
+int qlmb_comm_destroy(qlmb_comm *comm);
+int qlmb_comm_rank(const qlmb_comm *comm);
+int qlmb_comm_world(const qlmb_comm *comm);
+int qlmb_comm_allreduce_f32(qlmb_comm *comm, float *buf, unsigned long long n, int avg, void *stream);
+int qlmb_comm_allgather(qlmb_comm *comm, const void *send, void *recv, unsigned long long bytes, void *stream);
+int qlmb_comm_barrier(qlmb_comm *comm, void *stream);
+int qlmb_dp_grad_sync(qlmb_comm *comm, float *G, unsigned long long n, void *stream);
+int qlmb_dp_gnorm_close(qlmb_comm *comm, float *part, int nslice, int first_local, float *gs, void *stream);
+int qlmb_zero1_step(qlmb_comm *comm, float *P, const float *G, int8_t *d, int8_t *r, const float *s, int8_t *m8,
+                    float *m8s, uint8_t *v8, float *v8s, const qlmb_span *sp, int nspan, int ngrp, int group,
+                    int dmax, float lr, float b1, float b2, float wd, float gscale, const float *gsp,
+                    float inv_bc1, float inv_sqrt_bc2, int lrmode, uint64_t t, int adam, int64_t *stat,
+                    int packed, void *stream);
+int qlmb_zero1_gather_scales(qlmb_comm *comm, float *s, int ngrp, void *stream);
+int qlmb_ep_window_open(qlmb_comm *comm, void *window, qlmb_ep_peers *peers, void *stream);
+int qlmb_ep_window_close(qlmb_comm *comm, qlmb_ep_peers *peers, void *stream);
+int qlmb_ep_layer_forward(qlmb_comm *comm, const qlmb_moe_layer *home, void *harena, const qlmb_moe_layer *loc, void *earena,
+                          const qlmb_ep_peers *peers, int *assign_all, const void *f_norm, int x_dtype, const void *f_in,
+                          void *Ys, void *out, void *stream);
+int qlmb_ep_layer_backward(qlmb_comm *comm, const qlmb_moe_layer *home, void *harena, const qlmb_moe_layer *loc, void *earena,
+                           const qlmb_ep_peers *peers, const void *dout, const void *f_norm, const void *Ys, void *dXs,
+                           void *dfnorm, float *dW1, float *dW3, float *dW2, float *dWr, float beta, int inputs_fresh,
+                           void *stream);
 
 /* g_abt / g_ab on unquantised operands (the lm_head over the tied embedding, cudalm.cu:5832-5858):
  * C[M,N] = A[M,K] B[N,K]^T (+ C when beta = 1); A and B bf16, C fp32 or bf16; K % 64 == 0, N % 128 == 0.

@@ -289,6 +289,42 @@ class Reference:
         self.lib.ref_ngram_gather(_p(tbl), _p(key), _p(buf), C.c_int(N), C.c_int(De), C.c_int(nk))
         return buf
 
+    # ---- sparse engram (engram_setup cudalm.cu:5030-5047; kernels cpu_kern.h:665-688) ----
+    def eg_tables(self, Rraw, ord_of_sub):
+        """primes below Rraw + 1 (descending) and the splitmix64 multipliers of S sub-tables; loads the kernels' constants"""
+        ords = np.ascontiguousarray(ord_of_sub, np.int32); S = ords.size
+        prime = np.zeros(S, np.int32); mult = np.zeros(S * 4, np.uint64)
+        self.lib.ref_eg_tables(C.c_int(Rraw), C.c_int(S), _p(ords), _p(prime), _p(mult))
+        return prime, mult
+
+    def eg_key(self, tok, canon, T, S, Rp):
+        key = np.zeros(S * tok.size, np.int32)
+        self.lib.ref_eg_key(_p(tok), _p(canon), _p(key), C.c_int(tok.size), C.c_int(T), C.c_int(S), C.c_int(Rp))
+        return key
+
+    def eg_gather(self, tbl, key, N, S, De):
+        buf = np.zeros((N, S * De), np.float32)
+        self.lib.ref_eg_gather(_p(tbl), _p(key), _p(buf), C.c_int(N), C.c_int(S), C.c_int(De))
+        return buf
+
+    def eg_scatter_c(self, Gc, key, cidx, db, N, S, De, grp):
+        self.lib.ref_eg_scatter_c(_p(Gc), _p(key), _p(cidx), _p(db), C.c_int(N), C.c_int(S), C.c_int(De), C.c_int(grp))
+
+    # ---- exact 4-bit export (quantize_params / dequantize_params qtype 3, cudalm.cu:639-656, 688-695) ----
+    def q4n_export(self, P, group=128):
+        P = np.ascontiguousarray(P, np.float32)
+        cap = (P.size + group - 1) // group * 4 + P.size * 4 + 8
+        out = np.zeros(cap, np.uint8)
+        self.lib.ref_q4n_export.restype = C.c_ulonglong
+        n = int(self.lib.ref_q4n_export(_p(P), C.c_ulonglong(P.size), C.c_int(group), _p(out), C.c_ulonglong(cap)))
+        return out[:n].copy()
+
+    def q4n_decode(self, stream, n, group=128):
+        stream = np.ascontiguousarray(stream, np.uint8)
+        P = np.zeros(n, np.float32)
+        ok = self.lib.ref_q4n_decode(_p(stream), C.c_ulonglong(stream.size), _p(P), C.c_ulonglong(n), C.c_int(group))
+        return P if ok else None
+
     # ---- selection bias update (mbias_upd, cudalm.cu:3793-3802); b [ns, E] is updated in place ----
     def mbias_upd(self, b, counts, m, u, lmul, prop):
         ns, E = counts.shape

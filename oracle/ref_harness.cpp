@@ -152,6 +152,42 @@ void ref_ng_step(float *P, const float *Gc, signed char *d, signed char *r, floa
                                                          inv_bc1, inv_sqrt_bc2, t, nt, gs);
 }
 
+/* ---- sparse engram: the sub-tables' primes and multipliers as engram_setup derives them (cudalm.cu:5040-5047), keys,
+ * gather and the compact scatter (cpu_kern.h:665-688) ---- */
+void ref_eg_tables(int Rraw, int S, const int *ord_of_sub, int *prime, unsigned long long *mult)
+{
+    int p = Rraw + 1;
+    for (int s = 0; s < S; s++) {
+        do p--; while (p > 1 && !eg_isprime(p));
+        prime[s] = p;
+        for (int k = 0; k < 4; k++) mult[s * 4 + k] = splitmix64(0x5EED0E17A11ULL + (unsigned long long)(s * 4 + k)) | 1ULL;
+    }
+    cudaMemcpyToSymbol(c_eg_ord, ord_of_sub, (size_t)S * 4);
+    cudaMemcpyToSymbol(c_eg_prime, prime, (size_t)S * 4);
+    cudaMemcpyToSymbol(c_eg_mult, mult, (size_t)S * 32);
+}
+void ref_eg_key(const int *tok, const unsigned short *cn, int *key, int N, int T, int S, int Rp) { KL(k_eg_key, 1, 1)(tok, cn, key, N, T, S, Rp); }
+void ref_eg_gather(const float *tbl, const int *key, float *buf, int N, int S, int De) { KL(k_eg_gather, 1, 1)(tbl, key, buf, N, S, De); }
+void ref_eg_scatter_c(float *Gc, const int *key, const int *cidx, const float *db, int N, int S, int De, int grp)
+{ KL(k_eg_scatter_c, 1, 1)(Gc, key, cidx, db, N, S, De, grp); }
+
+/* ---- exact 4-bit export of a rendered parameter vector and its reader (quantize_params / dequantize_params with
+ * qtype 3, cudalm.cu:639-656, 688-695) ---- */
+unsigned long long ref_q4n_export(const float *P, unsigned long long n, int group, unsigned char *out, unsigned long long cap)
+{
+    size_t len = 0;
+    uint8_t *q = quantize_params(P, (size_t)n, 3, group, &len);
+    if (len <= cap) memcpy(out, q, len);
+    free(q);
+    return (unsigned long long)len;
+}
+
+int ref_q4n_decode(const unsigned char *in, unsigned long long len, float *P, unsigned long long n, int group)
+{
+    Rd r = {in, in + len};
+    return dequantize_params(&r, P, (size_t)n, 3, group);
+}
+
 /* ---- model file (model_save_bundle / model_load_full, cudalm.cu:554-565, 431-466) ---- */
 static void cfg_from_ints(Cfg *c, const int *h) { cfg_from_hdr(c, h, h[11] > 0 ? 5 : 4); }
 unsigned long long ref_param_count(const int *hdr13) { Cfg c; cfg_from_ints(&c, hdr13); return (unsigned long long)param_count(&c); }

@@ -367,11 +367,62 @@ def golden_nggate(ref):
     np.savez_compressed(os.path.join(OUT, "nggate.npz"), **out)
 
 
+def golden_engram(ref):
+    """Sparse engram (cudalm.cu:4963-5098): keys of S = 2 orders x 2 heads sub-tables (with and without a canonical
+    token map), the gather, and the compact gradient rows of the touched groups."""
+    rng = np.random.default_rng(31)
+    V, T, B, De, grp = 500, 32, 6, 32, 128
+    ords = np.array([2, 2, 3, 3], np.int32); S = ords.size
+    Rraw = 257; al = 128 // De; Rp = (Rraw + al - 1) // al * al
+    prime, mult = ref.eg_tables(Rraw, ords)
+    N = B * T
+    tok = rng.integers(0, V, N).astype(np.int32)
+    tok[40:60] = tok[8:28]                                              # repeated context: shared rows
+    canon = rng.integers(0, V, V).astype(np.uint16)
+    key = ref.eg_key(tok, None, T, S, Rp); keyc = ref.eg_key(tok, canon, T, S, Rp)
+    tbl = (rng.standard_normal((S * Rp, De)) * 0.02).astype(f32)
+    buf = ref.eg_gather(tbl, key, N, S, De)
+    ngrp = S * Rp * De // grp
+    tgi, cidx = ref.ng_touched(key, De, grp, ngrp)
+    db = (rng.standard_normal((N, S * De)) * 1e-3).astype(f32)
+    Gc = np.zeros(tgi.size * grp, f32)
+    ref.eg_scatter_c(Gc, key, cidx, db, N, S, De, grp)
+    order = np.argsort(tgi)                                             # rows in ascending group order
+    np.savez_compressed(os.path.join(OUT, "engram.npz"), cfg=np.array([V, T, B, De, grp, Rraw, Rp]), ords=ords, prime=prime,
+                        mult=mult, tok=tok, canon=canon, key=key, keyc=keyc, tbl=tbl, buf=buf, db=db, touched=tgi[order],
+                        Gc=Gc.reshape(-1, grp)[order])
+
+
+def golden_q4n(ref):
+    """Exact 4-bit export (quantize_params / dequantize_params qtype 3, cudalm.cu:639-656, 688-695) of a vector whose
+    groups are: rendered 4-bit digits with full range, with small digits only, all zero, tiny scales, a float span
+    (no grid: stored raw), one value off the grid, and a short last group."""
+    rng = np.random.default_rng(41)
+    group = 128
+    parts = []
+    for g in range(24):
+        sc = f32(np.exp(rng.uniform(-12, -2)))
+        hi = 7 if g % 3 else int(rng.integers(1, 7))
+        parts.append((rng.integers(-hi, hi + 1, group).astype(f32) * sc).astype(f32))
+    parts.append(np.zeros(group, f32))
+    parts.append((rng.integers(-7, 8, group).astype(f32) * f32(3e-41)).astype(f32))      # subnormal scale
+    parts.append((rng.standard_normal(group) * 0.02).astype(f32))                           # no grid
+    on = (rng.integers(-7, 8, group).astype(f32) * f32(0.0123)).astype(f32); on[77] = np.nextafter(on[77], f32(1))
+    parts.append(on)
+    parts.append(np.ones(group, f32))                                                       # gains
+    parts.append((rng.integers(-7, 8, 70).astype(f32) * f32(0.004)).astype(f32))           # short tail
+    P = np.concatenate(parts)
+    q = ref.q4n_export(P, group)
+    back = ref.q4n_decode(q, P.size, group)
+    assert back is not None and (back.view(np.uint32) == P.view(np.uint32)).all()
+    np.savez_compressed(os.path.join(OUT, "q4n.npz"), P=P, q=q, group=np.array([group]))
+
+
 def main():
     ref = loader.reference(exact=True)
     if ref is None:
         sys.exit("oracle/_ref/libcudalm_ref_exact.so missing: run `make -C oracle ref` first")
-    single = {"router_bias": golden_router_bias, "nggate": golden_nggate}
+    single = {"router_bias": golden_router_bias, "nggate": golden_nggate, "engram": golden_engram, "q4n": golden_q4n}
     if len(sys.argv) == 2 and sys.argv[1] in single:       # one fixture alone: python make_golden.py router_bias
         single[sys.argv[1]](ref)
         return
@@ -391,6 +442,8 @@ def main():
     golden_ngram(ref)
     golden_router_bias(ref)
     golden_nggate(ref)
+    golden_engram(ref)
+    golden_q4n(ref)
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print("%-24s %8d B" % (f, os.path.getsize(os.path.join(OUT, f))))

@@ -209,3 +209,91 @@ def test_zero1_sharded_state_equals_whole(cuda):
         ret = m.dict()
         mp.spawn(worker_zero1, args=(world, free_port(), ret), nprocs=world, join=True)
         assert all(ret.get(r) for r in range(world))
+
+
+def worker_native(rank, world, port, ret):
+    """The library's own communicator (NCCL bound inside the shared library; torch.distributed only hands the id
+    over): collectives, the ZeRO-1 step against the whole-span step, and one expert-parallel layer driven by
+    qlmb_ep_layer_forward / _backward against the Python-orchestrated layer (same kernels, same order: bit-equal)."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import ctypes as C
+    from cudalm_c_b200 import comm, dist_moe, qlm
+    from cudalm_c_b200._lib import BF16, EpPeers, check, lib, ptr, stream_ptr
+    box = [comm.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    cm = comm.Comm(box[0], rank, world)
+    # collectives
+    a = torch.full((1000,), float(rank + 1), device=dev)
+    cm.allreduce(a); assert float(a[0]) == sum(range(1, world + 1))
+    cm.allreduce(a, avg=True); assert float(a[0]) == sum(range(1, world + 1))
+    g = torch.zeros(world, 256, dtype=torch.int32, device=dev); g[rank] = rank + 7
+    cm.allgather_inplace(g); cm.barrier(); torch.cuda.synchronize()
+    assert all(int(g[r, 0]) == r + 7 and int(g[r, 255]) == r + 7 for r in range(world))
+    # ZeRO-1: codes equal the whole-span step's on every rank; the share's other state equals the whole's share
+    n = 128 * 16384
+    ngrp = n // 128; per = ngrp // world; e0, e1 = rank * per * 128, (rank + 1) * per * 128
+    gen = torch.Generator(device=dev); gen.manual_seed(5)
+    P = torch.randn(n, device=dev, generator=gen) * 0.02
+    whole = qlm.Qlm([(0, n)], n, dev); whole.init_from(P.clone(), render=False)
+    shard = qlm.Qlm([(0, n)], n, dev); shard.init_from(P.clone(), render=False)
+    for t in range(1, 4):
+        G = torch.randn(n, device=dev, generator=gen) * 1e-3
+        whole.step(None, G, 3e-4, 0.9, 0.95, 0.1, t)
+        cm.zero1_step(shard, None, G, 3e-4, 0.9, 0.95, 0.1, t)
+    torch.cuda.synchronize()
+    assert torch.equal(whole.d, shard.d)
+    for k in ("r", "m8", "v8"):
+        assert torch.equal(getattr(whole, k)[e0:e1], getattr(shard, k)[e0:e1]), k
+    for k in ("m8s", "v8s"):
+        assert torch.equal(getattr(whole, k)[rank * per:(rank + 1) * per], getattr(shard, k)[rank * per:(rank + 1) * per]), k
+    # expert-parallel layer: the natively orchestrated calls on a second window against the Python-orchestrated layer
+    if world > 1:
+        dist.destroy_process_group()
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    c = CFG
+    gen = torch.Generator(device=dev); gen.manual_seed(7)
+    full = [torch.randn(c["E"] * c["D"] * c["F"], device=dev, generator=gen) * 0.02 for _ in range(3)]
+    wr = torch.randn(c["D"], c["E"], device=dev, generator=gen) * 0.02
+    ep = dist_moe.PeerExpertParallelLayer(c, dev, rank, world, seed=7, weights=full + [wr])
+    out_py = ep.forward().clone(); dfn_py = ep.backward().clone()
+    dW_py = [w.clone() for w in ep.dW]; dWr_py = ep.dWr.clone()
+    torch.cuda.synchronize()
+    L, st = lib(), stream_ptr()
+    peers = EpPeers()
+    check(L.qlmb_ep_window_open(cm.h, ep.win_ptr, C.byref(peers), st))
+    for w in ep.dW:
+        w.zero_()
+    ep.dWr.zero_(); ep.Ys.zero_(); ep.dXs.zero_()
+    out = torch.empty_like(ep.fi); dfn = torch.empty_like(ep.fi)
+    cm.barrier()
+    check(L.qlmb_ep_layer_forward(cm.h, ep.home, ep.hptr, ep.loc, ep.eptr, C.byref(peers), ptr(ep.assign_all), ptr(ep.fn), BF16,
+                                  ptr(ep.fi), ptr(ep.Ys), ptr(out), st))
+    check(L.qlmb_ep_layer_backward(cm.h, ep.home, ep.hptr, ep.loc, ep.eptr, C.byref(peers), ptr(ep.dout), ptr(ep.fn), ptr(ep.Ys),
+                                   ptr(ep.dXs), ptr(dfn), ptr(ep.dW[0]), ptr(ep.dW[1]), ptr(ep.dW[2]), ptr(ep.dWr), 0.0, 1, st))
+    torch.cuda.synchronize()
+    assert torch.equal(out, out_py) and torch.equal(dfn, dfn_py)
+    assert all(torch.equal(a_, b_) for a_, b_ in zip(ep.dW, dW_py)) and torch.equal(ep.dWr, dWr_py)
+    check(L.qlmb_ep_window_close(cm.h, C.byref(peers), st))
+    ep.close()
+    cm.close()
+    ret[rank] = True
+    dist.destroy_process_group()
+
+
+def _run_native(world):
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(worker_native, args=(world, free_port(), ret), nprocs=world, join=True)
+        assert all(ret.get(r) for r in range(world))
+
+
+def test_native_comm_one_rank(cuda):
+    _run_native(1)
+
+
+def test_native_comm_two_ranks(cuda):
+    _run_native(two_gpus())
