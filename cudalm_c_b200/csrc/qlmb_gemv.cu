@@ -346,15 +346,6 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 3 : 2) k_gemv_stream(void *Y, i
 //           slots in groups of eight; a slot s reads activation row s % ntok (gate, up) or s (down) and writes
 //           partial row s (+ R for the second stack of matrices: gate and up in one launch)
 // part[ks][row][n] receives the slice sums; the finish kernels are the ones of the one-row path.
-struct Rows8 {
-    float *part; const void *X; int x_dtype; int K, N, kslice;
-    const uint8_t *codes; const float *scales; size_t e_codes, e_scales;
-    const uint8_t *codes2; const float *scales2;         // routed: second stack for groups z >= zdual
-    int B, nmat, rows_out;                               // dense: batch and stack; rows_out = rows of `part` per slice
-    const int *perm, *off; int E, ntok, x_by_token, zdual, R;   // routed (perm != nullptr)
-    const float *gamma;                                  // dense: rows are normalised on the way in (rinv * gamma, bf16)
-    uint32_t k65536;
-};
 
 __global__ void __launch_bounds__(256, 2) k_gemv_rows8(const __grid_constant__ Rows8 a)
 {
@@ -603,29 +594,75 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) k_gemv_mma(const __grid_
     float *ssc = reinterpret_cast<float *>(msm + (size_t)GR * ldx * sizeof(bf16));
     {
         const int g0 = blockIdx.x * (CW / 128), gmax = N / 128 - 1;
-        for (int i = threadIdx.x; i < kslice * 4; i += 256) {
-            const int gq = g0 + (i & 3) < gmax ? g0 + (i & 3) : gmax;
-            ssc[i] = __ldg(scales + (size_t)(k0 + (i >> 2)) * srow + gq);
+        if (g0 + 3 <= gmax && (srow & 3) == 0) {                  // four neighbouring scales of a row in one load
+            for (int i = threadIdx.x; i < kslice; i += 256)
+                reinterpret_cast<float4 *>(ssc)[i] = __ldg(reinterpret_cast<const float4 *>(scales + (size_t)(k0 + i) * srow + g0));
+        } else {
+            for (int i = threadIdx.x; i < kslice * 4; i += 256) {
+                const int gq = g0 + (i & 3) < gmax ? g0 + (i & 3) : gmax;
+                ssc[i] = __ldg(scales + (size_t)(k0 + (i >> 2)) * srow + gq);
+            }
         }
     }
+    const bool vec = a.x_dtype == QLMB_BF16;                     // bf16 rows are staged in 16-byte pieces, four loads in flight
     if (a.gamma) {                                       // 1 / rms of every row over the whole K: warp w takes rows w, w + 8, ...
         for (int r = warp; r < nrow; r += 8) {
             float ss = 0.0f;
-            for (int k = lane; k < K; k += 32) { const float x = ld_x(a.X, a.x_dtype, (size_t)s_x[r] * K + k); ss += x * x; }
+            if (vec) {
+                const uint4 *xr = reinterpret_cast<const uint4 *>(reinterpret_cast<const bf16 *>(a.X) + (size_t)s_x[r] * K);
+                for (int kc = lane; kc < K / 8; kc += 32) {
+                    const uint4 v = __ldg(xr + kc);
+                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) { const float2 f = __bfloat1622float2(h[j]); ss += f.x * f.x; ss += f.y * f.y; }
+                }
+            } else {
+                for (int k = lane; k < K; k += 32) { const float x = ld_x(a.X, a.x_dtype, (size_t)s_x[r] * K + k); ss += x * x; }
+            }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             if (lane == 0) s_rinv[r] = 1.0f / sqrtf(ss / (float)K + 1e-5f);
         }
         __syncthreads();
     }
-    for (int i = threadIdx.x; i < GR * kslice; i += 256) {
-        const int b = i / kslice, kk = i % kslice;
-        float x = 0.0f;
-        if (b < nrow) {
-            x = ld_x(a.X, a.x_dtype, (size_t)s_x[b] * K + k0 + kk);
-            if (a.gamma) x = x * s_rinv[b] * a.gamma[k0 + kk];
+    if (vec) {
+        const int cpr = kslice / 8, total = GR * cpr;
+        for (int i0 = threadIdx.x; i0 < total; i0 += 4 * 256) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int i = i0 + j * 256, b = i / cpr, kc = i - b * cpr;
+                v[j] = make_uint4(0u, 0u, 0u, 0u);
+                if (i < total && b < nrow)
+                    v[j] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const bf16 *>(a.X) + (size_t)s_x[b] * K + k0 + kc * 8));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int i = i0 + j * 256, b = i / cpr, kc = i - b * cpr;
+                if (i >= total) continue;
+                if (a.gamma && b < nrow) {
+                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&v[j]);
+                    const float ri = s_rinv[b];
+                    const float *gm = a.gamma + k0 + kc * 8;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const float2 f = __bfloat1622float2(h[q]);
+                        h[q] = __floats2bfloat162_rn(f.x * ri * gm[2 * q], f.y * ri * gm[2 * q + 1]);
+                    }
+                }
+                *reinterpret_cast<uint4 *>(xs + b * ldx + kc * 8) = v[j];
+            }
         }
-        xs[b * ldx + kk] = __float2bfloat16_rn(x);
+    } else {
+        for (int i = threadIdx.x; i < GR * kslice; i += 256) {
+            const int b = i / kslice, kk = i % kslice;
+            float x = 0.0f;
+            if (b < nrow) {
+                x = ld_x(a.X, a.x_dtype, (size_t)s_x[b] * K + k0 + kk);
+                if (a.gamma) x = x * s_rinv[b] * a.gamma[k0 + kk];
+            }
+            xs[b * ldx + kk] = __float2bfloat16_rn(x);
+        }
     }
     __syncthreads();
     float acc[MT][8][4];
@@ -1043,6 +1080,10 @@ static int gemv_decode_impl(void *Y, const void *X, const int8_t *codes, const f
     cudaStream_t st = as_stream(stream);
     // more than 4 live slots with bf16 activations: the tensor-core engine streams the weights
     // faster than fp32 FMAs can consume them (fp32 activations keep the exact fp32 path)
+    // many rows on a large matrix: the 256-row tensor-core tiles of the training engine read the weights once
+    // (940 GB/s at 4096 x 16384 with 64 rows, against 520 for two passes of 32-row groups)
+    if (!fr && layout == QLMB_KN && B > 32 && dtype == QLMB_BF16 && (K % 64) == 0 && (size_t)K * N >= ((size_t)16 << 20))
+        return qlmb_linear_fwd(Y, X, codes, scales, layout, B, K, N, nullptr, dtype, stream);
     if (layout == QLMB_KN && B > 4) {
         // groups of eight rows per pass over the weights (fp32 multiply-adds; the 256-row tensor-core tiles would be
         // seven eighths padding for a handful of rows)

@@ -10,6 +10,16 @@ namespace qlmb {
 
 typedef __nv_bfloat16 bf16;
 
+// ---- grouped decode GEMVs (qlmb_gemv.cu): rows in groups share one pass over the codes W[K][N] ----
+struct Rows8 {
+    float *part; const void *X; int x_dtype; int K, N, kslice;
+    const uint8_t *codes; const float *scales; size_t e_codes, e_scales;
+    const uint8_t *codes2; const float *scales2;         // routed: second stack for groups z >= zdual
+    int B, nmat, rows_out;                               // dense: batch and stack; rows_out = rows of `part` per slice
+    const int *perm, *off; int E, ntok, x_by_token, zdual, R;   // routed (perm != nullptr)
+    const float *gamma;                                  // dense: rows are normalised on the way in (rinv * gamma, bf16)
+    uint32_t k65536;
+};
 // ---- routing (qlmb_route.cu) ----
 int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N, int E, int K,
                 const float *bias, int bs, cudaStream_t st);
