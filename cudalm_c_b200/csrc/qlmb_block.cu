@@ -327,6 +327,8 @@ __global__ void __launch_bounds__(128) k_dec_attn(bf16_t *O, const bf16_t *Q, co
     __shared__ float red[4], part[4][64];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int g = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();                                          // positions, query and cache rows are written by the kernels before
     const int b = g / H, h = g % H, kvh = h / (H / KV), t = pos[b], KD = KV * 64, D = H * 64;
     if (t < 0 || t >= Tm) { if (tid == 0 && h == 0) report_bad_index(errword, 302, b, t); return; }   // whole block: no score past the cache
     float *sc = dec_sc;
@@ -761,9 +763,8 @@ extern "C" int qlmb_dec_attn(void *O, const void *Q, const void *Kc, const void 
         QLMB_CUDA(cudaFuncSetAttribute(k_dec_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_TM_MAX * (int)sizeof(float)));
         configured_dev[dev_] = true;
     }
-    k_dec_attn<<<(unsigned)(B * H), 128, smem, as_stream(stream)>>>((bf16_t *)O, (const bf16_t *)Q, (const bf16_t *)Kc,
-                                                                              (const bf16_t *)Vc, pos, win, B, Tm, H, KV,
-                                                                              1.0f / sqrtf((float)hd), device_error_word());
+    QLMB_CUDA(pdl_launch(B > 4, k_dec_attn, dim3((unsigned)(B * H)), dim3(128), smem, as_stream(stream), (bf16_t *)O, (const bf16_t *)Q,
+                         (const bf16_t *)Kc, (const bf16_t *)Vc, pos, win, B, Tm, H, KV, 1.0f / sqrtf((float)hd), device_error_word()));
     QLMB_LAUNCH_CHECK("k_dec_attn");
     return QLMB_OK;
 }

@@ -43,6 +43,8 @@ __global__ void __launch_bounds__(256, NB == 4 ? 2 : (BT <= 2 ? 4 : 2)) k_gemv_k
                                                  int ntok = 1, const float *gamma = nullptr, int dual_rows = 0,
                                                  const uint8_t *codes2 = nullptr, const float *scales2 = nullptr)
 {
+    pdl_trigger();
+    if (row_expert) pdl_wait();                 // the expert choice is the work of a kernel before this one
     // routed form: blockIdx.z is an output row, it reads activation row z % ntok and one matrix of a stack; B must be 1 then
     size_t xrow = 0, prow = 0;
     int PB = B;
@@ -84,6 +86,7 @@ __global__ void __launch_bounds__(256, NB == 4 ? 2 : (BT <= 2 ? 4 : 2)) k_gemv_k
 #pragma unroll
         for (int u = 0; u < NB; u++) fetch(u, k0 + warp + 32 * u);
     }
+    if (!row_expert) pdl_wait();                // the weights above do not depend on the kernels before; the rows below do
     // gamma (routed form, one activation row per block): the row is normalised on the way in, x * rinv * gamma rounded
     // to bf16 as the separate norm kernel stores it (e_rmsf in front of the q, k, v projections, cudalm.cu:7176)
     float rinv = 1.0f;
@@ -171,6 +174,17 @@ __global__ void __launch_bounds__(256, NB == 4 ? 2 : (BT <= 2 ? 4 : 2)) k_gemv_k
             }
         }
     }
+}
+
+// k_gemv_kn as a programmatic dependent launch, with the kernel's default arguments
+template <int BT, int NB>
+static cudaError_t launch_kn(bool early, dim3 grid, size_t smem, cudaStream_t st, float *part, const void *X, int dtype, const uint8_t *codes,
+                             const float *scales, int B, int K, int N, int kslice, const int *row_expert = nullptr,
+                             size_t e_codes = 0, size_t e_scales = 0, int ntok = 1, const float *gamma = nullptr,
+                             int dual_rows = 0, const uint8_t *codes2 = nullptr, const float *scales2 = nullptr)
+{
+    return pdl_launch(early, k_gemv_kn<BT, NB>, grid, dim3(256), smem, st, part, X, dtype, codes, scales, B, K, N, kslice, row_expert,
+                      e_codes, e_scales, ntok, gamma, dual_rows, codes2, scales2);
 }
 
 // ---- streaming form for codes W[K][N] and up to four activation rows: the whole product in one launch.
@@ -347,6 +361,53 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 3 : 2) k_gemv_stream(void *Y, i
 //           partial row s (+ R for the second stack of matrices: gate and up in one launch)
 // part[ks][row][n] receives the slice sums; the finish kernels are the ones of the one-row path.
 
+// Which rows does group blockIdx.z hold?  Dense: rows g*GR.. of matrix m.  Routed: the z-th group of GR slots in
+// expert order (perm sorted by expert, off = expert offsets).  Run by warp 0: the lanes read the expert offsets
+// side by side (one round of loads instead of one per expert), a shuffle scan finds the expert, then lane i reads slot i.
+template <int GR>
+__device__ __forceinline__ void group_lookup(const Rows8 &a, int lane, int *s_n, int *s_mat, int *s_x, int *s_o)
+{
+    int n = 0, mat = 0;
+    if (!a.perm) {
+        const int G = (a.B + GR - 1) / GR;
+        const int m = blockIdx.z / G, gg = blockIdx.z % G;
+        n = a.B - gg * GR < GR ? a.B - gg * GR : GR;
+        mat = m;
+        for (int i = lane; i < n; i += 32) { s_x[i] = gg * GR + i; s_o[i] = m * a.B + gg * GR + i; }
+    } else {
+        int z = blockIdx.z, second = 0;
+        if (a.zdual && z >= a.zdual) { z -= a.zdual; second = 1; }
+        int base_groups = 0, found = -1, first = 0, cnt = 0;
+        for (int e0 = 0; e0 < a.E && found < 0; e0 += 32) {
+            const int e = e0 + lane;
+            const int o0 = e < a.E ? a.off[e] : 0, o1 = e < a.E ? a.off[e + 1] : 0;
+            const int c = o1 - o0, ng = (c + GR - 1) / GR;
+            int incl = ng;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, d); if (lane >= d) incl += v; }
+            const unsigned hit = __ballot_sync(0xffffffffu, z < base_groups + incl);
+            if (hit) {
+                const int l = __ffs(hit) - 1;
+                const int excl = __shfl_sync(0xffffffffu, incl - ng, l);
+                found = e0 + l;
+                first = __shfl_sync(0xffffffffu, o0, l) + (z - base_groups - excl) * GR;
+                cnt = __shfl_sync(0xffffffffu, o1, l) - first;
+            }
+            base_groups += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (found >= 0) {
+            n = cnt < GR ? cnt : GR;
+            mat = found | (second << 16);
+            for (int i = lane; i < n; i += 32) {
+                const int sl = a.perm[first + i];
+                s_x[i] = a.x_by_token ? sl % a.ntok : sl;
+                s_o[i] = sl + second * a.R;
+            }
+        }
+    }
+    if (lane == 0) { *s_n = n; *s_mat = mat; }
+}
+
 __global__ void __launch_bounds__(256, 2) k_gemv_rows8(const __grid_constant__ Rows8 a)
 {
     constexpr int BT = 8, CPL = 8, CW = 256, U = 4;
@@ -355,37 +416,12 @@ __global__ void __launch_bounds__(256, 2) k_gemv_rows8(const __grid_constant__ R
     __shared__ float s_rinv[BT];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kslice = a.kslice, K = a.K, N = a.N;
-    if (threadIdx.x == 0) {
-        int n = 0, mat = 0;
-        if (!a.perm) {
-            const int G = (a.B + BT - 1) / BT;
-            const int m = blockIdx.z / G, g = blockIdx.z % G;
-            n = a.B - g * BT < BT ? a.B - g * BT : BT;
-            mat = m;
-            for (int i = 0; i < n; i++) { s_x[i] = g * BT + i; s_o[i] = m * a.B + g * BT + i; }
-        } else {
-            int z = blockIdx.z, second = 0;
-            if (a.zdual && z >= a.zdual) { z -= a.zdual; second = 1; }
-            for (int e = 0; e < a.E; e++) {
-                const int c = a.off[e + 1] - a.off[e], ng = (c + BT - 1) / BT;
-                if (z < ng) {
-                    n = c - z * BT < BT ? c - z * BT : BT;
-                    mat = e | (second << 16);
-                    for (int i = 0; i < n; i++) {
-                        const int sl = a.perm[a.off[e] + z * BT + i];
-                        s_x[i] = a.x_by_token ? sl % a.ntok : sl;
-                        s_o[i] = sl + second * a.R;
-                    }
-                    break;
-                }
-                z -= ng;
-            }
-        }
-        s_n = n; s_mat = mat;
-    }
+    pdl_trigger();
+    if (a.perm) pdl_wait();                              // the slot order is the work of a kernel before this one
+    if (warp == 0) group_lookup<BT>(a, lane, &s_n, &s_mat, s_x, s_o);
     __syncthreads();
     const int nrow = s_n;
-    if (nrow == 0) return;
+    if (nrow == 0) { if (!a.perm) pdl_wait(); return; }
     const int mat = s_mat & 0xffff, second = s_mat >> 16;
     const uint8_t *codes = (second ? a.codes2 : a.codes) + (size_t)mat * a.e_codes;
     const float *scales = (second ? a.scales2 : a.scales) + (size_t)mat * a.e_scales;
@@ -407,6 +443,7 @@ __global__ void __launch_bounds__(256, 2) k_gemv_rows8(const __grid_constant__ R
         }
     };
     fetch(0);
+    if (!a.perm) pdl_wait();                             // the weights above do not depend on the kernels before; the rows below do
     if (a.gamma) {                                       // warp w: 1 / rms of row w over the whole K
         if (warp < nrow) {
             float ss = 0.0f;
@@ -538,37 +575,12 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) k_gemv_mma(const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int kslice = a.kslice, K = a.K, N = a.N, ldx = kslice + PADK;
     bf16 *xs = reinterpret_cast<bf16 *>(msm);
-    if (threadIdx.x == 0) {
-        int n = 0, mat = 0;
-        if (!a.perm) {
-            const int G = (a.B + GR - 1) / GR;
-            const int m = blockIdx.z / G, gg = blockIdx.z % G;
-            n = a.B - gg * GR < GR ? a.B - gg * GR : GR;
-            mat = m;
-            for (int i = 0; i < n; i++) { s_x[i] = gg * GR + i; s_o[i] = m * a.B + gg * GR + i; }
-        } else {
-            int z = blockIdx.z, second = 0;
-            if (a.zdual && z >= a.zdual) { z -= a.zdual; second = 1; }
-            for (int e = 0; e < a.E; e++) {
-                const int c = a.off[e + 1] - a.off[e], ng = (c + GR - 1) / GR;
-                if (z < ng) {
-                    n = c - z * GR < GR ? c - z * GR : GR;
-                    mat = e | (second << 16);
-                    for (int i = 0; i < n; i++) {
-                        const int sl = a.perm[a.off[e] + z * GR + i];
-                        s_x[i] = a.x_by_token ? sl % a.ntok : sl;
-                        s_o[i] = sl + second * a.R;
-                    }
-                    break;
-                }
-                z -= ng;
-            }
-        }
-        s_n = n; s_mat = mat;
-    }
+    pdl_trigger();
+    if (a.perm) pdl_wait();                              // the slot order is the work of a kernel before this one
+    if (warp == 0) group_lookup<GR>(a, lane, &s_n, &s_mat, s_x, s_o);
     __syncthreads();
     const int nrow = s_n;
-    if (nrow == 0) return;
+    if (nrow == 0) { if (!a.perm) pdl_wait(); return; }
     const int mat = s_mat & 0xffff, second = s_mat >> 16;
     const uint8_t *codes = (second ? a.codes2 : a.codes) + (size_t)mat * a.e_codes;
     const float *scales = (second ? a.scales2 : a.scales) + (size_t)mat * a.e_scales;
@@ -604,6 +616,7 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) k_gemv_mma(const __grid_
             }
         }
     }
+    if (!a.perm) pdl_wait();                             // codes and scales above do not depend on the kernels before; the rows below do
     const bool vec = a.x_dtype == QLMB_BF16;                     // bf16 rows are staged in 16-byte pieces, four loads in flight
     if (a.gamma) {                                       // 1 / rms of every row over the whole K: warp w takes rows w, w + 8, ...
         for (int r = warp; r < nrow; r += 8) {
@@ -754,7 +767,7 @@ static int rows8_launch(Rows8 a, int nz, int ns, cudaStream_t st)
         QLMB_CUDA(cudaFuncSetAttribute(k_gemv_rows8, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         attr_done[dv] = true;
     }
-    k_gemv_rows8<<<dim3(nb, ns, nz), 256, sm_b, st>>>(a);
+    QLMB_CUDA(pdl_launch(true, k_gemv_rows8, dim3(nb, ns, nz), dim3(256), sm_b, st, a));
     QLMB_LAUNCH_CHECK("k_gemv_rows8");
     return QLMB_OK;
 }
@@ -787,8 +800,8 @@ static int mma_launch(Rows8 a, int nz, int ns, int mt, cudaStream_t st)
         QLMB_CUDA(cudaFuncSetAttribute(k_gemv_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         attr_done[dv] = true;
     }
-    if (mt == 1) k_gemv_mma<1><<<dim3(nb, ns, nz), 256, sm_b, st>>>(a);
-    else k_gemv_mma<2><<<dim3(nb, ns, nz), 256, sm_b, st>>>(a);
+    if (mt == 1) QLMB_CUDA(pdl_launch(true, k_gemv_mma<1>, dim3(nb, ns, nz), dim3(256), sm_b, st, a));
+    else QLMB_CUDA(pdl_launch(true, k_gemv_mma<2>, dim3(nb, ns, nz), dim3(256), sm_b, st, a));
     QLMB_LAUNCH_CHECK("k_gemv_mma");
     return QLMB_OK;
 }
@@ -860,6 +873,8 @@ __global__ void __launch_bounds__(256, BT <= 2 ? 4 : 2) k_gemv_nk(float *part, c
 // Y[b,n] = sum over K slices (ascending) of part[ks][b][n]
 __global__ void __launch_bounds__(256) k_gemv_finish(void *Y, int dtype, const float *part, int nslice, size_t BN_)
 {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= BN_) return;
     float s = 0.0f;
@@ -874,6 +889,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish(void *Y, int dtype, const f
 __global__ void __launch_bounds__(256) k_gemv_finish_res_norm(bf16 *F, bf16 *Fn, const float *part, int nslice, int B, int N,
                                                               const bf16 *res, const float *gamma)
 {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[8];
     const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float v[8], rs[8], gm[8], ss = 0.0f;
@@ -926,6 +943,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish_qkv(bf16 *Y, bf16 *Kc, bf16
                                                          int hd, const float *cosb, const float *sinb, const int *pos, int Tm,
                                                          int *errword)
 {
+    pdl_trigger();
+    pdl_wait();
     const int hf = hd / 2, nh = N / hd;
     const size_t g = (size_t)blockIdx.x * 256 + threadIdx.x, RN = (size_t)3 * B * N;
     if (g >= RN / 2) return;
@@ -956,6 +975,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish_qkv(bf16 *Y, bf16 *Kc, bf16
 __global__ void __launch_bounds__(256) k_gemv_finish_swiglu(bf16 *act, const float *pg, const float *pu, int nslice, size_t RN,
                                                             size_t slice_stride)
 {
+    pdl_trigger();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= RN) return;
     float g = 0.0f, u = 0.0f;
@@ -968,6 +989,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish_swiglu(bf16 *act, const flo
 __global__ void __launch_bounds__(256) k_gemv_finish_combine(bf16 *out, const bf16 *f_in, const float *part, const float *gate,
                                                              int nslice, int ntok, int Kk, int D)
 {
+    pdl_trigger();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= (size_t)ntok * D) return;
     const int n = (int)(i / D), j = (int)(i % D);
@@ -1007,13 +1030,13 @@ int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, con
         a.e_codes = (size_t)D * F / 2; a.e_scales = (size_t)D * F / 128;
         a.rows_out = 2 * R; a.perm = perm; a.off = off; a.E = L->E; a.ntok = N; a.x_by_token = 1; a.zdual = zmax; a.R = R;
         if ((rc = mma_launch(a, 2 * zmax, ns1, 1, st))) return rc;
-        k_gemv_finish_swiglu<<<(unsigned)(((size_t)R * F + 255) / 256), 256, 0, st>>>(act, pg, pg + (size_t)R * F, ns1, (size_t)R * F, (size_t)2 * R * F);
+        pdl_launch(N > 4, k_gemv_finish_swiglu, dim3((unsigned)(((size_t)R * F + 255) / 256)), dim3(256), 0, st, act, pg, pg + (size_t)R * F, ns1, (size_t)R * F, (size_t)2 * R * F);
         Rows8 b = {};
         b.part = pd; b.X = act; b.x_dtype = QLMB_BF16; b.K = F; b.N = D;
         b.codes = (const uint8_t *)L->w2_codes; b.scales = L->w2_scales; b.e_codes = (size_t)D * F / 2; b.e_scales = (size_t)D * F / 128;
         b.rows_out = R; b.perm = perm; b.off = off; b.E = L->E; b.ntok = N; b.x_by_token = 0; b.zdual = 0; b.R = R;
         if ((rc = mma_launch(b, zmax, ns2, 1, st))) return rc;
-        k_gemv_finish_combine<<<(unsigned)(((size_t)N * D + 255) / 256), 256, 0, st>>>((bf16 *)out, (const bf16 *)f_in, pd, gate, ns2, N, K, D);
+        pdl_launch(N > 4, k_gemv_finish_combine, dim3((unsigned)(((size_t)N * D + 255) / 256)), dim3(256), 0, st, (bf16 *)out, (const bf16 *)f_in, pd, gate, ns2, N, K, D);
         QLMB_LAUNCH_CHECK("moe_decode_experts");
         return QLMB_OK;
     }
@@ -1039,21 +1062,17 @@ int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, con
     const dim3 g1((F + 255) / 256, ns1, 2 * R), g2((D + 255) / 256, ns2, R);
     const size_t small_grid = (size_t)2 * sm_count();
     if ((size_t)g1.x * g1.y * g1.z <= small_grid)
-        k_gemv_kn<1, 4><<<g1, 256, (size_t)ks1 * sizeof(float), st>>>(
-            pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N, nullptr, R,
+        launch_kn<1, 4>(N > 4, g1, (size_t)ks1 * sizeof(float), st, pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N, nullptr, R,
             (const uint8_t *)L->w3_codes, L->w3_scales);
     else
-        k_gemv_kn<1><<<g1, 256, (size_t)ks1 * sizeof(float), st>>>(
-            pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N, nullptr, R,
+        launch_kn<1, 2>(N > 4, g1, (size_t)ks1 * sizeof(float), st, pg, f_norm, QLMB_BF16, (const uint8_t *)L->w1_codes, L->w1_scales, 1, D, F, ks1, assign, ec, es, N, nullptr, R,
             (const uint8_t *)L->w3_codes, L->w3_scales);
-    k_gemv_finish_swiglu<<<(unsigned)(((size_t)R * F + 255) / 256), 256, 0, st>>>(act, pg, pu, ns1, (size_t)R * F, (size_t)2 * R * F);
+    pdl_launch(N > 4, k_gemv_finish_swiglu, dim3((unsigned)(((size_t)R * F + 255) / 256)), dim3(256), 0, st, act, pg, pu, ns1, (size_t)R * F, (size_t)2 * R * F);
     if ((size_t)g2.x * g2.y * g2.z <= small_grid)
-        k_gemv_kn<1, 4><<<g2, 256, (size_t)ks2 * sizeof(float), st>>>(
-            pd, act, QLMB_BF16, (const uint8_t *)L->w2_codes, L->w2_scales, 1, F, D, ks2, assign, ec, es, R);
+        launch_kn<1, 4>(N > 4, g2, (size_t)ks2 * sizeof(float), st, pd, act, QLMB_BF16, (const uint8_t *)L->w2_codes, L->w2_scales, 1, F, D, ks2, assign, ec, es, R);
     else
-        k_gemv_kn<1><<<g2, 256, (size_t)ks2 * sizeof(float), st>>>(
-            pd, act, QLMB_BF16, (const uint8_t *)L->w2_codes, L->w2_scales, 1, F, D, ks2, assign, ec, es, R);
-    k_gemv_finish_combine<<<(unsigned)(((size_t)N * D + 255) / 256), 256, 0, st>>>((bf16 *)out, (const bf16 *)f_in, pd, gate, ns2, N, K, D);
+        launch_kn<1, 2>(N > 4, g2, (size_t)ks2 * sizeof(float), st, pd, act, QLMB_BF16, (const uint8_t *)L->w2_codes, L->w2_scales, 1, F, D, ks2, assign, ec, es, R);
+    pdl_launch(N > 4, k_gemv_finish_combine, dim3((unsigned)(((size_t)N * D + 255) / 256)), dim3(256), 0, st, (bf16 *)out, (const bf16 *)f_in, pd, gate, ns2, N, K, D);
     QLMB_LAUNCH_CHECK("moe_decode_experts");
     return QLMB_OK;
 }
@@ -1097,8 +1116,8 @@ static int gemv_decode_impl(void *Y, const void *X, const int8_t *codes, const f
         a.part = (float *)wsr; a.X = X; a.x_dtype = dtype; a.K = K; a.N = N;
         a.codes = (const uint8_t *)codes; a.scales = scales; a.B = B; a.nmat = 1; a.rows_out = B;
         if ((rcr = tc ? mma_launch(a, nz, ns, mt, st) : rows8_launch(a, nz, ns, st))) return rcr;
-        if (fr) k_gemv_finish_res_norm<<<B, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, a.part, ns, B, N, (const bf16 *)fr->res, fr->gamma);
-        else k_gemv_finish<<<(unsigned)(((size_t)B * N + 255) / 256), 256, 0, st>>>(Y, dtype, a.part, ns, (size_t)B * N);
+        if (fr) pdl_launch(B > 4, k_gemv_finish_res_norm, dim3(B), dim3(256), 0, st, (bf16 *)Y, (bf16 *)fr->Fn, a.part, ns, B, N, (const bf16 *)fr->res, fr->gamma);
+        else pdl_launch(B > 4, k_gemv_finish, dim3((unsigned)(((size_t)B * N + 255) / 256)), dim3(256), 0, st, Y, dtype, a.part, ns, (size_t)B * N);
         QLMB_LAUNCH_CHECK("qlmb_gemv_decode");
         return QLMB_OK;
     }
@@ -1164,12 +1183,17 @@ static int gemv_decode_impl(void *Y, const void *X, const int8_t *codes, const f
         else KERN<8><<<grid, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice); \
     } while (0)
     if (layout == QLMB_KN && bt == 1 && (size_t)nblk * nslice <= (size_t)2 * sm_count())
-        k_gemv_kn<1, 4><<<grid, 256, smem, st>>>(part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice);
-    else if (layout == QLMB_KN) GV_LAUNCH(k_gemv_kn);
+        launch_kn<1, 4>(B > 4, grid, smem, st, part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice);
+    else if (layout == QLMB_KN) {
+        if (bt == 1) launch_kn<1, 2>(B > 4, grid, smem, st, part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice);
+        else if (bt == 2) launch_kn<2, 2>(B > 4, grid, smem, st, part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice);
+        else if (bt == 4) launch_kn<4, 2>(B > 4, grid, smem, st, part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice);
+        else launch_kn<8, 2>(B > 4, grid, smem, st, part, X, dtype, (const uint8_t *)codes, scales, B, K, N, kslice);
+    }
     else GV_LAUNCH(k_gemv_nk);
 #undef GV_LAUNCH
-    if (fr) k_gemv_finish_res_norm<<<B, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, part, nslice, B, N, (const bf16 *)fr->res, fr->gamma);
-    else k_gemv_finish<<<(unsigned)(((size_t)B * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)B * N);
+    if (fr) pdl_launch(B > 4, k_gemv_finish_res_norm, dim3(B), dim3(256), 0, st, (bf16 *)Y, (bf16 *)fr->Fn, part, nslice, B, N, (const bf16 *)fr->res, fr->gamma);
+    else pdl_launch(B > 4, k_gemv_finish, dim3((unsigned)(((size_t)B * N + 255) / 256)), dim3(256), 0, st, Y, dtype, part, nslice, (size_t)B * N);
     QLMB_LAUNCH_CHECK("qlmb_gemv_decode");
     return QLMB_OK;
 }
@@ -1215,15 +1239,12 @@ static int gemv_stack_impl(void *Y, const void *X, const int8_t *codes, const fl
         a.B = B; a.nmat = nmat; a.rows_out = R; a.gamma = gamma;
         if ((rc = tc ? mma_launch(a, nz, nslice, mt, st) : rows8_launch(a, nz, nslice, st))) return rc;
     } else if ((size_t)nblk * nslice * R <= (size_t)2 * sm_count())
-        k_gemv_kn<1, 4><<<dim3(nblk, nslice, R), 256, (size_t)kslice * sizeof(float), st>>>(
-            part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
+        launch_kn<1, 4>(B > 4, dim3(nblk, nslice, R), (size_t)kslice * sizeof(float), st, part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
     else
-        k_gemv_kn<1><<<dim3(nblk, nslice, R), 256, (size_t)kslice * sizeof(float), st>>>(
-            part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
-    if (fr) k_gemv_finish_res_norm<<<R, 256, 0, st>>>((bf16 *)Y, (bf16 *)fr->Fn, part, nslice, R, N, (const bf16 *)fr->res, fr->gamma);
-    else if (fq) k_gemv_finish_qkv<<<(unsigned)(((size_t)R * N / 2 + 255) / 256), 256, 0, st>>>(
-        (bf16 *)Y, (bf16 *)fq->Kc, (bf16 *)fq->Vc, part, nslice, B, N, fq->hd, fq->cosb, fq->sinb, fq->pos, fq->Tm, device_error_word());
-    else k_gemv_finish<<<(unsigned)(((size_t)R * N + 255) / 256), 256, 0, st>>>(Y, dtype, part, nslice, (size_t)R * N);
+        launch_kn<1, 2>(B > 4, dim3(nblk, nslice, R), (size_t)kslice * sizeof(float), st, part, X, dtype, (const uint8_t *)codes, scales, 1, K, N, kslice, nullptr, (size_t)K * N / 2, (size_t)K * N / 128, B, gamma);
+    if (fr) pdl_launch(B > 4, k_gemv_finish_res_norm, dim3(R), dim3(256), 0, st, (bf16 *)Y, (bf16 *)fr->Fn, part, nslice, R, N, (const bf16 *)fr->res, fr->gamma);
+    else if (fq) pdl_launch(B > 4, k_gemv_finish_qkv, dim3((unsigned)(((size_t)R * N / 2 + 255) / 256)), dim3(256), 0, st, (bf16 *)Y, (bf16 *)fq->Kc, (bf16 *)fq->Vc, part, nslice, B, N, fq->hd, fq->cosb, fq->sinb, fq->pos, fq->Tm, device_error_word());
+    else pdl_launch(B > 4, k_gemv_finish, dim3((unsigned)(((size_t)R * N + 255) / 256)), dim3(256), 0, st, Y, dtype, part, nslice, (size_t)R * N);
     QLMB_LAUNCH_CHECK("qlmb_gemv_decode_stack");
     return QLMB_OK;
 }

@@ -149,10 +149,12 @@ __global__ void __launch_bounds__(256) k_router_small(float *rt, const void *X, 
     // 32 rows of Wr in flight per lane (the loads depend neither on the sum nor on the activations: the first batch is
     // requested before the row is staged); the sum itself stays in ascending order
     float w[32];
+    pdl_trigger();
     if (e < E) {
 #pragma unroll
         for (int u = 0; u < 32; u++) w[u] = j0 + u < j1 ? __ldg(Wr + (size_t)(j0 + u) * E + e) : 0.0f;
     }
+    pdl_wait();                                          // the router matrix above is no kernel's output; the row below is
     for (int j = threadIdx.x; j < D; j += 256)
         rs_x[j] = x_dtype == QLMB_BF16 ? __bfloat162float(((const bf16 *)X)[(size_t)n * D + j]) : ((const float *)X)[(size_t)n * D + j];
     __syncthreads();
@@ -431,7 +433,7 @@ int router_small(float *rt, const void *X, int x_dtype, const float *Wr, float *
         int rc = router_logits_small(rt, X, x_dtype, Wr, N, D, E, st);
         return rc ? rc : router_topk(rt, rprobs, assign, gate, N, E, K, bias, bs, st);
     }
-    k_router_small<<<N, 256, (size_t)D * sizeof(float), st>>>(rt, X, x_dtype, Wr, rprobs, assign, gate, N, D, E, K, bias, bs);
+    QLMB_CUDA(pdl_launch(N > 4, k_router_small, dim3(N), dim3(256), (size_t)D * sizeof(float), st, rt, X, x_dtype, Wr, rprobs, assign, gate, N, D, E, K, bias, bs));
     QLMB_LAUNCH_CHECK("k_router_small");
     return QLMB_OK;
 }

@@ -26,6 +26,13 @@ int cuda_fail(cudaError_t e, const char *what)
 static int *g_errword[64];
 static int g_sms[64];
 
+bool pdl_enabled(void)
+{
+    static int on = -1;
+    if (on < 0) { const char *e = getenv("QLMB_PDL"); on = (e && atoi(e) == 0) ? 0 : 1; }
+    return on != 0;
+}
+
 int *device_error_word(void)
 {
     int dev = 0;
