@@ -1009,13 +1009,13 @@ __global__ void __launch_bounds__(256) k_gemv_finish_combine(bf16 *out, const bf
 // Experts of a decode step with at most 128 routed rows: three routed GEMVs that read only the chosen experts'
 // codes (W1, W3: [E][D][F]; W2: [E][F][D]), SwiGLU and the gate-weighted combination in the slice-sum kernels.
 int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, const void *f_norm, const int *assign,
-                       const float *gate, cudaStream_t st, int *perm, int *off, int *counts, int *bad)
+                       const float *gate, cudaStream_t st, int *perm, int *off, int *counts, int *bad, int perm_ready)
 {
     const int N = L->N, D = L->D, F = L->F, K = L->K, R = K * N;
     if (R > 16 && perm && off && bad) {
         // many routed rows: sort the slots by expert once, then every expert's matrices are read once per group of
         // sixteen of its slots instead of once per slot
-        int rc = perm_build(assign, N, L->E, K, 1, 1, perm, nullptr, off, counts, bad, nullptr, nullptr, nullptr, st);
+        int rc = perm_ready ? 0 : perm_build(assign, N, L->E, K, 1, 1, perm, nullptr, off, counts, bad, nullptr, nullptr, nullptr, st);
         if (rc) return rc;
         const int zmax = L->E + R / 16;                  // sum over the experts of ceil(count / 16) never exceeds this
         const int ns1 = mma_slices(D, F, 2 * L->E, 1), ns2 = mma_slices(F, D, L->E, 1);

@@ -71,12 +71,15 @@ struct GemmProblem;   // see qlmb_gemm.cuh
 // router logits of a few rows (decode): deterministic, not the tiled kernel's summation order
 int router_logits_small(float *rt, const void *X, int x_dtype, const float *Wr, int N, int D, int E, cudaStream_t st);
 // the same logits and the selection in one launch (qlmb_route.cu); larger shapes fall back to the two kernels
+// perm / off / counts / bad (optional): with at most 256 routed slots the same launch groups the slots by expert;
+// *perm_done tells the caller whether it did
 int router_small(float *rt, const void *X, int x_dtype, const float *Wr, float *rprobs, int *assign, float *gate, int N, int D,
-                 int E, int K, const float *bias, int bs, cudaStream_t st);
+                 int E, int K, const float *bias, int bs, cudaStream_t st, int *perm = nullptr, int *off = nullptr,
+                 int *counts = nullptr, int *bad = nullptr, int *perm_done = nullptr);
 // experts of a decode step with at most 64 routed rows (qlmb_gemv.cu): routed GEMVs over the chosen experts' codes
 // perm / off / counts / bad: scratch of the permutation (K*N, E + 1, E and 1 ints) for steps with more than 16 routed rows
 int moe_decode_experts(const qlmb_moe_layer *L, void *out, const void *f_in, const void *f_norm, const int *assign,
                        const float *gate, cudaStream_t st, int *perm = nullptr, int *off = nullptr, int *counts = nullptr,
-                       int *bad = nullptr);
+                       int *bad = nullptr, int perm_ready = 0);
 
 }  // namespace qlmb

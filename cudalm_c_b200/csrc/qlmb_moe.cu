@@ -251,8 +251,12 @@ extern "C" int qlmb_moe_decode(const qlmb_moe_layer *L, void *arena, void *out, 
     const int N = L->N, D = L->D, F = L->F, E = L->E, K = L->K;
     Arena a = carve(arena, N, D, F, E, K);
     cudaStream_t st = as_stream(stream);
-    if ((rc = router_small(a.rt, f_norm, L->dtype, L->wr, a.rprobs, a.assign, a.gate, N, D, E, K, L->bias, L->bias_stride, st))) return rc;
-    return moe_decode_experts(L, out, f_in, f_norm, a.assign, a.gate, st, a.perm, a.off, a.counts, a.bad);
+    // more than 16 routed rows: the experts' GEMVs want the slots grouped by expert, which the router's launch does on the way
+    int grouped = 0;
+    const bool want = K * N > 16;
+    if ((rc = router_small(a.rt, f_norm, L->dtype, L->wr, a.rprobs, a.assign, a.gate, N, D, E, K, L->bias, L->bias_stride, st,
+                           want ? a.perm : nullptr, a.off, a.counts, a.bad, want ? &grouped : nullptr))) return rc;
+    return moe_decode_experts(L, out, f_in, f_norm, a.assign, a.gate, st, a.perm, a.off, a.counts, a.bad, grouped);
 }
 
 extern "C" int qlmb_moe_backward(const qlmb_moe_layer *L, void *arena, void *dfnorm, const void *dout,

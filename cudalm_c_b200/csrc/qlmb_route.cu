@@ -138,9 +138,14 @@ __global__ void __launch_bounds__(256) k_router_topk_warp(const float *rt, float
 // A decode step's few rows: logits and selection in one launch, one block per token.  The logits are those of
 // k_router_logits_small (lane = expert, eight warps each sum one eighth of the features in ascending order with fused
 // multiply-adds, the eight partial sums added in warp order); warp 0 then runs the selection above on them.
+// With perm != NULL (at most 256 routed slots) the block that finishes last also groups the K*N slots by expert in
+// stable order (what k_perm_cluster does in a launch of its own): perm[off[e] ..] = the slots of expert e ascending,
+// off[0..E], counts[0..E), *bad = an expert id out of range.  The blocks take tickets after a fence, so the last one sees
+// every block's choices; the result does not depend on which block that is.
+__device__ unsigned g_router_ticket;
 __global__ void __launch_bounds__(256) k_router_small(float *rt, const void *X, int x_dtype, const float *Wr, float *rprobs,
                                                       int *assign, float *gate, int N, int D, int E, int K,
-                                                      const float *bias, int bs)
+                                                      const float *bias, int bs, int *perm, int *off, int *counts, int *bad)
 {
     extern __shared__ float rs_x[];                      // D activations
     __shared__ float part[8][32];
@@ -172,15 +177,48 @@ __global__ void __launch_bounds__(256) k_router_small(float *rt, const void *X, 
     }
     part[warp][e] = acc;
     __syncthreads();
-    if (warp != 0) return;
-    float lg = 0.0f;
-    if (e < E) {
-        lg = part[0][e];
+    if (warp == 0) {
+        float lg = 0.0f;
+        if (e < E) {
+            lg = part[0][e];
 #pragma unroll
-        for (int w = 1; w < 8; w++) lg += part[w][e];
-        rt[(size_t)n * E + e] = lg;
+            for (int w = 1; w < 8; w++) lg += part[w][e];
+            rt[(size_t)n * E + e] = lg;
+        }
+        router_topk_row(lg, n, e, rprobs, assign, gate, N, E, K, bias, bs);
+        __threadfence();                                 // this token's choices are visible before its ticket is
     }
-    router_topk_row(lg, n, e, rprobs, assign, gate, N, E, K, bias, bs);
+    if (!perm) return;
+    __shared__ int s_last, s_asn[256], s_off[33], s_bad;
+    __syncthreads();
+    if (threadIdx.x == 0) { s_last = atomicAdd(&g_router_ticket, 1u) == (unsigned)(N - 1); s_bad = 0; }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int R = K * N, t = threadIdx.x;
+    int my = -1;
+    if (t < R) {
+        my = __ldcg(assign + t);
+        if (my < 0 || my >= E) { atomicMax(&s_bad, 1); my = -1; }
+        s_asn[t] = my;
+    }
+    __syncthreads();
+    if (warp == 0) {                                     // lane = expert: count, exclusive scan, offsets
+        int c = 0;
+        if (e < E) for (int i = 0; i < R; i++) c += s_asn[i] == e;
+        int incl = c;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, d); if (e >= d) incl += v; }
+        if (e < E) { s_off[e] = incl - c; off[e] = incl - c; if (counts) counts[e] = c; }
+        if (e == E - 1) { s_off[E] = incl; off[E] = incl; }
+    }
+    __syncthreads();
+    if (my >= 0) {
+        int rank = 0;
+        for (int i = 0; i < t; i++) rank += s_asn[i] == my;
+        perm[s_off[my] + rank] = t;
+    }
+    if (t == 0) { if (bad) *bad = s_bad; g_router_ticket = 0u; }
 }
 
 // ------------------------------------------------------------- permutation
@@ -427,13 +465,17 @@ int router_topk(const float *rt, float *rprobs, int *assign, float *gate, int N,
 }
 
 int router_small(float *rt, const void *X, int x_dtype, const float *Wr, float *rprobs, int *assign, float *gate, int N, int D,
-                 int E, int K, const float *bias, int bs, cudaStream_t st)
+                 int E, int K, const float *bias, int bs, cudaStream_t st, int *perm, int *off, int *counts, int *bad, int *perm_done)
 {
+    if (perm_done) *perm_done = 0;
     if (N > 64 || E > 32 || D > 8192) {
         int rc = router_logits_small(rt, X, x_dtype, Wr, N, D, E, st);
         return rc ? rc : router_topk(rt, rprobs, assign, gate, N, E, K, bias, bs, st);
     }
-    QLMB_CUDA(pdl_launch(N > 4, k_router_small, dim3(N), dim3(256), (size_t)D * sizeof(float), st, rt, X, x_dtype, Wr, rprobs, assign, gate, N, D, E, K, bias, bs));
+    const bool fuse = perm && off && perm_done && K * N <= 256;      // the last block also groups the slots by expert
+    if (fuse) *perm_done = 1;
+    QLMB_CUDA(pdl_launch(N > 4, k_router_small, dim3(N), dim3(256), (size_t)D * sizeof(float), st, rt, X, x_dtype, Wr, rprobs, assign, gate, N, D, E, K, bias, bs,
+                         fuse ? perm : (int *)nullptr, off, counts, bad));
     QLMB_LAUNCH_CHECK("k_router_small");
     return QLMB_OK;
 }

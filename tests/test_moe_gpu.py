@@ -190,7 +190,7 @@ def test_selection_bias_balances_the_load(cuda):
     assert peak[0] > 2 * int(m) and peak[-1] < peak[0] // 2, peak
 
 
-@pytest.mark.parametrize("N", [1, 8, 32, 48])
+@pytest.mark.parametrize("N", [1, 8, 32, 48, 64])
 def test_decode_step_matches_the_training_forward(cuda, N):
     """qlmb_moe_decode (dec_step's moe_forward on a few rows, cudalm.cu:7193): routed GEMVs up to 64 routed rows (one launch
     for logits + selection), the grouped-GEMM path above; the same experts and the same output as qlmb_moe_forward
@@ -213,6 +213,13 @@ def test_decode_step_matches_the_training_forward(cuda, N):
     assert torch.equal(Bd.member("gate", (K, N), torch.float32)[:, same] > 0, torch.ones(K, int(same.sum()), dtype=torch.bool, device=cuda))
     assert rel(out_d[same], out_f[same]) < TOL_F
     assert torch.equal(out_d, Bd.decode(fi, fn))         # deterministic
+    if K * N > 16:
+        # the router's launch grouped the slots by expert on the way: same table as the permutation kernel builds
+        from cudalm_c_b200._lib import check, lib, ptr, stream_ptr
+        perm = torch.full((K * N,), -7, dtype=torch.int32, device=cuda); off = torch.zeros(E + 1, dtype=torch.int32, device=cuda)
+        counts = torch.zeros(E, dtype=torch.int32, device=cuda); bad = torch.zeros(1, dtype=torch.int32, device=cuda)
+        check(lib().qlmb_perm_build(ptr(asg_d), N, E, K, 1, 1, ptr(perm), None, ptr(off), ptr(counts), ptr(bad), stream_ptr()))
+        assert torch.equal(Bd.member("perm", (K * N,), torch.int32), perm) and torch.equal(Bd.member("off", (E + 1,), torch.int32), off)
 
 
 def test_config2_full_size_properties(cuda):
