@@ -46,6 +46,7 @@ PROTOTYPES = {
     "qlmb_version": (ci, []),
     "qlmb_check_device": (ci, [vp]),
     "qlmb_selftest_wait_expires": (ci, [ci, vp]),
+    "qlmb_selftest_stream_read": (ci, [vp, u64, ci, ci, vp]),
     "qlmb_skipped_steps": (ci, [vp, ci, vp]),
     "qlmb_prof_enable": (ci, [ci]),
     "qlmb_side_stream_enable": (ci, [ci]),

@@ -69,6 +69,11 @@ int qlmb_check_device(void *stream);
  * times (1..65536), records error code 200 / site 9999 in the device error word and returns.  The next
  * qlmb_check_device reports QLMB_E_DEVICE and clears the word; later launches run as usual. */
 int qlmb_selftest_wait_expires(int polls, void *stream);
+/* No counterpart in the reference.  Calibration for the decode GEMV's roofline: a kernel that only LOADS a matrix of
+ * `rows` rows of `row_bytes` bytes (a multiple of 256) once, in the grid shape of the streaming GEMV (256-byte column
+ * blocks x kslices row slices, 16 rows in flight per lane), and does no arithmetic.  Its duration is what launch,
+ * first-load latency and the tail cost at that size; bench.py reports it beside the GEMV's. */
+int qlmb_selftest_stream_read(const void *W, unsigned long long row_bytes, int rows, int kslices, void *stream);
 
 /* Work that does not depend on each other inside one call (the three expert weight-gradient GEMMs
  * of the MoE backward against d(act) and dX, the router's backward chain against all of them) runs on
