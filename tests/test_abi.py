@@ -77,3 +77,20 @@ def test_no_fallback_when_library_missing(monkeypatch):
     monkeypatch.setattr(m, "lib_path", lambda: "/nonexistent/libqlm_b200.so")
     with pytest.raises(m.QlmbError):
         m.lib()
+
+
+def test_new_entry_points_reject_bad_arguments_without_a_gpu():
+    """Argument checks of the entry points added for the engram table, the exact 4-bit export and the native
+    communicator run before any CUDA call: status 1 and a message, nothing fatal."""
+    import cudalm_c_b200 as q
+    L = q.lib()
+    assert L.qlmb_eg_key(None, None, None, None, None, None, 8, 4, 2, 16, None) == 1 and b"qlmb_eg_key" in L.qlmb_last_error()
+    assert L.qlmb_eg_gather(None, None, None, 8, 2, 32, None) == 1
+    assert L.qlmb_q4n_export(None, 0, None, None, 1024, 128, None, None) == 1
+    assert L.qlmb_q4n_decode(None, None, None, 1024, 128, None) == 1
+    assert L.qlmb_q4n_work_bytes(1024, 128) >= 8 * 9 + 8 * 8 and L.qlmb_q4n_max_bytes(1000, 128) == 8 * 4 + 4000
+    assert L.qlmb_q4n_work_bytes(1024, 0) == 0
+    assert L.qlmb_comm_init(None, None, 0, 1) == 1 and b"qlmb_comm_init" in L.qlmb_last_error()
+    assert L.qlmb_comm_rank(None) == -1 and L.qlmb_comm_world(None) == 0
+    assert L.qlmb_comm_destroy(None) == 0
+    assert L.qlmb_selftest_stream_read(None, 256, 8, 1, None) == 1
