@@ -924,7 +924,8 @@ def run_train(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     cfg = model.Config()
-    m = model.QlmModel(cfg, dev, seed=1, aux=0.03, rank=rank, world=world)
+    fused = bool(args.fused_update) and world == 1
+    m = model.QlmModel(cfg, dev, seed=1, aux=0.03, rank=rank, world=world, fused=fused)
     N = cfg.B * cfg.T
     g = torch.Generator(device="cpu"); g.manual_seed(rank)
     toks = [torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).pin_memory() for _ in range(4)]
@@ -949,7 +950,7 @@ def run_train(args):
     for i in range(max(args.warmup, 3)):
         step(i)
     torch.cuda.synchronize()
-    if world == 1 and not args.no_graph:
+    if world == 1 and not args.no_graph and not fused:   # the fused update's step counter changes inside backward: not captured
         # one GPU: the host needs about as long to issue the step's launches as the GPU to run them, so forward
         # and backward are replayed from a CUDA graph (same kernels, same order; the library keeps its side streams off
         # while a stream is captured)
@@ -992,6 +993,9 @@ def run_train(args):
                                       L=cfg.L, D=cfg.D, heads=cfg.H,
                                       experts=cfg.E, top_k=cfg.K, F=cfg.F, V=cfg.V, B=cfg.B, T=cfg.T,
                                       params_quantised=int(m.q.nq), params_float=int(m.q.nfloat),
+                                      update=("fused per layer inside backward (qlm_fused_layer / _tail): one gradient block shared by all layers, "
+                                              "clip multiplier of the previous step" if fused else "separate (gpu_adam): global norm, then one pass over all spans"),
+                                      gradient_bytes=int(m.G.numel()) * 4,
                                       l2="weights 0.74 GB of codes, activations and gradients several GB per step: far beyond the 126 MB L2"),
                           roofline=dict(bound="tensor", kernel="whole step", achieved=round(flops / (ms * 1e-3) / 1e12, 1),   # per GPU
                                         peak=pk["tf_sustained"], unit="TFLOP/s",
@@ -1221,6 +1225,7 @@ def main():
     ap.add_argument("--params", type=int, default=125829120, help="span size of --workload adamw")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="N>1: peer = foreign rows read by peer loads inside the row kernels; nccl = all-to-all exchanges")
+    ap.add_argument("--fused-update", action="store_true", help="--workload train, one GPU: the reference's fused per-layer update (CUDALM_QLM_FUSED) instead of the separate optimizer pass")
     ap.add_argument("--no-graph", action="store_true", help="--workload train: issue every launch from the host instead of replaying forward + backward from a CUDA graph")
     ap.add_argument("--decode-b", default="1,8,64", help="live slots of --workload decode (comma list; BASELINE config 5 has 1,8,64)")
     ap.add_argument("--new-tokens", type=int, default=256, help="generated tokens of --workload decode (256 in BASELINE config 5; fewer for profiler captures)")

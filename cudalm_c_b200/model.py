@@ -48,10 +48,15 @@ class QlmModel:
     sharded (rank r owns experts r*E/W .. of every layer, PeerExpertParallelLayer), everything else replicated;
     the replicated gradients are all-reduced, the clip norm is global, every rank steps its own spans."""
 
-    def __init__(self, cfg, device, seed=1, aux=0.0, rank=0, world=1, group=None, init_blocks=None, P_init=None):
+    def __init__(self, cfg, device, seed=1, aux=0.0, rank=0, world=1, group=None, init_blocks=None, P_init=None, fused=False):
+        """fused (one GPU): the fused per-layer update of the reference (CUDALM_QLM_FUSED; qlm_fused_layer / qlm_fused_tail,
+        cudalm.cu:6105-6187, gradient layout calc_goffsets 6008-6040): all layers share ONE gradient block, which
+        backward() consumes as soon as a layer's gradients are complete; the clip multiplier is the previous step's."""
         c = self.c = cfg
         self.dev = device
         self.rank, self.world, self.group = rank, world, group
+        self.fused = bool(fused)
+        assert not (fused and world > 1)
         assert c.E % world == 0
         self.el = el = c.E // world
         o = self.o = Offsets(c, el)
@@ -104,7 +109,21 @@ class QlmModel:
         self.nf = self._fview(o.nf, c.D)
         self.fl = [{nm: self._fview(*lo[nm]) for nm in ("an1", "an2", "wr")} for lo in o.layers]
         del P
-        self.G = torch.zeros(o.total, dtype=torch.float32, device=device)
+        # gradients: the reference's layout, or (fused) emb | one layer block shared by all layers | nf
+        self.layer_n = o.layers[0]["w2"][0] + o.layers[0]["w2"][1] - o.layers[0]["an1"][0]
+        self.g_layer0 = o.layers[0]["an1"][0]
+        if self.fused:
+            self.g_nf = self.g_layer0 + self.layer_n
+            self.G = torch.zeros(self.g_nf + c.D, dtype=torch.float32, device=device)
+            for i in range(self.q.nspan):                               # qlm_set_gof: gradients are read from the shared block
+                self.q.spanH[i]["gof"] = int(self.q.spanH[i]["pof"]) - (i // 7) * self.layer_n
+            self.q.spanD = qlm.spans_to_device(self.q.spanH, device)
+            self.gnpart = torch.zeros(64 * (c.L + 2), dtype=torch.float32, device=device)
+            self.fgs = torch.ones(2, dtype=torch.float32, device=device)       # g_prev_gn = 1 before the first step
+            self.fused_lr = 3e-4
+        else:
+            self.g_nf = o.nf
+            self.G = torch.zeros(o.total, dtype=torch.float32, device=device)
         self.cosb, self.sinb = block.rope_tables(c.T, c.hd, device=device)
         N = c.B * c.T
         self.N = N
@@ -138,7 +157,42 @@ class QlmModel:
 
     def _g(self, l, nm):
         a, n = self.o.layers[l][nm]
+        if self.fused:
+            a -= l * self.layer_n                        # every layer's gradients live in the one shared block
         return self.G[a:a + n]
+
+    def _fused_layer(self, l, b1=0.9, b2=0.95, wd=0.1, wdf=0.0):
+        """qlm_fused_layer (cudalm.cu:6110-6140): layer l's gradients are complete and still in the shared block."""
+        q, t, lr = self.q, self.t + 1, self.fused_lr
+        qlm.sqsum(self.G[self.g_layer0:self.g_layer0 + self.layer_n], self.gnpart[64 * l:64 * l + 64])
+        s0 = 7 * l
+        gi0 = int(q.spanH[s0]["gi0"])
+        ng = int(sum(int(q.spanH[i]["ngrp"]) for i in range(s0, s0 + 7)))
+        q.step(None, self.G, lr, b1, b2, wd, t, gscale=1.0, gsp=self.fgs, gi_base=gi0, ng=ng)
+        bc1, bc2 = qlm.bias_corrections(b1, b2, t)
+        for nm in ("an1", "an2", "wr"):
+            a, n = self.o.layers[l][nm]
+            cs = self._cs(a)
+            qlm.adamw(self.fl[l][nm], self._g(l, nm), q.Mc[cs:cs + n], q.Vc[cs:cs + n], lr, b1, b2, wdf, bc1, bc2, self.fgs)
+
+    def _fused_tail(self, b1=0.9, b2=0.95, wd=0.1, wdf=0.0):
+        """qlm_fused_tail (cudalm.cu:6148-6187): emb and nf keep private gradient slots; the step's norm is closed on the
+        device and clips the NEXT step."""
+        c, o, q, t, lr = self.c, self.o, self.q, self.t + 1, self.fused_lr
+        bc1, bc2 = qlm.bias_corrections(b1, b2, t)
+        tail = ((self.emb.view(-1), o.emb, 0, c.V * c.D), (self.nf, o.nf, self.g_nf, c.D))
+        for pt, p_off, g_off, n in tail:
+            cs = self._cs(p_off)
+            qlm.adamw(pt, self.G[g_off:g_off + n], q.Mc[cs:cs + n], q.Vc[cs:cs + n], lr, b1, b2, wdf, bc1, bc2, self.fgs)
+        for i, (pt, p_off, g_off, n) in enumerate(tail):
+            qlm.sqsum(self.G[g_off:g_off + n], self.gnpart[64 * (c.L + i):64 * (c.L + i) + 64])
+        qlm.gnorm_close(self.gnpart, c.L + 2, self.fgs)
+
+    def _cs(self, p_off):
+        for off, n, cs in self.q.fs:
+            if off <= p_off < off + n:
+                return cs + (p_off - off)
+        raise ValueError("offset %d is not in a float span" % p_off)
 
     # ------------------------------------------------------------------ model file
     def params(self):
@@ -210,7 +264,7 @@ class QlmModel:
         G_emb = G[o.emb:o.emb + c.V * c.D].view(c.V, c.D)
         G_emb.zero_()
         loss, dfn = block.head_bwd(self.fn, self.emb, tgt, G_emb, chunk_rows=2048, denom=N * self.world)
-        g_nf = G[o.nf:o.nf + c.D]; g_nf.zero_()
+        g_nf = G[self.g_nf:self.g_nf + c.D]; g_nf.zero_()
         dout = torch.empty(N, c.D, dtype=torch.bfloat16, device=self.dev)
         block.rmsnorm_bwd(dout, self.x_final, self.nf, self.fnr, dfn, dgamma=g_nf, accumulate=False)
         for l in range(c.L - 1, -1, -1):
@@ -238,6 +292,8 @@ class QlmModel:
             linear.linear_wgrad(gv("wv", (c.D, c.KD)), dv, s["a_norm"], KN, beta=0.0)
             g = self._g(l, "an1"); g.zero_()
             block.rmsnorm_bwd(dout, s["a_in"], f["an1"], s["r1"], d_an, dgamma=g)             # dout now = d a_in
+            if self.fused:
+                self._fused_layer(l)
             if self.world > 1:      # an1 wq wk wv wo an2 wr are one contiguous range of G: sum over the ranks, overlapped
                 a0, a1 = o.layers[l]["an1"][0], o.layers[l]["wr"][0] + o.layers[l]["wr"][1]
                 self.pending.append(torch.distributed.all_reduce(G[a0:a1], group=self.group, async_op=True))
@@ -245,6 +301,8 @@ class QlmModel:
         if self.world > 1:
             self.pending.append(torch.distributed.all_reduce(G_emb, group=self.group, async_op=True))
             self.pending.append(torch.distributed.all_reduce(g_nf, group=self.group, async_op=True))
+        if self.fused:
+            self._fused_tail()
         self.saved = None
         return loss
 
@@ -254,6 +312,10 @@ class QlmModel:
         spans, bf16-moment AdamW over the float spans, servo tick every 100 steps."""
         self.t += 1
         q = self.q
+        if self.fused:                                   # backward() has updated everything already
+            if q.servo_every > 0 and self.t % q.servo_every == 0:
+                q.servo()
+            return
         for w in self.pending:
             w.wait()
         self.pending = []
@@ -283,6 +345,8 @@ class QlmModel:
             q.servo()
 
     def train_step(self, tok, tgt, lr=3e-4):
+        if self.fused:
+            self.fused_lr = lr                           # g_fused_lr: the layers are stepped inside backward()
         self.forward(tok)
         loss = self.backward(tok, tgt)
         self.update(lr)

@@ -111,3 +111,40 @@ def test_model_file_is_loadable_by_the_reference(cuda, tmp_path):
     hdr, P = ref.model_load(path, m.o.total)
     assert list(hdr[:11]) == [256, 128, 2, 2, 2, 128, 128, 7, 0, 0, 4]
     assert (P == m.params().cpu().numpy()).all()
+
+
+def test_fused_per_layer_update_equals_the_separate_update(cuda):
+    """The fused per-layer update inside backward (CUDALM_QLM_FUSED: qlm_fused_layer / qlm_fused_tail, cudalm.cu:6105-6187;
+    one gradient block shared by all layers) against the separate update on the same model, tokens and clip multiplier:
+    every state array and every float parameter bit for bit.  (Given the multiplier: the fused form clips with the
+    PREVIOUS step's norm, so the test hands it the norm the separate update computed.)  Then a second step runs on the
+    multiplier the fused tail closed on the device."""
+    from cudalm_c_b200 import model, qlm
+    import cudalm_c_b200 as q
+    cfg = model.Config(L=3, D=128, H=2, KV=2, hd=64, E=4, K=2, F=128, V=256, T=128, B=2)
+    a = model.QlmModel(cfg, cuda, seed=5)
+    b = model.QlmModel(cfg, cuda, seed=5, fused=True)
+    assert b.G.numel() == cfg.V * cfg.D + b.layer_n + cfg.D and b.G.numel() < a.G.numel()
+    g = torch.Generator(device="cpu"); g.manual_seed(1)
+    N = cfg.B * cfg.T
+    tok = torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).to(cuda)
+    tgt = torch.randint(0, cfg.V, (N,), generator=g, dtype=torch.int32).to(cuda)
+    a.forward(tok); la = a.backward(tok, tgt); a.update(3e-4, wdf=0.0)
+    b.fgs.copy_(a.gs)                                     # this step's multiplier and norm, as if from the step before
+    b.fused_lr = 3e-4
+    b.forward(tok); lb = b.backward(tok, tgt); b.update(3e-4)
+    torch.cuda.synchronize()
+    q.check(q.lib().qlmb_check_device(None))
+    assert torch.equal(la, lb) and a.t == b.t == 1
+    for k in ("d", "r", "s", "m8", "v8", "m8s", "v8s", "Mc", "Vc"):
+        assert torch.equal(getattr(a.q, k), getattr(b.q, k)), k
+    for ta, tb in zip(a.fp, b.fp):
+        assert torch.equal(ta, tb)
+    # the norm the fused tail closed is this step's norm (slices of 64 partial sums per layer instead of 64 chunks of G)
+    assert abs(float(b.fgs[1]) - float(a.gs[1])) <= 1e-5 * float(a.gs[1])
+    assert abs(float(b.fgs[0]) - float(a.gs[0])) <= 1e-5 * float(a.gs[0])
+    r1 = b.q.r.clone()
+    b.train_step(tok, tgt, lr=3e-4)
+    torch.cuda.synchronize()
+    q.check(q.lib().qlmb_check_device(None))
+    assert b.t == 2 and not torch.equal(r1, b.q.r)
