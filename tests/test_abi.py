@@ -94,3 +94,20 @@ def test_new_entry_points_reject_bad_arguments_without_a_gpu():
     assert L.qlmb_comm_rank(None) == -1 and L.qlmb_comm_world(None) == 0
     assert L.qlmb_comm_destroy(None) == 0
     assert L.qlmb_selftest_stream_read(None, 256, 8, 1, None) == 1
+
+
+def test_header_is_plain_c_and_links_from_c(tmp_path):
+    """include/qlm_b200.h compiles as C99 with warnings as errors and a C program linked against the library runs the
+    argument-error paths (status + message, no exit) on a machine without a GPU."""
+    import shutil
+    import subprocess
+    import cudalm_c_b200
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    libdir = os.path.dirname(cudalm_c_b200.lib_path())
+    exe = str(tmp_path / "probe")
+    subprocess.check_call(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"),
+                           os.path.join(ROOT, "tests", "c_abi", "probe.c"), "-L", libdir, "-lqlm_b200", "-Wl,-rpath," + libdir, "-o", exe])
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert out.stdout.startswith("ok ")
