@@ -95,7 +95,7 @@ PROTOTYPES = {
     "qlmb_gemv_decode_norm_stack": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "qlmb_dec_qkv": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]),
     "qlmb_gemv_decode_res_norm": (ci, [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, vp]),
-    "qlmb_dec_rope": (ci, [vp, ci, vp, vp, vp, ci, ci, ci, vp]),
+    "qlmb_dec_rope": (ci, [vp, ci, vp, vp, vp, ci, ci, ci, ci, vp]),
     "qlmb_dec_kv": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, vp]),
     "qlmb_dec_attn": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]),
     "qlmb_dec_greedy": (ci, [vp, vp, vp, ci, ci, vp]),

@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(256) k_softmax_ce(const void *lg, int lg_dtype
 // ------------------------------------------------------------------ decoder (one new token per live slot)
 // k_dec_rope (cudalm.cu:7023-7027): rotate the single row of slot b by the angle of its position pos[b]
 __global__ void __launch_bounds__(256) k_dec_rope(void *buf, int dtype, const float *cosb, const float *sinb, const int *pos,
-                                                  int B, int nh, int hd)
+                                                  int B, int nh, int hd, int Tm, int *errword)
 {
     const int hf = hd / 2;
     const size_t g = (size_t)blockIdx.x * 256 + threadIdx.x;
@@ -296,6 +296,8 @@ __global__ void __launch_bounds__(256) k_dec_rope(void *buf, int dtype, const fl
     const int i = (int)(g % hf);
     const size_t r = g / hf;
     const int b = (int)(r / nh), t = pos[b];
+    // a position outside the rotation tables: reported, the row is left as it is (no table read)
+    if (t < 0 || t >= Tm) { if (i == 0 && r % nh == 0) report_bad_index(errword, 304, b, t); return; }
     const size_t o = r * hd + i;
     const float c = cosb[(size_t)t * hf + i], sn = sinb[(size_t)t * hf + i];
     const float x = blk_ld(buf, dtype, o), y = blk_ld(buf, dtype, o + hf);
@@ -726,12 +728,12 @@ extern "C" int qlmb_softmax_ce(const void *logits, int lg_dtype, const int *tgt,
 
 // ---- decoder operators (dec_step, cudalm.cu:7166-7212) ----
 extern "C" int qlmb_dec_rope(void *buf, int dtype, const float *cosb, const float *sinb, const int *pos, int B, int nh, int hd,
-                             void *stream)
+                             int Tm, void *stream)
 {
-    QLMB_REQUIRE(buf && cosb && sinb && pos && dtype_ok(dtype) && nh > 0 && hd > 0 && hd % 2 == 0, "qlmb_dec_rope: bad argument");
+    QLMB_REQUIRE(buf && cosb && sinb && pos && dtype_ok(dtype) && nh > 0 && hd > 0 && hd % 2 == 0 && Tm > 0, "qlmb_dec_rope: bad argument");
     if (B <= 0) return QLMB_OK;
     const size_t total = (size_t)B * nh * (hd / 2);
-    k_dec_rope<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(buf, dtype, cosb, sinb, pos, B, nh, hd);
+    k_dec_rope<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(buf, dtype, cosb, sinb, pos, B, nh, hd, Tm, device_error_word());
     QLMB_LAUNCH_CHECK("k_dec_rope");
     return QLMB_OK;
 }

@@ -462,8 +462,8 @@ class Decoder:
                 qh = linear.gemv_decode(a_norm, *w["wq"], KN, c.D)
                 kh = linear.gemv_decode(a_norm, *w["wk"], KN, c.KD)
                 vh = linear.gemv_decode(a_norm, *w["wv"], KN, c.KD)
-                check(L_.qlmb_dec_rope(ptr(qh), 1, ptr(self.cosb), ptr(self.sinb), ptr(self.pos), B, c.H, c.hd, stream_ptr()))
-                check(L_.qlmb_dec_rope(ptr(kh), 1, ptr(self.cosb), ptr(self.sinb), ptr(self.pos), B, c.KV, c.hd, stream_ptr()))
+                check(L_.qlmb_dec_rope(ptr(qh), 1, ptr(self.cosb), ptr(self.sinb), ptr(self.pos), B, c.H, c.hd, self.Tm, stream_ptr()))
+                check(L_.qlmb_dec_rope(ptr(kh), 1, ptr(self.cosb), ptr(self.sinb), ptr(self.pos), B, c.KV, c.hd, self.Tm, stream_ptr()))
                 check(L_.qlmb_dec_kv(ptr(self.K[l]), ptr(self.V[l]), ptr(kh), ptr(vh), ptr(self.pos), B, self.Tm, c.KD, stream_ptr()))
             att = torch.empty(B, c.D, dtype=torch.bfloat16, device=m.dev)
             check(L_.qlmb_dec_attn(ptr(att), ptr(qh), ptr(self.K[l]), ptr(self.V[l]), ptr(self.pos), 0, B, self.Tm, c.H, c.KV,

@@ -570,9 +570,10 @@ int qlmb_gemv_decode_res_norm(void *F, void *Fn, const void *X, const int8_t *co
 
 /* ---- decoder: one new token per live slot (dec_step, cudalm.cu:7166-7212) ----
  * The K/V cache of a layer is bf16 [B, Tm, KV*hd]; pos[b] (device) is the position of slot b's new token.
- * k_dec_rope (cudalm.cu:7023-7027): rotate the single row of each slot by the angle of pos[b]. */
+ * k_dec_rope (cudalm.cu:7023-7027): rotate the single row of each slot by the angle of pos[b]; the tables have Tm rows,
+ * and a slot whose position lies outside them is reported through the device error word and left unrotated. */
 int qlmb_dec_rope(void *buf, int dtype, const float *cosb, const float *sinb, const int *pos, int B, int nh, int hd,
-                  void *stream);
+                  int Tm, void *stream);
 /* k_dec_kv (cudalm.cu:7028-7030): append the new key / value rows (bf16 [B, KD]) at pos[b]. */
 int qlmb_dec_kv(void *Kc, void *Vc, const void *k, const void *v, const int *pos, int B, int Tm, int KD, void *stream);
 /* k_dec_attn (cudalm.cu:7031-7047): O[b, h*hd..] = softmax(q k^T / sqrt(hd)) v over cached positions

@@ -71,6 +71,14 @@ def test_slot_past_its_cache_is_reported_not_written(cuda):
     dec.step()                                           # the context is intact: the next step runs
     torch.cuda.synchronize()
     q.check(q.lib().qlmb_check_device(None))
+    # the stand-alone rotation has the same guard: a position outside its tables leaves the row alone and is reported
+    from cudalm_c_b200._lib import ptr, stream_ptr
+    row = torch.randn(2, cfg.D, device=cuda).to(torch.bfloat16); keep = row.clone()
+    pos = torch.tensor([3, 32], dtype=torch.int32, device=cuda)
+    q.check(q.lib().qlmb_dec_rope(ptr(row), 1, ptr(dec.cosb), ptr(dec.sinb), ptr(pos), 2, cfg.H, cfg.hd, 32, stream_ptr()))
+    torch.cuda.synchronize()
+    assert q.lib().qlmb_check_device(None) == 4 and b"error code 201" in q.lib().qlmb_last_error()
+    assert torch.equal(row[1], keep[1]) and not torch.equal(row[0], keep[0])
 
 
 def test_sampler_topk_topp_temperature(cuda):

@@ -240,7 +240,7 @@ def test_dec_qkv_equals_the_separate_kernels(cuda, B):
     Y2 = torch.empty_like(Y)
     check(lib().qlmb_gemv_decode_norm_stack(ptr(Y2), ptr(X), ptr(gamma), ptr(Q.d), ptr(Q.s), 3, B, D, D, 1, stream_ptr()))
     pos2 = torch.cat([pos, pos])
-    check(lib().qlmb_dec_rope(ptr(Y2), 1, ptr(cosb), ptr(sinb), ptr(pos2), 2 * B, H, hd, stream_ptr()))
+    check(lib().qlmb_dec_rope(ptr(Y2), 1, ptr(cosb), ptr(sinb), ptr(pos2), 2 * B, H, hd, Tm, stream_ptr()))
     Kc2 = torch.full((B, Tm, D), 7.0, dtype=torch.bfloat16, device=cuda); Vc2 = Kc2.clone()
     check(lib().qlmb_dec_kv(ptr(Kc2), ptr(Vc2), ptr(Y2[B:2 * B]), ptr(Y2[2 * B:]), ptr(pos), B, Tm, D, stream_ptr()))
     assert rel(Y, Y2) < 1e-3 and (Y == Y2).float().mean() > 0.999
